@@ -1,0 +1,319 @@
+"""Model and engine configuration.
+
+Model hyper-parameters come from a checkpoint's ``config.json`` (``from_hf``) or
+from a named preset (random-init benchmarking).  ``EngineConfig`` carries the
+serving knobs that the CLI exposes.
+
+Reference parity: pegainfer-qwen3/src/config.rs:213-262,465-506;
+pegainfer-qwen35/src/config.rs:26-215; pegainfer-deepseek-v2-lite/src/config.rs:69-190;
+pegainfer-kimi-k2/src/config.rs:16-140; pegainfer-frontend/src/model_line.rs:93-206
+(shared serving flags).
+"""
+from __future__ import annotations
+
+import json
+import math
+import os
+from dataclasses import dataclass, field, replace
+from typing import Optional
+
+
+@dataclass
+class ModelConfig:
+    family: str = "qwen3"  # qwen3 | qwen35 | deepseek_v2 | kimi_k2
+    vocab_size: int = 1024
+    hidden_size: int = 256
+    num_layers: int = 2
+    num_q_heads: int = 4
+    num_kv_heads: int = 2
+    head_dim: int = 64
+    intermediate_size: int = 768
+    rms_eps: float = 1e-6
+    rope_theta: float = 1e6
+    max_position: int = 4096
+    tie_word_embeddings: bool = False
+    eos_token_ids: tuple = ()
+    qk_norm: bool = True
+    # Qwen3.5 hybrid
+    layer_types: tuple = ()  # "linear_attention" | "full_attention" per layer
+    partial_rotary_factor: float = 1.0
+    attn_output_gate: bool = False
+    norm_weight_offset: bool = False  # (1 + w) RMSNorm
+    gdn_num_k_heads: int = 0
+    gdn_num_v_heads: int = 0
+    gdn_head_dim: int = 128
+    gdn_conv_kernel: int = 4
+    # MLA
+    q_lora_rank: int = 0
+    kv_lora_rank: int = 0
+    qk_nope_head_dim: int = 0
+    qk_rope_head_dim: int = 0
+    v_head_dim: int = 0
+    rope_scaling: Optional[dict] = None
+    # MoE
+    n_routed_experts: int = 0
+    n_shared_experts: int = 0
+    num_experts_per_tok: int = 0
+    moe_intermediate_size: int = 0
+    first_k_dense_replace: int = 0
+    scoring_func: str = "softmax"
+    n_group: int = 1
+    topk_group: int = 1
+    norm_topk_prob: bool = False
+    routed_scaling_factor: float = 1.0
+    router_bias: bool = False
+    expert_quant: str = "bf16"  # bf16 | int4_g32 | fp8_block128
+    quant_group_size: int = 32
+    # MTP
+    num_mtp_layers: int = 0
+
+    # -- derived ---------------------------------------------------------------
+    @property
+    def q_size(self) -> int:
+        return self.num_q_heads * self.head_dim
+
+    @property
+    def kv_size(self) -> int:
+        return self.num_kv_heads * self.head_dim
+
+    @property
+    def rotary_dim(self) -> int:
+        return int(self.head_dim * self.partial_rotary_factor)
+
+    @property
+    def is_mla(self) -> bool:
+        return self.kv_lora_rank > 0
+
+    @property
+    def is_moe(self) -> bool:
+        return self.n_routed_experts > 0
+
+    @property
+    def qk_head_dim(self) -> int:
+        return self.qk_nope_head_dim + self.qk_rope_head_dim
+
+    def layer_is_moe(self, i: int) -> bool:
+        return self.is_moe and i >= self.first_k_dense_replace
+
+    def layer_type(self, i: int) -> str:
+        return self.layer_types[i] if self.layer_types else "full_attention"
+
+    def mla_softmax_scale(self) -> float:
+        scale = 1.0 / math.sqrt(self.qk_head_dim)
+        rs = self.rope_scaling or {}
+        if rs.get("type", rs.get("rope_type")) == "yarn":
+            m = yarn_get_mscale(rs.get("factor", 1.0), rs.get("mscale_all_dim", 0.0))
+            scale *= m * m
+        return scale
+
+    def param_count(self) -> int:
+        """Approximate parameter count (for memory planning)."""
+        h = self.hidden_size
+        per_layer = 0
+        if self.is_mla:
+            q = (h * self.q_lora_rank + self.q_lora_rank * self.num_q_heads * self.qk_head_dim) if self.q_lora_rank else h * self.num_q_heads * self.qk_head_dim
+            kv = h * (self.kv_lora_rank + self.qk_rope_head_dim) + self.kv_lora_rank * self.num_q_heads * (self.qk_nope_head_dim + self.v_head_dim)
+            per_layer += q + kv + self.num_q_heads * self.v_head_dim * h
+        else:
+            per_layer += h * (self.q_size + 2 * self.kv_size) + self.q_size * h
+        dense = 3 * h * self.intermediate_size
+        moe = 3 * h * self.moe_intermediate_size * (self.n_routed_experts + self.n_shared_experts) + h * self.n_routed_experts
+        n_moe = max(0, self.num_layers - self.first_k_dense_replace) if self.is_moe else 0
+        total = self.num_layers * per_layer + (self.num_layers - n_moe) * dense + n_moe * moe
+        total += self.vocab_size * h * (1 if self.tie_word_embeddings else 2)
+        return total
+
+
+def yarn_get_mscale(scale: float, mscale: float) -> float:
+    """YaRN attention-scale correction (pegainfer-deepseek-v2-lite/src/host_ops.rs:377-386)."""
+    if scale <= 1.0:
+        return 1.0
+    return 0.1 * mscale * math.log(scale) + 1.0
+
+
+def _hybrid_pattern(n: int) -> tuple:
+    return tuple("full_attention" if (i + 1) % 4 == 0 else "linear_attention" for i in range(n))
+
+
+_YARN_DSV2 = {"type": "yarn", "factor": 40.0, "original_max_position_embeddings": 4096, "beta_fast": 32, "beta_slow": 1, "mscale": 0.707, "mscale_all_dim": 0.707}
+_YARN_KIMI = {"type": "yarn", "factor": 64.0, "original_max_position_embeddings": 4096, "beta_fast": 32, "beta_slow": 1, "mscale": 1.0, "mscale_all_dim": 1.0}
+
+PRESETS = {
+    "tiny-qwen3": ModelConfig(),
+    "qwen3-0.6b": ModelConfig(vocab_size=151936, hidden_size=1024, num_layers=28, num_q_heads=16, num_kv_heads=8, head_dim=128, intermediate_size=3072, max_position=40960, tie_word_embeddings=True),
+    "qwen3-4b": ModelConfig(vocab_size=151936, hidden_size=2560, num_layers=36, num_q_heads=32, num_kv_heads=8, head_dim=128, intermediate_size=9728, max_position=40960, tie_word_embeddings=True),
+    "qwen3-8b": ModelConfig(vocab_size=151936, hidden_size=4096, num_layers=36, num_q_heads=32, num_kv_heads=8, head_dim=128, intermediate_size=12288, max_position=40960),
+    "tiny-qwen35": ModelConfig(family="qwen35", vocab_size=1024, hidden_size=256, num_layers=4, num_q_heads=4, num_kv_heads=2, head_dim=64, intermediate_size=512, layer_types=_hybrid_pattern(4), partial_rotary_factor=0.25, attn_output_gate=True, norm_weight_offset=True, gdn_num_k_heads=2, gdn_num_v_heads=4, gdn_head_dim=32, rope_theta=1e7),
+    "qwen3.5-27b": ModelConfig(family="qwen35", vocab_size=248320, hidden_size=5120, num_layers=64, num_q_heads=24, num_kv_heads=4, head_dim=256, intermediate_size=17408, layer_types=_hybrid_pattern(64), partial_rotary_factor=0.25, attn_output_gate=True, norm_weight_offset=True, gdn_num_k_heads=16, gdn_num_v_heads=48, gdn_head_dim=128, rope_theta=1e7, max_position=262144),
+    "tiny-dsv2": ModelConfig(family="deepseek_v2", vocab_size=1024, hidden_size=256, num_layers=3, num_q_heads=4, num_kv_heads=4, head_dim=48, intermediate_size=512, qk_norm=False, kv_lora_rank=64, qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32, n_routed_experts=8, n_shared_experts=2, num_experts_per_tok=2, moe_intermediate_size=128, first_k_dense_replace=1, rope_theta=10000.0, rope_scaling=dict(_YARN_DSV2)),
+    "dsv2-lite": ModelConfig(family="deepseek_v2", vocab_size=102400, hidden_size=2048, num_layers=27, num_q_heads=16, num_kv_heads=16, head_dim=192, intermediate_size=10944, qk_norm=False, kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, n_routed_experts=64, n_shared_experts=2, num_experts_per_tok=6, moe_intermediate_size=1408, first_k_dense_replace=1, rope_theta=10000.0, rope_scaling=dict(_YARN_DSV2), max_position=163840),
+    "tiny-kimi": ModelConfig(family="kimi_k2", vocab_size=1024, hidden_size=256, num_layers=3, num_q_heads=4, num_kv_heads=4, head_dim=48, intermediate_size=512, qk_norm=False, q_lora_rank=96, kv_lora_rank=64, qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32, n_routed_experts=16, n_shared_experts=1, num_experts_per_tok=4, moe_intermediate_size=128, first_k_dense_replace=1, scoring_func="sigmoid", n_group=4, topk_group=2, norm_topk_prob=True, routed_scaling_factor=2.827, router_bias=True, expert_quant="int4_g32", rope_theta=50000.0, rope_scaling=dict(_YARN_KIMI), rms_eps=1e-5, num_mtp_layers=1),
+    "kimi-k2": ModelConfig(family="kimi_k2", vocab_size=163840, hidden_size=7168, num_layers=61, num_q_heads=64, num_kv_heads=64, head_dim=192, intermediate_size=18432, qk_norm=False, q_lora_rank=1536, kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, n_routed_experts=384, n_shared_experts=1, num_experts_per_tok=8, moe_intermediate_size=2048, first_k_dense_replace=1, scoring_func="sigmoid", n_group=1, topk_group=1, norm_topk_prob=True, routed_scaling_factor=2.827, router_bias=True, expert_quant="int4_g32", rope_theta=50000.0, rope_scaling=dict(_YARN_KIMI), rms_eps=1e-5, max_position=131072, num_mtp_layers=1),
+}
+
+
+def preset(name: str, **overrides) -> ModelConfig:
+    if name not in PRESETS:
+        raise KeyError(f"unknown model preset {name!r}; known: {sorted(PRESETS)}")
+    return replace(PRESETS[name], **overrides)
+
+
+def detect_family(cfg: dict) -> str:
+    """Map a ``config.json`` to a model line (exactly one line must claim it)."""
+    mt = cfg.get("model_type", "")
+    archs = " ".join(cfg.get("architectures", []))
+    if mt in ("qwen3",) or "Qwen3ForCausalLM" in archs:
+        return "qwen3"
+    if mt.startswith("qwen3_5") or mt in ("qwen3_next",) or "Qwen3_5" in archs or "Qwen3Next" in archs:
+        return "qwen35"
+    if mt == "deepseek_v2" or "DeepseekV2" in archs:
+        return "deepseek_v2"
+    if mt in ("kimi_k2", "deepseek_v3", "kimi_k25") or "DeepseekV3" in archs or "Kimi" in archs:
+        return "kimi_k2"
+    raise ValueError(f"no model line recognises model_type={mt!r} architectures={archs!r}")
+
+
+def _eos_ids(model_dir: Optional[str], cfg: dict) -> tuple:
+    ids = None
+    if model_dir:
+        p = os.path.join(model_dir, "generation_config.json")
+        if os.path.exists(p):
+            with open(p) as f:
+                ids = json.load(f).get("eos_token_id")
+    if ids is None:
+        ids = cfg.get("eos_token_id")
+    if ids is None:
+        return ()
+    if isinstance(ids, int):
+        ids = [ids]
+    return tuple(dict.fromkeys(int(i) for i in ids))
+
+
+def from_hf(cfg: dict, model_dir: Optional[str] = None) -> ModelConfig:
+    family = detect_family(cfg)
+    top = cfg
+    if family == "qwen35" and "text_config" in cfg:
+        cfg = cfg["text_config"]
+    if family == "kimi_k2" and "text_config" in cfg:
+        cfg = cfg["text_config"]
+    common = dict(
+        family=family,
+        vocab_size=cfg["vocab_size"],
+        hidden_size=cfg["hidden_size"],
+        num_layers=cfg["num_hidden_layers"],
+        num_q_heads=cfg["num_attention_heads"],
+        num_kv_heads=cfg.get("num_key_value_heads", cfg["num_attention_heads"]),
+        intermediate_size=cfg["intermediate_size"],
+        rms_eps=cfg.get("rms_norm_eps", 1e-6),
+        max_position=cfg.get("max_position_embeddings", 4096),
+        tie_word_embeddings=bool(top.get("tie_word_embeddings", cfg.get("tie_word_embeddings", False))),
+        eos_token_ids=_eos_ids(model_dir, top),
+    )
+    if family == "qwen3":
+        return ModelConfig(head_dim=cfg.get("head_dim", cfg["hidden_size"] // cfg["num_attention_heads"]), rope_theta=cfg.get("rope_theta", 1e6), **common)
+    if family == "qwen35":
+        rp = cfg.get("rope_parameters", {})
+        return ModelConfig(
+            head_dim=cfg.get("head_dim", 256),
+            rope_theta=rp.get("rope_theta", cfg.get("rope_theta", 1e7)),
+            partial_rotary_factor=rp.get("partial_rotary_factor", cfg.get("partial_rotary_factor", 0.25)),
+            layer_types=tuple(cfg["layer_types"]),
+            attn_output_gate=True,
+            norm_weight_offset=True,
+            gdn_num_k_heads=cfg["linear_num_key_heads"],
+            gdn_num_v_heads=cfg["linear_num_value_heads"],
+            gdn_head_dim=cfg.get("linear_key_head_dim", 128),
+            gdn_conv_kernel=cfg.get("linear_conv_kernel_dim", 4),
+            **common,
+        )
+    mla = dict(
+        qk_norm=False,
+        q_lora_rank=cfg.get("q_lora_rank") or 0,
+        kv_lora_rank=cfg["kv_lora_rank"],
+        qk_nope_head_dim=cfg["qk_nope_head_dim"],
+        qk_rope_head_dim=cfg["qk_rope_head_dim"],
+        v_head_dim=cfg["v_head_dim"],
+        head_dim=cfg["qk_nope_head_dim"] + cfg["qk_rope_head_dim"],
+        rope_theta=cfg.get("rope_theta", 10000.0),
+        rope_scaling=cfg.get("rope_scaling"),
+        n_routed_experts=cfg.get("n_routed_experts", 0),
+        n_shared_experts=cfg.get("n_shared_experts", 0),
+        num_experts_per_tok=cfg.get("num_experts_per_tok", 0),
+        moe_intermediate_size=cfg.get("moe_intermediate_size", 0),
+        first_k_dense_replace=cfg.get("first_k_dense_replace", 0),
+        scoring_func=cfg.get("scoring_func", "softmax"),
+        n_group=cfg.get("n_group", 1) or 1,
+        topk_group=cfg.get("topk_group", 1) or 1,
+        norm_topk_prob=bool(cfg.get("norm_topk_prob", False)),
+        routed_scaling_factor=cfg.get("routed_scaling_factor", 1.0),
+    )
+    if family == "kimi_k2":
+        q = cfg.get("quantization_config") or top.get("quantization_config") or {}
+        quant = "bf16"
+        if q.get("quant_method") == "compressed-tensors" or q.get("format") == "pack-quantized":
+            quant = "int4_g32"
+        elif q.get("quant_method") == "fp8":
+            quant = "fp8_block128"
+        mla.update(router_bias=True, expert_quant=quant, num_mtp_layers=cfg.get("num_nextn_predict_layers", 0))
+    return ModelConfig(**common, **mla)
+
+
+def load_model_config(model_dir: str) -> ModelConfig:
+    with open(os.path.join(model_dir, "config.json")) as f:
+        return from_hf(json.load(f), model_dir)
+
+
+@dataclass
+class EngineConfig:
+    """Serving knobs (one per CLI flag)."""
+
+    model_path: Optional[str] = None
+    preset: Optional[str] = None
+    served_model_name: Optional[str] = None
+    port: int = 8000
+    host: str = "127.0.0.1"
+    cuda_graph: bool = True
+    dump_graph_dot: Optional[str] = None
+    device_ordinal: int = 0
+    tp_size: int = 1
+    dp_size: int = 1
+    ep_size: int = 1
+    kv_page_size: int = 16
+    num_kv_blocks: Optional[int] = None
+    gpu_memory_utilization: float = 0.90
+    kv_cache_memory_margin_mib: int = 150
+    no_prefix_cache: bool = False
+    kv_offload: bool = False
+    kv_offload_host_gib: float = 4.0
+    max_prefill_tokens: int = 1024
+    max_decode_batch: int = 256
+    max_model_len: Optional[int] = None
+    batch_invariant: bool = False
+    decode_overlap: bool = False
+    decode_sm_pct: int = 50
+    enable_lora: bool = False
+    max_loras: int = 4
+    max_lora_rank: int = 64
+    lora_modules: tuple = ()
+    spec_method: Optional[str] = None  # None | "mtp" | "draft"
+    spec_draft_len: int = 1
+    draft_model_path: Optional[str] = None
+    comm: str = "fused"  # fused | nccl
+    gemm: str = "sm100"  # sm100 | cublas
+    seed: int = 0
+    dtype: str = "bfloat16"
+
+    def validate(self) -> None:
+        if self.kv_page_size not in (16, 32, 64):
+            raise ValueError("--kv-page-size must be 16, 32 or 64")
+        if not (0.05 <= self.gpu_memory_utilization <= 0.99):
+            raise ValueError("--gpu-memory-utilization must be in [0.05, 0.99]")
+        if self.max_prefill_tokens < 1:
+            raise ValueError("--max-prefill-tokens must be positive")
+        if self.comm not in ("fused", "nccl"):
+            raise ValueError("--comm must be fused or nccl")
+        if self.gemm not in ("sm100", "cublas"):
+            raise ValueError("--gemm must be sm100 or cublas")
+        for n in ("tp_size", "dp_size", "ep_size"):
+            if getattr(self, n) < 1:
+                raise ValueError(f"--{n.replace('_', '-')} must be >= 1")

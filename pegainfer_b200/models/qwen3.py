@@ -1,0 +1,151 @@
+"""Qwen3 dense decoder (GQA, per-head QK-RMSNorm, half-split RoPE, SwiGLU).
+
+Weights are held per tensor-parallel rank: ``qkv`` is the row-concatenation
+``[q_rows; k_rows; v_rows]`` of this rank's head shards, ``gate_up`` is
+``[gate_rows; up_rows]`` of its FFN shard, ``o``/``down`` are column shards;
+embedding, lm_head and norms are replicated.  The forward pass consumes one ragged
+step (prefill chunks and decode rows mixed) described by an ``AttnMeta``.
+
+Reference parity: pegainfer-qwen3/src/weights/load.rs:61-286 (tensor names, fused
+qkv / gate_up, TP shard ranges, tied embeddings), src/batch_decode.rs:184-399 and
+src/prefill.rs:206-490 (layer op order), src/unified_forward.rs:138-613 (mixed step).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+
+from .. import ops
+from ..config import ModelConfig
+from ..loader.sources import RandomSource, WeightSource, shard_range
+from ..ops.reference import AttnMeta, rope_tables
+from ..parallel.tp import SINGLE, TPContext
+
+
+def qwen3_shapes(cfg: ModelConfig) -> dict:
+    """HF tensor names -> full (unsharded) shapes."""
+    h, d = cfg.hidden_size, cfg.head_dim
+    s = {"model.embed_tokens.weight": (cfg.vocab_size, h), "model.norm.weight": (h,)}
+    if not cfg.tie_word_embeddings:
+        s["lm_head.weight"] = (cfg.vocab_size, h)
+    for i in range(cfg.num_layers):
+        p = f"model.layers.{i}."
+        s[p + "input_layernorm.weight"] = (h,)
+        s[p + "post_attention_layernorm.weight"] = (h,)
+        s[p + "self_attn.q_proj.weight"] = (cfg.num_q_heads * d, h)
+        s[p + "self_attn.k_proj.weight"] = (cfg.num_kv_heads * d, h)
+        s[p + "self_attn.v_proj.weight"] = (cfg.num_kv_heads * d, h)
+        s[p + "self_attn.o_proj.weight"] = (h, cfg.num_q_heads * d)
+        s[p + "self_attn.q_norm.weight"] = (d,)
+        s[p + "self_attn.k_norm.weight"] = (d,)
+        s[p + "mlp.gate_proj.weight"] = (cfg.intermediate_size, h)
+        s[p + "mlp.up_proj.weight"] = (cfg.intermediate_size, h)
+        s[p + "mlp.down_proj.weight"] = (h, cfg.intermediate_size)
+    return s
+
+
+@dataclass
+class Qwen3Layer:
+    input_norm: torch.Tensor
+    qkv: torch.Tensor
+    q_norm: torch.Tensor
+    k_norm: torch.Tensor
+    o: torch.Tensor
+    post_norm: torch.Tensor
+    gate_up: torch.Tensor
+    down: torch.Tensor
+
+
+class Qwen3Model:
+    family = "qwen3"
+
+    def __init__(self, cfg: ModelConfig, source: Optional[WeightSource] = None, device="cpu", dtype=torch.bfloat16, tp: TPContext = SINGLE, seed: int = 0):
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.tp = tp
+        if cfg.num_q_heads % tp.world or cfg.num_kv_heads % tp.world or cfg.intermediate_size % tp.world:
+            raise ValueError(f"heads {cfg.num_q_heads}/{cfg.num_kv_heads} and FFN {cfg.intermediate_size} must divide tp={tp.world}")
+        self.q_heads = cfg.num_q_heads // tp.world
+        self.kv_heads = cfg.num_kv_heads // tp.world
+        source = source or RandomSource(qwen3_shapes(cfg), seed=seed, dtype=dtype)
+        self._load(source)
+        self.cos, self.sin = rope_tables(cfg.max_position, cfg.rotary_dim, cfg.rope_theta, dtype, self.device)
+
+    # -- loading ---------------------------------------------------------------
+    def _load(self, src: WeightSource) -> None:
+        cfg, dev, dt, tp = self.cfg, self.device, self.dtype, self.tp
+        d = cfg.head_dim
+        self.embed = src.get("model.embed_tokens.weight", dev, dt)
+        self.lm_head = self.embed if cfg.tie_word_embeddings else src.get("lm_head.weight", dev, dt)
+        self.final_norm = src.get("model.norm.weight", dev, dt)
+        qr = shard_range(cfg.num_q_heads, tp.rank, tp.world)
+        kr = shard_range(cfg.num_kv_heads, tp.rank, tp.world)
+        fr = shard_range(cfg.intermediate_size, tp.rank, tp.world)
+        self.layers = []
+        for i in range(cfg.num_layers):
+            p = f"model.layers.{i}."
+            q = src.get(p + "self_attn.q_proj.weight", dev, dt, rows=(qr[0] * d, qr[1] * d))
+            k = src.get(p + "self_attn.k_proj.weight", dev, dt, rows=(kr[0] * d, kr[1] * d))
+            v = src.get(p + "self_attn.v_proj.weight", dev, dt, rows=(kr[0] * d, kr[1] * d))
+            g = src.get(p + "mlp.gate_proj.weight", dev, dt, rows=fr)
+            u = src.get(p + "mlp.up_proj.weight", dev, dt, rows=fr)
+            self.layers.append(
+                Qwen3Layer(
+                    input_norm=src.get(p + "input_layernorm.weight", dev, dt),
+                    qkv=torch.cat([q, k, v], 0),
+                    q_norm=src.get(p + "self_attn.q_norm.weight", dev, dt),
+                    k_norm=src.get(p + "self_attn.k_norm.weight", dev, dt),
+                    o=src.get(p + "self_attn.o_proj.weight", dev, dt, cols=(qr[0] * d, qr[1] * d)),
+                    post_norm=src.get(p + "post_attention_layernorm.weight", dev, dt),
+                    gate_up=torch.cat([g, u], 0),
+                    down=src.get(p + "mlp.down_proj.weight", dev, dt, cols=fr),
+                )
+            )
+            del q, k, v, g, u
+
+    def weight_bytes(self) -> int:
+        n = self.embed.numel() + self.final_norm.numel()
+        if self.lm_head is not self.embed:
+            n += self.lm_head.numel()
+        for l in self.layers:
+            n += sum(t.numel() for t in (l.input_norm, l.qkv, l.q_norm, l.k_norm, l.o, l.post_norm, l.gate_up, l.down))
+        return n * self.embed.element_size()
+
+    # -- KV geometry -----------------------------------------------------------
+    def kv_geometry(self) -> dict:
+        return dict(num_layers=self.cfg.num_layers, kv_heads=self.kv_heads, head_dim=self.cfg.head_dim)
+
+    # -- forward -----------------------------------------------------------------
+    def forward_hidden(self, token_ids: torch.Tensor, meta: AttnMeta, kv, aux_layers=()) -> torch.Tensor:
+        """Returns final-normed hidden states ``[T, hidden]`` for every input row.
+        ``aux_layers``: layer indices whose residual-stream output is captured into
+        ``self.last_aux`` (speculative drafters consume target hidden states)."""
+        cfg, tp = self.cfg, self.tp
+        eps = cfg.rms_eps
+        residual = ops.embedding(token_ids, self.embed)
+        x = ops.rms_norm(residual, self.layers[0].input_norm, eps)
+        aux = []
+        n = len(self.layers)
+        for i, l in enumerate(self.layers):
+            qkv = ops.linear(x, l.qkv)
+            q = ops.qk_norm_rope_append(qkv, l.q_norm, l.k_norm, self.cos, self.sin, meta, kv.layer(i), self.q_heads, self.kv_heads, cfg.head_dim, eps)
+            a = ops.paged_attention(q, kv.layer(i), meta)
+            x = tp.row_linear_add_norm(a, l.o, residual, l.post_norm, eps)
+            act = ops.swiglu(ops.linear(x, l.gate_up))
+            next_norm = self.layers[i + 1].input_norm if i + 1 < n else self.final_norm
+            x = tp.row_linear_add_norm(act, l.down, residual, next_norm, eps)
+            if i in aux_layers:
+                aux.append(residual.clone())
+        self.last_aux = aux
+        return x
+
+    def logits(self, hidden: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if rows is not None:
+            hidden = ops.gather_rows(hidden, rows)
+        return ops.linear(hidden, self.lm_head)
+
+    def forward(self, token_ids, meta, kv, logits_rows=None):
+        return self.logits(self.forward_hidden(token_ids, meta, kv), logits_rows)

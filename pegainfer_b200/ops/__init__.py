@@ -1,0 +1,108 @@
+"""Op entry points used by every model.
+
+CUDA tensors run the hand-written sm_100a kernels (``ops.cuda``); CPU tensors run the
+PyTorch restatement (``ops.reference``).  ``set_mode("library")`` sends CUDA tensors
+through PyTorch/cuBLAS instead: that is the comparison arm (the reference's
+GEMM -> collective -> norm decomposition on vendor libraries), never a silent
+fallback: with mode ``sm100`` a missing extension raises.
+"""
+from __future__ import annotations
+
+import contextlib
+
+from . import reference
+from .reference import AttnMeta  # noqa: F401
+
+_MODE = "sm100"  # sm100 | library
+
+
+def set_mode(mode: str) -> None:
+    global _MODE
+    if mode not in ("sm100", "library"):
+        raise ValueError("mode must be 'sm100' or 'library'")
+    _MODE = mode
+
+
+def get_mode() -> str:
+    return _MODE
+
+
+@contextlib.contextmanager
+def mode(m: str):
+    prev = _MODE
+    set_mode(m)
+    try:
+        yield
+    finally:
+        set_mode(prev)
+
+
+def _impl(t):
+    if t.is_cuda and _MODE == "sm100":
+        from . import cuda
+
+        return cuda
+    return reference
+
+
+def embedding(ids, table):
+    return _impl(table).embedding(ids, table)
+
+
+def rms_norm(x, w, eps, offset=False):
+    return _impl(x).rms_norm(x, w, eps, offset)
+
+
+def add_rms_norm(x, residual, w, eps, offset=False, round_before_norm=True):
+    return _impl(x).add_rms_norm(x, residual, w, eps, offset, round_before_norm)
+
+
+def gated_rms_norm(x, gate, w, eps):
+    return _impl(x).gated_rms_norm(x, gate, w, eps)
+
+
+def swiglu(gate_up):
+    return _impl(gate_up).swiglu(gate_up)
+
+
+def linear(x, w, out_dtype=None):
+    return _impl(x).linear(x, w, out_dtype)
+
+
+def gather_rows(x, idx):
+    return _impl(x).gather_rows(x, idx)
+
+
+def qk_norm_rope_append(qkv, q_norm_w, k_norm_w, cos, sin, meta, kv_layer, num_q_heads, num_kv_heads, head_dim, eps, offset=False, gated=False):
+    return _impl(qkv).qk_norm_rope_append(qkv, q_norm_w, k_norm_w, cos, sin, meta, kv_layer, num_q_heads, num_kv_heads, head_dim, eps, offset, gated)
+
+
+def paged_attention(q, kv_layer, meta, scale=None, window=0):
+    return _impl(q).paged_attention(q, kv_layer, meta, scale, window)
+
+
+def argmax(logits):
+    return _impl(logits).argmax(logits)
+
+
+def sample(logits, temperature, top_k, top_p, min_p, u):
+    return _impl(logits).sample(logits, temperature, top_k, top_p, min_p, u)
+
+
+def logprobs_topk(logits, picked, k):
+    return _impl(logits).logprobs_topk(logits, picked, k)
+
+
+def __getattr__(name):
+    # ops added by later model families (MLA, MoE, GDN) resolve lazily
+    if hasattr(reference, name):
+        def _dispatch(*args, **kwargs):
+            import torch
+
+            first = next((a for a in args if isinstance(a, torch.Tensor)), None)
+            impl = _impl(first) if first is not None else reference
+            fn = getattr(impl, name, None) or getattr(reference, name)
+            return fn(*args, **kwargs)
+
+        return _dispatch
+    raise AttributeError(name)

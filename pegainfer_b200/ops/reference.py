@@ -1,0 +1,306 @@
+"""Plain PyTorch restatement of every op (oracle for the CUDA kernels, CPU path,
+and the library-backed comparison arm on GPU).
+
+Rounding points are explicit: intermediate results are rounded to the activation
+dtype exactly where the CUDA kernels round, so kernel tests can use tight bounds.
+All activations are token-major ``[tokens, features]``; weights are ``[out, in]``.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+
+# ----------------------------------------------------------------------------------
+# metadata shared by reference and CUDA attention paths
+# ----------------------------------------------------------------------------------
+@dataclass
+class AttnMeta:
+    """One step's ragged batch description.
+
+    ``q_indptr[b]..q_indptr[b+1]`` are the query rows of sequence ``b``;
+    ``kv_lens[b]`` is its KV length *after* this step's append; its pages are
+    ``block_table[b, :ceil(kv_lens[b] / page_size)]``.  ``slot_mapping[t]`` is the
+    flat KV slot (``page * page_size + offset``) where row ``t`` is appended.
+    Padding sequences (CUDA-graph buckets) have ``kv_lens == 0``: they point at
+    page 0, attend to nothing and produce zeros.
+    """
+
+    q_indptr: torch.Tensor  # int32 [B+1]
+    kv_lens: torch.Tensor  # int32 [B]
+    block_table: torch.Tensor  # int32 [B, W]
+    slot_mapping: torch.Tensor  # int32 [T]
+    positions: torch.Tensor  # int32 [T]
+    page_size: int
+    num_seqs: int
+    num_tokens: int
+    max_q_len: int
+    max_kv_len: int
+    decode_only: bool = False
+    # host copies (the reference path and planners read these; no device sync)
+    h_q_indptr: Optional[list] = None
+    h_kv_lens: Optional[list] = None
+    # per-step scratch planned by the CUDA path (split-KV partials etc.)
+    plan: Optional[object] = None
+
+
+# ----------------------------------------------------------------------------------
+# elementwise / norms
+# ----------------------------------------------------------------------------------
+def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    return table[ids.long()]
+
+
+def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float, offset: bool = False) -> torch.Tensor:
+    xf = x.float()
+    inv = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    wf = w.float() + 1.0 if offset else w.float()
+    return (xf * inv * wf).to(x.dtype)
+
+
+def add_rms_norm(x, residual, w, eps, offset=False, round_before_norm=True):
+    """``residual += x`` (in place); returns ``rms_norm(residual)``.
+
+    With ``round_before_norm`` the sum is rounded to the activation dtype before the
+    mean-square reduction (what the norm then sees is exactly the stored residual);
+    otherwise the reduction uses the unrounded fp32 sum.
+    """
+    s = x.float() + residual.float()
+    residual.copy_(s.to(residual.dtype))
+    src = residual.float() if round_before_norm else s
+    inv = torch.rsqrt(src.pow(2).mean(-1, keepdim=True) + eps)
+    wf = w.float() + 1.0 if offset else w.float()
+    return (src * inv * wf).to(x.dtype)
+
+
+def gated_rms_norm(x, gate, w, eps):
+    """Per-head ``rms_norm(x, w_f32) * silu(gate)``; x, gate: [T, H, D]."""
+    xf = x.float()
+    inv = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    g = gate.float()
+    return (xf * inv * w.float() * (g * torch.sigmoid(g))).to(x.dtype)
+
+
+def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    """``round(silu(gate)) * up`` on a fused ``[T, 2I]`` buffer (gate first)."""
+    i = gate_up.shape[-1] // 2
+    g = gate_up[..., :i].float()
+    u = gate_up[..., i:].float()
+    s = (g * torch.sigmoid(g)).to(gate_up.dtype).float()
+    return (s * u).to(gate_up.dtype)
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype=None) -> torch.Tensor:
+    if x.device.type == "cpu" and x.dtype == torch.bfloat16:
+        y = x.float() @ w.float().t()
+    else:
+        y = F.linear(x, w)
+    return y.to(out_dtype or x.dtype)
+
+
+def gather_rows(x: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+    return x[idx.long()]
+
+
+# ----------------------------------------------------------------------------------
+# RoPE
+# ----------------------------------------------------------------------------------
+def rope_tables(max_pos: int, rotary_dim: int, theta: float, dtype=torch.bfloat16, device="cpu", scaling: Optional[dict] = None):
+    """cos/sin tables ``[max_pos, rotary_dim/2]`` stored in the activation dtype
+    (pegainfer-core/src/rope.rs:46-90 keeps them in bf16)."""
+    half = rotary_dim // 2
+    inv_freq = 1.0 / (theta ** (torch.arange(0, half, dtype=torch.float64) * 2.0 / rotary_dim))
+    mscale = 1.0
+    if scaling and scaling.get("type", scaling.get("rope_type")) == "yarn":
+        inv_freq, mscale = _yarn_inv_freq(inv_freq, rotary_dim, theta, scaling)
+    t = torch.arange(max_pos, dtype=torch.float64)
+    ang = torch.outer(t, inv_freq)
+    cos = (ang.cos() * mscale).to(torch.float32).to(dtype).to(device)
+    sin = (ang.sin() * mscale).to(torch.float32).to(dtype).to(device)
+    return cos, sin
+
+
+def _yarn_inv_freq(inv_freq, dim, theta, sc):
+    from ..config import yarn_get_mscale
+
+    factor = sc["factor"]
+    orig = sc.get("original_max_position_embeddings", 4096)
+    beta_fast, beta_slow = sc.get("beta_fast", 32), sc.get("beta_slow", 1)
+
+    def corr_dim(rot):
+        return (dim * math.log(orig / (rot * 2 * math.pi))) / (2 * math.log(theta))
+
+    low = max(math.floor(corr_dim(beta_fast)), 0)
+    high = min(math.ceil(corr_dim(beta_slow)), dim - 1)
+    if low == high:
+        high += 0.001
+    ramp = ((torch.arange(dim // 2, dtype=torch.float64) - low) / (high - low)).clamp(0, 1)
+    mask = 1.0 - ramp
+    inv = inv_freq / factor * (1 - mask) + inv_freq * mask
+    mscale = yarn_get_mscale(factor, sc.get("mscale", 1.0)) / yarn_get_mscale(factor, sc.get("mscale_all_dim", 0.0))
+    return inv, mscale
+
+
+def _rope_half(x, cos, sin):
+    """Half-split rotation of the first ``2*cos.shape[-1]`` dims of x [T,H,D]."""
+    r = cos.shape[-1] * 2
+    xr = x[..., :r].float()
+    x1, x2 = xr[..., : r // 2], xr[..., r // 2 :]
+    c, s = cos.float().unsqueeze(1), sin.float().unsqueeze(1)
+    o1 = (x1 * c - x2 * s).to(x.dtype)
+    o2 = (x2 * c + x1 * s).to(x.dtype)
+    return torch.cat([o1, o2, x[..., r:]], dim=-1)
+
+
+def _rope_interleaved_in(x, cos, sin):
+    """Input pairs ``(x[2i], x[2i+1])``, output half-split (DeepSeek convention)."""
+    xf = x.float()
+    x1, x2 = xf[..., 0::2], xf[..., 1::2]
+    c, s = cos.float().unsqueeze(1), sin.float().unsqueeze(1)
+    o1 = (x1 * c - x2 * s).to(x.dtype)
+    o2 = (x2 * c + x1 * s).to(x.dtype)
+    return torch.cat([o1, o2], dim=-1)
+
+
+def qk_norm_rope_append(qkv, q_norm_w, k_norm_w, cos, sin, meta: AttnMeta, kv_layer, num_q_heads, num_kv_heads, head_dim, eps, offset=False, gated=False):
+    """Split fused qkv rows, per-head RMSNorm on q/k (optional), rotate, append k/v
+    to the paged cache.  Returns ``q [T, Hq, D]`` (and ``gate [T, Hq, D]`` if gated:
+    q_proj rows are then per-head ``[q(D), gate(D)]``)."""
+    t = qkv.shape[0]
+    qw = num_q_heads * head_dim * (2 if gated else 1)
+    q = qkv[:, :qw]
+    k = qkv[:, qw : qw + num_kv_heads * head_dim].reshape(t, num_kv_heads, head_dim)
+    v = qkv[:, qw + num_kv_heads * head_dim :].reshape(t, num_kv_heads, head_dim)
+    gate = None
+    if gated:
+        qg = q.reshape(t, num_q_heads, 2, head_dim)
+        q, gate = qg[:, :, 0], qg[:, :, 1].contiguous()
+    else:
+        q = q.reshape(t, num_q_heads, head_dim)
+    if q_norm_w is not None:
+        q = rms_norm(q, q_norm_w, eps, offset)
+        k = rms_norm(k, k_norm_w, eps, offset)
+    pos = meta.positions.long()
+    c, s = cos[pos], sin[pos]
+    q = _rope_half(q, c, s)
+    k = _rope_half(k, c, s)
+    ps = meta.page_size
+    slots = meta.slot_mapping.long()
+    kv_layer[slots // ps, 0, slots % ps] = k
+    kv_layer[slots // ps, 1, slots % ps] = v
+    return (q.contiguous(), gate) if gated else q.contiguous()
+
+
+# ----------------------------------------------------------------------------------
+# attention
+# ----------------------------------------------------------------------------------
+def _gather_kv(kv_layer, pages, kv_len, page_size):
+    k = kv_layer[pages, 0].reshape(-1, kv_layer.shape[-2], kv_layer.shape[-1])[:kv_len]
+    v = kv_layer[pages, 1].reshape(-1, kv_layer.shape[-2], kv_layer.shape[-1])[:kv_len]
+    return k, v
+
+
+def paged_attention(q, kv_layer, meta: AttnMeta, scale: Optional[float] = None, window: int = 0):
+    """Causal GQA attention of ragged query rows over paged KV.  q: [T, Hq, D]."""
+    t, hq, d = q.shape
+    hkv = kv_layer.shape[-2]
+    group = hq // hkv
+    scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    out = torch.empty_like(q)
+    qi = meta.h_q_indptr if meta.h_q_indptr is not None else meta.q_indptr.tolist()
+    kl = meta.h_kv_lens if meta.h_kv_lens is not None else meta.kv_lens.tolist()
+    ps = meta.page_size
+    for b in range(meta.num_seqs):
+        q0, q1 = qi[b], qi[b + 1]
+        if q1 == q0:
+            continue
+        if kl[b] == 0:
+            out[q0:q1] = 0
+            continue
+        pages = meta.block_table[b, : (kl[b] + ps - 1) // ps].long()
+        k, v = _gather_kv(kv_layer, pages, kl[b], meta.page_size)
+        qb = q[q0:q1].float()  # [n, Hq, D]
+        kf = k.float().repeat_interleave(group, dim=1)
+        vf = v.float().repeat_interleave(group, dim=1)
+        s = torch.einsum("qhd,khd->hqk", qb, kf) * scale
+        n = q1 - q0
+        qpos = torch.arange(kl[b] - n, kl[b], device=q.device).view(1, n, 1)
+        kpos = torch.arange(kl[b], device=q.device).view(1, 1, -1)
+        mask = kpos <= qpos
+        if window > 0:
+            mask = mask & (kpos > qpos - window)
+        s = s.masked_fill(~mask, float("-inf"))
+        p = torch.softmax(s, dim=-1)
+        out[q0:q1] = torch.einsum("hqk,khd->qhd", p, vf).to(q.dtype)
+    return out.reshape(t, hq * d)
+
+
+def dense_causal_attention(q, k, v, scale=None):
+    """Unpaged oracle: q [T,Hq,D], k/v [T,Hkv,D], one sequence, causal."""
+    t, hq, d = q.shape
+    group = hq // k.shape[1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    kf = k.float().repeat_interleave(group, dim=1)
+    vf = v.float().repeat_interleave(group, dim=1)
+    s = torch.einsum("qhd,khd->hqk", q.float(), kf) * scale
+    mask = torch.tril(torch.ones(t, t, dtype=torch.bool, device=q.device))
+    s = s.masked_fill(~mask, float("-inf"))
+    return torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), vf).to(q.dtype)
+
+
+# ----------------------------------------------------------------------------------
+# sampling
+# ----------------------------------------------------------------------------------
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    """Row-wise argmax; ties resolve to the lowest index."""
+    lf = logits.float()
+    m = lf.max(dim=-1, keepdim=True).values
+    idx = torch.arange(lf.shape[-1], device=lf.device).expand_as(lf)
+    big = torch.full_like(idx, lf.shape[-1])
+    return torch.where(lf == m, idx, big).min(dim=-1).values.to(torch.int32)
+
+
+def filtered_probs(logits, temperature, top_k, top_p, min_p):
+    """Temperature softmax followed by top-k, top-p and min-p filtering, renormalised.
+    All controls are per-row tensors."""
+    lf = logits.float() / temperature.clamp_min(1e-6).unsqueeze(-1)
+    probs = torch.softmax(lf, dim=-1)
+    sp, si = probs.sort(dim=-1, descending=True)
+    v = probs.shape[-1]
+    rank = torch.arange(v, device=probs.device).unsqueeze(0)
+    k = torch.where(top_k > 0, top_k, torch.full_like(top_k, v)).unsqueeze(-1)
+    keep = rank < k
+    csum = sp.cumsum(-1)
+    keep &= (csum - sp) < top_p.unsqueeze(-1)
+    keep &= sp >= (min_p.unsqueeze(-1) * sp[:, :1])
+    keep[:, 0] = True
+    sp = sp * keep
+    out = torch.zeros_like(probs).scatter_(-1, si, sp)
+    return out / out.sum(-1, keepdim=True)
+
+
+def logprobs_topk(logits, picked, k):
+    lp = torch.log_softmax(logits.float(), dim=-1)
+    chosen = lp.gather(-1, picked.long().unsqueeze(-1)).squeeze(-1)
+    if k > 0:
+        tv, ti = lp.topk(k, dim=-1)
+    else:
+        tv = ti = None
+    return chosen, tv, ti
+
+
+def sample(logits, temperature, top_k, top_p, min_p, u):
+    """Inverse-CDF draw (in vocabulary order) from the filtered distribution using
+    one uniform ``u`` per row.  Deterministic given ``u``."""
+    probs = filtered_probs(logits, temperature, top_k, top_p, min_p)
+    cdf = probs.double().cumsum(-1)
+    target = (u.double() * cdf[:, -1]).unsqueeze(-1)
+    idx = (cdf <= target).sum(-1).clamp_max(probs.shape[-1] - 1)
+    # never return a filtered-out token because of rounding at the tail
+    ok = probs.gather(-1, idx.unsqueeze(-1)).squeeze(-1) > 0
+    fallback = probs.argmax(-1)
+    return torch.where(ok, idx, fallback).to(torch.int32)

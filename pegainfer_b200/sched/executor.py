@@ -1,0 +1,219 @@
+"""Step batches and the model executor.
+
+The scheduler decides *what* runs (which requests, how many tokens, which pages);
+the executor turns one :class:`StepBatch` into device tensors, runs the model and
+the sampler, and returns one :class:`StepResult`.  Pure-decode batches replay a
+CUDA graph captured per batch bucket: inputs live in pointer-stable buffers and
+padding rows point at page 0.
+
+Reference parity: pegainfer-qwen3/src/executor.rs:2467-2603 (execute_prefill /
+execute_decode), src/batch_decode.rs:62-182 (bucket padding, graph replay),
+src/batch_decode_buffers.rs:26-200 (bucket list, pointer-stable buffers),
+src/scheduler/test_support.rs:27-289 (FakeExecutor for scheduler tests).
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..engine.contract import SamplingParams
+from ..kv.request_kv import KvView
+from ..ops.reference import AttnMeta
+from ..sample.select import batch_logprobs, select_batch
+
+DECODE_BUCKETS = tuple(list(range(1, 9)) + list(range(10, 33, 2)) + list(range(36, 65, 4)) + list(range(72, 129, 8)) + list(range(144, 257, 16)))
+
+
+def bucket_for(n: int, buckets: Sequence[int] = DECODE_BUCKETS) -> int:
+    for b in buckets:
+        if b >= n:
+            return b
+    raise ValueError(f"batch {n} exceeds the largest decode bucket {buckets[-1]}")
+
+
+@dataclass
+class SeqStep:
+    rid: int
+    input_tokens: list
+    start_pos: int
+    view: KvView
+    sample: bool = True
+    params: SamplingParams = field(default_factory=SamplingParams)
+    step_index: int = 0
+    logprobs: int = 0
+    all_rows: bool = False  # speculative verify: a token for every input row
+    lora_slot: int = -1
+    state_slot: int = -1  # recurrent-state slot (hybrid models)
+    fresh_state: bool = False
+
+
+@dataclass
+class StepBatch:
+    seqs: list
+    kind: str = "unified"  # prefill | decode | unified | verify
+
+    @property
+    def num_tokens(self) -> int:
+        return sum(len(s.input_tokens) for s in self.seqs)
+
+    def is_decode(self) -> bool:
+        return all(len(s.input_tokens) == 1 for s in self.seqs)
+
+
+@dataclass
+class StepResult:
+    tokens: dict = field(default_factory=dict)  # rid -> [token, ...]
+    logprobs: dict = field(default_factory=dict)  # rid -> [TokenLogprob, ...]
+    elapsed_s: float = 0.0
+
+
+class ModelExecutor:
+    """Interface the scheduler drives."""
+
+    vocab_size: int = 0
+
+    def execute(self, batch: StepBatch) -> StepResult:
+        raise NotImplementedError
+
+    def release_request(self, rid: int) -> None:
+        """Forget per-request executor state (recurrent slots, LoRA pins)."""
+
+
+def build_meta(seqs: Sequence[SeqStep], page_size: int, device, pad_to: int = 0, table_width: int = 0, pinned: bool = False):
+    """Flatten a list of per-sequence steps into ``(token_ids, AttnMeta)``."""
+    n = len(seqs)
+    b = max(n, pad_to)
+    q_indptr = np.zeros(b + 1, dtype=np.int32)
+    kv_lens = np.zeros(b, dtype=np.int32)
+    width = max([len(s.view.page_indices) for s in seqs] + [1, table_width])
+    table = np.zeros((b, width), dtype=np.int32)
+    toks, pos, slots = [], [], []
+    max_q = max_kv = 0
+    for i, s in enumerate(seqs):
+        nt = len(s.input_tokens)
+        q_indptr[i + 1] = q_indptr[i] + nt
+        kv_lens[i] = s.start_pos + nt
+        pages = s.view.page_indices
+        table[i, : len(pages)] = pages
+        toks.extend(s.input_tokens)
+        p = np.arange(s.start_pos, s.start_pos + nt, dtype=np.int64)
+        pos.append(p)
+        pg = np.asarray(pages, dtype=np.int64)
+        slots.append(pg[p // page_size] * page_size + p % page_size)
+        max_q = max(max_q, nt)
+        max_kv = max(max_kv, s.start_pos + nt)
+    t_real = int(q_indptr[n])
+    # padding sequences: one row each, zero KV, slot in page 0
+    for i in range(n, b):
+        q_indptr[i + 1] = q_indptr[i] + 1
+    t = int(q_indptr[b])
+    tok = np.zeros(t, dtype=np.int32)
+    tok[:t_real] = toks
+    posa = np.zeros(t, dtype=np.int32)
+    slota = np.zeros(t, dtype=np.int32)
+    if t_real:
+        posa[:t_real] = np.concatenate(pos)
+        slota[:t_real] = np.concatenate(slots)
+
+    def dev(a):
+        x = torch.from_numpy(a)
+        if torch.device(device).type == "cuda":
+            return x.pin_memory().to(device, non_blocking=True) if pinned else x.to(device)
+        return x
+
+    meta = AttnMeta(
+        q_indptr=dev(q_indptr),
+        kv_lens=dev(kv_lens),
+        block_table=dev(table),
+        slot_mapping=dev(slota),
+        positions=dev(posa),
+        page_size=page_size,
+        num_seqs=b,
+        num_tokens=t,
+        max_q_len=max(max_q, 1),
+        max_kv_len=max_kv,
+        decode_only=(max_q <= 1),
+        h_q_indptr=q_indptr.tolist(),
+        h_kv_lens=kv_lens.tolist(),
+    )
+    return dev(tok), meta
+
+
+class TorchExecutor(ModelExecutor):
+    """Runs a model object exposing ``forward_hidden`` / ``logits`` on CPU or GPU."""
+
+    def __init__(self, model, kv, page_size: int, cuda_graph: bool = False, max_decode_batch: int = 256, max_blocks_per_seq: int = 0, seed: int = 0):
+        self.model = model
+        self.kv = kv
+        self.page_size = page_size
+        self.device = model.device
+        self.vocab_size = model.cfg.vocab_size
+        self.seed = seed
+        self.steps = 0
+        self.use_graph = bool(cuda_graph) and self.device.type == "cuda"
+        self.max_decode_batch = max_decode_batch
+        self.max_blocks_per_seq = max_blocks_per_seq
+        self._graphs = None
+        if self.use_graph:
+            from ..utils.cuda_graph import DecodeGraphs
+
+            self._graphs = DecodeGraphs(self, max_decode_batch, max_blocks_per_seq)
+
+    # -- sampling ----------------------------------------------------------------
+    def _sample(self, logits, seqs, rows_per_seq):
+        params, steps = [], []
+        for s, nrows in zip(seqs, rows_per_seq):
+            for j in range(nrows):
+                params.append(s.params)
+                steps.append(s.step_index + j)
+        toks = select_batch(logits, params, steps, base_seed=self.seed + self.steps)
+        want_lp = max((s.logprobs for s in seqs), default=0)
+        lps = None
+        if any(s.logprobs > 0 for s in seqs):
+            lps = batch_logprobs(logits, toks, want_lp)
+        return toks, lps
+
+    def execute(self, batch: StepBatch) -> StepResult:
+        t0 = time.perf_counter()
+        self.steps += 1
+        seqs = batch.seqs
+        if self._graphs is not None and batch.is_decode() and len(seqs) <= self.max_decode_batch and all(s.sample and s.logprobs == 0 for s in seqs):
+            all_greedy = all(s.params.effectively_greedy(self.vocab_size) for s in seqs)
+            out = self._graphs.run(seqs, greedy=all_greedy)
+            if all_greedy:
+                toks = out.tolist()
+            else:
+                toks, _ = self._sample(out[: len(seqs)], seqs, [1] * len(seqs))
+                toks = toks.tolist()
+            return StepResult(tokens={s.rid: [toks[i]] for i, s in enumerate(seqs)}, elapsed_s=time.perf_counter() - t0)
+        token_ids, meta = build_meta(seqs, self.page_size, self.device)
+        hidden = self.model.forward_hidden(token_ids, meta, self.kv)
+        # rows that need logits
+        rows, rows_per_seq, sample_seqs = [], [], []
+        for i, s in enumerate(seqs):
+            if not s.sample:
+                continue
+            q0, q1 = meta.h_q_indptr[i], meta.h_q_indptr[i + 1]
+            r = list(range(q0, q1)) if s.all_rows else [q1 - 1]
+            rows.extend(r)
+            rows_per_seq.append(len(r))
+            sample_seqs.append(s)
+        res = StepResult()
+        if rows:
+            idx = torch.tensor(rows, dtype=torch.int32, device=self.device)
+            logits = self.model.logits(hidden, idx)
+            toks, lps = self._sample(logits, sample_seqs, rows_per_seq)
+            toks = toks.tolist()
+            k = 0
+            for s, nrows in zip(sample_seqs, rows_per_seq):
+                res.tokens[s.rid] = toks[k : k + nrows]
+                if lps is not None and s.logprobs > 0:
+                    res.logprobs[s.rid] = lps[k : k + nrows]
+                k += nrows
+        res.elapsed_s = time.perf_counter() - t0
+        return res
