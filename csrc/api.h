@@ -1,0 +1,54 @@
+// Public C API of libpegainfer_b200.so.  Every entry point returns 0 on success or a
+// negative PG_ERR_* code; pg_last_error() then holds a thread-local message.  Pointers
+// are device pointers unless named host_*.  `status` arguments are a device uint32 word
+// (pg_status_*) that kernels set when a bounded wait expires or an index is out of
+// range; kernels never trap.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+const char* pg_last_error(void);
+int pg_version(void);
+
+// ---- GEMM (gemm_sm100.cu) ----------------------------------------------------------
+int pg_gemm_workspace_bytes(int T, int M, int K, int device, long long* ws_bytes, long long* counter_bytes);
+int pg_gemm_bf16_tn(const void* x, const void* w, void* y, int y_is_f32, int T, int M, int K, long long ldx, long long ldw, long long ldy,
+                    void* ws, long long ws_bytes, void* counters, long long counter_bytes, void* status, int force_splits,
+                    cudaStream_t stream);
+int pg_make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, long long rows, long long cols, long long ld, int box_rows, int box_cols);
+
+// ---- row kernels (elementwise.cu) --------------------------------------------------
+int pg_gather_rows(const void* table, const void* ids, void* out, int rows, int width, long long table_rows, void* status, cudaStream_t stream);
+int pg_rms_norm(const void* x, void* residual, const void* w, void* y, int rows, int width, float eps, int offset, int round_before,
+                long long ldx, long long ldr, long long ldy, cudaStream_t stream);
+int pg_gated_rms_norm(const void* x, const void* gate, const void* w_f32, void* y, long long rows, int dim, float eps, cudaStream_t stream);
+int pg_swiglu(const void* gate_up, void* out, int rows, int inter, long long ldin, long long ldout, cudaStream_t stream);
+int pg_sigmoid_gate_mul(void* x, const void* gate, long long n, cudaStream_t stream);
+int pg_qk_norm_rope_append(const void* qkv, long long ld, const void* q_w, const void* k_w, const void* cos, const void* sin,
+                           const void* positions, const void* slots, void* q_out, void* gate_out, void* kv, int tokens, int hq, int hkv, int dim,
+                           int rot, int page_size, long long num_pages, int max_pos, int gated, int offset, float eps, void* status,
+                           cudaStream_t stream);
+
+// ---- attention (attention.cu) ------------------------------------------------------
+int pg_decode_splits(int num_seqs, int hkv, int max_kv_len, int sms);
+int pg_paged_attention(const void* q, const void* kv, void* out, const void* q_indptr, const void* kv_lens, const void* table, int table_stride,
+                       int num_seqs, int hq, int hkv, int dim, int page_size, long long num_pages, float scale, int mode, int splits,
+                       void* part_o, void* part_lse, int q_tiles, int window, void* status, cudaStream_t stream);
+
+// ---- sampling (sampling.cu) --------------------------------------------------------
+long long pg_argmax_scratch_bytes(int rows, int vocab);
+int pg_argmax(const void* logits, int is_f32, int rows, int vocab, long long ld, void* scratch, long long scratch_bytes, void* out,
+              cudaStream_t stream);
+int pg_sample(const void* logits, int is_f32, int rows, int vocab, long long ld, const void* temperature, const void* top_k, const void* top_p,
+              const void* min_p, const void* uniform, void* out, cudaStream_t stream);
+int pg_logprob_topk(const void* logits, int is_f32, int rows, int vocab, long long ld, const void* picked, int k, void* chosen_lp, void* top_lp,
+                    void* top_idx, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,334 @@
+// Memory-bound row kernels: embedding / row gather, RMSNorm (+ fused residual add,
+// (1+w) weights, round-before-norm), gated RMSNorm, SwiGLU, and the fused
+// QK-RMSNorm + RoPE + paged-KV append that sits between the qkv GEMM and attention.
+// All use 16-byte vector accesses; rows must be multiples of 8 bf16 elements.
+//
+// Functional parity with pegainfer-kernels/csrc/shared/{elementwise.cu:376-497,
+// flashinfer_norm.cu:40-312, fused_proj.cu:12-46, norm.cu:19-71, prefill_attention.cu:39-124},
+// csrc/qwen35/prefill_attention_hd256.cu:41-326 and paged_attention.cu:287-364 (KV append),
+// with an error status word where the reference traps on a bad position.
+#include "api.h"
+#include "common.cuh"
+
+namespace {
+
+__global__ void gather_rows_kernel(const bf16* __restrict__ table, const int* __restrict__ ids, bf16* __restrict__ out, int rows, int width,
+                                   long long table_rows, uint32_t* status) {
+  const int t = blockIdx.x;
+  long long id = ids[t];
+  if (id < 0 || id >= table_rows) {
+    if (threadIdx.x == 0) atomicCAS(status, PG_ST_OK, PG_ST_BOUNDS | (2u << 8));
+    id = 0;
+  }
+  const uint4* src = reinterpret_cast<const uint4*>(table + id * (long long)width);
+  uint4* dst = reinterpret_cast<uint4*>(out + (long long)t * width);
+  for (int i = threadIdx.x; i < width / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+// One CTA per row.  MODE 0: y = norm(x).  MODE 1: res += x; y = norm(res).
+template <int MODE>
+__global__ void __launch_bounds__(256) rms_norm_kernel(const bf16* __restrict__ x, bf16* __restrict__ residual, const bf16* __restrict__ w,
+                                                        bf16* __restrict__ y, int width, float eps, int offset, int round_before, long long ldx,
+                                                        long long ldr, long long ldy) {
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  const int nvec = width / 8;
+  constexpr int MAXV = 4;  // register-resident up to 8192 columns with 256 threads
+  float vals[MAXV][8];
+  float ss = 0.f;
+  const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + row * ldx);
+  bf16x8* rr = MODE == 1 ? reinterpret_cast<bf16x8*>(residual + row * ldr) : nullptr;
+#pragma unroll
+  for (int k = 0; k < MAXV; ++k) {
+    const int i = threadIdx.x + k * 256;
+    if (i < nvec) {
+      float f[8];
+      unpack8(xr[i], f);
+      if (MODE == 1) {
+        float r[8];
+        unpack8(rr[i], r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] += r[j];
+        bf16x8 packed = pack8(f);
+        rr[i] = packed;
+        if (round_before) unpack8(packed, f);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        vals[k][j] = f[j];
+        ss += f[j] * f[j];
+      }
+    }
+  }
+  // columns beyond the register window (width > 8192): recomputed in a second pass
+  for (int i = threadIdx.x + MAXV * 256; i < nvec; i += 256) {
+    float f[8];
+    unpack8(xr[i], f);
+    if (MODE == 1) {
+      float r[8];
+      unpack8(rr[i], r);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] += r[j];
+      bf16x8 packed = pack8(f);
+      rr[i] = packed;
+      if (round_before) unpack8(packed, f);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
+  }
+  ss = block_sum(ss, red);
+  const float inv = rsqrtf(ss / (float)width + eps);
+  const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
+  bf16x8* yr = reinterpret_cast<bf16x8*>(y + row * ldy);
+#pragma unroll
+  for (int k = 0; k < MAXV; ++k) {
+    const int i = threadIdx.x + k * 256;
+    if (i < nvec) {
+      float wf[8], o[8];
+      unpack8(wr[i], wf);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = vals[k][j] * inv * (offset ? wf[j] + 1.f : wf[j]);
+      yr[i] = pack8(o);
+    }
+  }
+  for (int i = threadIdx.x + MAXV * 256; i < nvec; i += 256) {
+    float f[8], wf[8], o[8];
+    // MODE 1 with round_before re-reads the stored residual (already the rounded sum)
+    unpack8(MODE == 1 ? rr[i] : xr[i], f);
+    unpack8(wr[i], wf);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = f[j] * inv * (offset ? wf[j] + 1.f : wf[j]);
+    yr[i] = pack8(o);
+  }
+}
+
+// Per (token, head): y = rms_norm(x, w_f32) * silu(gate); one warp per head row.
+__global__ void gated_rms_norm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ gate, const float* __restrict__ w, bf16* __restrict__ y,
+                                      long long rows, int dim, float eps) {
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const bf16* xr = x + row * dim;
+  const bf16* gr = gate + row * dim;
+  float ss = 0.f;
+  for (int i = lane; i < dim; i += 32) {
+    float v = __bfloat162float(xr[i]);
+    ss += v * v;
+  }
+  ss = warp_sum(ss);
+  const float inv = rsqrtf(ss / (float)dim + eps);
+  for (int i = lane; i < dim; i += 32) {
+    float v = __bfloat162float(xr[i]);
+    float g = __bfloat162float(gr[i]);
+    float s = g / (1.f + __expf(-g));
+    y[row * dim + i] = __float2bfloat16(v * inv * w[i] * s);
+  }
+}
+
+__global__ void swiglu_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int rows, int inter, long long ldin, long long ldout) {
+  const int nvec = inter / 8;
+  const long long total = (long long)rows * nvec;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+    const int row = (int)(idx / nvec), i = (int)(idx % nvec);
+    const bf16x8* g = reinterpret_cast<const bf16x8*>(gu + row * ldin) + i;
+    const bf16x8* u = reinterpret_cast<const bf16x8*>(gu + row * ldin + inter) + i;
+    float gf[8], uf[8], o[8];
+    unpack8(*g, gf);
+    unpack8(*u, uf);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = bf16_round(gf[j] / (1.f + __expf(-gf[j]))) * uf[j];
+    reinterpret_cast<bf16x8*>(out + row * ldout)[i] = pack8(o);
+  }
+}
+
+__global__ void sigmoid_gate_mul_kernel(bf16* __restrict__ x, const bf16* __restrict__ gate, long long n) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    float g = __bfloat162float(gate[i]);
+    x[i] = __float2bfloat16(__bfloat162float(x[i]) / (1.f + __expf(-g)));
+  }
+}
+
+// One warp per (token, head) over the fused qkv row.  Heads [0, Hq) are queries,
+// [Hq, Hq+Hkv) keys, [Hq+Hkv, Hq+2Hkv) values.
+struct RopeParams {
+  const bf16* qkv;
+  long long ld;
+  const bf16* q_w;
+  const bf16* k_w;
+  const bf16* cos;
+  const bf16* sin;
+  const int* positions;
+  const int* slots;
+  bf16* q_out;
+  bf16* gate_out;
+  bf16* kv;  // [pages, 2, page_size, Hkv, D]
+  int tokens, hq, hkv, dim, rot, page_size, max_pos, gated, offset, has_norm;
+  long long num_slots;
+  float eps;
+  uint32_t* status;
+};
+
+__global__ void __launch_bounds__(128) qk_norm_rope_append_kernel(const RopeParams p) {
+  __shared__ float buf[4][256];
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = p.hq + 2 * p.hkv;
+  const long long unit = (long long)blockIdx.x * 4 + w;
+  if (unit >= (long long)p.tokens * heads) return;
+  const int t = (int)(unit / heads), h = (int)(unit % heads);
+  const int D = p.dim;
+  const int qstride = p.gated ? 2 * D : D;
+  const bf16* src;
+  int kind;  // 0 q, 1 k, 2 v
+  if (h < p.hq) {
+    kind = 0;
+    src = p.qkv + t * p.ld + (long long)h * qstride;
+  } else if (h < p.hq + p.hkv) {
+    kind = 1;
+    src = p.qkv + t * p.ld + (long long)p.hq * qstride + (long long)(h - p.hq) * D;
+  } else {
+    kind = 2;
+    src = p.qkv + t * p.ld + (long long)p.hq * qstride + (long long)(h - p.hq) * D;  // keys then values are contiguous
+  }
+  long long slot = p.slots[t];
+  if (kind != 0 && (slot < 0 || slot >= p.num_slots)) {
+    if (lane == 0) atomicCAS(p.status, PG_ST_OK, PG_ST_BOUNDS | (3u << 8));
+    return;
+  }
+  const long long page = slot / p.page_size, off = slot % p.page_size;
+  if (kind == 2) {
+    bf16* dst = p.kv + (((page * 2 + 1) * p.page_size + off) * p.hkv + (h - p.hq - p.hkv)) * D;
+    for (int i = lane; i < D / 8; i += 32) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+    return;
+  }
+  int pos = p.positions[t];
+  if (pos < 0 || pos >= p.max_pos) {
+    if (lane == 0) atomicCAS(p.status, PG_ST_OK, PG_ST_BOUNDS | (4u << 8));
+    pos = pos < 0 ? 0 : p.max_pos - 1;
+  }
+  float ss = 0.f;
+  for (int i = lane; i < D; i += 32) {
+    float v = __bfloat162float(src[i]);
+    buf[w][i] = v;
+    ss += v * v;
+  }
+  if (p.has_norm) {
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)D + p.eps);
+    const bf16* nw = kind == 0 ? p.q_w : p.k_w;
+    for (int i = lane; i < D; i += 32) {
+      float wv = __bfloat162float(nw[i]);
+      buf[w][i] = bf16_round(buf[w][i] * inv * (p.offset ? wv + 1.f : wv));
+    }
+  }
+  __syncwarp();
+  bf16* dst;
+  if (kind == 0)
+    dst = p.q_out + ((long long)t * p.hq + h) * D;
+  else
+    dst = p.kv + (((page * 2 + 0) * p.page_size + off) * p.hkv + (h - p.hq)) * D;
+  const int half = p.rot / 2;
+  const bf16* cs = p.cos + (long long)pos * half;
+  const bf16* sn = p.sin + (long long)pos * half;
+  for (int i = lane; i < D; i += 32) {
+    float o;
+    if (i < half) {
+      o = buf[w][i] * __bfloat162float(cs[i]) - buf[w][i + half] * __bfloat162float(sn[i]);
+    } else if (i < p.rot) {
+      o = buf[w][i] * __bfloat162float(cs[i - half]) + buf[w][i - half] * __bfloat162float(sn[i - half]);
+    } else {
+      o = buf[w][i];
+    }
+    dst[i] = __float2bfloat16(o);
+  }
+  if (kind == 0 && p.gated) {
+    bf16* g = p.gate_out + ((long long)t * p.hq + h) * D;
+    for (int i = lane; i < D; i += 32) g[i] = src[D + i];
+  }
+}
+
+}  // namespace
+
+extern "C" int pg_gather_rows(const void* table, const void* ids, void* out, int rows, int width, long long table_rows, void* status,
+                              cudaStream_t stream) {
+  PG_REQUIRE(width % 8 == 0, "gather_rows: width %d must be a multiple of 8", width);
+  if (rows == 0) return PG_OK;
+  gather_rows_kernel<<<rows, 128, 0, stream>>>((const bf16*)table, (const int*)ids, (bf16*)out, rows, width, table_rows, (uint32_t*)status);
+  PG_LAUNCH_CHECK();
+  return PG_OK;
+}
+
+extern "C" int pg_rms_norm(const void* x, void* residual, const void* w, void* y, int rows, int width, float eps, int offset, int round_before,
+                           long long ldx, long long ldr, long long ldy, cudaStream_t stream) {
+  PG_REQUIRE(width % 8 == 0 && ldx % 8 == 0 && ldy % 8 == 0, "rms_norm: width/strides must be multiples of 8");
+  if (rows == 0) return PG_OK;
+  if (residual)
+    rms_norm_kernel<1><<<rows, 256, 0, stream>>>((const bf16*)x, (bf16*)residual, (const bf16*)w, (bf16*)y, width, eps, offset, round_before, ldx, ldr, ldy);
+  else
+    rms_norm_kernel<0><<<rows, 256, 0, stream>>>((const bf16*)x, nullptr, (const bf16*)w, (bf16*)y, width, eps, offset, 0, ldx, 0, ldy);
+  PG_LAUNCH_CHECK();
+  return PG_OK;
+}
+
+extern "C" int pg_gated_rms_norm(const void* x, const void* gate, const void* w_f32, void* y, long long rows, int dim, float eps, cudaStream_t stream) {
+  if (rows == 0) return PG_OK;
+  gated_rms_norm_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, stream>>>((const bf16*)x, (const bf16*)gate, (const float*)w_f32, (bf16*)y, rows, dim, eps);
+  PG_LAUNCH_CHECK();
+  return PG_OK;
+}
+
+extern "C" int pg_swiglu(const void* gate_up, void* out, int rows, int inter, long long ldin, long long ldout, cudaStream_t stream) {
+  PG_REQUIRE(inter % 8 == 0 && ldin % 8 == 0 && ldout % 8 == 0, "swiglu: sizes must be multiples of 8");
+  if (rows == 0) return PG_OK;
+  long long total = (long long)rows * (inter / 8);
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  swiglu_kernel<<<blocks, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, rows, inter, ldin, ldout);
+  PG_LAUNCH_CHECK();
+  return PG_OK;
+}
+
+extern "C" int pg_sigmoid_gate_mul(void* x, const void* gate, long long n, cudaStream_t stream) {
+  if (n == 0) return PG_OK;
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  sigmoid_gate_mul_kernel<<<(int)blocks, 256, 0, stream>>>((bf16*)x, (const bf16*)gate, n);
+  PG_LAUNCH_CHECK();
+  return PG_OK;
+}
+
+extern "C" int pg_qk_norm_rope_append(const void* qkv, long long ld, const void* q_w, const void* k_w, const void* cos, const void* sin,
+                                      const void* positions, const void* slots, void* q_out, void* gate_out, void* kv, int tokens, int hq, int hkv,
+                                      int dim, int rot, int page_size, long long num_pages, int max_pos, int gated, int offset, float eps,
+                                      void* status, cudaStream_t stream) {
+  PG_REQUIRE(dim % 8 == 0 && dim <= 256 && rot <= dim && rot % 2 == 0, "qk_norm_rope: unsupported head_dim %d / rotary %d", dim, rot);
+  if (tokens == 0) return PG_OK;
+  RopeParams p;
+  p.qkv = (const bf16*)qkv;
+  p.ld = ld;
+  p.q_w = (const bf16*)q_w;
+  p.k_w = (const bf16*)k_w;
+  p.cos = (const bf16*)cos;
+  p.sin = (const bf16*)sin;
+  p.positions = (const int*)positions;
+  p.slots = (const int*)slots;
+  p.q_out = (bf16*)q_out;
+  p.gate_out = (bf16*)gate_out;
+  p.kv = (bf16*)kv;
+  p.tokens = tokens;
+  p.hq = hq;
+  p.hkv = hkv;
+  p.dim = dim;
+  p.rot = rot;
+  p.page_size = page_size;
+  p.max_pos = max_pos;
+  p.gated = gated;
+  p.offset = offset;
+  p.has_norm = q_w != nullptr;
+  p.num_slots = num_pages * page_size;
+  p.eps = eps;
+  p.status = (uint32_t*)status;
+  long long units = (long long)tokens * (hq + 2 * hkv);
+  qk_norm_rope_append_kernel<<<(unsigned)((units + 3) / 4), 128, 0, stream>>>(p);
+  PG_LAUNCH_CHECK();
+  return PG_OK;
+}

@@ -1,0 +1,303 @@
+"""ctypes front end of the sm_100a kernels: same signatures as ``ops.reference``.
+
+Every function validates dtypes/shapes, takes the current CUDA stream and calls the
+C API of ``libpegainfer_b200.so``.  Per-device scratch (GEMM split-K workspace and tile
+counters, argmax partials, split-KV partials, the device status word) is allocated
+once with a fixed size so its addresses stay valid inside captured CUDA graphs.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional
+
+import torch
+
+from .. import _native
+from .reference import AttnMeta
+
+_c = ctypes
+_vp = ctypes.c_void_p
+_ll = ctypes.c_longlong
+_ci = ctypes.c_int
+_cf = ctypes.c_float
+
+GEMM_WS_BYTES = 96 << 20
+GEMM_COUNTERS = 1 << 16
+ATTN_PART_BYTES = 64 << 20
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return _vp(t.data_ptr()) if t is not None else _vp(0)
+
+
+def _stream():
+    return _vp(torch.cuda.current_stream().cuda_stream)
+
+
+class _DeviceCtx:
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.status = torch.zeros(4, dtype=torch.int32, device=device)
+        self.gemm_ws = torch.empty(GEMM_WS_BYTES, dtype=torch.uint8, device=device)
+        self.gemm_counters = torch.zeros(GEMM_COUNTERS, dtype=torch.int32, device=device)
+        self.argmax_scratch = torch.empty(8 << 20, dtype=torch.uint8, device=device)
+        self.attn_part = torch.empty(ATTN_PART_BYTES, dtype=torch.uint8, device=device)
+        self.sms = torch.cuda.get_device_properties(device).multi_processor_count
+        self.launches = 0
+
+
+_CTX: dict = {}
+
+
+def ctx(device) -> _DeviceCtx:
+    device = torch.device(device)
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    c = _CTX.get(idx)
+    if c is None:
+        with torch.cuda.device(idx):
+            c = _DeviceCtx(torch.device("cuda", idx))
+        _CTX[idx] = c
+    return c
+
+
+def lib():
+    return _native.load()
+
+
+def _check(rc, c: Optional[_DeviceCtx] = None, n: int = 1):
+    if rc != 0:
+        _native.check(rc)
+    if c is not None:
+        c.launches += n
+
+
+def launch_count(device=None) -> int:
+    """Kernels of this library launched so far on ``device`` (eager calls; a graph
+    replay re-launches what was captured without passing through here)."""
+    if device is None:
+        return sum(c.launches for c in _CTX.values())
+    return ctx(device).launches
+
+
+def read_status(device) -> int:
+    """Device status word: 0 = clean; low byte 1 = a bounded wait expired, 2 = an index
+    was out of range; bits 8.. identify the kernel site.  Synchronises."""
+    return int(ctx(device).status[0].item()) & 0xFFFFFFFF
+
+
+def clear_status(device) -> None:
+    ctx(device).status.zero_()
+
+
+# ----------------------------------------------------------------------------------
+def _bf16(t):
+    if t.dtype != torch.bfloat16:
+        raise TypeError(f"sm_100a kernels take bfloat16 activations/weights, got {t.dtype}")
+    return t
+
+
+def embedding(ids, table):
+    return gather_rows(table, ids)
+
+
+def gather_rows(x, idx):
+    _bf16(x)
+    x2 = x.reshape(-1, x.shape[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    idx = idx.to(torch.int32).contiguous()
+    out = torch.empty((idx.numel(), x2.shape[1]), dtype=x.dtype, device=x.device)
+    c = ctx(x.device)
+    _check(lib().pg_gather_rows(_ptr(x2), _ptr(idx), _ptr(out), _ci(idx.numel()), _ci(x2.shape[1]), _ll(x2.shape[0]), _ptr(c.status), _stream()), c)
+    return out
+
+
+def _rows2d(x):
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    return x2
+
+
+def rms_norm(x, w, eps, offset=False):
+    _bf16(x)
+    x2 = _rows2d(x)
+    if x2.shape[1] % 8 != 0:
+        from . import reference
+
+        return reference.rms_norm(x, w, eps, offset)
+    y = torch.empty((x2.shape[0], x2.shape[1]), dtype=x.dtype, device=x.device)
+    c = ctx(x.device)
+    _check(lib().pg_rms_norm(_ptr(x2), _vp(0), _ptr(w), _ptr(y), _ci(x2.shape[0]), _ci(x2.shape[1]), _cf(eps), _ci(int(offset)), _ci(0), _ll(x2.stride(0)), _ll(0), _ll(y.stride(0)), _stream()), c)
+    return y.view(x.shape)
+
+
+def add_rms_norm(x, residual, w, eps, offset=False, round_before_norm=True):
+    _bf16(x)
+    x2, r2 = _rows2d(x), residual.reshape(-1, residual.shape[-1])
+    assert r2.stride(-1) == 1 and r2.data_ptr() == residual.data_ptr(), "residual must be updatable in place"
+    y = torch.empty((x2.shape[0], x2.shape[1]), dtype=x.dtype, device=x.device)
+    c = ctx(x.device)
+    _check(lib().pg_rms_norm(_ptr(x2), _ptr(r2), _ptr(w), _ptr(y), _ci(x2.shape[0]), _ci(x2.shape[1]), _cf(eps), _ci(int(offset)), _ci(int(round_before_norm)), _ll(x2.stride(0)), _ll(r2.stride(0)), _ll(y.stride(0)), _stream()), c)
+    return y.view(x.shape)
+
+
+def gated_rms_norm(x, gate, w, eps):
+    _bf16(x)
+    x = x.contiguous()
+    gate = gate.contiguous()
+    w = w.float().contiguous()
+    y = torch.empty_like(x)
+    rows = x.numel() // x.shape[-1]
+    c = ctx(x.device)
+    _check(lib().pg_gated_rms_norm(_ptr(x), _ptr(gate), _ptr(w), _ptr(y), _ll(rows), _ci(x.shape[-1]), _cf(eps), _stream()), c)
+    return y
+
+
+def swiglu(gate_up):
+    _bf16(gate_up)
+    g2 = _rows2d(gate_up)
+    inter = g2.shape[1] // 2
+    out = torch.empty((g2.shape[0], inter), dtype=g2.dtype, device=g2.device)
+    c = ctx(g2.device)
+    _check(lib().pg_swiglu(_ptr(g2), _ptr(out), _ci(g2.shape[0]), _ci(inter), _ll(g2.stride(0)), _ll(out.stride(0)), _stream()), c)
+    return out.view(*gate_up.shape[:-1], inter)
+
+
+def linear(x, w, out_dtype=None, force_splits: int = 0, out: Optional[torch.Tensor] = None):
+    """``x[T, K] @ w[M, K].T`` on the tcgen05 GEMM (f32 accumulation)."""
+    _bf16(x)
+    _bf16(w)
+    x2 = _rows2d(x)
+    if w.stride(-1) != 1:
+        w = w.contiguous()
+    t, k = x2.shape
+    m = w.shape[0]
+    assert w.shape[1] == k, f"linear: x has K={k}, w has K={w.shape[1]}"
+    f32 = out_dtype == torch.float32
+    if out is None:
+        out = torch.empty((t, m), dtype=torch.float32 if f32 else torch.bfloat16, device=x.device)
+    if t == 0:
+        return out.view(*x.shape[:-1], m)
+    c = ctx(x.device)
+    rc = lib().pg_gemm_bf16_tn(
+        _ptr(x2), _ptr(w), _ptr(out), _ci(int(f32)), _ci(t), _ci(m), _ci(k), _ll(x2.stride(0)), _ll(w.stride(0)), _ll(out.stride(0)),
+        _ptr(c.gemm_ws), _ll(c.gemm_ws.numel()), _ptr(c.gemm_counters), _ll(c.gemm_counters.numel() * 4), _ptr(c.status), _ci(force_splits), _stream(),
+    )
+    _check(rc, c)
+    res = out.view(*x.shape[:-1], m)
+    if out_dtype is not None and res.dtype != out_dtype:
+        res = res.to(out_dtype)
+    return res
+
+
+def qk_norm_rope_append(qkv, q_norm_w, k_norm_w, cos, sin, meta: AttnMeta, kv_layer, num_q_heads, num_kv_heads, head_dim, eps, offset=False, gated=False):
+    _bf16(qkv)
+    t = qkv.shape[0]
+    assert qkv.stride(-1) == 1
+    q = torch.empty((t, num_q_heads, head_dim), dtype=qkv.dtype, device=qkv.device)
+    gate = torch.empty_like(q) if gated else None
+    assert kv_layer.is_contiguous()
+    num_pages, _, page_size = kv_layer.shape[0], kv_layer.shape[1], kv_layer.shape[2]
+    c = ctx(qkv.device)
+    rc = lib().pg_qk_norm_rope_append(
+        _ptr(qkv), _ll(qkv.stride(0)), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(cos), _ptr(sin), _ptr(meta.positions), _ptr(meta.slot_mapping),
+        _ptr(q), _ptr(gate), _ptr(kv_layer), _ci(t), _ci(num_q_heads), _ci(num_kv_heads), _ci(head_dim), _ci(cos.shape[-1] * 2), _ci(page_size),
+        _ll(num_pages), _ci(cos.shape[0]), _ci(int(gated)), _ci(int(offset)), _cf(eps), _ptr(c.status), _stream(),
+    )
+    _check(rc, c)
+    return (q, gate) if gated else q
+
+
+def plan_decode_splits(num_seqs: int, hkv: int, max_kv_len: int, device) -> int:
+    return int(lib().pg_decode_splits(_ci(num_seqs), _ci(hkv), _ci(max(max_kv_len, 1)), _ci(ctx(device).sms)))
+
+
+def paged_attention(q, kv_layer, meta: AttnMeta, scale=None, window=0, out: Optional[torch.Tensor] = None):
+    _bf16(q)
+    t, hq, d = q.shape
+    hkv = kv_layer.shape[-2]
+    page_size = kv_layer.shape[2]
+    scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    if out is None:
+        out = torch.empty((t, hq * d), dtype=q.dtype, device=q.device)
+    c = ctx(q.device)
+    table = meta.block_table
+    if meta.decode_only and window == 0:
+        splits = meta.plan if isinstance(meta.plan, int) else plan_decode_splits(meta.num_seqs, hkv, meta.max_kv_len, q.device)
+        need = meta.num_seqs * hq * splits * (d + 1) * 4
+        if need > c.attn_part.numel():
+            splits = max(1, c.attn_part.numel() // (meta.num_seqs * hq * (d + 1) * 4))
+        part_o = c.attn_part
+        lse_off = meta.num_seqs * hq * splits * d * 4
+        part_lse = c.attn_part[lse_off:]
+        rc = lib().pg_paged_attention(
+            _ptr(q), _ptr(kv_layer), _ptr(out), _ptr(meta.q_indptr), _ptr(meta.kv_lens), _ptr(table), _ci(table.stride(0)), _ci(meta.num_seqs),
+            _ci(hq), _ci(hkv), _ci(d), _ci(page_size), _ll(kv_layer.shape[0]), _cf(scale), _ci(0), _ci(splits), _ptr(part_o), _ptr(part_lse),
+            _ci(0), _ci(0), _ptr(c.status), _stream(),
+        )
+        _check(rc, c, 2 if splits > 1 else 1)
+        return out
+    qi = meta.h_q_indptr if meta.h_q_indptr is not None else meta.q_indptr.tolist()
+    q_tiles = sum((qi[b + 1] - qi[b] + 63) // 64 for b in range(meta.num_seqs))
+    rc = lib().pg_paged_attention(
+        _ptr(q), _ptr(kv_layer), _ptr(out), _ptr(meta.q_indptr), _ptr(meta.kv_lens), _ptr(table), _ci(table.stride(0)), _ci(meta.num_seqs),
+        _ci(hq), _ci(hkv), _ci(d), _ci(page_size), _ll(kv_layer.shape[0]), _cf(scale), _ci(1), _ci(1), _vp(0), _vp(0), _ci(q_tiles), _ci(window),
+        _ptr(c.status), _stream(),
+    )
+    _check(rc, c)
+    return out
+
+
+def sigmoid_gate_mul_(x, gate):
+    c = ctx(x.device)
+    assert x.is_contiguous() and gate.is_contiguous()
+    _check(lib().pg_sigmoid_gate_mul(_ptr(x), _ptr(gate), _ll(x.numel()), _stream()), c)
+    return x
+
+
+def argmax(logits, out: Optional[torch.Tensor] = None):
+    rows, vocab = logits.shape
+    assert logits.stride(-1) == 1
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    c = ctx(logits.device)
+    f32 = logits.dtype == torch.float32
+    if not f32:
+        _bf16(logits)
+    rc = lib().pg_argmax(_ptr(logits), _ci(int(f32)), _ci(rows), _ci(vocab), _ll(logits.stride(0)), _ptr(c.argmax_scratch), _ll(c.argmax_scratch.numel()), _ptr(out), _stream())
+    _check(rc, c, 2)
+    return out
+
+
+def sample(logits, temperature, top_k, top_p, min_p, u):
+    rows, vocab = logits.shape
+    if logits.stride(-1) != 1:
+        logits = logits.contiguous()
+    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    f32 = logits.dtype == torch.float32
+    c = ctx(logits.device)
+    rc = lib().pg_sample(
+        _ptr(logits), _ci(int(f32)), _ci(rows), _ci(vocab), _ll(logits.stride(0)), _ptr(temperature.float().contiguous()), _ptr(top_k.to(torch.int32).contiguous()),
+        _ptr(top_p.float().contiguous()), _ptr(min_p.float().contiguous()), _ptr(u.float().contiguous()), _ptr(out), _stream(),
+    )
+    _check(rc, c)
+    return out
+
+
+def logprobs_topk(logits, picked, k):
+    rows, vocab = logits.shape
+    if logits.stride(-1) != 1:
+        logits = logits.contiguous()
+    f32 = logits.dtype == torch.float32
+    dev = logits.device
+    chosen = torch.empty(rows, dtype=torch.float32, device=dev)
+    tv = torch.empty((rows, max(k, 1)), dtype=torch.float32, device=dev)
+    ti = torch.empty((rows, max(k, 1)), dtype=torch.int32, device=dev)
+    c = ctx(dev)
+    rc = lib().pg_logprob_topk(_ptr(logits), _ci(int(f32)), _ci(rows), _ci(vocab), _ll(logits.stride(0)), _ptr(picked.to(torch.int32).contiguous()), _ci(k), _ptr(chosen), _ptr(tv), _ptr(ti), _stream())
+    _check(rc, c)
+    if k == 0:
+        return chosen, None, None
+    return chosen, tv, ti

@@ -1,0 +1,221 @@
+"""sm_100a kernels against the PyTorch fp32 restatement of the same op."""
+import math
+
+import pytest
+import torch
+
+from pegainfer_b200 import ops
+from pegainfer_b200.ops import reference as R
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def cu():
+    from pegainfer_b200.ops import cuda
+
+    return cuda
+
+
+def bf16_close(a, b, rel=2 ** -7, abs_=1e-3):
+    a, b = a.float(), b.float()
+    err = (a - b).abs()
+    tol = abs_ + rel * b.abs()
+    bad = (err > tol).sum().item()
+    assert bad == 0, f"{bad}/{a.numel()} elements off; max err {err.max().item():.4g}"
+
+
+def status_clean():
+    assert cu().read_status(DEV) == 0, f"device status word {cu().read_status(DEV):#x}"
+
+
+@pytest.mark.parametrize(
+    "t,m,k",
+    [(1, 256, 128), (7, 384, 264), (16, 128, 64), (33, 1000, 520), (64, 4096, 4096), (64, 6144, 4096), (200, 512, 1024), (300, 1536, 2048), (1024, 2048, 1024)],
+)
+def test_gemm_matches_fp32(t, m, k):
+    torch.manual_seed(t * 7 + m)
+    x = (torch.randn(t, k, device=DEV) * 0.5).bfloat16()
+    w = (torch.randn(m, k, device=DEV) * 0.05).bfloat16()
+    ref = x.float() @ w.float().t()
+    y = cu().linear(x, w)
+    torch.cuda.synchronize()
+    status_clean()
+    assert y.shape == (t, m) and y.dtype == torch.bfloat16
+    err = (y.float() - ref).abs()
+    tol = 2 ** -7 * ref.abs() + 2e-2 * math.sqrt(k / 1024)
+    assert (err <= tol).all(), f"max err {err.max().item()} (ref max {ref.abs().max().item()})"
+    yf = cu().linear(x, w, out_dtype=torch.float32)
+    assert (yf - ref).abs().max().item() < 1e-2 * math.sqrt(k / 64)
+    # bit-identical rerun, also with a pinned split count
+    assert torch.equal(y, cu().linear(x, w))
+    for s in (1, 2, 3):
+        if k // 64 >= s:
+            ys = cu().linear(x, w, force_splits=s)
+            assert (ys.float() - ref).abs().max().item() <= tol.max().item() * 2
+    status_clean()
+
+
+def test_gemm_strided_input_and_batch_invariance():
+    torch.manual_seed(0)
+    k, m = 1024, 768
+    big = (torch.randn(96, 2 * k, device=DEV) * 0.3).bfloat16()
+    x = big[:, :k]  # row stride 2k
+    w = (torch.randn(m, k, device=DEV) * 0.05).bfloat16()
+    y = cu().linear(x, w, force_splits=2)
+    ref = x.float() @ w.float().t()
+    bf16_close(y, ref, rel=2 ** -6, abs_=3e-2)
+    # a row's result must not depend on how many other rows ride along
+    y1 = cu().linear(x[5:6], w, force_splits=2)
+    y40 = cu().linear(x[:40], w, force_splits=2)
+    assert torch.equal(y1[0], y[5]) and torch.equal(y40[5], y[5])
+    status_clean()
+
+
+@pytest.mark.parametrize("width", [256, 2048, 4096, 5120, 7168])
+@pytest.mark.parametrize("offset", [False, True])
+def test_rms_norm_and_fused_add(width, offset):
+    torch.manual_seed(width)
+    x = torch.randn(37, width, device=DEV).bfloat16()
+    res = torch.randn(37, width, device=DEV).bfloat16()
+    w = (torch.randn(width, device=DEV) * 0.2 + (0 if offset else 1)).bfloat16()
+    bf16_close(cu().rms_norm(x, w, 1e-6, offset), R.rms_norm(x, w, 1e-6, offset), rel=2 ** -7)
+    for rb in (True, False):
+        r1, r2 = res.clone(), res.clone()
+        y1 = cu().add_rms_norm(x, r1, w, 1e-6, offset, rb)
+        y2 = R.add_rms_norm(x, r2, w, 1e-6, offset, rb)
+        assert torch.equal(r1, r2)
+        bf16_close(y1, y2, rel=2 ** -7)
+
+
+def test_swiglu_gather_gated_norm():
+    torch.manual_seed(3)
+    gu = torch.randn(50, 2 * 1408, device=DEV).bfloat16() * 2
+    bf16_close(cu().swiglu(gu), R.swiglu(gu), rel=2 ** -7)
+    table = torch.randn(1000, 512, device=DEV).bfloat16()
+    ids = torch.randint(0, 1000, (77,), device=DEV, dtype=torch.int32)
+    assert torch.equal(cu().gather_rows(table, ids), table[ids.long()])
+    x = torch.randn(9, 6, 128, device=DEV).bfloat16()
+    g = torch.randn(9, 6, 128, device=DEV).bfloat16()
+    w = torch.rand(128, device=DEV) + 0.5
+    bf16_close(cu().gated_rms_norm(x, g, w, 1e-6), R.gated_rms_norm(x, g, w, 1e-6), rel=2 ** -6)
+    status_clean()
+
+
+def make_batch(q_lens, kv_lens, page_size, hkv, d, extra_pages=3, pad=0):
+    """Random paged KV + metadata for sequences with the given query / KV lengths."""
+    from pegainfer_b200.kv.request_kv import KvView
+    from pegainfer_b200.sched.executor import SeqStep, build_meta
+
+    n_pages = sum((l + page_size - 1) // page_size for l in kv_lens) + extra_pages + 1
+    perm = (torch.randperm(n_pages - 1) + 1).tolist()
+    seqs, p = [], 0
+    for ql, kl in zip(q_lens, kv_lens):
+        npg = (kl + page_size - 1) // page_size
+        pages = perm[p : p + npg]
+        p += npg
+        seqs.append(SeqStep(rid=len(seqs), input_tokens=[0] * ql, start_pos=kl - ql, view=KvView(pages, kl, page_size)))
+    kv = torch.randn(n_pages, 2, page_size, hkv, d, device=DEV).bfloat16()
+    _, meta = build_meta(seqs, page_size, DEV, pad_to=len(seqs) + pad)
+    return kv, meta
+
+
+@pytest.mark.parametrize("d,hq,hkv,page", [(128, 32, 8, 16), (64, 4, 2, 16), (256, 24, 4, 64), (128, 8, 8, 32), (128, 6, 1, 16)])
+def test_decode_attention(d, hq, hkv, page):
+    torch.manual_seed(d + hq)
+    kv_lens = [1, 15, 16, 17, 200, 1025, 333]
+    kv, meta = make_batch([1] * len(kv_lens), kv_lens, page, hkv, d, pad=2)
+    q = torch.randn(meta.num_tokens, hq, d, device=DEV).bfloat16()
+    ref = R.paged_attention(q, kv, meta)
+    for splits in (1, 3, None):
+        meta.plan = splits
+        out = cu().paged_attention(q, kv, meta)
+        bf16_close(out, ref, rel=2 ** -6, abs_=6e-3)
+        assert out[len(kv_lens):].abs().max().item() == 0  # padding rows are inert
+    status_clean()
+
+
+@pytest.mark.parametrize("d,hq,hkv,page", [(128, 32, 8, 16), (64, 4, 2, 16), (256, 12, 2, 64)])
+def test_prefill_attention_ragged_and_mixed(d, hq, hkv, page):
+    torch.manual_seed(d)
+    q_lens = [1, 64, 65, 130, 1, 17]
+    kv_lens = [40, 64, 200, 130, 1, 300]
+    kv, meta = make_batch(q_lens, kv_lens, page, hkv, d)
+    q = torch.randn(meta.num_tokens, hq, d, device=DEV).bfloat16()
+    ref = R.paged_attention(q, kv, meta)
+    out = cu().paged_attention(q, kv, meta)
+    bf16_close(out, ref, rel=2 ** -6, abs_=6e-3)
+    refw = R.paged_attention(q, kv, meta, window=48)
+    outw = cu().paged_attention(q, kv, meta, window=48)
+    bf16_close(outw, refw, rel=2 ** -6, abs_=6e-3)
+    status_clean()
+
+
+@pytest.mark.parametrize("d,rot,gated,offset", [(128, 128, False, False), (64, 64, False, False), (256, 64, True, True)])
+def test_qk_norm_rope_append(d, rot, gated, offset):
+    torch.manual_seed(rot)
+    hq, hkv, page = 8, 2, 16
+    q_lens, kv_lens = [5, 1, 20], [21, 33, 20]
+    kv, meta = make_batch(q_lens, kv_lens, page, hkv, d)
+    kv2 = kv.clone()
+    t = meta.num_tokens
+    qkv = torch.randn(t, hq * d * (2 if gated else 1) + 2 * hkv * d, device=DEV).bfloat16()
+    qw = (torch.randn(d, device=DEV) * 0.1 + (0 if offset else 1)).bfloat16()
+    kw = (torch.randn(d, device=DEV) * 0.1 + (0 if offset else 1)).bfloat16()
+    cos, sin = R.rope_tables(512, rot, 1e6, torch.bfloat16, DEV)
+    a = cu().qk_norm_rope_append(qkv, qw, kw, cos, sin, meta, kv, hq, hkv, d, 1e-6, offset, gated)
+    b = R.qk_norm_rope_append(qkv, qw, kw, cos, sin, meta, kv2, hq, hkv, d, 1e-6, offset, gated)
+    if gated:
+        assert torch.equal(a[1], b[1])
+        a, b = a[0], b[0]
+    bf16_close(a, b, rel=2 ** -7, abs_=2e-3)
+    bf16_close(kv, kv2, rel=2 ** -7, abs_=2e-3)
+    status_clean()
+
+
+def test_position_out_of_range_sets_status_not_trap():
+    hq, hkv, d, page = 4, 2, 64, 16
+    kv, meta = make_batch([2], [2], page, hkv, d)
+    meta.positions = torch.tensor([0, 9999], dtype=torch.int32, device=DEV)
+    qkv = torch.randn(2, (hq + 2 * hkv) * d, device=DEV).bfloat16()
+    w = torch.ones(d, device=DEV).bfloat16()
+    cos, sin = R.rope_tables(128, d, 1e6, torch.bfloat16, DEV)
+    cu().qk_norm_rope_append(qkv, w, w, cos, sin, meta, kv, hq, hkv, d, 1e-6)
+    torch.cuda.synchronize()
+    st = cu().read_status(DEV)
+    assert st & 0xFF == 2
+    cu().clear_status(DEV)
+    status_clean()
+
+
+@pytest.mark.parametrize("vocab", [1024, 151936])
+def test_argmax_sample_logprobs(vocab):
+    torch.manual_seed(vocab)
+    rows = 9
+    logits = (torch.randn(rows, vocab, device=DEV) * 3).bfloat16()
+    logits[0, 5] = logits[0, 77] = 50.0  # tie -> lowest index
+    am = cu().argmax(logits)
+    assert torch.equal(am, R.argmax(logits)) and am[0].item() == 5
+    temp = torch.tensor([0.7, 1.0, 1.3, 1.0, 0.5, 1.0, 2.0, 1.0, 1.0], device=DEV)
+    top_k = torch.tensor([0, 50, 0, 5, 1000, 0, 40, 1, 0], dtype=torch.int32, device=DEV)
+    top_p = torch.tensor([1.0, 1.0, 0.9, 0.5, 0.95, 1.0, 0.8, 1.0, 0.3], device=DEV)
+    min_p = torch.tensor([0.0, 0.0, 0.0, 0.0, 0.0, 0.05, 0.02, 0.0, 0.0], device=DEV)
+    agree = total = 0
+    for trial in range(6):
+        u = torch.rand(rows, device=DEV)
+        got = cu().sample(logits, temp, top_k, top_p, min_p, u)
+        ref = R.sample(logits, temp, top_k, top_p, min_p, u)
+        probs = R.filtered_probs(logits, temp, top_k, top_p, min_p)
+        # every drawn token must be inside the reference keep-set
+        assert (probs.gather(-1, got.long().unsqueeze(-1)) > 0).all()
+        assert torch.equal(got, cu().sample(logits, temp, top_k, top_p, min_p, u))  # replay is exact
+        agree += (got == ref).sum().item()
+        total += rows
+    assert agree >= total - 3, f"only {agree}/{total} draws match the fp64 inverse-CDF reference"
+    assert cu().sample(logits, temp, top_k, top_p, min_p, torch.rand(rows, device=DEV))[7].item() == R.argmax(logits)[7].item()
+    picked = R.argmax(logits)
+    c1, tv1, ti1 = cu().logprobs_topk(logits, picked, 5)
+    c2, tv2, ti2 = R.logprobs_topk(logits, picked, 5)
+    assert (c1 - c2).abs().max().item() < 1e-3 and (tv1 - tv2).abs().max().item() < 1e-3
+    assert torch.equal(ti1[1:, 0].long(), ti2[1:, 0])
+    status_clean()
