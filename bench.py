@@ -242,8 +242,10 @@ def e2e(args, eng, rank, world, device):
     t_submit = time.perf_counter()
     streams = []
     for i in range(n):
-        s = eng.submit(Request(prompt_tokens=host_prompts[i].tolist(), params=SamplingParams(temperature=0.0, ignore_eos=True), max_tokens=out_len))
-        s.add_listener(lambda upd, i=i: stamps[i].extend([time.perf_counter()] * len(upd.tokens)))
+        s = eng.submit(
+            Request(prompt_tokens=host_prompts[i].tolist(), params=SamplingParams(temperature=0.0, ignore_eos=True), max_tokens=out_len),
+            listener=lambda upd, i=i: stamps[i].extend([time.perf_counter()] * len(upd.tokens)),
+        )
         streams.append(s)
     for s in streams:
         toks, term, _ = s.collect(1800)

@@ -36,6 +36,7 @@ int pg_qk_norm_rope_append(const void* qkv, long long ld, const void* q_w, const
 
 // ---- attention (attention.cu) ------------------------------------------------------
 int pg_decode_splits(int num_seqs, int hkv, int max_kv_len, int sms);
+void pg_attn_set_decode_stages(int stages);  // 2 (three CTAs per SM) or 3 (two CTAs per SM, default)
 int pg_paged_attention(const void* q, const void* kv, void* out, const void* q_indptr, const void* kv_lens, const void* table, int table_stride,
                        int num_seqs, int hq, int hkv, int dim, int page_size, long long num_pages, float scale, int mode, int splits,
                        void* part_o, void* part_lse, int q_tiles, int window, void* status, cudaStream_t stream);

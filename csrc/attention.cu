@@ -91,7 +91,7 @@ __device__ __forceinline__ int swz(int r, int ch) {
 // decode
 // -----------------------------------------------------------------------------------
 template <int D, int STAGES>
-__global__ void __launch_bounds__(128) decode_attn_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(128, (STAGES == 2 && D <= 128) ? 3 : 1) decode_attn_kernel(const AttnParams p) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   constexpr int TILE = 16;
   constexpr int CH = D / 8;            // 16-byte chunks per row
@@ -134,19 +134,25 @@ __global__ void __launch_bounds__(128) decode_attn_kernel(const AttnParams p) {
   for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
   float m_run = NEG_BIG, l_run = 0.f;
 
+  // A 16-token tile never straddles a page (page sizes are multiples of 16): one table
+  // lookup per tile, then plain strides.
+  const long long row_stride = (long long)p.hkv * D;
+  const long long v_plane = (long long)p.page_size * row_stride;
   auto issue = [&](int tile, int stage) {
     bf16* ks_ = wsm + stage * STAGE_ELEMS;
     bf16* vs_ = ks_ + TILE * D;
     if (tile < t_end) {
+      const int tok0 = tile * TILE;
+      const int page = table_row[tok0 / p.page_size];
+      const bf16* kbase = p.kv + ((long long)page * 2 * p.page_size + (tok0 % p.page_size)) * row_stride + (long long)h * D;
 #pragma unroll
       for (int i = 0; i < (TILE * CH) / 32; ++i) {
         const int c = lane + 32 * i;
         const int r = c / CH, ch = c % CH;
-        const int tok = tile * TILE + r;
-        const bool valid = tok < kv_len;
-        const int tk = valid ? tok : 0;
-        cp_async16(ks_ + swz<D>(r, ch), kv_row<D>(p, table_row, tk, h, 0) + ch * 8, valid);
-        cp_async16(vs_ + swz<D>(r, ch), kv_row<D>(p, table_row, tk, h, 1) + ch * 8, valid);
+        const bool valid = tok0 + r < kv_len;
+        const bf16* src = kbase + (valid ? r : 0) * row_stride + ch * 8;
+        cp_async16(ks_ + swz<D>(r, ch), src, valid);
+        cp_async16(vs_ + swz<D>(r, ch), src + v_plane, valid);
       }
     }
     cp_async_commit();
@@ -481,9 +487,10 @@ __global__ void __launch_bounds__(128) prefill_attn_kernel(const AttnParams p, i
   }
 }
 
-template <int D>
-int launch_decode(const AttnParams& p, cudaStream_t stream) {
-  constexpr int STAGES = 3;
+int g_decode_stages = 3;
+
+template <int D, int STAGES>
+int launch_decode_s(const AttnParams& p, cudaStream_t stream) {
   const size_t pipe = (size_t)4 * STAGES * 2 * 16 * D * 2;
   const size_t merge = (size_t)(4 * 8 * D + 64) * 4;
   const size_t smem = pipe > merge ? pipe : merge;
@@ -502,6 +509,12 @@ int launch_decode(const AttnParams& p, cudaStream_t stream) {
 }
 
 template <int D>
+int launch_decode(const AttnParams& p, cudaStream_t stream) {
+  if (g_decode_stages == 2) return launch_decode_s<D, 2>(p, stream);
+  return launch_decode_s<D, 3>(p, stream);
+}
+
+template <int D>
 int launch_prefill(const AttnParams& p, int q_tiles, int window, cudaStream_t stream) {
   const size_t smem = (size_t)2 * 2 * 64 * D * 2;
   static bool set = false;
@@ -517,14 +530,31 @@ int launch_prefill(const AttnParams& p, int q_tiles, int window, cudaStream_t st
 
 }  // namespace
 
+extern "C" void pg_attn_set_decode_stages(int stages) { g_decode_stages = stages == 2 ? 2 : 3; }
+
+// Number of KV splits per (sequence, kv head): fill the resident CTA slots
+// (`per_sm` CTAs per SM) with as little wave-quantisation loss as possible, keeping at
+// least four 16-token tiles per split.
 extern "C" int pg_decode_splits(int num_seqs, int hkv, int max_kv_len, int sms) {
   const int ctas = num_seqs * hkv;
-  int s = (4 * sms + ctas - 1) / ctas;
-  const int max_by_len = (max_kv_len + 63) / 64;  // at least four 16-token tiles per split
-  if (s > max_by_len) s = max_by_len;
-  if (s > 32) s = 32;
-  if (s < 1) s = 1;
-  return s;
+  const int per_sm = g_decode_stages == 2 ? 3 : 2;
+  const int slots = sms * per_sm;
+  int max_by_len = (max_kv_len + 63) / 64;
+  if (max_by_len < 1) max_by_len = 1;
+  if (max_by_len > 32) max_by_len = 32;
+  int best = 1;
+  double best_score = -1.0;
+  for (int s = 1; s <= max_by_len; ++s) {
+    const long long total = (long long)ctas * s;
+    const long long waves = (total + slots - 1) / slots;
+    double eff = (double)total / (double)(waves * slots);
+    eff -= 0.01 * (s - 1);  // each extra split costs merge traffic and a shorter main loop
+    if (eff > best_score + 1e-9) {
+      best_score = eff;
+      best = s;
+    }
+  }
+  return best;
 }
 
 // mode 0: decode (one query row per sequence), mode 1: prefill / mixed.

@@ -247,14 +247,38 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           __threadfence();
           const float* ws_tile = p.ws + ((size_t)tile * p.splits * p.bn) * BM + r;
           const int nmax = min(p.bn, p.T - n0);
-          if (m < p.M) {
-            for (int n = 0; n < nmax; ++n) {
-              float sum = 0.f;
-              for (int q = 0; q < p.splits; ++q) sum += __ldcg(ws_tile + ((size_t)q * p.bn + n) * BM);
-              if (p.y_f32)
-                p.y_f32[(size_t)(n0 + n) * p.ldy + m] = sum;
-              else
-                p.y[(size_t)(n0 + n) * p.ldy + m] = __float2bfloat16(sum);
+          // 16 columns at a time, four splits' loads in flight together: the loop is
+          // bound by L2 latency, so independent loads must not be serialised by stores
+          for (int c = 0; c < nmax; c += 16) {
+            float acc[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+            for (int q0 = 0; q0 < p.splits; q0 += 4) {
+              float tmp[4][16];
+#pragma unroll
+              for (int qq = 0; qq < 4; ++qq) {
+                const bool live = q0 + qq < p.splits;
+                const float* src = ws_tile + ((size_t)(live ? q0 + qq : q0) * p.bn + c) * BM;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) tmp[qq][j] = live ? __ldcg(src + (size_t)j * BM) : 0.f;
+              }
+#pragma unroll
+              for (int qq = 0; qq < 4; ++qq) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) acc[j] += tmp[qq][j];
+              }
+            }
+            if (m < p.M) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const int n = c + j;
+                if (n < nmax) {
+                  if (p.y_f32)
+                    p.y_f32[(size_t)(n0 + n) * p.ldy + m] = acc[j];
+                  else
+                    p.y[(size_t)(n0 + n) * p.ldy + m] = __float2bfloat16(acc[j]);
+                }
+              }
             }
           }
           if (et == 0) p.counters[tile] = 0u;
@@ -319,18 +343,22 @@ int pg_make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, long long rows, long
   return PG_OK;
 }
 
-static int pick_bn(int T) {
+static int pick_bn(int T, int M, int sms) {
   if (T <= 16) return 16;
   if (T <= 32) return 32;
   if (T <= 64) return 64;
   if (T <= 128) return 128;
-  // large T: the widest tile that wastes the least padding
-  int best = 256, best_waste = ceil_div(T, 256) * 256 - T;
-  for (int bn = 240; bn >= 128; bn -= 16) {
-    int waste = ceil_div(T, bn) * bn - T;
-    if (waste < best_waste) {
+  // large T: time ~ waves x (MMA time ~ bn, plus the fixed 128-row weight tile per stage)
+  const int m_tiles = ceil_div(M, BM);
+  int best = 256;
+  long long best_cost = -1;
+  for (int bn = 256; bn >= 128; bn -= 16) {
+    const long long tiles = (long long)m_tiles * ceil_div(T, bn);
+    const long long waves = (tiles + sms - 1) / sms;
+    const long long cost = waves * (bn + 64);
+    if (best_cost < 0 || cost < best_cost) {
       best = bn;
-      best_waste = waste;
+      best_cost = cost;
     }
   }
   return best;
@@ -339,6 +367,7 @@ static int pick_bn(int T) {
 // Pick the k-split count that minimises (wave quantisation) x (partial-sum overhead).
 static int pick_splits(int tiles, int kblocks, int bn, int sms) {
   if (tiles >= 4 * sms) return 1;
+  if (bn > 64 && tiles * 2 > sms) return 1;  // wide tiles: the f32 partial round trip costs more than the idle SMs
   int best = 1;
   double best_cost = 1e30;
   for (int s = 1; s <= 16; ++s) {
@@ -360,7 +389,7 @@ static int pick_splits(int tiles, int kblocks, int bn, int sms) {
 extern "C" int pg_gemm_workspace_bytes(int T, int M, int K, int device, long long* ws_bytes, long long* counter_bytes) {
   int sms = 0;
   PG_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
-  int bn = pick_bn(T);
+  int bn = pick_bn(T, M, sms);
   int tiles = ceil_div(M, BM) * ceil_div(T, bn);
   int splits = pick_splits(tiles, ceil_div(K, BK), bn, sms);
   *ws_bytes = splits > 1 ? (long long)tiles * splits * bn * BM * 4 : 0;
@@ -391,7 +420,7 @@ extern "C" int pg_gemm_bf16_tn(const void* x, const void* w, void* y, int y_is_f
     }
   }
   GemmParams p;
-  p.bn = pick_bn(T);
+  p.bn = pick_bn(T, M, di.sms);
   p.m_tiles = ceil_div(M, BM);
   p.n_tiles = ceil_div(T, p.bn);
   p.kblocks = ceil_div(K, BK);

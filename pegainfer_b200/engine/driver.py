@@ -113,10 +113,12 @@ class SchedulerHandle:
         self.alive = True
         self.waiting_hint = 0
 
-    def submit(self, request: Request) -> RequestStream:
+    def submit(self, request: Request, listener=None) -> RequestStream:
         rid = next(self._ids)
         queued = QueuedRequest(id=rid, request=request)
         stream = RequestStream(rid, queued, self.partition)
+        if listener is not None:
+            stream.add_listener(listener)
         with self._lock:
             self._streams[rid] = stream
             self.waiting_hint += 1
@@ -210,14 +212,17 @@ class Engine:
     def num_partitions(self) -> int:
         return len(self._handles)
 
-    def submit(self, request: Request) -> RequestStream:
+    def submit(self, request: Request, listener=None) -> RequestStream:
+        """Route and enqueue a request.  ``listener`` (called from the scheduler thread
+        for every update) is attached before the request becomes visible to the
+        scheduler, so no update can be missed."""
         rank = request.data_parallel_rank
         if rank is not None:
             if not (0 <= rank < len(self._handles)):
                 raise ValueError(f"data_parallel_rank {rank} out of range for {len(self._handles)} partitions")
-            return self._handles[rank].submit(request)
+            return self._handles[rank].submit(request, listener)
         handle = min(self._handles, key=lambda h: (h.load(), h.partition))
-        return handle.submit(request)
+        return handle.submit(request, listener)
 
     def metrics(self) -> list:
         return [h.metrics_cell.read() for h in self._handles]

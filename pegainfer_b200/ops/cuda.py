@@ -61,8 +61,20 @@ def ctx(device) -> _DeviceCtx:
     return c
 
 
+_TUNED = False
+
+
 def lib():
-    return _native.load()
+    global _TUNED
+    l = _native.load()
+    if not _TUNED:
+        import os
+
+        _TUNED = True
+        stages = os.environ.get("PEGAINFER_ATTN_STAGES")
+        if stages:
+            l.pg_attn_set_decode_stages(_ci(int(stages)))
+    return l
 
 
 def _check(rc, c: Optional[_DeviceCtx] = None, n: int = 1):
