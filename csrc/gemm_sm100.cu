@@ -464,3 +464,49 @@ extern "C" int pg_gemm_bf16_tn(const void* x, const void* w, void* y, int y_is_f
   PG_LAUNCH_CHECK();
   return PG_OK;
 }
+
+// ---------------------------------------------------------------------------------
+// Allocation-free variant (see gemm_noalloc.h): same kernel, scratch inside the image.
+// ---------------------------------------------------------------------------------
+#include "gemm_noalloc.h"
+
+// In host code this name is only a handle for cudaGetSymbolAddress, never a pointer
+// that a kernel could be given.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[PG_NOALLOC_SCRATCH_BYTES];
+
+static void* g_noalloc_ptr[64];
+static bool g_noalloc_ready[64];
+static std::mutex g_noalloc_mu;
+
+extern "C" int pg_gemm_bf16_tn_noalloc(const void* x, const void* w, void* y, int T, int M, int K, long long ldx, long long ldw, long long ldy,
+                                       void* status, cudaStream_t stream) {
+  PG_REQUIRE(T > 0 && M > 0 && K > 0, "gemm_noalloc: empty problem %dx%dx%d", T, M, K);
+  int dev = 0;
+  PG_CUDA(cudaGetDevice(&dev));
+  PG_REQUIRE(dev >= 0 && dev < 64, "gemm_noalloc: device ordinal %d out of range", dev);
+  void* scratch = nullptr;
+  int sms = 0;
+  {
+    // once per device, with that device current: resolve the device address of the array
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    if (!g_noalloc_ready[dev]) {
+      void* ptr = nullptr;
+      PG_CUDA(cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch));
+      PG_REQUIRE(ptr != nullptr, "gemm_noalloc: scratch symbol resolved to a null address");
+      g_noalloc_ptr[dev] = ptr;
+      g_noalloc_ready[dev] = true;
+    }
+    scratch = g_noalloc_ptr[dev];
+  }
+  PG_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const int bn = pick_bn(T, M, sms);
+  const long long tiles = (long long)ceil_div(M, BM) * ceil_div(T, bn);
+  PG_REQUIRE(tiles <= PG_NOALLOC_MAX_TILES,
+             "gemm_noalloc: %lld output tiles (M=%d, T=%d) exceed the built-in scratch limit of %d tiles; use pg_gemm_bf16_tn with caller scratch",
+             tiles, M, T, (int)PG_NOALLOC_MAX_TILES);
+  unsigned char* base = static_cast<unsigned char*>(scratch);
+  // the counters must start at zero; the partial sums are fully written before they are read
+  PG_CUDA(cudaMemsetAsync(base, 0, (size_t)tiles * 4, stream));
+  return pg_gemm_bf16_tn(x, w, y, 0, T, M, K, ldx, ldw, ldy, base + PG_NOALLOC_COUNTER_BYTES,
+                         (long long)PG_NOALLOC_SCRATCH_BYTES - PG_NOALLOC_COUNTER_BYTES, base, PG_NOALLOC_COUNTER_BYTES, status, 0, stream);
+}
