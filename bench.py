@@ -247,6 +247,7 @@ def e2e(args, eng, rank, world, device):
             listener=lambda upd, i=i: stamps[i].extend([time.perf_counter()] * len(upd.tokens)),
         )
         streams.append(s)
+    eng.start()  # every rank queued the same requests first: replicated schedulers stay in lockstep
     for s in streams:
         toks, term, _ = s.collect(1800)
         assert term.kind == "finished" and len(toks) == out_len, (term, len(toks))
@@ -296,7 +297,7 @@ def main():
     total_len = args.prompt_len + args.warmup + args.steps + 2 * page
     blocks = 2 * args.conc * ((total_len + page - 1) // page + 2) + 8
     ecfg = EngineConfig(preset=args.model, num_kv_blocks=blocks, kv_page_size=page, cuda_graph=True, max_decode_batch=max(args.conc, 8), max_model_len=total_len + page, max_prefill_tokens=4096, no_prefix_cache=True)
-    eng = build_engine(ecfg, mcfg, device=device, dtype=torch.bfloat16, tp=tp)
+    eng = build_engine(ecfg, mcfg, device=device, dtype=torch.bfloat16, tp=tp, start=False)
     try:
         ko = kernel_only(args, eng, rank, world, device)
         ee = None if args.no_e2e else e2e(args, eng, rank, world, device)

@@ -20,6 +20,20 @@ int pg_gemm_workspace_bytes(int T, int M, int K, int device, long long* ws_bytes
 int pg_gemm_bf16_tn(const void* x, const void* w, void* y, int y_is_f32, int T, int M, int K, long long ldx, long long ldw, long long ldy,
                     void* ws, long long ws_bytes, void* counters, long long counter_bytes, void* status, int force_splits,
                     cudaStream_t stream);
+int pg_gemm_bf16_tn_after_gather(const void* x, const void* w, void* y, int y_is_f32, int T, int M, int K, long long ldx, long long ldw,
+                                 long long ldy, void* ws, long long ws_bytes, void* counters, long long counter_bytes, void* status,
+                                 const void* wait_flags, int world, unsigned long long wait_ns, cudaStream_t stream);
+// Tensor-parallel fused path: GEMM -> reduce-scatter -> +residual -> RMSNorm -> all-gather over NVLink peer memory.
+int pg_tp_gemm_rs_norm_ag(const void* a, const void* w, int T, int hidden, int K, long long lda, long long ldw, void* const* part,
+                          void* const* xout, void* const* flags, int rank, int world, int site, void* residual, long long ld_res,
+                          const void* norm_w, float eps, int offset, unsigned long long wait_ns, void* ws, long long ws_bytes, void* counters,
+                          long long counter_bytes, void* status, cudaStream_t stream);
+int pg_tp_wait(const void* wait_flags, int world, unsigned long long wait_ns, void* status, cudaStream_t stream);
+int pg_symm_alloc(long long bytes, void** out);
+int pg_symm_free(void* p);
+int pg_ipc_export(void* p, void* handle64);
+int pg_ipc_import(const void* handle64, void** out);
+int pg_ipc_close(void* p);
 int pg_make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, long long rows, long long cols, long long ld, int box_rows, int box_cols);
 
 // ---- row kernels (elementwise.cu) --------------------------------------------------

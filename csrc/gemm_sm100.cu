@@ -19,6 +19,8 @@
 //
 // Takes the place of the reference's cuBLAS/cuBLASLt layer
 // (pegainfer-kernels/csrc/shared/linear.cu:294-596).
+#include <string.h>
+
 #include <mutex>
 #include <unordered_map>
 
@@ -33,7 +35,36 @@ constexpr int A_BYTES = BM * BK * 2;
 constexpr int NUM_THREADS = 192;
 constexpr int MAX_STAGES = 12;
 
+constexpr int MAX_RANKS = 8;
+constexpr int FLAG_WORDS_PER_SITE = 32;  // [0..7] tiles-done epoch per rank, [8..15] rows-delivered epoch per rank,
+                                         // [16] epoch, [17]/[18] local CTA counters of the two phases
+
+// Tensor-parallel tail fused behind the GEMM tiles: reduce-scatter of the f32 partials
+// over peer memory, + residual, RMSNorm, all-gather of the normalised rows.
+struct TpFuse {
+  int enabled;
+  int rank, world, site;
+  float* part[MAX_RANKS];      // every rank's partial buffer [T, hidden] f32 (peer mapped)
+  bf16* xout[MAX_RANKS];       // every rank's normalised-activation buffer [T, hidden]
+  uint32_t* flags[MAX_RANKS];  // every rank's flag block
+  bf16* residual;              // local [T, hidden]; rows owned by this rank are read and updated
+  long long ld_res;
+  const bf16* norm_w;
+  float eps;
+  int offset;
+  unsigned long long wait_ns;
+};
+
+// Consumer side: X rows arrive from peers; wait for every rank's rows-delivered epoch.
+struct WaitSpec {
+  const uint32_t* flags;  // local flag block of the producing site (nullptr = no wait)
+  int world;
+  unsigned long long wait_ns;
+};
+
 struct GemmParams {
+  TpFuse tp;
+  WaitSpec wait;
   bf16* y;
   float* y_f32;
   long long ldy;
@@ -58,6 +89,25 @@ __device__ __forceinline__ bool named_bar_all(int id, int nthreads, bool pred) {
       : "r"((uint32_t)pred), "r"(id), "r"(nthreads)
       : "memory");
   return r != 0;
+}
+
+// Wait until flags[0..n) >= target (monotonic epochs written by peers with release.sys).
+__device__ __forceinline__ bool wait_epochs(const uint32_t* flags, int n, uint32_t target, unsigned long long limit_ns, uint32_t* status,
+                                            uint32_t site) {
+  const uint64_t t0 = globaltimer_ns();
+  for (int q = 0; q < n; ++q) {
+    uint32_t spins = 0;
+    while ((int32_t)(ld_acquire_sys(flags + q) - target) < 0) {
+      if ((++spins & 15u) == 0u) {
+        if (*((volatile uint32_t*)status) != PG_ST_OK) return false;
+        if (globaltimer_ns() - t0 > limit_ns) {
+          atomicCAS(status, PG_ST_OK, PG_ST_TIMEOUT | (site << 8) | ((uint32_t)q << 16));
+          return false;
+        }
+      }
+    }
+  }
+  return true;
 }
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -100,6 +150,9 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // epoch of the fused tail, read by every CTA before any CTA can advance it
+  uint32_t tp_epoch = 0;
+  if (p.tp.enabled) tp_epoch = *((volatile uint32_t*)(p.tp.flags[p.tp.rank] + p.tp.site * FLAG_WORDS_PER_SITE + 16));
 
   const int total = p.m_tiles * p.n_tiles * p.splits;
 
@@ -117,12 +170,38 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         last_phase[s] = 0;
       }
       bool ok = true;
+      bool x_ready = p.wait.flags == nullptr;
       for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
         const int tile = item / p.splits, s = item - tile * p.splits;
         const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
         const int kb0 = (int)(((long long)p.kblocks * s) / p.splits);
         const int kb1 = (int)(((long long)p.kblocks * (s + 1)) / p.splits);
-        for (int kb = kb0; kb < kb1; ++kb) {
+        int kb = kb0;
+        if (!x_ready) {
+          // The X rows come from peers (all-gather fused into this GEMM): stream the first
+          // weight tiles while they travel, then wait for every rank's delivery epoch and
+          // make the peer writes visible to the async proxy before TMA reads X.
+          const int pre = min(p.stages, kb1 - kb0);
+          for (int i = 0; i < pre; ++i) {
+            mbar_expect_tx(&full[i], (uint32_t)stage_bytes);
+            tma_load_2d(tiles + i * stage_bytes, &tm_w, &full[i], (kb0 + i) * BK, m_tile * BM, pol_w);
+            used[i] = true;
+            last_phase[i] = 0;
+          }
+          const uint32_t target = *((volatile const uint32_t*)(p.wait.flags + 16));
+          wait_epochs(p.wait.flags + 8, p.wait.world, target, p.wait.wait_ns, p.status, 2u);
+          fence_proxy_async_all();
+          x_ready = true;
+          for (int i = 0; i < pre; ++i)
+            tma_load_2d(tiles + i * stage_bytes + A_BYTES, &tm_x, &full[i], (kb0 + i) * BK, n_tile * p.bn, pol_x);
+          kb = kb0 + pre;
+          stage = pre;
+          if (stage == p.stages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        for (; kb < kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag)) {
             ok = false;
             break;
@@ -295,6 +374,113 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     tmem_dealloc(tmem_base, p.tmem_cols);
   }
   if (threadIdx.x == 0 && *abort_flag) atomicCAS(p.status, PG_ST_OK, PG_ST_TIMEOUT | (1u << 8));
+
+  if (p.tp.enabled) {
+    // ---- reduce-scatter + residual + RMSNorm + all-gather over peer memory ----
+    const TpFuse& tp = p.tp;
+    const int H = p.M;
+    uint32_t* myflags = tp.flags[tp.rank] + tp.site * FLAG_WORDS_PER_SITE;
+    const uint32_t next = tp_epoch + 1u;
+    float* red = reinterpret_cast<float*>(tiles);       // pipeline smem is idle now
+    uint32_t* s_ok = reinterpret_cast<uint32_t*>(tiles) + 64;
+    // phase 1 done: the last CTA of this GPU tells every rank that all partial tiles are stored
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      const uint32_t old = atomicAdd(&myflags[17], 1u);
+      if (old == gridDim.x - 1) {
+        myflags[17] = 0u;
+        for (int q = 0; q < tp.world; ++q) st_release_sys(tp.flags[q] + tp.site * FLAG_WORDS_PER_SITE + tp.rank, next);
+      }
+    }
+    const int rows_per = (p.T + tp.world - 1) / tp.world;
+    const int r0 = tp.rank * rows_per;
+    const int r1 = min(p.T, r0 + rows_per);
+    if (r0 + (int)blockIdx.x < r1) {
+      if (threadIdx.x == 0) *s_ok = wait_epochs(myflags, tp.world, next, tp.wait_ns, p.status, 3u) ? 1u : 0u;
+      __syncthreads();
+      const bool ok = *s_ok != 0u;
+      constexpr int MAXI = 11;  // hidden <= 192 * 11 * 4 = 8448
+      const int nvec = H / 4;
+      for (int row = r0 + blockIdx.x; row < r1 && ok; row += gridDim.x) {
+        float v[MAXI][4];
+        float ss = 0.f;
+#pragma unroll
+        for (int it = 0; it < MAXI; ++it) {
+          const int i = threadIdx.x + it * NUM_THREADS;
+          if (i < nvec) {
+            float4 part[MAX_RANKS];
+#pragma unroll
+            for (int q = 0; q < MAX_RANKS; ++q)
+              if (q < tp.world) part[q] = __ldcg(reinterpret_cast<const float4*>(tp.part[q] + (size_t)row * H) + i);
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int q = 0; q < MAX_RANKS; ++q)
+              if (q < tp.world) {
+                a.x += part[q].x;
+                a.y += part[q].y;
+                a.z += part[q].z;
+                a.w += part[q].w;
+              }
+            bf162* rp = reinterpret_cast<bf162*>(tp.residual + (size_t)row * tp.ld_res) + 2 * i;
+            const float2 ra = __bfloat1622float2(rp[0]), rb = __bfloat1622float2(rp[1]);
+            const bf162 n0 = __floats2bfloat162_rn(a.x + ra.x, a.y + ra.y), n1 = __floats2bfloat162_rn(a.z + rb.x, a.w + rb.y);
+            rp[0] = n0;
+            rp[1] = n1;
+            const float2 f0 = __bfloat1622float2(n0), f1 = __bfloat1622float2(n1);
+            v[it][0] = f0.x;
+            v[it][1] = f0.y;
+            v[it][2] = f1.x;
+            v[it][3] = f1.y;
+            ss += f0.x * f0.x + f0.y * f0.y + f1.x * f1.x + f1.y * f1.y;
+          }
+        }
+        ss = block_sum(ss, red);
+        const float inv = rsqrtf(ss / (float)H + tp.eps);
+#pragma unroll
+        for (int it = 0; it < MAXI; ++it) {
+          const int i = threadIdx.x + it * NUM_THREADS;
+          if (i < nvec) {
+            const bf162* wp = reinterpret_cast<const bf162*>(tp.norm_w) + 2 * i;
+            float2 w0 = __bfloat1622float2(wp[0]), w1 = __bfloat1622float2(wp[1]);
+            if (tp.offset) {
+              w0.x += 1.f;
+              w0.y += 1.f;
+              w1.x += 1.f;
+              w1.y += 1.f;
+            }
+            uint2 packed;
+            bf162 o0 = __floats2bfloat162_rn(v[it][0] * inv * w0.x, v[it][1] * inv * w0.y);
+            bf162 o1 = __floats2bfloat162_rn(v[it][2] * inv * w1.x, v[it][3] * inv * w1.y);
+            packed.x = *reinterpret_cast<uint32_t*>(&o0);
+            packed.y = *reinterpret_cast<uint32_t*>(&o1);
+#pragma unroll
+            for (int q = 0; q < MAX_RANKS; ++q)
+              if (q < tp.world) reinterpret_cast<uint2*>(tp.xout[q] + (size_t)row * H)[i] = packed;
+          }
+        }
+      }
+    }
+    // phase 2 done: the last CTA publishes "rows of this rank delivered" and advances the epoch
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      const uint32_t old = atomicAdd(&myflags[18], 1u);
+      if (old == gridDim.x - 1) {
+        myflags[18] = 0u;
+        for (int q = 0; q < tp.world; ++q) st_release_sys(tp.flags[q] + tp.site * FLAG_WORDS_PER_SITE + 8 + tp.rank, next);
+        __threadfence();
+        *((volatile uint32_t*)&myflags[16]) = next;
+      }
+    }
+  }
+}
+
+// Stand-alone wait for consumers of all-gathered rows that are not this GEMM.
+__global__ void tp_wait_kernel(WaitSpec w, uint32_t* status) {
+  if (threadIdx.x == 0) {
+    const uint32_t target = *((volatile const uint32_t*)(w.flags + 16));
+    wait_epochs(w.flags + 8, w.world, target, w.wait_ns, status, 4u);
+  }
 }
 
 // ---------------------------------------------------------------------------------
@@ -401,9 +587,9 @@ extern "C" int pg_gemm_workspace_bytes(int T, int M, int K, int device, long lon
 // `ws`/`counters` are caller-provided scratch (see pg_gemm_workspace_bytes); the counters
 // must be zero before the first use and are left zero by every completed launch.
 // `force_splits` > 0 pins the k-split count (batch-invariant serving); 0 = heuristic.
-extern "C" int pg_gemm_bf16_tn(const void* x, const void* w, void* y, int y_is_f32, int T, int M, int K, long long ldx, long long ldw,
-                               long long ldy, void* ws, long long ws_bytes, void* counters, long long counter_bytes, void* status,
-                               int force_splits, cudaStream_t stream) {
+static int gemm_impl(const void* x, const void* w, void* y, int y_is_f32, int T, int M, int K, long long ldx, long long ldw, long long ldy,
+                     void* ws, long long ws_bytes, void* counters, long long counter_bytes, void* status, int force_splits,
+                     const TpFuse* tp, const WaitSpec* wait, cudaStream_t stream) {
   PG_REQUIRE(T > 0 && M > 0 && K > 0, "gemm: empty problem %dx%dx%d", T, M, K);
   PG_REQUIRE(K % 8 == 0, "gemm: K=%d must be a multiple of 8 (16-byte TMA rows)", K);
   PG_REQUIRE(status != nullptr, "gemm: a device status word is required");
@@ -420,6 +606,9 @@ extern "C" int pg_gemm_bf16_tn(const void* x, const void* w, void* y, int y_is_f
     }
   }
   GemmParams p;
+  memset(&p, 0, sizeof(p));
+  if (tp) p.tp = *tp;
+  if (wait) p.wait = *wait;
   p.bn = pick_bn(T, M, di.sms);
   p.m_tiles = ceil_div(M, BM);
   p.n_tiles = ceil_div(T, p.bn);
@@ -462,6 +651,95 @@ extern "C" int pg_gemm_bf16_tn(const void* x, const void* w, void* y, int y_is_f
   const size_t smem = 1024 + (size_t)p.stages * stage_bytes + tail;
   gemm_bf16_tn_kernel<<<grid, NUM_THREADS, smem, stream>>>(tm_w, tm_x, p);
   PG_LAUNCH_CHECK();
+  return PG_OK;
+}
+
+extern "C" int pg_gemm_bf16_tn(const void* x, const void* w, void* y, int y_is_f32, int T, int M, int K, long long ldx, long long ldw,
+                               long long ldy, void* ws, long long ws_bytes, void* counters, long long counter_bytes, void* status,
+                               int force_splits, cudaStream_t stream) {
+  return gemm_impl(x, w, y, y_is_f32, T, M, K, ldx, ldw, ldy, ws, ws_bytes, counters, counter_bytes, status, force_splits, nullptr, nullptr, stream);
+}
+
+// Same GEMM, but X rows are being all-gathered into `x` by peers: the TMA producer streams
+// weight tiles first, then waits for every rank's rows-delivered epoch in `wait_flags` (the
+// local flag block of the producing site).
+extern "C" int pg_gemm_bf16_tn_after_gather(const void* x, const void* w, void* y, int y_is_f32, int T, int M, int K, long long ldx,
+                                            long long ldw, long long ldy, void* ws, long long ws_bytes, void* counters, long long counter_bytes,
+                                            void* status, const void* wait_flags, int world, unsigned long long wait_ns, cudaStream_t stream) {
+  WaitSpec ws_;
+  ws_.flags = (const uint32_t*)wait_flags;
+  ws_.world = world;
+  ws_.wait_ns = wait_ns;
+  return gemm_impl(x, w, y, y_is_f32, T, M, K, ldx, ldw, ldy, ws, ws_bytes, counters, counter_bytes, status, 0, nullptr,
+                   wait_flags ? &ws_ : nullptr, stream);
+}
+
+// Row-parallel projection fused with its collective:  partial = a[T, K_local] * w[hidden, K_local]^T
+// (tcgen05 tiles, f32) -> reduce-scatter over peer memory (fixed rank order) -> + residual ->
+// RMSNorm -> all-gather of the normalised rows into every rank's `xout`.  `part`, `xout`,
+// `flags` are arrays of `world` peer-mapped pointers (index = rank).  Consumers of `xout`
+// wait on flags[rank] + site * 32 (pg_gemm_bf16_tn_after_gather or pg_tp_wait).
+extern "C" int pg_tp_gemm_rs_norm_ag(const void* a, const void* w, int T, int hidden, int K, long long lda, long long ldw, void* const* part,
+                                     void* const* xout, void* const* flags, int rank, int world, int site, void* residual, long long ld_res,
+                                     const void* norm_w, float eps, int offset, unsigned long long wait_ns, void* ws, long long ws_bytes,
+                                     void* counters, long long counter_bytes, void* status, cudaStream_t stream) {
+  PG_REQUIRE(world >= 1 && world <= MAX_RANKS && rank >= 0 && rank < world, "tp gemm: bad rank %d / world %d", rank, world);
+  PG_REQUIRE(hidden % 8 == 0 && hidden <= NUM_THREADS * 11 * 4, "tp gemm: hidden %d must be a multiple of 8 and <= %d", hidden, NUM_THREADS * 11 * 4);
+  PG_REQUIRE(site >= 0 && site < 1024, "tp gemm: site %d out of range", site);
+  TpFuse tp;
+  memset(&tp, 0, sizeof(tp));
+  tp.enabled = 1;
+  tp.rank = rank;
+  tp.world = world;
+  tp.site = site;
+  for (int q = 0; q < world; ++q) {
+    tp.part[q] = (float*)part[q];
+    tp.xout[q] = (bf16*)xout[q];
+    tp.flags[q] = (uint32_t*)flags[q];
+  }
+  tp.residual = (bf16*)residual;
+  tp.ld_res = ld_res;
+  tp.norm_w = (const bf16*)norm_w;
+  tp.eps = eps;
+  tp.offset = offset;
+  tp.wait_ns = wait_ns;
+  return gemm_impl(a, w, part[rank], 1, T, hidden, K, lda, ldw, hidden, ws, ws_bytes, counters, counter_bytes, status, 0, &tp, nullptr, stream);
+}
+
+extern "C" int pg_tp_wait(const void* wait_flags, int world, unsigned long long wait_ns, void* status, cudaStream_t stream) {
+  WaitSpec w_;
+  w_.flags = (const uint32_t*)wait_flags;
+  w_.world = world;
+  w_.wait_ns = wait_ns;
+  tp_wait_kernel<<<1, 32, 0, stream>>>(w_, (uint32_t*)status);
+  PG_LAUNCH_CHECK();
+  return PG_OK;
+}
+
+// ---- peer memory plumbing (one process per GPU; handles travel through torch.distributed) ----
+extern "C" int pg_symm_alloc(long long bytes, void** out) {
+  PG_CUDA(cudaMalloc(out, (size_t)bytes));
+  PG_CUDA(cudaMemset(*out, 0, (size_t)bytes));
+  return PG_OK;
+}
+extern "C" int pg_symm_free(void* p) {
+  PG_CUDA(cudaFree(p));
+  return PG_OK;
+}
+extern "C" int pg_ipc_export(void* p, void* handle64) {
+  cudaIpcMemHandle_t h;
+  PG_CUDA(cudaIpcGetMemHandle(&h, p));
+  memcpy(handle64, &h, sizeof(h));
+  return PG_OK;
+}
+extern "C" int pg_ipc_import(const void* handle64, void** out) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  PG_CUDA(cudaIpcOpenMemHandle(out, h, cudaIpcMemLazyEnablePeerAccess));
+  return PG_OK;
+}
+extern "C" int pg_ipc_close(void* p) {
+  PG_CUDA(cudaIpcCloseMemHandle(p));
   return PG_OK;
 }
 

@@ -64,7 +64,7 @@ def profile_kv_blocks(model, ecfg: EngineConfig, page_size: int) -> int:
     return max(0, budget // per_block)
 
 
-def build_engine(ecfg: EngineConfig, mcfg: Optional[ModelConfig] = None, device=None, dtype=None, tp: TPContext = SINGLE, ep=None, model=None):
+def build_engine(ecfg: EngineConfig, mcfg: Optional[ModelConfig] = None, device=None, dtype=None, tp: TPContext = SINGLE, ep=None, model=None, start: bool = True):
     ecfg.validate()
     mcfg = mcfg or resolve_model_config(ecfg)
     if device is None:
@@ -112,6 +112,6 @@ def build_engine(ecfg: EngineConfig, mcfg: Optional[ModelConfig] = None, device=
         vocab_size=mcfg.vocab_size,
         eos_token_ids=tuple(mcfg.eos_token_ids),
     )
-    eng = Engine([sched], info)
+    eng = Engine([sched], info, start=start)
     eng.model, eng.executor, eng.scheduler, eng.pool, eng.kv = model, executor, sched, pool, kv
     return eng

@@ -187,7 +187,7 @@ def drive(scheduler, handle: SchedulerHandle, stop: threading.Event, idle_sleep:
 class Engine:
     """One engine identity fronting ``len(schedulers)`` partitions."""
 
-    def __init__(self, schedulers: list, info: EngineInfo, lora_client=None):
+    def __init__(self, schedulers: list, info: EngineInfo, lora_client=None, start: bool = True):
         if not schedulers:
             raise ValueError("an engine needs at least one scheduler")
         self.info = info
@@ -197,7 +197,16 @@ class Engine:
         self._stop = threading.Event()
         self._threads = []
         self._errors: list = []
-        for i, (s, h) in enumerate(zip(schedulers, self._handles)):
+        if start:
+            self.start()
+
+    def start(self) -> None:
+        """Spawn the scheduler threads.  An engine built with ``start=False`` queues
+        submissions until then, which gives replicated (SPMD) ranks an identical,
+        timing-independent admission order."""
+        if self._threads:
+            return
+        for i, (s, h) in enumerate(zip(self._schedulers, self._handles)):
             t = threading.Thread(target=self._run, args=(s, h), name=f"scheduler-{i}", daemon=True)
             t.start()
             self._threads.append(t)

@@ -125,21 +125,23 @@ class Qwen3Model:
         ``self.last_aux`` (speculative drafters consume target hidden states)."""
         cfg, tp = self.cfg, self.tp
         eps = cfg.rms_eps
+        tp.begin_step()
         residual = ops.embedding(token_ids, self.embed)
         x = ops.rms_norm(residual, self.layers[0].input_norm, eps)
         aux = []
         n = len(self.layers)
         for i, l in enumerate(self.layers):
-            qkv = ops.linear(x, l.qkv)
+            qkv = tp.col_linear(x, l.qkv)
             q = ops.qk_norm_rope_append(qkv, l.q_norm, l.k_norm, self.cos, self.sin, meta, kv.layer(i), self.q_heads, self.kv_heads, cfg.head_dim, eps)
             a = ops.paged_attention(q, kv.layer(i), meta)
             x = tp.row_linear_add_norm(a, l.o, residual, l.post_norm, eps)
-            act = ops.swiglu(ops.linear(x, l.gate_up))
+            act = ops.swiglu(tp.col_linear(x, l.gate_up))
             next_norm = self.layers[i + 1].input_norm if i + 1 < n else self.final_norm
             x = tp.row_linear_add_norm(act, l.down, residual, next_norm, eps)
             if i in aux_layers:
                 aux.append(residual.clone())
         self.last_aux = aux
+        tp.sync()
         return x
 
     def logits(self, hidden: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -46,6 +46,9 @@ class AttnMeta:
     h_kv_lens: Optional[list] = None
     # per-step scratch planned by the CUDA path (split-KV partials etc.)
     plan: Optional[object] = None
+    # recurrent-state slot of every sequence (hybrid linear-attention models)
+    state_slots: Optional[torch.Tensor] = None  # int32 [B]
+    h_state_slots: Optional[list] = None
 
 
 # ----------------------------------------------------------------------------------
@@ -304,3 +307,229 @@ def sample(logits, temperature, top_k, top_p, min_p, u):
     ok = probs.gather(-1, idx.unsqueeze(-1)).squeeze(-1) > 0
     fallback = probs.argmax(-1)
     return torch.where(ok, idx, fallback).to(torch.int32)
+
+
+# ----------------------------------------------------------------------------------
+# MoE routing and experts
+# ----------------------------------------------------------------------------------
+def router_topk(logits, top_k, scoring="softmax", bias=None, n_group=1, topk_group=1, norm_topk_prob=False, scale=1.0):
+    """Expert selection.  ``logits`` [T, E] f32.  Returns (ids int32 [T,k], weights f32 [T,k]).
+
+    softmax: probabilities over all experts, top-k by probability.
+    sigmoid: scores = sigmoid(logits); selection on ``scores + bias`` restricted to the
+    ``topk_group`` best of ``n_group`` expert groups (group score = sum of its two best
+    biased scores); weights come from the un-biased scores.
+    Ties resolve to the lowest expert id; ids are returned in selection order
+    (descending score).  Weights are renormalised to sum 1 when ``norm_topk_prob`` and
+    multiplied by ``scale``."""
+    lf = logits.float()
+    t, e = lf.shape
+    scores = torch.softmax(lf, -1) if scoring == "softmax" else torch.sigmoid(lf)
+    choice = scores + bias.float() if bias is not None else scores
+    if n_group > 1:
+        g = choice.view(t, n_group, e // n_group)
+        gscore = g.topk(min(2, e // n_group), dim=-1).values.sum(-1)
+        # stable: prefer lower group index on ties
+        order = torch.argsort(-gscore, dim=-1, stable=True)[:, :topk_group]
+        gmask = torch.zeros(t, n_group, dtype=torch.bool, device=lf.device).scatter_(1, order, True)
+        choice = choice.masked_fill(~gmask.unsqueeze(-1).expand_as(g).reshape(t, e), float("-inf"))
+    ids = torch.argsort(-choice, dim=-1, stable=True)[:, :top_k]
+    w = scores.gather(-1, ids)
+    if norm_topk_prob:
+        w = w / (w.sum(-1, keepdim=True) + 1e-20)
+    return ids.to(torch.int32), (w * scale).float()
+
+
+def dequant_int4_g32(packed, scales, group=32):
+    """compressed-tensors pack-quantized INT4: ``packed`` int32 [out, K/8] holds eight
+    offset-binary nibbles (value = nibble - 8), low nibble = lowest k; ``scales``
+    [out, K/group].  Returns the dequantised matrix in the scale dtype."""
+    out, k8 = packed.shape
+    shifts = torch.arange(0, 32, 4, device=packed.device, dtype=torch.int32)
+    nib = (packed.unsqueeze(-1) >> shifts) & 0xF
+    q = (nib.to(torch.int32) - 8).reshape(out, k8 * 8).float()
+    s = scales.float().repeat_interleave(group, dim=1)
+    return (q * s).to(scales.dtype)
+
+
+def quant_int4_g32(w, group=32):
+    """Symmetric INT4 group quantisation (inverse of ``dequant_int4_g32``)."""
+    out, k = w.shape
+    wf = w.float().view(out, k // group, group)
+    s = (wf.abs().amax(-1) / 7.0).clamp_min(1e-8)
+    q = torch.clamp(torch.round(wf / s.unsqueeze(-1)), -8, 7).to(torch.int32) + 8
+    q = q.view(out, k // 8, 8)
+    shifts = torch.arange(0, 32, 4, device=w.device, dtype=torch.int32)
+    # keep the bit pattern: pack in int64 then reinterpret the low 32 bits
+    packed64 = (q.to(torch.int64) << shifts.to(torch.int64)).sum(-1)
+    packed = (packed64 & 0xFFFFFFFF)
+    packed = torch.where(packed >= 2 ** 31, packed - 2 ** 32, packed).to(torch.int32)
+    return packed, s.to(w.dtype)
+
+
+def dequant_fp8_block(w_fp8, scale_inv, block=128):
+    """Block-scaled FP8 e4m3: ``w = fp8 * scale_inv[block_row, block_col]``."""
+    out, k = w_fp8.shape
+    s = scale_inv.float().repeat_interleave(block, 0)[:out].repeat_interleave(block, 1)[:, :k]
+    return (w_fp8.float() * s).to(torch.bfloat16)
+
+
+def moe_experts(x, ids, weights, w13, w2, expert_offset=0):
+    """Routed experts on local weights.  ``w13`` [E_local, 2I, H] (gate rows then up
+    rows), ``w2`` [E_local, H, I].  Tokens routed to experts outside
+    [expert_offset, expert_offset + E_local) contribute nothing.  Returns f32 [T, H]
+    (sum over the local selections of weight * expert(x))."""
+    t, h = x.shape
+    e_local = w13.shape[0]
+    out = torch.zeros(t, h, dtype=torch.float32, device=x.device)
+    for e in range(e_local):
+        sel = ids == (e + expert_offset)
+        rows = sel.any(-1).nonzero().flatten()
+        if rows.numel() == 0:
+            continue
+        xe = x[rows]
+        act = swiglu(linear(xe, w13[e]))
+        ye = linear(act, w2[e]).float()
+        we = (weights * sel.float()).sum(-1)[rows]
+        out.index_add_(0, rows, ye * we.unsqueeze(-1))
+    return out
+
+
+# ----------------------------------------------------------------------------------
+# MLA (multi-head latent attention), absorbed form over a paged latent cache
+# ----------------------------------------------------------------------------------
+def mla_append(kv_a, kv_norm_w, cos, sin, meta: AttnMeta, latent_layer, kv_lora, eps):
+    """Normalise the compressed KV, rotate the shared rope key (interleaved-pair input,
+    half-split output) and append ``[ckv | k_pe]`` rows to the paged latent cache
+    ``[pages, page_size, kv_lora + rope]``."""
+    ckv = rms_norm(kv_a[:, :kv_lora], kv_norm_w, eps)
+    pos = meta.positions.long()
+    kpe = _rope_interleaved_in(kv_a[:, kv_lora:].unsqueeze(1), cos[pos], sin[pos]).squeeze(1)
+    ps = meta.page_size
+    slots = meta.slot_mapping.long()
+    latent_layer[slots // ps, slots % ps] = torch.cat([ckv, kpe], -1)
+
+
+def mla_rope_q(q, cos, sin, meta: AttnMeta, nope):
+    """q [T, H, nope + rope]: rotate the rope tail (interleaved input -> half-split)."""
+    pos = meta.positions.long()
+    qpe = _rope_interleaved_in(q[..., nope:], cos[pos], sin[pos])
+    return torch.cat([q[..., :nope], qpe], -1)
+
+
+def mla_attention(q, w_uk, w_uv, latent_layer, meta: AttnMeta, scale, kv_lora):
+    """Absorbed MLA: ``q`` [T, H, nope + rope] (rope already applied), ``w_uk``
+    [H, nope, kv_lora], ``w_uv`` [H, v, kv_lora].  Returns [T, H * v]."""
+    t, h, _ = q.shape
+    nope = w_uk.shape[1]
+    v = w_uv.shape[1]
+    q_abs = torch.einsum("thn,hnc->thc", q[..., :nope].float(), w_uk.float()).to(q.dtype)
+    q_pe = q[..., nope:]
+    out = torch.zeros(t, h, v, dtype=q.dtype, device=q.device)
+    qi = meta.h_q_indptr if meta.h_q_indptr is not None else meta.q_indptr.tolist()
+    kl = meta.h_kv_lens if meta.h_kv_lens is not None else meta.kv_lens.tolist()
+    ps = meta.page_size
+    for b in range(meta.num_seqs):
+        q0, q1 = qi[b], qi[b + 1]
+        if q1 == q0 or kl[b] == 0:
+            continue
+        pages = meta.block_table[b, : (kl[b] + ps - 1) // ps].long()
+        lat = latent_layer[pages].reshape(-1, latent_layer.shape[-1])[: kl[b]].float()
+        ckv, kpe = lat[:, :kv_lora], lat[:, kv_lora:]
+        s = (torch.einsum("qhc,kc->hqk", q_abs[q0:q1].float(), ckv) + torch.einsum("qhr,kr->hqk", q_pe[q0:q1].float(), kpe)) * scale
+        n = q1 - q0
+        qpos = torch.arange(kl[b] - n, kl[b], device=q.device).view(1, n, 1)
+        kpos = torch.arange(kl[b], device=q.device).view(1, 1, -1)
+        s = s.masked_fill(kpos > qpos, float("-inf"))
+        p = torch.softmax(s, -1)
+        lo = torch.einsum("hqk,kc->qhc", p, ckv).to(q.dtype)
+        out[q0:q1] = torch.einsum("qhc,hvc->qhv", lo.float(), w_uv.float()).to(q.dtype)
+    return out.reshape(t, h * v)
+
+
+def moe_experts_int4(x, ids, weights, w13_packed, w13_scale, w2_packed, w2_scale, expert_offset=0, group=32):
+    """``moe_experts`` over INT4 group-quantised weights (dequantised per expert)."""
+    t, h = x.shape
+    e_local = w13_packed.shape[0]
+    out = torch.zeros(t, h, dtype=torch.float32, device=x.device)
+    for e in range(e_local):
+        sel = ids == (e + expert_offset)
+        rows = sel.any(-1).nonzero().flatten()
+        if rows.numel() == 0:
+            continue
+        w13 = dequant_int4_g32(w13_packed[e], w13_scale[e], group).to(x.dtype)
+        w2 = dequant_int4_g32(w2_packed[e], w2_scale[e], group).to(x.dtype)
+        act = swiglu(linear(x[rows], w13))
+        ye = linear(act, w2).float()
+        we = (weights * sel.float()).sum(-1)[rows]
+        out.index_add_(0, rows, ye * we.unsqueeze(-1))
+    return out
+
+
+# ----------------------------------------------------------------------------------
+# Gated DeltaNet (linear attention with a gated delta-rule recurrent state)
+# ----------------------------------------------------------------------------------
+def gdn_conv1d(x, conv_w, conv_state, meta: AttnMeta):
+    """Causal depthwise conv (kernel K) + SiLU over ragged sequences with carried state.
+    ``x`` [T, C]; ``conv_w`` [C, K]; ``conv_state`` [slots, C, K-1] holds the last K-1
+    inputs of each sequence and is updated in place.  The pre-activation sum is rounded
+    to the activation dtype before SiLU."""
+    t, c = x.shape
+    k = conv_w.shape[1]
+    out = torch.empty_like(x)
+    qi = meta.h_q_indptr if meta.h_q_indptr is not None else meta.q_indptr.tolist()
+    slots = meta.h_state_slots if meta.h_state_slots is not None else meta.state_slots.tolist()
+    wf = conv_w.float()
+    for b in range(meta.num_seqs):
+        q0, q1 = qi[b], qi[b + 1]
+        if q1 == q0 or slots[b] < 0:
+            out[q0:q1] = 0
+            continue
+        st = conv_state[slots[b]]  # [C, K-1]
+        seq = torch.cat([st.t().to(x.dtype), x[q0:q1]], 0)  # [K-1+n, C]
+        win = seq.float().unfold(0, k, 1)  # [n, C, K]
+        pre = (win * wf.unsqueeze(0)).sum(-1).to(x.dtype).float()
+        out[q0:q1] = (pre * torch.sigmoid(pre)).to(x.dtype)
+        conv_state[slots[b]] = seq[-(k - 1):].t().to(conv_state.dtype)
+    return out
+
+
+def gdn_gates(a, b, a_log, dt_bias):
+    """``g = -exp(A_log) * softplus(a + dt_bias)`` (f32), ``beta = sigmoid(b)`` (f32)."""
+    x = a.float() + dt_bias.float()
+    sp = torch.where(x > 20.0, x, torch.log1p(torch.exp(x)))
+    return -torch.exp(a_log.float()) * sp, torch.sigmoid(b.float())
+
+
+def gdn_recurrent(q, k, v, g, beta, state, meta: AttnMeta):
+    """Token-by-token gated delta rule.  ``q, k`` [T, Hk, Dk], ``v`` [T, Hv, Dv], ``g, beta``
+    [T, Hv] f32, ``state`` [slots, Hv, Dk, Dv] f32 updated in place.  Returns [T, Hv, Dv]."""
+    t, hk, dk = q.shape
+    hv, dv = v.shape[1], v.shape[2]
+    rep = hv // hk
+    qf = q.float()
+    kf = k.float()
+    qf = qf * torch.rsqrt(qf.pow(2).sum(-1, keepdim=True) + 1e-12) * (dk ** -0.5)
+    kf = kf * torch.rsqrt(kf.pow(2).sum(-1, keepdim=True) + 1e-12)
+    qf = qf.repeat_interleave(rep, dim=1)
+    kf = kf.repeat_interleave(rep, dim=1)
+    vf = v.float()
+    out = torch.zeros(t, hv, dv, dtype=q.dtype, device=q.device)
+    qi = meta.h_q_indptr if meta.h_q_indptr is not None else meta.q_indptr.tolist()
+    slots = meta.h_state_slots if meta.h_state_slots is not None else meta.state_slots.tolist()
+    for b in range(meta.num_seqs):
+        if slots[b] < 0:
+            continue
+        S = state[slots[b]]
+        for i in range(qi[b], qi[b + 1]):
+            S = S * torch.exp(g[i]).view(hv, 1, 1)
+            kv = torch.einsum("hkv,hk->hv", S, kf[i])
+            delta = (vf[i] - kv) * beta[i].view(hv, 1)
+            S = S + torch.einsum("hk,hv->hkv", kf[i], delta)
+            out[i] = torch.einsum("hkv,hk->hv", S, qf[i]).to(q.dtype)
+        state[slots[b]] = S
+    return out
+
+
+def sigmoid_gate_mul(x, gate):
+    return (x.float() * torch.sigmoid(gate.float())).to(x.dtype)

@@ -1,0 +1,116 @@
+"""Tensor parallelism with the collective fused into the GEMM kernels.
+
+A row-parallel projection (o_proj, down_proj) runs as ONE kernel launch per rank:
+tcgen05 GEMM tiles write f32 partials into this rank's symmetric buffer; once every
+rank's tiles are stored (epoch flags over NVLink), each rank reduces the token rows it
+owns from all peers in fixed rank order (reduce-scatter), adds the residual, applies
+RMSNorm and stores the normalised rows into every rank's activation buffer
+(all-gather).  The following column-parallel GEMM (qkv, gate_up) streams its first
+weight tiles while those rows travel and only then waits on the delivery flags, so the
+gather overlaps the GEMM's ramp-up.  Flags are monotonic epochs kept in device memory,
+so captured CUDA graphs replay without any reset.
+
+Reference decomposition this replaces: GEMM, ncclAllReduce, fused_add_rms_norm
+(pegainfer-qwen3/src/batch_decode.rs:320-347,378-396; weights.rs:616-644).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .. import _native
+from ..ops import cuda as K
+from .symm import SymmetricBuffer
+from .tp import TPContext
+
+FLAG_WORDS_PER_SITE = 32
+MAX_SITES = 1024
+_vp, _ll, _ci, _cf, _ull = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_float, ctypes.c_ulonglong
+
+
+class FusedTP(TPContext):
+    def __init__(self, rank: int, world: int, device, hidden: int, max_tokens: int, group=None, wait_s: float = 5.0):
+        super().__init__(rank, world, group, comm="fused")
+        import torch.distributed as dist
+
+        self.device = torch.device(device)
+        self.hidden = hidden
+        self.max_tokens = max_tokens
+        self.wait_ns = int(wait_s * 1e9)
+        self.lib = _native.load()
+        part_b = max_tokens * hidden * 4
+        x_b = max_tokens * hidden * 2
+        flag_b = MAX_SITES * FLAG_WORDS_PER_SITE * 4
+        self._off_x = (part_b + 255) // 256 * 256
+        self._off_f = self._off_x + (x_b + 255) // 256 * 256
+        self.buf = SymmetricBuffer(self._off_f + flag_b, rank, world, self.device, group)
+        self.part_table = self.buf.sub_table(0)
+        self.x_table = self.buf.sub_table(self._off_x)
+        self.flag_table = self.buf.sub_table(self._off_f)
+        self.x = self.buf.view(torch.bfloat16, (max_tokens, hidden), self._off_x)
+        self.flags = self.buf.view(torch.int32, (MAX_SITES, FLAG_WORDS_PER_SITE), self._off_f)
+        self._site = 0
+        self._pending_site = -1
+        self.fused = self
+        if world > 1:
+            dist.barrier(group=group)
+        torch.cuda.synchronize(self.device)
+
+    def begin_step(self) -> None:
+        self._site = 0
+        self._pending_site = -1
+
+    def _flag_ptr(self, site: int) -> int:
+        return self.buf.local_ptr + self._off_f + site * FLAG_WORDS_PER_SITE * 4
+
+    def row_linear_add_norm(self, a, w, residual, norm_w, eps, offset=False):
+        t, k = a.shape
+        if t > self.max_tokens:
+            raise ValueError(f"fused TP buffers hold {self.max_tokens} tokens, step has {t}")
+        if a.stride(-1) != 1:
+            a = a.contiguous()
+        site = self._site
+        self._site += 1
+        if self._site >= MAX_SITES:
+            raise RuntimeError("too many fused collective sites in one step")
+        c = K.ctx(a.device)
+        rc = self.lib.pg_tp_gemm_rs_norm_ag(
+            _vp(a.data_ptr()), _vp(w.data_ptr()), _ci(t), _ci(self.hidden), _ci(k), _ll(a.stride(0)), _ll(w.stride(0)), self.part_table, self.x_table,
+            self.flag_table, _ci(self.rank), _ci(self.world), _ci(site), _vp(residual.data_ptr()), _ll(residual.stride(0)), _vp(norm_w.data_ptr()),
+            _cf(eps), _ci(int(offset)), _ull(self.wait_ns), _vp(c.gemm_ws.data_ptr()), _ll(c.gemm_ws.numel()), _vp(c.gemm_counters.data_ptr()),
+            _ll(c.gemm_counters.numel() * 4), _vp(c.status.data_ptr()), _vp(torch.cuda.current_stream().cuda_stream),
+        )
+        K._check(rc, c)
+        self._pending_site = site
+        return self.x[:t]
+
+    def col_linear(self, x, w, out_dtype=None):
+        if self._pending_site < 0 or x.data_ptr() != self.x.data_ptr():
+            return K.linear(x, w, out_dtype)
+        site, self._pending_site = self._pending_site, -1
+        t, k = x.shape
+        m = w.shape[0]
+        f32 = out_dtype == torch.float32
+        out = torch.empty((t, m), dtype=torch.float32 if f32 else torch.bfloat16, device=x.device)
+        c = K.ctx(x.device)
+        rc = self.lib.pg_gemm_bf16_tn_after_gather(
+            _vp(x.data_ptr()), _vp(w.data_ptr()), _vp(out.data_ptr()), _ci(int(f32)), _ci(t), _ci(m), _ci(k), _ll(x.stride(0)), _ll(w.stride(0)),
+            _ll(out.stride(0)), _vp(c.gemm_ws.data_ptr()), _ll(c.gemm_ws.numel()), _vp(c.gemm_counters.data_ptr()), _ll(c.gemm_counters.numel() * 4),
+            _vp(c.status.data_ptr()), _vp(self._flag_ptr(site)), _ci(self.world), _ull(self.wait_ns), _vp(torch.cuda.current_stream().cuda_stream),
+        )
+        K._check(rc, c)
+        return out
+
+    def sync(self) -> None:
+        """Make the last gathered rows safe to read by kernels that do not wait themselves."""
+        if self._pending_site < 0:
+            return
+        site, self._pending_site = self._pending_site, -1
+        c = K.ctx(self.device)
+        rc = self.lib.pg_tp_wait(_vp(self._flag_ptr(site)), _ci(self.world), _ull(self.wait_ns), _vp(c.status.data_ptr()), _vp(torch.cuda.current_stream().cuda_stream))
+        K._check(rc, c)
+
+
+def make_fused_tp(rank: int, world: int, device, mcfg, max_tokens: int, group=None, wait_s: float = 5.0) -> FusedTP:
+    return FusedTP(rank, world, device, mcfg.hidden_size, max_tokens, group, wait_s)

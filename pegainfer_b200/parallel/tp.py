@@ -40,6 +40,16 @@ class TPContext:
         y = self.all_reduce(y)
         return ops.add_rms_norm(y, residual, norm_w, eps, offset)
 
+    def begin_step(self) -> None:
+        """Called at the start of every forward pass (fused mode numbers its sites)."""
+
+    def col_linear(self, x, w, out_dtype=None):
+        """Column-parallel projection of (possibly just all-gathered) activations."""
+        return ops.linear(x, w, out_dtype)
+
+    def sync(self) -> None:
+        """Gathered activations become readable by kernels that do not wait on flags."""
+
     def row_linear(self, a, w):
         """``all_reduce(a @ w.T)`` without the norm tail (last layer, MoE shared path)."""
         return self.all_reduce(ops.linear(a, w))

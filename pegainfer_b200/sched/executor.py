@@ -49,6 +49,7 @@ class SeqStep:
     all_rows: bool = False  # speculative verify: a token for every input row
     lora_slot: int = -1
     state_slot: int = -1  # recurrent-state slot (hybrid models)
+    next_token: int = -1  # token following the last input row when it is known (non-final prefill chunk)
     fresh_state: bool = False
 
 
@@ -69,6 +70,7 @@ class StepBatch:
 class StepResult:
     tokens: dict = field(default_factory=dict)  # rid -> [token, ...]
     logprobs: dict = field(default_factory=dict)  # rid -> [TokenLogprob, ...]
+    drafts: dict = field(default_factory=dict)  # rid -> [draft token per sampled row] (MTP)
     elapsed_s: float = 0.0
 
 
@@ -158,11 +160,15 @@ class TorchExecutor(ModelExecutor):
         self.use_graph = bool(cuda_graph) and self.device.type == "cuda"
         self.max_decode_batch = max_decode_batch
         self.max_blocks_per_seq = max_blocks_per_seq
+        self.mtp = None  # set by spec.MtpSpec
         self._graphs = None
         if self.use_graph:
             from ..utils.cuda_graph import DecodeGraphs
 
             self._graphs = DecodeGraphs(self, max_decode_batch, max_blocks_per_seq)
+
+    def prepare_meta(self, seqs, meta) -> None:
+        """Hook for model lines that carry extra per-sequence state (recurrent slots)."""
 
     # -- sampling ----------------------------------------------------------------
     def _sample(self, logits, seqs, rows_per_seq):
@@ -182,7 +188,7 @@ class TorchExecutor(ModelExecutor):
         t0 = time.perf_counter()
         self.steps += 1
         seqs = batch.seqs
-        if self._graphs is not None and batch.is_decode() and len(seqs) <= self.max_decode_batch and all(s.sample and s.logprobs == 0 for s in seqs):
+        if self._graphs is not None and self.mtp is None and batch.is_decode() and len(seqs) <= self.max_decode_batch and all(s.sample and s.logprobs == 0 for s in seqs):
             all_greedy = all(s.params.effectively_greedy(self.vocab_size) for s in seqs)
             out = self._graphs.run(seqs, greedy=all_greedy)
             if all_greedy:
@@ -192,6 +198,7 @@ class TorchExecutor(ModelExecutor):
                 toks = toks.tolist()
             return StepResult(tokens={s.rid: [toks[i]] for i, s in enumerate(seqs)}, elapsed_s=time.perf_counter() - t0)
         token_ids, meta = build_meta(seqs, self.page_size, self.device)
+        self.prepare_meta(seqs, meta)
         hidden = self.model.forward_hidden(token_ids, meta, self.kv)
         # rows that need logits
         rows, rows_per_seq, sample_seqs = [], [], []
@@ -215,5 +222,38 @@ class TorchExecutor(ModelExecutor):
                 if lps is not None and s.logprobs > 0:
                     res.logprobs[s.rid] = lps[k : k + nrows]
                 k += nrows
+        if self.mtp is not None:
+            self._mtp_drafts(seqs, meta, res)
         res.elapsed_s = time.perf_counter() - t0
         return res
+
+    def _mtp_drafts(self, seqs, meta, res: StepResult) -> None:
+        """Run the MTP block over every row of the step: it fills the MTP KV layer for
+        those positions and drafts one token after each sampled row."""
+        nxt, draft_rows, owners = [], [], []
+        for i, s in enumerate(seqs):
+            q0, n = meta.h_q_indptr[i], len(s.input_tokens)
+            sampled = res.tokens.get(s.rid)
+            for j in range(n):
+                if sampled is not None and s.all_rows:
+                    nxt.append(sampled[j])
+                elif j + 1 < n:
+                    nxt.append(s.input_tokens[j + 1])
+                elif sampled is not None:
+                    nxt.append(sampled[-1])
+                else:
+                    nxt.append(max(s.next_token, 0))
+            if sampled is not None:
+                rows = list(range(q0, q0 + n)) if s.all_rows else [q0 + n - 1]
+                draft_rows.extend(rows)
+                owners.append((s.rid, len(rows)))
+        nt = torch.tensor(nxt + [0] * (meta.num_tokens - len(nxt)), dtype=torch.int32, device=self.device)
+        h = self.mtp.forward(nt, self.model.last_residual, meta, self.kv)
+        if not draft_rows:
+            return
+        idx = torch.tensor(draft_rows, dtype=torch.int32, device=self.device)
+        toks = ops.argmax(self.model.logits(h, idx)).tolist()
+        k = 0
+        for rid, n in owners:
+            res.drafts[rid] = toks[k : k + n]
+            k += n

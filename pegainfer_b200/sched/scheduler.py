@@ -264,6 +264,7 @@ class ContinuousScheduler:
                         logprobs=r.q.request.logprobs if last else 0,
                         lora_slot=r.lora_slot,
                         fresh_state=r.prefill_pos == 0,
+                        next_token=-1 if last else r.kv.tokens[r.prefill_pos + n],
                     )
                 )
                 touched.append(r)
@@ -309,6 +310,7 @@ class ContinuousScheduler:
                     r.echo_done = True
                 tok = result.tokens[rid][0]
                 lp = result.logprobs.get(rid)
+                r.spec_state = result.drafts.get(rid)
                 self._resolve_token(r, tok, lp[0] if lp else None, ledger, first=True)
             if self.host_tier is not None and rid in self.running:
                 self.host_tier.on_blocks_sealed(r, self)
@@ -320,6 +322,7 @@ class ContinuousScheduler:
             lp = result.logprobs.get(rid)
             r.kv.apply_decode(tok)
             r.step_index += 1
+            r.spec_state = result.drafts.get(rid)
             self._resolve_token(r, tok, lp[0] if lp else None, ledger, first=False, appended=True)
             if self.host_tier is not None and rid in self.running:
                 self.host_tier.on_blocks_sealed(r, self)
@@ -362,26 +365,37 @@ class ContinuousScheduler:
 
     # -- speculative round -----------------------------------------------------------
     def _run_spec(self, decoders, ledger) -> None:
+        """One verify round: feed ``[current, drafts...]``, keep the matching prefix."""
+        from ..spec.speculative import accept_prefix_match
+
+        seqs = []
         try:
-            outcome = self.spec.round(decoders, self)
+            for r in decoders:
+                drafts = list(r.spec_state)
+                r.kv.schedule_speculative(1 + len(drafts))
+                seqs.append(
+                    SeqStep(rid=r.q.id, input_tokens=[r.kv.tokens[-1]] + drafts, start_pos=r.kv.committed, view=r.kv.view(), sample=True, params=r.q.request.params, step_index=r.step_index, all_rows=True)
+                )
+            result = self.ex.execute(StepBatch(seqs=seqs, kind="verify"))
         except Exception as exc:
             self.failed_batches += 1
             self._fail_batch(decoders, ledger, f"speculative step failed: {exc!r}")
             return
         for r in decoders:
             rid = r.q.id
-            if rid not in outcome:
-                continue
-            proposed, accepted_tokens = outcome[rid]
-            self._metrics.spec_decode.record(proposed, max(0, len(accepted_tokens) - 1))
-            emitted = []
-            finished = None
-            for tok in accepted_tokens:
+            drafts = list(r.spec_state)
+            accepted = accept_prefix_match(drafts, result.tokens[rid])
+            self._metrics.spec_decode.record(len(drafts), len(accepted) - 1)
+            r.kv.apply_speculative(len(accepted), accepted)
+            nd = result.drafts.get(rid)
+            r.spec_state = [nd[len(accepted) - 1]] if nd else None
+            emitted, finished = [], None
+            for tok in accepted:
                 if self._is_stop(r, tok):
                     finished = FinishReason.STOP
                     break
                 emitted.append(tok)
-                if r.out_tokens + len(emitted) >= r.q.request.max_tokens:
+                if r.out_tokens + len(emitted) >= r.q.request.max_tokens or r.kv.committed + 1 >= self.cfg.max_model_len:
                     finished = FinishReason.LENGTH
                     break
             if emitted:

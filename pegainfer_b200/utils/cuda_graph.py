@@ -48,6 +48,9 @@ class DecodeGraphs:
         self.np_table = self.h_table.numpy()
         self.q_indptr = torch.arange(B + 1, dtype=torch.int32, device=dev)
         self.out_tokens = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.h_slots = torch.zeros(B, dtype=torch.int32).pin_memory()
+        self.d_slots = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.uses_state = hasattr(executor.model, "rec")
         self.h_out = torch.zeros(B, dtype=torch.int32).pin_memory()
         self.graphs: dict = {}
         self.logits: dict = {}
@@ -78,6 +81,7 @@ class DecodeGraphs:
             max_kv_len=self.width * self.page_size,
             decode_only=True,
             plan=splits,
+            state_slots=self.d_slots[:b] if self.uses_state else None,
         )
 
     def _forward(self, b: int, greedy: bool, splits: int):
@@ -137,6 +141,12 @@ class DecodeGraphs:
             sm[B + n : B + b] = 0
             sm[2 * B + n : 2 * B + b] = 0
             sm[3 * B + n : 3 * B + b] = 0
+        if self.uses_state:
+            hs = self.h_slots.numpy()
+            for i, s in enumerate(seqs):
+                hs[i] = self.ex.model.rec.slot_for(s.rid, False)
+            hs[n:b] = 0
+            self.d_slots.copy_(self.h_slots, non_blocking=True)
         self.d_small.copy_(self.h_small, non_blocking=True)
         self.d_table[:b, :wmax].copy_(self.h_table[:b, :wmax], non_blocking=True)
         self.h2d_bytes += self.h_small.numel() * 4 + b * wmax * 4

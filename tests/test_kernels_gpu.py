@@ -219,3 +219,26 @@ def test_argmax_sample_logprobs(vocab):
     assert (c1 - c2).abs().max().item() < 1e-3 and (tv1 - tv2).abs().max().item() < 1e-3
     assert torch.equal(ti1[1:, 0].long(), ti2[1:, 0])
     status_clean()
+
+
+def test_bounded_wait_times_out_with_status_and_context_survives():
+    """A delivery flag that nothing sets: the wait gives up after its limit, reports
+    through the status word, and the device stays usable."""
+    import ctypes
+
+    from pegainfer_b200 import _native
+
+    lib = _native.load()
+    flags = torch.zeros(32, dtype=torch.int32, device=DEV)
+    flags[16] = 5  # epoch says "5 deliveries expected", nobody delivered
+    torch.cuda.synchronize()
+    c = cu().ctx(DEV)
+    rc = lib.pg_tp_wait(ctypes.c_void_p(flags.data_ptr()), ctypes.c_int(2), ctypes.c_ulonglong(200_000_000), ctypes.c_void_p(c.status.data_ptr()), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    torch.cuda.synchronize()
+    st = cu().read_status(DEV)
+    assert st & 0xFF == 1 and (st >> 8) & 0xFF == 4, hex(st)
+    cu().clear_status(DEV)
+    x = torch.ones(4, device=DEV)
+    assert (x + x).sum().item() == 8.0
+    status_clean()

@@ -1,0 +1,66 @@
+"""Model families on CPU (fp32, tiny presets): paged engine path vs dense recomputation."""
+import torch
+
+from pegainfer_b200.config import EngineConfig, preset
+from pegainfer_b200.engine.build import build_engine
+from pegainfer_b200.engine.contract import SamplingParams
+
+
+def gen(name, prompts, max_tokens, **kw):
+    ecfg = EngineConfig(preset=name, kv_page_size=16, num_kv_blocks=128, cuda_graph=False, **kw)
+    eng = build_engine(ecfg, preset(name), device="cpu", dtype=torch.float32)
+    try:
+        outs = eng.generate(prompts, SamplingParams(temperature=0.0, ignore_eos=True), max_tokens=max_tokens, timeout=300)
+        eng.pool.check_invariants()
+        return [o[0] for o in outs], eng
+    finally:
+        eng.shutdown()
+
+
+def prompts_for(n, length, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, 1024, (length + 3 * i,), generator=g).tolist() for i in range(n)]
+
+
+def _chunking_invariance(name):
+    ps = prompts_for(3, 40)
+    a, _ = gen(name, ps, 6, max_prefill_tokens=512)
+    b, _ = gen(name, ps, 6, max_prefill_tokens=24)  # chunked prefill + mixed steps
+    c = [gen(name, [p], 6, max_prefill_tokens=512)[0][0] for p in ps]  # one at a time
+    assert a == b == c
+
+
+def test_dsv2_shape_chunking_and_batching_invariance():
+    _chunking_invariance("tiny-dsv2")
+
+
+def test_kimi_shape_int4_group_routing_chunking_invariance():
+    _chunking_invariance("tiny-kimi")
+
+
+def test_mtp_speculative_decode_is_lossless_and_counts_acceptance():
+    ps = prompts_for(3, 30, seed=4)
+    plain, _ = gen("tiny-kimi", ps, 12)
+    spec, eng = gen("tiny-kimi", ps, 12, spec_method="mtp", max_prefill_tokens=20)
+    assert spec == plain  # greedy speculative decoding must not change the tokens
+    c = eng.scheduler._metrics.spec_decode
+    assert c.num_drafts > 0 and c.num_draft_tokens == c.num_drafts and 0 <= c.num_accepted_tokens <= c.num_draft_tokens
+
+
+def test_accept_prefix_match_truth_table():
+    from pegainfer_b200.spec.speculative import accept_prefix_match as f
+
+    assert f([5, 6, 7], [5, 6, 7, 8]) == [5, 6, 7, 8]
+    assert f([5, 6, 7], [5, 9, 7, 8]) == [5, 9]
+    assert f([5], [4, 1]) == [4]
+    assert f([], [3]) == [3]
+
+
+def test_qwen35_hybrid_chunking_and_batching_invariance():
+    _chunking_invariance("tiny-qwen35")
+
+
+def test_qwen35_recurrent_slots_are_recycled():
+    ps = prompts_for(4, 20, seed=9)
+    _, eng = gen("tiny-qwen35", ps, 4)
+    assert eng.model.rec.by_rid == {}

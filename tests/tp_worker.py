@@ -1,0 +1,87 @@
+"""Worker for the multi-GPU tensor-parallel test (launched by torchrun, one rank per GPU)."""
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch
+import torch.distributed as dist
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    from pegainfer_b200.config import preset
+    from pegainfer_b200.kv.buffer import KvBuffer, KvLayout
+    from pegainfer_b200.kv.request_kv import KvView
+    from pegainfer_b200.models.qwen3 import Qwen3Model
+    from pegainfer_b200.ops import cuda as K
+    from pegainfer_b200.parallel.fused import make_fused_tp
+    from pegainfer_b200.parallel.tp import SINGLE, TPContext
+    from pegainfer_b200.sched.executor import SeqStep, build_meta
+
+    mcfg = preset("qwen3-0.6b", num_layers=3, vocab_size=4096)
+    page, npages = 16, 64
+    tp_f = make_fused_tp(rank, world, dev, mcfg, max_tokens=512, wait_s=20.0)
+    models = {
+        "single": Qwen3Model(mcfg, device=dev, tp=SINGLE),
+        "nccl": Qwen3Model(mcfg, device=dev, tp=TPContext(rank, world, comm="nccl")),
+        "fused": Qwen3Model(mcfg, device=dev, tp=tp_f),
+    }
+
+    def kv_for(m):
+        return KvBuffer(KvLayout(page_size=page, num_pages=npages, dtype=torch.bfloat16, **m.kv_geometry()), dev)
+
+    kvs = {k: kv_for(m) for k, m in models.items()}
+    g = torch.Generator().manual_seed(5)
+    lens = [70, 33, 5]
+    prompts = [torch.randint(0, 4096, (n,), generator=g).tolist() for n in lens]
+    pages = [[1, 2, 3, 4, 5], [6, 7, 8], [9]]
+
+    def run(name, seqs):
+        tok, meta = build_meta(seqs, page, dev)
+        return models[name].forward(tok, meta, kvs[name]).float()
+
+    def check(tag, seqs):
+        ref = run("single", seqs)
+        out = {k: run(k, seqs) for k in ("nccl", "fused")}
+        again = run("fused", seqs)
+        torch.cuda.synchronize()
+        assert torch.equal(out["fused"], again), f"{tag}: fused TP is not bit-reproducible"
+        for k, v in out.items():
+            err = (v - ref).abs()
+            assert err.mean().item() < 0.03 and err.max().item() < 0.4, (tag, k, err.mean().item(), err.max().item())
+        # every rank must hold the same logits (the reduction order is fixed, rows are broadcast)
+        mine = out["fused"].contiguous()
+        gathered = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(gathered, mine)
+        assert all(torch.equal(gathered[0], t) for t in gathered), f"{tag}: ranks disagree"
+        return ref, out
+
+    prefill = [SeqStep(rid=i, input_tokens=p, start_pos=0, view=KvView(pages[i], len(p), page)) for i, p in enumerate(prompts)]
+    check("prefill", prefill)
+    decode = [SeqStep(rid=i, input_tokens=[7 + i], start_pos=lens[i], view=KvView(pages[i], lens[i] + 1, page)) for i in range(3)]
+    check("decode3", decode)
+    check("decode1", decode[:1])  # fewer rows than ranks: some ranks own nothing
+    # CUDA-graph replay of the fused path (epoch flags need no reset)
+    tok, meta = build_meta(decode, page, dev)
+    eager = models["fused"].forward(tok, meta, kvs["fused"]).float()
+    torch.cuda.synchronize()
+    gr = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(gr):
+        captured = models["fused"].forward(tok, meta, kvs["fused"])
+    for _ in range(3):
+        gr.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(captured.float(), eager), "graph replay differs from eager"
+    assert K.read_status(dev) == 0, f"status {K.read_status(dev):#x}"
+    dist.barrier()
+    if rank == 0:
+        print("TP_OK", flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
