@@ -48,6 +48,35 @@ int pg_qk_norm_rope_append(const void* qkv, long long ld, const void* q_w, const
                            int rot, int page_size, long long num_pages, int max_pos, int gated, int offset, float eps, void* status,
                            cudaStream_t stream);
 
+// ---- multi-head latent attention (mla.cu) ------------------------------------------
+int pg_mla_append(const void* kv_a, long long ld, const void* norm_w, const void* cos, const void* sin, const void* positions, const void* slots,
+                  void* latent, int tokens, int c, int rope, int max_pos, long long num_slots, float eps, void* status, cudaStream_t stream);
+int pg_mla_q_prep(const void* q, const void* cos, const void* sin, const void* positions, void* q_nope_hm, void* q_pe, int tokens, int heads,
+                  int nope, int rope, int max_pos, cudaStream_t stream);
+int pg_permute_021(const void* in, void* out, int A, int B, int D, cudaStream_t stream);
+int pg_mla_attention(const void* q_abs, const void* q_pe, const void* latent, void* out, const void* q_indptr, const void* kv_lens,
+                     const void* table, int table_stride, const void* unit_seq, int num_seqs, int tokens, int heads, int c, int rope,
+                     int page_size, float scale, int splits, void* part_o, void* part_lse, void* status, cudaStream_t stream);
+
+// ---- mixture of experts (moe_route.cu, moe_gemm.cu) --------------------------------
+int pg_router_topk(const void* logits, long long ld, const void* bias, void* ids, void* weights, int tokens, int E, int k, int sigmoid, int n_group,
+                   int topk_group, int norm, float scale, cudaStream_t stream);
+int pg_moe_align(const void* ids, int routes, int e0, int e_local, void* offsets, void* sorted_src, void* route_pos, cudaStream_t stream);
+int pg_moe_gather(const void* x, long long ldx, const void* sorted_src, const void* offsets, int e_local, int k, void* out, int width, int max_rows,
+                  cudaStream_t stream);
+int pg_moe_combine(const void* y, long long ldy, const void* route_pos, const void* weights, int tokens, int k, void* out, int width, int accumulate,
+                   cudaStream_t stream);
+int pg_moe_grouped_gemm(const void* x, long long ldx, long long x_rows, const void* w, const void* scales, int int4, void* y, long long ldy,
+                        const void* offsets, int E, int M, int K, int bn, void* status, cudaStream_t stream);
+
+// ---- Gated DeltaNet (gdn.cu) ------------------------------------------------------
+int pg_gdn_conv1d(const void* x, long long ldx, const void* w, void* state, void* out, long long ldo, const void* q_indptr, const void* slots,
+                  int num_seqs, int channels, int K, long long state_slot_stride, cudaStream_t stream);
+int pg_gdn_gates(const void* a, long long lda, const void* b, long long ldb, const void* a_log, const void* dt_bias, void* g, void* beta,
+                 int tokens, int hv, cudaStream_t stream);
+int pg_gdn_recurrent(const void* q, const void* k, long long ld_qk, const void* v, long long ld_v, const void* g, const void* beta, void* state,
+                     void* out, const void* q_indptr, const void* slots, int num_seqs, int hk, int hv, int dk, int dv, cudaStream_t stream);
+
 // ---- attention (attention.cu) ------------------------------------------------------
 int pg_decode_splits(int num_seqs, int hkv, int max_kv_len, int sms);
 void pg_attn_set_decode_stages(int stages);  // 2 (three CTAs per SM) or 3 (two CTAs per SM, default)

@@ -42,6 +42,7 @@ void pg_set_error(const char* fmt, ...);
     cudaError_t _e = (expr);                                                            \
     if (_e != cudaSuccess) {                                                            \
       pg_set_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__, __LINE__); \
+      (void)cudaGetLastError();                                                         \
       return PG_ERR_CUDA;                                                               \
     }                                                                                   \
   } while (0)

@@ -1,0 +1,420 @@
+// Grouped (per-expert) GEMM on tcgen05 for mixture-of-experts layers.
+//
+//   Y[r, :] = X[r, :] * W[e(r)]^T      rows r sorted by expert, expert e owns rows
+//                                      [offsets[e], offsets[e+1])
+//
+// Same operand roles as the dense GEMM: 128 weight rows of one expert are the UMMA A
+// operand, a tile of that expert's token rows is the B operand, so an expert with two
+// tokens still runs full-width MMAs and the kernel streams each expert's weights once
+// (the MoE-GEMV regime of decode).  Work items (expert, weight-row tile, token tile) are
+// derived on the device from `offsets`, so the launch shape does not depend on the
+// routing and the kernel can sit inside a captured graph.
+//
+// Weight formats:
+//   bf16   W [E, M, K]: TMA straight into the swizzled A tile.
+//   int4   W packed [E, M, K/8] int32 (offset-binary nibbles, low nibble = lowest k) with
+//          bf16 scales [E, M, K/32]: TMA brings the packed tile (4 KB per 128x64) into a
+//          raw buffer, four dequantisation warps expand it to bf16 ((nibble - 8) * scale,
+//          one rounding) directly into the 128-byte-swizzled A tile and hand it to the MMA
+//          warp through an mbarrier; HBM traffic stays at 4.5 bits per weight.
+//
+// warp 0 TMA producer | warp 1 MMA issuer + TMEM owner | warps 2-5 epilogue | warps 6-9 dequant (int4)
+//
+// Takes the place of the reference's Marlin W4A16 MoE kernel
+// (pegainfer-kernels/csrc/kimi_k2/kimi_marlin_wna16.cu:241-340, vllm_marlin/**) and its
+// per-expert dense GEMM loop (pegainfer-deepseek-v2-lite/src/runtime/moe.rs).
+#include <string.h>
+
+#include <mutex>
+
+#include "api.h"
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128, BK = 64;
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int RAW_BYTES = BM * BK / 2;  // packed int4 tile
+constexpr int MAX_STAGES = 10;
+constexpr int MAX_EXPERTS = 512;
+
+struct MoeGemmParams {
+  bf16* y;
+  long long ldy;
+  int M, K, E;
+  int bn, stages, kblocks, m_tiles;
+  uint32_t tmem_cols;
+  int int4;
+  const bf16* scales;  // [E, M, K/32]
+  const int* offsets;  // [E+1]
+  uint32_t* status;
+};
+
+struct Item {
+  int e, m_tile, row0, rows;
+};
+
+// Items are ordered expert-major; `cum` holds the running item count of experts before `e`.
+struct ItemCursor {
+  int e = 0;
+  int base = 0;
+};
+
+__device__ __forceinline__ bool locate(const MoeGemmParams& p, const int* s_tiles, int item, ItemCursor& c, Item& out) {
+  while (c.e < p.E && item >= c.base + s_tiles[c.e]) {
+    c.base += s_tiles[c.e];
+    ++c.e;
+  }
+  if (c.e >= p.E) return false;
+  const int local = item - c.base;
+  const int n_tiles = s_tiles[c.e] / p.m_tiles;
+  out.e = c.e;
+  out.m_tile = local / n_tiles;
+  const int n_tile = local - out.m_tile * n_tiles;
+  const int r0 = p.offsets[c.e], r1 = p.offsets[c.e + 1];
+  out.row0 = r0 + n_tile * p.bn;
+  out.rows = min(p.bn, r1 - out.row0);
+  return true;
+}
+
+__device__ __forceinline__ bool named_bar_all(int id, int nthreads, bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %1, 0;\n\t"
+      "bar.red.and.pred p, %2, %3, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(r)
+      : "r"((uint32_t)pred), "r"(id), "r"(nthreads)
+      : "memory");
+  return r != 0;
+}
+
+__global__ void __launch_bounds__(320, 1)
+moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const MoeGemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ int s_tiles[MAX_EXPERTS];
+  __shared__ int s_total;
+  const uint32_t base = smem_u32(smem_raw);
+  uint8_t* tiles = smem_raw + (((base + 1023u) & ~1023u) - base);
+  const int b_bytes = p.bn * 128;
+  const int stage_bytes = A_BYTES + b_bytes + (p.int4 ? RAW_BYTES : 0);
+  uint64_t* full = reinterpret_cast<uint64_t*>(tiles + p.stages * stage_bytes);
+  uint64_t* empty = full + MAX_STAGES;
+  uint64_t* aready = empty + MAX_STAGES;
+  uint64_t* tfull = aready + MAX_STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+      mbar_init(&aready[s], 128);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tm_w);
+    tma_prefetch_desc(&tm_x);
+  }
+  // per-expert item counts (every CTA derives the same list from the routing offsets)
+  for (int e = threadIdx.x; e < p.E; e += blockDim.x) {
+    const int n = p.offsets[e + 1] - p.offsets[e];
+    s_tiles[e] = n > 0 ? p.m_tiles * ((n + p.bn - 1) / p.bn) : 0;
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, p.tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (threadIdx.x == 0) {
+    int t = 0;
+    for (int e = 0; e < p.E; ++e) t += s_tiles[e];
+    s_total = t;
+  }
+  __syncthreads();
+  const uint32_t tmem_base = *tmem_slot;
+  const int total = s_total;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const uint64_t pol_w = l2_policy_evict_first();
+      const uint64_t pol_x = l2_policy_evict_last();
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t last_phase[MAX_STAGES];
+      bool used[MAX_STAGES];
+#pragma unroll
+      for (int s = 0; s < MAX_STAGES; ++s) {
+        used[s] = false;
+        last_phase[s] = 0;
+      }
+      ItemCursor cur;
+      Item it;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
+        if (!locate(p, s_tiles, item, cur, it)) break;
+        for (int kb = 0; kb < p.kblocks; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          uint8_t* st = tiles + stage * stage_bytes;
+          if (p.int4) {
+            mbar_expect_tx(&full[stage], (uint32_t)(RAW_BYTES + b_bytes));
+            tma_load_3d(st + A_BYTES + b_bytes, &tm_w, &full[stage], kb * (BK / 8), it.m_tile * BM, it.e, pol_w);
+          } else {
+            mbar_expect_tx(&full[stage], (uint32_t)(A_BYTES + b_bytes));
+            tma_load_3d(st, &tm_w, &full[stage], kb * BK, it.m_tile * BM, it.e, pol_w);
+          }
+          tma_load_2d(st + A_BYTES, &tm_x, &full[stage], kb * BK, it.row0, pol_x);
+          used[stage] = true;
+          last_phase[stage] = phase;
+          if (++stage == p.stages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      for (int s = 0; s < p.stages; ++s) {
+        if (!used[s]) continue;
+        uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(&full[s], last_phase[s])) {
+          if (globaltimer_ns() - t0 > PG_WAIT_LIMIT_NS) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_bf16_f32(BM, (uint32_t)p.bn);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
+        if (!mbar_wait(&tempty[acc], acc_phase ^ 1u, abort_flag)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * p.bn);
+        for (int kb = 0; kb < p.kblocks; ++kb) {
+          // int4: a_ready implies the packed tile and X landed and the bf16 A tile is written
+          if (!mbar_wait(p.int4 ? &aready[stage] : &full[stage], phase, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(tiles + stage * stage_bytes);
+          const uint32_t b_addr = a_addr + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)
+            umma_bf16_ss(d_tmem, umma_desc_k_sw128(a_addr + k * 32), umma_desc_k_sw128(b_addr + k * 32), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit(&empty[stage]);
+          if (++stage == p.stages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit(&tfull[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else if (warp < 6) {
+    const int wq = warp & 3;
+    const int r = wq * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    ItemCursor cur;
+    Item it;
+    for (int item = blockIdx.x; item < total; item += gridDim.x) {
+      if (!locate(p, s_tiles, item, cur, it)) break;
+      bool ok = mbar_wait(&tfull[acc], acc_phase, abort_flag);
+      ok = named_bar_all(1, 128, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int m = it.m_tile * BM + r;
+      const uint32_t t_row = tmem_base + ((uint32_t)(wq * 32) << 16) + (uint32_t)(acc * p.bn);
+      for (int c = 0; c < p.bn; c += 16) {
+        if (c >= it.rows) break;  // uniform across the warp
+        uint32_t v[16];
+        tmem_ld16(t_row + c, v);
+        tmem_ld_wait();
+        if (m < p.M) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (c + j < it.rows) p.y[(size_t)(it.row0 + c + j) * p.ldy + m] = __float2bfloat16(__uint_as_float(v[j]));
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  } else if (p.int4) {
+    // dequantisation warps: thread r expands row r of the packed tile into the swizzled A tile
+    const int r = threadIdx.x - 192;  // 0..127
+    int stage = 0;
+    uint32_t phase = 0;
+    ItemCursor cur;
+    Item it;
+    const int groups_per_row = p.K / 32;
+    bool ok = true;
+    for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
+      if (!locate(p, s_tiles, item, cur, it)) break;
+      const int m = it.m_tile * BM + r;
+      const bf16* srow = p.scales + ((size_t)it.e * p.M + (m < p.M ? m : 0)) * groups_per_row;
+      for (int kb = 0; kb < p.kblocks; ++kb) {
+        if (!mbar_wait(&full[stage], phase, abort_flag)) {
+          ok = false;
+          break;
+        }
+        uint8_t* st = tiles + stage * stage_bytes;
+        const uint4* raw = reinterpret_cast<const uint4*>(st + A_BYTES + b_bytes + r * 32);
+        const uint4 lo = raw[0], hi = raw[1];
+        const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+        const int g0 = kb * 2;
+        const bf16 s0 = (m < p.M && g0 < groups_per_row) ? srow[g0] : __float2bfloat16(0.f);
+        const bf16 s1 = (m < p.M && g0 + 1 < groups_per_row) ? srow[g0 + 1] : __float2bfloat16(0.f);
+        const bf162 sc0 = __halves2bfloat162(s0, s0), sc1 = __halves2bfloat162(s1, s1);
+        const bf162 bias = __floats2bfloat162_rn(136.f, 136.f);
+        uint8_t* a_row = st + r * 128;
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          // 8 nibbles of word `ch` -> 8 bf16; (0x4300 | n) is the bf16 value 128 + n
+          const uint32_t w = words[ch];
+          uint32_t o[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const uint32_t n0 = (w >> (8 * q)) & 0xFu, n1 = (w >> (8 * q + 4)) & 0xFu;
+            uint32_t packed = (0x4300u | n0) | ((0x4300u | n1) << 16);
+            bf162 val = *reinterpret_cast<bf162*>(&packed);
+            val = __hmul2(__hsub2(val, bias), ch < 4 ? sc0 : sc1);
+            o[q] = *reinterpret_cast<uint32_t*>(&val);
+          }
+          *reinterpret_cast<uint4*>(a_row + ((ch ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(&aready[stage]);
+        if (++stage == p.stages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, p.tmem_cols);
+  }
+  if (threadIdx.x == 0 && *abort_flag) atomicCAS(p.status, PG_ST_OK, PG_ST_TIMEOUT | (5u << 8));
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn moe_get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+bool g_attr_set[64];
+int g_sms[64], g_max_smem[64];
+int g_static_smem = 0;
+std::mutex g_mu;
+
+}  // namespace
+
+// x [rows, K] bf16 (rows sorted by expert), offsets [E+1] device int32, y [rows, M] bf16.
+// w: bf16 [E, M, K], or packed int32 [E, M, K/8] with scales bf16 [E, M, K/32] when int4 != 0.
+// `bn` is the token tile (multiple of 16, <= 256): pick it near the expected rows per expert.
+extern "C" int pg_moe_grouped_gemm(const void* x, long long ldx, long long x_rows, const void* w, const void* scales, int int4, void* y,
+                                   long long ldy, const void* offsets, int E, int M, int K, int bn, void* status, cudaStream_t stream) {
+  PG_REQUIRE(E >= 1 && E <= MAX_EXPERTS, "moe gemm: %d experts not supported (<= %d)", E, MAX_EXPERTS);
+  PG_REQUIRE(K % 64 == 0, "moe gemm: K=%d must be a multiple of 64", K);
+  PG_REQUIRE(bn >= 16 && bn <= 256 && bn % 16 == 0, "moe gemm: token tile %d must be a multiple of 16 in [16, 256]", bn);
+  PG_REQUIRE(status != nullptr, "moe gemm: a device status word is required");
+  if (x_rows == 0) return PG_OK;
+  EncodeTiledFn enc = moe_get_encode();
+  PG_REQUIRE(enc != nullptr, "cuTensorMapEncodeTiled is not available from this driver");
+  int dev = 0;
+  PG_CUDA(cudaGetDevice(&dev));
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (!g_attr_set[dev & 63]) {
+      PG_CUDA(cudaDeviceGetAttribute(&g_sms[dev & 63], cudaDevAttrMultiProcessorCount, dev));
+      PG_CUDA(cudaDeviceGetAttribute(&g_max_smem[dev & 63], cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+      cudaFuncAttributes fa;
+      PG_CUDA(cudaFuncGetAttributes(&fa, moe_gemm_kernel));
+      g_static_smem = (int)fa.sharedSizeBytes;
+      PG_CUDA(cudaFuncSetAttribute(moe_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, g_max_smem[dev & 63] - g_static_smem));
+      g_attr_set[dev & 63] = true;
+    }
+  }
+  MoeGemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.y = (bf16*)y;
+  p.ldy = ldy;
+  p.M = M;
+  p.K = K;
+  p.E = E;
+  p.bn = bn;
+  p.kblocks = K / BK;
+  p.m_tiles = ceil_div(M, BM);
+  p.int4 = int4;
+  p.scales = (const bf16*)scales;
+  p.offsets = (const int*)offsets;
+  p.status = (uint32_t*)status;
+  const int stage_bytes = A_BYTES + bn * 128 + (int4 ? RAW_BYTES : 0);
+  const int tail = (3 * MAX_STAGES + 4) * 8 + 64;
+  p.stages = (g_max_smem[dev & 63] - g_static_smem - 1024 - tail) / stage_bytes;
+  if (p.stages > MAX_STAGES) p.stages = MAX_STAGES;
+  PG_REQUIRE(p.stages >= 2, "moe gemm: not enough shared memory");
+  uint32_t cols = 32;
+  while (cols < (uint32_t)(2 * bn)) cols <<= 1;
+  p.tmem_cols = cols;
+
+  CUtensorMap tm_w, tm_x;
+  cuuint32_t estr[3] = {1, 1, 1};
+  if (int4) {
+    cuuint64_t dims[3] = {(cuuint64_t)(K / 8), (cuuint64_t)M, (cuuint64_t)E};
+    cuuint64_t strides[2] = {(cuuint64_t)(K / 8) * 4, (cuuint64_t)M * (K / 8) * 4};
+    cuuint32_t box[3] = {BK / 8, BM, 1};
+    CUresult r = enc(&tm_w, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, const_cast<void*>(w), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    PG_REQUIRE(r == CUDA_SUCCESS, "moe gemm: packed weight tensor map failed (%d)", (int)r);
+  } else {
+    cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)M, (cuuint64_t)E};
+    cuuint64_t strides[2] = {(cuuint64_t)K * 2, (cuuint64_t)M * K * 2};
+    cuuint32_t box[3] = {BK, BM, 1};
+    CUresult r = enc(&tm_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(w), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    PG_REQUIRE(r == CUDA_SUCCESS, "moe gemm: weight tensor map failed (%d)", (int)r);
+  }
+  int rc = pg_make_tmap_bf16_2d(&tm_x, x, x_rows, K, ldx, bn, BK);
+  if (rc) return rc;
+  const size_t smem = 1024 + (size_t)p.stages * stage_bytes + tail;
+  moe_gemm_kernel<<<g_sms[dev & 63], int4 ? 320 : 192, smem, stream>>>(tm_w, tm_x, p);
+  PG_LAUNCH_CHECK();
+  return PG_OK;
+}

@@ -313,3 +313,222 @@ def logprobs_topk(logits, picked, k):
     if k == 0:
         return chosen, None, None
     return chosen, tv, ti
+
+
+# ----------------------------------------------------------------------------------
+# Gated DeltaNet
+# ----------------------------------------------------------------------------------
+def sigmoid_gate_mul(x, gate):
+    return sigmoid_gate_mul_(x.contiguous(), gate.contiguous())
+
+
+def gdn_conv1d(x, conv_w, conv_state, meta: AttnMeta):
+    _bf16(x)
+    assert x.stride(-1) == 1 and conv_w.is_contiguous() and conv_state.is_contiguous()
+    t, ch = x.shape
+    out = torch.empty((t, ch), dtype=x.dtype, device=x.device)
+    c = ctx(x.device)
+    k = conv_w.shape[1]
+    rc = lib().pg_gdn_conv1d(_ptr(x), _ll(x.stride(0)), _ptr(conv_w), _ptr(conv_state), _ptr(out), _ll(out.stride(0)), _ptr(meta.q_indptr), _ptr(meta.state_slots),
+                             _ci(meta.num_seqs), _ci(ch), _ci(k), _ll(conv_state.stride(0)), _stream())
+    _check(rc, c)
+    return out
+
+
+def gdn_gates(a, b, a_log, dt_bias):
+    t, hv = a.shape
+    g = torch.empty((t, hv), dtype=torch.float32, device=a.device)
+    beta = torch.empty_like(g)
+    c = ctx(a.device)
+    assert a.stride(-1) == 1 and b.stride(-1) == 1
+    rc = lib().pg_gdn_gates(_ptr(a), _ll(a.stride(0)), _ptr(b), _ll(b.stride(0)), _ptr(a_log), _ptr(dt_bias), _ptr(g), _ptr(beta), _ci(t), _ci(hv), _stream())
+    _check(rc, c)
+    return g, beta
+
+
+def gdn_recurrent(q, k, v, g, beta, state, meta: AttnMeta):
+    t, hk, dk = q.shape
+    hv, dv = v.shape[1], v.shape[2]
+    assert q.stride(2) == 1 and q.stride(1) == dk and k.stride(1) == dk and v.stride(1) == dv and q.stride(0) == k.stride(0)
+    assert state.is_contiguous() and state.dtype == torch.float32
+    out = torch.empty((t, hv, dv), dtype=q.dtype, device=q.device)
+    c = ctx(q.device)
+    rc = lib().pg_gdn_recurrent(_ptr(q), _ptr(k), _ll(q.stride(0)), _ptr(v), _ll(v.stride(0)), _ptr(g.contiguous()), _ptr(beta.contiguous()), _ptr(state), _ptr(out),
+                                _ptr(meta.q_indptr), _ptr(meta.state_slots), _ci(meta.num_seqs), _ci(hk), _ci(hv), _ci(dk), _ci(dv), _stream())
+    _check(rc, c)
+    return out
+
+
+# ----------------------------------------------------------------------------------
+# mixture of experts
+# ----------------------------------------------------------------------------------
+def router_topk(logits, top_k, scoring="softmax", bias=None, n_group=1, topk_group=1, norm_topk_prob=False, scale=1.0):
+    assert logits.dtype == torch.float32 and logits.stride(-1) == 1
+    t, e = logits.shape
+    ids = torch.empty((t, top_k), dtype=torch.int32, device=logits.device)
+    w = torch.empty((t, top_k), dtype=torch.float32, device=logits.device)
+    c = ctx(logits.device)
+    b = bias.float().contiguous() if bias is not None else None
+    rc = lib().pg_router_topk(_ptr(logits), _ll(logits.stride(0)), _ptr(b), _ptr(ids), _ptr(w), _ci(t), _ci(e), _ci(top_k), _ci(int(scoring == "sigmoid")), _ci(n_group),
+                              _ci(topk_group), _ci(int(norm_topk_prob)), _cf(scale), _stream())
+    _check(rc, c)
+    return ids, w
+
+
+def _token_tile(routes: int, experts: int) -> int:
+    avg = max(1, (routes + experts - 1) // experts)
+    bn = 16
+    while bn < avg and bn < 128:
+        bn *= 2
+    return bn
+
+
+def moe_route_plan(ids, e0: int, e_local: int):
+    """Stable sort of the routes that hit experts [e0, e0 + e_local)."""
+    routes = ids.numel()
+    dev = ids.device
+    offsets = torch.empty(e_local + 1, dtype=torch.int32, device=dev)
+    sorted_src = torch.empty(max(routes, 1), dtype=torch.int32, device=dev)
+    route_pos = torch.empty(max(routes, 1), dtype=torch.int32, device=dev)
+    c = ctx(dev)
+    _check(lib().pg_moe_align(_ptr(ids.contiguous()), _ci(routes), _ci(e0), _ci(e_local), _ptr(offsets), _ptr(sorted_src), _ptr(route_pos), _stream()), c)
+    return offsets, sorted_src, route_pos
+
+
+def grouped_gemm(xs, offsets, w, scales=None, bn: int = 16):
+    """``xs`` [rows, K] sorted by expert; ``w`` bf16 [E, M, K] or packed int32 [E, M, K/8] + scales."""
+    rows, k = xs.shape
+    e, m = w.shape[0], w.shape[1]
+    int4 = scales is not None
+    y = torch.empty((rows, m), dtype=torch.bfloat16, device=xs.device)
+    c = ctx(xs.device)
+    rc = lib().pg_moe_grouped_gemm(_ptr(xs), _ll(xs.stride(0)), _ll(rows), _ptr(w), _ptr(scales), _ci(int(int4)), _ptr(y), _ll(y.stride(0)), _ptr(offsets), _ci(e), _ci(m),
+                                   _ci(k), _ci(bn), _ptr(c.status), _stream())
+    _check(rc, c)
+    return y
+
+
+def _moe_pipeline(x, ids, weights, w13, s13, w2, s2, expert_offset):
+    _bf16(x)
+    t, h = x.shape
+    k = ids.shape[1]
+    e_local = w13.shape[0]
+    routes = t * k
+    c = ctx(x.device)
+    offsets, sorted_src, route_pos = moe_route_plan(ids, expert_offset, e_local)
+    xs = torch.empty((routes, h), dtype=x.dtype, device=x.device)
+    _check(lib().pg_moe_gather(_ptr(x), _ll(x.stride(0)), _ptr(sorted_src), _ptr(offsets), _ci(e_local), _ci(k), _ptr(xs), _ci(h), _ci(routes), _stream()), c)
+    bn = _token_tile(routes, e_local)
+    y1 = grouped_gemm(xs, offsets, w13, s13, bn)
+    act = swiglu(y1)
+    y2 = grouped_gemm(act, offsets, w2, s2, bn)
+    out = torch.empty((t, h), dtype=torch.float32, device=x.device)
+    _check(lib().pg_moe_combine(_ptr(y2), _ll(y2.stride(0)), _ptr(route_pos), _ptr(weights.contiguous()), _ci(t), _ci(k), _ptr(out), _ci(h), _ci(0), _stream()), c)
+    return out
+
+
+def moe_experts(x, ids, weights, w13, w2, expert_offset=0):
+    return _moe_pipeline(x, ids, weights, w13, None, w2, None, expert_offset)
+
+
+def moe_experts_int4(x, ids, weights, w13_packed, w13_scale, w2_packed, w2_scale, expert_offset=0, group=32):
+    assert group == 32, "the int4 grouped GEMM is built for group size 32"
+    return _moe_pipeline(x, ids, weights, w13_packed, w13_scale, w2_packed, w2_scale, expert_offset)
+
+
+# ----------------------------------------------------------------------------------
+# multi-head latent attention
+# ----------------------------------------------------------------------------------
+def mla_append(kv_a, kv_norm_w, cos, sin, meta: AttnMeta, latent_layer, kv_lora, eps):
+    _bf16(kv_a)
+    assert kv_a.stride(-1) == 1 and latent_layer.is_contiguous()
+    t = kv_a.shape[0]
+    rope = kv_a.shape[1] - kv_lora
+    c = ctx(kv_a.device)
+    num_slots = latent_layer.shape[0] * latent_layer.shape[1]
+    rc = lib().pg_mla_append(_ptr(kv_a), _ll(kv_a.stride(0)), _ptr(kv_norm_w), _ptr(cos), _ptr(sin), _ptr(meta.positions), _ptr(meta.slot_mapping), _ptr(latent_layer), _ci(t),
+                             _ci(kv_lora), _ci(rope), _ci(cos.shape[0]), _ll(num_slots), _cf(eps), _ptr(c.status), _stream())
+    _check(rc, c)
+
+
+class _MlaQ:
+    """Query after RoPE in the layout the absorbed attention wants."""
+
+    def __init__(self, nope_hm, pe, tokens, heads, nope):
+        self.nope_hm, self.pe, self.tokens, self.heads, self.nope = nope_hm, pe, tokens, heads, nope
+
+
+def mla_rope_q(q, cos, sin, meta: AttnMeta, nope):
+    _bf16(q)
+    t, h, d = q.shape
+    rope = d - nope
+    q = q.contiguous()
+    nope_hm = torch.empty((h, t, nope), dtype=q.dtype, device=q.device)
+    pe = torch.empty((t, h, rope), dtype=q.dtype, device=q.device)
+    c = ctx(q.device)
+    _check(lib().pg_mla_q_prep(_ptr(q), _ptr(cos), _ptr(sin), _ptr(meta.positions), _ptr(nope_hm), _ptr(pe), _ci(t), _ci(h), _ci(nope), _ci(rope), _ci(cos.shape[0]), _stream()), c)
+    return _MlaQ(nope_hm, pe, t, h, nope)
+
+
+_HEAD_OFFSETS: dict = {}
+
+
+def _head_offsets(heads: int, tokens: int, device):
+    key = (heads, tokens, device.index)
+    o = _HEAD_OFFSETS.get(key)
+    if o is None:
+        o = (torch.arange(heads + 1, dtype=torch.int32, device=device) * tokens).contiguous()
+        if len(_HEAD_OFFSETS) < 512:
+            _HEAD_OFFSETS[key] = o
+    return o
+
+
+_WUK_T: dict = {}
+
+
+def mla_attention(q: "_MlaQ", w_uk, w_uv, latent_layer, meta: AttnMeta, scale, kv_lora):
+    """``w_uk`` [H, nope, kv_lora], ``w_uv`` [H, v, kv_lora].  The absorb GEMM wants W_UK as
+    an [out = kv_lora, in = nope] weight per head; that transposed copy is made once per
+    layer and kept."""
+    w_uk_t = _WUK_T.get(w_uk.data_ptr())
+    if w_uk_t is None:
+        w_uk_t = w_uk.transpose(1, 2).contiguous()
+        _WUK_T[w_uk.data_ptr()] = w_uk_t
+    t, h = q.tokens, q.heads
+    dev = latent_layer.device
+    c = ctx(dev)
+    if t == 0:
+        return torch.empty((0, h * w_uv.shape[1]), dtype=torch.bfloat16, device=dev)
+    offs = _head_offsets(h, t, dev)
+    bn = _token_tile(h * t, h)
+    q_abs = grouped_gemm(q.nope_hm.view(h * t, q.nope), offs, w_uk_t, None, bn)  # [H*T, kv_lora]
+    rope = q.pe.shape[-1]
+    page_size = latent_layer.shape[1]
+    if meta.plan is not None and isinstance(meta.plan, tuple):
+        unit_seq = meta.plan[1]
+    else:
+        qi = meta.h_q_indptr if meta.h_q_indptr is not None else meta.q_indptr.tolist()
+        seq_of = []
+        for b in range(meta.num_seqs):
+            seq_of.extend([b] * (qi[b + 1] - qi[b]))
+        unit_seq = torch.tensor(seq_of, dtype=torch.int32, device=dev)
+    groups = h // 16
+    if meta.decode_only:
+        splits = meta.plan[0] if isinstance(meta.plan, tuple) else max(1, min(16, (4 * c.sms) // max(1, t * groups), (meta.max_kv_len + 127) // 128))
+    else:
+        splits = 1
+    need = t * h * splits * (kv_lora + 1) * 4
+    if need > c.attn_part.numel():
+        splits = 1
+    part_o = c.attn_part
+    part_lse = c.attn_part[t * h * splits * kv_lora * 4 :]
+    lat_out = torch.empty((h * t, kv_lora), dtype=torch.bfloat16, device=dev)
+    rc = lib().pg_mla_attention(_ptr(q_abs), _ptr(q.pe), _ptr(latent_layer), _ptr(lat_out), _ptr(meta.q_indptr), _ptr(meta.kv_lens), _ptr(meta.block_table),
+                                _ci(meta.block_table.stride(0)), _ptr(unit_seq), _ci(meta.num_seqs), _ci(t), _ci(h), _ci(kv_lora), _ci(rope), _ci(page_size), _cf(scale),
+                                _ci(splits), _ptr(part_o), _ptr(part_lse), _ptr(c.status), _stream())
+    _check(rc, c, 2 if splits > 1 else 1)
+    v_hm = grouped_gemm(lat_out, offs, w_uv, None, bn)  # [H*T, v]
+    vdim = w_uv.shape[1]
+    out = torch.empty((t, h * vdim), dtype=torch.bfloat16, device=dev)
+    _check(lib().pg_permute_021(_ptr(v_hm), _ptr(out), _ci(h), _ci(t), _ci(vdim), _stream()), c)
+    return out

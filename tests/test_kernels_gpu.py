@@ -242,3 +242,145 @@ def test_bounded_wait_times_out_with_status_and_context_survives():
     x = torch.ones(4, device=DEV)
     assert (x + x).sum().item() == 8.0
     status_clean()
+
+
+def _state_meta(q_lens, slots):
+    from pegainfer_b200.kv.request_kv import KvView
+    from pegainfer_b200.sched.executor import SeqStep, build_meta
+
+    seqs = [SeqStep(rid=i, input_tokens=[0] * n, start_pos=0, view=KvView([1], n, 1 << 20)) for i, n in enumerate(q_lens)]
+    _, meta = build_meta(seqs, 1 << 20, DEV)
+    meta.h_state_slots = list(slots)
+    meta.state_slots = torch.tensor(slots, dtype=torch.int32, device=DEV)
+    return meta
+
+
+@pytest.mark.parametrize("dk,hk,hv", [(128, 2, 6), (32, 2, 4)])
+def test_gated_delta_net_kernels(dk, hk, hv):
+    torch.manual_seed(dk)
+    dv = dk
+    q_lens, slots = [1, 19, 5, 1], [3, 1, 4, 2]
+    meta = _state_meta(q_lens, slots)
+    t = meta.num_tokens
+    ch = 2 * hk * dk + hv * dv
+    x = torch.randn(t, ch, device=DEV).bfloat16()
+    conv_w = (torch.randn(ch, 4, device=DEV) * 0.5).bfloat16()
+    st1 = torch.randn(6, ch, 3, device=DEV).bfloat16()
+    st2 = st1.clone()
+    y1 = cu().gdn_conv1d(x, conv_w, st1, meta)
+    y2 = R.gdn_conv1d(x, conv_w, st2, meta)
+    bf16_close(y1, y2, rel=2 ** -6, abs_=4e-3)
+    assert torch.equal(st1, st2)
+    a = torch.randn(t, hv, device=DEV).bfloat16()
+    b = torch.randn(t, hv, device=DEV).bfloat16()
+    a_log = torch.randn(hv, device=DEV) * 0.5
+    dt_bias = torch.randn(hv, device=DEV) * 0.5
+    g1, b1 = cu().gdn_gates(a, b, a_log, dt_bias)
+    g2, b2 = R.gdn_gates(a, b, a_log, dt_bias)
+    assert (g1 - g2).abs().max().item() < 1e-4 and (b1 - b2).abs().max().item() < 1e-5
+    q = y2[:, : hk * dk].reshape(t, hk, dk)
+    k = y2[:, hk * dk : 2 * hk * dk].reshape(t, hk, dk)
+    v = y2[:, 2 * hk * dk :].reshape(t, hv, dv)
+    s1 = torch.randn(6, hv, dk, dv, device=DEV) * 0.1
+    s2 = s1.clone()
+    o1 = cu().gdn_recurrent(q, k, v, g2, b2, s1, meta)
+    o2 = R.gdn_recurrent(q, k, v, g2, b2, s2, meta)
+    bf16_close(o1, o2, rel=2 ** -6, abs_=4e-3)
+    assert (s1 - s2).abs().max().item() < 2e-3
+    status_clean()
+
+
+@pytest.mark.parametrize("scoring,e,k,ng,tg,norm", [("softmax", 64, 6, 1, 1, False), ("sigmoid", 384, 8, 1, 1, True), ("sigmoid", 64, 4, 8, 3, True), ("softmax", 16, 2, 4, 2, False)])
+def test_router_topk(scoring, e, k, ng, tg, norm):
+    torch.manual_seed(e + k)
+    logits = torch.randn(50, e, device=DEV) * 2
+    bias = torch.randn(e, device=DEV) * 0.1 if scoring == "sigmoid" else None
+    i1, w1 = cu().router_topk(logits, k, scoring, bias, ng, tg, norm, 2.5)
+    i2, w2 = R.router_topk(logits, k, scoring, bias, ng, tg, norm, 2.5)
+    assert torch.equal(i1, i2)
+    assert (w1 - w2).abs().max().item() < 1e-5 * 2.5 + 1e-6
+    status_clean()
+
+
+@pytest.mark.parametrize("t,h,inter,e,k,int4", [(5, 256, 128, 8, 2, False), (64, 2048, 1408, 16, 6, False), (3, 512, 256, 8, 3, True), (130, 1024, 512, 12, 4, True), (700, 512, 256, 4, 2, False)])
+def test_moe_pipeline_matches_per_expert_reference(t, h, inter, e, k, int4):
+    torch.manual_seed(t + h)
+    x = (torch.randn(t, h, device=DEV) * 0.5).bfloat16()
+    logits = torch.randn(t, e + 4, device=DEV)
+    ids, w = R.router_topk(logits, k, "softmax")
+    off = 2  # local experts are [2, 2 + e): some routes fall outside
+    if int4:
+        p13 = torch.randint(-(2 ** 31), 2 ** 31 - 1, (e, 2 * inter, h // 8), dtype=torch.int32, device=DEV)
+        s13 = (torch.rand(e, 2 * inter, h // 32, device=DEV) * 0.004 + 0.002).bfloat16()
+        p2 = torch.randint(-(2 ** 31), 2 ** 31 - 1, (e, h, inter // 8), dtype=torch.int32, device=DEV)
+        s2 = (torch.rand(e, h, inter // 32, device=DEV) * 0.004 + 0.002).bfloat16()
+        got = cu().moe_experts_int4(x, ids, w, p13, s13, p2, s2, off)
+        ref = R.moe_experts_int4(x, ids, w, p13, s13, p2, s2, off)
+    else:
+        w13 = (torch.randn(e, 2 * inter, h, device=DEV) * 0.03).bfloat16()
+        w2 = (torch.randn(e, h, inter, device=DEV) * 0.03).bfloat16()
+        got = cu().moe_experts(x, ids, w, w13, w2, off)
+        ref = R.moe_experts(x, ids, w, w13, w2, off)
+    torch.cuda.synchronize()
+    status_clean()
+    err = (got - ref).abs()
+    assert err.max().item() < 2e-2 * max(1.0, ref.abs().max().item()), (err.max().item(), ref.abs().max().item())
+    assert torch.equal(got, cu().moe_experts_int4(x, ids, w, p13, s13, p2, s2, off) if int4 else cu().moe_experts(x, ids, w, w13, w2, off))
+
+
+def test_int4_dequant_inside_grouped_gemm_is_exact_on_one_hot_inputs():
+    torch.manual_seed(0)
+    e, m, k = 3, 256, 128
+    packed = torch.randint(-(2 ** 31), 2 ** 31 - 1, (e, m, k // 8), dtype=torch.int32, device=DEV)
+    scales = (torch.rand(e, m, k // 32, device=DEV) * 0.01 + 0.001).bfloat16()
+    xs = torch.zeros(3 * 16, k, device=DEV).bfloat16()
+    for r in range(48):
+        xs[r, (r * 5) % k] = 1.0
+    offsets = torch.tensor([0, 16, 32, 48], dtype=torch.int32, device=DEV)
+    y = cu().grouped_gemm(xs, offsets, packed, scales, 16)
+    for ex in range(e):
+        wd = R.dequant_int4_g32(packed[ex], scales[ex])
+        ref = xs[ex * 16 : (ex + 1) * 16].float() @ wd.float().t()
+        assert torch.equal(y[ex * 16 : (ex + 1) * 16].float(), ref.bfloat16().float())
+    status_clean()
+
+
+def _mla_setup(q_lens, kv_lens, heads, page=16, seed=0):
+    torch.manual_seed(seed)
+    c, rope, nope, v = 512, 64, 128, 128
+    kv, meta = make_batch(q_lens, kv_lens, page, 1, 8)  # reuse the page-table builder
+    n_pages = kv.shape[0]
+    latent = (torch.randn(n_pages, page, c + rope, device=DEV) * 0.5).bfloat16()
+    t = meta.num_tokens
+    q = (torch.randn(t, heads, nope + rope, device=DEV) * 0.5).bfloat16()
+    w_uk = (torch.randn(heads, nope, c, device=DEV) * 0.05).bfloat16()
+    w_uv = (torch.randn(heads, v, c, device=DEV) * 0.05).bfloat16()
+    cos, sin = R.rope_tables(4096, rope, 10000.0, torch.bfloat16, DEV)
+    return meta, latent, q, w_uk, w_uv, cos, sin, c, nope
+
+
+@pytest.mark.parametrize("heads", [16, 64])
+def test_mla_decode_and_prefill_match_reference(heads):
+    for q_lens, kv_lens in (([1, 1, 1, 1], [1, 31, 32, 700]), ([5, 40, 1], [5, 90, 33])):
+        meta, latent, q, w_uk, w_uv, cos, sin, c, nope = _mla_setup(q_lens, kv_lens, heads, seed=heads)
+        scale = 0.1
+        q_ref = R.mla_rope_q(q, cos, sin, meta, nope)
+        ref = R.mla_attention(q_ref, w_uk, w_uv, latent, meta, scale, c)
+        q_cu = cu().mla_rope_q(q, cos, sin, meta, nope)
+        got = cu().mla_attention(q_cu, w_uk, w_uv, latent, meta, scale, c)
+        torch.cuda.synchronize()
+        status_clean()
+        err = (got.float() - ref.float()).abs()
+        assert err.max().item() < 3e-2 * max(1.0, ref.float().abs().max().item()), (q_lens, err.max().item(), ref.float().abs().max().item())
+
+
+def test_mla_append_matches_reference():
+    meta, latent, q, w_uk, w_uv, cos, sin, c, nope = _mla_setup([3, 1, 20], [19, 40, 20], 16, seed=3)
+    t = meta.num_tokens
+    kv_a = torch.randn(t, c + 64, device=DEV).bfloat16()
+    w = (torch.rand(c, device=DEV) + 0.5).bfloat16()
+    l1, l2 = latent.clone(), latent.clone()
+    cu().mla_append(kv_a, w, cos, sin, meta, l1, c, 1e-6)
+    R.mla_append(kv_a, w, cos, sin, meta, l2, c, 1e-6)
+    bf16_close(l1, l2, rel=2 ** -7, abs_=4e-3)
+    status_clean()
