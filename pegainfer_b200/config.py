@@ -146,6 +146,9 @@ PRESETS = {
     "tiny-qwen35": ModelConfig(family="qwen35", vocab_size=1024, hidden_size=256, num_layers=4, num_q_heads=4, num_kv_heads=2, head_dim=64, intermediate_size=512, layer_types=_hybrid_pattern(4), partial_rotary_factor=0.25, attn_output_gate=True, norm_weight_offset=True, gdn_num_k_heads=2, gdn_num_v_heads=4, gdn_head_dim=32, rope_theta=1e7),
     "qwen3.5-27b": ModelConfig(family="qwen35", vocab_size=248320, hidden_size=5120, num_layers=64, num_q_heads=24, num_kv_heads=4, head_dim=256, intermediate_size=17408, layer_types=_hybrid_pattern(64), partial_rotary_factor=0.25, attn_output_gate=True, norm_weight_offset=True, gdn_num_k_heads=16, gdn_num_v_heads=48, gdn_head_dim=128, rope_theta=1e7, max_position=262144),
     "tiny-dsv2": ModelConfig(family="deepseek_v2", vocab_size=1024, hidden_size=256, num_layers=3, num_q_heads=4, num_kv_heads=4, head_dim=48, intermediate_size=512, qk_norm=False, kv_lora_rank=64, qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32, n_routed_experts=8, n_shared_experts=2, num_experts_per_tok=2, moe_intermediate_size=128, first_k_dense_replace=1, rope_theta=10000.0, rope_scaling=dict(_YARN_DSV2)),
+    "small-dsv2": ModelConfig(family="deepseek_v2", vocab_size=4096, hidden_size=1024, num_layers=3, num_q_heads=16, num_kv_heads=16, head_dim=192, intermediate_size=2048, qk_norm=False, kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, n_routed_experts=16, n_shared_experts=2, num_experts_per_tok=4, moe_intermediate_size=256, first_k_dense_replace=1, rope_theta=10000.0, rope_scaling=dict(_YARN_DSV2), max_position=8192),
+    "small-kimi": ModelConfig(family="kimi_k2", vocab_size=4096, hidden_size=1024, num_layers=3, num_q_heads=16, num_kv_heads=16, head_dim=192, intermediate_size=2048, qk_norm=False, q_lora_rank=512, kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, n_routed_experts=32, n_shared_experts=1, num_experts_per_tok=4, moe_intermediate_size=256, first_k_dense_replace=1, scoring_func="sigmoid", n_group=4, topk_group=2, norm_topk_prob=True, routed_scaling_factor=2.827, router_bias=True, expert_quant="int4_g32", rope_theta=50000.0, rope_scaling=dict(_YARN_KIMI), rms_eps=1e-5, max_position=8192, num_mtp_layers=1),
+    "small-qwen35": ModelConfig(family="qwen35", vocab_size=4096, hidden_size=1024, num_layers=4, num_q_heads=8, num_kv_heads=2, head_dim=256, intermediate_size=2048, layer_types=_hybrid_pattern(4), partial_rotary_factor=0.25, attn_output_gate=True, norm_weight_offset=True, gdn_num_k_heads=4, gdn_num_v_heads=8, gdn_head_dim=128, rope_theta=1e7, max_position=8192),
     "dsv2-lite": ModelConfig(family="deepseek_v2", vocab_size=102400, hidden_size=2048, num_layers=27, num_q_heads=16, num_kv_heads=16, head_dim=192, intermediate_size=10944, qk_norm=False, kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, n_routed_experts=64, n_shared_experts=2, num_experts_per_tok=6, moe_intermediate_size=1408, first_k_dense_replace=1, rope_theta=10000.0, rope_scaling=dict(_YARN_DSV2), max_position=163840),
     "tiny-kimi": ModelConfig(family="kimi_k2", vocab_size=1024, hidden_size=256, num_layers=3, num_q_heads=4, num_kv_heads=4, head_dim=48, intermediate_size=512, qk_norm=False, q_lora_rank=96, kv_lora_rank=64, qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32, n_routed_experts=16, n_shared_experts=1, num_experts_per_tok=4, moe_intermediate_size=128, first_k_dense_replace=1, scoring_func="sigmoid", n_group=4, topk_group=2, norm_topk_prob=True, routed_scaling_factor=2.827, router_bias=True, expert_quant="int4_g32", rope_theta=50000.0, rope_scaling=dict(_YARN_KIMI), rms_eps=1e-5, num_mtp_layers=1),
     "kimi-k2": ModelConfig(family="kimi_k2", vocab_size=163840, hidden_size=7168, num_layers=61, num_q_heads=64, num_kv_heads=64, head_dim=192, intermediate_size=18432, qk_norm=False, q_lora_rank=1536, kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, n_routed_experts=384, n_shared_experts=1, num_experts_per_tok=8, moe_intermediate_size=2048, first_k_dense_replace=1, scoring_func="sigmoid", n_group=1, topk_group=1, norm_topk_prob=True, routed_scaling_factor=2.827, router_bias=True, expert_quant="int4_g32", rope_theta=50000.0, rope_scaling=dict(_YARN_KIMI), rms_eps=1e-5, max_position=131072, num_mtp_layers=1),
@@ -285,6 +288,7 @@ class EngineConfig:
     no_prefix_cache: bool = False
     kv_offload: bool = False
     kv_offload_host_gib: float = 4.0
+    kv_offload_l1_disabled: bool = False  # test mode: evict idle GPU blocks before every probe
     max_prefill_tokens: int = 1024
     max_decode_batch: int = 256
     max_model_len: Optional[int] = None

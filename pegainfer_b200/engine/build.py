@@ -97,7 +97,7 @@ def build_engine(ecfg: EngineConfig, mcfg: Optional[ModelConfig] = None, device=
     if ecfg.kv_offload:
         from ..kv.host_tier import HostTier
 
-        host_tier = HostTier(kv, pool, int(ecfg.kv_offload_host_gib * (1 << 30)))
+        host_tier = HostTier(kv, pool, int(ecfg.kv_offload_host_gib * (1 << 30)), l1_retention_disabled=ecfg.kv_offload_l1_disabled)
     spec = None
     if ecfg.spec_method:
         from ..spec.speculative import build_spec
@@ -113,5 +113,5 @@ def build_engine(ecfg: EngineConfig, mcfg: Optional[ModelConfig] = None, device=
         eos_token_ids=tuple(mcfg.eos_token_ids),
     )
     eng = Engine([sched], info, start=start)
-    eng.model, eng.executor, eng.scheduler, eng.pool, eng.kv = model, executor, sched, pool, kv
+    eng.model, eng.executor, eng.scheduler, eng.pool, eng.kv, eng.host_tier = model, executor, sched, pool, kv, host_tier
     return eng

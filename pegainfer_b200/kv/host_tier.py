@@ -1,0 +1,264 @@
+"""Host-memory tier of the KV cache (offload + restore by content hash).
+
+* SAVE: when a running request seals (fills and registers) a block, and after the step
+  that wrote it has synchronised, the block's data (all layers: a strided view of the
+  KV buffer) is copied to a pinned host slab on a dedicated copy stream.  The source
+  block is pinned (one extra pool reference) until the copy has landed, so an evicted
+  and rewritten block can never be stored under an old hash.  A failed or skipped save
+  only forfeits a future hit.
+* QUERY / LOAD: at admission the request's prefix hashes are probed: blocks already on
+  the GPU are left to the normal prefix match; the following run of blocks present in
+  the host tier is loaded into freshly reserved GPU blocks (never dipping below the
+  scheduler's reserve floor) while the request is *parked*; when the copy has landed the
+  blocks are committed into the prefix cache under their hashes, so the ordinary
+  ``match_and_add_prefix`` simply sees a longer hit.
+* Any error or lack of space degrades to "prefill from scratch", never to a client error.
+* ``flush_saves_then`` is the barrier used when a finish must not be reported before
+  the KV is visible to a peer (prefill/decode disaggregation).
+
+Reference parity: pegainfer-kv-offload/src/engine.rs:67-505 (register / save / query /
+load / flush), pegainfer-qwen3/src/executor.rs:1037-1091,1706-1845,1986-2030 (prefetch
+state machine, save of sealed blocks, settle), src/scheduler.rs:146-197 (parking),
+pegainfer-kv-store/src/store.rs:90-730 (resolve_prefix orchestration).
+"""
+from __future__ import annotations
+
+import time
+from collections import OrderedDict
+from dataclasses import dataclass, field
+from typing import Callable, Optional
+
+import torch
+
+from .request_kv import RequestKv, chain_hash
+
+
+@dataclass
+class _Save:
+    bid: int
+    slot: int
+    h: bytes
+    event: Optional[object]
+
+
+@dataclass
+class _Load:
+    rid: int
+    blocks: list
+    hashes: list
+    parent: Optional[bytes]
+    event: Optional[object]
+    started: float
+
+
+@dataclass
+class TierStats:
+    saves: int = 0
+    save_skips: int = 0
+    host_hits: int = 0
+    loads: int = 0
+    load_failures: int = 0
+    evictions: int = 0
+
+
+class HostTier:
+    def __init__(self, kv, pool, host_bytes: int, reserve_floor: int = 2, l1_retention_disabled: bool = False, load_deadline_s: float = 15.0):
+        self.kv, self.pool = kv, pool
+        self.data = kv.data
+        self.device = self.data.device
+        one = self.data[:, 0]
+        self.block_shape = tuple(one.shape)
+        self.block_bytes = one.numel() * one.element_size()
+        self.num_slots = max(1, host_bytes // self.block_bytes)
+        self.slab = torch.empty((self.num_slots,) + self.block_shape, dtype=self.data.dtype)
+        self.cuda = self.device.type == "cuda"
+        if self.cuda:
+            self.slab = self.slab.pin_memory()
+            self.stream = torch.cuda.Stream(self.device)
+        self.by_hash: "OrderedDict[bytes, int]" = OrderedDict()  # LRU: oldest first
+        self.free_slots = list(range(self.num_slots - 1, -1, -1))
+        self.saving: list = []
+        self.loading: dict = {}
+        self.ready: list = []
+        self.saved_upto: dict = {}  # rid -> number of this request's blocks already offered
+        self.reserve_floor = reserve_floor
+        self.l1_retention_disabled = l1_retention_disabled
+        self.load_deadline_s = load_deadline_s
+        self.stats = TierStats()
+        self._probed: set = set()
+
+    # -- save path ---------------------------------------------------------------------
+    def _take_slot(self) -> Optional[int]:
+        if self.free_slots:
+            return self.free_slots.pop()
+        if self.by_hash:
+            _, slot = self.by_hash.popitem(last=False)
+            self.stats.evictions += 1
+            return slot
+        return None
+
+    def on_blocks_sealed(self, r, sched) -> None:
+        """Offer every newly registered block of request ``r`` to the host tier."""
+        kv: RequestKv = r.kv
+        done = self.saved_upto.get(r.q.id, kv.cached_tokens // kv.bs)
+        upto = kv._registered_blocks
+        if upto <= done:
+            return
+        # recompute the chain hashes of the new blocks
+        parent = None
+        hashes = []
+        for i in range(upto):
+            parent = chain_hash(parent, kv.tokens[i * kv.bs : (i + 1) * kv.bs], kv.salt)
+            hashes.append(parent)
+        for i in range(done, upto):
+            self._save_block(kv.blocks[i], hashes[i])
+        self.saved_upto[r.q.id] = upto
+
+    def _save_block(self, bid: int, h: bytes) -> None:
+        if h in self.by_hash or any(s.h == h for s in self.saving):
+            self.stats.save_skips += 1
+            return
+        if self.pool.block_hash(bid) != h:  # block is a private duplicate: nothing to publish
+            self.stats.save_skips += 1
+            return
+        slot = self._take_slot()
+        if slot is None:
+            self.stats.save_skips += 1
+            return
+        self.pool.acquire(bid)  # keep-alive until the copy landed
+        ev = None
+        try:
+            if self.cuda:
+                self.stream.wait_stream(torch.cuda.current_stream(self.device))
+                with torch.cuda.stream(self.stream):
+                    self.slab[slot].copy_(self.data[:, bid], non_blocking=True)
+                    ev = torch.cuda.Event()
+                    ev.record(self.stream)
+            else:
+                self.slab[slot].copy_(self.data[:, bid])
+        except Exception:
+            self.pool.release([bid])
+            self.free_slots.append(slot)
+            self.stats.save_skips += 1
+            return
+        self.saving.append(_Save(bid, slot, h, ev))
+
+    # -- query / load path -----------------------------------------------------------------
+    def host_hit_run(self, hashes: list, start: int) -> int:
+        n = 0
+        for h in hashes[start:]:
+            if h not in self.by_hash:
+                break
+            n += 1
+        return n
+
+    def should_park(self, q, sched) -> bool:
+        """Called at admission.  Starts a host->GPU load when it would extend the prefix
+        hit; the request then waits in ``sched.parked`` until ``drain_ready``."""
+        if q.id in self._probed:
+            return False
+        self._probed.add(q.id)
+        if not self.pool.enable_prefix_cache:
+            return False
+        self.poll(sched)
+        if self.l1_retention_disabled:
+            self.pool.evict_inactive()
+        req = q.request
+        salt = b""
+        if req.lora_adapter:
+            salt += b"lora:" + req.lora_adapter.encode()
+        if req.cache_salt:
+            salt += b"salt:" + req.cache_salt.encode()
+        bs = self.pool.block_size
+        max_blocks = (len(req.prompt_tokens) - 1) // bs
+        hashes, parent = [], None
+        for i in range(max_blocks):
+            parent = chain_hash(parent, req.prompt_tokens[i * bs : (i + 1) * bs], salt)
+            hashes.append(parent)
+        gpu_hit = self.pool.probe(hashes)
+        n = self.host_hit_run(hashes, gpu_hit)
+        if n == 0:
+            return False
+        blocks = self.pool.reserve(n, floor=self.reserve_floor + sched._future_blocks())
+        if blocks is None:
+            return False  # no room: recompute instead
+        self.stats.host_hits += n
+        want = hashes[gpu_hit : gpu_hit + n]
+        ev = None
+        try:
+            slots = []
+            for h in want:
+                self.by_hash.move_to_end(h)
+                slots.append(self.by_hash[h])
+            if self.cuda:
+                with torch.cuda.stream(self.stream):
+                    for bid, slot in zip(blocks, slots):
+                        self.data[:, bid].copy_(self.slab[slot], non_blocking=True)
+                    ev = torch.cuda.Event()
+                    ev.record(self.stream)
+            else:
+                for bid, slot in zip(blocks, slots):
+                    self.data[:, bid].copy_(self.slab[slot])
+        except Exception:
+            self.pool.free_unregistered_tail(blocks)
+            self.stats.load_failures += 1
+            return False
+        self.loading[q.id] = _Load(q.id, blocks, want, hashes[gpu_hit - 1] if gpu_hit else None, ev, time.monotonic())
+        self.stats.loads += 1
+        return True
+
+    def poll(self, sched=None) -> None:
+        # completed saves: publish hash -> slot, drop the keep-alive
+        still = []
+        for s in self.saving:
+            if s.event is None or s.event.query():
+                self.by_hash[s.h] = s.slot
+                self.by_hash.move_to_end(s.h)
+                self.pool.release([s.bid])
+                self.stats.saves += 1
+            else:
+                still.append(s)
+        self.saving = still
+        # completed loads: the blocks join the prefix cache, the request may be admitted
+        for rid in list(self.loading):
+            ld = self.loading[rid]
+            if ld.event is None or ld.event.query():
+                if self.cuda:
+                    torch.cuda.current_stream(self.device).wait_event(ld.event)
+                self.pool.commit_reserved(ld.blocks, ld.hashes, ld.parent)
+                del self.loading[rid]
+                self.ready.append(rid)
+            elif time.monotonic() - ld.started > self.load_deadline_s:
+                # give up: the reservation is returned once the copy can no longer write
+                ld.event.synchronize()
+                self.pool.free_unregistered_tail(ld.blocks)
+                del self.loading[rid]
+                self.stats.load_failures += 1
+                self.ready.append(rid)
+
+    def drain_ready(self, sched) -> list:
+        out, self.ready = self.ready, []
+        return out
+
+    def cancel(self, rid: int) -> None:
+        ld = self.loading.pop(rid, None)
+        if ld is not None:
+            if ld.event is not None:
+                ld.event.synchronize()
+            self.pool.free_unregistered_tail(ld.blocks)
+
+    def on_retire(self, r, sched) -> None:
+        self.saved_upto.pop(r.q.id, None)
+        self._probed.discard(r.q.id)
+
+    def flush_saves_then(self, cb: Callable[[], None], deadline_s: float = 5.0) -> None:
+        """Run ``cb`` once every in-flight save has landed (or the deadline passed)."""
+        t0 = time.monotonic()
+        while self.saving and time.monotonic() - t0 < deadline_s:
+            self.poll()
+            if self.saving:
+                time.sleep(0.0005)
+        cb()
+
+    def contains(self, h: bytes) -> bool:
+        return h in self.by_hash

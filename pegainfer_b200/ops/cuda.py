@@ -504,8 +504,8 @@ def mla_attention(q: "_MlaQ", w_uk, w_uv, latent_layer, meta: AttnMeta, scale, k
     q_abs = grouped_gemm(q.nope_hm.view(h * t, q.nope), offs, w_uk_t, None, bn)  # [H*T, kv_lora]
     rope = q.pe.shape[-1]
     page_size = latent_layer.shape[1]
-    if meta.plan is not None and isinstance(meta.plan, tuple):
-        unit_seq = meta.plan[1]
+    if meta.decode_only:
+        unit_seq = meta.q_indptr  # one row per sequence: q_indptr[i] == i
     else:
         qi = meta.h_q_indptr if meta.h_q_indptr is not None else meta.q_indptr.tolist()
         seq_of = []
@@ -514,7 +514,7 @@ def mla_attention(q: "_MlaQ", w_uk, w_uv, latent_layer, meta: AttnMeta, scale, k
         unit_seq = torch.tensor(seq_of, dtype=torch.int32, device=dev)
     groups = h // 16
     if meta.decode_only:
-        splits = meta.plan[0] if isinstance(meta.plan, tuple) else max(1, min(16, (4 * c.sms) // max(1, t * groups), (meta.max_kv_len + 127) // 128))
+        splits = max(1, min(16, (4 * c.sms) // max(1, t * groups), (min(meta.max_kv_len, 4096) + 127) // 128))
     else:
         splits = 1
     need = t * h * splits * (kv_lora + 1) * 4

@@ -84,3 +84,83 @@ def test_sampling_params_and_logprobs_on_gpu():
         assert len(lps) == 4 and all(lp is not None and lp.logprob <= 0 and len(lp.top) == 3 for lp in lps)
     finally:
         eng.shutdown()
+
+
+def _family_engine(name, cuda_graph, **kw):
+    ecfg = EngineConfig(preset=name, num_kv_blocks=512, cuda_graph=cuda_graph, max_decode_batch=8, max_model_len=1024, max_prefill_tokens=128, **kw)
+    return build_engine(ecfg, preset(name), device="cuda:0", dtype=torch.bfloat16)
+
+
+def _family_logits_close(name, mean_tol=0.03, max_tol=0.5):
+    """Kernel path vs PyTorch library path of the same weights, one ragged prefill step."""
+    from pegainfer_b200.kv.request_kv import KvView
+    from pegainfer_b200.sched.executor import SeqStep, build_meta
+
+    eng = _family_engine(name, False)
+    try:
+        g = torch.Generator().manual_seed(2)
+        ps = [torch.randint(0, 4096, (n,), generator=g).tolist() for n in (50, 17, 33)]
+        seqs, page, nxt = [], 16, 1
+        for i, p in enumerate(ps):
+            npg = (len(p) + page - 1) // page
+            seqs.append(SeqStep(rid=100 + i, input_tokens=p, start_pos=0, view=KvView(list(range(nxt, nxt + npg)), len(p), page), fresh_state=True))
+            nxt += npg
+        tok, meta = build_meta(seqs, page, "cuda:0")
+        eng.executor.prepare_meta(seqs, meta)
+        a = eng.model.forward(tok, meta, eng.kv).float()
+        eng.kv.data.zero_()
+        for s in seqs:
+            eng.executor.release_request(s.rid)
+        eng.executor.prepare_meta(seqs, meta)
+        with ops.mode("library"):
+            b = eng.model.forward(tok, meta, eng.kv).float()
+        torch.cuda.synchronize()
+        err = (a - b).abs()
+        assert err.mean().item() < mean_tol and err.max().item() < max_tol, (name, err.mean().item(), err.max().item())
+        from pegainfer_b200.ops import cuda as K
+
+        assert K.read_status("cuda:0") == 0
+    finally:
+        eng.shutdown()
+
+
+def test_dsv2_shape_kernels_vs_library():
+    _family_logits_close("small-dsv2")
+
+
+def test_kimi_shape_int4_kernels_vs_library():
+    _family_logits_close("small-kimi")
+
+
+def test_qwen35_hybrid_kernels_vs_library():
+    _family_logits_close("small-qwen35")
+
+
+@pytest.mark.parametrize("name", ["small-dsv2", "small-kimi", "small-qwen35"])
+def test_family_generate_graph_equals_eager(name):
+    e1, e2 = _family_engine(name, False), _family_engine(name, True)
+    try:
+        g = torch.Generator().manual_seed(7)
+        ps = [torch.randint(0, 4096, (20 + 9 * i,), generator=g).tolist() for i in range(3)]
+        o1 = e1.generate(ps, max_tokens=8)
+        o2 = e2.generate(ps, max_tokens=8)
+        assert [x[0] for x in o1] == [x[0] for x in o2]
+        assert e2.executor._graphs.replays > 0
+    finally:
+        e1.shutdown()
+        e2.shutdown()
+
+
+def test_kimi_mtp_speculative_is_lossless_on_gpu():
+    plain = _family_engine("small-kimi", False)
+    spec = _family_engine("small-kimi", False, spec_method="mtp")
+    try:
+        g = torch.Generator().manual_seed(11)
+        ps = [torch.randint(0, 4096, (25 + 5 * i,), generator=g).tolist() for i in range(2)]
+        a = plain.generate(ps, max_tokens=10)
+        b = spec.generate(ps, max_tokens=10)
+        assert [x[0] for x in a] == [x[0] for x in b]
+        assert spec.scheduler._metrics.spec_decode.num_drafts > 0
+    finally:
+        plain.shutdown()
+        spec.shutdown()
