@@ -43,6 +43,7 @@ def parse():
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (marks the result invalid)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--profile-host", default=None, help="write a cProfile of the scheduler thread during the e2e phase to this path")
     return ap.parse_args()
 
 
@@ -99,6 +100,15 @@ class ClockSampler:
         out["reasons"] = sorted(reasons)
         out["samples"] = len(sm)
         return out
+
+
+def hard_exit(code: int = 0):
+    """Leave without interpreter teardown: with scheduler threads, captured graphs and
+    peer-mapped memory alive, a normal exit has been seen to stall in process-group and
+    CUDA teardown long after the result line was printed."""
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(code)
 
 
 def reference_arm(args):
@@ -233,7 +243,9 @@ def e2e(args, eng, rank, world, device):
     from pegainfer_b200.engine.contract import Request, SamplingParams
 
     n, plen = args.conc, args.prompt_len
-    out_len = args.warmup + args.steps + 1
+    per_step = max(1, 4096 // plen)
+    ramp = (n + per_step - 1) // per_step  # admission is staggered by the prefill chunk budget
+    out_len = args.warmup + args.steps + 1 + ramp
     g = torch.Generator().manual_seed(4321)
     host_prompts = torch.randint(0, eng.model.cfg.vocab_size, (n, plen), generator=g, dtype=torch.int32).pin_memory()
     graphs = eng.executor._graphs
@@ -247,19 +259,44 @@ def e2e(args, eng, rank, world, device):
             listener=lambda upd, i=i: stamps[i].extend([time.perf_counter()] * len(upd.tokens)),
         )
         streams.append(s)
+    prof = None
+    if args.profile_host:
+        import cProfile
+
+        prof = cProfile.Profile()
+        inner = eng.scheduler.step
+
+        def profiled(ledger):
+            prof.enable()
+            try:
+                return inner(ledger)
+            finally:
+                prof.disable()
+
+        eng.scheduler.step = profiled
     eng.start()  # every rank queued the same requests first: replicated schedulers stay in lockstep
     for s in streams:
         toks, term, _ = s.collect(1800)
         assert term.kind == "finished" and len(toks) == out_len, (term, len(toks))
     torch.cuda.synchronize(device)
-    # timed region: from the moment every request has emitted its (warmup+1)-th token to the end
+    # timed region: all requests decoding together, i.e. from the moment the last-admitted
+    # request has emitted its (warmup+1)-th token until the first request finishes
     t_begin = max(st[args.warmup] for st in stamps)
-    t_end = max(st[-1] for st in stamps)
-    tokens = sum(sum(1 for t in st if t > t_begin) for st in stamps)
+    t_end = min(st[-1] for st in stamps)
+    tokens = sum(sum(1 for t in st if t_begin < t <= t_end) for st in stamps)
     dt = max_over_ranks(t_end - t_begin, world, device)
     ttft = sorted(st[0] - t_submit for st in stamps)
     tpot = sorted((st[-1] - st[0]) / (len(st) - 1) for st in stamps)
     steps_run = max(1, graphs.replays)
+    if prof is not None and rank == 0:
+        import io
+        import pstats
+
+        buf = io.StringIO()
+        pstats.Stats(prof, stream=buf).sort_stats("cumulative").print_stats(45)
+        os.makedirs(os.path.dirname(os.path.abspath(args.profile_host)), exist_ok=True)
+        with open(args.profile_host, "w") as f:
+            f.write(buf.getvalue())
     return dict(
         value=tokens / dt,
         ttft_p50_ms=1e3 * statistics.median(ttft),
@@ -294,15 +331,17 @@ def main():
 
         tp = make_fused_tp(rank, world, device, mcfg, max_tokens=4096 + args.conc)
     page = args.page_size
-    total_len = args.prompt_len + args.warmup + args.steps + 2 * page
+    ramp = (args.conc + max(1, 4096 // args.prompt_len) - 1) // max(1, 4096 // args.prompt_len)
+    total_len = args.prompt_len + args.warmup + args.steps + ramp + 2 * page
     blocks = 2 * args.conc * ((total_len + page - 1) // page + 2) + 8
-    ecfg = EngineConfig(preset=args.model, num_kv_blocks=blocks, kv_page_size=page, cuda_graph=True, max_decode_batch=max(args.conc, 8), max_model_len=total_len + page, max_prefill_tokens=4096, no_prefix_cache=True)
+    ecfg = EngineConfig(preset=args.model, num_kv_blocks=blocks, kv_page_size=page, cuda_graph=True, precapture_graphs=True, max_decode_batch=max(args.conc, 8), max_model_len=total_len + page, max_prefill_tokens=4096, no_prefix_cache=True)
     eng = build_engine(ecfg, mcfg, device=device, dtype=torch.bfloat16, tp=tp, start=False)
     try:
         ko = kernel_only(args, eng, rank, world, device)
         ee = None if args.no_e2e else e2e(args, eng, rank, world, device)
     finally:
         eng.shutdown()
+    barrier(world, device)
     if rank == 0:
         ms_per_step = ko["ms_total"] / args.steps
         value = args.conc * args.steps / (ko["ms_total"] / 1e3)
@@ -335,11 +374,7 @@ def main():
         if ee is not None:
             line["e2e"] = {"value": round(ee["value"], 2), "unit": "tok/s", "h2d_bytes_per_step": ee["h2d_bytes_per_step"], "d2h_bytes_per_step": ee["d2h_bytes_per_step"], "ttft_p50_ms": round(ee["ttft_p50_ms"], 2), "tpot_p50_ms": round(ee["tpot_p50_ms"], 3)}
         print(json.dumps(line))
-    if world > 1:
-        import torch.distributed as dist
-
-        dist.destroy_process_group()
-    return 0
+    hard_exit(0)
 
 
 if __name__ == "__main__":

@@ -69,6 +69,18 @@ int pg_moe_combine(const void* y, long long ldy, const void* route_pos, const vo
 int pg_moe_grouped_gemm(const void* x, long long ldx, long long x_rows, const void* w, const void* scales, int int4, void* y, long long ldy,
                         const void* offsets, int E, int M, int K, int bn, void* status, cudaStream_t stream);
 
+int pg_moe_grouped_gemm_return(const void* x, long long ldx, long long x_rows, const void* w, const void* scales, int int4, long long ldy,
+                               const void* offsets, int E, int M, int K, int bn, void* status, const void* scatter_src, void* const* peer_out,
+                               void* const* peer_flags, int cap, int rank, int world, int site, cudaStream_t stream);
+// ---- expert-parallel dispatch / combine over peer memory (ep.cu) -------------------
+int pg_ep_dispatch(const void* x, long long ldx, const void* ids, int tokens, const void* valid_tokens, int k, int hidden, int e_local, int cap,
+                   void* const* slab, void* const* recv_ids, void* const* flags, int rank, int world, int site, unsigned long long wait_ns,
+                   cudaStream_t stream);
+int pg_ep_align(const void* recv_ids, int world, int cap, int live, int e_local, void* offsets, void* sorted_src, const void* site_flags,
+                unsigned long long wait_ns, void* status, cudaStream_t stream);
+int pg_ep_combine(const void* comb, const void* ids, const void* weights, int tokens, int k, void* out, int hidden, const void* valid_tokens,
+                  void* site_flags, int world, unsigned long long wait_ns, void* status, cudaStream_t stream);
+
 // ---- Gated DeltaNet (gdn.cu) ------------------------------------------------------
 int pg_gdn_conv1d(const void* x, long long ldx, const void* w, void* state, void* out, long long ldo, const void* q_indptr, const void* slots,
                   int num_seqs, int channels, int K, long long state_slot_stride, cudaStream_t stream);

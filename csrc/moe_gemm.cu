@@ -48,6 +48,12 @@ struct MoeGemmParams {
   const bf16* scales;  // [E, M, K/32]
   const int* offsets;  // [E+1]
   uint32_t* status;
+  // expert-parallel return path: output row r goes to rank (scatter_src[r] / cap), slot
+  // (scatter_src[r] % cap) of that rank's combine buffer; the tail raises the "returned" epoch
+  const int* scatter_src;
+  bf16* peer_out[8];
+  uint32_t* peer_flags[8];
+  int cap, rank, world, site;
 };
 
 struct Item {
@@ -143,6 +149,8 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
   __syncthreads();
   const uint32_t tmem_base = *tmem_slot;
   const int total = s_total;
+  uint32_t ep_epoch = 0;
+  if (p.scatter_src != nullptr) ep_epoch = *((volatile uint32_t*)(p.peer_flags[p.rank] + p.site * 32 + 16));
 
   if (warp == 0) {
     if (lane == 0) {
@@ -249,9 +257,20 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
         tmem_ld16(t_row + c, v);
         tmem_ld_wait();
         if (m < p.M) {
+          if (p.scatter_src == nullptr) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j)
-            if (c + j < it.rows) p.y[(size_t)(it.row0 + c + j) * p.ldy + m] = __float2bfloat16(__uint_as_float(v[j]));
+            for (int j = 0; j < 16; ++j)
+              if (c + j < it.rows) p.y[(size_t)(it.row0 + c + j) * p.ldy + m] = __float2bfloat16(__uint_as_float(v[j]));
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              if (c + j < it.rows) {
+                const int idx = p.scatter_src[it.row0 + c + j];
+                const int dst_rank = idx / p.cap, slot = idx - dst_rank * p.cap;
+                p.peer_out[dst_rank][(size_t)slot * p.ldy + m] = __float2bfloat16(__uint_as_float(v[j]));
+              }
+            }
+          }
         }
       }
       tc_fence_before();
@@ -321,6 +340,17 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     tmem_dealloc(tmem_base, p.tmem_cols);
   }
   if (threadIdx.x == 0 && *abort_flag) atomicCAS(p.status, PG_ST_OK, PG_ST_TIMEOUT | (5u << 8));
+  if (p.scatter_src != nullptr && threadIdx.x == 0) {
+    // every output row of this CTA is on its way to its source rank: the last CTA of this
+    // GPU raises the "returned" epoch on all ranks
+    uint32_t* myflags = p.peer_flags[p.rank] + p.site * 32;
+    __threadfence_system();
+    const uint32_t old = atomicAdd(&myflags[17], 1u);
+    if (old == gridDim.x - 1) {
+      myflags[17] = 0u;
+      for (int q = 0; q < p.world; ++q) st_release_sys(p.peer_flags[q] + p.site * 32 + 8 + p.rank, ep_epoch + 1u);
+    }
+  }
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -348,13 +378,14 @@ std::mutex g_mu;
 // x [rows, K] bf16 (rows sorted by expert), offsets [E+1] device int32, y [rows, M] bf16.
 // w: bf16 [E, M, K], or packed int32 [E, M, K/8] with scales bf16 [E, M, K/32] when int4 != 0.
 // `bn` is the token tile (multiple of 16, <= 256): pick it near the expected rows per expert.
-extern "C" int pg_moe_grouped_gemm(const void* x, long long ldx, long long x_rows, const void* w, const void* scales, int int4, void* y,
-                                   long long ldy, const void* offsets, int E, int M, int K, int bn, void* status, cudaStream_t stream) {
+static int moe_gemm_impl(const void* x, long long ldx, long long x_rows, const void* w, const void* scales, int int4, void* y, long long ldy,
+                         const void* offsets, int E, int M, int K, int bn, void* status, const void* scatter_src, void* const* peer_out,
+                         void* const* peer_flags, int cap, int rank, int world, int site, cudaStream_t stream) {
   PG_REQUIRE(E >= 1 && E <= MAX_EXPERTS, "moe gemm: %d experts not supported (<= %d)", E, MAX_EXPERTS);
   PG_REQUIRE(K % 64 == 0, "moe gemm: K=%d must be a multiple of 64", K);
   PG_REQUIRE(bn >= 16 && bn <= 256 && bn % 16 == 0, "moe gemm: token tile %d must be a multiple of 16 in [16, 256]", bn);
   PG_REQUIRE(status != nullptr, "moe gemm: a device status word is required");
-  if (x_rows == 0) return PG_OK;
+  if (x_rows == 0 && scatter_src == nullptr) return PG_OK;
   EncodeTiledFn enc = moe_get_encode();
   PG_REQUIRE(enc != nullptr, "cuTensorMapEncodeTiled is not available from this driver");
   int dev = 0;
@@ -385,6 +416,17 @@ extern "C" int pg_moe_grouped_gemm(const void* x, long long ldx, long long x_row
   p.scales = (const bf16*)scales;
   p.offsets = (const int*)offsets;
   p.status = (uint32_t*)status;
+  p.scatter_src = (const int*)scatter_src;
+  if (scatter_src) {
+    for (int q = 0; q < world; ++q) {
+      p.peer_out[q] = (bf16*)peer_out[q];
+      p.peer_flags[q] = (uint32_t*)peer_flags[q];
+    }
+    p.cap = cap;
+    p.rank = rank;
+    p.world = world;
+    p.site = site;
+  }
   const int stage_bytes = A_BYTES + bn * 128 + (int4 ? RAW_BYTES : 0);
   const int tail = (3 * MAX_STAGES + 4) * 8 + 64;
   p.stages = (g_max_smem[dev & 63] - g_static_smem - 1024 - tail) / stage_bytes;
@@ -417,4 +459,20 @@ extern "C" int pg_moe_grouped_gemm(const void* x, long long ldx, long long x_row
   moe_gemm_kernel<<<g_sms[dev & 63], int4 ? 320 : 192, smem, stream>>>(tm_w, tm_x, p);
   PG_LAUNCH_CHECK();
   return PG_OK;
+}
+
+extern "C" int pg_moe_grouped_gemm(const void* x, long long ldx, long long x_rows, const void* w, const void* scales, int int4, void* y,
+                                   long long ldy, const void* offsets, int E, int M, int K, int bn, void* status, cudaStream_t stream) {
+  return moe_gemm_impl(x, ldx, x_rows, w, scales, int4, y, ldy, offsets, E, M, K, bn, status, nullptr, nullptr, nullptr, 0, 0, 1, 0, stream);
+}
+
+// Expert-parallel W2: output rows are stored straight into their source ranks' combine
+// buffers (row stride ldy) and the kernel's tail raises this rank's "returned" epoch.
+extern "C" int pg_moe_grouped_gemm_return(const void* x, long long ldx, long long x_rows, const void* w, const void* scales, int int4, long long ldy,
+                                          const void* offsets, int E, int M, int K, int bn, void* status, const void* scatter_src,
+                                          void* const* peer_out, void* const* peer_flags, int cap, int rank, int world, int site,
+                                          cudaStream_t stream) {
+  PG_REQUIRE(scatter_src != nullptr && world >= 1 && world <= 8, "moe gemm return: needs the sorted-source table and 1..8 ranks");
+  return moe_gemm_impl(x, ldx, x_rows, w, scales, int4, nullptr, ldy, offsets, E, M, K, bn, status, scatter_src, peer_out, peer_flags, cap, rank, world,
+                       site, stream);
 }

@@ -276,6 +276,7 @@ class EngineConfig:
     port: int = 8000
     host: str = "127.0.0.1"
     cuda_graph: bool = True
+    precapture_graphs: bool = False  # capture every decode bucket at start-up
     dump_graph_dot: Optional[str] = None
     device_ordinal: int = 0
     tp_size: int = 1

@@ -85,6 +85,8 @@ def build_engine(ecfg: EngineConfig, mcfg: Optional[ModelConfig] = None, device=
     executor = (model.make_executor if hasattr(model, "make_executor") else TorchExecutor)(
         model, kv, page, cuda_graph=ecfg.cuda_graph, max_decode_batch=ecfg.max_decode_batch, max_blocks_per_seq=max_blocks_per_seq, seed=ecfg.seed
     )
+    if ecfg.precapture_graphs and getattr(executor, "_graphs", None) is not None:
+        executor._graphs.precapture(True, ecfg.max_decode_batch)
     scfg = SchedulerConfig(
         max_prefill_tokens=ecfg.max_prefill_tokens,
         max_decode_batch=ecfg.max_decode_batch,

@@ -243,6 +243,7 @@ class MlaMoeModel:
 
     # -- forward ----------------------------------------------------------------------
     def forward_hidden(self, token_ids, meta: AttnMeta, kv, aux_layers=()):
+        self.ep.begin_step()
         residual = ops.embedding(token_ids, self.embed)
         x = ops.rms_norm(residual, self.layers[0].input_norm, self.cfg.rms_eps)
         n = len(self.layers)

@@ -483,17 +483,14 @@ def _head_offsets(heads: int, tokens: int, device):
     return o
 
 
-_WUK_T: dict = {}
-
-
 def mla_attention(q: "_MlaQ", w_uk, w_uv, latent_layer, meta: AttnMeta, scale, kv_lora):
     """``w_uk`` [H, nope, kv_lora], ``w_uv`` [H, v, kv_lora].  The absorb GEMM wants W_UK as
     an [out = kv_lora, in = nope] weight per head; that transposed copy is made once per
     layer and kept."""
-    w_uk_t = _WUK_T.get(w_uk.data_ptr())
+    w_uk_t = getattr(w_uk, "_pg_transposed", None)  # lives and dies with the weight tensor
     if w_uk_t is None:
         w_uk_t = w_uk.transpose(1, 2).contiguous()
-        _WUK_T[w_uk.data_ptr()] = w_uk_t
+        w_uk._pg_transposed = w_uk_t
     t, h = q.tokens, q.heads
     dev = latent_layer.device
     c = ctx(dev)

@@ -34,8 +34,11 @@ class EPContext:
         self.tokens = tokens
         self.fused = fused
 
+    def begin_step(self) -> None:
+        """Start of a forward pass (the fused path numbers its MoE layers)."""
+
     def moe(self, x, ids, wts, experts, cfg):
-        if self.world == 1:
+        if self.world == 1 and self.comm != "fused":
             return _local_experts(x, ids, wts, experts, cfg)
         if self.comm == "fused" and x.is_cuda:
             return self.fused.moe(x, ids, wts, experts, cfg)

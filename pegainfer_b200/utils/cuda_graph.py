@@ -99,25 +99,45 @@ class DecodeGraphs:
         return _K().plan_decode_splits(b, geo["kv_heads"], min(self.width * self.page_size, 2048), self.device)
 
     def capture(self, b: int, greedy: bool):
+        """Capture bucket ``b``.  The warm-up pass and the capture run on padding inputs
+        (page 0, kv_len 0, state slot 0), so capturing never touches live KV or
+        recurrent state; the caller stages real inputs afterwards."""
         key = (b, greedy)
         splits = self._splits_for(b)
-        # warm up outside capture (lazy function attributes, allocator high-water mark)
+        self.d_small.zero_()
+        self.d_slots.zero_()
         s = torch.cuda.Stream(self.device)
         s.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(s):
             before = _K().launch_count(self.device)
             self._forward(b, greedy, splits)
             self.kernels_per_graph[key] = _K().launch_count(self.device) - before
+            s.synchronize()
+            g = torch.cuda.CUDAGraph()
+            if self.pool is None:
+                self.pool = torch.cuda.graph_pool_handle()
+            g.capture_begin(pool=self.pool)
+            try:
+                logits = self._forward(b, greedy, splits)
+            finally:
+                g.capture_end()
         torch.cuda.current_stream(self.device).wait_stream(s)
-        torch.cuda.synchronize(self.device)
-        g = torch.cuda.CUDAGraph()
-        if self.pool is None:
-            self.pool = torch.cuda.graph_pool_handle()
-        with torch.cuda.graph(g, pool=self.pool):
-            logits = self._forward(b, greedy, splits)
         self.graphs[key] = g
         self.logits[key] = logits
         return g
+
+    def precapture(self, greedy: bool = True, max_batch: int = 0) -> int:
+        """Capture every bucket up front so serving never pays a capture on the request
+        path (pegainfer-qwen3/src/executor.rs:1428-1496 pre-capture sweep)."""
+        n = 0
+        for b in self.buckets:
+            if max_batch and b > max_batch:
+                break
+            if (b, greedy) not in self.graphs:
+                self.capture(b, greedy)
+                n += 1
+        torch.cuda.synchronize(self.device)
+        return n
 
     def stage(self, seqs, b: int) -> None:
         """Fill the pinned mirrors for ``seqs`` padded to bucket ``b`` and start the
@@ -157,12 +177,10 @@ class DecodeGraphs:
         n = len(seqs)
         b = bucket_for(n, self.buckets)
         key = (b, greedy)
-        self.stage(seqs, b)
         g = self.graphs.get(key)
         if g is None:
-            # the warm-up pass inside capture() runs this very step once (idempotent:
-            # same tokens, same slots), so the buffers must already hold it
             g = self.capture(b, greedy)
+        self.stage(seqs, b)
         g.replay()
         self.replays += 1
         if greedy:

@@ -384,3 +384,35 @@ def test_mla_append_matches_reference():
     R.mla_append(kv_a, w, cos, sin, meta, l2, c, 1e-6)
     bf16_close(l1, l2, rel=2 ** -7, abs_=4e-3)
     status_clean()
+
+
+@pytest.mark.parametrize("int4", [False, True])
+def test_fused_ep_single_rank_self_dispatch_matches_local_pipeline(int4):
+    """World of one: the dispatch / return / combine kernels talk to this GPU's own
+    buffers, which exercises slots, epochs and the scatter epilogue without a peer."""
+    from types import SimpleNamespace
+
+    from pegainfer_b200.parallel.fused_ep import FusedEP
+
+    torch.manual_seed(5)
+    t, h, inter, e, k = 24, 512, 256, 8, 3
+    ep = FusedEP(0, 1, DEV, h, k, max_tokens=32, wait_s=1.0)
+    x = (torch.randn(t, h, device=DEV) * 0.5).bfloat16()
+    ids, w = R.router_topk(torch.randn(t, e, device=DEV), k, "softmax")
+    if int4:
+        ex = dict(w13_packed=torch.randint(-(2 ** 31), 2 ** 31 - 1, (e, 2 * inter, h // 8), dtype=torch.int32, device=DEV), w13_scale=(torch.rand(e, 2 * inter, h // 32, device=DEV) * 0.004 + 0.002).bfloat16(),
+                  w2_packed=torch.randint(-(2 ** 31), 2 ** 31 - 1, (e, h, inter // 8), dtype=torch.int32, device=DEV), w2_scale=(torch.rand(e, h, inter // 32, device=DEV) * 0.004 + 0.002).bfloat16(), offset=0)
+        ref = cu().moe_experts_int4(x, ids, w, ex["w13_packed"], ex["w13_scale"], ex["w2_packed"], ex["w2_scale"], 0)
+    else:
+        ex = dict(w13=(torch.randn(e, 2 * inter, h, device=DEV) * 0.03).bfloat16(), w2=(torch.randn(e, h, inter, device=DEV) * 0.03).bfloat16(), offset=0)
+        ref = cu().moe_experts(x, ids, w, ex["w13"], ex["w2"], 0)
+    cfg = SimpleNamespace(quant_group_size=32)
+    for step in range(3):  # epochs advance; a smaller step after a larger one must ignore stale slots
+        n = t if step != 1 else 5
+        ep.begin_step()
+        got = ep.moe(x[:n], ids[:n], w[:n], ex, cfg)
+        got2 = ep.moe(x[:n], ids[:n], w[:n], ex, cfg)  # second site in the same step
+        torch.cuda.synchronize()
+        status_clean()
+        assert torch.equal(got, got2)
+        assert (got - ref[:n]).abs().max().item() < 1e-2 * max(1.0, ref.abs().max().item())
