@@ -81,6 +81,10 @@ int pg_ep_align(const void* recv_ids, int world, int cap, int live, int e_local,
 int pg_ep_combine(const void* comb, const void* ids, const void* weights, int tokens, int k, void* out, int hidden, const void* valid_tokens,
                   void* site_flags, int world, unsigned long long wait_ns, void* status, cudaStream_t stream);
 
+// ---- LoRA (lora.cu) -----------------------------------------------------------------
+int pg_lora_delta(const void* x, long long ldx, const void* A, const void* B, const void* scale, const void* slots, void* y, long long ldy,
+                  int tokens, int K, int M, int r_max, int num_slots, cudaStream_t stream);
+
 // ---- Gated DeltaNet (gdn.cu) ------------------------------------------------------
 int pg_gdn_conv1d(const void* x, long long ldx, const void* w, void* state, void* out, long long ldo, const void* q_indptr, const void* slots,
                   int num_seqs, int channels, int K, long long state_slot_stride, cudaStream_t stream);

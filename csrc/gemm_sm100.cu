@@ -53,6 +53,7 @@ struct TpFuse {
   float eps;
   int offset;
   unsigned long long wait_ns;
+  unsigned long long* timing;  // optional: 8 globaltimer stamps per site written by CTA 0 (profiling)
 };
 
 // Consumer side: X rows arrive from peers; wait for every rank's rows-delivered epoch.
@@ -60,6 +61,7 @@ struct WaitSpec {
   const uint32_t* flags;  // local flag block of the producing site (nullptr = no wait)
   int world;
   unsigned long long wait_ns;
+  unsigned long long* timing;  // optional: [6] wait start, [7] wait end of the producing site's slot
 };
 
 struct GemmParams {
@@ -151,6 +153,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   // epoch of the fused tail, read by every CTA before any CTA can advance it
+  if (p.tp.enabled && p.tp.timing && blockIdx.x == 0 && threadIdx.x == 0) p.tp.timing[p.tp.site * 8 + 0] = globaltimer_ns();
   uint32_t tp_epoch = 0;
   if (p.tp.enabled) tp_epoch = *((volatile uint32_t*)(p.tp.flags[p.tp.rank] + p.tp.site * FLAG_WORDS_PER_SITE + 16));
 
@@ -189,7 +192,9 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             last_phase[i] = 0;
           }
           const uint32_t target = *((volatile const uint32_t*)(p.wait.flags + 16));
+          if (p.wait.timing && blockIdx.x == 0) p.wait.timing[6] = globaltimer_ns();
           wait_epochs(p.wait.flags + 8, p.wait.world, target, p.wait.wait_ns, p.status, 2u);
+          if (p.wait.timing && blockIdx.x == 0) p.wait.timing[7] = globaltimer_ns();
           fence_proxy_async_all();
           x_ready = true;
           for (int i = 0; i < pre; ++i)
@@ -381,6 +386,8 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     const int H = p.M;
     uint32_t* myflags = tp.flags[tp.rank] + tp.site * FLAG_WORDS_PER_SITE;
     const uint32_t next = tp_epoch + 1u;
+    unsigned long long* tm = (tp.timing && blockIdx.x == 0 && threadIdx.x == 0) ? tp.timing + tp.site * 8 : nullptr;
+    if (tm) tm[1] = globaltimer_ns();
     float* red = reinterpret_cast<float*>(tiles);       // pipeline smem is idle now
     uint32_t* s_ok = reinterpret_cast<uint32_t*>(tiles) + 64;
     // phase 1 done: the last CTA of this GPU tells every rank that all partial tiles are stored
@@ -391,12 +398,14 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         myflags[17] = 0u;
         for (int q = 0; q < tp.world; ++q) st_release_sys(tp.flags[q] + tp.site * FLAG_WORDS_PER_SITE + tp.rank, next);
       }
+      if (tm) tm[2] = globaltimer_ns();
     }
     const int rows_per = (p.T + tp.world - 1) / tp.world;
     const int r0 = tp.rank * rows_per;
     const int r1 = min(p.T, r0 + rows_per);
     if (r0 + (int)blockIdx.x < r1) {
       if (threadIdx.x == 0) *s_ok = wait_epochs(myflags, tp.world, next, tp.wait_ns, p.status, 3u) ? 1u : 0u;
+      if (tm) tm[3] = globaltimer_ns();
       __syncthreads();
       const bool ok = *s_ok != 0u;
       constexpr int MAXI = 11;  // hidden <= 192 * 11 * 4 = 8448
@@ -462,6 +471,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     }
     // phase 2 done: the last CTA publishes "rows of this rank delivered" and advances the epoch
     __syncthreads();
+    if (tm) tm[4] = globaltimer_ns();
     if (threadIdx.x == 0) {
       __threadfence_system();
       const uint32_t old = atomicAdd(&myflags[18], 1u);
@@ -471,6 +481,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         __threadfence();
         *((volatile uint32_t*)&myflags[16]) = next;
       }
+      if (tm) tm[5] = globaltimer_ns();
     }
   }
 }
@@ -654,6 +665,11 @@ static int gemm_impl(const void* x, const void* w, void* y, int y_is_f32, int T,
   return PG_OK;
 }
 
+static unsigned long long* g_tp_timing = nullptr;
+static int g_tp_last_site = 0;
+// Profiling hook: device buffer of 8 x uint64 per site (nullptr switches it off).
+extern "C" void pg_tp_set_timing(void* buf) { g_tp_timing = (unsigned long long*)buf; }
+
 extern "C" int pg_gemm_bf16_tn(const void* x, const void* w, void* y, int y_is_f32, int T, int M, int K, long long ldx, long long ldw,
                                long long ldy, void* ws, long long ws_bytes, void* counters, long long counter_bytes, void* status,
                                int force_splits, cudaStream_t stream) {
@@ -670,6 +686,7 @@ extern "C" int pg_gemm_bf16_tn_after_gather(const void* x, const void* w, void* 
   ws_.flags = (const uint32_t*)wait_flags;
   ws_.world = world;
   ws_.wait_ns = wait_ns;
+  ws_.timing = g_tp_timing ? g_tp_timing + g_tp_last_site * 8 : nullptr;
   return gemm_impl(x, w, y, y_is_f32, T, M, K, ldx, ldw, ldy, ws, ws_bytes, counters, counter_bytes, status, 0, nullptr,
                    wait_flags ? &ws_ : nullptr, stream);
 }
@@ -703,6 +720,8 @@ extern "C" int pg_tp_gemm_rs_norm_ag(const void* a, const void* w, int T, int hi
   tp.eps = eps;
   tp.offset = offset;
   tp.wait_ns = wait_ns;
+  tp.timing = g_tp_timing;
+  g_tp_last_site = site;
   return gemm_impl(a, w, part[rank], 1, T, hidden, K, lda, ldw, hidden, ws, ws_bytes, counters, counter_bytes, status, 0, &tp, nullptr, stream);
 }
 
@@ -711,6 +730,7 @@ extern "C" int pg_tp_wait(const void* wait_flags, int world, unsigned long long 
   w_.flags = (const uint32_t*)wait_flags;
   w_.world = world;
   w_.wait_ns = wait_ns;
+  w_.timing = nullptr;
   tp_wait_kernel<<<1, 32, 0, stream>>>(w_, (uint32_t*)status);
   PG_LAUNCH_CHECK();
   return PG_OK;

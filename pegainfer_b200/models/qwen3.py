@@ -68,6 +68,7 @@ class Qwen3Model:
         self.tp = tp
         if cfg.num_q_heads % tp.world or cfg.num_kv_heads % tp.world or cfg.intermediate_size % tp.world:
             raise ValueError(f"heads {cfg.num_q_heads}/{cfg.num_kv_heads} and FFN {cfg.intermediate_size} must divide tp={tp.world}")
+        self.lora = None  # set by lora.manager.LoraManager
         self.q_heads = cfg.num_q_heads // tp.world
         self.kv_heads = cfg.num_kv_heads // tp.world
         source = source or RandomSource(qwen3_shapes(cfg), seed=seed, dtype=dtype)
@@ -132,12 +133,31 @@ class Qwen3Model:
         n = len(self.layers)
         for i, l in enumerate(self.layers):
             qkv = tp.col_linear(x, l.qkv)
+            ls = meta.lora_slots if self.lora is not None else None
+            if ls is not None:
+                qs, ks = self.q_heads * cfg.head_dim, self.kv_heads * cfg.head_dim
+                self.lora.apply(i, "q_proj", x, qkv[:, :qs], ls)
+                self.lora.apply(i, "k_proj", x, qkv[:, qs : qs + ks], ls)
+                self.lora.apply(i, "v_proj", x, qkv[:, qs + ks :], ls)
             q = ops.qk_norm_rope_append(qkv, l.q_norm, l.k_norm, self.cos, self.sin, meta, kv.layer(i), self.q_heads, self.kv_heads, cfg.head_dim, eps)
             a = ops.paged_attention(q, kv.layer(i), meta)
-            x = tp.row_linear_add_norm(a, l.o, residual, l.post_norm, eps)
-            act = ops.swiglu(tp.col_linear(x, l.gate_up))
             next_norm = self.layers[i + 1].input_norm if i + 1 < n else self.final_norm
-            x = tp.row_linear_add_norm(act, l.down, residual, next_norm, eps)
+            if ls is None:
+                x = tp.row_linear_add_norm(a, l.o, residual, l.post_norm, eps)
+                act = ops.swiglu(tp.col_linear(x, l.gate_up))
+                x = tp.row_linear_add_norm(act, l.down, residual, next_norm, eps)
+            else:  # adapter deltas join the partial sums before the all-reduce
+                y = ops.linear(a, l.o)
+                self.lora.apply(i, "o_proj", a, y, ls)
+                x = ops.add_rms_norm(tp.all_reduce(y), residual, l.post_norm, eps)
+                gu = ops.linear(x, l.gate_up)
+                ff = gu.shape[1] // 2
+                self.lora.apply(i, "gate_proj", x, gu[:, :ff], ls)
+                self.lora.apply(i, "up_proj", x, gu[:, ff:], ls)
+                act = ops.swiglu(gu)
+                y = ops.linear(act, l.down)
+                self.lora.apply(i, "down_proj", act, y, ls)
+                x = ops.add_rms_norm(tp.all_reduce(y), residual, next_norm, eps)
             if i in aux_layers:
                 aux.append(residual.clone())
         self.last_aux = aux

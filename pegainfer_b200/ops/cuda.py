@@ -529,3 +529,16 @@ def mla_attention(q: "_MlaQ", w_uk, w_uv, latent_layer, meta: AttnMeta, scale, k
     out = torch.empty((t, h * vdim), dtype=torch.bfloat16, device=dev)
     _check(lib().pg_permute_021(_ptr(v_hm), _ptr(out), _ci(h), _ci(t), _ci(vdim), _stream()), c)
     return out
+
+
+def lora_delta_(y, x, A, B, scale, slots):
+    """In place: ``y[t] += scale[s] * B[s] @ (A[s] @ x[t])`` with ``s = slots[t]`` (negative = skip)."""
+    _bf16(x)
+    assert x.stride(-1) == 1 and y.stride(-1) == 1 and A.is_contiguous() and B.is_contiguous()
+    t, k = x.shape
+    m = y.shape[1]
+    c = ctx(x.device)
+    rc = lib().pg_lora_delta(_ptr(x), _ll(x.stride(0)), _ptr(A), _ptr(B), _ptr(scale), _ptr(slots), _ptr(y), _ll(y.stride(0)), _ci(t), _ci(k), _ci(m), _ci(A.shape[1]),
+                             _ci(A.shape[0]), _stream())
+    _check(rc, c)
+    return y

@@ -48,6 +48,8 @@ class AttnMeta:
     plan: Optional[object] = None
     # recurrent-state slot of every sequence (hybrid linear-attention models)
     state_slots: Optional[torch.Tensor] = None  # int32 [B]
+    # LoRA adapter slot of every token row (None when no request in the step uses one)
+    lora_slots: Optional[torch.Tensor] = None  # int32 [T]
     h_state_slots: Optional[list] = None
 
 
@@ -533,3 +535,13 @@ def gdn_recurrent(q, k, v, g, beta, state, meta: AttnMeta):
 
 def sigmoid_gate_mul(x, gate):
     return (x.float() * torch.sigmoid(gate.float())).to(x.dtype)
+
+
+def lora_delta_(y, x, A, B, scale, slots):
+    """In place: ``y[t] += scale[s] * B[s] @ (A[s] @ x[t])`` with ``s = slots[t]`` (negative = skip)."""
+    sl = slots.tolist()
+    for s_id in sorted(set(v for v in sl if v >= 0)):
+        rows = torch.tensor([i for i, v in enumerate(sl) if v == s_id], device=x.device)
+        tv = x[rows].float() @ A[s_id].float().t()
+        y[rows] = (y[rows].float() + float(scale[s_id]) * (tv @ B[s_id].float().t())).to(y.dtype)
+    return y

@@ -188,7 +188,7 @@ class TorchExecutor(ModelExecutor):
         t0 = time.perf_counter()
         self.steps += 1
         seqs = batch.seqs
-        if self._graphs is not None and self.mtp is None and batch.is_decode() and len(seqs) <= self.max_decode_batch and all(s.sample and s.logprobs == 0 for s in seqs):
+        if self._graphs is not None and self.mtp is None and batch.is_decode() and len(seqs) <= self.max_decode_batch and all(s.sample and s.logprobs == 0 and s.lora_slot < 0 for s in seqs):
             all_greedy = all(s.params.effectively_greedy(self.vocab_size) for s in seqs)
             out = self._graphs.run(seqs, greedy=all_greedy)
             if all_greedy:
@@ -198,6 +198,12 @@ class TorchExecutor(ModelExecutor):
                 toks = toks.tolist()
             return StepResult(tokens={s.rid: [toks[i]] for i, s in enumerate(seqs)}, elapsed_s=time.perf_counter() - t0)
         token_ids, meta = build_meta(seqs, self.page_size, self.device)
+        if any(s.lora_slot >= 0 for s in seqs):
+            rows = []
+            for s in seqs:
+                rows.extend([s.lora_slot] * len(s.input_tokens))
+            rows += [-1] * (meta.num_tokens - len(rows))
+            meta.lora_slots = torch.tensor(rows, dtype=torch.int32, device=self.device)
         self.prepare_meta(seqs, meta)
         hidden = self.model.forward_hidden(token_ids, meta, self.kv)
         # rows that need logits
