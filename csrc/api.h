@@ -17,6 +17,9 @@ int pg_version(void);
 
 // ---- GEMM (gemm_sm100.cu) ----------------------------------------------------------
 int pg_gemm_workspace_bytes(int T, int M, int K, int device, long long* ws_bytes, long long* counter_bytes);
+// How a problem would be launched on the current device:
+// out[6] = {token tile, k-splits, cluster size, grid, pipeline stages, co-resident clusters of that size}.
+int pg_gemm_plan(int T, int M, int K, int force_splits, int* out);
 int pg_gemm_bf16_tn(const void* x, const void* w, void* y, int y_is_f32, int T, int M, int K, long long ldx, long long ldw, long long ldy,
                     void* ws, long long ws_bytes, void* counters, long long counter_bytes, void* status, int force_splits,
                     cudaStream_t stream);
@@ -26,8 +29,8 @@ int pg_gemm_bf16_tn_after_gather(const void* x, const void* w, void* y, int y_is
 // Tensor-parallel fused path: GEMM -> reduce-scatter -> +residual -> RMSNorm -> all-gather over NVLink peer memory.
 int pg_tp_gemm_rs_norm_ag(const void* a, const void* w, int T, int hidden, int K, long long lda, long long ldw, void* const* part,
                           void* const* xout, void* const* flags, int rank, int world, int site, void* residual, long long ld_res,
-                          const void* norm_w, float eps, int offset, unsigned long long wait_ns, void* ws, long long ws_bytes, void* counters,
-                          long long counter_bytes, void* status, cudaStream_t stream);
+                          const void* norm_w, float eps, int offset, int one_shot, long long part_offset, unsigned long long wait_ns, void* ws,
+                          long long ws_bytes, void* counters, long long counter_bytes, void* status, cudaStream_t stream);
 int pg_tp_wait(const void* wait_flags, int world, unsigned long long wait_ns, void* status, cudaStream_t stream);
 int pg_symm_alloc(long long bytes, void** out);
 int pg_symm_free(void* p);

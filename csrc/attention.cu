@@ -92,6 +92,7 @@ __device__ __forceinline__ int swz(int r, int ch) {
 // -----------------------------------------------------------------------------------
 template <int D, int STAGES>
 __global__ void __launch_bounds__(128, (STAGES == 2 && D <= 128) ? 3 : 1) decode_attn_kernel(const AttnParams p) {
+  PG_PDL_ENTRY();
   extern __shared__ __align__(128) uint8_t smem_raw[];
   constexpr int TILE = 16;
   constexpr int CH = D / 8;            // 16-byte chunks per row
@@ -265,6 +266,7 @@ __global__ void __launch_bounds__(128, (STAGES == 2 && D <= 128) ? 3 : 1) decode
 
 template <int D>
 __global__ void __launch_bounds__(128) decode_merge_kernel(const AttnParams p) {
+  PG_PDL_ENTRY();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long unit = (long long)blockIdx.x * 4 + warp;  // (b, hq)
   if (unit >= (long long)p.num_seqs * p.hq) return;
@@ -296,6 +298,7 @@ __global__ void __launch_bounds__(128) decode_merge_kernel(const AttnParams p) {
 // -----------------------------------------------------------------------------------
 template <int D>
 __global__ void __launch_bounds__(128) prefill_attn_kernel(const AttnParams p, int window) {
+  PG_PDL_ENTRY();
   extern __shared__ __align__(128) uint8_t smem_raw[];
   constexpr int BQ = 64, BKV = 64;
   constexpr int CH = D / 8, KS = D / 16, NT = D / 8;
@@ -499,10 +502,10 @@ int launch_decode_s(const AttnParams& p, cudaStream_t stream) {
     PG_CUDA(cudaFuncSetAttribute(decode_attn_kernel<D, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     set = true;
   }
-  decode_attn_kernel<D, STAGES><<<p.num_seqs * p.hkv * p.splits, 128, smem, stream>>>(p);
+  PG_CUDA(launch_pdl(decode_attn_kernel<D, STAGES>, dim3(p.num_seqs * p.hkv * p.splits), dim3(128), (size_t)(smem), stream, p));
   PG_LAUNCH_CHECK();
   if (p.splits > 1) {
-    decode_merge_kernel<D><<<(p.num_seqs * p.hq + 3) / 4, 128, 0, stream>>>(p);
+    PG_CUDA(launch_pdl(decode_merge_kernel<D>, dim3((p.num_seqs * p.hq + 3) / 4), dim3(128), (size_t)(0), stream, p));
     PG_LAUNCH_CHECK();
   }
   return PG_OK;
@@ -523,7 +526,7 @@ int launch_prefill(const AttnParams& p, int q_tiles, int window, cudaStream_t st
     set = true;
   }
   dim3 grid(q_tiles, p.hq);
-  prefill_attn_kernel<D><<<grid, 128, smem, stream>>>(p, window);
+  PG_CUDA(launch_pdl(prefill_attn_kernel<D>, dim3(grid), dim3(128), (size_t)(smem), stream, p, window));
   PG_LAUNCH_CHECK();
   return PG_OK;
 }

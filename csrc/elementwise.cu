@@ -14,6 +14,7 @@ namespace {
 
 __global__ void gather_rows_kernel(const bf16* __restrict__ table, const int* __restrict__ ids, bf16* __restrict__ out, int rows, int width,
                                    long long table_rows, uint32_t* status) {
+  PG_PDL_ENTRY();
   const int t = blockIdx.x;
   long long id = ids[t];
   if (id < 0 || id >= table_rows) {
@@ -30,6 +31,7 @@ template <int MODE>
 __global__ void __launch_bounds__(256) rms_norm_kernel(const bf16* __restrict__ x, bf16* __restrict__ residual, const bf16* __restrict__ w,
                                                         bf16* __restrict__ y, int width, float eps, int offset, int round_before, long long ldx,
                                                         long long ldr, long long ldy) {
+  PG_PDL_ENTRY();
   __shared__ float red[32];
   const int row = blockIdx.x;
   const int nvec = width / 8;
@@ -105,6 +107,7 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const bf16* __restrict__ 
 // Per (token, head): y = rms_norm(x, w_f32) * silu(gate); one warp per head row.
 __global__ void gated_rms_norm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ gate, const float* __restrict__ w, bf16* __restrict__ y,
                                       long long rows, int dim, float eps) {
+  PG_PDL_ENTRY();
   const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int lane = threadIdx.x & 31;
@@ -126,6 +129,7 @@ __global__ void gated_rms_norm_kernel(const bf16* __restrict__ x, const bf16* __
 }
 
 __global__ void swiglu_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int rows, int inter, long long ldin, long long ldout) {
+  PG_PDL_ENTRY();
   const int nvec = inter / 8;
   const long long total = (long long)rows * nvec;
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
@@ -142,6 +146,7 @@ __global__ void swiglu_kernel(const bf16* __restrict__ gu, bf16* __restrict__ ou
 }
 
 __global__ void sigmoid_gate_mul_kernel(bf16* __restrict__ x, const bf16* __restrict__ gate, long long n) {
+  PG_PDL_ENTRY();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
     float g = __bfloat162float(gate[i]);
     x[i] = __float2bfloat16(__bfloat162float(x[i]) / (1.f + __expf(-g)));
@@ -169,6 +174,7 @@ struct RopeParams {
 };
 
 __global__ void __launch_bounds__(128) qk_norm_rope_append_kernel(const RopeParams p) {
+  PG_PDL_ENTRY();
   __shared__ float buf[4][256];
   const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads = p.hq + 2 * p.hkv;
@@ -252,7 +258,7 @@ extern "C" int pg_gather_rows(const void* table, const void* ids, void* out, int
                               cudaStream_t stream) {
   PG_REQUIRE(width % 8 == 0, "gather_rows: width %d must be a multiple of 8", width);
   if (rows == 0) return PG_OK;
-  gather_rows_kernel<<<rows, 128, 0, stream>>>((const bf16*)table, (const int*)ids, (bf16*)out, rows, width, table_rows, (uint32_t*)status);
+  PG_CUDA(launch_pdl(gather_rows_kernel, dim3(rows), dim3(128), (size_t)(0), stream, (const bf16*)table, (const int*)ids, (bf16*)out, rows, width, table_rows, (uint32_t*)status));
   PG_LAUNCH_CHECK();
   return PG_OK;
 }
@@ -262,16 +268,16 @@ extern "C" int pg_rms_norm(const void* x, void* residual, const void* w, void* y
   PG_REQUIRE(width % 8 == 0 && ldx % 8 == 0 && ldy % 8 == 0, "rms_norm: width/strides must be multiples of 8");
   if (rows == 0) return PG_OK;
   if (residual)
-    rms_norm_kernel<1><<<rows, 256, 0, stream>>>((const bf16*)x, (bf16*)residual, (const bf16*)w, (bf16*)y, width, eps, offset, round_before, ldx, ldr, ldy);
+    PG_CUDA(launch_pdl(rms_norm_kernel<1>, dim3(rows), dim3(256), (size_t)(0), stream, (const bf16*)x, (bf16*)residual, (const bf16*)w, (bf16*)y, width, eps, offset, round_before, ldx, ldr, ldy));
   else
-    rms_norm_kernel<0><<<rows, 256, 0, stream>>>((const bf16*)x, nullptr, (const bf16*)w, (bf16*)y, width, eps, offset, 0, ldx, 0, ldy);
+    PG_CUDA(launch_pdl(rms_norm_kernel<0>, dim3(rows), dim3(256), (size_t)(0), stream, (const bf16*)x, nullptr, (const bf16*)w, (bf16*)y, width, eps, offset, 0, ldx, 0, ldy));
   PG_LAUNCH_CHECK();
   return PG_OK;
 }
 
 extern "C" int pg_gated_rms_norm(const void* x, const void* gate, const void* w_f32, void* y, long long rows, int dim, float eps, cudaStream_t stream) {
   if (rows == 0) return PG_OK;
-  gated_rms_norm_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, stream>>>((const bf16*)x, (const bf16*)gate, (const float*)w_f32, (bf16*)y, rows, dim, eps);
+  PG_CUDA(launch_pdl(gated_rms_norm_kernel, dim3((unsigned)((rows + 3) / 4)), dim3(128), (size_t)(0), stream, (const bf16*)x, (const bf16*)gate, (const float*)w_f32, (bf16*)y, rows, dim, eps));
   PG_LAUNCH_CHECK();
   return PG_OK;
 }
@@ -282,7 +288,7 @@ extern "C" int pg_swiglu(const void* gate_up, void* out, int rows, int inter, lo
   long long total = (long long)rows * (inter / 8);
   int blocks = (int)((total + 255) / 256);
   if (blocks > 148 * 16) blocks = 148 * 16;
-  swiglu_kernel<<<blocks, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, rows, inter, ldin, ldout);
+  PG_CUDA(launch_pdl(swiglu_kernel, dim3(blocks), dim3(256), (size_t)(0), stream, (const bf16*)gate_up, (bf16*)out, rows, inter, ldin, ldout));
   PG_LAUNCH_CHECK();
   return PG_OK;
 }
@@ -291,7 +297,7 @@ extern "C" int pg_sigmoid_gate_mul(void* x, const void* gate, long long n, cudaS
   if (n == 0) return PG_OK;
   long long blocks = (n + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  sigmoid_gate_mul_kernel<<<(int)blocks, 256, 0, stream>>>((bf16*)x, (const bf16*)gate, n);
+  PG_CUDA(launch_pdl(sigmoid_gate_mul_kernel, dim3((int)blocks), dim3(256), (size_t)(0), stream, (bf16*)x, (const bf16*)gate, n));
   PG_LAUNCH_CHECK();
   return PG_OK;
 }
@@ -328,7 +334,7 @@ extern "C" int pg_qk_norm_rope_append(const void* qkv, long long ld, const void*
   p.eps = eps;
   p.status = (uint32_t*)status;
   long long units = (long long)tokens * (hq + 2 * hkv);
-  qk_norm_rope_append_kernel<<<(unsigned)((units + 3) / 4), 128, 0, stream>>>(p);
+  PG_CUDA(launch_pdl(qk_norm_rope_append_kernel, dim3((unsigned)((units + 3) / 4)), dim3(128), (size_t)(0), stream, p));
   PG_LAUNCH_CHECK();
   return PG_OK;
 }

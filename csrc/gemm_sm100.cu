@@ -19,6 +19,7 @@
 //
 // Takes the place of the reference's cuBLAS/cuBLASLt layer
 // (pegainfer-kernels/csrc/shared/linear.cu:294-596).
+#include <stdlib.h>
 #include <string.h>
 
 #include <mutex>
@@ -52,6 +53,8 @@ struct TpFuse {
   const bf16* norm_w;
   float eps;
   int offset;
+  int one_shot;            // 1: every rank reduces all rows itself and keeps them local (no gather hop)
+  long long part_offset;   // element offset of this call's partial buffer inside every rank's `part` (double buffering)
   unsigned long long wait_ns;
   unsigned long long* timing;  // optional: 8 globaltimer stamps per site written by CTA 0 (profiling)
 };
@@ -73,6 +76,7 @@ struct GemmParams {
   int M, T, K;
   int bn;
   int m_tiles, n_tiles, kblocks, splits;
+  int cluster;  // > 1: the k-splits of one tile are the CTAs of one cluster and reduce through distributed shared memory
   int stages;
   uint32_t tmem_cols;
   float* ws;
@@ -118,11 +122,14 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   const uint32_t base = smem_u32(smem_raw);
   uint8_t* tiles = smem_raw + (((base + 1023u) & ~1023u) - base);
   const int stage_bytes = A_BYTES + p.bn * 128;
-  uint64_t* full = reinterpret_cast<uint64_t*>(tiles + p.stages * stage_bytes);
+  float* kred = reinterpret_cast<float*>(tiles + p.stages * stage_bytes);  // [bn][128] f32, cluster mode only
+  uint64_t* full = reinterpret_cast<uint64_t*>(tiles + p.stages * stage_bytes + (p.cluster > 1 ? p.bn * BM * 4 : 0));
   uint64_t* empty = full + MAX_STAGES;
   uint64_t* tfull = empty + MAX_STAGES;
   uint64_t* tempty = tfull + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  uint64_t* kfull = tempty + 2;  // every CTA of the cluster has stored its partial tile (4 warps x cluster arrivals)
+  uint64_t* kfree = tempty + 3;  // every CTA of the cluster has finished reading this CTA's partial tile
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   uint32_t* last_flag = tmem_slot + 2;
 
@@ -138,6 +145,8 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       mbar_init(&tfull[a], 1);
       mbar_init(&tempty[a], 4);
     }
+    mbar_init(kfull, 4u * (uint32_t)p.cluster);
+    mbar_init(kfree, 4u * (uint32_t)p.cluster);
     *abort_flag = 0;
     *last_flag = 0;
     mbar_fence_init();
@@ -150,12 +159,15 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   }
   tc_fence_before();
   __syncthreads();
+  if (p.cluster > 1) cluster_sync_all();  // peers' barriers are initialised before any remote arrive
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // epoch of the fused tail, read by every CTA before any CTA can advance it
+  // Programmatic dependent launch: the prologue above, and the producer's first weight tiles
+  // below, overlap the tail of the previous kernel in the stream; everything that reads or
+  // writes activations, scratch or flags comes after pdl_wait().
+  if (threadIdx.x == 0) pdl_launch_dependents();
+  else pdl_wait();
   if (p.tp.enabled && p.tp.timing && blockIdx.x == 0 && threadIdx.x == 0) p.tp.timing[p.tp.site * 8 + 0] = globaltimer_ns();
-  uint32_t tp_epoch = 0;
-  if (p.tp.enabled) tp_epoch = *((volatile uint32_t*)(p.tp.flags[p.tp.rank] + p.tp.site * FLAG_WORDS_PER_SITE + 16));
 
   const int total = p.m_tiles * p.n_tiles * p.splits;
 
@@ -173,7 +185,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         last_phase[s] = 0;
       }
       bool ok = true;
-      bool x_ready = p.wait.flags == nullptr;
+      bool x_ready = false;
       for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
         const int tile = item / p.splits, s = item - tile * p.splits;
         const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
@@ -181,9 +193,9 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         const int kb1 = (int)(((long long)p.kblocks * (s + 1)) / p.splits);
         int kb = kb0;
         if (!x_ready) {
-          // The X rows come from peers (all-gather fused into this GEMM): stream the first
-          // weight tiles while they travel, then wait for every rank's delivery epoch and
-          // make the peer writes visible to the async proxy before TMA reads X.
+          // Weights never change, the token rows X come from the previous kernel (or, with the
+          // all-gather fused into this GEMM, from peers): stream the first weight tiles, then
+          // wait for the producer of X, then issue the X halves of those stages.
           const int pre = min(p.stages, kb1 - kb0);
           for (int i = 0; i < pre; ++i) {
             mbar_expect_tx(&full[i], (uint32_t)stage_bytes);
@@ -191,11 +203,15 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             used[i] = true;
             last_phase[i] = 0;
           }
-          const uint32_t target = *((volatile const uint32_t*)(p.wait.flags + 16));
-          if (p.wait.timing && blockIdx.x == 0) p.wait.timing[6] = globaltimer_ns();
-          wait_epochs(p.wait.flags + 8, p.wait.world, target, p.wait.wait_ns, p.status, 2u);
-          if (p.wait.timing && blockIdx.x == 0) p.wait.timing[7] = globaltimer_ns();
-          fence_proxy_async_all();
+          pdl_wait();
+          if (p.wait.flags != nullptr) {
+            // every rank's delivery epoch, then make the peer writes visible to the async proxy
+            const uint32_t target = *((volatile const uint32_t*)(p.wait.flags + 16));
+            if (p.wait.timing && blockIdx.x == 0) p.wait.timing[6] = globaltimer_ns();
+            wait_epochs(p.wait.flags + 8, p.wait.world, target, p.wait.wait_ns, p.status, 2u);
+            if (p.wait.timing && blockIdx.x == 0) p.wait.timing[7] = globaltimer_ns();
+            fence_proxy_async_all();
+          }
           x_ready = true;
           for (int i = 0; i < pre; ++i)
             tma_load_2d(tiles + i * stage_bytes + A_BYTES, &tm_x, &full[i], (kb0 + i) * BK, n_tile * p.bn, pol_x);
@@ -279,10 +295,14 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     const int et = threadIdx.x - 64;  // 0..127 among epilogue threads
     int acc = 0;
     uint32_t acc_phase = 0;
+    uint32_t kphase = 0;
+    const uint32_t cr = p.cluster > 1 ? cluster_ctarank() : 0u;
     for (int item = blockIdx.x; item < total; item += gridDim.x) {
       const int tile = item / p.splits, s = item - tile * p.splits;
       const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
       bool ok = mbar_wait(&tfull[acc], acc_phase, abort_flag);
+      // cluster mode: the peers must be done reading this CTA's previous partial tile
+      if (p.cluster > 1) ok = mbar_wait_cluster(kfree, kphase ^ 1u, abort_flag) && ok;
       ok = named_bar_all(1, 128, ok);
       if (!ok) break;
       tc_fence_after();
@@ -307,6 +327,9 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
               }
             }
           }
+        } else if (p.cluster > 1) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) kred[(c + j) * BM + r] = __uint_as_float(v[j]);
         } else {
 #pragma unroll
           for (int j = 0; j < 16; ++j) ws_part[(size_t)(c + j) * BM] = __uint_as_float(v[j]);
@@ -319,7 +342,51 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
 
-      if (p.splits > 1) {
+      if (p.cluster > 1) {
+        // Split-K reduction through distributed shared memory: every CTA of the cluster holds
+        // the f32 partial of the same output tile; CTA `cr` sums a slice of the columns over
+        // all CTAs in split order (deterministic) and stores it.
+        const uint32_t S = (uint32_t)p.cluster;
+        __syncwarp();
+        if ((uint32_t)lane < S) mbar_arrive_remote(dsmem_addr(smem_u32(kfull), (uint32_t)lane));
+        const bool full_ok = named_bar_all(1, 128, mbar_wait_cluster(kfull, kphase, abort_flag));
+        if (full_ok) {
+          const int nmax = min(p.bn, p.T - n0);
+          const int c_lo = (int)(((uint32_t)p.bn * cr) / S);
+          const int c_hi = min(nmax, (int)(((uint32_t)p.bn * (cr + 1u)) / S));
+          const uint32_t my = smem_u32(kred) + (uint32_t)r * 4u;
+          uint32_t peer[8];
+#pragma unroll
+          for (uint32_t q = 0; q < 8; ++q) peer[q] = dsmem_addr(my, q < S ? q : 0u);
+          for (int c = c_lo; c < c_hi; c += 4) {
+            float tmp[4][8];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t off = (uint32_t)(min(c + j, c_hi - 1) * BM) * 4u;
+#pragma unroll
+              for (uint32_t q = 0; q < 8; ++q) tmp[j][q] = q < S ? ld_dsmem_f32(peer[q] + off) : 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              float sum = 0.f;
+#pragma unroll
+              for (uint32_t q = 0; q < 8; ++q)
+                if (q < S) sum += tmp[j][q];
+              if (c + j < c_hi && m < p.M) {
+                if (p.y_f32)
+                  p.y_f32[(size_t)(n0 + c + j) * p.ldy + m] = sum;
+                else
+                  p.y[(size_t)(n0 + c + j) * p.ldy + m] = __float2bfloat16(sum);
+              }
+            }
+          }
+        }
+        // done with every peer's partial tile (also on the abort path, so nobody waits in vain)
+        __syncwarp();
+        if ((uint32_t)lane < S) mbar_arrive_remote(dsmem_addr(smem_u32(kfree), (uint32_t)lane));
+        kphase ^= 1u;
+        if (!full_ok) break;
+      } else if (p.splits > 1) {
         __threadfence();
         named_bar_all(1, 128, true);
         if (et == 0) {
@@ -373,6 +440,8 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 
   tc_fence_before();
   __syncthreads();
+  // no CTA may leave while a peer can still read its shared memory or arrive on its barriers
+  if (p.cluster > 1) cluster_sync_all();
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
@@ -385,6 +454,8 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     const TpFuse& tp = p.tp;
     const int H = p.M;
     uint32_t* myflags = tp.flags[tp.rank] + tp.site * FLAG_WORDS_PER_SITE;
+    // the epoch advances only after every CTA of this launch has finished its tail, so each CTA reads the same value here
+    const uint32_t tp_epoch = *((volatile uint32_t*)&myflags[16]);
     const uint32_t next = tp_epoch + 1u;
     unsigned long long* tm = (tp.timing && blockIdx.x == 0 && threadIdx.x == 0) ? tp.timing + tp.site * 8 : nullptr;
     if (tm) tm[1] = globaltimer_ns();
@@ -400,68 +471,127 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       }
       if (tm) tm[2] = globaltimer_ns();
     }
+    // Rows this rank reduces: its own slice (two-shot: reduce-scatter, then the rows are
+    // pushed to every rank) or all of them (one-shot: every rank reduces every row itself
+    // and keeps the result local; cheaper for a handful of decode rows, one hop less).
     const int rows_per = (p.T + tp.world - 1) / tp.world;
-    const int r0 = tp.rank * rows_per;
-    const int r1 = min(p.T, r0 + rows_per);
-    if (r0 + (int)blockIdx.x < r1) {
-      if (threadIdx.x == 0) *s_ok = wait_epochs(myflags, tp.world, next, tp.wait_ns, p.status, 3u) ? 1u : 0u;
-      if (tm) tm[3] = globaltimer_ns();
-      __syncthreads();
-      const bool ok = *s_ok != 0u;
-      constexpr int MAXI = 11;  // hidden <= 192 * 11 * 4 = 8448
-      const int nvec = H / 4;
-      for (int row = r0 + blockIdx.x; row < r1 && ok; row += gridDim.x) {
-        float v[MAXI][4];
-        float ss = 0.f;
+    const int r0 = tp.one_shot ? 0 : tp.rank * rows_per;
+    const int r1 = tp.one_shot ? p.T : min(p.T, r0 + rows_per);
+    const int rows = max(r1 - r0, 0);
+    const int nvec = H / 4;
+    // G CTAs share one row when there are fewer rows than CTAs (each takes a column slice
+    // and the slices exchange their sum of squares through tagged slots, in fixed order)
+    int G = 1;
+    if (rows > 0 && rows < (int)gridDim.x) {
+      G = min(min((int)gridDim.x / rows, 16), max(nvec / 64, 1));
+    }
+    const int per = (nvec + G - 1) / G;
+    const uint32_t tag = tp_epoch * 1024u + (uint32_t)tp.site + 1u;  // unique per (site, call) on this rank
+    unsigned long long* ss_slots = reinterpret_cast<unsigned long long*>(tp.flags[tp.rank] + 768 * FLAG_WORDS_PER_SITE);
+    const float* part_base[MAX_RANKS];
 #pragma unroll
-        for (int it = 0; it < MAXI; ++it) {
-          const int i = threadIdx.x + it * NUM_THREADS;
-          if (i < nvec) {
-            float4 part[MAX_RANKS];
+    for (int q = 0; q < MAX_RANKS; ++q) part_base[q] = q < tp.world ? tp.part[q] + tp.part_offset : nullptr;
+    bool waited = false, ok = true;
+    for (int unit = blockIdx.x; unit < rows * G; unit += gridDim.x) {
+      if (!waited) {
+        if (threadIdx.x == 0) *s_ok = wait_epochs(myflags, tp.world, next, tp.wait_ns, p.status, 3u) ? 1u : 0u;
+        if (tm) tm[3] = globaltimer_ns();
+        __syncthreads();
+        ok = *s_ok != 0u;
+        waited = true;
+      }
+      if (!ok) break;
+      const int row = r0 + unit / G, g = unit % G;
+      const int lo = g * per, hi = min(nvec, lo + per);
+      const int iters = (hi - lo + NUM_THREADS - 1) / NUM_THREADS;
+      const int grp = max(1, 16 / tp.world);
+      float ss = 0.f;
+      bf16* res_row = tp.residual + (size_t)row * tp.ld_res;
+      // pass 1: sum the partials of all ranks (loads batched so that one NVLink round trip
+      // covers up to 16 vectors), add the residual, store it back, accumulate squares
+      for (int it0 = 0; it0 < iters; it0 += grp) {
+        float4 buf[16];
 #pragma unroll
-            for (int q = 0; q < MAX_RANKS; ++q)
-              if (q < tp.world) part[q] = __ldcg(reinterpret_cast<const float4*>(tp.part[q] + (size_t)row * H) + i);
+        for (int gi = 0; gi < 16; ++gi) {
+          const int it = it0 + gi / tp.world, q = gi % tp.world;
+          const int i = lo + threadIdx.x + it * NUM_THREADS;
+          if (gi < grp * tp.world && it < iters && i < hi) buf[gi] = __ldcg(reinterpret_cast<const float4*>(part_base[q] + (size_t)row * H) + i);
+        }
+#pragma unroll
+        for (int gg = 0; gg < 16; ++gg) {
+          if (gg >= grp) break;
+          const int it = it0 + gg;
+          const int i = lo + threadIdx.x + it * NUM_THREADS;
+          if (it < iters && i < hi) {
             float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-            for (int q = 0; q < MAX_RANKS; ++q)
-              if (q < tp.world) {
-                a.x += part[q].x;
-                a.y += part[q].y;
-                a.z += part[q].z;
-                a.w += part[q].w;
-              }
-            bf162* rp = reinterpret_cast<bf162*>(tp.residual + (size_t)row * tp.ld_res) + 2 * i;
+            for (int q = 0; q < tp.world; ++q) {
+              const float4 b = buf[gg * tp.world + q];
+              a.x += b.x;
+              a.y += b.y;
+              a.z += b.z;
+              a.w += b.w;
+            }
+            bf162* rp = reinterpret_cast<bf162*>(res_row) + 2 * i;
             const float2 ra = __bfloat1622float2(rp[0]), rb = __bfloat1622float2(rp[1]);
             const bf162 n0 = __floats2bfloat162_rn(a.x + ra.x, a.y + ra.y), n1 = __floats2bfloat162_rn(a.z + rb.x, a.w + rb.y);
             rp[0] = n0;
             rp[1] = n1;
             const float2 f0 = __bfloat1622float2(n0), f1 = __bfloat1622float2(n1);
-            v[it][0] = f0.x;
-            v[it][1] = f0.y;
-            v[it][2] = f1.x;
-            v[it][3] = f1.y;
             ss += f0.x * f0.x + f0.y * f0.y + f1.x * f1.x + f1.y * f1.y;
           }
         }
-        ss = block_sum(ss, red);
-        const float inv = rsqrtf(ss / (float)H + tp.eps);
-#pragma unroll
-        for (int it = 0; it < MAXI; ++it) {
-          const int i = threadIdx.x + it * NUM_THREADS;
-          if (i < nvec) {
-            const bf162* wp = reinterpret_cast<const bf162*>(tp.norm_w) + 2 * i;
-            float2 w0 = __bfloat1622float2(wp[0]), w1 = __bfloat1622float2(wp[1]);
-            if (tp.offset) {
-              w0.x += 1.f;
-              w0.y += 1.f;
-              w1.x += 1.f;
-              w1.y += 1.f;
+      }
+      ss = block_sum(ss, red);
+      if (G > 1) {
+        unsigned long long* slot = ss_slots + (size_t)(row - r0) * 16;
+        if (threadIdx.x == 0) {
+          const unsigned long long v = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(ss);
+          asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(slot + g), "l"(v) : "memory");
+        }
+        float tot = 0.f;
+        if (threadIdx.x == 0) {
+          const uint64_t t0 = globaltimer_ns();
+          for (int j = 0; j < G; ++j) {
+            unsigned long long v;
+            uint32_t spins = 0;
+            while (true) {
+              asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(slot + j) : "memory");
+              if ((uint32_t)(v >> 32) == tag) break;
+              if ((++spins & 63u) == 0u && globaltimer_ns() - t0 > tp.wait_ns) {
+                atomicCAS(p.status, PG_ST_OK, PG_ST_TIMEOUT | (10u << 8));
+                break;
+              }
             }
-            uint2 packed;
-            bf162 o0 = __floats2bfloat162_rn(v[it][0] * inv * w0.x, v[it][1] * inv * w0.y);
-            bf162 o1 = __floats2bfloat162_rn(v[it][2] * inv * w1.x, v[it][3] * inv * w1.y);
-            packed.x = *reinterpret_cast<uint32_t*>(&o0);
-            packed.y = *reinterpret_cast<uint32_t*>(&o1);
+            tot += __uint_as_float((uint32_t)v);
+          }
+          red[33] = tot;
+        }
+        __syncthreads();
+        ss = red[33];
+      }
+      const float inv = rsqrtf(ss / (float)H + tp.eps);
+      // pass 2: normalise what this thread just stored (its own writes) and deliver it
+      for (int it = 0; it < iters; ++it) {
+        const int i = lo + threadIdx.x + it * NUM_THREADS;
+        if (i < hi) {
+          const bf162* rp = reinterpret_cast<const bf162*>(res_row) + 2 * i;
+          const float2 f0 = __bfloat1622float2(rp[0]), f1 = __bfloat1622float2(rp[1]);
+          const bf162* wp = reinterpret_cast<const bf162*>(tp.norm_w) + 2 * i;
+          float2 w0 = __bfloat1622float2(wp[0]), w1 = __bfloat1622float2(wp[1]);
+          if (tp.offset) {
+            w0.x += 1.f;
+            w0.y += 1.f;
+            w1.x += 1.f;
+            w1.y += 1.f;
+          }
+          uint2 packed;
+          bf162 o0 = __floats2bfloat162_rn(f0.x * inv * w0.x, f0.y * inv * w0.y);
+          bf162 o1 = __floats2bfloat162_rn(f1.x * inv * w1.x, f1.y * inv * w1.y);
+          packed.x = *reinterpret_cast<uint32_t*>(&o0);
+          packed.y = *reinterpret_cast<uint32_t*>(&o1);
+          if (tp.one_shot) {
+            reinterpret_cast<uint2*>(tp.xout[tp.rank] + (size_t)row * H)[i] = packed;
+          } else {
 #pragma unroll
             for (int q = 0; q < MAX_RANKS; ++q)
               if (q < tp.world) reinterpret_cast<uint2*>(tp.xout[q] + (size_t)row * H)[i] = packed;
@@ -473,11 +603,12 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     __syncthreads();
     if (tm) tm[4] = globaltimer_ns();
     if (threadIdx.x == 0) {
-      __threadfence_system();
+      if (!tp.one_shot) __threadfence_system();
       const uint32_t old = atomicAdd(&myflags[18], 1u);
       if (old == gridDim.x - 1) {
         myflags[18] = 0u;
-        for (int q = 0; q < tp.world; ++q) st_release_sys(tp.flags[q] + tp.site * FLAG_WORDS_PER_SITE + 8 + tp.rank, next);
+        if (!tp.one_shot)
+          for (int q = 0; q < tp.world; ++q) st_release_sys(tp.flags[q] + tp.site * FLAG_WORDS_PER_SITE + 8 + tp.rank, next);
         __threadfence();
         *((volatile uint32_t*)&myflags[16]) = next;
       }
@@ -517,6 +648,7 @@ struct DeviceInfo {
   int sms = 0;
   int max_smem = 0;
   bool attr_set = false;
+  int max_clusters[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};  // co-resident clusters of size S at one CTA per SM (0 = not usable)
 };
 DeviceInfo g_dev[64];
 std::mutex g_mu;
@@ -583,6 +715,24 @@ static int pick_splits(int tiles, int kblocks, int bn, int sms) {
   return best;
 }
 
+// Cluster size for the distributed-shared-memory split-K (token tiles up to 64 wide):
+// time ~ rounds x (k-blocks per CTA + a fixed per-item cost worth ~6 k-blocks of streaming).
+static int pick_cluster(int tiles, int kblocks, const int* max_clusters) {
+  int best = 1;
+  double best_cost = 1e30;
+  for (int s = 1; s <= 8; ++s) {
+    if (max_clusters[s] <= 0) continue;
+    if (s > 1 && kblocks / s < 4) break;
+    const int rounds = ceil_div(tiles, max_clusters[s]);
+    const double cost = (double)rounds * ((double)ceil_div(kblocks, s) + (s > 1 ? 6.0 : 4.0));
+    if (cost < best_cost - 1e-9) {
+      best_cost = cost;
+      best = s;
+    }
+  }
+  return best;
+}
+
 extern "C" int pg_gemm_workspace_bytes(int T, int M, int K, int device, long long* ws_bytes, long long* counter_bytes) {
   int sms = 0;
   PG_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
@@ -600,7 +750,7 @@ extern "C" int pg_gemm_workspace_bytes(int T, int M, int K, int device, long lon
 // `force_splits` > 0 pins the k-split count (batch-invariant serving); 0 = heuristic.
 static int gemm_impl(const void* x, const void* w, void* y, int y_is_f32, int T, int M, int K, long long ldx, long long ldw, long long ldy,
                      void* ws, long long ws_bytes, void* counters, long long counter_bytes, void* status, int force_splits,
-                     const TpFuse* tp, const WaitSpec* wait, cudaStream_t stream) {
+                     const TpFuse* tp, const WaitSpec* wait, cudaStream_t stream, int* plan_out = nullptr) {
   PG_REQUIRE(T > 0 && M > 0 && K > 0, "gemm: empty problem %dx%dx%d", T, M, K);
   PG_REQUIRE(K % 8 == 0, "gemm: K=%d must be a multiple of 8 (16-byte TMA rows)", K);
   PG_REQUIRE(status != nullptr, "gemm: a device status word is required");
@@ -613,6 +763,26 @@ static int gemm_impl(const void* x, const void* w, void* y, int y_is_f32, int T,
       PG_CUDA(cudaDeviceGetAttribute(&di.sms, cudaDevAttrMultiProcessorCount, dev));
       PG_CUDA(cudaDeviceGetAttribute(&di.max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
       PG_CUDA(cudaFuncSetAttribute(gemm_bf16_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem));
+      di.max_clusters[1] = di.sms;
+      const char* env = getenv("PEGAINFER_GEMM_CLUSTER");
+      const bool use_clusters = !(env && env[0] == '0');
+      for (int s = 2; s <= 8 && use_clusters; ++s) {
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim = dim3((unsigned)(s * di.sms));
+        cfg.blockDim = dim3(NUM_THREADS);
+        cfg.dynamicSmemBytes = (size_t)di.max_smem;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = (unsigned)s;
+        at[0].val.clusterDim.y = 1;
+        at[0].val.clusterDim.z = 1;
+        cfg.attrs = at;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_tn_kernel, &cfg) == cudaSuccess) di.max_clusters[s] = n;
+        else (void)cudaGetLastError();
+      }
       di.attr_set = true;
     }
   }
@@ -625,19 +795,32 @@ static int gemm_impl(const void* x, const void* w, void* y, int y_is_f32, int T,
   p.n_tiles = ceil_div(T, p.bn);
   p.kblocks = ceil_div(K, BK);
   const int tiles = p.m_tiles * p.n_tiles;
-  p.splits = force_splits > 0 ? force_splits : pick_splits(tiles, p.kblocks, p.bn, di.sms);
-  if (p.splits > p.kblocks) p.splits = p.kblocks;
-  if (force_splits <= 0) {
-    // never outgrow the caller's scratch: fewer splits only cost load balance
-    while (p.splits > 1 && (ws == nullptr || ws_bytes < (long long)tiles * p.splits * p.bn * BM * 4 || counter_bytes < (long long)tiles * 4)) --p.splits;
+  p.cluster = 1;
+  p.splits = 0;
+  if (p.bn <= 64 && force_splits <= 8 && di.max_clusters[2] > 0) {
+    // narrow token tiles: the k-splits of a tile form one cluster and reduce on chip
+    const int s = force_splits > 0 ? (di.max_clusters[force_splits] > 0 ? force_splits : 0) : pick_cluster(tiles, p.kblocks, di.max_clusters);
+    if (s > 0 && s <= p.kblocks) {
+      p.splits = s;
+      p.cluster = s;
+    }
   }
-  if (p.splits > 1) {
-    PG_REQUIRE(ws != nullptr && ws_bytes >= (long long)tiles * p.splits * p.bn * BM * 4, "gemm: workspace too small for %d splits", p.splits);
-    PG_REQUIRE(counters != nullptr && counter_bytes >= (long long)tiles * 4, "gemm: counter buffer too small");
+  if (p.splits == 0) {
+    p.splits = force_splits > 0 ? force_splits : pick_splits(tiles, p.kblocks, p.bn, di.sms);
+    if (p.splits > p.kblocks) p.splits = p.kblocks;
+    if (force_splits <= 0) {
+      // never outgrow the caller's scratch: fewer splits only cost load balance
+      while (p.splits > 1 && (ws == nullptr || ws_bytes < (long long)tiles * p.splits * p.bn * BM * 4 || counter_bytes < (long long)tiles * 4)) --p.splits;
+    }
+    if (p.splits > 1) {
+      PG_REQUIRE(ws != nullptr && ws_bytes >= (long long)tiles * p.splits * p.bn * BM * 4, "gemm: workspace too small for %d splits", p.splits);
+      PG_REQUIRE(counters != nullptr && counter_bytes >= (long long)tiles * 4, "gemm: counter buffer too small");
+    }
   }
   const int stage_bytes = A_BYTES + p.bn * 128;
-  const int tail = (2 * MAX_STAGES + 4) * 8 + 64;
-  p.stages = (di.max_smem - 1024 - tail) / stage_bytes;
+  const int tail = (2 * MAX_STAGES + 6) * 8 + 64;
+  const int red_bytes = p.cluster > 1 ? p.bn * BM * 4 : 0;
+  p.stages = (di.max_smem - 1024 - tail - red_bytes) / stage_bytes;
   if (p.stages > MAX_STAGES) p.stages = MAX_STAGES;
   PG_REQUIRE(p.stages >= 2, "gemm: not enough shared memory for a 2-stage pipeline");
   uint32_t cols = 32;
@@ -652,17 +835,59 @@ static int gemm_impl(const void* x, const void* w, void* y, int y_is_f32, int T,
   p.ws = (float*)ws;
   p.counters = (uint32_t*)counters;
   p.status = (uint32_t*)status;
+  if (plan_out != nullptr) {
+    const int total_items = tiles * p.splits;
+    plan_out[0] = p.bn;
+    plan_out[1] = p.splits;
+    plan_out[2] = p.cluster;
+    plan_out[3] = p.cluster > 1 ? (tiles < di.max_clusters[p.cluster] ? tiles : di.max_clusters[p.cluster]) * p.cluster : (total_items < di.sms ? total_items : di.sms);
+    plan_out[4] = p.stages;
+    plan_out[5] = di.max_clusters[p.cluster];
+    return PG_OK;
+  }
   CUtensorMap tm_w, tm_x;
   int rc = pg_make_tmap_bf16_2d(&tm_w, w, M, K, ldw, BM, BK);
   if (rc) return rc;
   rc = pg_make_tmap_bf16_2d(&tm_x, x, T, K, ldx, p.bn, BK);
   if (rc) return rc;
   const int total = tiles * p.splits;
-  const int grid = total < di.sms ? total : di.sms;
-  const size_t smem = 1024 + (size_t)p.stages * stage_bytes + tail;
-  gemm_bf16_tn_kernel<<<grid, NUM_THREADS, smem, stream>>>(tm_w, tm_x, p);
+  int grid = total < di.sms ? total : di.sms;
+  if (p.cluster > 1) grid = (tiles < di.max_clusters[p.cluster] ? tiles : di.max_clusters[p.cluster]) * p.cluster;
+  const size_t smem = 1024 + (size_t)p.stages * stage_bytes + red_bytes + tail;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute at[2];
+  int na = 0;
+  if (p.cluster > 1) {
+    at[na].id = cudaLaunchAttributeClusterDimension;
+    at[na].val.clusterDim.x = (unsigned)p.cluster;
+    at[na].val.clusterDim.y = 1;
+    at[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  cfg.attrs = at;
+  cfg.numAttrs = (unsigned)na;
+  if (pdl_enabled()) {
+    at[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.numAttrs = (unsigned)na;
+  PG_CUDA(cudaLaunchKernelEx(&cfg, gemm_bf16_tn_kernel, tm_w, tm_x, p));
   PG_LAUNCH_CHECK();
   return PG_OK;
+}
+
+// How a problem would be launched on the current device (for tests, reports and tuning):
+// out = {bn, splits, cluster, grid, stages, max co-resident clusters of that size}.
+extern "C" int pg_gemm_plan(int T, int M, int K, int force_splits, int* out) {
+  PG_REQUIRE(out != nullptr, "gemm plan: null output");
+  void* fake = reinterpret_cast<void*>(uintptr_t(256));
+  return gemm_impl(fake, fake, fake, 0, T, M, K, K, K, M, fake, 1ll << 40, fake, 1ll << 40, fake, force_splits, nullptr, nullptr, nullptr, out);
 }
 
 static unsigned long long* g_tp_timing = nullptr;
@@ -698,11 +923,11 @@ extern "C" int pg_gemm_bf16_tn_after_gather(const void* x, const void* w, void* 
 // wait on flags[rank] + site * 32 (pg_gemm_bf16_tn_after_gather or pg_tp_wait).
 extern "C" int pg_tp_gemm_rs_norm_ag(const void* a, const void* w, int T, int hidden, int K, long long lda, long long ldw, void* const* part,
                                      void* const* xout, void* const* flags, int rank, int world, int site, void* residual, long long ld_res,
-                                     const void* norm_w, float eps, int offset, unsigned long long wait_ns, void* ws, long long ws_bytes,
-                                     void* counters, long long counter_bytes, void* status, cudaStream_t stream) {
+                                     const void* norm_w, float eps, int offset, int one_shot, long long part_offset, unsigned long long wait_ns,
+                                     void* ws, long long ws_bytes, void* counters, long long counter_bytes, void* status, cudaStream_t stream) {
   PG_REQUIRE(world >= 1 && world <= MAX_RANKS && rank >= 0 && rank < world, "tp gemm: bad rank %d / world %d", rank, world);
   PG_REQUIRE(hidden % 8 == 0 && hidden <= NUM_THREADS * 11 * 4, "tp gemm: hidden %d must be a multiple of 8 and <= %d", hidden, NUM_THREADS * 11 * 4);
-  PG_REQUIRE(site >= 0 && site < 1024, "tp gemm: site %d out of range", site);
+  PG_REQUIRE(site >= 0 && site < 768, "tp gemm: site %d out of range", site);
   TpFuse tp;
   memset(&tp, 0, sizeof(tp));
   tp.enabled = 1;
@@ -719,10 +944,12 @@ extern "C" int pg_tp_gemm_rs_norm_ag(const void* a, const void* w, int T, int hi
   tp.norm_w = (const bf16*)norm_w;
   tp.eps = eps;
   tp.offset = offset;
+  tp.one_shot = one_shot;
+  tp.part_offset = part_offset;
   tp.wait_ns = wait_ns;
   tp.timing = g_tp_timing;
   g_tp_last_site = site;
-  return gemm_impl(a, w, part[rank], 1, T, hidden, K, lda, ldw, hidden, ws, ws_bytes, counters, counter_bytes, status, 0, &tp, nullptr, stream);
+  return gemm_impl(a, w, (float*)part[rank] + part_offset, 1, T, hidden, K, lda, ldw, hidden, ws, ws_bytes, counters, counter_bytes, status, 0, &tp, nullptr, stream);
 }
 
 extern "C" int pg_tp_wait(const void* wait_flags, int world, unsigned long long wait_ns, void* status, cudaStream_t stream) {

@@ -68,6 +68,7 @@ __device__ __forceinline__ ArgPair block_argmax(ArgPair a, ArgPair* red) {
 template <typename T>
 __global__ void __launch_bounds__(256) argmax_partial_kernel(const T* __restrict__ logits, long long ld, int vocab, ArgPair* __restrict__ partial,
                                                               int tiles) {
+  PG_PDL_ENTRY();
   __shared__ ArgPair red[32];
   const int row = blockIdx.y, tile = blockIdx.x;
   const T* r = logits + row * ld;
@@ -82,6 +83,7 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(const T* __restrict
 }
 
 __global__ void __launch_bounds__(128) argmax_final_kernel(const ArgPair* __restrict__ partial, int tiles, int* __restrict__ out) {
+  PG_PDL_ENTRY();
   __shared__ ArgPair red[32];
   const int row = blockIdx.x;
   ArgPair best{-FLT_MAX, 0x7fffffff};
@@ -113,6 +115,7 @@ template <typename T>
 __global__ void __launch_bounds__(ST) sample_kernel(const T* __restrict__ logits, long long ld, int vocab, const float* __restrict__ temperature,
                                                      const int* __restrict__ top_k, const float* __restrict__ top_p,
                                                      const float* __restrict__ min_p, const float* __restrict__ uniform, int* __restrict__ out) {
+  PG_PDL_ENTRY();
   __shared__ float red[32];
   __shared__ uint32_t h_cnt[256];
   __shared__ float h_mass[256];
@@ -244,6 +247,7 @@ template <typename T>
 __global__ void __launch_bounds__(256) logprob_topk_kernel(const T* __restrict__ logits, long long ld, int vocab, const int* __restrict__ picked,
                                                             int k, float* __restrict__ chosen_lp, float* __restrict__ top_lp,
                                                             int* __restrict__ top_idx) {
+  PG_PDL_ENTRY();
   __shared__ float red[32];
   __shared__ ArgPair ared[32];
   __shared__ int taken[32];
@@ -290,11 +294,11 @@ extern "C" int pg_argmax(const void* logits, int is_f32, int rows, int vocab, lo
   PG_REQUIRE(scratch_bytes >= pg_argmax_scratch_bytes(rows, vocab), "argmax: scratch too small");
   dim3 grid(tiles, rows);
   if (is_f32)
-    argmax_partial_kernel<float><<<grid, 256, 0, stream>>>((const float*)logits, ld, vocab, (ArgPair*)scratch, tiles);
+    PG_CUDA(launch_pdl(argmax_partial_kernel<float>, dim3(grid), dim3(256), (size_t)(0), stream, (const float*)logits, ld, vocab, (ArgPair*)scratch, tiles));
   else
-    argmax_partial_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)logits, ld, vocab, (ArgPair*)scratch, tiles);
+    PG_CUDA(launch_pdl(argmax_partial_kernel<bf16>, dim3(grid), dim3(256), (size_t)(0), stream, (const bf16*)logits, ld, vocab, (ArgPair*)scratch, tiles));
   PG_LAUNCH_CHECK();
-  argmax_final_kernel<<<rows, 128, 0, stream>>>((const ArgPair*)scratch, tiles, (int*)out);
+  PG_CUDA(launch_pdl(argmax_final_kernel, dim3(rows), dim3(128), (size_t)(0), stream, (const ArgPair*)scratch, tiles, (int*)out));
   PG_LAUNCH_CHECK();
   return PG_OK;
 }
@@ -303,11 +307,11 @@ extern "C" int pg_sample(const void* logits, int is_f32, int rows, int vocab, lo
                          const void* top_p, const void* min_p, const void* uniform, void* out, cudaStream_t stream) {
   if (rows == 0) return PG_OK;
   if (is_f32)
-    sample_kernel<float><<<rows, ST, 0, stream>>>((const float*)logits, ld, vocab, (const float*)temperature, (const int*)top_k, (const float*)top_p,
-                                                  (const float*)min_p, (const float*)uniform, (int*)out);
+    PG_CUDA(launch_pdl(sample_kernel<float>, dim3(rows), dim3(ST), (size_t)(0), stream, (const float*)logits, ld, vocab, (const float*)temperature, (const int*)top_k, (const float*)top_p,
+                                                  (const float*)min_p, (const float*)uniform, (int*)out));
   else
-    sample_kernel<bf16><<<rows, ST, 0, stream>>>((const bf16*)logits, ld, vocab, (const float*)temperature, (const int*)top_k, (const float*)top_p,
-                                                 (const float*)min_p, (const float*)uniform, (int*)out);
+    PG_CUDA(launch_pdl(sample_kernel<bf16>, dim3(rows), dim3(ST), (size_t)(0), stream, (const bf16*)logits, ld, vocab, (const float*)temperature, (const int*)top_k, (const float*)top_p,
+                                                 (const float*)min_p, (const float*)uniform, (int*)out));
   PG_LAUNCH_CHECK();
   return PG_OK;
 }
@@ -317,11 +321,11 @@ extern "C" int pg_logprob_topk(const void* logits, int is_f32, int rows, int voc
   PG_REQUIRE(k >= 0 && k <= 32, "logprob_topk: k=%d out of range [0, 32]", k);
   if (rows == 0) return PG_OK;
   if (is_f32)
-    logprob_topk_kernel<float><<<rows, 256, 0, stream>>>((const float*)logits, ld, vocab, (const int*)picked, k, (float*)chosen_lp, (float*)top_lp,
-                                                         (int*)top_idx);
+    PG_CUDA(launch_pdl(logprob_topk_kernel<float>, dim3(rows), dim3(256), (size_t)(0), stream, (const float*)logits, ld, vocab, (const int*)picked, k, (float*)chosen_lp, (float*)top_lp,
+                                                         (int*)top_idx));
   else
-    logprob_topk_kernel<bf16><<<rows, 256, 0, stream>>>((const bf16*)logits, ld, vocab, (const int*)picked, k, (float*)chosen_lp, (float*)top_lp,
-                                                        (int*)top_idx);
+    PG_CUDA(launch_pdl(logprob_topk_kernel<bf16>, dim3(rows), dim3(256), (size_t)(0), stream, (const bf16*)logits, ld, vocab, (const int*)picked, k, (float*)chosen_lp, (float*)top_lp,
+                                                        (int*)top_idx));
   PG_LAUNCH_CHECK();
   return PG_OK;
 }

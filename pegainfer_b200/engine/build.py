@@ -51,6 +51,10 @@ def profile_kv_blocks(model, ecfg: EngineConfig, page_size: int) -> int:
     per_block = geo["num_layers"] * 2 * page_size * geo["kv_heads"] * geo["head_dim"] * elem
     if "bytes_per_block" in geo:
         per_block = geo["bytes_per_block"](page_size)
+    draft = getattr(model, "draft_model", None)
+    if draft is not None:  # the draft model's KV buffer shares the block ids
+        dg = draft.kv_geometry()
+        per_block += dg["bytes_per_block"](page_size) if "bytes_per_block" in dg else dg["num_layers"] * 2 * page_size * dg["kv_heads"] * dg["head_dim"] * elem
     if model.device.type != "cuda":
         return ecfg.num_kv_blocks or 512
     free, total = torch.cuda.mem_get_info(model.device)
@@ -74,6 +78,11 @@ def build_engine(ecfg: EngineConfig, mcfg: Optional[ModelConfig] = None, device=
         dtype = torch.bfloat16 if device.type == "cuda" else torch.float32
     if model is None:
         model = build_model(mcfg, ecfg, device, dtype, tp, ep)
+    if ecfg.spec_method == "draft" and getattr(model, "draft_model", None) is None:
+        # built before the KV profile so that its weights and its share of every block are counted
+        from ..spec.draft_model import load_draft_model
+
+        model.draft_model = load_draft_model(ecfg, model)
     page = ecfg.kv_page_size
     nblocks = ecfg.num_kv_blocks or profile_kv_blocks(model, ecfg, page)
     if nblocks < 2:

@@ -204,6 +204,15 @@ def linear(x, w, out_dtype=None, force_splits: int = 0, out: Optional[torch.Tens
     return res
 
 
+def gemm_plan(t: int, m: int, k: int, force_splits: int = 0) -> dict:
+    """Launch plan of ``linear`` for a problem size on the current device."""
+    import ctypes
+
+    out = (ctypes.c_int * 6)()
+    _check(lib().pg_gemm_plan(_ci(t), _ci(m), _ci(k), _ci(force_splits), out), None)
+    return dict(zip(("bn", "splits", "cluster", "grid", "stages", "max_clusters"), list(out)))
+
+
 def qk_norm_rope_append(qkv, q_norm_w, k_norm_w, cos, sin, meta: AttnMeta, kv_layer, num_q_heads, num_kv_heads, head_dim, eps, offset=False, gated=False):
     _bf16(qkv)
     t = qkv.shape[0]

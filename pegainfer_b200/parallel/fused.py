@@ -39,7 +39,7 @@ class FusedTP(TPContext):
         self.max_tokens = max_tokens
         self.wait_ns = int(wait_s * 1e9)
         self.lib = _native.load()
-        part_b = max_tokens * hidden * 4
+        part_b = 2 * max_tokens * hidden * 4  # double buffered: a fast rank may already write the next site's partials
         x_b = max_tokens * hidden * 2
         flag_b = MAX_SITES * FLAG_WORDS_PER_SITE * 4
         self._off_x = (part_b + 255) // 256 * 256
@@ -52,12 +52,15 @@ class FusedTP(TPContext):
         self.flags = self.buf.view(torch.int32, (MAX_SITES, FLAG_WORDS_PER_SITE), self._off_f)
         self._site = 0
         self._pending_site = -1
+        self.one_shot_rows = 256  # one-shot all-reduce while tokens * world stays below this
         self.fused = self
         if world > 1:
             dist.barrier(group=group)
         torch.cuda.synchronize(self.device)
 
     def begin_step(self) -> None:
+        if self._site & 1:
+            raise RuntimeError("fused TP needs an even number of row-parallel projections per step (partial buffers alternate)")
         self._site = 0
         self._pending_site = -1
 
@@ -74,15 +77,17 @@ class FusedTP(TPContext):
         self._site += 1
         if self._site >= MAX_SITES:
             raise RuntimeError("too many fused collective sites in one step")
+        one_shot = t * self.world <= self.one_shot_rows
+        part_offset = (site & 1) * self.max_tokens * self.hidden
         c = K.ctx(a.device)
         rc = self.lib.pg_tp_gemm_rs_norm_ag(
             _vp(a.data_ptr()), _vp(w.data_ptr()), _ci(t), _ci(self.hidden), _ci(k), _ll(a.stride(0)), _ll(w.stride(0)), self.part_table, self.x_table,
             self.flag_table, _ci(self.rank), _ci(self.world), _ci(site), _vp(residual.data_ptr()), _ll(residual.stride(0)), _vp(norm_w.data_ptr()),
-            _cf(eps), _ci(int(offset)), _ull(self.wait_ns), _vp(c.gemm_ws.data_ptr()), _ll(c.gemm_ws.numel()), _vp(c.gemm_counters.data_ptr()),
+            _cf(eps), _ci(int(offset)), _ci(int(one_shot)), _ll(part_offset), _ull(self.wait_ns), _vp(c.gemm_ws.data_ptr()), _ll(c.gemm_ws.numel()), _vp(c.gemm_counters.data_ptr()),
             _ll(c.gemm_counters.numel() * 4), _vp(c.status.data_ptr()), _vp(torch.cuda.current_stream().cuda_stream),
         )
         K._check(rc, c)
-        self._pending_site = site
+        self._pending_site = -1 if one_shot else site  # one-shot rows are local: stream order is enough
         return self.x[:t]
 
     def col_linear(self, x, w, out_dtype=None):

@@ -115,6 +115,8 @@ class ContinuousScheduler:
     # -- admission ---------------------------------------------------------------
     def _lifetime_blocks(self, prompt_len: int, max_tokens: int) -> int:
         total = min(prompt_len + max_tokens, self.cfg.max_model_len)
+        if self.spec is not None:  # a verify step schedules the current token plus the drafts past the last output
+            total += 1 + int(getattr(self.spec, "draft_len", 1))
         return blocks_for(total, self.pool.block_size)
 
     def _future_blocks(self) -> int:
@@ -195,6 +197,8 @@ class ContinuousScheduler:
                 self.host_tier.on_retire(r, self)
             r.kv.release()
             self.ex.release_request(rid)
+            if self.spec is not None and hasattr(self.spec, "release"):
+                self.spec.release(rid)
             if self.tracer:
                 self.tracer.finish(r.q)
 
@@ -369,10 +373,19 @@ class ContinuousScheduler:
         from ..spec.speculative import accept_prefix_match
 
         seqs = []
+        propose = getattr(self.spec, "propose", None)
+        all_drafts = {}
         try:
+            if propose is not None:
+                # a separate draft model: schedule the verify pages first, the drafts are written at the same positions
+                for r in decoders:
+                    r.kv.schedule_speculative(1 + self.spec.draft_len)
+                all_drafts = propose(decoders)
             for r in decoders:
-                drafts = list(r.spec_state)
-                r.kv.schedule_speculative(1 + len(drafts))
+                if propose is None:
+                    all_drafts[r.q.id] = list(r.spec_state)
+                    r.kv.schedule_speculative(1 + len(all_drafts[r.q.id]))
+                drafts = all_drafts[r.q.id]
                 seqs.append(
                     SeqStep(rid=r.q.id, input_tokens=[r.kv.tokens[-1]] + drafts, start_pos=r.kv.committed, view=r.kv.view(), sample=True, params=r.q.request.params, step_index=r.step_index, all_rows=True)
                 )
@@ -383,7 +396,7 @@ class ContinuousScheduler:
             return
         for r in decoders:
             rid = r.q.id
-            drafts = list(r.spec_state)
+            drafts = all_drafts[rid]
             accepted = accept_prefix_match(drafts, result.tokens[rid])
             self._metrics.spec_decode.record(len(drafts), len(accepted) - 1)
             r.kv.apply_speculative(len(accepted), accepted)

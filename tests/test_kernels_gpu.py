@@ -56,6 +56,24 @@ def test_gemm_matches_fp32(t, m, k):
     status_clean()
 
 
+@pytest.mark.parametrize("t,m,k,s", [(64, 4096, 4096, 4), (50, 1000, 2048, 8), (16, 24576, 1024, 3), (64, 24576, 4096, 0), (8, 30000, 512, 5), (64, 4096, 12288, 7), (33, 128, 8192, 6)])
+def test_gemm_cluster_split_k(t, m, k, s):
+    """Narrow token tiles reduce their k-splits across a thread-block cluster (several rounds per cluster included)."""
+    torch.manual_seed(m + k)
+    x = (torch.randn(t, k, device=DEV) * 0.5).bfloat16()
+    w = (torch.randn(m, k, device=DEV) * 0.05).bfloat16()
+    ref = x.float() @ w.float().t()
+    tol = 2 ** -7 * ref.abs() + 2e-2 * math.sqrt(k / 1024)
+    y = cu().linear(x, w, force_splits=s)
+    y2 = cu().linear(x, w, force_splits=s)
+    yf = cu().linear(x, w, out_dtype=torch.float32, force_splits=s)
+    torch.cuda.synchronize()
+    status_clean()
+    assert ((y.float() - ref).abs() <= tol).all(), f"max err {(y.float() - ref).abs().max().item()}"
+    assert torch.equal(y, y2)
+    assert (yf - ref).abs().max().item() < 1e-2 * math.sqrt(k / 64)
+
+
 def test_gemm_strided_input_and_batch_invariance():
     torch.manual_seed(0)
     k, m = 1024, 768

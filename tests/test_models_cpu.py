@@ -64,3 +64,18 @@ def test_qwen35_recurrent_slots_are_recycled():
     ps = prompts_for(4, 20, seed=9)
     _, eng = gen("tiny-qwen35", ps, 4)
     assert eng.model.rec.by_rid == {}
+
+
+def test_draft_model_speculative_decode_is_lossless():
+    """A separate draft model (other random weights) proposes k tokens per round; greedy output must
+    equal plain decoding of the target for every draft length."""
+    ps = prompts_for(3, 21, seed=5)
+    plain, _ = gen("tiny-qwen3", ps, 14)
+    same, eng = gen("tiny-qwen3", ps, 14, spec_method="draft", draft_model_path="preset:tiny-qwen3", spec_draft_len=3, seed=-1, max_prefill_tokens=32)
+    other, eng2 = gen("tiny-qwen3", ps, 14, spec_method="draft", draft_model_path="preset:tiny-qwen3", spec_draft_len=2, max_prefill_tokens=32)
+    plain_m1, _ = gen("tiny-qwen3", ps, 14, seed=-1)
+    assert other == plain
+    assert same == plain_m1
+    c2 = eng2.scheduler._metrics.spec_decode
+    assert c2.num_drafts > 0 and c2.num_draft_tokens == 2 * c2.num_drafts
+    assert eng2.scheduler.spec.draft_forwards > 0
