@@ -20,6 +20,9 @@ int pg_gemm_workspace_bytes(int T, int M, int K, int device, long long* ws_bytes
 // How a problem would be launched on the current device:
 // out[6] = {token tile, k-splits, cluster size, grid, pipeline stages, co-resident clusters of that size}.
 int pg_gemm_plan(int T, int M, int K, int force_splits, int* out);
+// One-shot hint: the next GEMM launched from the calling thread also pulls `bytes` at `ptr`
+// (the weights of the GEMM after it) into L2 with its idle producer lanes.
+void pg_gemm_prefetch_next(const void* ptr, long long bytes);
 int pg_gemm_bf16_tn(const void* x, const void* w, void* y, int y_is_f32, int T, int M, int K, long long ldx, long long ldw, long long ldy,
                     void* ws, long long ws_bytes, void* counters, long long counter_bytes, void* status, int force_splits,
                     cudaStream_t stream);
@@ -69,10 +72,11 @@ int pg_moe_gather(const void* x, long long ldx, const void* sorted_src, const vo
                   cudaStream_t stream);
 int pg_moe_combine(const void* y, long long ldy, const void* route_pos, const void* weights, int tokens, int k, void* out, int width, int accumulate,
                    cudaStream_t stream);
-int pg_moe_grouped_gemm(const void* x, long long ldx, long long x_rows, const void* w, const void* scales, int int4, void* y, long long ldy,
+// quant: 0 = bf16 weights, 1 = packed INT4 group-32 (+ bf16 scales), 2 = FP8 e4m3 (+ f32 scale_inv per 128x128 block)
+int pg_moe_grouped_gemm(const void* x, long long ldx, long long x_rows, const void* w, const void* scales, int quant, void* y, long long ldy,
                         const void* offsets, int E, int M, int K, int bn, void* status, cudaStream_t stream);
 
-int pg_moe_grouped_gemm_return(const void* x, long long ldx, long long x_rows, const void* w, const void* scales, int int4, long long ldy,
+int pg_moe_grouped_gemm_return(const void* x, long long ldx, long long x_rows, const void* w, const void* scales, int quant, long long ldy,
                                const void* offsets, int E, int M, int K, int bn, void* status, const void* scatter_src, void* const* peer_out,
                                void* const* peer_flags, int cap, int rank, int world, int site, cudaStream_t stream);
 // ---- expert-parallel dispatch / combine over peer memory (ep.cu) -------------------

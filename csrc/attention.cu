@@ -31,6 +31,12 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool vali
   const int sz = valid ? 16 : 0;
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(sz) : "memory");
 }
+// Same, marked evict-first in L2: the KV cache is streamed once per step and must not push
+// out lines that are about to be reused (prefetched weights of the next GEMM).
+__device__ __forceinline__ void cp_async16_stream(void* dst, const void* src, bool valid, uint64_t policy) {
+  const int sz = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2, %3;" ::"r"(smem_u32(dst)), "l"(src), "r"(sz), "l"(policy) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
@@ -139,6 +145,7 @@ __global__ void __launch_bounds__(128, (STAGES == 2 && D <= 128) ? 3 : 1) decode
   // lookup per tile, then plain strides.
   const long long row_stride = (long long)p.hkv * D;
   const long long v_plane = (long long)p.page_size * row_stride;
+  const uint64_t kv_policy = l2_policy_evict_first();
   auto issue = [&](int tile, int stage) {
     bf16* ks_ = wsm + stage * STAGE_ELEMS;
     bf16* vs_ = ks_ + TILE * D;
@@ -152,8 +159,8 @@ __global__ void __launch_bounds__(128, (STAGES == 2 && D <= 128) ? 3 : 1) decode
         const int r = c / CH, ch = c % CH;
         const bool valid = tok0 + r < kv_len;
         const bf16* src = kbase + (valid ? r : 0) * row_stride + ch * 8;
-        cp_async16(ks_ + swz<D>(r, ch), src, valid);
-        cp_async16(vs_ + swz<D>(r, ch), src + v_plane, valid);
+        cp_async16_stream(ks_ + swz<D>(r, ch), src, valid, kv_policy);
+        cp_async16_stream(vs_ + swz<D>(r, ch), src + v_plane, valid, kv_policy);
       }
     }
     cp_async_commit();

@@ -40,12 +40,13 @@ constexpr int MAX_RANKS = 8;
 constexpr int FLAG_WORDS_PER_SITE = 32;  // [0..7] tiles-done epoch per rank, [8..15] rows-delivered epoch per rank,
                                          // [16] epoch, [17]/[18] local CTA counters of the two phases
 
-// Tensor-parallel tail fused behind the GEMM tiles: reduce-scatter of the f32 partials
-// over peer memory, + residual, RMSNorm, all-gather of the normalised rows.
+// Tensor-parallel tail fused behind the GEMM tiles: the tile epilogues push their f32
+// partials into the receive buffers of the reducing ranks (reduce-scatter by posted peer
+// stores), then + residual, RMSNorm, all-gather of the normalised rows.
 struct TpFuse {
   int enabled;
   int rank, world, site;
-  float* part[MAX_RANKS];      // every rank's partial buffer [T, hidden] f32 (peer mapped)
+  float* part[MAX_RANKS];      // every rank's receive buffer [source rank][rows][hidden] f32 (peer mapped)
   bf16* xout[MAX_RANKS];       // every rank's normalised-activation buffer [T, hidden]
   uint32_t* flags[MAX_RANKS];  // every rank's flag block
   bf16* residual;              // local [T, hidden]; rows owned by this rank are read and updated
@@ -82,7 +83,90 @@ struct GemmParams {
   float* ws;
   uint32_t* counters;
   uint32_t* status;
+  const uint8_t* pf_ptr;  // weights of the next GEMM in the stream: pulled into L2 while this kernel runs
+  long long pf_bytes;
 };
+
+// Where a finished f32 output element goes.  Plain GEMM: the local output.  Tensor-parallel
+// partial: pushed (posted peer stores, no round trip) into the receive buffer
+// [source rank][row][hidden] of the rank(s) that reduce this row, so that the transfer of a
+// tile overlaps the MMAs of the tiles still being computed and the reduction later reads
+// local memory only.
+__device__ __forceinline__ void store_out(const GemmParams& p, int n, int m, float v) {
+  if (p.tp.enabled) {
+    const TpFuse& tp = p.tp;
+    if (tp.one_shot) {
+      const size_t off = (size_t)tp.part_offset + ((size_t)tp.rank * p.T + n) * p.M + m;
+#pragma unroll
+      for (int q = 0; q < MAX_RANKS; ++q)
+        if (q < tp.world) tp.part[q][off] = v;
+    } else {
+      const int rows_per = (p.T + tp.world - 1) / tp.world;
+      const int q = n / rows_per;
+      tp.part[q][(size_t)tp.part_offset + ((size_t)tp.rank * rows_per + (n - q * rows_per)) * p.M + m] = v;
+    }
+  } else if (p.y_f32) {
+    p.y_f32[(size_t)n * p.ldy + m] = v;
+  } else {
+    p.y[(size_t)n * p.ldy + m] = __float2bfloat16(v);
+  }
+}
+
+// Row reduction of the tensor-parallel tail: sum the partials that the `W` ranks pushed
+// into this rank's receive buffer (source q at src_row + q * src_stride) in rank order, add
+// the residual, store it back, return this thread's share of the sum of squares.  All loops
+// are unrolled at compile time so that up to 16 row vectors are in flight per thread and
+// everything stays in registers (dynamic indexing would spill `buf` to local memory and
+// serialise the loads).
+constexpr int TP_KEEP = 12;
+template <int W>
+__device__ __forceinline__ float tp_sum_rows(const float* src_row, size_t src_stride, bf16* res_row, int lo, int hi, int iters, uint2 (&keep)[TP_KEEP]) {
+  constexpr int GRP = (16 / W) < 1 ? 1 : (16 / W) > TP_KEEP ? TP_KEEP : (16 / W);
+  constexpr int NB = (TP_KEEP + GRP - 1) / GRP;
+  float ss = 0.f;
+#pragma unroll
+  for (int b = 0; b < NB; ++b) {
+    if (b * GRP < iters) {
+      float4 buf[GRP][W];
+      uint2 res[GRP];
+#pragma unroll
+      for (int g = 0; g < GRP; ++g) {
+        const int it = b * GRP + g;
+        const int i = lo + (int)threadIdx.x + it * NUM_THREADS;
+        const bool live = it < TP_KEEP && it < iters && i < hi;
+#pragma unroll
+        for (int q = 0; q < W; ++q)
+          buf[g][q] = live ? __ldcg(reinterpret_cast<const float4*>(src_row + (size_t)q * src_stride) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        res[g] = live ? *(reinterpret_cast<const uint2*>(res_row) + i) : make_uint2(0u, 0u);
+      }
+#pragma unroll
+      for (int g = 0; g < GRP; ++g) {
+        const int it = b * GRP + g;
+        const int i = lo + (int)threadIdx.x + it * NUM_THREADS;
+        if (it < TP_KEEP && it < iters && i < hi) {
+          float4 a = buf[g][0];
+#pragma unroll
+          for (int q = 1; q < W; ++q) {
+            a.x += buf[g][q].x;
+            a.y += buf[g][q].y;
+            a.z += buf[g][q].z;
+            a.w += buf[g][q].w;
+          }
+          const float2 ra = __bfloat1622float2(*reinterpret_cast<const bf162*>(&res[g].x)), rb = __bfloat1622float2(*reinterpret_cast<const bf162*>(&res[g].y));
+          const bf162 n0 = __floats2bfloat162_rn(a.x + ra.x, a.y + ra.y), n1 = __floats2bfloat162_rn(a.z + rb.x, a.w + rb.y);
+          uint2 packed;
+          packed.x = *reinterpret_cast<const uint32_t*>(&n0);
+          packed.y = *reinterpret_cast<const uint32_t*>(&n1);
+          *(reinterpret_cast<uint2*>(res_row) + i) = packed;
+          if (it < TP_KEEP) keep[it] = packed;
+          const float2 f0 = __bfloat1622float2(n0), f1 = __bfloat1622float2(n1);
+          ss += f0.x * f0.x + f0.y * f0.y + f1.x * f1.x + f1.y * f1.y;
+        }
+      }
+    }
+  }
+  return ss;
+}
 
 __device__ __forceinline__ bool named_bar_all(int id, int nthreads, bool pred) {
   uint32_t r;
@@ -239,6 +323,19 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           }
         }
       }
+      // All of this CTA's own loads are issued.  From here to the first load of the next GEMM
+      // in the stream (epilogue, launch gap, the small kernel in between, the next prologue)
+      // HBM would sit idle: pull a slice of the NEXT GEMM's weights into L2 meanwhile
+      // (weights never change, so no ordering is needed; the prefetch is fire-and-forget).
+      if (p.pf_bytes > 0) {
+        constexpr long long CH = 16384;
+        const long long nch = (p.pf_bytes + CH - 1) / CH;
+        for (long long c = blockIdx.x; c < nch; c += gridDim.x) {
+          const long long left = p.pf_bytes - c * CH;
+          const uint32_t sz = (uint32_t)(left < CH ? left : CH) & ~15u;
+          if (sz) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.pf_ptr + c * CH), "r"(sz) : "memory");
+        }
+      }
       // Drain: every bulk copy this thread issued must have landed before the CTA exits.
       for (int s = 0; s < p.stages; ++s) {
         if (!used[s]) continue;
@@ -319,12 +416,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int n = n0 + c + j;
-              if (n < p.T) {
-                if (p.y_f32)
-                  p.y_f32[(size_t)n * p.ldy + m] = __uint_as_float(v[j]);
-                else
-                  p.y[(size_t)n * p.ldy + m] = __float2bfloat16(__uint_as_float(v[j]));
-              }
+              if (n < p.T) store_out(p, n, m, __uint_as_float(v[j]));
             }
           }
         } else if (p.cluster > 1) {
@@ -372,12 +464,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 #pragma unroll
               for (uint32_t q = 0; q < 8; ++q)
                 if (q < S) sum += tmp[j][q];
-              if (c + j < c_hi && m < p.M) {
-                if (p.y_f32)
-                  p.y_f32[(size_t)(n0 + c + j) * p.ldy + m] = sum;
-                else
-                  p.y[(size_t)(n0 + c + j) * p.ldy + m] = __float2bfloat16(sum);
-              }
+              if (c + j < c_hi && m < p.M) store_out(p, n0 + c + j, m, sum);
             }
           }
         }
@@ -423,12 +510,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
                 const int n = c + j;
-                if (n < nmax) {
-                  if (p.y_f32)
-                    p.y_f32[(size_t)(n0 + n) * p.ldy + m] = acc[j];
-                  else
-                    p.y[(size_t)(n0 + n) * p.ldy + m] = __float2bfloat16(acc[j]);
-                }
+                if (n < nmax) store_out(p, n0 + n, m, acc[j]);
               }
             }
           }
@@ -467,6 +549,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       const uint32_t old = atomicAdd(&myflags[17], 1u);
       if (old == gridDim.x - 1) {
         myflags[17] = 0u;
+        __threadfence_system();  // acquire side of the counter: every CTA's pushed tiles precede the signal
         for (int q = 0; q < tp.world; ++q) st_release_sys(tp.flags[q] + tp.site * FLAG_WORDS_PER_SITE + tp.rank, next);
       }
       if (tm) tm[2] = globaltimer_ns();
@@ -481,16 +564,18 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     const int nvec = H / 4;
     // G CTAs share one row when there are fewer rows than CTAs (each takes a column slice
     // and the slices exchange their sum of squares through tagged slots, in fixed order)
+    // (only worth the exchange when there are far fewer rows than CTAs)
     int G = 1;
-    if (rows > 0 && rows < (int)gridDim.x) {
+    if (rows > 0 && rows * 4 <= (int)gridDim.x) {
       G = min(min((int)gridDim.x / rows, 16), max(nvec / 64, 1));
     }
+    G = max(G, (nvec + TP_KEEP * NUM_THREADS - 1) / (TP_KEEP * NUM_THREADS));  // a thread keeps at most TP_KEEP vectors of a row
     const int per = (nvec + G - 1) / G;
     const uint32_t tag = tp_epoch * 1024u + (uint32_t)tp.site + 1u;  // unique per (site, call) on this rank
     unsigned long long* ss_slots = reinterpret_cast<unsigned long long*>(tp.flags[tp.rank] + 768 * FLAG_WORDS_PER_SITE);
-    const float* part_base[MAX_RANKS];
-#pragma unroll
-    for (int q = 0; q < MAX_RANKS; ++q) part_base[q] = q < tp.world ? tp.part[q] + tp.part_offset : nullptr;
+    // every rank pushed its partial rows into this rank's receive buffer [source rank][row][hidden]
+    const float* recv = tp.part[tp.rank] + tp.part_offset;
+    const size_t src_stride = (size_t)(tp.one_shot ? p.T : rows_per) * H;
     bool waited = false, ok = true;
     for (int unit = blockIdx.x; unit < rows * G; unit += gridDim.x) {
       if (!waited) {
@@ -504,42 +589,19 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       const int row = r0 + unit / G, g = unit % G;
       const int lo = g * per, hi = min(nvec, lo + per);
       const int iters = (hi - lo + NUM_THREADS - 1) / NUM_THREADS;
-      const int grp = max(1, 16 / tp.world);
-      float ss = 0.f;
       bf16* res_row = tp.residual + (size_t)row * tp.ld_res;
-      // pass 1: sum the partials of all ranks (loads batched so that one NVLink round trip
-      // covers up to 16 vectors), add the residual, store it back, accumulate squares
-      for (int it0 = 0; it0 < iters; it0 += grp) {
-        float4 buf[16];
-#pragma unroll
-        for (int gi = 0; gi < 16; ++gi) {
-          const int it = it0 + gi / tp.world, q = gi % tp.world;
-          const int i = lo + threadIdx.x + it * NUM_THREADS;
-          if (gi < grp * tp.world && it < iters && i < hi) buf[gi] = __ldcg(reinterpret_cast<const float4*>(part_base[q] + (size_t)row * H) + i);
-        }
-#pragma unroll
-        for (int gg = 0; gg < 16; ++gg) {
-          if (gg >= grp) break;
-          const int it = it0 + gg;
-          const int i = lo + threadIdx.x + it * NUM_THREADS;
-          if (it < iters && i < hi) {
-            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int q = 0; q < tp.world; ++q) {
-              const float4 b = buf[gg * tp.world + q];
-              a.x += b.x;
-              a.y += b.y;
-              a.z += b.z;
-              a.w += b.w;
-            }
-            bf162* rp = reinterpret_cast<bf162*>(res_row) + 2 * i;
-            const float2 ra = __bfloat1622float2(rp[0]), rb = __bfloat1622float2(rp[1]);
-            const bf162 n0 = __floats2bfloat162_rn(a.x + ra.x, a.y + ra.y), n1 = __floats2bfloat162_rn(a.z + rb.x, a.w + rb.y);
-            rp[0] = n0;
-            rp[1] = n1;
-            const float2 f0 = __bfloat1622float2(n0), f1 = __bfloat1622float2(n1);
-            ss += f0.x * f0.x + f0.y * f0.y + f1.x * f1.x + f1.y * f1.y;
-          }
-        }
+      const float* src_row = recv + (size_t)(row - r0) * H;
+      uint2 keep[TP_KEEP];  // this thread's updated residual values (4 bf16 each), reused by pass 2
+      float ss;
+      switch (tp.world) {
+        case 1: ss = tp_sum_rows<1>(src_row, src_stride, res_row, lo, hi, iters, keep); break;
+        case 2: ss = tp_sum_rows<2>(src_row, src_stride, res_row, lo, hi, iters, keep); break;
+        case 3: ss = tp_sum_rows<3>(src_row, src_stride, res_row, lo, hi, iters, keep); break;
+        case 4: ss = tp_sum_rows<4>(src_row, src_stride, res_row, lo, hi, iters, keep); break;
+        case 5: ss = tp_sum_rows<5>(src_row, src_stride, res_row, lo, hi, iters, keep); break;
+        case 6: ss = tp_sum_rows<6>(src_row, src_stride, res_row, lo, hi, iters, keep); break;
+        case 7: ss = tp_sum_rows<7>(src_row, src_stride, res_row, lo, hi, iters, keep); break;
+        default: ss = tp_sum_rows<8>(src_row, src_stride, res_row, lo, hi, iters, keep); break;
       }
       ss = block_sum(ss, red);
       if (G > 1) {
@@ -570,14 +632,15 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         ss = red[33];
       }
       const float inv = rsqrtf(ss / (float)H + tp.eps);
-      // pass 2: normalise what this thread just stored (its own writes) and deliver it
-      for (int it = 0; it < iters; ++it) {
+      // pass 2: normalise the values kept in registers and deliver them
+#pragma unroll
+      for (int it = 0; it < TP_KEEP; ++it) {
         const int i = lo + threadIdx.x + it * NUM_THREADS;
-        if (i < hi) {
-          const bf162* rp = reinterpret_cast<const bf162*>(res_row) + 2 * i;
-          const float2 f0 = __bfloat1622float2(rp[0]), f1 = __bfloat1622float2(rp[1]);
-          const bf162* wp = reinterpret_cast<const bf162*>(tp.norm_w) + 2 * i;
-          float2 w0 = __bfloat1622float2(wp[0]), w1 = __bfloat1622float2(wp[1]);
+        if (it < iters && i < hi) {
+          const uint2 kv = keep[it];
+          const float2 f0 = __bfloat1622float2(*reinterpret_cast<const bf162*>(&kv.x)), f1 = __bfloat1622float2(*reinterpret_cast<const bf162*>(&kv.y));
+          const uint2 wv = *(reinterpret_cast<const uint2*>(tp.norm_w) + i);
+          float2 w0 = __bfloat1622float2(*reinterpret_cast<const bf162*>(&wv.x)), w1 = __bfloat1622float2(*reinterpret_cast<const bf162*>(&wv.y));
           if (tp.offset) {
             w0.x += 1.f;
             w0.y += 1.f;
@@ -715,6 +778,10 @@ static int pick_splits(int tiles, int kblocks, int bn, int sms) {
   return best;
 }
 
+// One-shot hint consumed by the next GEMM launched from this thread.
+thread_local const void* t_pf_ptr = nullptr;
+thread_local long long t_pf_bytes = 0;
+
 // Cluster size for the distributed-shared-memory split-K (token tiles up to 64 wide):
 // time ~ rounds x (k-blocks per CTA + a fixed per-item cost worth ~6 k-blocks of streaming).
 static int pick_cluster(int tiles, int kblocks, const int* max_clusters) {
@@ -835,6 +902,12 @@ static int gemm_impl(const void* x, const void* w, void* y, int y_is_f32, int T,
   p.ws = (float*)ws;
   p.counters = (uint32_t*)counters;
   p.status = (uint32_t*)status;
+  if (plan_out == nullptr) {
+    p.pf_ptr = (const uint8_t*)t_pf_ptr;
+    p.pf_bytes = (t_pf_ptr && T <= 256) ? t_pf_bytes : 0;  // only the weight-streaming regime has idle HBM time to fill
+    t_pf_ptr = nullptr;
+    t_pf_bytes = 0;
+  }
   if (plan_out != nullptr) {
     const int total_items = tiles * p.splits;
     plan_out[0] = p.bn;
@@ -884,6 +957,19 @@ static int gemm_impl(const void* x, const void* w, void* y, int y_is_f32, int T,
 
 // How a problem would be launched on the current device (for tests, reports and tuning):
 // out = {bn, splits, cluster, grid, stages, max co-resident clusters of that size}.
+// The next GEMM launched from the calling thread also pulls `bytes` at `ptr` (16-byte
+// aligned; normally the leading part of the weight matrix of the GEMM that follows it in
+// the stream) into L2.  bytes <= 0 or ptr == nullptr clears the hint.
+extern "C" void pg_gemm_prefetch_next(const void* ptr, long long bytes) {
+  if (ptr == nullptr || bytes <= 0 || ((uintptr_t)ptr & 15) != 0) {
+    t_pf_ptr = nullptr;
+    t_pf_bytes = 0;
+    return;
+  }
+  t_pf_ptr = ptr;
+  t_pf_bytes = bytes;
+}
+
 extern "C" int pg_gemm_plan(int T, int M, int K, int force_splits, int* out) {
   PG_REQUIRE(out != nullptr, "gemm plan: null output");
   void* fake = reinterpret_cast<void*>(uintptr_t(256));
@@ -926,7 +1012,8 @@ extern "C" int pg_tp_gemm_rs_norm_ag(const void* a, const void* w, int T, int hi
                                      const void* norm_w, float eps, int offset, int one_shot, long long part_offset, unsigned long long wait_ns,
                                      void* ws, long long ws_bytes, void* counters, long long counter_bytes, void* status, cudaStream_t stream) {
   PG_REQUIRE(world >= 1 && world <= MAX_RANKS && rank >= 0 && rank < world, "tp gemm: bad rank %d / world %d", rank, world);
-  PG_REQUIRE(hidden % 8 == 0 && hidden <= NUM_THREADS * 11 * 4, "tp gemm: hidden %d must be a multiple of 8 and <= %d", hidden, NUM_THREADS * 11 * 4);
+  PG_REQUIRE(hidden % 8 == 0 && hidden <= 16 * TP_KEEP * NUM_THREADS * 4, "tp gemm: hidden %d must be a multiple of 8 and <= %d", hidden, 16 * TP_KEEP * NUM_THREADS * 4);
+  PG_REQUIRE(((uintptr_t)residual & 7) == 0 && ld_res % 4 == 0 && ((uintptr_t)norm_w & 7) == 0, "tp gemm: residual rows and norm weights must be 8-byte aligned");
   PG_REQUIRE(site >= 0 && site < 768, "tp gemm: site %d out of range", site);
   TpFuse tp;
   memset(&tp, 0, sizeof(tp));

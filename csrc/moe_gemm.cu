@@ -17,8 +17,12 @@
 //          raw buffer, four dequantisation warps expand it to bf16 ((nibble - 8) * scale,
 //          one rounding) directly into the 128-byte-swizzled A tile and hand it to the MMA
 //          warp through an mbarrier; HBM traffic stays at 4.5 bits per weight.
+//   fp8    W e4m3 [E, M, K] with f32 scale_inv [E, ceil(M/128), ceil(K/128)] (block-scaled
+//          checkpoints): TMA brings the raw 8 KB tile, the same four warps convert e4m3 ->
+//          f32 (exact), multiply by the block's scale_inv and round once to bf16 into the
+//          swizzled A tile; HBM traffic is one byte per weight.
 //
-// warp 0 TMA producer | warp 1 MMA issuer + TMEM owner | warps 2-5 epilogue | warps 6-9 dequant (int4)
+// warp 0 TMA producer | warp 1 MMA issuer + TMEM owner | warps 2-5 epilogue | warps 6-9 dequant (int4 / fp8)
 //
 // Takes the place of the reference's Marlin W4A16 MoE kernel
 // (pegainfer-kernels/csrc/kimi_k2/kimi_marlin_wna16.cu:241-340, vllm_marlin/**) and its
@@ -26,6 +30,8 @@
 #include <string.h>
 
 #include <mutex>
+
+#include <cuda_fp8.h>
 
 #include "api.h"
 #include "common.cuh"
@@ -35,6 +41,7 @@ namespace {
 constexpr int BM = 128, BK = 64;
 constexpr int A_BYTES = BM * BK * 2;
 constexpr int RAW_BYTES = BM * BK / 2;  // packed int4 tile
+constexpr int RAW_BYTES_FP8 = BM * BK;  // fp8 tile
 constexpr int MAX_STAGES = 10;
 constexpr int MAX_EXPERTS = 512;
 
@@ -44,8 +51,8 @@ struct MoeGemmParams {
   int M, K, E;
   int bn, stages, kblocks, m_tiles;
   uint32_t tmem_cols;
-  int int4;
-  const bf16* scales;  // [E, M, K/32]
+  int quant;           // 0 bf16, 1 int4 group-32, 2 fp8 e4m3 with 128x128 block scales
+  const void* scales;  // int4: bf16 [E, M, K/32]; fp8: f32 scale_inv [E, ceil(M/128), ceil(K/128)]
   const int* offsets;  // [E+1]
   uint32_t* status;
   // expert-parallel return path: output row r goes to rank (scatter_src[r] / cap), slot
@@ -104,7 +111,8 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
   const uint32_t base = smem_u32(smem_raw);
   uint8_t* tiles = smem_raw + (((base + 1023u) & ~1023u) - base);
   const int b_bytes = p.bn * 128;
-  const int stage_bytes = A_BYTES + b_bytes + (p.int4 ? RAW_BYTES : 0);
+  const int raw_bytes = p.quant == 1 ? RAW_BYTES : p.quant == 2 ? RAW_BYTES_FP8 : 0;
+  const int stage_bytes = A_BYTES + b_bytes + raw_bytes;
   uint64_t* full = reinterpret_cast<uint64_t*>(tiles + p.stages * stage_bytes);
   uint64_t* empty = full + MAX_STAGES;
   uint64_t* aready = empty + MAX_STAGES;
@@ -176,9 +184,9 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
             break;
           }
           uint8_t* st = tiles + stage * stage_bytes;
-          if (p.int4) {
-            mbar_expect_tx(&full[stage], (uint32_t)(RAW_BYTES + b_bytes));
-            tma_load_3d(st + A_BYTES + b_bytes, &tm_w, &full[stage], kb * (BK / 8), it.m_tile * BM, it.e, pol_w);
+          if (p.quant) {
+            mbar_expect_tx(&full[stage], (uint32_t)(raw_bytes + b_bytes));
+            tma_load_3d(st + A_BYTES + b_bytes, &tm_w, &full[stage], p.quant == 1 ? kb * (BK / 8) : kb * BK, it.m_tile * BM, it.e, pol_w);
           } else {
             mbar_expect_tx(&full[stage], (uint32_t)(A_BYTES + b_bytes));
             tma_load_3d(st, &tm_w, &full[stage], kb * BK, it.m_tile * BM, it.e, pol_w);
@@ -213,8 +221,8 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * p.bn);
         for (int kb = 0; kb < p.kblocks; ++kb) {
-          // int4: a_ready implies the packed tile and X landed and the bf16 A tile is written
-          if (!mbar_wait(p.int4 ? &aready[stage] : &full[stage], phase, abort_flag)) {
+          // quantised weights: a_ready implies the raw tile and X landed and the bf16 A tile is written
+          if (!mbar_wait(p.quant ? &aready[stage] : &full[stage], phase, abort_flag)) {
             ok = false;
             break;
           }
@@ -279,7 +287,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
-  } else if (p.int4) {
+  } else if (p.quant == 1) {
     // dequantisation warps: thread r expands row r of the packed tile into the swizzled A tile
     const int r = threadIdx.x - 192;  // 0..127
     int stage = 0;
@@ -291,7 +299,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
       if (!locate(p, s_tiles, item, cur, it)) break;
       const int m = it.m_tile * BM + r;
-      const bf16* srow = p.scales + ((size_t)it.e * p.M + (m < p.M ? m : 0)) * groups_per_row;
+      const bf16* srow = reinterpret_cast<const bf16*>(p.scales) + ((size_t)it.e * p.M + (m < p.M ? m : 0)) * groups_per_row;
       for (int kb = 0; kb < p.kblocks; ++kb) {
         if (!mbar_wait(&full[stage], phase, abort_flag)) {
           ok = false;
@@ -321,6 +329,58 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
             o[q] = *reinterpret_cast<uint32_t*>(&val);
           }
           *reinterpret_cast<uint4*>(a_row + ((ch ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(&aready[stage]);
+        if (++stage == p.stages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else if (p.quant == 2) {
+    // fp8 dequantisation warps: thread r expands the 64 e4m3 bytes of row r (exact in half,
+    // then f32 * scale_inv of the 128x128 block, rounded once to bf16) into the swizzled A tile
+    const int r = threadIdx.x - 192;  // 0..127
+    int stage = 0;
+    uint32_t phase = 0;
+    ItemCursor cur;
+    Item it;
+    const int mb = (p.M + 127) / 128, kbk = (p.K + 127) / 128;
+    const float* sc = reinterpret_cast<const float*>(p.scales);
+    bool ok = true;
+    for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
+      if (!locate(p, s_tiles, item, cur, it)) break;
+      const float* srow = sc + ((size_t)it.e * mb + it.m_tile) * kbk;
+      for (int kb = 0; kb < p.kblocks; ++kb) {
+        if (!mbar_wait(&full[stage], phase, abort_flag)) {
+          ok = false;
+          break;
+        }
+        uint8_t* st = tiles + stage * stage_bytes;
+        const uint4* raw = reinterpret_cast<const uint4*>(st + A_BYTES + b_bytes + r * 64);
+        const float scale = srow[kb >> 1];
+        uint8_t* a_row = st + r * 128;
+#pragma unroll
+        for (int half = 0; half < 4; ++half) {
+          const uint4 v = raw[half];
+          const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            // 8 bytes -> 8 bf16 = one 16-byte chunk of the A row
+            uint32_t o[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint32_t w = words[hh * 2 + (q >> 1)];
+              const __nv_fp8x2_storage_t pair = (__nv_fp8x2_storage_t)((w >> (16 * (q & 1))) & 0xFFFFu);
+              const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(pair, __NV_E4M3);
+              const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hr));
+              const bf162 b = __floats2bfloat162_rn(f.x * scale, f.y * scale);
+              o[q] = *reinterpret_cast<const uint32_t*>(&b);
+            }
+            const int ch = half * 2 + hh;
+            *reinterpret_cast<uint4*>(a_row + ((ch ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+          }
         }
         fence_proxy_async_smem();
         mbar_arrive(&aready[stage]);
@@ -376,9 +436,10 @@ std::mutex g_mu;
 }  // namespace
 
 // x [rows, K] bf16 (rows sorted by expert), offsets [E+1] device int32, y [rows, M] bf16.
-// w: bf16 [E, M, K], or packed int32 [E, M, K/8] with scales bf16 [E, M, K/32] when int4 != 0.
+// w: bf16 [E, M, K] (quant 0); packed int32 [E, M, K/8] with scales bf16 [E, M, K/32] (quant 1);
+// fp8 e4m3 [E, M, K] with f32 scale_inv [E, ceil(M/128), ceil(K/128)] (quant 2).
 // `bn` is the token tile (multiple of 16, <= 256): pick it near the expected rows per expert.
-static int moe_gemm_impl(const void* x, long long ldx, long long x_rows, const void* w, const void* scales, int int4, void* y, long long ldy,
+static int moe_gemm_impl(const void* x, long long ldx, long long x_rows, const void* w, const void* scales, int quant, void* y, long long ldy,
                          const void* offsets, int E, int M, int K, int bn, void* status, const void* scatter_src, void* const* peer_out,
                          void* const* peer_flags, int cap, int rank, int world, int site, cudaStream_t stream) {
   PG_REQUIRE(E >= 1 && E <= MAX_EXPERTS, "moe gemm: %d experts not supported (<= %d)", E, MAX_EXPERTS);
@@ -412,8 +473,10 @@ static int moe_gemm_impl(const void* x, long long ldx, long long x_rows, const v
   p.bn = bn;
   p.kblocks = K / BK;
   p.m_tiles = ceil_div(M, BM);
-  p.int4 = int4;
-  p.scales = (const bf16*)scales;
+  PG_REQUIRE(quant >= 0 && quant <= 2, "moe gemm: unknown weight storage mode %d", quant);
+  PG_REQUIRE(quant == 0 || scales != nullptr, "moe gemm: quantised weights need scales");
+  p.quant = quant;
+  p.scales = scales;
   p.offsets = (const int*)offsets;
   p.status = (uint32_t*)status;
   p.scatter_src = (const int*)scatter_src;
@@ -427,7 +490,7 @@ static int moe_gemm_impl(const void* x, long long ldx, long long x_rows, const v
     p.world = world;
     p.site = site;
   }
-  const int stage_bytes = A_BYTES + bn * 128 + (int4 ? RAW_BYTES : 0);
+  const int stage_bytes = A_BYTES + bn * 128 + (quant == 1 ? RAW_BYTES : quant == 2 ? RAW_BYTES_FP8 : 0);
   const int tail = (3 * MAX_STAGES + 4) * 8 + 64;
   p.stages = (g_max_smem[dev & 63] - g_static_smem - 1024 - tail) / stage_bytes;
   if (p.stages > MAX_STAGES) p.stages = MAX_STAGES;
@@ -438,7 +501,14 @@ static int moe_gemm_impl(const void* x, long long ldx, long long x_rows, const v
 
   CUtensorMap tm_w, tm_x;
   cuuint32_t estr[3] = {1, 1, 1};
-  if (int4) {
+  if (quant == 2) {
+    cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)M, (cuuint64_t)E};
+    cuuint64_t strides[2] = {(cuuint64_t)K, (cuuint64_t)M * K};
+    cuuint32_t box[3] = {BK, BM, 1};
+    CUresult r = enc(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(w), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    PG_REQUIRE(r == CUDA_SUCCESS, "moe gemm: fp8 weight tensor map failed (%d)", (int)r);
+  } else if (quant == 1) {
     cuuint64_t dims[3] = {(cuuint64_t)(K / 8), (cuuint64_t)M, (cuuint64_t)E};
     cuuint64_t strides[2] = {(cuuint64_t)(K / 8) * 4, (cuuint64_t)M * (K / 8) * 4};
     cuuint32_t box[3] = {BK / 8, BM, 1};
@@ -456,23 +526,23 @@ static int moe_gemm_impl(const void* x, long long ldx, long long x_rows, const v
   int rc = pg_make_tmap_bf16_2d(&tm_x, x, x_rows, K, ldx, bn, BK);
   if (rc) return rc;
   const size_t smem = 1024 + (size_t)p.stages * stage_bytes + tail;
-  moe_gemm_kernel<<<g_sms[dev & 63], int4 ? 320 : 192, smem, stream>>>(tm_w, tm_x, p);
+  moe_gemm_kernel<<<g_sms[dev & 63], quant ? 320 : 192, smem, stream>>>(tm_w, tm_x, p);
   PG_LAUNCH_CHECK();
   return PG_OK;
 }
 
-extern "C" int pg_moe_grouped_gemm(const void* x, long long ldx, long long x_rows, const void* w, const void* scales, int int4, void* y,
+extern "C" int pg_moe_grouped_gemm(const void* x, long long ldx, long long x_rows, const void* w, const void* scales, int quant, void* y,
                                    long long ldy, const void* offsets, int E, int M, int K, int bn, void* status, cudaStream_t stream) {
-  return moe_gemm_impl(x, ldx, x_rows, w, scales, int4, y, ldy, offsets, E, M, K, bn, status, nullptr, nullptr, nullptr, 0, 0, 1, 0, stream);
+  return moe_gemm_impl(x, ldx, x_rows, w, scales, quant, y, ldy, offsets, E, M, K, bn, status, nullptr, nullptr, nullptr, 0, 0, 1, 0, stream);
 }
 
 // Expert-parallel W2: output rows are stored straight into their source ranks' combine
 // buffers (row stride ldy) and the kernel's tail raises this rank's "returned" epoch.
-extern "C" int pg_moe_grouped_gemm_return(const void* x, long long ldx, long long x_rows, const void* w, const void* scales, int int4, long long ldy,
+extern "C" int pg_moe_grouped_gemm_return(const void* x, long long ldx, long long x_rows, const void* w, const void* scales, int quant, long long ldy,
                                           const void* offsets, int E, int M, int K, int bn, void* status, const void* scatter_src,
                                           void* const* peer_out, void* const* peer_flags, int cap, int rank, int world, int site,
                                           cudaStream_t stream) {
   PG_REQUIRE(scatter_src != nullptr && world >= 1 && world <= 8, "moe gemm return: needs the sorted-source table and 1..8 ranks");
-  return moe_gemm_impl(x, ldx, x_rows, w, scales, int4, nullptr, ldy, offsets, E, M, K, bn, status, scatter_src, peer_out, peer_flags, cap, rank, world,
+  return moe_gemm_impl(x, ldx, x_rows, w, scales, quant, nullptr, ldy, offsets, E, M, K, bn, status, scatter_src, peer_out, peer_flags, cap, rank, world,
                        site, stream);
 }

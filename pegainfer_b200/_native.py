@@ -116,7 +116,17 @@ def load():
     if _lib is not None:
         return _lib
     if not is_current():
-        build()
+        # several ranks of one box may get here together: one builds, the others wait on the lock
+        import fcntl
+
+        os.makedirs(LIB_DIR, exist_ok=True)
+        with open(os.path.join(LIB_DIR, ".build.lock"), "w") as lk:
+            fcntl.flock(lk, fcntl.LOCK_EX)
+            try:
+                if not is_current():
+                    build()
+            finally:
+                fcntl.flock(lk, fcntl.LOCK_UN)
     _lib = ctypes.CDLL(LIB_PATH)
     _lib.pg_last_error.restype = ctypes.c_char_p
     return _lib

@@ -153,6 +153,10 @@ PRESETS = {
     "tiny-kimi": ModelConfig(family="kimi_k2", vocab_size=1024, hidden_size=256, num_layers=3, num_q_heads=4, num_kv_heads=4, head_dim=48, intermediate_size=512, qk_norm=False, q_lora_rank=96, kv_lora_rank=64, qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32, n_routed_experts=16, n_shared_experts=1, num_experts_per_tok=4, moe_intermediate_size=128, first_k_dense_replace=1, scoring_func="sigmoid", n_group=4, topk_group=2, norm_topk_prob=True, routed_scaling_factor=2.827, router_bias=True, expert_quant="int4_g32", rope_theta=50000.0, rope_scaling=dict(_YARN_KIMI), rms_eps=1e-5, num_mtp_layers=1),
     "kimi-k2": ModelConfig(family="kimi_k2", vocab_size=163840, hidden_size=7168, num_layers=61, num_q_heads=64, num_kv_heads=64, head_dim=192, intermediate_size=18432, qk_norm=False, q_lora_rank=1536, kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, n_routed_experts=384, n_shared_experts=1, num_experts_per_tok=8, moe_intermediate_size=2048, first_k_dense_replace=1, scoring_func="sigmoid", n_group=1, topk_group=1, norm_topk_prob=True, routed_scaling_factor=2.827, router_bias=True, expert_quant="int4_g32", rope_theta=50000.0, rope_scaling=dict(_YARN_KIMI), rms_eps=1e-5, max_position=131072, num_mtp_layers=1),
 }
+# the DeepSeek-V2 shapes with block-scaled FP8 e4m3 experts (128x128 scale blocks)
+for _name in ("tiny-dsv2", "small-dsv2", "dsv2-lite"):
+    if _name in PRESETS:
+        PRESETS[_name + "-fp8"] = replace(PRESETS[_name], expert_quant="fp8_block128")
 
 
 def preset(name: str, **overrides) -> ModelConfig:

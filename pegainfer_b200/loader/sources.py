@@ -224,7 +224,21 @@ class SafetensorsSource(WeightSource):
             t = sl[:]
         if dtype is not None and t.dtype != dtype and t.dtype.is_floating_point != dtype.is_floating_point:
             raise WeightError(f"{name}: dtype {t.dtype} cannot load as {dtype}")
+        if t.dtype == torch.float8_e4m3fn and dtype not in (None, torch.float8_e4m3fn) and (name + "_scale_inv") in self.name_to_file:
+            # block-scaled FP8 checkpoint, tensor wanted in a wider type: dequantise at the load boundary
+            t = self._dequant_fp8(name, t, rows, cols)
         return staged_upload(t.contiguous(), device, dtype)
+
+    def _dequant_fp8(self, name, t, rows, cols, block: int = 128):
+        """``w = fp8 * scale_inv[row // block, col // block]`` for the requested slice."""
+        sname = name + "_scale_inv"
+        scale = self._handle(self.name_to_file[sname]).get_slice(sname)[:].float()
+        full_rows, full_cols = self.shape(name)
+        r0 = rows[0] if rows is not None else 0
+        c0 = cols[0] if cols is not None else 0
+        ridx = (torch.arange(r0, r0 + t.shape[0]) // block).clamp_(max=scale.shape[0] - 1)
+        cidx = (torch.arange(c0, c0 + t.shape[1]) // block).clamp_(max=scale.shape[1] - 1)
+        return t.float() * scale[ridx][:, cidx]
 
 
 _STAGING = {}

@@ -77,6 +77,9 @@ def mla_moe_shapes(cfg: ModelConfig) -> dict:
                     if cfg.expert_quant == "int4_g32":
                         s[ep + name + ".weight_packed"] = (shp[0], shp[1] // 8)
                         s[ep + name + ".weight_scale"] = (shp[0], shp[1] // cfg.quant_group_size)
+                    elif cfg.expert_quant == "fp8_block128":
+                        s[ep + name + ".weight"] = shp
+                        s[ep + name + ".weight_scale_inv"] = ((shp[0] + 127) // 128, (shp[1] + 127) // 128)
                     else:
                         s[ep + name + ".weight"] = shp
         else:
@@ -101,6 +104,16 @@ class _QuantRandomSource(RandomSource):
             g.manual_seed(self._seed_for(name))
             t = torch.empty(shape, dtype=torch.float32, device=device).uniform_(0.003, 0.0056, generator=g)
             return t.to(dtype or self.dtype)
+        if name.endswith("weight_scale_inv"):
+            shape = self.shapes[name]
+            g = torch.Generator(device=torch.device(device))
+            g.manual_seed(self._seed_for(name))
+            # N(0, 0.02) weights have block maxima near 4.5 sigma: scale_inv ~ 0.09 / 448
+            return torch.empty(shape, dtype=torch.float32, device=device).uniform_(1.6e-4, 2.4e-4, generator=g)
+        if dtype == torch.float8_e4m3fn:
+            # synthetic FP8 experts: N(0, 1) * 100 in e4m3 times scale_inv ~ 2e-4 gives N(0, 0.02)
+            w = super().get(name, device, torch.float32, rows, cols) * (100.0 / 0.02)
+            return w.clamp_(-448.0, 448.0).to(torch.float8_e4m3fn)
         return super().get(name, device, dtype, rows, cols)
 
 
@@ -190,6 +203,14 @@ class MlaMoeModel:
                 pk = torch.stack([torch.cat([src.get(f"{m}experts.{e}.{n}.weight_packed", dev, torch.int32) for n in names], 0) for e in range(e0, e1)])
                 sc = torch.stack([torch.cat([src.get(f"{m}experts.{e}.{n}.weight_scale", dev, dt) for n in names], 0) for e in range(e0, e1)])
                 ex[key + "_packed"], ex[key + "_scale"] = pk, sc
+        elif cfg.expert_quant == "fp8_block128":
+            if cfg.moe_intermediate_size % 128 or cfg.hidden_size % 128:
+                raise ValueError("block-scaled FP8 experts need hidden and expert intermediate sizes that are multiples of 128")
+            f8 = torch.float8_e4m3fn
+            for key, names in (("w13", ("gate_proj", "up_proj")), ("w2", ("down_proj",))):
+                w8 = torch.stack([torch.cat([src.get(f"{m}experts.{e}.{n}.weight", dev, f8) for n in names], 0) for e in range(e0, e1)])
+                sc = torch.stack([torch.cat([src.get(f"{m}experts.{e}.{n}.weight_scale_inv", dev, torch.float32) for n in names], 0) for e in range(e0, e1)])
+                ex[key + "_fp8"], ex[key + "_scale"] = w8, sc.contiguous()
         else:
             ex["w13"] = torch.stack([torch.cat([src.get(f"{m}experts.{e}.gate_proj.weight", dev, dt), src.get(f"{m}experts.{e}.up_proj.weight", dev, dt)], 0) for e in range(e0, e1)])
             ex["w2"] = torch.stack([src.get(f"{m}experts.{e}.down_proj.weight", dev, dt) for e in range(e0, e1)])

@@ -132,8 +132,11 @@ class Qwen3Model:
         aux = []
         n = len(self.layers)
         for i, l in enumerate(self.layers):
-            qkv = tp.col_linear(x, l.qkv)
             ls = meta.lora_slots if self.lora is not None else None
+            decode = ls is None and meta.num_tokens <= 256  # weight-streaming regime: chain L2 prefetches GEMM to GEMM
+            if decode:
+                ops.prefetch_weights(l.o)
+            qkv = tp.col_linear(x, l.qkv)
             if ls is not None:
                 qs, ks = self.q_heads * cfg.head_dim, self.kv_heads * cfg.head_dim
                 self.lora.apply(i, "q_proj", x, qkv[:, :qs], ls)
@@ -143,8 +146,14 @@ class Qwen3Model:
             a = ops.paged_attention(q, kv.layer(i), meta)
             next_norm = self.layers[i + 1].input_norm if i + 1 < n else self.final_norm
             if ls is None:
+                if decode:
+                    ops.prefetch_weights(l.gate_up)
                 x = tp.row_linear_add_norm(a, l.o, residual, l.post_norm, eps)
+                if decode:
+                    ops.prefetch_weights(l.down)
                 act = ops.swiglu(tp.col_linear(x, l.gate_up))
+                if decode:
+                    ops.prefetch_weights(self.layers[i + 1].qkv if i + 1 < n else self.lm_head)
                 x = tp.row_linear_add_norm(act, l.down, residual, next_norm, eps)
             else:  # adapter deltas join the partial sums before the all-reduce
                 y = ops.linear(a, l.o)

@@ -8,6 +8,7 @@ once with a fixed size so its addresses stay valid inside captured CUDA graphs.
 from __future__ import annotations
 
 import ctypes
+import os
 import math
 from typing import Optional
 
@@ -202,6 +203,18 @@ def linear(x, w, out_dtype=None, force_splits: int = 0, out: Optional[torch.Tens
     if out_dtype is not None and res.dtype != out_dtype:
         res = res.to(out_dtype)
     return res
+
+
+_PREFETCH_CAP = int(float(os.environ.get("PEGAINFER_GEMM_PREFETCH_MB", "8")) * (1 << 20))
+
+
+def prefetch_weights(w: torch.Tensor) -> None:
+    """Hint for the next ``linear`` launched from this thread: while it runs, its idle
+    producer lanes pull the leading part of ``w`` (the weights of the GEMM that follows)
+    into L2, so the launch gap and the small kernel in between find HBM busy."""
+    if _PREFETCH_CAP <= 0 or not w.is_cuda:
+        return
+    lib().pg_gemm_prefetch_next(_ptr(w), _ll(min(w.numel() * w.element_size(), _PREFETCH_CAP) & ~15))
 
 
 def gemm_plan(t: int, m: int, k: int, force_splits: int = 0) -> dict:
@@ -404,14 +417,27 @@ def moe_route_plan(ids, e0: int, e_local: int):
     return offsets, sorted_src, route_pos
 
 
+def quant_code(w) -> int:
+    """Weight storage mode of the grouped GEMM: 0 bf16, 1 packed INT4 group-32, 2 block-scaled FP8 e4m3."""
+    if w.dtype == torch.int32:
+        return 1
+    if w.dtype in (torch.float8_e4m3fn, torch.uint8):
+        return 2
+    return 0
+
+
 def grouped_gemm(xs, offsets, w, scales=None, bn: int = 16):
-    """``xs`` [rows, K] sorted by expert; ``w`` bf16 [E, M, K] or packed int32 [E, M, K/8] + scales."""
+    """``xs`` [rows, K] sorted by expert; ``w`` bf16 [E, M, K], packed int32 [E, M, K/8] with bf16
+    scales [E, M, K/32], or FP8 e4m3 [E, M, K] with f32 ``scale_inv`` [E, ceil(M/128), ceil(K/128)]."""
     rows, k = xs.shape
     e, m = w.shape[0], w.shape[1]
-    int4 = scales is not None
+    mode = quant_code(w)
+    assert (mode == 0) == (scales is None), "quantised expert weights need their scales"
+    if mode == 2:
+        assert scales.dtype == torch.float32 and scales.shape == (e, (m + 127) // 128, (k + 127) // 128), "FP8 experts need f32 scale_inv per 128x128 block"
     y = torch.empty((rows, m), dtype=torch.bfloat16, device=xs.device)
     c = ctx(xs.device)
-    rc = lib().pg_moe_grouped_gemm(_ptr(xs), _ll(xs.stride(0)), _ll(rows), _ptr(w), _ptr(scales), _ci(int(int4)), _ptr(y), _ll(y.stride(0)), _ptr(offsets), _ci(e), _ci(m),
+    rc = lib().pg_moe_grouped_gemm(_ptr(xs), _ll(xs.stride(0)), _ll(rows), _ptr(w), _ptr(scales), _ci(mode), _ptr(y), _ll(y.stride(0)), _ptr(offsets), _ci(e), _ci(m),
                                    _ci(k), _ci(bn), _ptr(c.status), _stream())
     _check(rc, c)
     return y
@@ -443,6 +469,11 @@ def moe_experts(x, ids, weights, w13, w2, expert_offset=0):
 def moe_experts_int4(x, ids, weights, w13_packed, w13_scale, w2_packed, w2_scale, expert_offset=0, group=32):
     assert group == 32, "the int4 grouped GEMM is built for group size 32"
     return _moe_pipeline(x, ids, weights, w13_packed, w13_scale, w2_packed, w2_scale, expert_offset)
+
+
+def moe_experts_fp8(x, ids, weights, w13_fp8, w13_scale, w2_fp8, w2_scale, expert_offset=0, block=128):
+    assert block == 128, "the FP8 grouped GEMM is built for 128x128 scale blocks"
+    return _moe_pipeline(x, ids, weights, w13_fp8, w13_scale, w2_fp8, w2_scale, expert_offset)
 
 
 # ----------------------------------------------------------------------------------

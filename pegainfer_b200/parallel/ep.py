@@ -22,6 +22,8 @@ from .. import ops
 
 
 def _local_experts(x, ids, wts, experts, cfg):
+    if "w13_fp8" in experts:
+        return ops.moe_experts_fp8(x, ids, wts, experts["w13_fp8"], experts["w13_scale"], experts["w2_fp8"], experts["w2_scale"], experts["offset"])
     if "w13_packed" in experts:
         return ops.moe_experts_int4(x, ids, wts, experts["w13_packed"], experts["w13_scale"], experts["w2_packed"], experts["w2_scale"], experts["offset"], cfg.quant_group_size)
     return ops.moe_experts(x, ids, wts, experts["w13"], experts["w2"], experts["offset"])

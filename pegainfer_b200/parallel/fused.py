@@ -1,11 +1,13 @@
 """Tensor parallelism with the collective fused into the GEMM kernels.
 
 A row-parallel projection (o_proj, down_proj) runs as ONE kernel launch per rank:
-tcgen05 GEMM tiles write f32 partials into this rank's symmetric buffer; once every
-rank's tiles are stored (epoch flags over NVLink), each rank reduces the token rows it
-owns from all peers in fixed rank order (reduce-scatter), adds the residual, applies
-RMSNorm and stores the normalised rows into every rank's activation buffer
-(all-gather).  The following column-parallel GEMM (qkv, gate_up) streams its first
+the epilogue of every tcgen05 GEMM tile pushes its f32 partial straight into the receive
+buffer of the rank that owns those token rows (posted NVLink stores, so the transfer of
+a tile overlaps the MMAs of the tiles still being computed); once every rank has
+signalled its tiles (epoch flags), each rank sums the partials of its rows from local
+memory in fixed rank order (reduce-scatter), adds the residual, applies RMSNorm and
+stores the normalised rows into every rank's activation buffer (all-gather).  With few
+rows (decode) every rank receives all partials and reduces all rows itself: one hop.  The following column-parallel GEMM (qkv, gate_up) streams its first
 weight tiles while those rows travel and only then waits on the delivery flags, so the
 gather overlaps the GEMM's ramp-up.  Flags are monotonic epochs kept in device memory,
 so captured CUDA graphs replay without any reset.
@@ -39,7 +41,11 @@ class FusedTP(TPContext):
         self.max_tokens = max_tokens
         self.wait_ns = int(wait_s * 1e9)
         self.lib = _native.load()
-        part_b = 2 * max_tokens * hidden * 4  # double buffered: a fast rank may already write the next site's partials
+        self.one_shot_rows = 256  # one-shot all-reduce while tokens * world stays below this
+        # receive buffer [source rank][rows][hidden] f32, double buffered by site parity: a fast
+        # rank may already push the next site's tiles while this rank still reduces the current one
+        self._part_elems = max(self.one_shot_rows, max_tokens + world) * hidden
+        part_b = 2 * self._part_elems * 4
         x_b = max_tokens * hidden * 2
         flag_b = MAX_SITES * FLAG_WORDS_PER_SITE * 4
         self._off_x = (part_b + 255) // 256 * 256
@@ -52,7 +58,6 @@ class FusedTP(TPContext):
         self.flags = self.buf.view(torch.int32, (MAX_SITES, FLAG_WORDS_PER_SITE), self._off_f)
         self._site = 0
         self._pending_site = -1
-        self.one_shot_rows = 256  # one-shot all-reduce while tokens * world stays below this
         self.fused = self
         if world > 1:
             dist.barrier(group=group)
@@ -78,7 +83,7 @@ class FusedTP(TPContext):
         if self._site >= MAX_SITES:
             raise RuntimeError("too many fused collective sites in one step")
         one_shot = t * self.world <= self.one_shot_rows
-        part_offset = (site & 1) * self.max_tokens * self.hidden
+        part_offset = (site & 1) * self._part_elems
         c = K.ctx(a.device)
         rc = self.lib.pg_tp_gemm_rs_norm_ag(
             _vp(a.data_ptr()), _vp(w.data_ptr()), _ci(t), _ci(self.hidden), _ci(k), _ll(a.stride(0)), _ll(w.stride(0)), self.part_table, self.x_table,

@@ -81,9 +81,9 @@ class FusedEP(EPContext):
         self._site += 1
         if site >= MAX_SITES:
             raise RuntimeError("too many MoE layers for the EP flag table")
-        int4 = "w13_packed" in experts
-        w13 = experts["w13_packed"] if int4 else experts["w13"]
-        w2 = experts["w2_packed"] if int4 else experts["w2"]
+        key = "_packed" if "w13_packed" in experts else "_fp8" if "w13_fp8" in experts else ""
+        w13, w2 = experts["w13" + key], experts["w2" + key]
+        mode = K.quant_code(w13)
         s13 = experts.get("w13_scale")
         s2 = experts.get("w2_scale")
         e_local = w13.shape[0]
@@ -112,7 +112,7 @@ class FusedEP(EPContext):
         m = w2.shape[1]
         kk = act.shape[1]
         rc = self.lib.pg_moe_grouped_gemm_return(_vp(act.data_ptr()), _ll(act.stride(0)), _ll(max_rows), _vp(w2.data_ptr()), _vp(s2.data_ptr()) if s2 is not None else _vp(0),
-                                                 _ci(int(int4)), _ll(h), _vp(offsets.data_ptr()), _ci(e_local), _ci(m), _ci(kk), _ci(bn), _vp(c.status.data_ptr()),
+                                                 _ci(mode), _ll(h), _vp(offsets.data_ptr()), _ci(e_local), _ci(m), _ci(kk), _ci(bn), _vp(c.status.data_ptr()),
                                                  _vp(sorted_src.data_ptr()), self.comb_table, self.flag_table, _ci(self.cap), _ci(self.rank), _ci(self.world), _ci(site), st)
         K._check(rc, c)
         out = torch.empty((t, h), dtype=torch.float32, device=dev)

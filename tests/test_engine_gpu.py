@@ -70,7 +70,11 @@ def test_graph_decode_equals_eager_and_bucket_padding():
 
 
 def test_sampling_params_and_logprobs_on_gpu():
-    eng = engine(True)
+    # Without the prefix cache both runs execute the same kernels on the same shapes, so a
+    # seeded replay must be exact (a cache hit changes the prefill token tile and with it
+    # the k-split order: last-bit logit differences that top-k over near-flat random-init
+    # logits amplifies; pinning that is what --batch-invariant is for).
+    eng = engine(True, no_prefix_cache=True)
     try:
         p = prompts(2, seed=5)
         a = eng.generate(p, SamplingParams(temperature=0.8, top_k=20, top_p=0.9, seed=7), max_tokens=8)
@@ -130,6 +134,10 @@ def test_dsv2_shape_kernels_vs_library():
 
 def test_kimi_shape_int4_kernels_vs_library():
     _family_logits_close("small-kimi")
+
+
+def test_dsv2_shape_fp8_block_scaled_experts_kernels_vs_library():
+    _family_logits_close("small-dsv2-fp8")
 
 
 def test_qwen35_hybrid_kernels_vs_library():

@@ -346,6 +346,35 @@ def test_moe_pipeline_matches_per_expert_reference(t, h, inter, e, k, int4):
     assert torch.equal(got, cu().moe_experts_int4(x, ids, w, p13, s13, p2, s2, off) if int4 else cu().moe_experts(x, ids, w, w13, w2, off))
 
 
+@pytest.mark.parametrize("t,h,inter,e,k", [(3, 512, 256, 8, 3), (130, 1024, 512, 12, 4), (64, 2048, 1408, 16, 6)])
+def test_moe_pipeline_fp8_block_scaled_experts(t, h, inter, e, k):
+    """FP8 e4m3 experts with 128x128 scale blocks, dequantised inside the grouped GEMM."""
+    torch.manual_seed(t + h + 1)
+    x = (torch.randn(t, h, device=DEV) * 0.5).bfloat16()
+    ids, w = R.router_topk(torch.randn(t, e + 4, device=DEV), k, "softmax")
+    off = 2
+    q13, s13 = zip(*[R.quant_fp8_block(torch.randn(2 * inter, h, device=DEV) * 0.03) for _ in range(e)])
+    q2, s2 = zip(*[R.quant_fp8_block(torch.randn(h, inter, device=DEV) * 0.03) for _ in range(e)])
+    q13, s13, q2, s2 = torch.stack(q13), torch.stack(s13).contiguous(), torch.stack(q2), torch.stack(s2).contiguous()
+    got = cu().moe_experts_fp8(x, ids, w, q13, s13, q2, s2, off)
+    ref = R.moe_experts_fp8(x, ids, w, q13, s13, q2, s2, off)
+    torch.cuda.synchronize()
+    status_clean()
+    err = (got - ref).abs()
+    assert err.max().item() < 2e-2 * max(1.0, ref.abs().max().item()), (err.max().item(), ref.abs().max().item())
+    assert torch.equal(got, cu().moe_experts_fp8(x, ids, w, q13, s13, q2, s2, off))
+    # one-hot rows read single weights back: the in-kernel dequantisation is exact
+    m, kk = 256, 256
+    q, sc = R.quant_fp8_block(torch.randn(m, kk, device=DEV) * 0.05)
+    xs = torch.zeros(32, kk, device=DEV).bfloat16()
+    for r in range(32):
+        xs[r, (r * 37) % kk] = 1.0
+    y = cu().grouped_gemm(xs, torch.tensor([0, 32], dtype=torch.int32, device=DEV), q[None], sc[None].contiguous(), 32)
+    wd = R.dequant_fp8_block(q, sc)
+    assert torch.equal(y.float(), (xs.float() @ wd.float().t()).bfloat16().float())
+    status_clean()
+
+
 def test_int4_dequant_inside_grouped_gemm_is_exact_on_one_hot_inputs():
     torch.manual_seed(0)
     e, m, k = 3, 256, 128

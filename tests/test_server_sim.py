@@ -186,3 +186,22 @@ def test_fatal_step_fails_requests_instead_of_hanging():
         assert c.get("/health").status_code == 503
     finally:
         eng.shutdown()
+
+
+def test_serving_bench_harness_against_sim_engine(tmp_path):
+    """The HTTP load generator reports every request and sane latency percentiles."""
+    import json
+    import os
+    import sys
+
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import bench_serving
+
+    assert bench_serving.percentiles([1.0, 2.0, 3.0, 4.0])["p50"] in (2.0, 3.0)
+    out = tmp_path / "r.json"
+    rc = bench_serving.main(["--spawn", "sim", "--num-prompts", "12", "--input-len", "24", "--output-len", "6", "--concurrency", "3", "--warmup", "1", "--json", str(out)])
+    assert rc == 0
+    r = json.loads(out.read_text())
+    assert r["completed"] == 12 and r["failed"] == 0
+    assert r["output_tokens"] == 12 * 6 and r["input_tokens"] == 12 * 24
+    assert r["ttft_ms"]["p50"] > 0 and r["e2el_ms"]["p99"] >= r["ttft_ms"]["p50"]
