@@ -58,6 +58,9 @@ class EPContext:
         dist.all_gather_into_tensor(idg, ids.contiguous(), group=self.group)
         dist.all_gather_into_tensor(wg, wts.contiguous(), group=self.group)
         y = _local_experts(xs, idg, wg, experts, cfg).float()
+        if dist.get_backend(self.group) == "gloo":  # no reduce-scatter on gloo (CPU runs): all-reduce, keep this rank's rows
+            dist.all_reduce(y, group=self.group)
+            return y[self.rank * t : (self.rank + 1) * t].contiguous()
         out = torch.empty((t, x.shape[1]), dtype=torch.float32, device=x.device)
         dist.reduce_scatter_tensor(out, y, group=self.group)
         return out

@@ -43,8 +43,10 @@ def drive_replicated(scheduler, handle: SchedulerHandle, stop: threading.Event, 
     import torch.distributed as dist
 
     collected: list = []
-    ledger = RequestLedger(sink=(handle.dispatch if (rank == 0 and mode == "tp") else collected.append))
-    local: dict = {}  # rid -> QueuedRequest on this rank
+    direct = rank == 0 and mode == "tp"
+    ledger = RequestLedger(sink=handle.dispatch if direct else collected.append)
+    mine: dict = {}  # rid -> QueuedRequest registered with this rank's scheduler
+    tracked: dict = {}  # rank 0 only: rid -> QueuedRequest of every open request (abort flags, failure reporting)
     known_aborts: set = set()
     try:
         while True:
@@ -56,10 +58,9 @@ def drive_replicated(scheduler, handle: SchedulerHandle, stop: threading.Event, 
                         q = handle._submit_q.get_nowait()
                     except queue.Empty:
                         break
-                    target = None if mode == "tp" else partition_of(q)
-                    local[q.id] = q
-                    new.append((q.id, q.request, q.queued_at, target))
-                aborts = [rid for rid, q in local.items() if q.is_aborted() and rid not in known_aborts]
+                    tracked[q.id] = q
+                    new.append((q.id, q.request, q.queued_at, None if mode == "tp" else partition_of(q)))
+                aborts = [rid for rid, q in tracked.items() if q.is_aborted() and rid not in known_aborts]
                 payload = (new, aborts, stop.is_set())
             box = [payload]
             dist.broadcast_object_list(box, src=0, group=group)
@@ -69,45 +70,56 @@ def drive_replicated(scheduler, handle: SchedulerHandle, stop: threading.Event, 
             for rid, req, queued_at, target in new:
                 if target is not None and target != rank:
                     continue
-                q = local.get(rid) if rank == 0 else None
+                q = tracked.get(rid) if rank == 0 else None
                 if q is None:
                     q = QueuedRequest(id=rid, request=req, queued_at=queued_at)
-                    local[rid] = q
+                mine[rid] = q
                 ledger.register(q)
                 scheduler.submit(q)
             for rid in aborts:
                 known_aborts.add(rid)
-                if rid in local:
-                    local[rid].abort_flag.set()
+                if rid in mine:
+                    mine[rid].abort_flag.set()
             busy = scheduler.step(ledger)
             if rank == 0:
                 handle.metrics_cell.publish(scheduler.metrics())
             ledger.commit_step()
-            for rid in [r for r in local if not ledger.is_open(r)]:
-                local.pop(rid, None)
+            for rid in [r for r in mine if not ledger.is_open(r)]:
+                mine.pop(rid, None)
+                if direct:
+                    tracked.pop(rid, None)
+                    known_aborts.discard(rid)
             if mode == "dp":
                 # every rank's updates of this step go back to the frontend on rank 0
                 gathered = [None] * world if rank == 0 else None
                 dist.gather_object(collected[:], gathered, dst=0, group=group)
-                collected.clear()
                 if rank == 0:
                     for outs in gathered:
                         for so in outs or []:
+                            for upd in so.updates:
+                                if upd.terminal is not None:
+                                    tracked.pop(upd.id, None)
+                                    known_aborts.discard(upd.id)
                             handle.dispatch(so)
-            else:
-                collected.clear()
+            collected.clear()
             if not busy and not new:
                 time.sleep(0.001)
     except Exception as exc:  # a lost rank or a fatal step: fail-stop for every open request
         log.error("control loop ended: %r", exc)
         if rank == 0:
-            upd = [RequestUpdate(id=rid, terminal=Terminal.failed(f"engine failure: {exc!r}")) for rid in list(local)]
+            upd = [RequestUpdate(id=rid, terminal=Terminal.failed(f"engine failure: {exc!r}")) for rid in list(tracked)]
             if upd:
                 handle.dispatch(StepOutputs(updates=upd))
-        handle.alive = False
         raise
     finally:
         handle.alive = False
+        if rank == 0:  # nothing submitted after the loop stopped may hang
+            while True:
+                try:
+                    q = handle._submit_q.get_nowait()
+                except queue.Empty:
+                    break
+                handle.dispatch(StepOutputs(updates=[RequestUpdate(id=q.id, terminal=Terminal.failed("engine shut down"))]))
 
 
 class ReplicatedEngine(Engine):
@@ -133,12 +145,39 @@ class ReplicatedEngine(Engine):
             self._errors.append(exc)
 
 
+def build_replicated_engine(ecfg, mcfg, rank: int, world: int, device, dtype, control, tp=None, ep=None) -> ReplicatedEngine:
+    """This rank's engine for a multi-process deployment.  ``tp`` (dense model lines) or
+    ``ep`` (MLA + MoE lines: data-parallel attention, experts spread over the ranks) is the
+    rank's communication context; ``control`` is the host-side (gloo) group that carries
+    the event broadcast, the lock-step agreement and the result gather."""
+    from ..engine.build import build_engine
+    from .tp import TPContext
+
+    moe = mcfg.family in ("deepseek_v2", "kimi_k2")
+    eng = build_engine(ecfg, mcfg, device=device, dtype=dtype, tp=tp or TPContext(), ep=ep, start=False)
+    sched = eng.scheduler
+    partition_of = None
+    if moe:
+        from .dp import DpScheduler, LockstepExecutor
+
+        sched.__class__ = DpScheduler
+        sched.ex = LockstepExecutor(eng.executor, control, world)
+        rr = [-1]
+
+        def partition_of(q):  # rank 0 decides; round-robin is load-balanced for equal-cost requests
+            rr[0] = (rr[0] + 1) % world
+            return rr[0]
+
+    rep = ReplicatedEngine(sched, eng.info, control, rank, world, "dp" if moe else "tp", partition_of)
+    rep.model, rep.executor, rep.scheduler, rep.pool, rep.kv = eng.model, eng.executor, sched, eng.pool, eng.kv
+    return rep
+
+
 def launch_distributed(ecfg, mcfg, ns) -> int:
     """Entry point under torchrun: build this rank's shard, then serve (rank 0) or follow."""
     import torch
     import torch.distributed as dist
 
-    from ..engine.build import build_engine
     from ..server.openai import serve
     from ..server.tokenizer import load_tokenizer
     from .tp import TPContext
@@ -150,9 +189,8 @@ def launch_distributed(ecfg, mcfg, ns) -> int:
     dist.init_process_group("nccl", device_id=device)
     control = dist.new_group(backend="gloo", timeout=timedelta(seconds=float(os.environ.get("PEGAINFER_CONTROL_TIMEOUT_S", "60"))))
     moe = mcfg.family in ("deepseek_v2", "kimi_k2")
-    tp, ep, mode = TPContext(), None, "tp"
+    tp, ep = None, None
     if moe:
-        mode = "dp"
         if ecfg.comm == "fused":
             from .fused_ep import make_fused_ep
 
@@ -167,23 +205,7 @@ def launch_distributed(ecfg, mcfg, ns) -> int:
         tp = make_fused_tp(rank, world, device, mcfg, max_tokens=ecfg.max_prefill_tokens + ecfg.max_decode_batch)
     else:
         tp = TPContext(rank, world, comm="nccl")
-    eng = build_engine(ecfg, mcfg, device=device, dtype=torch.bfloat16, tp=tp, ep=ep, start=False)
-    sched = eng.scheduler
-    partition_of = None
-    if moe:
-        from .dp import DpScheduler, LockstepExecutor
-
-        lock = LockstepExecutor(eng.executor, control, world)
-        sched.__class__ = DpScheduler
-        sched.ex = lock
-        rr = [0]
-
-        def partition_of(q):  # round-robin is load-balanced for equal-cost requests; rank 0 decides
-            rr[0] = (rr[0] + 1) % world
-            return rr[0]
-
-    rep = ReplicatedEngine(sched, eng.info, control, rank, world, mode, partition_of)
-    rep.model, rep.executor, rep.scheduler, rep.pool, rep.kv = eng.model, eng.executor, sched, eng.pool, eng.kv
+    rep = build_replicated_engine(ecfg, mcfg, rank, world, device, torch.bfloat16, control, tp=tp, ep=ep)
     dist.barrier()
     rep.start()
     if rank == 0:

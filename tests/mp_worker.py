@@ -1,0 +1,71 @@
+"""Worker for the multi-process CPU tests (gloo): ``python -m torch.distributed.run ... tests/mp_worker.py MODE OUT``.
+
+Modes
+  tp        tiny Qwen3 with tensor parallelism over the ranks (replicated schedulers,
+            rank 0 owns the requests); rank 0 writes the generated tokens
+  dp_ep     tiny DeepSeek-V2 shape: data-parallel attention, experts spread over the ranks,
+            lock-step executor; rank 0 routes requests and collects every rank's updates
+  rank_loss like tp, but the last rank leaves between steps (no collective in flight): the
+            others must fail their open requests on the host instead of hanging
+"""
+import json
+import os
+import sys
+import threading
+import time
+from datetime import timedelta
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch
+import torch.distributed as dist
+
+from pegainfer_b200.config import EngineConfig, preset
+from pegainfer_b200.engine.contract import Request, SamplingParams
+from pegainfer_b200.parallel.ep import EPContext
+from pegainfer_b200.parallel.launch import build_replicated_engine
+from pegainfer_b200.parallel.tp import TPContext
+
+
+def main():
+    mode, out_path = sys.argv[1], sys.argv[2]
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dist.init_process_group("gloo", timeout=timedelta(seconds=8 if mode == "rank_loss" else 120))
+    control = dist.group.WORLD
+    g = torch.Generator().manual_seed(11)
+    prompts = [torch.randint(0, 1024, (18 + 5 * i,), generator=g).tolist() for i in range(4)]
+    if mode == "dp_ep":
+        name, tp, ep = "tiny-dsv2", None, EPContext(rank, world, group=control, comm="nccl", tokens="dp")
+    else:
+        name, tp, ep = "tiny-qwen3", TPContext(rank, world, group=control, comm="nccl"), None
+    ecfg = EngineConfig(preset=name, kv_page_size=16, num_kv_blocks=128, cuda_graph=False, max_prefill_tokens=32)
+    eng = build_replicated_engine(ecfg, preset(name), rank, world, "cpu", torch.float32, control, tp=tp, ep=ep)
+    result = {"rank": rank}
+    if rank == 0:
+        n_tok = 400 if mode == "rank_loss" else 6
+        streams = [eng.submit(Request(prompt_tokens=p, params=SamplingParams(temperature=0.0, ignore_eos=True), max_tokens=n_tok)) for p in prompts]
+    if mode == "rank_loss" and rank == world - 1:
+        # leave between steps: stop the local loop after a few iterations, then exit without telling anyone
+        eng.start()
+        time.sleep(0.4)
+        os._exit(0)
+    eng.start()
+    if rank == 0:
+        outs = [s.collect(60) for s in streams]
+        result["tokens"] = [o[0] for o in outs]
+        result["terminals"] = [o[1].kind if hasattr(o[1], "kind") else str(o[1]) for o in outs]
+        result["messages"] = [getattr(o[1], "message", "") for o in outs]
+        if mode != "rank_loss":
+            eng.shutdown()
+        with open(out_path, "w") as f:
+            json.dump(result, f)
+    else:
+        deadline = time.monotonic() + 90
+        while eng.healthy() and time.monotonic() < deadline:
+            time.sleep(0.05)
+    sys.stdout.flush()
+    os._exit(0)  # a peer may be gone: skip the process-group teardown
+
+
+if __name__ == "__main__":
+    main()

@@ -36,9 +36,9 @@ def main():
 
     kvs = {k: kv_for(m) for k, m in models.items()}
     g = torch.Generator().manual_seed(5)
-    lens = [70, 33, 5]
+    lens = [170, 33, 5]  # 208 rows: two-shot (reduce-scatter + all-gather) on 2..8 ranks; the decode steps below are one-shot
     prompts = [torch.randint(0, 4096, (n,), generator=g).tolist() for n in lens]
-    pages = [[1, 2, 3, 4, 5], [6, 7, 8], [9]]
+    pages = [list(range(1, 12)), [12, 13, 14], [15]]
 
     def run(name, seqs):
         tok, meta = build_meta(seqs, page, dev)
@@ -62,6 +62,9 @@ def main():
 
     prefill = [SeqStep(rid=i, input_tokens=p, start_pos=0, view=KvView(pages[i], len(p), page)) for i, p in enumerate(prompts)]
     check("prefill", prefill)
+    # a chunk above the fused row limit takes the library all-reduce; results must agree as well
+    big = [SeqStep(rid=9, input_tokens=torch.randint(0, 4096, (300,), generator=g).tolist(), start_pos=0, view=KvView(list(range(20, 39)), 300, page))]
+    check("prefill300", big)
     decode = [SeqStep(rid=i, input_tokens=[7 + i], start_pos=lens[i], view=KvView(pages[i], lens[i] + 1, page)) for i in range(3)]
     check("decode3", decode)
     check("decode1", decode[:1])  # fewer rows than ranks: some ranks own nothing
