@@ -23,6 +23,8 @@ int pg_gemm_plan(int T, int M, int K, int force_splits, int* out);
 // One-shot hint: the next GEMM launched from the calling thread also pulls `bytes` at `ptr`
 // (the weights of the GEMM after it) into L2 with its idle producer lanes.
 void pg_gemm_prefetch_next(const void* ptr, long long bytes);
+// Profiling hook: device buffer of 16 x uint64 per CTA filled with globaltimer phase stamps by every following GEMM (nullptr = off).
+void pg_gemm_set_timing(void* buf);
 int pg_gemm_bf16_tn(const void* x, const void* w, void* y, int y_is_f32, int T, int M, int K, long long ldx, long long ldw, long long ldy,
                     void* ws, long long ws_bytes, void* counters, long long counter_bytes, void* status, int force_splits,
                     cudaStream_t stream);

@@ -27,6 +27,7 @@
 // deepep_shim_impl.cuh:148-470) and of ncclAllToAll-style baselines.
 #include "api.h"
 #include "common.cuh"
+#include "route_sort.cuh"
 
 namespace {
 
@@ -96,41 +97,22 @@ __global__ void __launch_bounds__(128) ep_dispatch_kernel(const bf16* __restrict
 
 // One CTA: wait for all sources, then the same stable counting sort as moe_align over the
 // live part of the receive table (`live` routes per source; entries beyond that are left
-// over from larger steps and must not be read).
-__global__ void __launch_bounds__(512) ep_align_kernel(const int* __restrict__ recv_ids, int world, int cap, int live, int e_local,
-                                                        int* __restrict__ offsets, int* __restrict__ sorted_src, const uint32_t* __restrict__ flags,
-                                                        unsigned long long wait_ns, uint32_t* status) {
-  __shared__ int cnt[512];
-  __shared__ int start[513];
+// over from larger steps and must not be read).  The table is written by peers, so it is
+// read past L1 (ld.cg) while being staged into shared memory.
+__global__ void __launch_bounds__(ROUTE_SORT_THREADS) ep_align_kernel(const int* __restrict__ recv_ids, int world, int cap, int live, int e_local,
+                                                                       int* __restrict__ offsets, int* __restrict__ sorted_src,
+                                                                       const uint32_t* __restrict__ flags, unsigned long long wait_ns, uint32_t* status) {
+  __shared__ RouteSortSmem sm;
   if (threadIdx.x == 0) {
     const uint32_t target = *((volatile const uint32_t*)(flags + 16)) + 1u;
     wait_epochs(flags, world, target, wait_ns, status, 8u);
   }
   __syncthreads();
-  const int e = threadIdx.x;
-  int c = 0;
-  if (e < e_local) {
-    for (int q = 0; q < world; ++q)
-      for (int i = 0; i < live; ++i) c += (__ldcg(recv_ids + q * cap + i) == e);
-  }
-  cnt[e] = e < e_local ? c : 0;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int acc = 0;
-    for (int i = 0; i < e_local; ++i) {
-      start[i] = acc;
-      acc += cnt[i];
-    }
-    start[e_local] = acc;
-  }
-  __syncthreads();
-  for (int i = threadIdx.x; i <= e_local; i += blockDim.x) offsets[i] = start[i];
-  if (e < e_local) {
-    int pos = start[e];
-    for (int q = 0; q < world; ++q)
-      for (int i = 0; i < live; ++i)
-        if (__ldcg(recv_ids + q * cap + i) == e) sorted_src[pos++] = q * cap + i;
-  }
+  route_sort(
+      sm, world * live, e_local, offsets, [&](int i) { return __ldcg(recv_ids + (i / live) * cap + (i % live)); },
+      [&](int i, int pos) {
+        if (pos >= 0) sorted_src[pos] = (i / live) * cap + (i % live);
+      });
 }
 
 // out[t] = sum_j w[t, j] * comb[t*k + j]; grid = tokens.  The last CTA advances the epoch.
@@ -206,7 +188,7 @@ extern "C" int pg_ep_dispatch(const void* x, long long ldx, const void* ids, int
 extern "C" int pg_ep_align(const void* recv_ids, int world, int cap, int live, int e_local, void* offsets, void* sorted_src, const void* site_flags,
                            unsigned long long wait_ns, void* status, cudaStream_t stream) {
   PG_REQUIRE(e_local >= 1 && e_local <= 512 && live <= cap, "ep_align: bad geometry (%d local experts, live %d, cap %d)", e_local, live, cap);
-  ep_align_kernel<<<1, 512, 0, stream>>>((const int*)recv_ids, world, cap, live, e_local, (int*)offsets, (int*)sorted_src, (const uint32_t*)site_flags,
+  ep_align_kernel<<<1, ROUTE_SORT_THREADS, 0, stream>>>((const int*)recv_ids, world, cap, live, e_local, (int*)offsets, (int*)sorted_src, (const uint32_t*)site_flags,
                                          wait_ns, (uint32_t*)status);
   PG_LAUNCH_CHECK();
   return PG_OK;

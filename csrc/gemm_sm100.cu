@@ -83,6 +83,7 @@ struct GemmParams {
   float* ws;
   uint32_t* counters;
   uint32_t* status;
+  unsigned long long* timing;  // optional profiling: 16 globaltimer stamps per CTA (nullptr = off)
   const uint8_t* pf_ptr;  // weights of the next GEMM in the stream: pulled into L2 while this kernel runs
   long long pf_bytes;
 };
@@ -168,6 +169,98 @@ __device__ __forceinline__ float tp_sum_rows(const float* src_row, size_t src_st
   return ss;
 }
 
+// Four consecutive output features m..m+3 of token row n (the vector form of store_out).
+__device__ __forceinline__ void store_out4(const GemmParams& p, int n, int m, float4 v) {
+  const bool vec = (p.M & 3) == 0 && m + 3 < p.M;
+  if (!vec) {
+    const float f[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (m + i < p.M) store_out(p, n, m + i, f[i]);
+    return;
+  }
+  if (p.tp.enabled) {
+    const TpFuse& tp = p.tp;
+    if (tp.one_shot) {
+      const size_t off = (size_t)tp.part_offset + ((size_t)tp.rank * p.T + n) * p.M + m;
+#pragma unroll
+      for (int q = 0; q < MAX_RANKS; ++q)
+        if (q < tp.world) *reinterpret_cast<float4*>(tp.part[q] + off) = v;
+    } else {
+      const int rows_per = (p.T + tp.world - 1) / tp.world;
+      const int q = n / rows_per;
+      *reinterpret_cast<float4*>(tp.part[q] + (size_t)tp.part_offset + ((size_t)tp.rank * rows_per + (n - q * rows_per)) * p.M + m) = v;
+    }
+  } else if (p.y_f32) {
+    if ((p.ldy & 3) == 0)
+      *reinterpret_cast<float4*>(p.y_f32 + (size_t)n * p.ldy + m) = v;
+    else {
+      float* o = p.y_f32 + (size_t)n * p.ldy + m;
+      o[0] = v.x, o[1] = v.y, o[2] = v.z, o[3] = v.w;
+    }
+  } else {
+    const bf162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    bf16* o = p.y + (size_t)n * p.ldy + m;
+    if ((p.ldy & 3) == 0) {
+      uint2 pk;
+      pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+      pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(o) = pk;
+    } else {
+      o[0] = lo.x, o[1] = lo.y, o[2] = hi.x, o[3] = hi.y;
+    }
+  }
+}
+
+// Split-K reduction through distributed shared memory.  Every CTA of the cluster holds the
+// f32 partial [column][128 rows] of the same output tile; CTA `cr` sums its slice of the
+// columns over all S CTAs in split order (deterministic) and stores it.  A thread takes 4
+// rows of one column per pass, 4 columns per pass across the 128 threads; all (at most
+// ~16) 16-byte loads of a thread are issued before the first use, so the whole slice costs
+// one shared-memory round trip.
+template <int S>
+__device__ __forceinline__ void cluster_reduce(const GemmParams& p, const float* kred, uint32_t cr, int et, int n0, int m0) {
+  constexpr int MAXC = (64 + S - 1) / S + 1;  // columns of one slice (token tiles up to 64 wide)
+  constexpr int MAXP = (MAXC + 3) / 4;
+  const int nmax = min(p.bn, p.T - n0);
+  const int c_lo = (p.bn * (int)cr) / S;
+  const int c_hi = min(nmax, (p.bn * ((int)cr + 1)) / S);
+  const int sub = et >> 5, r4 = (et & 31) * 4;
+  const uint32_t mine = smem_u32(kred) + (uint32_t)r4 * 4u;
+  uint32_t peer[S];
+#pragma unroll
+  for (int q = 0; q < S; ++q) peer[q] = dsmem_addr(mine, (uint32_t)q);
+  constexpr int PB = (8 / S) < 1 ? 1 : (8 / S);  // passes per batch: about 8 vectors in flight per thread
+  constexpr int NBATCH = (MAXP + PB - 1) / PB;
+#pragma unroll
+  for (int b = 0; b < NBATCH; ++b) {
+    float4 v[PB][S];
+#pragma unroll
+    for (int i = 0; i < PB; ++i) {
+      const int col = c_lo + (b * PB + i) * 4 + sub;
+      if (b * PB + i < MAXP && col < c_hi) {
+#pragma unroll
+        for (int q = 0; q < S; ++q) v[i][q] = ld_dsmem_f32x4(peer[q] + (uint32_t)col * (BM * 4u));
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < PB; ++i) {
+      const int col = c_lo + (b * PB + i) * 4 + sub;
+      if (b * PB + i < MAXP && col < c_hi) {
+        float4 a = v[i][0];
+#pragma unroll
+        for (int q = 1; q < S; ++q) {
+          a.x += v[i][q].x;
+          a.y += v[i][q].y;
+          a.z += v[i][q].z;
+          a.w += v[i][q].w;
+        }
+        store_out4(p, n0 + col, m0 + r4, a);
+      }
+    }
+  }
+}
+
 __device__ __forceinline__ bool named_bar_all(int id, int nthreads, bool pred) {
   uint32_t r;
   asm volatile(
@@ -219,6 +312,8 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  unsigned long long* tstamp = p.timing ? p.timing + (size_t)blockIdx.x * 16 : nullptr;
+  if (tstamp && threadIdx.x == 0) tstamp[0] = globaltimer_ns();
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
@@ -249,6 +344,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   // Programmatic dependent launch: the prologue above, and the producer's first weight tiles
   // below, overlap the tail of the previous kernel in the stream; everything that reads or
   // writes activations, scratch or flags comes after pdl_wait().
+  if (tstamp && threadIdx.x == 0) tstamp[1] = globaltimer_ns();
   if (threadIdx.x == 0) pdl_launch_dependents();
   else pdl_wait();
   if (p.tp.enabled && p.tp.timing && blockIdx.x == 0 && threadIdx.x == 0) p.tp.timing[p.tp.site * 8 + 0] = globaltimer_ns();
@@ -288,6 +384,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             last_phase[i] = 0;
           }
           pdl_wait();
+          if (tstamp) tstamp[2] = globaltimer_ns();
           if (p.wait.flags != nullptr) {
             // every rank's delivery epoch, then make the peer writes visible to the async proxy
             const uint32_t target = *((volatile const uint32_t*)(p.wait.flags + 16));
@@ -323,6 +420,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           }
         }
       }
+      if (tstamp) tstamp[3] = globaltimer_ns();
       // All of this CTA's own loads are issued.  From here to the first load of the next GEMM
       // in the stream (epilogue, launch gap, the small kernel in between, the next prologue)
       // HBM would sit idle: pull a slice of the NEXT GEMM's weights into L2 meanwhile
@@ -365,6 +463,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             ok = false;
             break;
           }
+          if (tstamp && item == (int)blockIdx.x && kb == kb0) tstamp[4] = globaltimer_ns();
           tc_fence_after();
           const uint32_t a_addr = smem_u32(tiles + stage * stage_bytes);
           const uint32_t b_addr = a_addr + A_BYTES;
@@ -381,6 +480,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         }
         if (!ok) break;
         umma_commit(&tfull[acc]);
+        if (tstamp) tstamp[5] = globaltimer_ns();
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
@@ -402,29 +502,43 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       if (p.cluster > 1) ok = mbar_wait_cluster(kfree, kphase ^ 1u, abort_flag) && ok;
       ok = named_bar_all(1, 128, ok);
       if (!ok) break;
+      if (tstamp && et == 0) tstamp[6] = globaltimer_ns();
       tc_fence_after();
       const int m = m_tile * BM + r;
       const int n0 = n_tile * p.bn;
       const uint32_t t_row = tmem_base + ((uint32_t)(wq * 32) << 16) + (uint32_t)(acc * p.bn);
       float* ws_part = p.ws + ((size_t)(tile * p.splits + s) * p.bn) * BM + r;
-      for (int c = 0; c < p.bn; c += 16) {
-        uint32_t v[16];
-        tmem_ld16(t_row + c, v);
-        tmem_ld_wait();
-        if (p.splits == 1) {
-          if (m < p.M) {
+      if (p.cluster > 1) {
+        // the partial goes to shared memory, 32 accumulator columns per TMEM round trip
+        for (int c = 0; c < p.bn; c += 32) {
+          uint32_t v[2][16];
+          tmem_ld16(t_row + c, v[0]);
+          if (c + 16 < p.bn) tmem_ld16(t_row + c + 16, v[1]);
+          tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int n = n0 + c + j;
-              if (n < p.T) store_out(p, n, m, __uint_as_float(v[j]));
-            }
+          for (int j = 0; j < 16; ++j) kred[(c + j) * BM + r] = __uint_as_float(v[0][j]);
+          if (c + 16 < p.bn) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) kred[(c + 16 + j) * BM + r] = __uint_as_float(v[1][j]);
           }
-        } else if (p.cluster > 1) {
+        }
+      } else {
+        for (int c = 0; c < p.bn; c += 16) {
+          uint32_t v[16];
+          tmem_ld16(t_row + c, v);
+          tmem_ld_wait();
+          if (p.splits == 1) {
+            if (m < p.M) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) kred[(c + j) * BM + r] = __uint_as_float(v[j]);
-        } else {
+              for (int j = 0; j < 16; ++j) {
+                const int n = n0 + c + j;
+                if (n < p.T) store_out(p, n, m, __uint_as_float(v[j]));
+              }
+            }
+          } else {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) ws_part[(size_t)(c + j) * BM] = __uint_as_float(v[j]);
+            for (int j = 0; j < 16; ++j) ws_part[(size_t)(c + j) * BM] = __uint_as_float(v[j]);
+          }
         }
       }
       // accumulator buffer is free again
@@ -441,33 +555,22 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         const uint32_t S = (uint32_t)p.cluster;
         __syncwarp();
         if ((uint32_t)lane < S) mbar_arrive_remote(dsmem_addr(smem_u32(kfull), (uint32_t)lane));
+        if (tstamp && et == 0) tstamp[7] = globaltimer_ns();
         const bool full_ok = named_bar_all(1, 128, mbar_wait_cluster(kfull, kphase, abort_flag));
+        if (tstamp && et == 0) tstamp[8] = globaltimer_ns();
         if (full_ok) {
-          const int nmax = min(p.bn, p.T - n0);
-          const int c_lo = (int)(((uint32_t)p.bn * cr) / S);
-          const int c_hi = min(nmax, (int)(((uint32_t)p.bn * (cr + 1u)) / S));
-          const uint32_t my = smem_u32(kred) + (uint32_t)r * 4u;
-          uint32_t peer[8];
-#pragma unroll
-          for (uint32_t q = 0; q < 8; ++q) peer[q] = dsmem_addr(my, q < S ? q : 0u);
-          for (int c = c_lo; c < c_hi; c += 4) {
-            float tmp[4][8];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint32_t off = (uint32_t)(min(c + j, c_hi - 1) * BM) * 4u;
-#pragma unroll
-              for (uint32_t q = 0; q < 8; ++q) tmp[j][q] = q < S ? ld_dsmem_f32(peer[q] + off) : 0.f;
-            }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              float sum = 0.f;
-#pragma unroll
-              for (uint32_t q = 0; q < 8; ++q)
-                if (q < S) sum += tmp[j][q];
-              if (c + j < c_hi && m < p.M) store_out(p, n0 + c + j, m, sum);
-            }
+          const int m0 = m_tile * BM;
+          switch (p.cluster) {
+            case 2: cluster_reduce<2>(p, kred, cr, et, n0, m0); break;
+            case 3: cluster_reduce<3>(p, kred, cr, et, n0, m0); break;
+            case 4: cluster_reduce<4>(p, kred, cr, et, n0, m0); break;
+            case 5: cluster_reduce<5>(p, kred, cr, et, n0, m0); break;
+            case 6: cluster_reduce<6>(p, kred, cr, et, n0, m0); break;
+            case 7: cluster_reduce<7>(p, kred, cr, et, n0, m0); break;
+            default: cluster_reduce<8>(p, kred, cr, et, n0, m0); break;
           }
         }
+        if (tstamp && et == 0) tstamp[9] = globaltimer_ns();
         // done with every peer's partial tile (also on the abort path, so nobody waits in vain)
         __syncwarp();
         if ((uint32_t)lane < S) mbar_arrive_remote(dsmem_addr(smem_u32(kfree), (uint32_t)lane));
@@ -522,8 +625,10 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 
   tc_fence_before();
   __syncthreads();
+  if (tstamp && threadIdx.x == 0) tstamp[10] = globaltimer_ns();
   // no CTA may leave while a peer can still read its shared memory or arrive on its barriers
   if (p.cluster > 1) cluster_sync_all();
+  if (tstamp && threadIdx.x == 0) tstamp[11] = globaltimer_ns();
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
@@ -779,6 +884,7 @@ static int pick_splits(int tiles, int kblocks, int bn, int sms) {
 }
 
 // One-shot hint consumed by the next GEMM launched from this thread.
+unsigned long long* g_gemm_timing = nullptr;  // profiling hook, see pg_gemm_set_timing
 thread_local const void* t_pf_ptr = nullptr;
 thread_local long long t_pf_bytes = 0;
 
@@ -902,6 +1008,7 @@ static int gemm_impl(const void* x, const void* w, void* y, int y_is_f32, int T,
   p.ws = (float*)ws;
   p.counters = (uint32_t*)counters;
   p.status = (uint32_t*)status;
+  p.timing = g_gemm_timing;
   if (plan_out == nullptr) {
     p.pf_ptr = (const uint8_t*)t_pf_ptr;
     p.pf_bytes = (t_pf_ptr && T <= 256) ? t_pf_bytes : 0;  // only the weight-streaming regime has idle HBM time to fill
@@ -969,6 +1076,13 @@ extern "C" void pg_gemm_prefetch_next(const void* ptr, long long bytes) {
   t_pf_ptr = ptr;
   t_pf_bytes = bytes;
 }
+
+// Profiling hook: a device buffer of 16 x uint64 per CTA (148 CTAs at most) that every
+// following GEMM launch fills with globaltimer stamps of its phases: [0] entry, [1] prologue
+// done, [2] predecessor complete, [3] all loads issued, [4] first stage landed, [5] last MMA
+// committed, [6] accumulator ready, [7] partial stored, [8] all partials of the cluster
+// stored, [9] reduced and written, [10] roles done, [11] cluster released.  nullptr = off.
+extern "C" void pg_gemm_set_timing(void* buf) { g_gemm_timing = (unsigned long long*)buf; }
 
 extern "C" int pg_gemm_plan(int T, int M, int K, int force_splits, int* out) {
   PG_REQUIRE(out != nullptr, "gemm plan: null output");

@@ -16,6 +16,7 @@
 
 #include "api.h"
 #include "common.cuh"
+#include "route_sort.cuh"
 
 namespace {
 
@@ -165,44 +166,16 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const RouterParams p) 
   }
 }
 
-// One CTA.  Thread e < E_local walks every route in order and numbers the ones that
-// chose expert (e + e0): a stable counting sort, so the sorted order (and with it the
-// f32 summation order downstream) never depends on scheduling.
-__global__ void __launch_bounds__(512) moe_align_kernel(const int* __restrict__ ids, int routes, int e0, int e_local, int* __restrict__ offsets,
-                                                         int* __restrict__ sorted_src, int* __restrict__ route_pos) {
-  __shared__ int cnt[512];
-  __shared__ int start[513];
-  const int e = threadIdx.x;
-  int c = 0;
-  if (e < e_local) {
-    for (int r = 0; r < routes; ++r) c += (ids[r] == e + e0);
-  }
-  cnt[e] = e < e_local ? c : 0;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int acc = 0;
-    for (int i = 0; i < e_local; ++i) {
-      start[i] = acc;
-      acc += cnt[i];
-    }
-    start[e_local] = acc;
-  }
-  __syncthreads();
-  for (int i = threadIdx.x; i <= e_local; i += blockDim.x) offsets[i] = start[i];
-  for (int r = threadIdx.x; r < routes; r += blockDim.x) {
-    const int id = ids[r] - e0;
-    if (id < 0 || id >= e_local) route_pos[r] = -1;
-  }
-  if (e < e_local) {
-    int pos = start[e];
-    for (int r = 0; r < routes; ++r) {
-      if (ids[r] == e + e0) {
-        sorted_src[pos] = r;  // route index = token * k + slot
-        route_pos[r] = pos;
-        ++pos;
-      }
-    }
-  }
+// One CTA: stable counting sort of the routes by local expert (see route_sort.cuh).
+__global__ void __launch_bounds__(ROUTE_SORT_THREADS) moe_align_kernel(const int* __restrict__ ids, int routes, int e0, int e_local, int* __restrict__ offsets,
+                                                                        int* __restrict__ sorted_src, int* __restrict__ route_pos) {
+  __shared__ RouteSortSmem sm;
+  route_sort(
+      sm, routes, e_local, offsets, [&](int i) { return ids[i] - e0; },
+      [&](int i, int pos) {
+        route_pos[i] = pos;  // route index = token * k + slot
+        if (pos >= 0) sorted_src[pos] = i;
+      });
 }
 
 __global__ void moe_gather_kernel(const bf16* __restrict__ x, long long ldx, const int* __restrict__ sorted_src, const int* __restrict__ offsets,
@@ -266,7 +239,7 @@ extern "C" int pg_router_topk(const void* logits, long long ld, const void* bias
 
 extern "C" int pg_moe_align(const void* ids, int routes, int e0, int e_local, void* offsets, void* sorted_src, void* route_pos, cudaStream_t stream) {
   PG_REQUIRE(e_local >= 1 && e_local <= 512, "moe_align: %d local experts not supported (<= 512)", e_local);
-  moe_align_kernel<<<1, 512, 0, stream>>>((const int*)ids, routes, e0, e_local, (int*)offsets, (int*)sorted_src, (int*)route_pos);
+  moe_align_kernel<<<1, ROUTE_SORT_THREADS, 0, stream>>>((const int*)ids, routes, e0, e_local, (int*)offsets, (int*)sorted_src, (int*)route_pos);
   PG_LAUNCH_CHECK();
   return PG_OK;
 }
