@@ -346,7 +346,7 @@ def main():
         ms_per_step = ko["ms_total"] / args.steps
         value = args.conc * args.steps / (ko["ms_total"] / 1e3)
         line = {
-            "metric": "decode out tok/s per box @conc 64 (Qwen3-8B TP)",
+            "metric": "decode out tok/s per box @conc 64 (Qwen3-8B TP)" if (args.model == "qwen3-8b" and args.conc == 64) else f"decode out tok/s per box @conc {args.conc} ({args.model} TP{world})",
             "value": round(value, 2),
             "unit": "tok/s",
             "n_gpus": world,
@@ -355,7 +355,7 @@ def main():
             "ms_per_step": round(ms_per_step, 4),
             "higher_is_better": True,
             "scaling": "strong",
-            "vs_baseline": round(value / PUBLISHED_QWEN3_8B_TOK_S, 3),
+            "vs_baseline": round(value / PUBLISHED_QWEN3_8B_TOK_S, 3) if args.model == "qwen3-8b" else None,
             "dtype": "bf16",
             "data": "synthetic uniform-random token prompts, random-init N(0,0.02) weights",
             "impl": args.impl,

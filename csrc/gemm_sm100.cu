@@ -212,52 +212,30 @@ __device__ __forceinline__ void store_out4(const GemmParams& p, int n, int m, fl
   }
 }
 
-// Split-K reduction through distributed shared memory.  Every CTA of the cluster holds the
-// f32 partial [column][128 rows] of the same output tile; CTA `cr` sums its slice of the
-// columns over all S CTAs in split order (deterministic) and stores it.  A thread takes 4
-// rows of one column per pass, 4 columns per pass across the 128 threads; all (at most
-// ~16) 16-byte loads of a thread are issued before the first use, so the whole slice costs
-// one shared-memory round trip.
-template <int S>
-__device__ __forceinline__ void cluster_reduce(const GemmParams& p, const float* kred, uint32_t cr, int et, int n0, int m0) {
-  constexpr int MAXC = (64 + S - 1) / S + 1;  // columns of one slice (token tiles up to 64 wide)
-  constexpr int MAXP = (MAXC + 3) / 4;
+// Split-K reduction through distributed shared memory.  The k-splits of one output tile are
+// the S CTAs of a cluster; the token columns are cut into S slices of `w` columns and CTA o
+// reduces slice o.  Every CTA pushes slice o of its f32 partial into CTA o's shared memory
+// (posted st.shared::cluster, slot [source CTA][column][128 rows]) and arrives on CTA o's
+// mbarrier, so the reduction itself reads local shared memory only: this function sums the
+// S slots in split order (deterministic) and stores the result.  A thread takes 4 rows of
+// one column per pass, 4 columns per pass across the 128 epilogue threads.
+__device__ __forceinline__ void cluster_reduce_local(const GemmParams& p, const float* kred, int S, int w, uint32_t cr, int et, int n0, int m0) {
   const int nmax = min(p.bn, p.T - n0);
-  const int c_lo = (p.bn * (int)cr) / S;
-  const int c_hi = min(nmax, (p.bn * ((int)cr + 1)) / S);
+  const int c_lo = (int)cr * w;
+  const int ncols = min(nmax, c_lo + w) - c_lo;
   const int sub = et >> 5, r4 = (et & 31) * 4;
-  const uint32_t mine = smem_u32(kred) + (uint32_t)r4 * 4u;
-  uint32_t peer[S];
-#pragma unroll
-  for (int q = 0; q < S; ++q) peer[q] = dsmem_addr(mine, (uint32_t)q);
-  constexpr int PB = (8 / S) < 1 ? 1 : (8 / S);  // passes per batch: about 8 vectors in flight per thread
-  constexpr int NBATCH = (MAXP + PB - 1) / PB;
-#pragma unroll
-  for (int b = 0; b < NBATCH; ++b) {
-    float4 v[PB][S];
-#pragma unroll
-    for (int i = 0; i < PB; ++i) {
-      const int col = c_lo + (b * PB + i) * 4 + sub;
-      if (b * PB + i < MAXP && col < c_hi) {
-#pragma unroll
-        for (int q = 0; q < S; ++q) v[i][q] = ld_dsmem_f32x4(peer[q] + (uint32_t)col * (BM * 4u));
-      }
+  for (int j = sub; j < ncols; j += 4) {
+    const float* src = kred + (size_t)j * BM + r4;
+    float4 a = *reinterpret_cast<const float4*>(src);
+#pragma unroll 4
+    for (int q = 1; q < S; ++q) {
+      const float4 b = *reinterpret_cast<const float4*>(src + (size_t)q * w * BM);
+      a.x += b.x;
+      a.y += b.y;
+      a.z += b.z;
+      a.w += b.w;
     }
-#pragma unroll
-    for (int i = 0; i < PB; ++i) {
-      const int col = c_lo + (b * PB + i) * 4 + sub;
-      if (b * PB + i < MAXP && col < c_hi) {
-        float4 a = v[i][0];
-#pragma unroll
-        for (int q = 1; q < S; ++q) {
-          a.x += v[i][q].x;
-          a.y += v[i][q].y;
-          a.z += v[i][q].z;
-          a.w += v[i][q].w;
-        }
-        store_out4(p, n0 + col, m0 + r4, a);
-      }
-    }
+    store_out4(p, n0 + c_lo + j, m0 + r4, a);
   }
 }
 
@@ -299,13 +277,13 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   const uint32_t base = smem_u32(smem_raw);
   uint8_t* tiles = smem_raw + (((base + 1023u) & ~1023u) - base);
   const int stage_bytes = A_BYTES + p.bn * 128;
-  float* kred = reinterpret_cast<float*>(tiles + p.stages * stage_bytes);  // [bn][128] f32, cluster mode only
-  uint64_t* full = reinterpret_cast<uint64_t*>(tiles + p.stages * stage_bytes + (p.cluster > 1 ? p.bn * BM * 4 : 0));
+  float* kred = reinterpret_cast<float*>(tiles + p.stages * stage_bytes);  // [source CTA][slice column][128] f32, cluster mode only
+  uint64_t* full = reinterpret_cast<uint64_t*>(tiles + p.stages * stage_bytes + (p.cluster > 1 ? (p.bn + 8) * BM * 4 : 0));
   uint64_t* empty = full + MAX_STAGES;
   uint64_t* tfull = empty + MAX_STAGES;
   uint64_t* tempty = tfull + 2;
-  uint64_t* kfull = tempty + 2;  // every CTA of the cluster has stored its partial tile (4 warps x cluster arrivals)
-  uint64_t* kfree = tempty + 3;  // every CTA of the cluster has finished reading this CTA's partial tile
+  uint64_t* kfull = tempty + 2;  // every CTA of the cluster has pushed its slice into this CTA (4 warps x cluster arrivals)
+  uint64_t* kfree = tempty + 3;  // every CTA of the cluster has reduced the previous item (its slots may be overwritten)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   uint32_t* last_flag = tmem_slot + 2;
@@ -494,11 +472,13 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     uint32_t acc_phase = 0;
     uint32_t kphase = 0;
     const uint32_t cr = p.cluster > 1 ? cluster_ctarank() : 0u;
+    const int kw = p.cluster > 1 ? (p.bn + p.cluster - 1) / p.cluster : p.bn;  // columns per slice
+    bool cluster_arrived = false;
     for (int item = blockIdx.x; item < total; item += gridDim.x) {
       const int tile = item / p.splits, s = item - tile * p.splits;
       const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
       bool ok = mbar_wait(&tfull[acc], acc_phase, abort_flag);
-      // cluster mode: the peers must be done reading this CTA's previous partial tile
+      // cluster mode: every owner must have reduced the previous item before its slots are overwritten
       if (p.cluster > 1) ok = mbar_wait_cluster(kfree, kphase ^ 1u, abort_flag) && ok;
       ok = named_bar_all(1, 128, ok);
       if (!ok) break;
@@ -509,17 +489,30 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       const uint32_t t_row = tmem_base + ((uint32_t)(wq * 32) << 16) + (uint32_t)(acc * p.bn);
       float* ws_part = p.ws + ((size_t)(tile * p.splits + s) * p.bn) * BM + r;
       if (p.cluster > 1) {
-        // the partial goes to shared memory, 32 accumulator columns per TMEM round trip
+        // push the partial: column c belongs to slice c / kw, i.e. to CTA c / kw of the cluster;
+        // 32 accumulator columns per TMEM round trip, one running remote address per slice
+        const uint32_t slot = smem_u32(kred) + (uint32_t)(((int)cr * kw) * BM + r) * 4u;  // this CTA's slot, same offset in every owner
+        int owner = 0, jj = 0;
+        uint32_t dst = dsmem_addr(slot, 0u);
         for (int c = 0; c < p.bn; c += 32) {
           uint32_t v[2][16];
           tmem_ld16(t_row + c, v[0]);
           if (c + 16 < p.bn) tmem_ld16(t_row + c + 16, v[1]);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 16; ++j) kred[(c + j) * BM + r] = __uint_as_float(v[0][j]);
-          if (c + 16 < p.bn) {
+          for (int h = 0; h < 2; ++h) {
+            if (c + h * 16 < p.bn) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) kred[(c + 16 + j) * BM + r] = __uint_as_float(v[1][j]);
+              for (int j = 0; j < 16; ++j) {
+                st_dsmem_f32(dst, __uint_as_float(v[h][j]));
+                dst += BM * 4u;
+                if (++jj == kw) {
+                  jj = 0;
+                  ++owner;
+                  dst = dsmem_addr(slot, (uint32_t)min(owner, p.cluster - 1));
+                }
+              }
+            }
           }
         }
       } else {
@@ -549,31 +542,25 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       if (acc == 0) acc_phase ^= 1u;
 
       if (p.cluster > 1) {
-        // Split-K reduction through distributed shared memory: every CTA of the cluster holds
-        // the f32 partial of the same output tile; CTA `cr` sums a slice of the columns over
-        // all CTAs in split order (deterministic) and stores it.
+        // every CTA has pushed its slices once all 4 x S warps have arrived on this CTA's barrier
         const uint32_t S = (uint32_t)p.cluster;
+        const bool last_item = item + (int)gridDim.x >= total;
         __syncwarp();
         if ((uint32_t)lane < S) mbar_arrive_remote(dsmem_addr(smem_u32(kfull), (uint32_t)lane));
+        if (last_item) {
+          cluster_arrive_release();  // no further access to the peers' shared memory from this thread
+          cluster_arrived = true;
+        }
         if (tstamp && et == 0) tstamp[7] = globaltimer_ns();
         const bool full_ok = named_bar_all(1, 128, mbar_wait_cluster(kfull, kphase, abort_flag));
         if (tstamp && et == 0) tstamp[8] = globaltimer_ns();
-        if (full_ok) {
-          const int m0 = m_tile * BM;
-          switch (p.cluster) {
-            case 2: cluster_reduce<2>(p, kred, cr, et, n0, m0); break;
-            case 3: cluster_reduce<3>(p, kred, cr, et, n0, m0); break;
-            case 4: cluster_reduce<4>(p, kred, cr, et, n0, m0); break;
-            case 5: cluster_reduce<5>(p, kred, cr, et, n0, m0); break;
-            case 6: cluster_reduce<6>(p, kred, cr, et, n0, m0); break;
-            case 7: cluster_reduce<7>(p, kred, cr, et, n0, m0); break;
-            default: cluster_reduce<8>(p, kred, cr, et, n0, m0); break;
-          }
-        }
+        if (full_ok) cluster_reduce_local(p, kred, (int)S, kw, cr, et, n0, m_tile * BM);
         if (tstamp && et == 0) tstamp[9] = globaltimer_ns();
-        // done with every peer's partial tile (also on the abort path, so nobody waits in vain)
-        __syncwarp();
-        if ((uint32_t)lane < S) mbar_arrive_remote(dsmem_addr(smem_u32(kfree), (uint32_t)lane));
+        // this CTA's slots may be overwritten by the next item (also said on the abort path, so nobody waits in vain)
+        if (!last_item) {
+          __syncwarp();
+          if ((uint32_t)lane < S) mbar_arrive_remote(dsmem_addr(smem_u32(kfree), (uint32_t)lane));
+        }
         kphase ^= 1u;
         if (!full_ok) break;
       } else if (p.splits > 1) {
@@ -621,13 +608,19 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         }
       }
     }
+    if (p.cluster > 1 && !cluster_arrived) cluster_arrive_release();  // no items, or the loop ended early
   }
+  // producer and MMA warps never touch the peers' shared memory
+  if (p.cluster > 1 && warp < 2) cluster_arrive_release();
 
   tc_fence_before();
   __syncthreads();
   if (tstamp && threadIdx.x == 0) tstamp[10] = globaltimer_ns();
-  // no CTA may leave while a peer can still read its shared memory or arrive on its barriers
-  if (p.cluster > 1) cluster_sync_all();
+  // No CTA may leave while a peer can still push into its shared memory or arrive on its
+  // barriers: every thread of the cluster has arrived once it is past its last remote access
+  // (the epilogue threads right after pushing the last item), so this wait is normally over
+  // by the time the local reduction has finished.
+  if (p.cluster > 1) cluster_wait_acquire();
   if (tstamp && threadIdx.x == 0) tstamp[11] = globaltimer_ns();
   if (warp == 1) {
     __syncwarp();
@@ -992,7 +985,7 @@ static int gemm_impl(const void* x, const void* w, void* y, int y_is_f32, int T,
   }
   const int stage_bytes = A_BYTES + p.bn * 128;
   const int tail = (2 * MAX_STAGES + 6) * 8 + 64;
-  const int red_bytes = p.cluster > 1 ? p.bn * BM * 4 : 0;
+  const int red_bytes = p.cluster > 1 ? (p.bn + 8) * BM * 4 : 0;  // S slots of ceil(bn / S) columns
   p.stages = (di.max_smem - 1024 - tail - red_bytes) / stage_bytes;
   if (p.stages > MAX_STAGES) p.stages = MAX_STAGES;
   PG_REQUIRE(p.stages >= 2, "gemm: not enough shared memory for a 2-stage pipeline");
