@@ -6,7 +6,7 @@ distinct weight / KV buffers (larger than L2 in total, so every launch streams f
 HBM), replayed after warm-up and timed with CUDA events.  Fractions are against the
 measured peaks in MEASURED_PEAKS.json (copy bandwidth, cuBLAS bf16 throughput).
 
-    python bench_ops.py [--only gemm|attn|small] [--iters 16] [--json out.json]
+    python bench_ops.py [--only gemm|attn|small|gdn|moe|mla] [--iters 16] [--json out.json]
     python bench_ops.py --single gemm:64x4096x4096      # one op, few launches (ncu target)
 
 Plays the role of the reference's kernel/op report binaries
@@ -133,21 +133,159 @@ def small_cases(iters):
     return rows
 
 
+def _meta_for(q_lens, kv_lens, page):
+    from pegainfer_b200.kv.request_kv import KvView
+    from pegainfer_b200.sched.executor import SeqStep, build_meta
+
+    seqs, nxt = [], 1
+    for i, (ql, kl) in enumerate(zip(q_lens, kv_lens)):
+        npg = (kl + page - 1) // page
+        seqs.append(SeqStep(rid=i, input_tokens=[0] * ql, start_pos=kl - ql, view=KvView(list(range(nxt, nxt + npg)), kl, page)))
+        nxt += npg
+    _, meta = build_meta(seqs, page, DEV)
+    return meta, nxt
+
+
+def gdn_cases(iters, only=None):
+    """Gated DeltaNet recurrence at the Qwen3.5-27B shape (16 K-heads, 48 V-heads, 128x128 state)."""
+    from pegainfer_b200.ops import cuda as K
+
+    rows = []
+    hk, hv, dk, dv = 16, 48, 128, 128
+    for name, q_lens in only or (("decode bs32", [1] * 32), ("decode bs64", [1] * 64), ("prefill 1x2048", [2048]), ("prefill 8x2048", [2048] * 8)):
+        meta, _ = _meta_for(q_lens, q_lens, 16)
+        meta.state_slots = torch.arange(len(q_lens), dtype=torch.int32, device=DEV)
+        t = sum(q_lens)
+        q = torch.randn(t, hk, dk, device=DEV).bfloat16()
+        k = torch.randn(t, hk, dk, device=DEV).bfloat16()
+        v = torch.randn(t, hv, dv, device=DEV).bfloat16()
+        g = -torch.rand(t, hv, device=DEV) * 0.1
+        beta = torch.rand(t, hv, device=DEV)
+        states = [torch.zeros(len(q_lens), hv, dk, dv, device=DEV) for _ in range(3)]
+        ms = time_graph(lambda i: K.gdn_recurrent(q, k, v, g, beta, states[i], meta), 3, max(2, iters // 4))
+        state_bytes = len(q_lens) * hv * dk * dv * 4 * 2
+        rows.append((f"gdn_recurrent {name} 48vh 128x128", ms, state_bytes + t * (2 * hk * dk + 2 * hv * dv) * 2, 4.0 * t * hv * dk * dv * 2))
+    return rows
+
+
+def moe_cases(iters):
+    """Routed-expert pipeline (align, gather, W13, SwiGLU, W2, combine) on one GPU."""
+    from pegainfer_b200.ops import cuda as K
+    from pegainfer_b200.ops import reference as R
+
+    rows = []
+    for name, t, h, inter, e, k, quant in (("dsv2-lite bf16 64 exp top-6", 64, 2048, 1408, 64, 6, "bf16"), ("dsv2-lite fp8 64 exp top-6", 64, 2048, 1408, 64, 6, "fp8"),
+                                            ("kimi-k2 int4 48 local exp top-8 (EP8 share)", 128, 7168, 2048, 48, 8, "int4")):
+        x = torch.randn(t, h, device=DEV).bfloat16() * 0.5
+        ids, w = R.router_topk(torch.randn(t, e, device=DEV), k, "softmax")
+        nvar = 3
+        if quant == "bf16":
+            ws = [(torch.randn(e, 2 * inter, h, device=DEV).bfloat16() * 0.02, torch.randn(e, h, inter, device=DEV).bfloat16() * 0.02) for _ in range(nvar)]
+            fn = lambda i: K.moe_experts(x, ids, w, ws[i][0], ws[i][1], 0)
+            wbytes = e * 3 * inter * h * 2
+        elif quant == "fp8":
+            ws = [((torch.randn(e, 2 * inter, h, device=DEV) * 100).clamp(-448, 448).to(torch.float8_e4m3fn), torch.full((e, 2 * inter // 128, h // 128), 2e-4, device=DEV),
+                   (torch.randn(e, h, inter, device=DEV) * 100).clamp(-448, 448).to(torch.float8_e4m3fn), torch.full((e, h // 128, inter // 128), 2e-4, device=DEV)) for _ in range(nvar)]
+            fn = lambda i: K.moe_experts_fp8(x, ids, w, ws[i][0], ws[i][1], ws[i][2], ws[i][3], 0)
+            wbytes = e * 3 * inter * h
+        else:
+            ws = [(torch.randint(-(2 ** 31), 2 ** 31 - 1, (e, 2 * inter, h // 8), dtype=torch.int32, device=DEV), (torch.rand(e, 2 * inter, h // 32, device=DEV) * 0.004).bfloat16(),
+                   torch.randint(-(2 ** 31), 2 ** 31 - 1, (e, h, inter // 8), dtype=torch.int32, device=DEV), (torch.rand(e, h, inter // 32, device=DEV) * 0.004).bfloat16()) for _ in range(nvar)]
+            fn = lambda i: K.moe_experts_int4(x, ids, w, ws[i][0], ws[i][1], ws[i][2], ws[i][3], 0)
+            wbytes = e * 3 * inter * h // 2 + e * 3 * inter * h // 32 * 2
+        ms = time_graph(fn, nvar, max(2, iters // 4))
+        rows.append((f"moe experts {name} T{t}", ms, wbytes, 2.0 * t * k * 3 * inter * h))
+    return rows
+
+
+def mla_cases(iters):
+    """Absorbed MLA decode attention over the paged latent cache (512 + 64 wide)."""
+    from pegainfer_b200.ops import cuda as K
+    from pegainfer_b200.ops import reference as R
+
+    rows = []
+    c, rope, nope, vd = 512, 64, 128, 128
+    for heads, bs, ctx in ((16, 64, 640), (64, 16, 1152), (64, 128, 1152)):
+        meta, npages = _meta_for([1] * bs, [ctx] * bs, 16)
+        latents = [torch.randn(npages, 16, c + rope, device=DEV).bfloat16() * 0.5 for _ in range(3)]
+        q = torch.randn(bs, heads, nope + rope, device=DEV).bfloat16() * 0.5
+        w_uk = torch.randn(heads, nope, c, device=DEV).bfloat16() * 0.05
+        w_uv = torch.randn(heads, vd, c, device=DEV).bfloat16() * 0.05
+        cos, sin = R.rope_tables(4096, rope, 10000.0, torch.bfloat16, DEV)
+        qq = K.mla_rope_q(q, cos, sin, meta, nope)
+        scale = (nope + rope) ** -0.5
+        ms = time_graph(lambda i: K.mla_attention(qq, w_uk, w_uv, latents[i], meta, scale, c), 3, max(2, iters // 4))
+        rows.append((f"mla decode (absorb + attn + v_up) {heads}h bs{bs} ctx{ctx}", ms, bs * ctx * (c + rope) * 2, 2.0 * bs * ctx * heads * (c + rope + c)))
+    return rows
+
+
+GEMM_PHASES = ["entry", "prologue done", "predecessor complete", "all loads issued", "first stage landed", "last MMA committed", "accumulator ready",
+               "partial pushed", "cluster partials in", "reduced + stored", "roles done", "cluster released"]
+
+
+def gemm_phase_timeline(t, m, k):
+    """Per-CTA globaltimer stamps of one eager GEMM launch with cold L2 (profiling hook of the
+    GEMM kernel): min / median / max over the CTAs, microseconds from the first CTA's entry."""
+    import ctypes
+
+    import numpy as np
+
+    from pegainfer_b200 import _native
+    from pegainfer_b200.ops import cuda as K
+
+    lib = _native.load()
+    x = (torch.randn(t, k, device=DEV) * 0.1).bfloat16()
+    ws = [(torch.randn(m, k, device=DEV) * 0.02).bfloat16() for _ in range(4)]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
+    timing = torch.zeros(148 * 16, dtype=torch.int64, device=DEV)
+    for w in ws:
+        K.linear(x, w)
+    torch.cuda.synchronize()
+    plan = K.gemm_plan(t, m, k)
+    rows = None
+    for rep in range(3):
+        flush.zero_()
+        timing.zero_()
+        torch.cuda.synchronize()
+        lib.pg_gemm_set_timing(ctypes.c_void_p(timing.data_ptr()))
+        K.linear(x, ws[rep])
+        torch.cuda.synchronize()
+        lib.pg_gemm_set_timing(ctypes.c_void_p(0))
+        tm = timing.view(148, 16).cpu().numpy().astype(np.float64)[: plan["grid"]]
+        t0 = tm[:, 0].min()
+        rows = []
+        for i, name in enumerate(GEMM_PHASES):
+            col = tm[:, i]
+            col = col[col > 0]
+            if len(col):
+                rows.append((name, (col.min() - t0) / 1e3, (np.median(col) - t0) / 1e3, (col.max() - t0) / 1e3))
+    print(f"gemm T{t} M{m} K{k}: plan {plan}")
+    print(f"{'phase':26s} {'min us':>8s} {'median':>8s} {'max':>8s}")
+    for name, a, b, c in rows:
+        print(f"{name:26s} {a:8.2f} {b:8.2f} {c:8.2f}")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default=None)
     ap.add_argument("--iters", type=int, default=16)
     ap.add_argument("--json", default=None)
-    ap.add_argument("--single", default=None, help="e.g. gemm:64x4096x4096, attn:64x1152, prefill:4x1024")
+    ap.add_argument("--single", default=None, help="e.g. gemm:64x4096x4096, attn:64x1152, prefill:4x1024, gdn:8x2048 (sequences x tokens)")
     ap.add_argument("--library", action="store_true", help="also time torch/cuBLAS for the GEMM rows")
+    ap.add_argument("--phases", default=None, help="gemm:TxMxK: print the per-CTA phase timeline of one GEMM launch")
     args = ap.parse_args()
     hbm, tf, src = peaks()
     rows = []
+    if args.phases:
+        gemm_phase_timeline(*[int(v) for v in args.phases.split(":")[1].split("x")])
+        return
     if args.single:
         kind, shape = args.single.split(":")
         dims = [int(v) for v in shape.split("x")]
         if kind == "gemm":
             ms, by, fl = gemm_case(*dims, iters=args.iters)
+        elif kind == "gdn":
+            name, ms, by, fl = gdn_cases(args.iters, only=[("single", [dims[1]] * dims[0])])[0]
         elif kind == "attn":
             ms, by, fl = attn_decode_case(dims[0], dims[1], 32, 8, 128, 16, args.iters)
         else:
@@ -174,6 +312,12 @@ def main():
                 rows.append((f"prefill attn {ns}x{ql} 32q/8kv hd128", ms, by, fl))
         if args.only in (None, "small"):
             rows.extend(small_cases(args.iters))
+        if args.only in (None, "gdn"):
+            rows.extend(gdn_cases(args.iters))
+        if args.only in (None, "moe"):
+            rows.extend(moe_cases(args.iters))
+        if args.only in (None, "mla"):
+            rows.extend(mla_cases(args.iters))
     out = []
     print(f"{'op':58s} {'us':>9s} {'GB/s':>8s} {'%HBM':>6s} {'TFLOP/s':>8s} {'%bf16':>6s}   (peaks: {src} {hbm:.0f} GB/s, {tf:.0f} TFLOP/s)")
     for name, ms, by, fl in rows:

@@ -100,7 +100,8 @@ int pg_gdn_conv1d(const void* x, long long ldx, const void* w, void* state, void
 int pg_gdn_gates(const void* a, long long lda, const void* b, long long ldb, const void* a_log, const void* dt_bias, void* g, void* beta,
                  int tokens, int hv, cudaStream_t stream);
 int pg_gdn_recurrent(const void* q, const void* k, long long ld_qk, const void* v, long long ld_v, const void* g, const void* beta, void* state,
-                     void* out, const void* q_indptr, const void* slots, int num_seqs, int hk, int hv, int dk, int dv, cudaStream_t stream);
+                     void* out, const void* q_indptr, const void* slots, int num_seqs, int hk, int hv, int dk, int dv, int max_q_len,
+                     cudaStream_t stream);
 
 // ---- attention (attention.cu) ------------------------------------------------------
 int pg_decode_splits(int num_seqs, int hkv, int max_kv_len, int sms);

@@ -3,17 +3,20 @@
 //  * gdn_conv1d: causal depthwise conv (kernel <= 4) + SiLU over ragged sequences with a
 //    carried [C, K-1] input history per sequence slot (prefill and decode in one kernel).
 //  * gdn_gates: g = -exp(A_log) * softplus(a + dt_bias), beta = sigmoid(b).
-//  * gdn_recurrent: the gated delta rule.  One CTA per (sequence, value head); thread v
-//    owns column v of the f32 state S[Dk, Dv] in registers, so S^T k, the rank-1 update
-//    and S^T q are thread-local dot products over Dk with no cross-thread reduction; the
-//    CTA stages 8 tokens of (q, k, v, g, beta) in shared memory per barrier.  A decode
-//    step is one pass over the 64 KiB state (read + write: HBM bound); a prefill chunk
-//    walks its tokens in order with the state resident in registers.
+//  * gdn_recurrent: the gated delta rule.  The columns of the f32 state S[Dk, Dv] evolve
+//    independently, so a CTA takes 32 columns of one (sequence, value head) and four lanes
+//    of a warp share a column, each keeping a quarter of its Dk elements in registers:
+//    S^T k, the rank-1 update and S^T q are register dot products plus two shuffles, and a
+//    single long prompt already spreads over heads x Dv/32 CTAs.  A decode step is one pass
+//    over the state (read + write: HBM bound); a prefill chunk walks its tokens in order
+//    with the state resident in registers.
 //
 // Functional parity with pegainfer-kernels/csrc/qwen35/conv1d.cu:19-165,
 // gated_delta_rule.cu:28-347 and the chunk-wise Triton prefill pipeline
 // (tools/triton/gated_delta_rule_chunkwise_kernels.py), whose result equals this
 // recurrence.
+#include <cuda_fp16.h>
+
 #include "api.h"
 #include "common.cuh"
 
@@ -61,87 +64,169 @@ __global__ void gdn_gates_kernel(const bf16* __restrict__ a, long long lda, cons
   beta[idx] = 1.f / (1.f + expf(-__bfloat162float(b[t * ldb + h])));
 }
 
-constexpr int TOK_STAGE = 8;
+constexpr int TOK_STAGE = 16;
+constexpr int GDN_COLS = 32;  // state columns per CTA (4 threads per column)
 
 // q, k: [T, Hk, DK] (row stride ld_qk elements, heads contiguous); v: [T, Hv, DV]; out [T, Hv, DV].
-template <int DK>
+// CTA = (32 state columns of one value head, sequence); four lanes of a warp share a column,
+// each holding a quarter of its DK state elements in registers.  Tokens are staged 16 at a
+// time through two shared-memory buffers: the raw q/k/v/g/beta of the next 16 tokens are
+// loaded into registers before the current 16 are processed and normalised into the other
+// buffer afterwards, so global latency overlaps the recurrence and there is one barrier per
+// 16 tokens.  The kernel is bound by FMA issue (3 x Dk x Dv multiply-adds per token and head
+// on the CUDA cores): measured variants with two columns per thread and fp16 staging moved
+// shared-memory traffic down 4x without changing the time.
+template <int DK, bool PIPE>
 __global__ void __launch_bounds__(128) gdn_recurrent_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, long long ld_qk,
                                                              const bf16* __restrict__ v, long long ld_v, const float* __restrict__ g,
                                                              const float* __restrict__ beta, float* __restrict__ state, bf16* __restrict__ out,
                                                              const int* __restrict__ q_indptr, const int* __restrict__ slots, int hk, int hv,
-                                                             int dv) {
-  __shared__ float sq[TOK_STAGE][DK], sk[TOK_STAGE][DK];
-  __shared__ float sv[TOK_STAGE][128], sg[TOK_STAGE], sb[TOK_STAGE];
-  const int h = blockIdx.x, b = blockIdx.y;
+                                                             int dv, int col_groups) {
+  constexpr int QK = DK / 4;    // state elements per thread
+  constexpr int QS = QK + 4;    // padded quarter stride in shared memory: the four quarters land in different banks
+  constexpr int QL = DK / 32;   // q / k elements per lane when a warp holds one token
+  constexpr int TPW = TOK_STAGE / 4;  // tokens per warp and stage
+  constexpr int VPT = TOK_STAGE * GDN_COLS / 128;
+  __shared__ __align__(16) float sq[2][TOK_STAGE][4 * QS], sk[2][TOK_STAGE][4 * QS];
+  __shared__ float sv[2][TOK_STAGE][GDN_COLS], sg[2][TOK_STAGE], sb[2][TOK_STAGE];
+  const int h = blockIdx.x / col_groups, cg = blockIdx.x % col_groups, b = blockIdx.y;
   const int slot = slots[b];
   const int q0 = q_indptr[b], q1 = q_indptr[b + 1];
   if (q1 == q0 || slot < 0) return;
   const int kh = h / (hv / hk);
-  const int tid = threadIdx.x;
-  const bool owner = tid < dv;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int qtr = tid & 3, lc = tid >> 2, col = cg * GDN_COLS + lc;
+  const bool owner = col < dv;
   float* S = state + (((long long)slot * hv + h) * DK) * dv;  // [DK][dv], v contiguous
-  float s_col[DK];
-  if (owner) {
+  float s_col[QK];
 #pragma unroll
-    for (int i = 0; i < DK; ++i) s_col[i] = S[(long long)i * dv + tid];
-  }
+  for (int i = 0; i < QK; ++i) s_col[i] = owner ? S[(long long)(qtr * QK + i) * dv + col] : 0.f;
   const float q_scale = rsqrtf((float)DK);
-  for (int t0 = q0; t0 < q1; t0 += TOK_STAGE) {
-    const int nt = min(TOK_STAGE, q1 - t0);
-    __syncthreads();
-    // stage nt tokens: each warp normalises q and k of tokens w, w+4
-    const int warp = tid >> 5, lane = tid & 31;
-    for (int j = warp; j < nt; j += 4) {
+
+  // raw next-stage values held in registers between fetch and commit
+  float rq[TPW][QL], rk[TPW][QL], rv[VPT], rg = 0.f, rb = 0.f;
+  auto fetch = [&](int t0, int nt) {
+#pragma unroll
+    for (int jj = 0; jj < TPW; ++jj) {
+      const int j = warp + 4 * jj;
       const bf16* qp = q + (long long)(t0 + j) * ld_qk + (long long)kh * DK;
       const bf16* kp = k + (long long)(t0 + j) * ld_qk + (long long)kh * DK;
+#pragma unroll
+      for (int i = 0; i < QL; ++i) {
+        rq[jj][i] = j < nt ? __bfloat162float(qp[lane + 32 * i]) : 0.f;
+        rk[jj][i] = j < nt ? __bfloat162float(kp[lane + 32 * i]) : 0.f;
+      }
+    }
+#pragma unroll
+    for (int x = 0; x < VPT; ++x) {
+      const int idx = tid + 128 * x, j = idx / GDN_COLS, d = cg * GDN_COLS + idx % GDN_COLS;
+      rv[x] = (j < nt && d < dv) ? __bfloat162float(v[(long long)(t0 + j) * ld_v + (long long)h * dv + d]) : 0.f;
+    }
+    if (tid < nt) {
+      rg = expf(g[(long long)(t0 + tid) * hv + h]);
+      rb = beta[(long long)(t0 + tid) * hv + h];
+    }
+  };
+  auto commit = [&](int buf, int nt) {
+#pragma unroll
+    for (int jj = 0; jj < TPW; ++jj) {
+      const int j = warp + 4 * jj;
       float qs = 0.f, ks = 0.f;
-      for (int i = lane; i < DK; i += 32) {
-        const float a = __bfloat162float(qp[i]), c = __bfloat162float(kp[i]);
-        sq[j][i] = a;
-        sk[j][i] = c;
-        qs += a * a;
-        ks += c * c;
+#pragma unroll
+      for (int i = 0; i < QL; ++i) {
+        qs += rq[jj][i] * rq[jj][i];
+        ks += rk[jj][i] * rk[jj][i];
       }
       qs = warp_sum(qs);
       ks = warp_sum(ks);
       const float qn = rsqrtf(qs + 1e-12f) * q_scale, kn = rsqrtf(ks + 1e-12f);
-      for (int i = lane; i < DK; i += 32) {
-        sq[j][i] *= qn;
-        sk[j][i] *= kn;
-      }
-      if (lane == 0) {
-        sg[j] = expf(g[(long long)(t0 + j) * hv + h]);
-        sb[j] = beta[(long long)(t0 + j) * hv + h];
+#pragma unroll
+      for (int i = 0; i < QL; ++i) {
+        const int e = lane + 32 * i;
+        sq[buf][j][(e / QK) * QS + (e % QK)] = rq[jj][i] * qn;
+        sk[buf][j][(e / QK) * QS + (e % QK)] = rk[jj][i] * kn;
       }
     }
-    for (int idx = tid; idx < nt * dv; idx += 128) {
-      const int j = idx / dv, d = idx % dv;
-      sv[j][d] = __bfloat162float(v[(long long)(t0 + j) * ld_v + (long long)h * dv + d]);
+#pragma unroll
+    for (int x = 0; x < VPT; ++x) {
+      const int idx = tid + 128 * x;
+      sv[buf][idx / GDN_COLS][idx % GDN_COLS] = rv[x];
     }
+    if (tid < nt) {
+      sg[buf][tid] = rg;
+      sb[buf][tid] = rb;
+    }
+  };
+  auto process = [&](int buf, int t0, int nt) {
+    for (int j = 0; j < nt; ++j) {
+      const float decay = sg[buf][j];
+      const float4* kq = reinterpret_cast<const float4*>(&sk[buf][j][qtr * QS]);
+      const float4* qq = reinterpret_cast<const float4*>(&sq[buf][j][qtr * QS]);
+      // four independent accumulation chains per dot product
+      float4 kv4 = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int i = 0; i < QK / 4; ++i) {
+        const float4 kk = kq[i];
+        s_col[4 * i + 0] *= decay;
+        s_col[4 * i + 1] *= decay;
+        s_col[4 * i + 2] *= decay;
+        s_col[4 * i + 3] *= decay;
+        kv4.x += s_col[4 * i + 0] * kk.x;
+        kv4.y += s_col[4 * i + 1] * kk.y;
+        kv4.z += s_col[4 * i + 2] * kk.z;
+        kv4.w += s_col[4 * i + 3] * kk.w;
+      }
+      float kv = (kv4.x + kv4.y) + (kv4.z + kv4.w);
+      kv += __shfl_xor_sync(0xffffffffu, kv, 1);
+      kv += __shfl_xor_sync(0xffffffffu, kv, 2);
+      const float delta = (sv[buf][j][lc] - kv) * sb[buf][j];
+      float4 o4 = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int i = 0; i < QK / 4; ++i) {
+        const float4 kk = kq[i], qv = qq[i];
+        s_col[4 * i + 0] += kk.x * delta;
+        s_col[4 * i + 1] += kk.y * delta;
+        s_col[4 * i + 2] += kk.z * delta;
+        s_col[4 * i + 3] += kk.w * delta;
+        o4.x += s_col[4 * i + 0] * qv.x;
+        o4.y += s_col[4 * i + 1] * qv.y;
+        o4.z += s_col[4 * i + 2] * qv.z;
+        o4.w += s_col[4 * i + 3] * qv.w;
+      }
+      float o = (o4.x + o4.y) + (o4.z + o4.w);
+      o += __shfl_xor_sync(0xffffffffu, o, 1);
+      o += __shfl_xor_sync(0xffffffffu, o, 2);
+      if (owner && qtr == 0) out[((long long)(t0 + j) * hv + h) * dv + col] = __float2bfloat16(o);
+    }
+  };
+
+  if (PIPE) {
+    fetch(q0, min(TOK_STAGE, q1 - q0));
+    commit(0, min(TOK_STAGE, q1 - q0));
     __syncthreads();
-    if (owner) {
-      for (int j = 0; j < nt; ++j) {
-        const float decay = sg[j];
-        float kv = 0.f;
-#pragma unroll
-        for (int i = 0; i < DK; ++i) {
-          s_col[i] *= decay;
-          kv += s_col[i] * sk[j][i];
-        }
-        const float delta = (sv[j][tid] - kv) * sb[j];
-        float o = 0.f;
-#pragma unroll
-        for (int i = 0; i < DK; ++i) {
-          s_col[i] += sk[j][i] * delta;
-          o += s_col[i] * sq[j][i];
-        }
-        out[((long long)(t0 + j) * hv + h) * dv + tid] = __float2bfloat16(o);
-      }
+    int buf = 0;
+    for (int t0 = q0; t0 < q1; t0 += TOK_STAGE, buf ^= 1) {
+      const int nt = min(TOK_STAGE, q1 - t0);
+      const int nnext = min(TOK_STAGE, q1 - (t0 + TOK_STAGE));
+      if (nnext > 0) fetch(t0 + TOK_STAGE, nnext);
+      process(buf, t0, nt);
+      if (nnext > 0) commit(buf ^ 1, nnext);
+      __syncthreads();
+    }
+  } else {
+    // decode and other short steps: no prefetch registers, more CTAs per SM for the state stream
+    for (int t0 = q0; t0 < q1; t0 += TOK_STAGE) {
+      const int nt = min(TOK_STAGE, q1 - t0);
+      fetch(t0, nt);
+      commit(0, nt);
+      __syncthreads();
+      process(0, t0, nt);
+      __syncthreads();
     }
   }
   if (owner) {
 #pragma unroll
-    for (int i = 0; i < DK; ++i) S[(long long)i * dv + tid] = s_col[i];
+    for (int i = 0; i < QK; ++i) S[(long long)(qtr * QK + i) * dv + col] = s_col[i];
   }
 }
 
@@ -169,14 +254,24 @@ extern "C" int pg_gdn_gates(const void* a, long long lda, const void* b, long lo
 
 extern "C" int pg_gdn_recurrent(const void* q, const void* k, long long ld_qk, const void* v, long long ld_v, const void* g, const void* beta,
                                 void* state, void* out, const void* q_indptr, const void* slots, int num_seqs, int hk, int hv, int dk, int dv,
-                                cudaStream_t stream) {
+                                int max_q_len, cudaStream_t stream) {
+  // steps longer than one stage of 16 tokens use the variant that prefetches the next stage
+  const bool long_steps = max_q_len > 16;
   PG_REQUIRE(dv <= 128 && hv % hk == 0, "gdn_recurrent: dv=%d must be <= 128 and hv %% hk == 0", dv);
   if (num_seqs == 0) return PG_OK;
-  dim3 grid(hv, num_seqs);
+  const int col_groups = (dv + GDN_COLS - 1) / GDN_COLS;
+  dim3 grid(hv * col_groups, num_seqs);
 #define PG_GDN_LAUNCH(DKV)                                                                                                                  \
-  gdn_recurrent_kernel<DKV><<<grid, 128, 0, stream>>>((const bf16*)q, (const bf16*)k, ld_qk, (const bf16*)v, ld_v, (const float*)g,        \
-                                                      (const float*)beta, (float*)state, (bf16*)out, (const int*)q_indptr, (const int*)slots, \
-                                                      hk, hv, dv)
+  do {                                                                                                                                      \
+    if (long_steps)                                                                                                                         \
+      gdn_recurrent_kernel<DKV, true><<<grid, 128, 0, stream>>>((const bf16*)q, (const bf16*)k, ld_qk, (const bf16*)v, ld_v, (const float*)g, \
+                                                                (const float*)beta, (float*)state, (bf16*)out, (const int*)q_indptr,        \
+                                                                (const int*)slots, hk, hv, dv, col_groups);                                  \
+    else                                                                                                                                    \
+      gdn_recurrent_kernel<DKV, false><<<grid, 128, 0, stream>>>((const bf16*)q, (const bf16*)k, ld_qk, (const bf16*)v, ld_v, (const float*)g, \
+                                                                 (const float*)beta, (float*)state, (bf16*)out, (const int*)q_indptr,       \
+                                                                 (const int*)slots, hk, hv, dv, col_groups);                                 \
+  } while (0)
   if (dk == 128)
     PG_GDN_LAUNCH(128);
   else if (dk == 64)

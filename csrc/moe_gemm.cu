@@ -12,17 +12,18 @@
 //
 // Weight formats:
 //   bf16   W [E, M, K]: TMA straight into the swizzled A tile.
-//   int4   W packed [E, M, K/8] int32 (offset-binary nibbles, low nibble = lowest k) with
+//   int4   W packed [E, M, K/8] int32 (offset-binary nibbles, pair-interleaved inside each word:
+//          bits 0-15 hold elements 0,2,4,6 and bits 16-31 elements 1,3,5,7 of the word's eight) with
 //          bf16 scales [E, M, K/32]: TMA brings the packed tile (4 KB per 128x64) into a
-//          raw buffer, four dequantisation warps expand it to bf16 ((nibble - 8) * scale,
+//          raw buffer, eight dequantisation warps expand it to bf16 ((nibble - 8) * scale,
 //          one rounding) directly into the 128-byte-swizzled A tile and hand it to the MMA
 //          warp through an mbarrier; HBM traffic stays at 4.5 bits per weight.
 //   fp8    W e4m3 [E, M, K] with f32 scale_inv [E, ceil(M/128), ceil(K/128)] (block-scaled
-//          checkpoints): TMA brings the raw 8 KB tile, the same four warps convert e4m3 ->
+//          checkpoints): TMA brings the raw 8 KB tile, the same eight warps convert e4m3 ->
 //          f32 (exact), multiply by the block's scale_inv and round once to bf16 into the
 //          swizzled A tile; HBM traffic is one byte per weight.
 //
-// warp 0 TMA producer | warp 1 MMA issuer + TMEM owner | warps 2-5 epilogue | warps 6-9 dequant (int4 / fp8)
+// warp 0 TMA producer | warp 1 MMA issuer + TMEM owner | warps 2-5 epilogue | warps 6-13 dequant (int4 / fp8)
 //
 // Takes the place of the reference's Marlin W4A16 MoE kernel
 // (pegainfer-kernels/csrc/kimi_k2/kimi_marlin_wna16.cu:241-340, vllm_marlin/**) and its
@@ -103,7 +104,7 @@ __device__ __forceinline__ bool named_bar_all(int id, int nthreads, bool pred) {
   return r != 0;
 }
 
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(448, 1)
 moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const MoeGemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ int s_tiles[MAX_EXPERTS];
@@ -126,7 +127,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
-      mbar_init(&aready[s], 128);
+      mbar_init(&aready[s], 256);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull[a], 1);
@@ -288,8 +289,13 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
       if (acc == 0) acc_phase ^= 1u;
     }
   } else if (p.quant == 1) {
-    // dequantisation warps: thread r expands row r of the packed tile into the swizzled A tile
-    const int r = threadIdx.x - 192;  // 0..127
+    // dequantisation warps (8 warps, two threads per weight row): thread (r, hf) expands the
+    // 32 nibbles of one scale group into four 16-byte chunks of the swizzled A tile.  The
+    // packed words carry their nibbles pair-interleaved (low half: even elements, high half:
+    // odd elements; done once at load), so (w >> 4i) & 0x000F000F | 0x43004300 is already the
+    // bf16 pair (128 + e[2i], 128 + e[2i+1]).
+    const int dq = threadIdx.x - 192;  // 0..255
+    const int r = dq >> 1, hf = dq & 1;
     int stage = 0;
     uint32_t phase = 0;
     ItemCursor cur;
@@ -299,49 +305,62 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
       if (!locate(p, s_tiles, item, cur, it)) break;
       const int m = it.m_tile * BM + r;
-      const bf16* srow = reinterpret_cast<const bf16*>(p.scales) + ((size_t)it.e * p.M + (m < p.M ? m : 0)) * groups_per_row;
-      for (int kb = 0; kb < p.kblocks; ++kb) {
-        if (!mbar_wait(&full[stage], phase, abort_flag)) {
-          ok = false;
-          break;
+      const bf16* srow = reinterpret_cast<const bf16*>(p.scales) + ((size_t)it.e * p.M + (m < p.M ? m : 0)) * groups_per_row + hf;
+      // The scales come from global memory: fetch them four k-blocks ahead so that their latency
+      // is off the per-k-block chain (raw tile landed -> expand -> hand to the MMA warp).
+      const bf16 zero = __float2bfloat16(0.f);
+      bf16 sc[4], nx[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) sc[u] = (m < p.M && u * 2 + hf < groups_per_row) ? srow[u * 2] : zero;
+      for (int kb0 = 0; kb0 < p.kblocks && ok; kb0 += 4) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int g0 = (kb0 + 4 + u) * 2;
+          nx[u] = (m < p.M && g0 + hf < groups_per_row) ? srow[g0] : zero;
         }
-        uint8_t* st = tiles + stage * stage_bytes;
-        const uint4* raw = reinterpret_cast<const uint4*>(st + A_BYTES + b_bytes + r * 32);
-        const uint4 lo = raw[0], hi = raw[1];
-        const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-        const int g0 = kb * 2;
-        const bf16 s0 = (m < p.M && g0 < groups_per_row) ? srow[g0] : __float2bfloat16(0.f);
-        const bf16 s1 = (m < p.M && g0 + 1 < groups_per_row) ? srow[g0 + 1] : __float2bfloat16(0.f);
-        const bf162 sc0 = __halves2bfloat162(s0, s0), sc1 = __halves2bfloat162(s1, s1);
-        const bf162 bias = __floats2bfloat162_rn(136.f, 136.f);
-        uint8_t* a_row = st + r * 128;
 #pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
-          // 8 nibbles of word `ch` -> 8 bf16; (0x4300 | n) is the bf16 value 128 + n
-          const uint32_t w = words[ch];
-          uint32_t o[4];
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const uint32_t n0 = (w >> (8 * q)) & 0xFu, n1 = (w >> (8 * q + 4)) & 0xFu;
-            uint32_t packed = (0x4300u | n0) | ((0x4300u | n1) << 16);
-            bf162 val = *reinterpret_cast<bf162*>(&packed);
-            val = __hmul2(__hsub2(val, bias), ch < 4 ? sc0 : sc1);
-            o[q] = *reinterpret_cast<uint32_t*>(&val);
+        for (int u = 0; u < 4; ++u) {
+          if (kb0 + u >= p.kblocks || !ok) break;
+          if (!mbar_wait(&full[stage], phase, abort_flag)) {
+            ok = false;
+            break;
           }
-          *reinterpret_cast<uint4*>(a_row + ((ch ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+          uint8_t* st = tiles + stage * stage_bytes;
+          const uint4 raw = *reinterpret_cast<const uint4*>(st + A_BYTES + b_bytes + r * 32 + hf * 16);
+          const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+          const bf162 s2 = __halves2bfloat162(sc[u], sc[u]);
+          const bf162 bias = __floats2bfloat162_rn(136.f, 136.f);
+          uint8_t* a_row = st + r * 128;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t o[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint32_t t = ((words[c] >> (4 * i)) & 0x000F000Fu) | 0x43004300u;
+              bf162 val = *reinterpret_cast<bf162*>(&t);
+              val = __hmul2(__hsub2(val, bias), s2);
+              o[i] = *reinterpret_cast<uint32_t*>(&val);
+            }
+            const int ch = hf * 4 + c;
+            *reinterpret_cast<uint4*>(a_row + ((ch ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+          }
+          fence_proxy_async_smem();
+          mbar_arrive(&aready[stage]);
+          if (++stage == p.stages) {
+            stage = 0;
+            phase ^= 1u;
+          }
         }
-        fence_proxy_async_smem();
-        mbar_arrive(&aready[stage]);
-        if (++stage == p.stages) {
-          stage = 0;
-          phase ^= 1u;
-        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) sc[u] = nx[u];
       }
     }
   } else if (p.quant == 2) {
-    // fp8 dequantisation warps: thread r expands the 64 e4m3 bytes of row r (exact in half,
-    // then f32 * scale_inv of the 128x128 block, rounded once to bf16) into the swizzled A tile
-    const int r = threadIdx.x - 192;  // 0..127
+    // fp8 dequantisation warps (8 warps, two threads per weight row): thread (r, hf) expands 32
+    // e4m3 bytes of row r (exact in half, then f32 * scale_inv of the 128x128 block, rounded
+    // once to bf16) into four 16-byte chunks of the swizzled A tile
+    const int dq = threadIdx.x - 192;  // 0..255
+    const int r = dq >> 1, hf = dq & 1;
     int stage = 0;
     uint32_t phase = 0;
     ItemCursor cur;
@@ -352,42 +371,55 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
       if (!locate(p, s_tiles, item, cur, it)) break;
       const float* srow = sc + ((size_t)it.e * mb + it.m_tile) * kbk;
-      for (int kb = 0; kb < p.kblocks; ++kb) {
-        if (!mbar_wait(&full[stage], phase, abort_flag)) {
-          ok = false;
-          break;
-        }
-        uint8_t* st = tiles + stage * stage_bytes;
-        const uint4* raw = reinterpret_cast<const uint4*>(st + A_BYTES + b_bytes + r * 64);
-        const float scale = srow[kb >> 1];
-        uint8_t* a_row = st + r * 128;
+      // scale_inv of the next four k-blocks (two 128-wide blocks) is fetched while the current four are expanded
+      float cs[2], ns[2];
+      cs[0] = srow[0];
+      cs[1] = kbk > 1 ? srow[1] : 0.f;
+      for (int kb0 = 0; kb0 < p.kblocks && ok; kb0 += 4) {
+        const int nb = (kb0 + 4) >> 1;
+        ns[0] = nb < kbk ? srow[nb] : 0.f;
+        ns[1] = nb + 1 < kbk ? srow[nb + 1] : 0.f;
 #pragma unroll
-        for (int half = 0; half < 4; ++half) {
-          const uint4 v = raw[half];
-          const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+        for (int u = 0; u < 4; ++u) {
+          if (kb0 + u >= p.kblocks || !ok) break;
+          if (!mbar_wait(&full[stage], phase, abort_flag)) {
+            ok = false;
+            break;
+          }
+          uint8_t* st = tiles + stage * stage_bytes;
+          const uint4* raw = reinterpret_cast<const uint4*>(st + A_BYTES + b_bytes + r * 64 + hf * 32);
+          const float scale = cs[u >> 1];
+          uint8_t* a_row = st + r * 128;
 #pragma unroll
-          for (int hh = 0; hh < 2; ++hh) {
-            // 8 bytes -> 8 bf16 = one 16-byte chunk of the A row
-            uint32_t o[4];
+          for (int half = 0; half < 2; ++half) {
+            const uint4 v = raw[half];
+            const uint32_t words[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const uint32_t w = words[hh * 2 + (q >> 1)];
-              const __nv_fp8x2_storage_t pair = (__nv_fp8x2_storage_t)((w >> (16 * (q & 1))) & 0xFFFFu);
-              const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(pair, __NV_E4M3);
-              const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hr));
-              const bf162 b = __floats2bfloat162_rn(f.x * scale, f.y * scale);
-              o[q] = *reinterpret_cast<const uint32_t*>(&b);
+            for (int hh = 0; hh < 2; ++hh) {
+              // 8 bytes -> 8 bf16 = one 16-byte chunk of the A row
+              uint32_t o[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint32_t w = words[hh * 2 + (q >> 1)];
+                const __nv_fp8x2_storage_t pair = (__nv_fp8x2_storage_t)((w >> (16 * (q & 1))) & 0xFFFFu);
+                const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(pair, __NV_E4M3);
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hr));
+                const bf162 b2 = __floats2bfloat162_rn(f.x * scale, f.y * scale);
+                o[q] = *reinterpret_cast<const uint32_t*>(&b2);
+              }
+              const int ch = hf * 4 + half * 2 + hh;
+              *reinterpret_cast<uint4*>(a_row + ((ch ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
             }
-            const int ch = half * 2 + hh;
-            *reinterpret_cast<uint4*>(a_row + ((ch ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+          }
+          fence_proxy_async_smem();
+          mbar_arrive(&aready[stage]);
+          if (++stage == p.stages) {
+            stage = 0;
+            phase ^= 1u;
           }
         }
-        fence_proxy_async_smem();
-        mbar_arrive(&aready[stage]);
-        if (++stage == p.stages) {
-          stage = 0;
-          phase ^= 1u;
-        }
+        cs[0] = ns[0];
+        cs[1] = ns[1];
       }
     }
   }
@@ -526,7 +558,7 @@ static int moe_gemm_impl(const void* x, long long ldx, long long x_rows, const v
   int rc = pg_make_tmap_bf16_2d(&tm_x, x, x_rows, K, ldx, bn, BK);
   if (rc) return rc;
   const size_t smem = 1024 + (size_t)p.stages * stage_bytes + tail;
-  moe_gemm_kernel<<<g_sms[dev & 63], quant ? 320 : 192, smem, stream>>>(tm_w, tm_x, p);
+  moe_gemm_kernel<<<g_sms[dev & 63], quant ? 448 : 192, smem, stream>>>(tm_w, tm_x, p);
   PG_LAUNCH_CHECK();
   return PG_OK;
 }

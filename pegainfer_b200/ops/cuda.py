@@ -376,7 +376,7 @@ def gdn_recurrent(q, k, v, g, beta, state, meta: AttnMeta):
     out = torch.empty((t, hv, dv), dtype=q.dtype, device=q.device)
     c = ctx(q.device)
     rc = lib().pg_gdn_recurrent(_ptr(q), _ptr(k), _ll(q.stride(0)), _ptr(v), _ll(v.stride(0)), _ptr(g.contiguous()), _ptr(beta.contiguous()), _ptr(state), _ptr(out),
-                                _ptr(meta.q_indptr), _ptr(meta.state_slots), _ci(meta.num_seqs), _ci(hk), _ci(hv), _ci(dk), _ci(dv), _stream())
+                                _ptr(meta.q_indptr), _ptr(meta.state_slots), _ci(meta.num_seqs), _ci(hk), _ci(hv), _ci(dk), _ci(dv), _ci(int(meta.max_q_len)), _stream())
     _check(rc, c)
     return out
 
@@ -426,6 +426,21 @@ def quant_code(w) -> int:
     return 0
 
 
+def paired_int4(w):
+    """INT4 expert weights in the nibble order the grouped GEMM reads (pair-interleaved).  Model
+    loaders repack once at load; a tensor that still has the checkpoint order is repacked here
+    and the copy is kept on it."""
+    if w.dtype != torch.int32 or getattr(w, "_pg_nibbles", None) == "paired":
+        return w
+    cp = getattr(w, "_pg_paired_copy", None)
+    if cp is None:
+        from .reference import repack_int4_pairs
+
+        cp = repack_int4_pairs(w)
+        w._pg_paired_copy = cp
+    return cp
+
+
 def grouped_gemm(xs, offsets, w, scales=None, bn: int = 16):
     """``xs`` [rows, K] sorted by expert; ``w`` bf16 [E, M, K], packed int32 [E, M, K/8] with bf16
     scales [E, M, K/32], or FP8 e4m3 [E, M, K] with f32 ``scale_inv`` [E, ceil(M/128), ceil(K/128)]."""
@@ -433,6 +448,8 @@ def grouped_gemm(xs, offsets, w, scales=None, bn: int = 16):
     e, m = w.shape[0], w.shape[1]
     mode = quant_code(w)
     assert (mode == 0) == (scales is None), "quantised expert weights need their scales"
+    if mode == 1:
+        w = paired_int4(w)
     if mode == 2:
         assert scales.dtype == torch.float32 and scales.shape == (e, (m + 127) // 128, (k + 127) // 128), "FP8 experts need f32 scale_inv per 128x128 block"
     y = torch.empty((rows, m), dtype=torch.bfloat16, device=xs.device)

@@ -369,6 +369,51 @@ def quant_int4_g32(w, group=32):
     return packed, s.to(w.dtype)
 
 
+_PAIR_ORDER = (0, 2, 4, 6, 1, 3, 5, 7)  # nibble position j of a pair-interleaved word holds element _PAIR_ORDER[j]
+
+
+def _renibble(packed, order, chunk_rows=1 << 16):
+    flat = packed.reshape(-1, packed.shape[-1])
+    out = torch.empty_like(flat)
+    shifts = torch.arange(0, 32, 4, device=packed.device, dtype=torch.int64)
+    for r0 in range(0, flat.shape[0], chunk_rows):
+        blk = flat[r0 : r0 + chunk_rows].to(torch.int64) & 0xFFFFFFFF
+        nib = (blk.unsqueeze(-1) >> shifts) & 0xF
+        new = torch.zeros_like(blk)
+        for j, e in enumerate(order):
+            new |= nib[..., e] << (4 * j)
+        new = torch.where(new >= 2 ** 31, new - 2 ** 32, new)
+        out[r0 : r0 + chunk_rows] = new.to(torch.int32)
+    return out.reshape(packed.shape)
+
+
+def repack_int4_pairs(packed):
+    """Load-time repack of compressed-tensors INT4 words for the sm_100a grouped GEMM: inside
+    every int32 the low 16 bits take elements 0, 2, 4, 6 and the high 16 bits elements 1, 3,
+    5, 7, so that one shift + mask yields two consecutive elements as a bf16 pair."""
+    out = _renibble(packed, _PAIR_ORDER)
+    out._pg_nibbles = "paired"
+    return out
+
+
+def unrepack_int4_pairs(packed):
+    inv = [0] * 8
+    for j, e in enumerate(_PAIR_ORDER):
+        inv[e] = j
+    return _renibble(packed, inv)
+
+
+def plain_int4(packed):
+    """The compressed-tensors nibble order of ``packed``, whichever order it is stored in."""
+    if getattr(packed, "_pg_nibbles", None) != "paired":
+        return packed
+    plain = getattr(packed, "_pg_plain_copy", None)
+    if plain is None:
+        plain = unrepack_int4_pairs(packed)
+        packed._pg_plain_copy = plain
+    return plain
+
+
 def dequant_fp8_block(w_fp8, scale_inv, block=128):
     """Block-scaled FP8 e4m3: ``w = fp8 * scale_inv[block_row, block_col]``."""
     out, k = w_fp8.shape
@@ -452,6 +497,7 @@ def mla_attention(q, w_uk, w_uv, latent_layer, meta: AttnMeta, scale, kv_lora):
 def moe_experts_int4(x, ids, weights, w13_packed, w13_scale, w2_packed, w2_scale, expert_offset=0, group=32):
     """``moe_experts`` over INT4 group-quantised weights (dequantised per expert)."""
     t, h = x.shape
+    w13_packed, w2_packed = plain_int4(w13_packed), plain_int4(w2_packed)
     e_local = w13_packed.shape[0]
     out = torch.zeros(t, h, dtype=torch.float32, device=x.device)
     for e in range(e_local):

@@ -84,6 +84,8 @@ class FusedEP(EPContext):
         key = "_packed" if "w13_packed" in experts else "_fp8" if "w13_fp8" in experts else ""
         w13, w2 = experts["w13" + key], experts["w2" + key]
         mode = K.quant_code(w13)
+        if mode == 1:
+            w13, w2 = K.paired_int4(w13), K.paired_int4(w2)
         s13 = experts.get("w13_scale")
         s2 = experts.get("w2_scale")
         e_local = w13.shape[0]
