@@ -15,11 +15,12 @@
 //   int4   W packed [E, M, K/8] int32 (offset-binary nibbles, pair-interleaved inside each word:
 //          bits 0-15 hold elements 0,2,4,6 and bits 16-31 elements 1,3,5,7 of the word's eight) with
 //          bf16 scales [E, M, K/32]: TMA brings the packed tile (4 KB per 128x64) into a
-//          raw buffer, eight dequantisation warps expand it to bf16 ((nibble - 8) * scale,
+//          raw buffer, the dequantisation warps (four groups of two, each group taking every
+//          fourth k-block) expand it to bf16 ((nibble - 8) * scale,
 //          one rounding) directly into the 128-byte-swizzled A tile and hand it to the MMA
 //          warp through an mbarrier; HBM traffic stays at 4.5 bits per weight.
 //   fp8    W e4m3 [E, M, K] with f32 scale_inv [E, ceil(M/128), ceil(K/128)] (block-scaled
-//          checkpoints): TMA brings the raw 8 KB tile, the same eight warps convert e4m3 ->
+//          checkpoints): TMA brings the raw 8 KB tile, the same warps convert e4m3 ->
 //          f32 (exact), multiply by the block's scale_inv and round once to bf16 into the
 //          swizzled A tile; HBM traffic is one byte per weight.
 //
@@ -127,7 +128,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
-      mbar_init(&aready[s], 256);
+      mbar_init(&aready[s], 64);  // one dequant group
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull[a], 1);
@@ -288,138 +289,120 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
-  } else if (p.quant == 1) {
-    // dequantisation warps (8 warps, two threads per weight row): thread (r, hf) expands the
-    // 32 nibbles of one scale group into four 16-byte chunks of the swizzled A tile.  The
-    // packed words carry their nibbles pair-interleaved (low half: even elements, high half:
-    // odd elements; done once at load), so (w >> 4i) & 0x000F000F | 0x43004300 is already the
-    // bf16 pair (128 + e[2i], 128 + e[2i+1]).
+  } else if (p.quant != 0) {
+    // Dequantisation warps.  The chain of one k-block (raw tile landed -> expand -> write the
+    // swizzled bf16 A tile -> proxy fence -> hand to the MMA warp) has a latency of several
+    // hundred cycles that no single group of threads can hide, so the eight warps form four
+    // groups of 64 threads and group g takes every fourth k-block (counted across work items):
+    // four tiles are being expanded at any time.  A thread expands rows t and t + 64.
     const int dq = threadIdx.x - 192;  // 0..255
-    const int r = dq >> 1, hf = dq & 1;
-    int stage = 0;
-    uint32_t phase = 0;
+    const int grp = dq >> 6, t = dq & 63;
     ItemCursor cur;
     Item it;
+    long long kbg0 = 0;  // global index of this item's first k-block
+    bool ok = true;
+    const bool int4 = p.quant == 1;
     const int groups_per_row = p.K / 32;
-    bool ok = true;
-    for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
-      if (!locate(p, s_tiles, item, cur, it)) break;
-      const int m = it.m_tile * BM + r;
-      const bf16* srow = reinterpret_cast<const bf16*>(p.scales) + ((size_t)it.e * p.M + (m < p.M ? m : 0)) * groups_per_row + hf;
-      // The scales come from global memory: fetch them four k-blocks ahead so that their latency
-      // is off the per-k-block chain (raw tile landed -> expand -> hand to the MMA warp).
-      const bf16 zero = __float2bfloat16(0.f);
-      bf16 sc[4], nx[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) sc[u] = (m < p.M && u * 2 + hf < groups_per_row) ? srow[u * 2] : zero;
-      for (int kb0 = 0; kb0 < p.kblocks && ok; kb0 += 4) {
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int g0 = (kb0 + 4 + u) * 2;
-          nx[u] = (m < p.M && g0 + hf < groups_per_row) ? srow[g0] : zero;
-        }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          if (kb0 + u >= p.kblocks || !ok) break;
-          if (!mbar_wait(&full[stage], phase, abort_flag)) {
-            ok = false;
-            break;
-          }
-          uint8_t* st = tiles + stage * stage_bytes;
-          const uint4 raw = *reinterpret_cast<const uint4*>(st + A_BYTES + b_bytes + r * 32 + hf * 16);
-          const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
-          const bf162 s2 = __halves2bfloat162(sc[u], sc[u]);
-          const bf162 bias = __floats2bfloat162_rn(136.f, 136.f);
-          uint8_t* a_row = st + r * 128;
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint32_t o[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              uint32_t t = ((words[c] >> (4 * i)) & 0x000F000Fu) | 0x43004300u;
-              bf162 val = *reinterpret_cast<bf162*>(&t);
-              val = __hmul2(__hsub2(val, bias), s2);
-              o[i] = *reinterpret_cast<uint32_t*>(&val);
-            }
-            const int ch = hf * 4 + c;
-            *reinterpret_cast<uint4*>(a_row + ((ch ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-          }
-          fence_proxy_async_smem();
-          mbar_arrive(&aready[stage]);
-          if (++stage == p.stages) {
-            stage = 0;
-            phase ^= 1u;
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) sc[u] = nx[u];
-      }
-    }
-  } else if (p.quant == 2) {
-    // fp8 dequantisation warps (8 warps, two threads per weight row): thread (r, hf) expands 32
-    // e4m3 bytes of row r (exact in half, then f32 * scale_inv of the 128x128 block, rounded
-    // once to bf16) into four 16-byte chunks of the swizzled A tile
-    const int dq = threadIdx.x - 192;  // 0..255
-    const int r = dq >> 1, hf = dq & 1;
-    int stage = 0;
-    uint32_t phase = 0;
-    ItemCursor cur;
-    Item it;
     const int mb = (p.M + 127) / 128, kbk = (p.K + 127) / 128;
-    const float* sc = reinterpret_cast<const float*>(p.scales);
-    bool ok = true;
-    for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
+    for (int item = blockIdx.x; item < total && ok; item += gridDim.x, kbg0 += p.kblocks) {
       if (!locate(p, s_tiles, item, cur, it)) break;
-      const float* srow = sc + ((size_t)it.e * mb + it.m_tile) * kbk;
-      // scale_inv of the next four k-blocks (two 128-wide blocks) is fetched while the current four are expanded
-      float cs[2], ns[2];
-      cs[0] = srow[0];
-      cs[1] = kbk > 1 ? srow[1] : 0.f;
-      for (int kb0 = 0; kb0 < p.kblocks && ok; kb0 += 4) {
-        const int nb = (kb0 + 4) >> 1;
-        ns[0] = nb < kbk ? srow[nb] : 0.f;
-        ns[1] = nb + 1 < kbk ? srow[nb + 1] : 0.f;
+      const int first = (int)(((long long)grp - kbg0) & 3);  // first k-block of this item that belongs to the group
+      // scales of the group's next k-block are fetched one turn (four k-blocks) ahead
+      const bf16* srow[2];
+      bool live[2];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          if (kb0 + u >= p.kblocks || !ok) break;
-          if (!mbar_wait(&full[stage], phase, abort_flag)) {
-            ok = false;
-            break;
+      for (int h = 0; h < 2; ++h) {
+        const int m = it.m_tile * BM + t + 64 * h;
+        live[h] = m < p.M;
+        srow[h] = reinterpret_cast<const bf16*>(p.scales) + ((size_t)it.e * p.M + (live[h] ? m : 0)) * groups_per_row;
+      }
+      const float* frow = reinterpret_cast<const float*>(p.scales) + ((size_t)it.e * mb + it.m_tile) * kbk;
+      const bf16 zero = __float2bfloat16(0.f);
+      bf16 sc[2][2], nx[2][2];
+      float fs = 0.f, fnx = 0.f;
+      auto load_scales = [&](int kb, bf16 (&dst)[2][2], float& fdst) {
+        if (kb >= p.kblocks) return;
+        if (int4) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            dst[h][0] = (live[h] && kb * 2 < groups_per_row) ? srow[h][kb * 2] : zero;
+            dst[h][1] = (live[h] && kb * 2 + 1 < groups_per_row) ? srow[h][kb * 2 + 1] : zero;
           }
-          uint8_t* st = tiles + stage * stage_bytes;
-          const uint4* raw = reinterpret_cast<const uint4*>(st + A_BYTES + b_bytes + r * 64 + hf * 32);
-          const float scale = cs[u >> 1];
+        } else {
+          fdst = frow[kb >> 1];
+        }
+      };
+      load_scales(first, sc, fs);
+      for (int kb = first; kb < p.kblocks && ok; kb += 4) {
+        load_scales(kb + 4, nx, fnx);
+        const long long kbg = kbg0 + kb;
+        const int stage = (int)(kbg % p.stages);
+        const uint32_t phase = (uint32_t)((kbg / p.stages) & 1);
+        if (!mbar_wait(&full[stage], phase, abort_flag)) {
+          ok = false;
+          break;
+        }
+        uint8_t* st = tiles + stage * stage_bytes;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int r = t + 64 * h;
           uint8_t* a_row = st + r * 128;
+          if (int4) {
+            const uint4* raw = reinterpret_cast<const uint4*>(st + A_BYTES + b_bytes + r * 32);
+            const bf162 bias = __floats2bfloat162_rn(136.f, 136.f);
 #pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            const uint4 v = raw[half];
-            const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+            for (int hf = 0; hf < 2; ++hf) {
+              const uint4 rw = raw[hf];
+              const uint32_t words[4] = {rw.x, rw.y, rw.z, rw.w};
+              const bf162 s2 = __halves2bfloat162(sc[h][hf], sc[h][hf]);
 #pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-              // 8 bytes -> 8 bf16 = one 16-byte chunk of the A row
-              uint32_t o[4];
+              for (int c = 0; c < 4; ++c) {
+                // pair-interleaved nibbles: (w >> 4i) & 0x000F000F | 0x43004300 = bf16 pair (128 + e[2i], 128 + e[2i+1])
+                uint32_t o[4];
 #pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const uint32_t w = words[hh * 2 + (q >> 1)];
-                const __nv_fp8x2_storage_t pair = (__nv_fp8x2_storage_t)((w >> (16 * (q & 1))) & 0xFFFFu);
-                const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(pair, __NV_E4M3);
-                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hr));
-                const bf162 b2 = __floats2bfloat162_rn(f.x * scale, f.y * scale);
-                o[q] = *reinterpret_cast<const uint32_t*>(&b2);
+                for (int i = 0; i < 4; ++i) {
+                  uint32_t tt = ((words[c] >> (4 * i)) & 0x000F000Fu) | 0x43004300u;
+                  bf162 val = *reinterpret_cast<bf162*>(&tt);
+                  val = __hmul2(__hsub2(val, bias), s2);
+                  o[i] = *reinterpret_cast<uint32_t*>(&val);
+                }
+                const int ch = hf * 4 + c;
+                *reinterpret_cast<uint4*>(a_row + ((ch ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
               }
-              const int ch = hf * 4 + half * 2 + hh;
-              *reinterpret_cast<uint4*>(a_row + ((ch ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+          } else {
+            // fp8 e4m3: exact in half, f32 * scale_inv of the 128x128 block, rounded once to bf16
+            const uint4* raw = reinterpret_cast<const uint4*>(st + A_BYTES + b_bytes + r * 64);
+#pragma unroll
+            for (int half = 0; half < 4; ++half) {
+              const uint4 v = raw[half];
+              const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+              for (int hh = 0; hh < 2; ++hh) {
+                uint32_t o[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  const uint32_t w = words[hh * 2 + (q >> 1)];
+                  const __nv_fp8x2_storage_t pair = (__nv_fp8x2_storage_t)((w >> (16 * (q & 1))) & 0xFFFFu);
+                  const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(pair, __NV_E4M3);
+                  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hr));
+                  const bf162 b2 = __floats2bfloat162_rn(f.x * fs, f.y * fs);
+                  o[q] = *reinterpret_cast<const uint32_t*>(&b2);
+                }
+                const int ch = half * 2 + hh;
+                *reinterpret_cast<uint4*>(a_row + ((ch ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+              }
             }
           }
-          fence_proxy_async_smem();
-          mbar_arrive(&aready[stage]);
-          if (++stage == p.stages) {
-            stage = 0;
-            phase ^= 1u;
-          }
         }
-        cs[0] = ns[0];
-        cs[1] = ns[1];
+        fence_proxy_async_smem();
+        mbar_arrive(&aready[stage]);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          sc[h][0] = nx[h][0];
+          sc[h][1] = nx[h][1];
+        }
+        fs = fnx;
       }
     }
   }

@@ -39,6 +39,11 @@ class FusedTP(TPContext):
         # measured at 1024 rows on 2 GPUs the fused site is ~30 us slower than GEMM + NCCL +
         # norm, while up to a few hundred rows (decode) it is at parity or ahead.
         self.fused_max_rows = int(os.environ.get("PEGAINFER_TP_FUSED_MAX_ROWS", fused_max_rows))
+        # Measured on Qwen3-8B decode (64 rows): the fused site is within 1-2 % of GEMM + NCCL +
+        # norm on 2 and 4 GPUs, but 27 % behind on 8, where NCCL reduces inside the switch (NVLS)
+        # and the two-hop peer-store protocol pays the skew of eight ranks twice.  Above this
+        # world size every step takes the library all-reduce.
+        self.fused_max_world = int(os.environ.get("PEGAINFER_TP_FUSED_MAX_WORLD", "4"))
         import torch.distributed as dist
 
         self.device = torch.device(device)
@@ -79,7 +84,7 @@ class FusedTP(TPContext):
 
     def row_linear_add_norm(self, a, w, residual, norm_w, eps, offset=False):
         t, k = a.shape
-        if t > self.fused_max_rows:
+        if t > self.fused_max_rows or self.world > self.fused_max_world:
             import torch.distributed as dist
 
             from .. import ops

@@ -463,3 +463,25 @@ def test_fused_ep_single_rank_self_dispatch_matches_local_pipeline(int4):
         status_clean()
         assert torch.equal(got, got2)
         assert (got - ref[:n]).abs().max().item() < 1e-2 * max(1.0, ref.abs().max().item())
+
+
+@pytest.mark.parametrize("t,k,m,r,slots_n", [(9, 1024, 2048, 16, 3), (64, 4096, 1024, 64, 4), (1, 512, 512, 8, 2)])
+def test_lora_delta_kernel_mixed_slots(t, k, m, r, slots_n):
+    """Per-token adapter delta y += scale[s] * B[s] (A[s] x) with a mixed batch (some rows without adapter),
+    also on a column slice of a wider output (fused qkv)."""
+    torch.manual_seed(t + r)
+    x = (torch.randn(t, k, device=DEV) * 0.5).bfloat16()
+    A = (torch.randn(slots_n, r, k, device=DEV) * 0.05).bfloat16()
+    B = (torch.randn(slots_n, m, r, device=DEV) * 0.05).bfloat16()
+    scale = torch.rand(slots_n, device=DEV) * 2
+    slots = torch.randint(-1, slots_n, (t,), dtype=torch.int32, device=DEV)
+    wide = (torch.randn(t, m + 256, device=DEV) * 0.3).bfloat16()
+    y1, y2 = wide.clone(), wide.clone()
+    cu().lora_delta_(y1[:, 128 : 128 + m], x, A, B, scale, slots)
+    R.lora_delta_(y2[:, 128 : 128 + m], x, A, B, scale, slots)
+    torch.cuda.synchronize()
+    bf16_close(y1, y2, rel=2 ** -6, abs_=2e-2)
+    untouched = slots < 0
+    assert torch.equal(y1[untouched], wide[untouched])
+    assert torch.equal(y1[:, :128], wide[:, :128]) and torch.equal(y1[:, 128 + m :], wide[:, 128 + m :])
+    status_clean()

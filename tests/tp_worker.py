@@ -9,6 +9,8 @@ import torch.distributed as dist
 
 
 def main():
+    os.environ["PEGAINFER_TP_FUSED_MAX_WORLD"] = "8"  # exercise the fused kernels at every world size
+
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
