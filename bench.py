@@ -200,6 +200,7 @@ def kernel_only(args, eng, rank, world, device):
         sn[s, 2, :n] = pos + 1
     graphs.np_table[:n, :need_pages] = pg
     graphs.d_table.copy_(graphs.h_table)
+    graphs.invalidate_table()
     graphs.d_small.zero_()
     graphs.d_small[:n].copy_(torch.tensor(first_tokens, dtype=torch.int32))
     d_pos, d_slot, d_kvl = graphs.d_small[B : B + b], graphs.d_small[2 * B : 2 * B + b], graphs.d_small[3 * B : 3 * B + b]

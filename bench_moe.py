@@ -104,6 +104,7 @@ def main():
             sn[s, 2, :n_local] = pos + 1
         graphs.np_table[:n_local, :need_pages] = pg
         graphs.d_table.copy_(graphs.h_table)
+        graphs.invalidate_table()
         graphs.d_small.zero_()
         graphs.d_small[:n_local].copy_(torch.tensor(first, dtype=torch.int32))
         graphs.d_small[B : B + b].copy_(sched[0, 0])

@@ -294,7 +294,8 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     // swizzled bf16 A tile -> proxy fence -> hand to the MMA warp) has a latency of several
     // hundred cycles that no single group of threads can hide, so the eight warps form four
     // groups of 64 threads and group g takes every fourth k-block (counted across work items):
-    // four tiles are being expanded at any time.  A thread expands rows t and t + 64.
+    // four tiles are being expanded at any time.  A thread expands rows t and t + 64.  The stage
+    // count is a multiple of 4 (host side), so group g only ever touches stages = g (mod 4).
     const int dq = threadIdx.x - 192;  // 0..255
     const int grp = dq >> 6, t = dq & 63;
     ItemCursor cur;
@@ -509,6 +510,14 @@ static int moe_gemm_impl(const void* x, long long ldx, long long x_rows, const v
   const int tail = (3 * MAX_STAGES + 4) * 8 + 64;
   p.stages = (g_max_smem[dev & 63] - g_static_smem - 1024 - tail) / stage_bytes;
   if (p.stages > MAX_STAGES) p.stages = MAX_STAGES;
+  if (quant) {
+    // The four dequant groups take k-blocks 0,1,2,3 (mod 4).  With a stage count that is a
+    // multiple of 4 every stage barrier is only ever waited on by one group, in order; any other
+    // count lets a group wait on a barrier that is still two phases behind, and a parity wait
+    // cannot tell that from "done".
+    p.stages -= p.stages % 4;
+    PG_REQUIRE(p.stages >= 4, "moe gemm: token tile %d leaves fewer than 4 pipeline stages for quantised weights", bn);
+  }
   PG_REQUIRE(p.stages >= 2, "moe gemm: not enough shared memory");
   uint32_t cols = 32;
   while (cols < (uint32_t)(2 * bn)) cols <<= 1;

@@ -123,7 +123,9 @@ class RequestKv:
     def view(self) -> KvView:
         """Pages covering every scheduled token (exactly, no spare pages)."""
         n = blocks_for(self.scheduled, self.bs)
-        return KvView(self.blocks[:n], self.scheduled, self.bs)
+        # the common case (every block is scheduled) hands out the list itself: views are
+        # transient, consumed within the step that asked for them
+        return KvView(self.blocks if n == len(self.blocks) else self.blocks[:n], self.scheduled, self.bs)
 
     prefill_view = view
     decode_view = view

@@ -59,6 +59,13 @@ class DecodeGraphs:
         self.d2h_bytes = 0
         self.replays = 0
         self.kernels_per_graph: dict = {}
+        self.invalidate_table()
+
+    def invalidate_table(self) -> None:
+        """Forget what ``stage`` knows about the block-table mirror (call after writing it directly)."""
+        self._row_state = [(-1, 0)] * self.max_b
+        self._table_b = 0
+        self._table_w = 0
 
     # views of the arena for a bucket
     def _views(self, b: int):
@@ -146,16 +153,33 @@ class DecodeGraphs:
         B = self.max_b
         sm, tb = self.np_small, self.np_table
         wmax = 1
+        rows = self._row_state  # per table row: (request id, pages already written): a decode step adds at most one page
+        dirty = False
+        ps = self.page_size
+        toks, poss, slots = [0] * n, [0] * n, [0] * n
         for i, s in enumerate(seqs):
             pos = s.start_pos
             pages = s.view.page_indices
-            sm[i] = s.input_tokens[0]
-            sm[B + i] = pos
-            sm[2 * B + i] = pages[pos // self.page_size] * self.page_size + pos % self.page_size
-            sm[3 * B + i] = pos + 1
+            toks[i] = s.input_tokens[0]
+            poss[i] = pos
+            slots[i] = pages[pos // ps] * ps + pos % ps
             np_ = len(pages)
-            tb[i, :np_] = pages
-            wmax = max(wmax, np_)
+            rid, have = rows[i]
+            if rid != s.rid or have > np_:
+                tb[i, :np_] = pages
+                rows[i] = (s.rid, np_)
+                dirty = True
+            elif have < np_:
+                tb[i, have:np_] = pages[have:]
+                rows[i] = (s.rid, np_)
+                dirty = True
+            if np_ > wmax:
+                wmax = np_
+        sm[:n] = toks
+        sm[B : B + n] = poss
+        sm[2 * B : 2 * B + n] = slots
+        sm[3 * B : 3 * B + n] = poss
+        sm[3 * B : 3 * B + n] += 1
         if n < b:
             sm[n:b] = 0
             sm[B + n : B + b] = 0
@@ -168,8 +192,12 @@ class DecodeGraphs:
             hs[n:b] = 0
             self.d_slots.copy_(self.h_slots, non_blocking=True)
         self.d_small.copy_(self.h_small, non_blocking=True)
-        self.d_table[:b, :wmax].copy_(self.h_table[:b, :wmax], non_blocking=True)
-        self.h2d_bytes += self.h_small.numel() * 4 + b * wmax * 4
+        self.h2d_bytes += self.h_small.numel() * 4
+        if dirty or b != self._table_b or wmax > self._table_w:
+            # the block table only changes when a sequence crosses a page boundary or rows change hands
+            self.d_table[:b, :wmax].copy_(self.h_table[:b, :wmax], non_blocking=True)
+            self.h2d_bytes += b * wmax * 4
+            self._table_b, self._table_w = b, wmax
 
     def run(self, seqs, greedy: bool = True) -> torch.Tensor:
         from ..sched.executor import bucket_for
