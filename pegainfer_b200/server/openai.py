@@ -78,6 +78,36 @@ def _stops(body: dict) -> list:
     return [x for x in s if x]
 
 
+class _LoopBridge:
+    """Scheduler thread -> event loop hand-off.  A decode step produces one update per running
+    request; waking the loop once per update (a lock and a socket write each) costs the
+    scheduler thread about a millisecond per step at 64 streams, so updates are queued here and
+    the loop is woken once per burst."""
+
+    def __init__(self, loop):
+        import threading
+
+        self.loop = loop
+        self._lock = threading.Lock()
+        self._pending: list = []
+        self._scheduled = False
+
+    def push(self, q, upd) -> None:
+        with self._lock:
+            self._pending.append((q, upd))
+            if self._scheduled:
+                return
+            self._scheduled = True
+        self.loop.call_soon_threadsafe(self._drain)
+
+    def _drain(self) -> None:
+        with self._lock:
+            items, self._pending = self._pending, []
+            self._scheduled = False
+        for q, upd in items:
+            q.put_nowait(upd)
+
+
 class Frontend:
     """Protocol logic independent of the web framework (unit-testable)."""
 
@@ -90,6 +120,7 @@ class Frontend:
         self.metrics = ServerMetrics(model_name)
         self.lora = lora_manager
         self.created = int(time.time())
+        self._bridges: dict = {}  # event loop id -> _LoopBridge
 
     # -- request construction ---------------------------------------------------
     def _prompt_ids(self, prompt) -> list:
@@ -141,13 +172,21 @@ class Frontend:
         )
 
     # -- streaming core ----------------------------------------------------------------
+    def _bridge_for(self, loop) -> "_LoopBridge":
+        b = self._bridges.get(id(loop))
+        if b is None or b.loop is not loop:
+            b = _LoopBridge(loop)
+            self._bridges[id(loop)] = b
+        return b
+
     async def run_request(self, req: Request, stops: list, disconnected=None) -> AsyncIterator[dict]:
         """Yields events: {"text", "token_ids", "logprobs", "finish_reason", "usage", ...}."""
         loop = asyncio.get_running_loop()
         q: asyncio.Queue = asyncio.Queue()
         t_start = time.monotonic()
+        bridge = self._bridge_for(loop)
         try:
-            stream = self.engine.submit(req, listener=lambda upd: loop.call_soon_threadsafe(q.put_nowait, upd))
+            stream = self.engine.submit(req, listener=lambda upd: bridge.push(q, upd))
         except ValueError as e:
             raise BadRequest(str(e))
         detok = IncrementalDetokenizer(self.tok)
@@ -156,14 +195,21 @@ class Frontend:
         t_last = None
         first = True
         text_all = ""
+        watch = None
+        if disconnected is not None:
+            # client-gone detection runs beside the token path instead of as a timeout around
+            # every queue read (a timer and a task per token add up at a few thousand tokens/s)
+            async def _watch():
+                while not stream.closed:
+                    await asyncio.sleep(0.25)
+                    if await disconnected():
+                        stream.abort()
+                        return
+
+            watch = asyncio.create_task(_watch())
         try:
             while True:
-                try:
-                    upd: RequestUpdate = await asyncio.wait_for(q.get(), timeout=0.25)
-                except asyncio.TimeoutError:
-                    if disconnected is not None and await disconnected():
-                        stream.abort()
-                    continue
+                upd: RequestUpdate = await q.get()
                 ev: dict = {}
                 now = time.monotonic()
                 if upd.cached_tokens is not None:
@@ -219,6 +265,8 @@ class Frontend:
                 if ev:
                     yield ev
         finally:
+            if watch is not None:
+                watch.cancel()
             if not stream.closed:
                 stream.abort()
 
@@ -448,6 +496,11 @@ def create_app(fe: Frontend):
 
 
 def serve(engine, tokenizer, model_name: str, host: str = "127.0.0.1", port: int = 8000, declared_engines=None, lora_manager=None, log_level="warning"):
+    import sys
+
+    # The scheduler thread and the event loop share the interpreter lock; the default 5 ms switch
+    # interval lets a busy event loop hold a decode step up for longer than the step itself.
+    sys.setswitchinterval(2e-4)
     """Blocking: run the HTTP server until interrupted (the engine is already up)."""
     import uvicorn
 
