@@ -271,6 +271,211 @@ __global__ void __launch_bounds__(128, (STAGES == 2 && D <= 128) ? 3 : 1) decode
   }
 }
 
+// -----------------------------------------------------------------------------------
+// decode, persistent form
+// -----------------------------------------------------------------------------------
+// One work unit = (sequence, kv head, KV split), as above, but the grid is one CTA per
+// resident slot and every CTA walks units blockIdx.x, blockIdx.x + gridDim.x, ...  Each
+// warp treats its share of the tiles of all those units as ONE stream: the cp.async issue
+// cursor runs two tiles ahead of the compute cursor across unit boundaries, so the pipeline
+// is filled once per CTA instead of once per unit (a unit is only a handful of tiles per
+// warp, and a pipeline that covers DRAM latency takes about as long to fill).  The merge
+// scratch is separate from the pipeline buffers, because loads of the next unit are in
+// flight while the four warps of a CTA combine their partials of the current one.
+struct DecodeUnit {
+  int b, h, split, kv_len, qrow, t_begin, t_end;
+  const int* table_row;
+};
+
+__device__ __forceinline__ bool load_decode_unit(const AttnParams& p, int u, DecodeUnit& o) {
+  if (u >= p.num_seqs * p.hkv * p.splits) return false;
+  o.split = u % p.splits;
+  o.h = (u / p.splits) % p.hkv;
+  o.b = u / (p.splits * p.hkv);
+  o.kv_len = p.kv_lens[o.b];
+  o.qrow = p.q_indptr[o.b];
+  o.table_row = p.table + (long long)o.b * p.table_stride;
+  const int n_tiles = (o.kv_len + 15) / 16;
+  const int tps = (n_tiles + p.splits - 1) / p.splits;
+  o.t_begin = o.split * tps;
+  o.t_end = min(n_tiles, o.t_begin + tps);
+  return true;
+}
+
+template <int D>
+__global__ void __launch_bounds__(128, D <= 128 ? 2 : 1) decode_attn_persistent_kernel(const AttnParams p) {
+  PG_PDL_ENTRY();
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  constexpr int STAGES = 3;
+  constexpr int TILE = 16;
+  constexpr int CH = D / 8;
+  constexpr int KS = D / 16;
+  constexpr int NT = D / 8;
+  constexpr int STAGE_ELEMS = 2 * TILE * D;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int G = p.hq / p.hkv;
+  bf16* wsm = reinterpret_cast<bf16*>(smem_raw) + warp * STAGES * STAGE_ELEMS;
+  // merge scratch behind the pipelines: [warp][8 rows][D] f32 + (m, l) per warp and row
+  float* mo = reinterpret_cast<float*>(smem_raw + (size_t)4 * STAGES * STAGE_ELEMS * 2);
+  float* mm = mo + 4 * 8 * D;
+  float* ml = mm + 4 * 8;
+  const long long row_stride = (long long)p.hkv * D;
+  const long long v_plane = (long long)p.page_size * row_stride;
+  const uint64_t kv_policy = l2_policy_evict_first();
+
+  // issue cursor
+  DecodeUnit ui;
+  int iu = blockIdx.x;
+  bool vi = load_decode_unit(p, iu, ui);
+  int ti = vi ? ui.t_begin + warp : 0;
+  auto issue_next = [&](int stage) {
+    while (vi && ti >= ui.t_end) {
+      iu += gridDim.x;
+      vi = load_decode_unit(p, iu, ui);
+      ti = vi ? ui.t_begin + warp : 0;
+    }
+    if (vi) {
+      bf16* ks_ = wsm + stage * STAGE_ELEMS;
+      bf16* vs_ = ks_ + TILE * D;
+      const int tok0 = ti * TILE;
+      const int page = ui.table_row[tok0 / p.page_size];
+      const bf16* kbase = p.kv + ((long long)page * 2 * p.page_size + (tok0 % p.page_size)) * row_stride + (long long)ui.h * D;
+#pragma unroll
+      for (int i = 0; i < (TILE * CH) / 32; ++i) {
+        const int c = lane + 32 * i;
+        const int r = c / CH, ch = c % CH;
+        const bool valid = tok0 + r < ui.kv_len;
+        const bf16* src = kbase + (valid ? r : 0) * row_stride + ch * 8;
+        cp_async16_stream(ks_ + swz<D>(r, ch), src, valid, kv_policy);
+        cp_async16_stream(vs_ + swz<D>(r, ch), src + v_plane, valid, kv_policy);
+      }
+      ti += 4;
+    }
+    cp_async_commit();  // one group per call, also when nothing was left to load
+  };
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) issue_next(s);
+
+  // compute cursor
+  DecodeUnit uc;
+  int cu = blockIdx.x;
+  bool vc = load_decode_unit(p, cu, uc);
+  int it = 0;
+  while (vc) {
+    uint32_t qf[KS][2];
+    {
+      const bf16* qh = p.q + ((long long)uc.qrow * p.hq + (long long)uc.h * G + g) * D;
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        if (g < G) {
+          qf[ks][0] = *reinterpret_cast<const uint32_t*>(qh + ks * 16 + 2 * t4);
+          qf[ks][1] = *reinterpret_cast<const uint32_t*>(qh + ks * 16 + 8 + 2 * t4);
+        } else {
+          qf[ks][0] = 0u;
+          qf[ks][1] = 0u;
+        }
+      }
+    }
+    float o[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    float m_run = NEG_BIG, l_run = 0.f;
+    for (int tile = uc.t_begin + warp; tile < uc.t_end; tile += 4, ++it) {
+      cp_async_wait<STAGES - 2>();
+      __syncwarp();
+      issue_next((it + STAGES - 1) % STAGES);
+      const bf16* ks_ = wsm + (it % STAGES) * STAGE_ELEMS;
+      const bf16* vs_ = ks_ + TILE * D;
+      float s_acc[2][4];
+#pragma unroll
+      for (int n = 0; n < 2; ++n) s_acc[n][0] = s_acc[n][1] = s_acc[n][2] = s_acc[n][3] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        const int j = lane >> 3, r = lane & 7;
+        const int row = (j >> 1) * 8 + r;
+        const int ch = ks * 2 + (j & 1);
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4(smem_u32(ks_ + swz<D>(row, ch)), b0, b1, b2, b3);
+        const uint32_t a[4] = {qf[ks][0], 0u, qf[ks][1], 0u};
+        mma16816(s_acc[0], a, b0, b1);
+        mma16816(s_acc[1], a, b2, b3);
+      }
+      float sv[4];
+      const int tok0 = tile * TILE + 2 * t4;
+      sv[0] = (tok0 < uc.kv_len) ? s_acc[0][0] * p.scale_log2 : NEG_BIG;
+      sv[1] = (tok0 + 1 < uc.kv_len) ? s_acc[0][1] * p.scale_log2 : NEG_BIG;
+      sv[2] = (tok0 + 8 < uc.kv_len) ? s_acc[1][0] * p.scale_log2 : NEG_BIG;
+      sv[3] = (tok0 + 9 < uc.kv_len) ? s_acc[1][1] * p.scale_log2 : NEG_BIG;
+      float mx = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m_run, mx);
+      const float corr = exp2f(m_run - m_new);
+      float pv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) pv[i] = sv[i] <= NEG_BIG ? 0.f : exp2f(sv[i] - m_new);
+      float ps = pv[0] + pv[1] + pv[2] + pv[3];
+      ps += __shfl_xor_sync(0xffffffffu, ps, 1);
+      ps += __shfl_xor_sync(0xffffffffu, ps, 2);
+      l_run = l_run * corr + ps;
+      m_run = m_new;
+      const uint32_t pa[4] = {pack_bf16(pv[0], pv[1]), 0u, pack_bf16(pv[2], pv[3]), 0u};
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        o[n][0] *= corr;
+        o[n][1] *= corr;
+      }
+#pragma unroll
+      for (int n2 = 0; n2 < NT / 2; ++n2) {
+        const int j = lane >> 3, r = lane & 7;
+        const int row = (j & 1) * 8 + r;
+        const int ch = n2 * 2 + (j >> 1);
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4_t(smem_u32(vs_ + swz<D>(row, ch)), b0, b1, b2, b3);
+        mma16816(o[2 * n2], pa, b0, b1);
+        mma16816(o[2 * n2 + 1], pa, b2, b3);
+      }
+    }
+    // unit done for this warp: combine the four warps (the next unit's loads stay in flight)
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      mo[(warp * 8 + g) * D + n * 8 + 2 * t4] = o[n][0];
+      mo[(warp * 8 + g) * D + n * 8 + 2 * t4 + 1] = o[n][1];
+    }
+    if (t4 == 0) {
+      mm[warp * 8 + g] = m_run;
+      ml[warp * 8 + g] = l_run;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * D; idx += 128) {
+      const int row = idx / D, d = idx % D;
+      float M = NEG_BIG;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) M = fmaxf(M, mm[w * 8 + row]);
+      float L = 0.f, O = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float f = exp2f(mm[w * 8 + row] - M);
+        L += f * ml[w * 8 + row];
+        O += f * mo[(w * 8 + row) * D + d];
+      }
+      const int hq = uc.h * G + row;
+      const float val = L > 0.f ? O / L : 0.f;
+      if (p.splits == 1) {
+        p.out[((long long)uc.qrow * p.hq + hq) * D + d] = __float2bfloat16(val);
+      } else {
+        p.part_o[(((long long)uc.b * p.hq + hq) * p.splits + uc.split) * D + d] = val;
+        if (d == 0) p.part_lse[((long long)uc.b * p.hq + hq) * p.splits + uc.split] = L > 0.f ? M + log2f(L) : NEG_BIG;
+      }
+    }
+    __syncthreads();  // the scratch is free again
+    cu += gridDim.x;
+    vc = load_decode_unit(p, cu, uc);
+  }
+  cp_async_wait<0>();
+}
+
 template <int D>
 __global__ void __launch_bounds__(128) decode_merge_kernel(const AttnParams p) {
   PG_PDL_ENTRY();
@@ -518,8 +723,38 @@ int launch_decode_s(const AttnParams& p, cudaStream_t stream) {
   return PG_OK;
 }
 
+int g_decode_persistent = -1;  // PEGAINFER_ATTN_PERSISTENT=0 selects the one-unit-per-CTA kernel
+
+template <int D>
+int launch_decode_persistent(const AttnParams& p, cudaStream_t stream) {
+  const size_t pipe = (size_t)4 * 3 * 2 * 16 * D * 2;
+  const size_t merge = (size_t)(4 * 8 * D + 64) * 4;
+  const size_t smem = pipe + merge;
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    PG_CUDA(cudaGetDevice(&dev));
+    PG_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    PG_CUDA(cudaFuncSetAttribute(decode_attn_persistent_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  }
+  const int units = p.num_seqs * p.hkv * p.splits;
+  const int slots = sms * (D <= 128 ? 2 : 1);
+  PG_CUDA(launch_pdl(decode_attn_persistent_kernel<D>, dim3(units < slots ? units : slots), dim3(128), smem, stream, p));
+  PG_LAUNCH_CHECK();
+  if (p.splits > 1) {
+    PG_CUDA(launch_pdl(decode_merge_kernel<D>, dim3((p.num_seqs * p.hq + 3) / 4), dim3(128), (size_t)(0), stream, p));
+    PG_LAUNCH_CHECK();
+  }
+  return PG_OK;
+}
+
 template <int D>
 int launch_decode(const AttnParams& p, cudaStream_t stream) {
+  if (g_decode_persistent < 0) {
+    const char* e = getenv("PEGAINFER_ATTN_PERSISTENT");
+    g_decode_persistent = (e && e[0] == '0') ? 0 : 1;
+  }
+  if (g_decode_persistent) return launch_decode_persistent<D>(p, stream);
   if (g_decode_stages == 2) return launch_decode_s<D, 2>(p, stream);
   return launch_decode_s<D, 3>(p, stream);
 }
