@@ -76,6 +76,10 @@ def build_engine(ecfg: EngineConfig, mcfg: Optional[ModelConfig] = None, device=
     device = torch.device(device)
     if dtype is None:
         dtype = torch.bfloat16 if device.type == "cuda" else torch.float32
+    if ecfg.batch_invariant and device.type == "cuda":
+        from ..ops import cuda as K
+
+        K.set_batch_invariant(True)
     if model is None:
         model = build_model(mcfg, ecfg, device, dtype, tp, ep)
     if ecfg.spec_method == "draft" and getattr(model, "draft_model", None) is None:

@@ -193,6 +193,8 @@ def linear(x, w, out_dtype=None, force_splits: int = 0, out: Optional[torch.Tens
         out = torch.empty((t, m), dtype=torch.float32 if f32 else torch.bfloat16, device=x.device)
     if t == 0:
         return out.view(*x.shape[:-1], m)
+    if _BATCH_INVARIANT and force_splits == 0:
+        force_splits = 1
     c = ctx(x.device)
     rc = lib().pg_gemm_bf16_tn(
         _ptr(x2), _ptr(w), _ptr(out), _ci(int(f32)), _ci(t), _ci(m), _ci(k), _ll(x2.stride(0)), _ll(w.stride(0)), _ll(out.stride(0)),
@@ -244,7 +246,28 @@ def qk_norm_rope_append(qkv, q_norm_w, k_norm_w, cos, sin, meta: AttnMeta, kv_la
     return (q, gate) if gated else q
 
 
+_BATCH_INVARIANT = False
+INVARIANT_KV_SPLITS = 4
+
+
+def set_batch_invariant(on: bool) -> None:
+    """Numeric policy for ``--batch-invariant`` serving: a row's result must not depend on what
+    else rides in the batch.  GEMMs run with one k-split (the k order inside a CTA is fixed and
+    independent of the token tile), decode attention uses a constant number of KV splits (the
+    split boundaries then depend on the sequence's own length only); the default policy picks
+    both from the batch shape.  Reference: pegainfer-kernels/src/ops/linear.rs NumericPolicy,
+    pegainfer-qwen3/src/lib.rs:498-548."""
+    global _BATCH_INVARIANT
+    _BATCH_INVARIANT = bool(on)
+
+
+def batch_invariant() -> bool:
+    return _BATCH_INVARIANT
+
+
 def plan_decode_splits(num_seqs: int, hkv: int, max_kv_len: int, device) -> int:
+    if _BATCH_INVARIANT:
+        return INVARIANT_KV_SPLITS
     return int(lib().pg_decode_splits(_ci(num_seqs), _ci(hkv), _ci(max(max_kv_len, 1)), _ci(ctx(device).sms)))
 
 

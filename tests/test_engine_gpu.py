@@ -172,3 +172,38 @@ def test_kimi_mtp_speculative_is_lossless_on_gpu():
     finally:
         plain.shutdown()
         spec.shutdown()
+
+
+def test_batch_invariant_policy_row_result_independent_of_batch():
+    """With the batch-invariant numeric policy a sequence decodes to bit-identical logits alone
+    and inside a larger batch (default policy: split counts follow the batch shape)."""
+    from pegainfer_b200.kv.request_kv import KvView
+    from pegainfer_b200.ops import cuda as K
+    from pegainfer_b200.sched.executor import SeqStep, build_meta
+
+    eng = engine(False, no_prefix_cache=True)
+    K.set_batch_invariant(True)
+    try:
+        ps = [p[:40 + 5 * i] for i, p in enumerate(prompts(20, seed=9))]  # 20 rows: a wider token tile than a single row gets
+        page, nxt = 16, 1
+        seqs = []
+        for i, p in enumerate(ps):
+            npg = (len(p) + 1 + page - 1) // page
+            seqs.append(SeqStep(rid=i, input_tokens=p, start_pos=0, view=KvView(list(range(nxt, nxt + npg)), len(p), page)))
+            nxt += npg
+        # prefill each sequence on its own, then decode one token alone and together
+        for sq in seqs:
+            tok, meta = build_meta([sq], page, "cuda:0")
+            eng.model.forward(tok, meta, eng.kv)
+        dec = [SeqStep(rid=s.rid, input_tokens=[11 + s.rid], start_pos=len(s.input_tokens), view=KvView(s.view.page_indices, len(s.input_tokens) + 1, page)) for s in seqs]
+        tok, meta = build_meta(dec, page, "cuda:0")
+        together = eng.model.forward(tok, meta, eng.kv).float()
+        for i, d in enumerate(dec):
+            tok1, meta1 = build_meta([d], page, "cuda:0")
+            alone = eng.model.forward(tok1, meta1, eng.kv).float()
+            assert torch.equal(alone[0], together[i]), f"row {i} differs between batch sizes 1 and {len(dec)}"
+        torch.cuda.synchronize()
+        assert K.read_status("cuda:0") == 0
+    finally:
+        K.set_batch_invariant(False)
+        eng.shutdown()
