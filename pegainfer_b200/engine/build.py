@@ -106,6 +106,7 @@ def build_engine(ecfg: EngineConfig, mcfg: Optional[ModelConfig] = None, device=
         max_model_len=max_len,
         eos_token_ids=tuple(mcfg.eos_token_ids),
         batch_invariant=ecfg.batch_invariant,
+        decode_overlap=ecfg.decode_overlap and tp.world == 1,
         vocab_size=mcfg.vocab_size,
     )
     host_tier = None

@@ -49,16 +49,34 @@ class _DeviceCtx:
 
 
 _CTX: dict = {}
+_LANE = [0]  # 1 while ops are being queued on the prefill lane (second stream)
+
+
+class lane_scratch:
+    """Ops launched inside this block use a second set of per-device scratch buffers (split-K
+    workspace and counters, attention partials, argmax scratch), because they run on another
+    stream concurrently with ops that use the first set.  The status word is shared."""
+
+    def __enter__(self):
+        _LANE[0] += 1
+
+    def __exit__(self, *exc):
+        _LANE[0] -= 1
 
 
 def ctx(device) -> _DeviceCtx:
     device = torch.device(device)
     idx = device.index if device.index is not None else torch.cuda.current_device()
-    c = _CTX.get(idx)
+    key = (idx, 1 if _LANE[0] else 0)
+    c = _CTX.get(key)
     if c is None:
         with torch.cuda.device(idx):
             c = _DeviceCtx(torch.device("cuda", idx))
-        _CTX[idx] = c
+        if key[1]:  # one status word per device
+            main = _CTX.get((idx, 0))
+            if main is not None:
+                c.status = main.status
+        _CTX[key] = c
     return c
 
 

@@ -161,6 +161,7 @@ class TorchExecutor(ModelExecutor):
         self.max_decode_batch = max_decode_batch
         self.max_blocks_per_seq = max_blocks_per_seq
         self.mtp = None  # set by spec.MtpSpec
+        self._lane_stream = None  # second stream of the decode-overlap prefill lane
         self._graphs = None
         if self.use_graph:
             from ..utils.cuda_graph import DecodeGraphs
@@ -231,6 +232,60 @@ class TorchExecutor(ModelExecutor):
         if self.mtp is not None:
             self._mtp_drafts(seqs, meta, res)
         res.elapsed_s = time.perf_counter() - t0
+        return res
+
+    # -- prefill lane (decode overlap) -----------------------------------------------
+    def launch_async(self, batch: StepBatch):
+        """Start a prompt-chunk batch on the executor's second CUDA stream and return without
+        waiting: the forward pass, the greedy pick of every sampled row and the copy of the
+        picked tokens into pinned memory are queued behind each other on that stream, followed
+        by an event.  Decode steps keep running on the main stream meanwhile (shared SMs).
+        On CPU the batch simply runs here and now.  Reference: pegainfer-qwen3
+        src/executor.rs:490-589 (decode-overlap prefill lane, polled through an event)."""
+        if self.device.type != "cuda":
+            return ("done", self.execute(batch))
+        self.steps += 1
+        if self._lane_stream is None:
+            self._lane_stream = torch.cuda.Stream(self.device)
+        lane = self._lane_stream
+        lane.wait_stream(torch.cuda.current_stream(self.device))
+        seqs = batch.seqs
+        from ..ops import cuda as K
+
+        with torch.cuda.stream(lane), K.lane_scratch():
+            token_ids, meta = build_meta(seqs, self.page_size, self.device, pinned=True)
+            self.prepare_meta(seqs, meta)
+            hidden = self.model.forward_hidden(token_ids, meta, self.kv)
+            rows, owners = [], []
+            for i, s in enumerate(seqs):
+                if s.sample:
+                    rows.append(meta.h_q_indptr[i + 1] - 1)
+                    owners.append(s.rid)
+            host = None
+            keep = [token_ids, meta, hidden]
+            if rows:
+                idx = torch.tensor(rows, dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
+                toks = ops.argmax(self.model.logits(hidden, idx))
+                host = torch.empty(len(rows), dtype=toks.dtype).pin_memory()
+                host.copy_(toks, non_blocking=True)
+                keep += [idx, toks]
+            ev = torch.cuda.Event()
+            ev.record(lane)
+        return ("cuda", ev, owners, host, keep)
+
+    def finish_async(self, pending, wait: bool = False) -> Optional[StepResult]:
+        """The result of ``launch_async`` once its event has fired (``None`` before that)."""
+        if pending[0] == "done":
+            return pending[1]
+        _, ev, owners, host, _keep = pending
+        if wait:
+            ev.synchronize()
+        elif not ev.query():
+            return None
+        res = StepResult()
+        if host is not None:
+            for rid, tok in zip(owners, host.tolist()):
+                res.tokens[rid] = [tok]
         return res
 
     def _mtp_drafts(self, seqs, meta, res: StepResult) -> None:

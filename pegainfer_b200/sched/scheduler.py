@@ -48,10 +48,11 @@ class SchedulerConfig:
     eos_token_ids: tuple = ()
     batch_invariant: bool = False
     vocab_size: int = 0
+    decode_overlap: bool = False  # prompt chunks run on a second stream while decode steps continue
 
 
 class _Running:
-    __slots__ = ("q", "kv", "prefill_pos", "out_tokens", "step_index", "phase", "echo_done", "t_first", "spec_ready", "lora_slot", "state_slot", "report_cached", "spec_state")
+    __slots__ = ("q", "kv", "prefill_pos", "out_tokens", "step_index", "phase", "echo_done", "t_first", "spec_ready", "lora_slot", "state_slot", "report_cached", "spec_state", "inflight")
 
     def __init__(self, q: QueuedRequest, kv: RequestKv):
         self.q = q
@@ -67,6 +68,7 @@ class _Running:
         self.state_slot = -1
         self.report_cached = None
         self.spec_state = None
+        self.inflight = False  # a prompt chunk of this request is executing on the prefill lane
 
 
 def plan_kind(has_prefill: bool, has_decode: bool, spec_ready: bool) -> Optional[str]:
@@ -86,6 +88,8 @@ class ContinuousScheduler:
         self.pool = pool
         self.cfg = cfg
         self.spec = spec
+        self._lane = None  # (chunks, pending) of the prompt chunks running on the executor's second stream
+        self.overlapped_chunks = 0
         self.host_tier = host_tier
         self.lora = lora_registry
         self.tracer = tracer
@@ -203,7 +207,7 @@ class ContinuousScheduler:
                 self.tracer.finish(r.q)
 
     def _reap_aborted(self, ledger) -> None:
-        for rid in [rid for rid, r in self.running.items() if r.q.is_aborted()]:
+        for rid in [rid for rid, r in self.running.items() if r.q.is_aborted() and not r.inflight]:  # pages of an in-flight chunk are still being written
             ledger.finish(rid, FinishReason.ABORT)
             self._retire(rid)
         for rid in [rid for rid, q in self.parked.items() if q.is_aborted()]:
@@ -218,7 +222,7 @@ class ContinuousScheduler:
         budget = self.cfg.max_prefill_tokens
         out = []
         for r in self.running.values():
-            if r.phase != "prefill" or budget <= 0:
+            if r.phase != "prefill" or budget <= 0 or r.inflight:
                 continue
             if r.prefill_pos == 0 and r.kv.committed == 0 and not r.kv.blocks:
                 cached = r.kv.match_and_add_prefix() if (self.spec is None or self.spec.allows_prefix_cache) else 0
@@ -235,43 +239,126 @@ class ContinuousScheduler:
         return out
 
     # -- step ----------------------------------------------------------------------
+    def _chunk_steps(self, chunks) -> list:
+        """Schedule the KV of every chunk and describe it as executor input."""
+        seqs = []
+        for r, n in chunks:
+            r.kv.schedule_prefill(n)
+            last = r.prefill_pos + n == r.kv.prompt_len
+            seqs.append(
+                SeqStep(
+                    rid=r.q.id,
+                    input_tokens=r.kv.tokens[r.prefill_pos : r.prefill_pos + n],
+                    start_pos=r.prefill_pos,
+                    view=r.kv.view(),
+                    sample=last,
+                    params=r.q.request.params,
+                    step_index=0,
+                    logprobs=r.q.request.logprobs if last else 0,
+                    lora_slot=r.lora_slot,
+                    fresh_state=r.prefill_pos == 0,
+                    next_token=-1 if last else r.kv.tokens[r.prefill_pos + n],
+                )
+            )
+        return seqs
+
+    def _resolve_chunks(self, chunks, result, ledger) -> None:
+        for r, n in chunks:
+            rid = r.q.id
+            if rid not in self.running:
+                continue
+            r.kv.apply_prefill_chunk()
+            if r.report_cached is not None:  # once, with the first chunk
+                ledger.report_cached_tokens(rid, r.report_cached)
+                r.report_cached = None
+            r.prefill_pos += n
+            if r.prefill_pos == r.kv.prompt_len:
+                r.phase = "decode"
+                if self.tracer:
+                    self.tracer.enter_decode(r.q)
+                if r.q.request.echo and not r.echo_done:
+                    ledger.push_prompt_echo(rid, PromptEcho(tokens=list(r.q.request.prompt_tokens), logprobs=[None] * r.kv.prompt_len))
+                    r.echo_done = True
+                tok = result.tokens[rid][0]
+                lp = result.logprobs.get(rid)
+                r.spec_state = result.drafts.get(rid)
+                self._resolve_token(r, tok, lp[0] if lp else None, ledger, first=True)
+            if self.host_tier is not None and rid in self.running:
+                self.host_tier.on_blocks_sealed(r, self)
+
+    # -- prefill lane (decode overlap) ---------------------------------------------
+    def _poll_lane(self, ledger, wait: bool = False) -> None:
+        """Collect the prompt chunks that were running beside the decode steps, if they are done."""
+        if self._lane is None:
+            return
+        chunks, pending = self._lane
+        try:
+            result = self.ex.finish_async(pending, wait=wait)
+        except Exception as exc:
+            self._lane = None
+            self.failed_batches += 1
+            for r, _ in chunks:
+                r.inflight = False
+            self._fail_batch([r for r, _ in chunks], ledger, f"step failed: {exc!r}")
+            return
+        if result is None:
+            return
+        self._lane = None
+        for r, _ in chunks:
+            r.inflight = False
+        self._resolve_chunks(chunks, result, ledger)
+
+    def _lane_accepts(self, chunks) -> bool:
+        # the lane samples greedily on the device and returns tokens only
+        for r, n in chunks:
+            req = r.q.request
+            if r.lora_slot >= 0 or req.logprobs or not req.params.effectively_greedy(self.cfg.vocab_size or (1 << 30)):
+                return False
+        return hasattr(self.ex, "launch_async")
+
+    # -- step ----------------------------------------------------------------------
     def step(self, ledger) -> bool:
         self.steps += 1
+        self._poll_lane(ledger)
         self._reap_aborted(ledger)
         if self.host_tier is not None:
             self.host_tier.poll(self)
             self._unpark_ready()
         self._admit(ledger)
-        chunks = self.take_prefill_chunks()
+        chunks = self.take_prefill_chunks() if self._lane is None else []  # one set of chunks on the lane at a time
         decoders = [r for r in self.running.values() if r.phase == "decode"]
+        if self._lane is not None and not decoders:
+            self._poll_lane(ledger, wait=True)  # nothing to overlap with: wait for the lane
+            return True
+        if self.cfg.decode_overlap and chunks and decoders and self.spec is None and self._lane_accepts(chunks):
+            # Decode overlap: the prompt chunks go to the executor's second stream and this step
+            # continues as a pure decode step, so running requests keep their token cadence while
+            # a long prompt is being processed.
+            try:
+                pending = self.ex.launch_async(StepBatch(seqs=self._chunk_steps(chunks), kind="prefill"))
+            except OutOfBlocks as exc:
+                self._fail_batch([r for r, _ in chunks], ledger, f"KV pool exhausted: {exc}")
+                return True
+            except Exception as exc:
+                self.failed_batches += 1
+                self._fail_batch([r for r, _ in chunks], ledger, f"step failed: {exc!r}")
+                return True
+            for r, _ in chunks:
+                r.inflight = True
+            self._lane = (chunks, pending)
+            self.overlapped_chunks += len(chunks)
+            chunks = []
         spec_ready = self.spec is not None and bool(decoders) and not chunks and all(self.spec.ready(r) for r in decoders)
         kind = plan_kind(bool(chunks), bool(decoders), spec_ready)
         if kind is None:
-            return False
+            return self._lane is not None
         if kind == "spec":
             self._run_spec(decoders, ledger)
             return True
         seqs, touched = [], []
         try:
-            for r, n in chunks:
-                r.kv.schedule_prefill(n)
-                last = r.prefill_pos + n == r.kv.prompt_len
-                seqs.append(
-                    SeqStep(
-                        rid=r.q.id,
-                        input_tokens=r.kv.tokens[r.prefill_pos : r.prefill_pos + n],
-                        start_pos=r.prefill_pos,
-                        view=r.kv.view(),
-                        sample=last,
-                        params=r.q.request.params,
-                        step_index=0,
-                        logprobs=r.q.request.logprobs if last else 0,
-                        lora_slot=r.lora_slot,
-                        fresh_state=r.prefill_pos == 0,
-                        next_token=-1 if last else r.kv.tokens[r.prefill_pos + n],
-                    )
-                )
-                touched.append(r)
+            seqs.extend(self._chunk_steps(chunks))
+            touched.extend(r for r, _ in chunks)
             for r in decoders:
                 r.kv.schedule_decode()
                 seqs.append(
@@ -298,26 +385,7 @@ class ContinuousScheduler:
             self._fail_batch(touched, ledger, f"step failed: {exc!r}")
             return True
         # resolve
-        for r, n in chunks:
-            rid = r.q.id
-            r.kv.apply_prefill_chunk()
-            if r.report_cached is not None:  # once, with the first chunk
-                ledger.report_cached_tokens(rid, r.report_cached)
-                r.report_cached = None
-            r.prefill_pos += n
-            if r.prefill_pos == r.kv.prompt_len:
-                r.phase = "decode"
-                if self.tracer:
-                    self.tracer.enter_decode(r.q)
-                if r.q.request.echo and not r.echo_done:
-                    ledger.push_prompt_echo(rid, PromptEcho(tokens=list(r.q.request.prompt_tokens), logprobs=[None] * r.kv.prompt_len))
-                    r.echo_done = True
-                tok = result.tokens[rid][0]
-                lp = result.logprobs.get(rid)
-                r.spec_state = result.drafts.get(rid)
-                self._resolve_token(r, tok, lp[0] if lp else None, ledger, first=True)
-            if self.host_tier is not None and rid in self.running:
-                self.host_tier.on_blocks_sealed(r, self)
+        self._resolve_chunks(chunks, result, ledger)
         for r in decoders:
             rid = r.q.id
             if rid not in self.running:

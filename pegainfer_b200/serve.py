@@ -50,6 +50,9 @@ def _qwen3_validate(ns, provided):
         log.warning("LoRA requests run outside CUDA graphs; graph replay stays on for adapter-free batches")
     if ns.decode_overlap and ns.tp_size > 1:
         raise SystemExit("--decode-overlap is not available together with tensor parallelism")
+    if "decode_sm_pct" in provided:
+        # the overlap lane shares the SMs between its two streams; a fixed SM split (green contexts) is not built
+        raise SystemExit("--decode-sm-pct is not supported: --decode-overlap runs prefill and decode on two streams that share the SMs")
 
 
 LINES = [

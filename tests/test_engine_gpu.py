@@ -13,7 +13,8 @@ pytestmark = pytest.mark.gpu
 
 def engine(cuda_graph, **kw):
     mcfg = preset("qwen3-0.6b", num_layers=3, vocab_size=8192)
-    ecfg = EngineConfig(preset="qwen3-0.6b", num_kv_blocks=512, cuda_graph=cuda_graph, max_decode_batch=16, max_model_len=1024, max_prefill_tokens=256, **kw)
+    kw.setdefault("max_prefill_tokens", 256)
+    ecfg = EngineConfig(preset="qwen3-0.6b", num_kv_blocks=512, cuda_graph=cuda_graph, max_decode_batch=16, max_model_len=1024, **kw)
     return build_engine(ecfg, mcfg, device="cuda:0", dtype=torch.bfloat16)
 
 
@@ -207,3 +208,42 @@ def test_batch_invariant_policy_row_result_independent_of_batch():
     finally:
         K.set_batch_invariant(False)
         eng.shutdown()
+
+
+def test_decode_overlap_second_stream_matches_plain_engine():
+    """Prompt chunks on the prefill lane (second stream, own scratch buffers) while CUDA-graph decode
+    steps continue: same tokens as the plain engine, and the lane was really used."""
+    import time
+
+    from pegainfer_b200.engine.contract import Request
+
+    ps = prompts(6, seed=13)
+
+    def run(**kw):
+        eng = engine(True, no_prefix_cache=True, **kw)
+        try:
+            streams = []
+            for i, p in enumerate(ps):
+                streams.append(eng.submit(Request(prompt_tokens=p, params=SamplingParams(temperature=0.0, ignore_eos=True), max_tokens=24)))
+                if i in (1, 3):
+                    time.sleep(0.05)  # later prompts arrive while the first ones decode
+            outs = [s.collect(120)[0] for s in streams]
+            torch.cuda.synchronize()
+            from pegainfer_b200.ops import cuda as K
+
+            assert K.read_status("cuda:0") == 0
+            return outs, eng.scheduler.overlapped_chunks
+        finally:
+            eng.shutdown()
+
+    # batch-invariant numerics: a unified step (chunk + decode rows in one GEMM) and the overlapped
+    # form (two GEMMs) then give bit-identical rows, so the tokens can be compared exactly
+    from pegainfer_b200.ops import cuda as K
+
+    try:
+        plain, n0 = run(max_prefill_tokens=64, batch_invariant=True)
+        over, n1 = run(decode_overlap=True, max_prefill_tokens=64, batch_invariant=True)
+    finally:
+        K.set_batch_invariant(False)
+    assert n0 == 0 and n1 > 0
+    assert over == plain

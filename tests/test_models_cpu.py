@@ -119,3 +119,13 @@ def test_fp8_block_scaled_experts_run_and_match_dequantised_reference():
             eng.shutdown()
 
     assert run(512) == run(16)
+
+
+def test_decode_overlap_prefill_lane_keeps_outputs():
+    """With decode overlap, prompt chunks of later requests run on the prefill lane while earlier
+    requests keep decoding; the generated tokens are the same as without it."""
+    ps = prompts_for(4, 30, seed=8)
+    plain, _ = gen("tiny-qwen3", ps, 10, max_prefill_tokens=24)
+    over, eng = gen("tiny-qwen3", ps, 10, max_prefill_tokens=24, decode_overlap=True)
+    assert over == plain
+    assert eng.scheduler.overlapped_chunks > 0
