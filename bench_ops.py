@@ -57,7 +57,7 @@ def time_graph(fn, n_variants, iters, reps=5):
     return best
 
 
-def gemm_case(t, m, k, iters, lib=False):
+def gemm_case(t, m, k, iters, lib=False, mode="auto"):
     from pegainfer_b200.ops import cuda as K
 
     nvar = max(2, min(16, int(300e6 // (m * k * 2)) + 1))
@@ -66,6 +66,10 @@ def gemm_case(t, m, k, iters, lib=False):
     out = torch.empty(t, m, device=DEV, dtype=torch.bfloat16)
     if lib:
         fn = lambda i: torch.nn.functional.linear(x, ws[i])
+    elif mode == "one_cta":  # a pinned split count keeps the problem on the one-CTA kernel
+        fn = lambda i: K.linear(x, ws[i], out=out, force_splits=1)
+    elif mode == "two_sm":
+        fn = lambda i: K.linear_2sm(x, ws[i])
     else:
         fn = lambda i: K.linear(x, ws[i], out=out)
     ms = time_graph(fn, nvar, iters)
@@ -282,8 +286,8 @@ def main():
     if args.single:
         kind, shape = args.single.split(":")
         dims = [int(v) for v in shape.split("x")]
-        if kind == "gemm":
-            ms, by, fl = gemm_case(*dims, iters=args.iters)
+        if kind in ("gemm", "gemm2sm", "gemm1cta"):
+            ms, by, fl = gemm_case(*dims, iters=args.iters, mode={"gemm": "auto", "gemm2sm": "two_sm", "gemm1cta": "one_cta"}[kind])
         elif kind == "gdn":
             name, ms, by, fl = gdn_cases(args.iters, only=[("single", [dims[1]] * dims[0])])[0]
         elif kind == "attn":
@@ -298,6 +302,12 @@ def main():
             for t, m, k in shapes:
                 ms, by, fl = gemm_case(t, m, k, args.iters)
                 rows.append((f"gemm T{t} M{m} K{k}", ms, by, fl))
+                if t >= 256:
+                    ms1, _, _ = gemm_case(t, m, k, args.iters, mode="one_cta")
+                    rows.append((f"  one-CTA kernel T{t} M{m} K{k}", ms1, by, fl))
+                    if t < 512:
+                        ms2, _, _ = gemm_case(t, m, k, args.iters, mode="two_sm")
+                        rows.append((f"  two-SM kernel T{t} M{m} K{k}", ms2, by, fl))
                 if args.library:
                     ms2, _, _ = gemm_case(t, m, k, args.iters, lib=True)
                     rows.append((f"  cuBLAS T{t} M{m} K{k}", ms2, by, fl))

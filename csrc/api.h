@@ -42,6 +42,11 @@ int pg_symm_free(void* p);
 int pg_ipc_export(void* p, void* handle64);
 int pg_ipc_import(const void* handle64, void** out);
 int pg_ipc_close(void* p);
+// Two-SM (cta_group::2) bf16 GEMM for tensor-bound problems (gemm2sm_sm100.cu); pg_gemm_bf16_tn
+// routes eligible problems to it (PEGAINFER_GEMM_2SM=0 turns that off).
+int pg_gemm2sm_eligible(int T, int M, int K);
+int pg_gemm2sm_bf16_tn(const void* x, const void* w, void* y, int T, int M, int K, long long ldx, long long ldw, long long ldy, void* status,
+                       cudaStream_t stream);
 int pg_make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, long long rows, long long cols, long long ld, int box_rows, int box_cols);
 
 // ---- row kernels (elementwise.cu) --------------------------------------------------
@@ -108,7 +113,9 @@ int pg_decode_splits(int num_seqs, int hkv, int max_kv_len, int sms);
 void pg_attn_set_decode_stages(int stages);  // 2 (three CTAs per SM) or 3 (two CTAs per SM, default)
 int pg_paged_attention(const void* q, const void* kv, void* out, const void* q_indptr, const void* kv_lens, const void* table, int table_stride,
                        int num_seqs, int hq, int hkv, int dim, int page_size, long long num_pages, float scale, int mode, int splits,
-                       void* part_o, void* part_lse, int q_tiles, int window, void* status, cudaStream_t stream);
+                       void* part_o, void* part_lse, int q_tiles, int window, void* status, void* merge_counters, cudaStream_t stream);
+// merge_counters: B * Hkv zeroed uint32 (left zero by every launch) lets the persistent decode kernel merge the KV
+// splits itself; nullptr runs the separate merge kernel.
 
 // ---- sampling (sampling.cu) --------------------------------------------------------
 long long pg_argmax_scratch_bytes(int rows, int vocab);

@@ -1091,6 +1091,9 @@ extern "C" void pg_tp_set_timing(void* buf) { g_tp_timing = (unsigned long long*
 extern "C" int pg_gemm_bf16_tn(const void* x, const void* w, void* y, int y_is_f32, int T, int M, int K, long long ldx, long long ldw,
                                long long ldy, void* ws, long long ws_bytes, void* counters, long long counter_bytes, void* status,
                                int force_splits, cudaStream_t stream) {
+  // tensor-bound problems go to the two-SM kernel; a pinned split count (batch-invariant
+  // serving) keeps every problem size on this one kernel
+  if (!y_is_f32 && force_splits <= 0 && pg_gemm2sm_eligible(T, M, K)) return pg_gemm2sm_bf16_tn(x, w, y, T, M, K, ldx, ldw, ldy, status, stream);
   return gemm_impl(x, w, y, y_is_f32, T, M, K, ldx, ldw, ldy, ws, ws_bytes, counters, counter_bytes, status, force_splits, nullptr, nullptr, stream);
 }
 

@@ -299,6 +299,7 @@ class EngineConfig:
     max_model_len: Optional[int] = None
     batch_invariant: bool = False
     decode_overlap: bool = False
+    run_ahead: bool = True  # greedy graph decode launches the next step before reading this one's tokens
     decode_sm_pct: int = 50
     enable_lora: bool = False
     max_loras: int = 4

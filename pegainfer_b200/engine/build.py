@@ -107,6 +107,9 @@ def build_engine(ecfg: EngineConfig, mcfg: Optional[ModelConfig] = None, device=
         eos_token_ids=tuple(mcfg.eos_token_ids),
         batch_invariant=ecfg.batch_invariant,
         decode_overlap=ecfg.decode_overlap and tp.world == 1,
+        # ranks of a DP+EP group run different batches but must launch the same number of steps, so
+        # only single-GPU and replicated (TP) schedulers may launch ahead
+        run_ahead=ecfg.run_ahead and device.type == "cuda" and ep is None and not ecfg.kv_offload,
         vocab_size=mcfg.vocab_size,
     )
     host_tier = None

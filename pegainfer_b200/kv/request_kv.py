@@ -94,9 +94,9 @@ class RequestKv:
     def blocks_needed(self, new_tokens: int) -> int:
         return max(0, blocks_for(self.committed + new_tokens, self.bs) - len(self.blocks))
 
-    def _schedule(self, n: int) -> None:
+    def _schedule(self, n: int, lookahead: int = 0) -> None:
         assert self.scheduled == self.committed, "previous schedule not applied or reverted"
-        need = self.blocks_needed(n)
+        need = self.blocks_needed(n + lookahead)
         new = self.pool.allocate(need) if need else []
         self.blocks.extend(new)
         self._sched_new_blocks = new
@@ -106,8 +106,10 @@ class RequestKv:
         assert self.committed + n <= self.prompt_len
         self._schedule(n)
 
-    def schedule_decode(self) -> None:
-        self._schedule(1)
+    def schedule_decode(self, lookahead: int = 0) -> None:
+        """Pages for the token fed this step; with ``lookahead`` also for that many positions
+        after it, so that the following step can be launched before this one is applied."""
+        self._schedule(1, lookahead)
 
     def schedule_speculative(self, k: int) -> None:
         self._schedule(k)

@@ -51,12 +51,15 @@ class SeqStep:
     state_slot: int = -1  # recurrent-state slot (hybrid models)
     next_token: int = -1  # token following the last input row when it is known (non-final prefill chunk)
     fresh_state: bool = False
+    table_pages: Optional[list] = None  # decode run-ahead: the request's pages including the one for the next position
+    final: bool = False  # decode run-ahead: this step's token is the request's last (length limit)
 
 
 @dataclass
 class StepBatch:
     seqs: list
     kind: str = "unified"  # prefill | decode | unified | verify
+    run_ahead: bool = False  # a greedy graph decode step may launch the following step before it returns
 
     @property
     def num_tokens(self) -> int:
@@ -185,15 +188,41 @@ class TorchExecutor(ModelExecutor):
             lps = batch_logprobs(logits, toks, want_lp)
         return toks, lps
 
+    @property
+    def supports_run_ahead(self) -> bool:
+        return self._graphs is not None and self.mtp is None and not self._graphs.uses_state
+
+    def _graph_decode(self, batch: StepBatch) -> bool:
+        seqs = batch.seqs
+        return self._graphs is not None and self.mtp is None and batch.is_decode() and len(seqs) <= self.max_decode_batch and all(s.sample and s.logprobs == 0 and s.lora_slot < 0 for s in seqs)
+
     def execute(self, batch: StepBatch) -> StepResult:
+        g = self._graphs
+        if g is not None and g.pending is not None:
+            # A decode step is already running ahead.  If it is exactly this batch the graph
+            # path below picks it up; otherwise (a prompt chunk came along, a request joined,
+            # sampling changed) take the rows it did compute and run only the rest.
+            seqs = batch.seqs
+            whole = self._graph_decode(batch) and all(g.covers(s) for s in seqs) and all(s.params.effectively_greedy(self.vocab_size) for s in seqs)
+            if not whole:
+                claimed = g.claim(seqs)
+                if claimed:
+                    rest = [s for s in seqs if s.rid not in claimed]
+                    res = self._execute(StepBatch(seqs=rest, kind=batch.kind)) if rest else StepResult()
+                    for rid, tok in claimed.items():
+                        res.tokens[rid] = [tok]
+                    return res
+        return self._execute(batch)
+
+    def _execute(self, batch: StepBatch) -> StepResult:
         t0 = time.perf_counter()
         self.steps += 1
         seqs = batch.seqs
-        if self._graphs is not None and self.mtp is None and batch.is_decode() and len(seqs) <= self.max_decode_batch and all(s.sample and s.logprobs == 0 and s.lora_slot < 0 for s in seqs):
+        if self._graph_decode(batch):
             all_greedy = all(s.params.effectively_greedy(self.vocab_size) for s in seqs)
-            out = self._graphs.run(seqs, greedy=all_greedy)
+            out = self._graphs.run(seqs, greedy=all_greedy, ahead=batch.run_ahead and all_greedy)
             if all_greedy:
-                toks = out.tolist()
+                toks = out
             else:
                 toks, _ = self._sample(out[: len(seqs)], seqs, [1] * len(seqs))
                 toks = toks.tolist()

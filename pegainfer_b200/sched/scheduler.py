@@ -49,6 +49,7 @@ class SchedulerConfig:
     batch_invariant: bool = False
     vocab_size: int = 0
     decode_overlap: bool = False  # prompt chunks run on a second stream while decode steps continue
+    run_ahead: bool = False  # a decode step launches the following one before its tokens are read
 
 
 class _Running:
@@ -89,6 +90,7 @@ class ContinuousScheduler:
         self.cfg = cfg
         self.spec = spec
         self._lane = None  # (chunks, pending) of the prompt chunks running on the executor's second stream
+        self._ahead = bool(cfg.run_ahead) and spec is None and bool(getattr(executor, "supports_run_ahead", False))
         self.overlapped_chunks = 0
         self.host_tier = host_tier
         self.lora = lora_registry
@@ -359,8 +361,12 @@ class ContinuousScheduler:
         try:
             seqs.extend(self._chunk_steps(chunks))
             touched.extend(r for r, _ in chunks)
+            ahead = self._ahead
             for r in decoders:
-                r.kv.schedule_decode()
+                # run-ahead: the page of the next position exists before this step is applied, and a
+                # request whose length limit this step reaches is marked so nothing runs ahead for it
+                final = ahead and (r.out_tokens + 1 >= r.q.request.max_tokens or r.kv.committed + 2 >= self.cfg.max_model_len)
+                r.kv.schedule_decode(1 if ahead and not final else 0)
                 seqs.append(
                     SeqStep(
                         rid=r.q.id,
@@ -372,6 +378,8 @@ class ContinuousScheduler:
                         step_index=r.step_index,
                         logprobs=r.q.request.logprobs,
                         lora_slot=r.lora_slot,
+                        table_pages=r.kv.blocks if ahead else None,
+                        final=final,
                     )
                 )
                 touched.append(r)
@@ -379,7 +387,7 @@ class ContinuousScheduler:
             self._fail_batch(touched, ledger, f"KV pool exhausted: {exc}")
             return True
         try:
-            result = self.ex.execute(StepBatch(seqs=seqs, kind=kind))
+            result = self.ex.execute(StepBatch(seqs=seqs, kind=kind, run_ahead=self._ahead and kind == "decode"))
         except Exception as exc:
             self.failed_batches += 1
             self._fail_batch(touched, ledger, f"step failed: {exc!r}")

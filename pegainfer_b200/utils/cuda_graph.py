@@ -6,6 +6,16 @@ page 0 with ``kv_len == 0`` so they attend to nothing and their KV write lands i
 reserved padding page.  The greedy variant captures the argmax too, so a replay
 yields token ids directly.  ``dump_dot`` writes the captured graph as Graphviz text.
 
+Run-ahead: a greedy decode step can be followed at once by the launch of the NEXT step,
+before the host has read this step's tokens.  The next step's positions, slots and KV
+lengths are known on the host (every sequence advances by one; its next page is already
+in the block table), and its input tokens are gathered on the device from the tokens the
+running step is about to write.  The scheduler's host work between two steps then
+overlaps the GPU work of the step that is already running.  A sequence that turns out to
+have finished just wastes its row of the step that ran ahead; a step whose rows nobody
+claims is dropped, its only side effect being KV written at positions that are not yet
+committed.
+
 Reference parity: pegainfer-core/src/cuda_graph.rs:42-234 (capture / replay state),
 pegainfer-qwen3/src/batch_decode.rs:99-167 (bucket padding, graph per bucket and
 attention path), pegainfer-core/src/cuda_graph/dump.rs:24-135 (DOT export).
@@ -28,6 +38,19 @@ def _K():
     return cuda
 
 
+class _InFlight:
+    """A decode step that has been launched: where each request's token will appear."""
+
+    __slots__ = ("rows", "pos", "event", "host", "n")
+
+    def __init__(self, rows, pos, event, host, n):
+        self.rows = rows  # rid -> row of the step
+        self.pos = pos  # rid -> position of the token the step feeds
+        self.event = event
+        self.host = host  # pinned int32 buffer the tokens are copied into
+        self.n = n
+
+
 class DecodeGraphs:
     def __init__(self, executor, max_batch: int, max_blocks_per_seq: int):
         from ..sched.executor import DECODE_BUCKETS, bucket_for
@@ -39,9 +62,9 @@ class DecodeGraphs:
         self.width = max(max_blocks_per_seq, 1)
         self.page_size = executor.page_size
         B, W, dev = self.max_b, self.width, self.device
-        # one int32 arena: tokens | positions | slots | kv_lens, mirrored in pinned memory
-        self.h_small = torch.zeros(4 * B, dtype=torch.int32).pin_memory()
-        self.d_small = torch.zeros(4 * B, dtype=torch.int32, device=dev)
+        # one int32 arena: tokens | positions | slots | kv_lens | source rows (run-ahead), mirrored in pinned memory
+        self.h_small = torch.zeros(5 * B, dtype=torch.int32).pin_memory()
+        self.d_small = torch.zeros(5 * B, dtype=torch.int32, device=dev)
         self.h_table = torch.zeros((B, W), dtype=torch.int32).pin_memory()
         self.d_table = torch.zeros((B, W), dtype=torch.int32, device=dev)
         self.np_small = self.h_small.numpy()
@@ -52,6 +75,11 @@ class DecodeGraphs:
         self.d_slots = torch.zeros(B, dtype=torch.int32, device=dev)
         self.uses_state = hasattr(executor.model, "rec")
         self.h_out = torch.zeros(B, dtype=torch.int32).pin_memory()
+        self.h_out2 = torch.zeros(B, dtype=torch.int32).pin_memory()
+        self.pending: Optional[_InFlight] = None  # the step that is running ahead, if any
+        self._staged = None  # event behind the last host->device copies out of the pinned mirrors
+        self.ahead_launches = 0
+        self.ahead_claimed = 0
         self.graphs: dict = {}
         self.logits: dict = {}
         self.pool = None
@@ -146,9 +174,12 @@ class DecodeGraphs:
         torch.cuda.synchronize(self.device)
         return n
 
-    def stage(self, seqs, b: int) -> None:
+    def stage(self, seqs, b: int, ahead_of: Optional[_InFlight] = None) -> None:
         """Fill the pinned mirrors for ``seqs`` padded to bucket ``b`` and start the
-        host->device copies on the current stream."""
+        host->device copies on the current stream.  With ``ahead_of`` the step fed is the
+        one AFTER ``seqs``' own (every position one further) and the input tokens do not
+        come from the host: they are gathered on the device from the rows of the step
+        ``ahead_of`` that is still running."""
         n = len(seqs)
         B = self.max_b
         sm, tb = self.np_small, self.np_table
@@ -156,11 +187,14 @@ class DecodeGraphs:
         rows = self._row_state  # per table row: (request id, pages already written): a decode step adds at most one page
         dirty = False
         ps = self.page_size
+        adv = 0 if ahead_of is None else 1
+        if self._staged is not None:
+            self._staged.synchronize()  # the previous copies have read the mirrors (long done in practice)
         toks, poss, slots = [0] * n, [0] * n, [0] * n
         for i, s in enumerate(seqs):
-            pos = s.start_pos
-            pages = s.view.page_indices
-            toks[i] = s.input_tokens[0]
+            pos = s.start_pos + adv
+            pages = s.table_pages if s.table_pages is not None else s.view.page_indices
+            toks[i] = ahead_of.rows[s.rid] if adv else s.input_tokens[0]
             poss[i] = pos
             slots[i] = pages[pos // ps] * ps + pos % ps
             np_ = len(pages)
@@ -175,13 +209,14 @@ class DecodeGraphs:
                 dirty = True
             if np_ > wmax:
                 wmax = np_
-        sm[:n] = toks
+        t0 = 4 * B if adv else 0  # run-ahead: the list holds source rows, not tokens
+        sm[t0 : t0 + n] = toks
         sm[B : B + n] = poss
         sm[2 * B : 2 * B + n] = slots
         sm[3 * B : 3 * B + n] = poss
         sm[3 * B : 3 * B + n] += 1
         if n < b:
-            sm[n:b] = 0
+            sm[t0 + n : t0 + b] = 0
             sm[B + n : B + b] = 0
             sm[2 * B + n : 2 * B + b] = 0
             sm[3 * B + n : 3 * B + b] = 0
@@ -191,32 +226,102 @@ class DecodeGraphs:
                 hs[i] = self.ex.model.rec.slot_for(s.rid, False)
             hs[n:b] = 0
             self.d_slots.copy_(self.h_slots, non_blocking=True)
-        self.d_small.copy_(self.h_small, non_blocking=True)
-        self.h2d_bytes += self.h_small.numel() * 4
+        if adv:
+            self.d_small[B:].copy_(self.h_small[B:], non_blocking=True)
+            self.h2d_bytes += 4 * B * 4
+            # rows keep their place unless a sequence left the batch: a plain copy then, else a gather
+            if toks == list(range(n)):
+                self.d_small[:n].copy_(self.out_tokens[:n], non_blocking=True)
+            else:
+                torch.index_select(self.out_tokens, 0, self.d_small[4 * B : 4 * B + n], out=self.d_small[:n])
+        else:
+            self.d_small[: 4 * B].copy_(self.h_small[: 4 * B], non_blocking=True)
+            self.h2d_bytes += 4 * B * 4
         if dirty or b != self._table_b or wmax > self._table_w:
             # the block table only changes when a sequence crosses a page boundary or rows change hands
             self.d_table[:b, :wmax].copy_(self.h_table[:b, :wmax], non_blocking=True)
             self.h2d_bytes += b * wmax * 4
             self._table_b, self._table_w = b, wmax
+        if self._staged is None:
+            self._staged = torch.cuda.Event()
+        self._staged.record()
 
-    def run(self, seqs, greedy: bool = True) -> torch.Tensor:
+    def _launch(self, seqs, b: int, key, ahead_of: Optional[_InFlight] = None) -> _InFlight:
+        """Stage, replay and queue the copy of the picked tokens into pinned memory."""
+        self.stage(seqs, b, ahead_of)
+        self.graphs[key].replay()
+        self.replays += 1
+        n = len(seqs)
+        host = self.h_out2 if (ahead_of is not None and ahead_of.host is self.h_out) else self.h_out
+        host[:n].copy_(self.out_tokens[:n], non_blocking=True)
+        self.d2h_bytes += n * 4
+        ev = torch.cuda.Event()
+        ev.record()
+        adv = 0 if ahead_of is None else 1
+        return _InFlight({s.rid: i for i, s in enumerate(seqs)}, {s.rid: s.start_pos + adv for s in seqs}, ev, host, n)
+
+    def covers(self, s) -> bool:
+        """True if the step that is running ahead computes exactly this decode row."""
+        p = self.pending
+        return p is not None and len(s.input_tokens) == 1 and p.pos.get(s.rid, -1) == s.start_pos
+
+    def claim(self, seqs) -> dict:
+        """Take the tokens of the rows among ``seqs`` that the step running ahead has
+        computed (``rid -> token``) and forget that step.  Nothing is waited for when no
+        row matches: whatever the dropped step writes is ordered before later work on the
+        stream."""
+        p = self.pending
+        if p is None:
+            return {}
+        hit = [s for s in seqs if self.covers(s)]
+        self.pending = None
+        if not hit:
+            return {}
+        p.event.synchronize()
+        self.ahead_claimed += 1
+        return {s.rid: int(p.host[p.rows[s.rid]]) for s in hit}
+
+    def _launch_ahead(self, seqs, cur: _InFlight) -> None:
+        """Launch the step after ``cur`` for every sequence that will still be running."""
+        from ..sched.executor import bucket_for
+
+        ps = self.page_size
+        nxt = [s for s in seqs if not s.final]
+        if not nxt or any(s.table_pages is None or (s.start_pos + 1) // ps >= len(s.table_pages) for s in nxt):
+            return
+        b = bucket_for(len(nxt), self.buckets)
+        key = (b, True)
+        if key not in self.graphs:
+            return  # captured by the next ordinary step
+        self.pending = self._launch(nxt, b, key, ahead_of=cur)
+        self.ahead_launches += 1
+
+    def run(self, seqs, greedy: bool = True, ahead: bool = False):
+        """One decode step for ``seqs``: token ids (a list) when ``greedy``, else the logits.
+        If a step is running ahead, the caller has checked that it covers every row."""
         from ..sched.executor import bucket_for
 
         n = len(seqs)
-        b = bucket_for(n, self.buckets)
-        key = (b, greedy)
-        g = self.graphs.get(key)
-        if g is None:
-            g = self.capture(b, greedy)
-        self.stage(seqs, b)
-        g.replay()
-        self.replays += 1
-        if greedy:
-            self.h_out[:n].copy_(self.out_tokens[:n], non_blocking=True)
-            torch.cuda.current_stream(self.device).synchronize()
-            self.d2h_bytes += n * 4
-            return self.h_out[:n]
-        return self.logits[key][:n]
+        cur, self.pending = self.pending, None
+        if cur is not None:
+            assert greedy and all(cur.pos.get(s.rid, -1) == s.start_pos for s in seqs)
+            self.ahead_claimed += 1
+        else:
+            b = bucket_for(n, self.buckets)
+            key = (b, greedy)
+            if key not in self.graphs:
+                self.capture(b, greedy)
+            if not greedy:
+                self.stage(seqs, b)
+                self.graphs[key].replay()
+                self.replays += 1
+                return self.logits[key][:n]
+            cur = self._launch(seqs, b, key)
+        if ahead and not self.uses_state:
+            self._launch_ahead(seqs, cur)
+        cur.event.synchronize()
+        host = cur.host.tolist()
+        return [host[cur.rows[s.rid]] for s in seqs]
 
     def dump_dot(self, path: str, b: Optional[int] = None, greedy: bool = True) -> str:
         """Write the captured graph of bucket ``b`` as Graphviz DOT text."""

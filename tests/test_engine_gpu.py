@@ -247,3 +247,47 @@ def test_decode_overlap_second_stream_matches_plain_engine():
         K.set_batch_invariant(False)
     assert n0 == 0 and n1 > 0
     assert over == plain
+
+
+def test_run_ahead_decode_matches_step_by_step_engine():
+    """Decode run-ahead (the next CUDA-graph step is launched before this step's tokens are read)
+    against the engine that reads every step first: same tokens with staggered length limits, a
+    stop token that ends a request without warning, and prompts that arrive while others decode."""
+    import time
+
+    from pegainfer_b200.engine.contract import Request
+    from pegainfer_b200.ops import cuda as K
+
+    ps = prompts(6, seed=29)
+    limits = [40, 9, 33, 17, 40, 26]
+
+    def run(stops, **kw):
+        eng = engine(True, no_prefix_cache=True, batch_invariant=True, max_prefill_tokens=64, **kw)
+        try:
+            streams = []
+            for i, p in enumerate(ps):
+                sp = SamplingParams(temperature=0.0, ignore_eos=True, stop_token_ids=tuple(stops.get(i, ())))
+                streams.append(eng.submit(Request(prompt_tokens=p, params=sp, max_tokens=limits[i])))
+                if i in (2, 4):
+                    time.sleep(0.05)
+            outs = [s.collect(120) for s in streams]
+            torch.cuda.synchronize()
+            assert K.read_status("cuda:0") == 0
+            g = eng.executor._graphs
+            assert eng.pool.used() == 0, "every block, look-ahead pages included, went back to the pool"
+            return [(o[0], o[1].finish_reason) for o in outs], g.ahead_launches, g.ahead_claimed
+        finally:
+            eng.shutdown()
+
+    try:
+        base, _, _ = run({}, run_ahead=False)
+        # a token from the middle of two outputs becomes their stop token
+        stops = {0: [base[0][0][20]], 4: [base[4][0][11]]}
+        plain, l0, c0 = run(stops, run_ahead=False)
+        ahead, l1, c1 = run(stops, run_ahead=True)
+    finally:
+        K.set_batch_invariant(False)
+    assert l0 == 0 and c0 == 0
+    assert l1 > 20 and c1 > 20, (l1, c1)
+    assert len(plain[0][0]) <= 20 and len(plain[4][0]) <= 11
+    assert ahead == plain

@@ -56,6 +56,28 @@ def test_gemm_matches_fp32(t, m, k):
     status_clean()
 
 
+@pytest.mark.parametrize("t,m,k", [(256, 256, 64), (512, 1024, 256), (300, 700, 520), (1000, 1500, 1032), (2048, 4096, 4096), (4096, 6144, 1024), (777, 151936 // 16, 512)])
+def test_gemm_two_sm_pair_tiles(t, m, k):
+    """cta_group::2 kernel (a CTA pair per 256 x 256 tile) called directly: full tiles, ragged
+    edges in both dimensions, several tiles per pair (both accumulator buffers, ring wrap)."""
+    torch.manual_seed(t + m + k)
+    x = (torch.randn(t, k, device=DEV) * 0.5).bfloat16()
+    w = (torch.randn(m, k, device=DEV) * 0.05).bfloat16()
+    ref = x.float() @ w.float().t()
+    y = cu().linear_2sm(x, w)
+    torch.cuda.synchronize()
+    status_clean()
+    err = (y.float() - ref).abs()
+    tol = 2 ** -7 * ref.abs() + 2e-2 * math.sqrt(max(k, 1024) / 1024)
+    assert (err <= tol).all(), f"max err {err.max().item()} (ref max {ref.abs().max().item()})"
+    assert torch.equal(y, cu().linear_2sm(x, w))
+    # a strided activation view (row stride larger than K) goes through the tensor map
+    big = (torch.randn(t, k + 64, device=DEV) * 0.5).bfloat16()
+    y2 = cu().linear_2sm(big[:, :k], w)
+    assert (y2.float() - big[:, :k].float() @ w.float().t()).abs().max().item() < 0.1 * math.sqrt(max(k, 1024) / 1024)
+    status_clean()
+
+
 @pytest.mark.parametrize("t,m,k,s", [(64, 4096, 4096, 4), (50, 1000, 2048, 8), (16, 24576, 1024, 3), (64, 24576, 4096, 0), (8, 30000, 512, 5), (64, 4096, 12288, 7), (33, 128, 8192, 6)])
 def test_gemm_cluster_split_k(t, m, k, s):
     """Narrow token tiles reduce their k-splits across a thread-block cluster (several rounds per cluster included)."""

@@ -209,3 +209,60 @@ def test_host_tier_restores_evicted_prefix_and_keeps_tokens():
     finally:
         plain.shutdown()
         off.shutdown()
+
+
+class AheadExecutor(FakeExecutor):
+    """The run-ahead protocol as the scheduler sees it: after a decode step flagged ``run_ahead``
+    the next position of every non-final request counts as already launched, which needs the
+    page of that position in ``table_pages``."""
+
+    supports_run_ahead = True
+
+    def __init__(self, block_size):
+        super().__init__()
+        self.bs = block_size
+        self.pending = {}
+        self.claimed = self.wasted = 0
+
+    def execute(self, batch):
+        hit = {s.rid for s in batch.seqs if len(s.input_tokens) == 1 and self.pending.get(s.rid) == s.start_pos}
+        self.claimed += len(hit)
+        self.wasted += len(self.pending) - len(hit)
+        self.pending = {}
+        res = super().execute(batch)
+        if batch.run_ahead:
+            assert batch.kind == "decode"
+            for s in batch.seqs:
+                if not s.final:
+                    assert s.table_pages is not None and (s.start_pos + 1) // self.bs < len(s.table_pages), "no page for the position that runs ahead"
+                    self.pending[s.rid] = s.start_pos + 1
+        return res
+
+
+def test_run_ahead_lookahead_pages_and_final_marks():
+    bs = 4
+    reqs = [
+        Request(prompt_tokens=list(range(9)), max_tokens=11),
+        Request(prompt_tokens=list(range(50, 56)), max_tokens=7, params=SamplingParams(stop_token_ids=(((2 * 7 + 9) % 97),))),  # stops at position 9, unannounced
+        Request(prompt_tokens=list(range(20, 23)), max_tokens=1),
+        Request(prompt_tokens=list(range(30, 41)), max_tokens=5),
+    ]
+    # the pool holds exactly the lifetime blocks of all four: look-ahead pages must stay inside the reservation
+    need = sum((len(r.prompt_tokens) + r.max_tokens + bs - 1) // bs for r in reqs)
+    plain = _drive(ContinuousScheduler(FakeExecutor(), BlockPool(need + 1, bs), SchedulerConfig(max_prefill_tokens=64, max_decode_batch=8, max_model_len=64)), reqs)
+    ex = AheadExecutor(bs)
+    pool = BlockPool(need + 1, bs)
+    sched = ContinuousScheduler(ex, pool, SchedulerConfig(max_prefill_tokens=64, max_decode_batch=8, max_model_len=64, run_ahead=True))
+    ahead = _drive(sched, reqs)
+    assert sched.failed_batches == 0 and pool.used() == 0
+    for rid in plain:
+        assert [t for u in plain[rid] for t in u.tokens] == [t for u in ahead[rid] for t in u.tokens]
+        assert plain[rid][-1].terminal == ahead[rid][-1].terminal
+    assert ahead[2][-1].terminal.finish_reason == FinishReason.STOP
+    # every decode row but the first of each request was launched ahead; the only wasted row is the unannounced stop
+    assert ex.claimed > 10 and ex.wasted == 1, (ex.claimed, ex.wasted)
+    # a request at the context limit is marked final as well
+    ex2 = AheadExecutor(bs)
+    sched2 = ContinuousScheduler(ex2, BlockPool(8, bs), SchedulerConfig(max_prefill_tokens=64, max_decode_batch=8, max_model_len=12, run_ahead=True))
+    out = _drive(sched2, [Request(prompt_tokens=list(range(6)), max_tokens=50)])
+    assert out[1][-1].terminal.finish_reason == FinishReason.LENGTH and ex2.wasted == 0 and sched2.failed_batches == 0
