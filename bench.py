@@ -251,6 +251,7 @@ def e2e(args, eng, rank, world, device):
     host_prompts = torch.randint(0, eng.model.cfg.vocab_size, (n, plen), generator=g, dtype=torch.int32).pin_memory()
     graphs = eng.executor._graphs
     h2d0, d2h0 = graphs.h2d_bytes, graphs.d2h_bytes
+    wait0, launch0, replays0 = graphs.wait_s, graphs.launch_s, graphs.replays
     stamps = [[] for _ in range(n)]
     t_submit = time.perf_counter()
     streams = []
@@ -304,6 +305,10 @@ def e2e(args, eng, rank, world, device):
         tpot_p50_ms=1e3 * statistics.median(tpot),
         h2d_bytes_per_step=(graphs.h2d_bytes - h2d0) // steps_run,
         d2h_bytes_per_step=(graphs.d2h_bytes - d2h0) // steps_run,
+        # where the engine thread's time goes per decode step: waiting for the GPU vs staging and launching
+        host_wait_ms_per_step=round(1e3 * (graphs.wait_s - wait0) / max(1, graphs.replays - replays0), 3),
+        host_launch_ms_per_step=round(1e3 * (graphs.launch_s - launch0) / max(1, graphs.replays - replays0), 3),
+        steps_launched_ahead=graphs.ahead_claimed,
     )
 
 
@@ -373,7 +378,8 @@ def main():
             "gpu_launches": ko["kernels_per_step"] * args.steps,
         }
         if ee is not None:
-            line["e2e"] = {"value": round(ee["value"], 2), "unit": "tok/s", "h2d_bytes_per_step": ee["h2d_bytes_per_step"], "d2h_bytes_per_step": ee["d2h_bytes_per_step"], "ttft_p50_ms": round(ee["ttft_p50_ms"], 2), "tpot_p50_ms": round(ee["tpot_p50_ms"], 3)}
+            line["e2e"] = {"value": round(ee["value"], 2), "unit": "tok/s", "h2d_bytes_per_step": ee["h2d_bytes_per_step"], "d2h_bytes_per_step": ee["d2h_bytes_per_step"], "ttft_p50_ms": round(ee["ttft_p50_ms"], 2), "tpot_p50_ms": round(ee["tpot_p50_ms"], 3),
+                           "host_wait_ms_per_step": ee["host_wait_ms_per_step"], "host_launch_ms_per_step": ee["host_launch_ms_per_step"], "steps_launched_ahead": ee["steps_launched_ahead"]}
         print(json.dumps(line))
     hard_exit(0)
 

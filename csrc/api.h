@@ -113,9 +113,7 @@ int pg_decode_splits(int num_seqs, int hkv, int max_kv_len, int sms);
 void pg_attn_set_decode_stages(int stages);  // 2 (three CTAs per SM) or 3 (two CTAs per SM, default)
 int pg_paged_attention(const void* q, const void* kv, void* out, const void* q_indptr, const void* kv_lens, const void* table, int table_stride,
                        int num_seqs, int hq, int hkv, int dim, int page_size, long long num_pages, float scale, int mode, int splits,
-                       void* part_o, void* part_lse, int q_tiles, int window, void* status, void* merge_counters, cudaStream_t stream);
-// merge_counters: B * Hkv zeroed uint32 (left zero by every launch) lets the persistent decode kernel merge the KV
-// splits itself; nullptr runs the separate merge kernel.
+                       void* part_o, void* part_lse, int q_tiles, int window, void* status, cudaStream_t stream);
 
 // ---- sampling (sampling.cu) --------------------------------------------------------
 long long pg_argmax_scratch_bytes(int rows, int vocab);

@@ -77,7 +77,6 @@ struct AttnParams {
   float* part_lse;  // [B, Hq, splits]
   long long num_pages;
   uint32_t* status;
-  uint32_t* merge_cnt;  // [B * Hkv] arrival counters of the fused split merge (zero between launches), or nullptr
 };
 
 // Row address of token `tok` of sequence b, kv head h (kvsel 0 = K, 1 = V).
@@ -321,7 +320,6 @@ __global__ void __launch_bounds__(128, D <= 128 ? 2 : 1) decode_attn_persistent_
   float* mo = reinterpret_cast<float*>(smem_raw + (size_t)4 * STAGES * STAGE_ELEMS * 2);
   float* mm = mo + 4 * 8 * D;
   float* ml = mm + 4 * 8;
-  volatile int* s_last = reinterpret_cast<volatile int*>(ml + 4 * 8);
   const long long row_stride = (long long)p.hkv * D;
   const long long v_plane = (long long)p.page_size * row_stride;
   const uint64_t kv_policy = l2_policy_evict_first();
@@ -469,38 +467,6 @@ __global__ void __launch_bounds__(128, D <= 128 ? 2 : 1) decode_attn_persistent_
       } else {
         p.part_o[(((long long)uc.b * p.hq + hq) * p.splits + uc.split) * D + d] = val;
         if (d == 0) p.part_lse[((long long)uc.b * p.hq + hq) * p.splits + uc.split] = L > 0.f ? M + log2f(L) : NEG_BIG;
-      }
-    }
-    if (p.splits > 1 && p.merge_cnt != nullptr) {
-      // The CTA that stores the last split of this (sequence, kv head) also merges the splits:
-      // no separate merge launch.  The counter returns to zero for the next launch.
-      __threadfence();
-      __syncthreads();
-      if (threadIdx.x == 0) {
-        const uint32_t old = atomicAdd(&p.merge_cnt[uc.b * p.hkv + uc.h], 1u);
-        const bool last = old == (uint32_t)(p.splits - 1);
-        if (last) p.merge_cnt[uc.b * p.hkv + uc.h] = 0u;
-        *s_last = last ? 1 : 0;
-      }
-      __syncthreads();
-      if (*s_last) {
-        __threadfence();
-        for (int idx = threadIdx.x; idx < G * D; idx += 128) {
-          const int row = idx / D, d = idx % D;
-          const long long unit = (long long)uc.b * p.hq + uc.h * G + row;
-          const float* lse = p.part_lse + unit * p.splits;
-          float M = NEG_BIG;
-          for (int sp = 0; sp < p.splits; ++sp) M = fmaxf(M, __ldcg(lse + sp));
-          float W = 0.f, acc = 0.f;
-          for (int sp = 0; sp < p.splits; ++sp) {
-            const float l = __ldcg(lse + sp);
-            if (l <= NEG_BIG) continue;
-            const float f = exp2f(l - M);
-            W += f;
-            acc += f * __ldcg(p.part_o + (unit * p.splits + sp) * D + d);
-          }
-          p.out[((long long)uc.qrow * p.hq + uc.h * G + row) * D + d] = __float2bfloat16(W > 0.f ? acc / W : 0.f);
-        }
       }
     }
     __syncthreads();  // the scratch is free again
@@ -762,7 +728,7 @@ int g_decode_persistent = -1;  // PEGAINFER_ATTN_PERSISTENT=0 selects the one-un
 template <int D>
 int launch_decode_persistent(const AttnParams& p, cudaStream_t stream) {
   const size_t pipe = (size_t)4 * 3 * 2 * 16 * D * 2;
-  const size_t merge = (size_t)(4 * 8 * D + 64 + 4) * 4;
+  const size_t merge = (size_t)(4 * 8 * D + 64) * 4;
   const size_t smem = pipe + merge;
   static int sms = 0;
   if (!sms) {
@@ -775,7 +741,7 @@ int launch_decode_persistent(const AttnParams& p, cudaStream_t stream) {
   const int slots = sms * (D <= 128 ? 2 : 1);
   PG_CUDA(launch_pdl(decode_attn_persistent_kernel<D>, dim3(units < slots ? units : slots), dim3(128), smem, stream, p));
   PG_LAUNCH_CHECK();
-  if (p.splits > 1 && p.merge_cnt == nullptr) {
+  if (p.splits > 1) {
     PG_CUDA(launch_pdl(decode_merge_kernel<D>, dim3((p.num_seqs * p.hq + 3) / 4), dim3(128), (size_t)(0), stream, p));
     PG_LAUNCH_CHECK();
   }
@@ -840,7 +806,7 @@ extern "C" int pg_decode_splits(int num_seqs, int hkv, int max_kv_len, int sms) 
 extern "C" int pg_paged_attention(const void* q, const void* kv, void* out, const void* q_indptr, const void* kv_lens, const void* table,
                                   int table_stride, int num_seqs, int hq, int hkv, int dim, int page_size, long long num_pages, float scale,
                                   int mode, int splits, void* part_o, void* part_lse, int q_tiles, int window, void* status,
-                                  void* merge_counters, cudaStream_t stream) {
+                                  cudaStream_t stream) {
   PG_REQUIRE(dim == 64 || dim == 128 || dim == 256, "paged_attention: head_dim %d not supported (64, 128, 256)", dim);
   PG_REQUIRE(hq % hkv == 0 && hq / hkv <= 8, "paged_attention: GQA group %d/%d not supported (<= 8)", hq, hkv);
   PG_REQUIRE(page_size == 16 || page_size == 32 || page_size == 64, "paged_attention: page size %d not supported", page_size);
@@ -863,7 +829,6 @@ extern "C" int pg_paged_attention(const void* q, const void* kv, void* out, cons
   p.part_lse = (float*)part_lse;
   p.num_pages = num_pages;
   p.status = (uint32_t*)status;
-  p.merge_cnt = (uint32_t*)merge_counters;
   if (mode == 0) {
     PG_REQUIRE(p.splits == 1 || (part_o && part_lse), "paged_attention: split-KV decode needs partial buffers");
     if (dim == 64) return launch_decode<64>(p, stream);

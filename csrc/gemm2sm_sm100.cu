@@ -32,24 +32,37 @@
 
 namespace {
 
-constexpr int BM = 128;   // weight rows per CTA (256 per pair)
-constexpr int BNH = 128;  // token rows staged per CTA (the pair's tile is 256 tokens wide)
-constexpr int BN = 256;
+constexpr int BM = 128;  // weight rows per CTA (256 per pair)
 constexpr int BK = 64;
 constexpr int A_BYTES = BM * BK * 2;
-constexpr int B_BYTES = BNH * BK * 2;
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int STAGES = 6;
+constexpr int MAX_STAGES = 12;
 constexpr int NUM_THREADS = 192;
-constexpr uint32_t TMEM_COLS = 512;
+constexpr int RASTER_GROUP = 8;  // weight-row pairs per raster group
 
 struct Gemm2Params {
   bf16* y;
   long long ldy;
   int M, T, K;
   int m_pairs, n_tiles, kblocks;
+  int bn;      // token columns of a pair's tile (multiple of 32, <= 256); each CTA stages bn / 2 token rows
+  int stages;  // shared-memory ring depth
+  uint32_t tmem_cols;
   uint32_t* status;
 };
+
+// Work item -> (weight-row pair, token tile).  Items walk RASTER_GROUP weight-row pairs across
+// all token tiles before moving on, so the CTA pairs that run at the same time cover a
+// near-square patch of the output and share both operands through L2 (walking all weight
+// rows of one token tile first would stream the whole weight matrix once per token tile).
+__device__ __forceinline__ void tile_of(const Gemm2Params& p, int item, int& m_pair, int& n_tile) {
+  const int per_group = RASTER_GROUP * p.n_tiles;
+  const int group = item / per_group;
+  const int first = group * RASTER_GROUP;
+  const int gsz = min(RASTER_GROUP, p.m_pairs - first);
+  const int within = item - group * per_group;
+  m_pair = first + within % gsz;
+  n_tile = within / gsz;
+}
 
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t* dst_smem, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols) : "memory");
@@ -90,9 +103,11 @@ gemm2sm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = smem_u32(smem_raw);
   uint8_t* tiles = smem_raw + (((base + 1023u) & ~1023u) - base);
-  uint64_t* full = reinterpret_cast<uint64_t*>(tiles + STAGES * STAGE_BYTES);
-  uint64_t* empty = full + STAGES;
-  uint64_t* tfull = empty + STAGES;
+  const int bnh = p.bn >> 1;
+  const int stage_bytes = A_BYTES + bnh * 128;
+  uint64_t* full = reinterpret_cast<uint64_t*>(tiles + p.stages * stage_bytes);
+  uint64_t* empty = full + MAX_STAGES;
+  uint64_t* tfull = empty + MAX_STAGES;
   uint64_t* tempty = tfull + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -104,7 +119,7 @@ gemm2sm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
   const int pairs = gridDim.x >> 1;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < p.stages; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
@@ -118,7 +133,7 @@ gemm2sm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
     tma_prefetch_desc(&tm_x);
   }
   if (warp == 1) {
-    tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    tmem_alloc_pair(tmem_slot, p.tmem_cols);
     tmem_relinquish_pair();
   }
   tc_fence_before();
@@ -133,35 +148,37 @@ gemm2sm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
 
   if (warp == 0) {
     if (lane == 0) {
-      const uint64_t pol_w = l2_policy_evict_first();
-      const uint64_t pol_x = l2_policy_evict_last();
+      // both operands are re-read (weights by every token tile, tokens by every weight-row pair)
+      const uint64_t pol_w = l2_policy_evict_normal();
+      const uint64_t pol_x = l2_policy_evict_normal();
       int stage = 0;
       uint32_t phase = 0;
-      uint32_t last_phase[STAGES];
-      bool used[STAGES];
+      uint32_t last_phase[MAX_STAGES];
+      bool used[MAX_STAGES];
 #pragma unroll
-      for (int s = 0; s < STAGES; ++s) {
+      for (int s = 0; s < MAX_STAGES; ++s) {
         used[s] = false;
         last_phase[s] = 0;
       }
       bool ok = true;
       for (int item = pair; item < total && ok; item += pairs) {
-        const int m_pair = item % p.m_pairs, n_tile = item / p.m_pairs;
+        int m_pair, n_tile;
+        tile_of(p, item, m_pair, n_tile);
         const int w_row = m_pair * (2 * BM) + (int)rank * BM;
-        const int x_row = n_tile * BN + (int)rank * BNH;
+        const int x_row = n_tile * p.bn + (int)rank * bnh;
         for (int kb = 0; kb < p.kblocks; ++kb) {
           if (!mbar_wait_cluster(&empty[stage], phase ^ 1u, abort_flag)) {
             ok = false;
             break;
           }
-          uint8_t* a_dst = tiles + stage * STAGE_BYTES;
+          uint8_t* a_dst = tiles + stage * stage_bytes;
           const uint32_t bar = dsmem_addr(smem_u32(&full[stage]), 0u);
-          if (rank == 0) mbar_expect_tx(&full[stage], 2u * (uint32_t)STAGE_BYTES);
+          if (rank == 0) mbar_expect_tx(&full[stage], 2u * (uint32_t)stage_bytes);
           tma_load_2d_pair(a_dst, &tm_w, bar, kb * BK, w_row, pol_w);
           tma_load_2d_pair(a_dst + A_BYTES, &tm_x, bar, kb * BK, x_row, pol_x);
           used[stage] = true;
           last_phase[stage] = phase;
-          if (++stage == STAGES) {
+          if (++stage == p.stages) {
             stage = 0;
             phase ^= 1u;
           }
@@ -169,7 +186,7 @@ gemm2sm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
       }
       // Drain: the MMAs that read this CTA's stages have completed (so the loads have landed and
       // the leader's multicast arrivals on this CTA's barriers are in) before the CTA may exit.
-      for (int s = 0; s < STAGES; ++s) {
+      for (int s = 0; s < p.stages; ++s) {
         if (!used[s]) continue;
         uint64_t t0 = globaltimer_ns();
         while (!mbar_try_wait_cluster(&empty[s], last_phase[s])) {
@@ -179,7 +196,7 @@ gemm2sm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
     }
   } else if (warp == 1) {
     if (lane == 0 && rank == 0) {
-      const uint32_t idesc = umma_idesc_bf16_f32(2 * BM, BN);
+      const uint32_t idesc = umma_idesc_bf16_f32(2 * BM, (uint32_t)p.bn);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -188,21 +205,21 @@ gemm2sm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
       for (int item = pair; item < total && ok; item += pairs) {
         if (!mbar_wait_cluster(&tempty[acc], acc_phase ^ 1u, abort_flag)) break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * p.bn);
         for (int kb = 0; kb < p.kblocks; ++kb) {
           if (!mbar_wait_cluster(&full[stage], phase, abort_flag)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(tiles + stage * STAGE_BYTES);
+          const uint32_t a_addr = smem_u32(tiles + stage * stage_bytes);
           const uint32_t b_addr = a_addr + A_BYTES;
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
             umma_bf16_ss_pair(d_tmem, umma_desc_k_sw128(a_addr + k * 32), umma_desc_k_sw128(b_addr + k * 32), idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
           umma_commit_pair(&empty[stage], (uint16_t)3);
-          if (++stage == STAGES) {
+          if (++stage == p.stages) {
             stage = 0;
             phase ^= 1u;
           }
@@ -220,14 +237,15 @@ gemm2sm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int item = pair; item < total; item += pairs) {
-      const int m_pair = item % p.m_pairs, n_tile = item / p.m_pairs;
+      int m_pair, n_tile;
+      tile_of(p, item, m_pair, n_tile);
       if (!mbar_wait_cluster(&tfull[acc], acc_phase, abort_flag)) break;
       tc_fence_after();
       const int m = m_pair * (2 * BM) + (int)rank * BM + r;
-      const int n0 = n_tile * BN;
-      const uint32_t t_row = tmem_base + ((uint32_t)(wq * 32) << 16) + (uint32_t)(acc * BN);
+      const int n0 = n_tile * p.bn;
+      const uint32_t t_row = tmem_base + ((uint32_t)(wq * 32) << 16) + (uint32_t)(acc * p.bn);
       bf16* yc = p.y + m;
-      for (int c = 0; c < BN; c += 32) {
+      for (int c = 0; c < p.bn; c += 32) {
         uint32_t v[2][16];
         tmem_ld16(t_row + c, v[0]);
         tmem_ld16(t_row + c + 16, v[1]);
@@ -257,7 +275,7 @@ gemm2sm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
   cluster_sync_all();  // neither CTA tears down shared memory or TMEM the other may still reach
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    tmem_dealloc_pair(tmem_base, p.tmem_cols);
   }
   if (threadIdx.x == 0 && *abort_flag) atomicCAS(p.status, PG_ST_OK, PG_ST_TIMEOUT | (11u << 8));
 }
@@ -267,6 +285,7 @@ struct Dev2 {
   bool set = false;
   bool usable = false;
   int sms = 0;
+  int max_smem = 0;
   int max_pairs = 0;
 };
 Dev2 g_dev2[64];
@@ -281,9 +300,13 @@ extern "C" int pg_gemm2sm_eligible(int T, int M, int K) {
     g_enabled = (e && e[0] == '0') ? 0 : 1;
   }
   if (!g_enabled) return 0;
-  // Tensor-bound problems only: below this the one-CTA kernel's narrower token tiles and
-  // k-splits fill the machine better.
-  return (T >= 512 && M >= 1024 && K >= 256 && K % 8 == 0) ? 1 : 0;
+  // Tensor-bound problems with at least about one full round of CTA pairs: below that the
+  // one-CTA kernel's narrower token tiles and k-splits fill the machine better.  Very deep
+  // problems (K > 8192) stay on the one-CTA kernel as well: there the operand slabs that the
+  // concurrently running 256 x 256 tiles share (17 slabs of 256 x K) approach the L2 capacity
+  // and this kernel measured slower (493 vs 372 us at T = M = 4096, K = 12288).
+  if (T < 256 || M < 1024 || K < 256 || K > 8192 || K % 8 != 0) return 0;
+  return (long long)ceil_div(M, 2 * BM) * ceil_div(T, 256) >= 64 ? 1 : 0;
 }
 
 extern "C" int pg_gemm2sm_bf16_tn(const void* x, const void* w, void* y, int T, int M, int K, long long ldx, long long ldw, long long ldy, void* status,
@@ -293,17 +316,18 @@ extern "C" int pg_gemm2sm_bf16_tn(const void* x, const void* w, void* y, int T, 
   int dev = 0;
   PG_CUDA(cudaGetDevice(&dev));
   Dev2& di = g_dev2[dev & 63];
-  const size_t smem = 1024 + (size_t)STAGES * STAGE_BYTES + (2 * STAGES + 4) * 8 + 64;
+  const int tail = (2 * MAX_STAGES + 4) * 8 + 64;
   {
     std::lock_guard<std::mutex> lk(g_mu2);
     if (!di.set) {
       PG_CUDA(cudaDeviceGetAttribute(&di.sms, cudaDevAttrMultiProcessorCount, dev));
-      PG_CUDA(cudaFuncSetAttribute(gemm2sm_bf16_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      PG_CUDA(cudaDeviceGetAttribute(&di.max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+      PG_CUDA(cudaFuncSetAttribute(gemm2sm_bf16_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem));
       cudaLaunchConfig_t cfg;
       memset(&cfg, 0, sizeof(cfg));
       cfg.gridDim = dim3((unsigned)(2 * di.sms));
       cfg.blockDim = dim3(NUM_THREADS);
-      cfg.dynamicSmemBytes = smem;
+      cfg.dynamicSmemBytes = (size_t)di.max_smem;
       cudaLaunchAttribute at[1];
       at[0].id = cudaLaunchAttributeClusterDimension;
       at[0].val.clusterDim.x = 2;
@@ -327,13 +351,33 @@ extern "C" int pg_gemm2sm_bf16_tn(const void* x, const void* w, void* y, int T, 
   p.T = T;
   p.K = K;
   p.m_pairs = ceil_div(M, 2 * BM);
-  p.n_tiles = ceil_div(T, BN);
+  // token-tile width: fewest rounds of CTA pairs; a round costs about (width + 256): the MMA
+  // time follows the width, the 128 weight rows per CTA and the per-k-block hand-offs do not
+  {
+    long long best_cost = -1;
+    for (int bn = 256; bn >= 128; bn -= 32) {
+      const long long tiles = (long long)p.m_pairs * ceil_div(T, bn);
+      const long long rounds = (tiles + di.max_pairs - 1) / di.max_pairs;
+      const long long cost = rounds * (bn + 256);
+      if (best_cost < 0 || cost < best_cost) {
+        best_cost = cost;
+        p.bn = bn;
+      }
+    }
+  }
+  p.n_tiles = ceil_div(T, p.bn);
   p.kblocks = ceil_div(K, BK);
+  const int stage_bytes = A_BYTES + (p.bn / 2) * 128;
+  p.stages = (di.max_smem - 1024 - tail) / stage_bytes;
+  if (p.stages > MAX_STAGES) p.stages = MAX_STAGES;
+  PG_REQUIRE(p.stages >= 2, "gemm2sm: not enough shared memory");
+  p.tmem_cols = 2 * p.bn > 256 ? 512u : 256u;
   p.status = (uint32_t*)status;
+  const size_t smem = 1024 + (size_t)p.stages * stage_bytes + tail;
   CUtensorMap tm_w, tm_x;
   int rc = pg_make_tmap_bf16_2d(&tm_w, w, M, K, ldw, BM, BK);
   if (rc) return rc;
-  rc = pg_make_tmap_bf16_2d(&tm_x, x, T, K, ldx, BNH, BK);
+  rc = pg_make_tmap_bf16_2d(&tm_x, x, T, K, ldx, p.bn / 2, BK);
   if (rc) return rc;
   const int total = p.m_pairs * p.n_tiles;
   const int npairs = total < di.max_pairs ? total : di.max_pairs;

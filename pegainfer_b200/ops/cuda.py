@@ -44,7 +44,6 @@ class _DeviceCtx:
         self.gemm_counters = torch.zeros(GEMM_COUNTERS, dtype=torch.int32, device=device)
         self.argmax_scratch = torch.empty(8 << 20, dtype=torch.uint8, device=device)
         self.attn_part = torch.empty(ATTN_PART_BYTES, dtype=torch.uint8, device=device)
-        self.attn_counters = torch.zeros(1 << 16, dtype=torch.int32, device=device)  # split-merge arrival counters (self-resetting)
         self.sms = torch.cuda.get_device_properties(device).multi_processor_count
         self.launches = 0
 
@@ -326,16 +325,16 @@ def paged_attention(q, kv_layer, meta: AttnMeta, scale=None, window=0, out: Opti
         rc = lib().pg_paged_attention(
             _ptr(q), _ptr(kv_layer), _ptr(out), _ptr(meta.q_indptr), _ptr(meta.kv_lens), _ptr(table), _ci(table.stride(0)), _ci(meta.num_seqs),
             _ci(hq), _ci(hkv), _ci(d), _ci(page_size), _ll(kv_layer.shape[0]), _cf(scale), _ci(0), _ci(splits), _ptr(part_o), _ptr(part_lse),
-            _ci(0), _ci(0), _ptr(c.status), _ptr(c.attn_counters if meta.num_seqs * hkv <= c.attn_counters.numel() else None), _stream(),
+            _ci(0), _ci(0), _ptr(c.status), _stream(),
         )
-        _check(rc, c, 1)
+        _check(rc, c, 2 if splits > 1 else 1)
         return out
     qi = meta.h_q_indptr if meta.h_q_indptr is not None else meta.q_indptr.tolist()
     q_tiles = sum((qi[b + 1] - qi[b] + 63) // 64 for b in range(meta.num_seqs))
     rc = lib().pg_paged_attention(
         _ptr(q), _ptr(kv_layer), _ptr(out), _ptr(meta.q_indptr), _ptr(meta.kv_lens), _ptr(table), _ci(table.stride(0)), _ci(meta.num_seqs),
         _ci(hq), _ci(hkv), _ci(d), _ci(page_size), _ll(kv_layer.shape[0]), _cf(scale), _ci(1), _ci(1), _vp(0), _vp(0), _ci(q_tiles), _ci(window),
-        _ptr(c.status), _vp(0), _stream(),
+        _ptr(c.status), _stream(),
     )
     _check(rc, c)
     return out

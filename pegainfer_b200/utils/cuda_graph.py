@@ -23,6 +23,7 @@ attention path), pegainfer-core/src/cuda_graph/dump.rs:24-135 (DOT export).
 from __future__ import annotations
 
 import os
+import time
 from typing import Optional
 
 import numpy as np
@@ -80,6 +81,8 @@ class DecodeGraphs:
         self._staged = None  # event behind the last host->device copies out of the pinned mirrors
         self.ahead_launches = 0
         self.ahead_claimed = 0
+        self.wait_s = 0.0  # host time spent waiting for a step's tokens
+        self.launch_s = 0.0  # host time spent staging and launching steps
         self.graphs: dict = {}
         self.logits: dict = {}
         self.pool = None
@@ -248,6 +251,7 @@ class DecodeGraphs:
 
     def _launch(self, seqs, b: int, key, ahead_of: Optional[_InFlight] = None) -> _InFlight:
         """Stage, replay and queue the copy of the picked tokens into pinned memory."""
+        t0 = time.perf_counter()
         self.stage(seqs, b, ahead_of)
         self.graphs[key].replay()
         self.replays += 1
@@ -258,6 +262,7 @@ class DecodeGraphs:
         ev = torch.cuda.Event()
         ev.record()
         adv = 0 if ahead_of is None else 1
+        self.launch_s += time.perf_counter() - t0
         return _InFlight({s.rid: i for i, s in enumerate(seqs)}, {s.rid: s.start_pos + adv for s in seqs}, ev, host, n)
 
     def covers(self, s) -> bool:
@@ -319,7 +324,9 @@ class DecodeGraphs:
             cur = self._launch(seqs, b, key)
         if ahead and not self.uses_state:
             self._launch_ahead(seqs, cur)
+        t0 = time.perf_counter()
         cur.event.synchronize()
+        self.wait_s += time.perf_counter() - t0
         host = cur.host.tolist()
         return [host[cur.rows[s.rid]] for s in seqs]
 

@@ -56,7 +56,7 @@ def test_gemm_matches_fp32(t, m, k):
     status_clean()
 
 
-@pytest.mark.parametrize("t,m,k", [(256, 256, 64), (512, 1024, 256), (300, 700, 520), (1000, 1500, 1032), (2048, 4096, 4096), (4096, 6144, 1024), (777, 151936 // 16, 512)])
+@pytest.mark.parametrize("t,m,k", [(256, 256, 64), (512, 1024, 256), (300, 700, 520), (1000, 1500, 1032), (2048, 4096, 4096), (4096, 6144, 1024), (777, 151936 // 16, 512), (1024, 6144, 512), (640, 2048, 256), (900, 1024, 320)])
 def test_gemm_two_sm_pair_tiles(t, m, k):
     """cta_group::2 kernel (a CTA pair per 256 x 256 tile) called directly: full tiles, ragged
     edges in both dimensions, several tiles per pair (both accumulator buffers, ring wrap)."""
