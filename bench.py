@@ -299,6 +299,9 @@ def e2e(args, eng, rank, world, device):
         os.makedirs(os.path.dirname(os.path.abspath(args.profile_host)), exist_ok=True)
         with open(args.profile_host, "w") as f:
             f.write(buf.getvalue())
+    ts = graphs.timing_summary(last=args.steps)
+    if ts and rank == 0:
+        print("graph timing over the last %d replays: %s" % (ts["replays"], json.dumps({k: round(v, 4) for k, v in ts.items()})), file=sys.stderr)
     return dict(
         value=tokens / dt,
         ttft_p50_ms=1e3 * statistics.median(ttft),

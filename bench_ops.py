@@ -169,6 +169,9 @@ def gdn_cases(iters, only=None):
         ms = time_graph(lambda i: K.gdn_recurrent(q, k, v, g, beta, states[i], meta), 3, max(2, iters // 4))
         state_bytes = len(q_lens) * hv * dk * dv * 4 * 2
         rows.append((f"gdn_recurrent {name} 48vh 128x128", ms, state_bytes + t * (2 * hk * dk + 2 * hv * dv) * 2, 4.0 * t * hv * dk * dv * 2))
+        if max(q_lens) >= 64:  # the row above ran the chunk-wise scan; this one the token-by-token kernel
+            ms = time_graph(lambda i: K.gdn_recurrent(q, k, v, g, beta, states[i], meta, chunked=False), 3, max(2, iters // 4))
+            rows.append((f"  recurrence kernel {name}", ms, state_bytes + t * (2 * hk * dk + 2 * hv * dv) * 2, 4.0 * t * hv * dk * dv * 2))
     return rows
 
 

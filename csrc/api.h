@@ -106,7 +106,11 @@ int pg_gdn_gates(const void* a, long long lda, const void* b, long long ldb, con
                  int tokens, int hv, cudaStream_t stream);
 int pg_gdn_recurrent(const void* q, const void* k, long long ld_qk, const void* v, long long ld_v, const void* g, const void* beta, void* state,
                      void* out, const void* q_indptr, const void* slots, int num_seqs, int hk, int hv, int dk, int dv, int max_q_len,
-                     cudaStream_t stream);
+                     int skip_len, cudaStream_t stream);
+// Chunk-wise (64-token) tensor-core form of the same rule for sequences of >= min_len tokens (gdn_chunk.cu).
+int pg_gdn_chunked(const void* q, const void* k, long long ld_qk, const void* v, long long ld_v, const void* g, const void* beta, void* state,
+                   void* out, const void* q_indptr, const void* slots, int num_seqs, int hk, int hv, int dk, int dv, int min_len,
+                   cudaStream_t stream);
 
 // ---- attention (attention.cu) ------------------------------------------------------
 int pg_decode_splits(int num_seqs, int hkv, int max_kv_len, int sms);

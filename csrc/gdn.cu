@@ -81,7 +81,7 @@ __global__ void __launch_bounds__(128) gdn_recurrent_kernel(const bf16* __restri
                                                              const bf16* __restrict__ v, long long ld_v, const float* __restrict__ g,
                                                              const float* __restrict__ beta, float* __restrict__ state, bf16* __restrict__ out,
                                                              const int* __restrict__ q_indptr, const int* __restrict__ slots, int hk, int hv,
-                                                             int dv, int col_groups) {
+                                                             int dv, int col_groups, int skip_len) {
   constexpr int QK = DK / 4;    // state elements per thread
   constexpr int QS = QK + 4;    // padded quarter stride in shared memory: the four quarters land in different banks
   constexpr int QL = DK / 32;   // q / k elements per lane when a warp holds one token
@@ -93,6 +93,7 @@ __global__ void __launch_bounds__(128) gdn_recurrent_kernel(const bf16* __restri
   const int slot = slots[b];
   const int q0 = q_indptr[b], q1 = q_indptr[b + 1];
   if (q1 == q0 || slot < 0) return;
+  if (skip_len > 0 && q1 - q0 >= skip_len) return;  // long sequences belong to the chunk-wise kernel
   const int kh = h / (hv / hk);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int qtr = tid & 3, lc = tid >> 2, col = cg * GDN_COLS + lc;
@@ -254,7 +255,8 @@ extern "C" int pg_gdn_gates(const void* a, long long lda, const void* b, long lo
 
 extern "C" int pg_gdn_recurrent(const void* q, const void* k, long long ld_qk, const void* v, long long ld_v, const void* g, const void* beta,
                                 void* state, void* out, const void* q_indptr, const void* slots, int num_seqs, int hk, int hv, int dk, int dv,
-                                int max_q_len, cudaStream_t stream) {
+                                int max_q_len, int skip_len, cudaStream_t stream) {
+  // skip_len > 0: sequences of at least that many tokens are left to pg_gdn_chunked
   // steps longer than one stage of 16 tokens use the variant that prefetches the next stage
   const bool long_steps = max_q_len > 16;
   PG_REQUIRE(dv <= 128 && hv % hk == 0, "gdn_recurrent: dv=%d must be <= 128 and hv %% hk == 0", dv);
@@ -266,11 +268,11 @@ extern "C" int pg_gdn_recurrent(const void* q, const void* k, long long ld_qk, c
     if (long_steps)                                                                                                                         \
       gdn_recurrent_kernel<DKV, true><<<grid, 128, 0, stream>>>((const bf16*)q, (const bf16*)k, ld_qk, (const bf16*)v, ld_v, (const float*)g, \
                                                                 (const float*)beta, (float*)state, (bf16*)out, (const int*)q_indptr,        \
-                                                                (const int*)slots, hk, hv, dv, col_groups);                                  \
+                                                                (const int*)slots, hk, hv, dv, col_groups, skip_len);                        \
     else                                                                                                                                    \
       gdn_recurrent_kernel<DKV, false><<<grid, 128, 0, stream>>>((const bf16*)q, (const bf16*)k, ld_qk, (const bf16*)v, ld_v, (const float*)g, \
                                                                  (const float*)beta, (float*)state, (bf16*)out, (const int*)q_indptr,       \
-                                                                 (const int*)slots, hk, hv, dv, col_groups);                                 \
+                                                                 (const int*)slots, hk, hv, dv, col_groups, skip_len);                       \
   } while (0)
   if (dk == 128)
     PG_GDN_LAUNCH(128);

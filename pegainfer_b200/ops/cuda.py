@@ -424,16 +424,28 @@ def gdn_gates(a, b, a_log, dt_bias):
     return g, beta
 
 
-def gdn_recurrent(q, k, v, g, beta, state, meta: AttnMeta):
+_GDN_CHUNKED = os.environ.get("PEGAINFER_GDN_CHUNKED", "1") != "0"
+_GDN_CHUNK_MIN = 32  # sequences of at least this many tokens in a step take the chunk-wise kernel
+
+
+def gdn_recurrent(q, k, v, g, beta, state, meta: AttnMeta, chunked: Optional[bool] = None):
     t, hk, dk = q.shape
     hv, dv = v.shape[1], v.shape[2]
     assert q.stride(2) == 1 and q.stride(1) == dk and k.stride(1) == dk and v.stride(1) == dv and q.stride(0) == k.stride(0)
     assert state.is_contiguous() and state.dtype == torch.float32
     out = torch.empty((t, hv, dv), dtype=q.dtype, device=q.device)
     c = ctx(q.device)
-    rc = lib().pg_gdn_recurrent(_ptr(q), _ptr(k), _ll(q.stride(0)), _ptr(v), _ll(v.stride(0)), _ptr(g.contiguous()), _ptr(beta.contiguous()), _ptr(state), _ptr(out),
-                                _ptr(meta.q_indptr), _ptr(meta.state_slots), _ci(meta.num_seqs), _ci(hk), _ci(hv), _ci(dk), _ci(dv), _ci(int(meta.max_q_len)), _stream())
-    _check(rc, c)
+    g, beta = g.contiguous(), beta.contiguous()
+    # prompt chunks go through the chunk-wise tensor-core scan, short rows (decode) through the recurrence
+    chunked = (_GDN_CHUNKED if chunked is None else chunked) and int(meta.max_q_len) >= _GDN_CHUNK_MIN and dk == 128 and dv % 64 == 0 and q.stride(0) % 8 == 0 and v.stride(0) % 8 == 0
+    args = (_ptr(q), _ptr(k), _ll(q.stride(0)), _ptr(v), _ll(v.stride(0)), _ptr(g), _ptr(beta), _ptr(state), _ptr(out),
+            _ptr(meta.q_indptr), _ptr(meta.state_slots), _ci(meta.num_seqs), _ci(hk), _ci(hv), _ci(dk), _ci(dv))
+    if chunked:
+        rc = lib().pg_gdn_chunked(*args, _ci(_GDN_CHUNK_MIN), _stream())
+        _check(rc, c)
+    if not chunked or meta.num_seqs > 1:
+        rc = lib().pg_gdn_recurrent(*args, _ci(int(meta.max_q_len)), _ci(_GDN_CHUNK_MIN if chunked else 0), _stream())
+        _check(rc, c)
     return out
 
 

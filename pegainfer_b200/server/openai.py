@@ -108,6 +108,30 @@ class _LoopBridge:
             q.put_nowait(upd)
 
 
+def _merge_updates(first: RequestUpdate, q) -> RequestUpdate:
+    """``first`` followed by every update already waiting in ``q``, as one update."""
+    out = RequestUpdate(
+        id=first.id, scheduled=first.scheduled, tokens=list(first.tokens), logprobs=list(first.logprobs or []), cached_tokens=first.cached_tokens,
+        prompt_echo=first.prompt_echo, kv_transfer=first.kv_transfer, terminal=first.terminal,
+    )
+    while out.terminal is None:
+        try:
+            nxt = q.get_nowait()
+        except asyncio.QueueEmpty:
+            break
+        if nxt.logprobs or out.logprobs:  # keep the per-token alignment
+            out.logprobs = (out.logprobs or [None] * len(out.tokens)) + list(nxt.logprobs or [None] * len(nxt.tokens))
+        out.tokens.extend(nxt.tokens)
+        if out.cached_tokens is None:
+            out.cached_tokens = nxt.cached_tokens
+        if out.prompt_echo is None:
+            out.prompt_echo = nxt.prompt_echo
+        if nxt.kv_transfer is not None:
+            out.kv_transfer = nxt.kv_transfer
+        out.terminal = nxt.terminal
+    return out
+
+
 class Frontend:
     """Protocol logic independent of the web framework (unit-testable)."""
 
@@ -210,6 +234,11 @@ class Frontend:
         try:
             while True:
                 upd: RequestUpdate = await q.get()
+                if not stops and not q.empty():
+                    # the engine ran ahead of this connection: fold everything that is waiting into one
+                    # event, so a frontend that falls behind sends fewer, larger chunks instead of lagging
+                    # (with stop strings every update is looked at on its own: token counts end at the hit)
+                    upd = _merge_updates(upd, q)
                 ev: dict = {}
                 now = time.monotonic()
                 if upd.cached_tokens is not None:

@@ -81,6 +81,7 @@ class DecodeGraphs:
         self._staged = None  # event behind the last host->device copies out of the pinned mirrors
         self.ahead_launches = 0
         self.ahead_claimed = 0
+        self._timing = [] if os.environ.get("PEGAINFER_GRAPH_TIMING") == "1" else None  # (start, end) events of every replay
         self.wait_s = 0.0  # host time spent waiting for a step's tokens
         self.launch_s = 0.0  # host time spent staging and launching steps
         self.graphs: dict = {}
@@ -253,7 +254,14 @@ class DecodeGraphs:
         """Stage, replay and queue the copy of the picked tokens into pinned memory."""
         t0 = time.perf_counter()
         self.stage(seqs, b, ahead_of)
-        self.graphs[key].replay()
+        if self._timing is not None:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            self.graphs[key].replay()
+            e1.record()
+            self._timing.append((e0, e1))
+        else:
+            self.graphs[key].replay()
         self.replays += 1
         n = len(seqs)
         host = self.h_out2 if (ahead_of is not None and ahead_of.host is self.h_out) else self.h_out
@@ -264,6 +272,19 @@ class DecodeGraphs:
         adv = 0 if ahead_of is None else 1
         self.launch_s += time.perf_counter() - t0
         return _InFlight({s.rid: i for i, s in enumerate(seqs)}, {s.rid: s.start_pos + adv for s in seqs}, ev, host, n)
+
+    def timing_summary(self, last: int = 0) -> dict:
+        """With ``PEGAINFER_GRAPH_TIMING=1``: device time of the replays and of the gaps between
+        consecutive replays (copies, launch latency, a GPU waiting for the host), over the last
+        ``last`` replays (0 = all)."""
+        if not self._timing or len(self._timing) < 2:
+            return {}
+        torch.cuda.synchronize(self.device)
+        ev = self._timing[-last:] if last else self._timing
+        run = [a.elapsed_time(b) for a, b in ev]
+        gap = [ev[i][1].elapsed_time(ev[i + 1][0]) for i in range(len(ev) - 1)]
+        gap.sort()
+        return dict(replays=len(ev), graph_ms_mean=sum(run) / len(run), gap_ms_mean=sum(gap) / len(gap), gap_ms_p50=gap[len(gap) // 2], gap_ms_max=gap[-1])
 
     def covers(self, s) -> bool:
         """True if the step that is running ahead computes exactly this decode row."""

@@ -330,6 +330,46 @@ def test_gated_delta_net_kernels(dk, hk, hv):
     status_clean()
 
 
+@pytest.mark.parametrize("q_lens", [[200, 64, 1, 33, 130, 31], [2048], [65, 127]])
+def test_gated_delta_chunk_scan_matches_recurrence(q_lens):
+    """The 64-token chunk-wise tensor-core scan against the token-by-token rule (fp32 PyTorch
+    restatement and the recurrence kernel): ragged lengths, a partial last chunk, a decode row and
+    a short chunk in the same step (those two stay on the recurrence kernel), non-zero start state."""
+    torch.manual_seed(len(q_lens) * 31 + q_lens[0])
+    dk = dv = 128
+    hk, hv = 2, 4
+    slots = list(range(1, len(q_lens) + 1))
+    meta = _state_meta(q_lens, slots)
+    t = meta.num_tokens
+    q = torch.randn(t, hk, dk, device=DEV).bfloat16()
+    k = torch.randn(t, hk, dk, device=DEV).bfloat16()
+    v = torch.randn(t, hv, dv, device=DEV).bfloat16()
+    a = torch.randn(t, hv, device=DEV).bfloat16()
+    b = torch.randn(t, hv, device=DEV).bfloat16()
+    g, beta = R.gdn_gates(a, b, torch.randn(hv, device=DEV) * 0.5, torch.randn(hv, device=DEV) * 0.5)
+    s0 = torch.randn(len(q_lens) + 2, hv, dk, dv, device=DEV) * 0.1
+    s_ref, s_rec, s_chk = s0.clone(), s0.clone(), s0.clone()
+    o_ref = R.gdn_recurrent(q, k, v, g, beta, s_ref, meta)
+    o_rec = cu().gdn_recurrent(q, k, v, g, beta, s_rec, meta, chunked=False)
+    o_chk = cu().gdn_recurrent(q, k, v, g, beta, s_chk, meta, chunked=True)
+    torch.cuda.synchronize()
+    status_clean()
+    scale = o_ref.float().abs().max().item()
+    e_rec = (o_rec.float() - o_ref.float()).abs().max().item()
+    e_chk = (o_chk.float() - o_ref.float()).abs().max().item()
+    es_chk = (s_chk - s_ref).abs().max().item()
+    es_rec = (s_rec - s_ref).abs().max().item()
+    # bf16 operands (keys, corrections, the state as an operand) against the all-f32 rule
+    assert e_chk < 0.03 * scale + 2e-3, f"chunk scan out err {e_chk} (recurrence kernel {e_rec}, scale {scale})"
+    assert es_chk < 0.03 * s_ref.abs().max().item(), f"chunk scan state err {es_chk} (recurrence kernel {es_rec})"
+    assert torch.equal(s_chk[0], s0[0]) and torch.equal(s_chk[-1], s0[-1]), "slots of other requests are untouched"
+    # rows of the short sequences took the recurrence kernel in both runs
+    for i, n in enumerate(q_lens):
+        if n < 32:
+            lo = sum(q_lens[:i])
+            assert torch.equal(o_chk[lo : lo + n], o_rec[lo : lo + n])
+
+
 @pytest.mark.parametrize("scoring,e,k,ng,tg,norm", [("softmax", 64, 6, 1, 1, False), ("sigmoid", 384, 8, 1, 1, True), ("sigmoid", 64, 4, 8, 3, True), ("softmax", 16, 2, 4, 2, False)])
 def test_router_topk(scoring, e, k, ng, tg, norm):
     torch.manual_seed(e + k)

@@ -205,3 +205,26 @@ def test_serving_bench_harness_against_sim_engine(tmp_path):
     assert r["completed"] == 12 and r["failed"] == 0
     assert r["output_tokens"] == 12 * 6 and r["input_tokens"] == 12 * 24
     assert r["ttft_ms"]["p50"] > 0 and r["e2el_ms"]["p99"] >= r["ttft_ms"]["p50"]
+
+
+def test_waiting_updates_fold_into_one_event():
+    """A connection that fell behind gets everything that is waiting as one update: tokens in
+    order, logprobs aligned to them, the terminal last."""
+    import asyncio
+
+    from pegainfer_b200.engine.contract import FinishReason, RequestUpdate, Terminal, TokenLogprob
+    from pegainfer_b200.server.openai import _merge_updates
+
+    async def go():
+        q = asyncio.Queue()
+        q.put_nowait(RequestUpdate(id=7, tokens=[3], logprobs=[TokenLogprob(token=3, logprob=-0.5, top=[])]))
+        q.put_nowait(RequestUpdate(id=7, tokens=[4, 5], cached_tokens=16))
+        q.put_nowait(RequestUpdate(id=7, tokens=[6], terminal=Terminal.finished(FinishReason.LENGTH)))
+        q.put_nowait(RequestUpdate(id=7, tokens=[99]))  # never merged: it follows the terminal
+        first = RequestUpdate(id=7, tokens=[1, 2])
+        return _merge_updates(first, q), q.qsize()
+
+    m, left = asyncio.run(go())
+    assert m.tokens == [1, 2, 3, 4, 5, 6] and left == 1
+    assert [None if l is None else l.token for l in m.logprobs] == [None, None, 3, None, None, None]
+    assert m.cached_tokens == 16 and m.terminal.finish_reason == FinishReason.LENGTH
