@@ -525,7 +525,8 @@ __global__ void __launch_bounds__(128) prefill_attn_kernel(const AttnParams p, i
   // locate (sequence, q tile) for this CTA
   int b = 0, tile_in_seq = 0;
   {
-    int rem = blockIdx.x;
+    // late query tiles attend to the most keys: hand them out first so the long CTAs do not form the tail
+    int rem = (int)gridDim.x - 1 - (int)blockIdx.x;
     for (; b < p.num_seqs; ++b) {
       const int n = p.q_indptr[b + 1] - p.q_indptr[b];
       const int nt = (n + BQ - 1) / BQ;
