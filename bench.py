@@ -299,9 +299,9 @@ def e2e(args, eng, rank, world, device):
         os.makedirs(os.path.dirname(os.path.abspath(args.profile_host)), exist_ok=True)
         with open(args.profile_host, "w") as f:
             f.write(buf.getvalue())
-    ts = graphs.timing_summary(last=args.steps)
+    ts = graphs.timing_summary(last=graphs.replays - replays0)
     if ts and rank == 0:
-        print("graph timing over the last %d replays: %s" % (ts["replays"], json.dumps({k: round(v, 4) for k, v in ts.items()})), file=sys.stderr)
+        print("graph timing of the %d end-to-end replays: %s" % (ts["replays"], json.dumps({k: (round(v, 4) if isinstance(v, float) else v) for k, v in ts.items()})), file=sys.stderr)
     return dict(
         value=tokens / dt,
         ttft_p50_ms=1e3 * statistics.median(ttft),
@@ -343,7 +343,7 @@ def main():
     ramp = (args.conc + max(1, 4096 // args.prompt_len) - 1) // max(1, 4096 // args.prompt_len)
     total_len = args.prompt_len + args.warmup + args.steps + ramp + 2 * page
     blocks = 2 * args.conc * ((total_len + page - 1) // page + 2) + 8
-    ecfg = EngineConfig(preset=args.model, num_kv_blocks=blocks, kv_page_size=page, cuda_graph=True, precapture_graphs=True, max_decode_batch=max(args.conc, 8), max_model_len=total_len + page, max_prefill_tokens=4096, no_prefix_cache=True)
+    ecfg = EngineConfig(preset=args.model, num_kv_blocks=blocks, kv_page_size=page, cuda_graph=True, precapture_graphs=True, max_decode_batch=max(args.conc, 8), max_model_len=total_len + page, max_prefill_tokens=4096, no_prefix_cache=True, tune_gc=True)
     eng = build_engine(ecfg, mcfg, device=device, dtype=torch.bfloat16, tp=tp, start=False)
     try:
         ko = kernel_only(args, eng, rank, world, device)

@@ -305,7 +305,13 @@ extern "C" int pg_gemm2sm_eligible(int T, int M, int K) {
   // problems (K > 8192) stay on the one-CTA kernel as well: there the operand slabs that the
   // concurrently running 256 x 256 tiles share (17 slabs of 256 x K) approach the L2 capacity
   // and this kernel measured slower (493 vs 372 us at T = M = 4096, K = 12288).
-  if (T < 256 || M < 1024 || K < 256 || K > 8192 || K % 8 != 0) return 0;
+  static int max_k = 0;
+  if (max_k == 0) {
+    const char* e = getenv("PEGAINFER_GEMM_2SM_MAXK");
+    max_k = e ? atoi(e) : 8192;
+    if (max_k <= 0) max_k = 8192;
+  }
+  if (T < 256 || M < 1024 || K < 256 || K > max_k || K % 8 != 0) return 0;
   return (long long)ceil_div(M, 2 * BM) * ceil_div(T, 256) >= 64 ? 1 : 0;
 }
 

@@ -300,6 +300,7 @@ class EngineConfig:
     batch_invariant: bool = False
     decode_overlap: bool = False
     run_ahead: bool = True  # greedy graph decode launches the next step before reading this one's tokens
+    tune_gc: bool = False  # freeze start-up objects and raise the collector thresholds (utils/runtime.py); the server and the benches turn it on
     decode_sm_pct: int = 50
     enable_lora: bool = False
     max_loras: int = 4

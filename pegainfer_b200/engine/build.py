@@ -131,6 +131,10 @@ def build_engine(ecfg: EngineConfig, mcfg: Optional[ModelConfig] = None, device=
         vocab_size=mcfg.vocab_size,
         eos_token_ids=tuple(mcfg.eos_token_ids),
     )
+    if ecfg.tune_gc and device.type == "cuda":
+        from ..utils.runtime import tune_gc
+
+        tune_gc()
     eng = Engine([sched], info, start=start)
     eng.model, eng.executor, eng.scheduler, eng.pool, eng.kv, eng.host_tier = model, executor, sched, pool, kv, host_tier
     return eng

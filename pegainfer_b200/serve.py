@@ -106,6 +106,7 @@ def build_parser() -> argparse.ArgumentParser:
     x.add_argument("--spec-draft-len", type=int, default=1)
     x.add_argument("--decode-overlap", action="store_true")
     x.add_argument("--no-run-ahead", action="store_true", help="read every decode step's tokens before launching the next step")
+    x.add_argument("--no-gc-tuning", action="store_true", help="leave the interpreter's garbage collector at its defaults")
     x.add_argument("--decode-sm-pct", type=int, default=50)
     x.add_argument("--max-batch", type=int, default=64)
     x.add_argument("--ep-backend", choices=["fused", "nccl"], default=None)
@@ -145,7 +146,7 @@ def engine_config_from(ns: argparse.Namespace) -> EngineConfig:
         kv_page_size=ns.kv_page_size, num_kv_blocks=ns.num_kv_blocks, gpu_memory_utilization=ns.gpu_memory_utilization,
         kv_cache_memory_margin_mib=ns.kv_cache_memory_margin_mib, no_prefix_cache=ns.no_prefix_cache, kv_offload=ns.kv_offload,
         kv_offload_host_gib=ns.kv_offload_host_gib, max_prefill_tokens=ns.max_prefill_tokens, max_decode_batch=ns.max_decode_batch,
-        max_model_len=ns.max_model_len, batch_invariant=ns.batch_invariant, decode_overlap=ns.decode_overlap, run_ahead=not ns.no_run_ahead, decode_sm_pct=ns.decode_sm_pct,
+        max_model_len=ns.max_model_len, batch_invariant=ns.batch_invariant, decode_overlap=ns.decode_overlap, run_ahead=not ns.no_run_ahead, tune_gc=not ns.no_gc_tuning, decode_sm_pct=ns.decode_sm_pct,
         enable_lora=ns.enable_lora, max_loras=ns.max_loras, max_lora_rank=ns.max_lora_rank, lora_modules=tuple(ns.lora_modules), spec_method=ns.spec_method,
         spec_draft_len=ns.spec_draft_len, draft_model_path=ns.draft_model_path, comm=ns.ep_backend or ns.comm, gemm=ns.gemm, seed=ns.seed,
     )
