@@ -51,6 +51,7 @@ int pg_make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, long long rows, long
 
 // ---- row kernels (elementwise.cu) --------------------------------------------------
 int pg_gather_rows(const void* table, const void* ids, void* out, int rows, int width, long long table_rows, void* status, cudaStream_t stream);
+int pg_gather_words(const void* src, const void* idx, void* dst, int n, int src_len, void* status, cudaStream_t stream);
 int pg_rms_norm(const void* x, void* residual, const void* w, void* y, int rows, int width, float eps, int offset, int round_before,
                 long long ldx, long long ldr, long long ldy, cudaStream_t stream);
 int pg_gated_rms_norm(const void* x, const void* gate, const void* w_f32, void* y, long long rows, int dim, float eps, cudaStream_t stream);

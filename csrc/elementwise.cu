@@ -26,6 +26,20 @@ __global__ void gather_rows_kernel(const bf16* __restrict__ table, const int* __
   for (int i = threadIdx.x; i < width / 8; i += blockDim.x) dst[i] = src[i];
 }
 
+// dst[i] = src[idx[i]] for 32-bit words (token ids moved between decode steps on the device).
+__global__ void gather_words_kernel(const uint32_t* __restrict__ src, const int* __restrict__ idx, uint32_t* __restrict__ dst, int n, int src_len,
+                                    uint32_t* status) {
+  PG_PDL_ENTRY();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  int j = idx[i];
+  if (j < 0 || j >= src_len) {
+    atomicCAS(status, PG_ST_OK, PG_ST_BOUNDS | (12u << 8));
+    j = 0;
+  }
+  dst[i] = src[j];
+}
+
 // One CTA per row.  MODE 0: y = norm(x).  MODE 1: res += x; y = norm(res).
 template <int MODE>
 __global__ void __launch_bounds__(256) rms_norm_kernel(const bf16* __restrict__ x, bf16* __restrict__ residual, const bf16* __restrict__ w,
@@ -259,6 +273,13 @@ extern "C" int pg_gather_rows(const void* table, const void* ids, void* out, int
   PG_REQUIRE(width % 8 == 0, "gather_rows: width %d must be a multiple of 8", width);
   if (rows == 0) return PG_OK;
   PG_CUDA(launch_pdl(gather_rows_kernel, dim3(rows), dim3(128), (size_t)(0), stream, (const bf16*)table, (const int*)ids, (bf16*)out, rows, width, table_rows, (uint32_t*)status));
+  PG_LAUNCH_CHECK();
+  return PG_OK;
+}
+
+extern "C" int pg_gather_words(const void* src, const void* idx, void* dst, int n, int src_len, void* status, cudaStream_t stream) {
+  if (n <= 0) return PG_OK;
+  PG_CUDA(launch_pdl(gather_words_kernel, dim3((n + 127) / 128), dim3(128), (size_t)(0), stream, (const uint32_t*)src, (const int*)idx, (uint32_t*)dst, n, src_len, (uint32_t*)status));
   PG_LAUNCH_CHECK();
   return PG_OK;
 }

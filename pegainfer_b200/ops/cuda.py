@@ -144,6 +144,13 @@ def gather_rows(x, idx):
     return out
 
 
+def gather_words(src: torch.Tensor, idx: torch.Tensor, dst: torch.Tensor) -> None:
+    """``dst[i] = src[idx[i]]`` for int32 tensors (views allowed, unit stride)."""
+    assert src.dtype == dst.dtype == idx.dtype == torch.int32 and src.stride(0) == 1 and dst.stride(0) == 1 and idx.stride(0) == 1
+    c = ctx(src.device)
+    _check(lib().pg_gather_words(_ptr(src), _ptr(idx), _ptr(dst), _ci(dst.numel()), _ci(src.numel()), _ptr(c.status), _stream()), c)
+
+
 def _rows2d(x):
     x2 = x.reshape(-1, x.shape[-1])
     if x2.stride(-1) != 1:

@@ -82,6 +82,7 @@ class DecodeGraphs:
         self.ahead_launches = 0
         self.ahead_claimed = 0
         self._timing = [] if os.environ.get("PEGAINFER_GRAPH_TIMING") == "1" else None  # (start, end) events of every replay
+        self._host_ms = []  # (stage, replay call) host milliseconds per replay, with the timing switch
         self.wait_s = 0.0  # host time spent waiting for a step's tokens
         self.launch_s = 0.0  # host time spent staging and launching steps
         self.graphs: dict = {}
@@ -94,7 +95,7 @@ class DecodeGraphs:
         self.invalidate_table()
         # first use of a framework kernel loads its module (tens of milliseconds): do that now for the
         # two copies the run-ahead path issues between replays, not on a live decode step
-        torch.index_select(self.out_tokens, 0, self.d_small[4 * B : 4 * B + 1], out=self.d_small[:1])
+        _K().gather_words(self.out_tokens, self.d_small[4 * B : 4 * B + 1], self.d_small[:1])
         self.d_small[:1].copy_(self.out_tokens[:1], non_blocking=True)
         self.h_out[:1].copy_(self.out_tokens[:1], non_blocking=True)
         torch.cuda.synchronize(dev)
@@ -247,7 +248,7 @@ class DecodeGraphs:
             if toks == list(range(n)):
                 self.d_small[:n].copy_(self.out_tokens[:n], non_blocking=True)
             else:
-                torch.index_select(self.out_tokens, 0, self.d_small[4 * B : 4 * B + n], out=self.d_small[:n])
+                _K().gather_words(self.out_tokens, self.d_small[4 * B : 4 * B + n], self.d_small[:n])
         else:
             self.d_small[: 4 * B].copy_(self.h_small[: 4 * B], non_blocking=True)
             self.h2d_bytes += 4 * B * 4
@@ -265,11 +266,13 @@ class DecodeGraphs:
         t0 = time.perf_counter()
         self.stage(seqs, b, ahead_of)
         if self._timing is not None:
+            t1 = time.perf_counter()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             self.graphs[key].replay()
             e1.record()
             self._timing.append((e0, e1))
+            self._host_ms.append((round(1e3 * (t1 - t0), 3), round(1e3 * (time.perf_counter() - t1), 3)))
         else:
             self.graphs[key].replay()
         self.replays += 1
@@ -295,7 +298,7 @@ class DecodeGraphs:
         gap = [ev[i][1].elapsed_time(ev[i + 1][0]) for i in range(len(ev) - 1)]
         srt = sorted(gap)
         return dict(replays=len(ev), graph_ms_mean=sum(run) / len(run), gap_ms_mean=sum(gap) / len(gap), gap_ms_p50=srt[len(srt) // 2], gap_ms_max=srt[-1],
-                    graph_ms=[round(x, 3) for x in run], gap_ms=[round(x, 3) for x in gap])
+                    graph_ms=[round(x, 3) for x in run], gap_ms=[round(x, 3) for x in gap], host_stage_replay_ms=self._host_ms[-len(ev):])
 
     def covers(self, s) -> bool:
         """True if the step that is running ahead computes exactly this decode row."""
