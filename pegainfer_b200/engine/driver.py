@@ -145,9 +145,22 @@ class SchedulerHandle:
         return m.num_running_reqs + 4 * max(m.num_waiting_reqs, self.waiting_hint)
 
 
+def _bind_thread_to_device(scheduler) -> None:
+    """Make the executor's GPU the current CUDA device of the calling thread.  The current device
+    is per host thread and starts at device 0: on any other GPU a thread that does not do this
+    records events and picks "current" streams on the wrong device, and kernels launched through
+    the C API (which follow the thread's current device) land on GPU 0."""
+    dev = getattr(getattr(scheduler, "ex", None), "device", None)
+    if dev is not None and getattr(dev, "type", None) == "cuda":
+        import torch
+
+        torch.cuda.set_device(dev)
+
+
 def drive(scheduler, handle: SchedulerHandle, stop: threading.Event, idle_sleep: float = 0.0005) -> None:
     """Busy-poll drive loop for one scheduler partition."""
     ledger = RequestLedger(sink=handle.dispatch)
+    _bind_thread_to_device(scheduler)
     try:
         while not stop.is_set():
             drained = 0

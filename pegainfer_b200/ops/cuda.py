@@ -67,6 +67,10 @@ class lane_scratch:
 def ctx(device) -> _DeviceCtx:
     device = torch.device(device)
     idx = device.index if device.index is not None else torch.cuda.current_device()
+    if torch.cuda.current_device() != idx:
+        # kernels launched through the C API and torch.cuda.current_stream() follow the calling
+        # thread's current device, which starts at 0 in every new thread
+        torch.cuda.set_device(idx)
     key = (idx, 1 if _LANE[0] else 0)
     c = _CTX.get(key)
     if c is None:

@@ -42,6 +42,9 @@ def drive_replicated(scheduler, handle: SchedulerHandle, stop: threading.Event, 
     """Control loop of one rank.  ``mode``: "tp" (replicated scheduler) or "dp" (own partition)."""
     import torch.distributed as dist
 
+    from ..engine.driver import _bind_thread_to_device
+
+    _bind_thread_to_device(scheduler)  # the current CUDA device is per thread and starts at 0
     collected: list = []
     direct = rank == 0 and mode == "tp"
     ledger = RequestLedger(sink=handle.dispatch if direct else collected.append)

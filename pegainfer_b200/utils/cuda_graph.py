@@ -259,7 +259,7 @@ class DecodeGraphs:
             self._table_b, self._table_w = b, wmax
         if self._staged is None:
             self._staged = torch.cuda.Event()
-        self._staged.record()
+        self._staged.record(torch.cuda.current_stream(self.device))  # never "the current device's" stream: that is per thread
 
     def _launch(self, seqs, b: int, key, ahead_of: Optional[_InFlight] = None) -> _InFlight:
         """Stage, replay and queue the copy of the picked tokens into pinned memory."""
@@ -268,9 +268,9 @@ class DecodeGraphs:
         if self._timing is not None:
             t1 = time.perf_counter()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
+            e0.record(torch.cuda.current_stream(self.device))
             self.graphs[key].replay()
-            e1.record()
+            e1.record(torch.cuda.current_stream(self.device))
             self._timing.append((e0, e1))
             self._host_ms.append((round(1e3 * (t1 - t0), 3), round(1e3 * (time.perf_counter() - t1), 3)))
         else:
@@ -281,7 +281,7 @@ class DecodeGraphs:
         host[:n].copy_(self.out_tokens[:n], non_blocking=True)
         self.d2h_bytes += n * 4
         ev = torch.cuda.Event()
-        ev.record()
+        ev.record(torch.cuda.current_stream(self.device))
         adv = 0 if ahead_of is None else 1
         self.launch_s += time.perf_counter() - t0
         return _InFlight({s.rid: i for i, s in enumerate(seqs)}, {s.rid: s.start_pos + adv for s in seqs}, ev, host, n)

@@ -83,6 +83,34 @@ def main():
     assert torch.equal(captured.float(), eager), "graph replay differs from eager"
     assert K.read_status(dev) == 0, f"status {K.read_status(dev):#x}"
     dist.barrier()
+
+    # The whole engine on every rank: scheduler thread, CUDA-graph decode with run-ahead, requests
+    # that end at different lengths (rows are squeezed out between steps).  Every rank must read the
+    # same tokens on the host: the scheduler thread of a rank other than 0 starts with GPU 0 as its
+    # current device, and anything that follows "the current device" there goes wrong quietly.
+    from pegainfer_b200.config import EngineConfig
+    from pegainfer_b200.engine.build import build_engine
+    from pegainfer_b200.engine.contract import Request, SamplingParams
+
+    ecfg = EngineConfig(preset="qwen3-0.6b", num_kv_blocks=256, cuda_graph=True, max_decode_batch=8, max_model_len=512, max_prefill_tokens=256, no_prefix_cache=True)
+    eng = build_engine(ecfg, mcfg, device=dev, dtype=torch.bfloat16, tp=tp_f, model=models["fused"], start=False)
+    limits = [24, 7, 15, 24, 11]
+    streams = [
+        eng.submit(Request(prompt_tokens=torch.randint(0, 4096, (20 + 9 * i,), generator=g).tolist(), params=SamplingParams(temperature=0.0, ignore_eos=True), max_tokens=n))
+        for i, n in enumerate(limits)
+    ]
+    eng.start()  # all requests queued first: the replicated schedulers see the same admission order
+    outs = [s.collect(120)[0] for s in streams]
+    torch.cuda.synchronize()
+    assert [len(o) for o in outs] == limits
+    assert eng.executor._graphs.ahead_claimed > 10
+    flat = torch.tensor([t for o in outs for t in o], dtype=torch.int64, device=dev)
+    gathered = [torch.empty_like(flat) for _ in range(world)]
+    dist.all_gather(gathered, flat)
+    assert all(torch.equal(gathered[0], t) for t in gathered), "ranks read different tokens on the host"
+    assert K.read_status(dev) == 0, f"status {K.read_status(dev):#x}"
+    eng.shutdown()
+    dist.barrier()
     if rank == 0:
         print("TP_OK", flush=True)
     dist.destroy_process_group()
