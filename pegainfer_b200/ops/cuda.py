@@ -454,7 +454,11 @@ def gdn_recurrent(q, k, v, g, beta, state, meta: AttnMeta, chunked: Optional[boo
     if chunked:
         rc = lib().pg_gdn_chunked(*args, _ci(_GDN_CHUNK_MIN), _stream())
         _check(rc, c)
-    if not chunked or meta.num_seqs > 1:
+    short_rows = True  # is there a sequence below the chunk threshold (decode rows in a unified step)?
+    if chunked and meta.h_q_indptr is not None:
+        qi = meta.h_q_indptr
+        short_rows = any(qi[i + 1] - qi[i] < _GDN_CHUNK_MIN for i in range(meta.num_seqs))
+    if not chunked or short_rows:
         rc = lib().pg_gdn_recurrent(*args, _ci(int(meta.max_q_len)), _ci(_GDN_CHUNK_MIN if chunked else 0), _stream())
         _check(rc, c)
     return out
