@@ -12,7 +12,9 @@
 // Every product is a bf16 mma.sync with f32 accumulation; the state itself stays in f32
 // registers (as the accumulator of the last product) for the whole sequence and is rounded to
 // bf16 only as an operand.  All decay factors that appear are exp of a non-positive number.
-// T comes from forward substitution in f32 (64 columns x 4 lanes, fully unrolled).
+// T comes from forward substitution in f32 (64 columns x 4 lanes, fully unrolled).  The raw
+// rows of the next chunk are copied into a staging buffer by cp.async while the current
+// chunk is processed.
 //
 // CTA = (sequence, value head, half of the Dv columns); 8 warps.  Takes the place of the
 // reference's chunk-wise Triton pipeline (pegainfer-kernels/tools/triton/
@@ -43,6 +45,12 @@ __device__ __forceinline__ void mma16816(float* c, const uint32_t* a, uint32_t b
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const int sz = valid ? 16 : 0;  // 0: nothing is read, the 16 bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -82,6 +90,9 @@ struct ChunkSmem {
   bf16 p[C * LDV];    // masked, decayed Q K^T
   bf16 d[C * LDV];    // D = U - W S0
   bf16 s[DK * LDV];   // bf16 copy of the state, [dk][dv]
+  bf16 raw_k[C * LDK];  // next chunk's raw k, q, v rows (cp.async staging, filled while this chunk is processed)
+  bf16 raw_q[C * LDK];
+  bf16 raw_v[C * LDV];
   float a[C * LDA];   // A (strictly lower part is used)
   float gsum[C];      // G_i
   float beta[C];
@@ -120,33 +131,58 @@ gdn_chunk_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, long lo
     *reinterpret_cast<uint32_t*>(&sm.s[(warp * 16 + gq + 8) * LDV + col]) = pack2(hi.x, hi.y);
   }
 
+  // Raw rows of a chunk go to shared memory by cp.async (rows past the sequence end are
+  // zero-filled); the copy of chunk c + 1 is started once chunk c has been read out of the
+  // staging buffers and lands while chunk c is processed.
+  auto stage_chunk = [&](int t0) {
+    const int nt = min(C, q1 - t0);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int c = tid + 256 * i, r = c >> 4, ch = c & 15;  // 64 rows x 16 chunks of 8 elements
+      const bool ok = r < nt;
+      const long long src_row = (long long)(t0 + (ok ? r : 0)) * ld_qk + (long long)kh * DK + ch * 8;
+      cp_async16(&sm.raw_k[r * LDK + ch * 8], k + src_row, ok);
+      cp_async16(&sm.raw_q[r * LDK + ch * 8], q + src_row, ok);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int c = tid + 256 * i, r = c >> 3, ch = c & 7;  // 64 rows x 8 chunks
+      const bool ok = r < nt;
+      cp_async16(&sm.raw_v[r * LDV + ch * 8], v + (long long)(t0 + (ok ? r : 0)) * ld_v + (long long)h * dv + dv0 + ch * 8, ok);
+    }
+    cp_async_commit();
+  };
+  stage_chunk(q0);
+
   for (int t0 = q0; t0 < q1; t0 += C) {
     const int nt = min(C, q1 - t0);
-    // ---- phase A: load, normalise, decay sums -----------------------------------------
+    // ---- phase A: normalise the staged rows, decay sums ---------------------------------
     // thread = (row = tid / 4, quarter = tid % 4): 32 elements of q and k of one token
     const int row = tid >> 2, qt = tid & 3;
-    const bool live = row < nt;
     float kf[32], qf[32];
+    float g_raw = 0.f, b_raw = 0.f;
+    if (warp < 2) {
+      const int r = warp * 32 + lane;
+      if (r < nt) {
+        g_raw = g[(long long)(t0 + r) * hv + h];
+        b_raw = beta[(long long)(t0 + r) * hv + h];
+      }
+    }
+    cp_async_wait_all();
+    __syncthreads();
     {
-      const bf16* kp = k + (long long)(t0 + row) * ld_qk + (long long)kh * DK + qt * 32;
-      const bf16* qp = q + (long long)(t0 + row) * ld_qk + (long long)kh * DK + qt * 32;
       float ks = 0.f, qs = 0.f;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        bf16x8 kk, qq;
-        if (live) {
-          kk = *reinterpret_cast<const bf16x8*>(kp + i * 8);
-          qq = *reinterpret_cast<const bf16x8*>(qp + i * 8);
-        }
+        const bf16x8 kk = *reinterpret_cast<const bf16x8*>(&sm.raw_k[row * LDK + qt * 32 + i * 8]);
+        const bf16x8 qq = *reinterpret_cast<const bf16x8*>(&sm.raw_q[row * LDK + qt * 32 + i * 8]);
         float kt[8], qtmp[8];
-        if (live) {
-          unpack8(kk, kt);
-          unpack8(qq, qtmp);
-        }
+        unpack8(kk, kt);
+        unpack8(qq, qtmp);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          kf[i * 8 + e] = live ? kt[e] : 0.f;
-          qf[i * 8 + e] = live ? qtmp[e] : 0.f;
+          kf[i * 8 + e] = kt[e];
+          qf[i * 8 + e] = qtmp[e];
           ks += kf[i * 8 + e] * kf[i * 8 + e];
           qs += qf[i * 8 + e] * qf[i * 8 + e];
         }
@@ -170,14 +206,14 @@ gdn_chunk_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, long lo
     if (warp < 2) {
       // inclusive scan of g over the 64 rows (two warps, the second adds the first's total)
       const int r = warp * 32 + lane;
-      float x = r < nt ? g[(long long)(t0 + r) * hv + h] : 0.f;
+      float x = g_raw;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         const float y = __shfl_up_sync(0xffffffffu, x, o);
         if (lane >= o) x += y;
       }
       sm.gsum[r] = x;  // warp 1 holds partial sums until the fix-up below
-      sm.beta[r] = r < nt ? beta[(long long)(t0 + r) * hv + h] : 0.f;
+      sm.beta[r] = b_raw;
     }
     __syncthreads();
     if (warp == 1) sm.gsum[32 + lane] += sm.gsum[31];
@@ -191,20 +227,18 @@ gdn_chunk_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, long lo
         *reinterpret_cast<uint32_t*>(&sm.kd[row * LDK + qt * 32 + 2 * i]) = pack2(kf[2 * i] * fd, kf[2 * i + 1] * fd);
       }
       // beta * V: 16 columns of this token per thread
-      const bf16* vp = v + (long long)(t0 + row) * ld_v + (long long)h * dv + dv0 + qt * 16;
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
         float vt[8];
-        if (live) {
-          const bf16x8 vv = *reinterpret_cast<const bf16x8*>(vp + i * 8);
-          unpack8(vv, vt);
-        }
+        const bf16x8 vv = *reinterpret_cast<const bf16x8*>(&sm.raw_v[row * LDV + qt * 16 + i * 8]);
+        unpack8(vv, vt);
 #pragma unroll
         for (int e = 0; e < 4; ++e)
-          *reinterpret_cast<uint32_t*>(&sm.vb[row * LDV + qt * 16 + i * 8 + 2 * e]) = live ? pack2(vt[2 * e] * bi, vt[2 * e + 1] * bi) : 0u;
+          *reinterpret_cast<uint32_t*>(&sm.vb[row * LDV + qt * 16 + i * 8 + 2 * e]) = pack2(vt[2 * e] * bi, vt[2 * e + 1] * bi);
       }
     }
     __syncthreads();
+    if (t0 + C < q1) stage_chunk(t0 + C);  // every thread has read this chunk out of the staging buffers
 
     // ---- phase B: K K^T and Q K^T (64 x 64 each), warp = 16 rows x 32 columns ----------
     {
