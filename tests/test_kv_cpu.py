@@ -266,3 +266,28 @@ def test_run_ahead_lookahead_pages_and_final_marks():
     sched2 = ContinuousScheduler(ex2, BlockPool(8, bs), SchedulerConfig(max_prefill_tokens=64, max_decode_batch=8, max_model_len=12, run_ahead=True))
     out = _drive(sched2, [Request(prompt_tokens=list(range(6)), max_tokens=50)])
     assert out[1][-1].terminal.finish_reason == FinishReason.LENGTH and ex2.wasted == 0 and sched2.failed_batches == 0
+
+
+def test_thread_binding_and_gc_tuning_are_safe_without_a_gpu():
+    """The scheduler thread binds to the executor's GPU when there is one and does nothing on CPU;
+    the collector tuning can be applied more than once."""
+    import gc
+
+    from pegainfer_b200.engine.driver import _bind_thread_to_device
+    from pegainfer_b200.utils.runtime import tune_gc
+
+    class _S:
+        ex = FakeExecutor()
+
+    _bind_thread_to_device(_S())  # no device attribute
+    _S.ex.device = torch.device("cpu")
+    _bind_thread_to_device(_S())
+    before = gc.get_threshold()
+    try:
+        tune_gc()
+        tune_gc()
+        assert gc.get_threshold()[0] >= 50_000
+        assert gc.get_freeze_count() > 0
+    finally:
+        gc.unfreeze()
+        gc.set_threshold(*before)
