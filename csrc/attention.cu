@@ -508,8 +508,9 @@ __global__ void __launch_bounds__(128) decode_merge_kernel(const AttnParams p) {
 // -----------------------------------------------------------------------------------
 // prefill / mixed
 // -----------------------------------------------------------------------------------
-template <int D>
-__global__ void __launch_bounds__(128) prefill_attn_kernel(const AttnParams p, int window) {
+// MINB: CTAs per SM the register allocation aims for (3 costs a few spilled words at D = 128).
+template <int D, int MINB>
+__global__ void __launch_bounds__(128, MINB) prefill_attn_kernel(const AttnParams p, int window) {
   PG_PDL_ENTRY();
   extern __shared__ __align__(128) uint8_t smem_raw[];
   constexpr int BQ = 64, BKV = 64;
@@ -581,17 +582,35 @@ __global__ void __launch_bounds__(128) prefill_attn_kernel(const AttnParams p, i
   const int kv_end = min(kv_len, max_pos + 1);
   const int n_kv_tiles = (kv_end - kv_start + BKV - 1) / BKV;
 
+  // A thread copies the same 16-byte chunk `ch` of RPT rows of every K and V tile.  Tiles start at
+  // multiples of 64 tokens and pages hold 16, 32 or 64, so a tile spans at most four pages: their
+  // table entries are read once per tile and the row addresses follow by shifts (a table lookup and
+  // a division per chunk made address generation the larger part of this kernel's instructions).
+  constexpr int RPT = BKV * CH / 128, RSTEP = 128 / CH;
+  const int ps_shift = __ffs(p.page_size) - 1;
+  const long long row_stride = (long long)p.hkv * D;
+  const long long v_plane = (long long)p.page_size * row_stride;
+  const int my_ch = threadIdx.x % CH, my_r0 = threadIdx.x / CH;
+  const bf16* kv_head = p.kv + (long long)h * D + my_ch * 8;
   auto issue = [&](int kt, int stage) {
     bf16* ks_ = sm + stage * 2 * TILE_ELEMS;
     bf16* vs_ = ks_ + TILE_ELEMS;
     if (kt < n_kv_tiles) {
-      for (int c = threadIdx.x; c < BKV * CH; c += 128) {
-        const int r = c / CH, ch = c % CH;
-        const int tok = kv_start + kt * BKV + r;
-        const bool valid = tok < kv_end;
-        const int tk = valid ? tok : 0;
-        cp_async16(ks_ + swz<D>(r, ch), kv_row<D>(p, table_row, tk, h, 0) + ch * 8, valid);
-        cp_async16(vs_ + swz<D>(r, ch), kv_row<D>(p, table_row, tk, h, 1) + ch * 8, valid);
+      const int tok_base = kv_start + kt * BKV;
+      const int pg_first = tok_base >> ps_shift;
+      int pg[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) pg[j] = (j << ps_shift) < BKV ? table_row[min(pg_first + j, p.table_stride - 1)] : 0;
+#pragma unroll
+      for (int i = 0; i < RPT; ++i) {
+        const int r = my_r0 + i * RSTEP;
+        const bool valid = tok_base + r < kv_end;
+        const int rr = valid ? r : 0;
+        const int j = rr >> ps_shift;
+        const int page = j == 0 ? pg[0] : j == 1 ? pg[1] : j == 2 ? pg[2] : pg[3];
+        const bf16* src = kv_head + ((long long)page * 2 * p.page_size + (rr & (p.page_size - 1))) * row_stride;
+        cp_async16(ks_ + swz<D>(r, my_ch), src, valid);
+        cp_async16(vs_ + swz<D>(r, my_ch), src + v_plane, valid);
       }
     }
     cp_async_commit();
@@ -760,18 +779,32 @@ int launch_decode(const AttnParams& p, cudaStream_t stream) {
   return launch_decode_s<D, 3>(p, stream);
 }
 
-template <int D>
-int launch_prefill(const AttnParams& p, int q_tiles, int window, cudaStream_t stream) {
+int g_prefill_ctas = 0;  // PEGAINFER_PREFILL_CTAS=2|3: register budget of the prefill kernel (CTAs per SM)
+
+template <int D, int MINB>
+int launch_prefill_b(const AttnParams& p, int q_tiles, int window, cudaStream_t stream) {
   const size_t smem = (size_t)2 * 2 * 64 * D * 2;
   static bool set = false;
   if (!set) {
-    PG_CUDA(cudaFuncSetAttribute(prefill_attn_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    PG_CUDA(cudaFuncSetAttribute(prefill_attn_kernel<D, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     set = true;
   }
   dim3 grid(q_tiles, p.hq);
-  PG_CUDA(launch_pdl(prefill_attn_kernel<D>, dim3(grid), dim3(128), (size_t)(smem), stream, p, window));
+  PG_CUDA(launch_pdl(prefill_attn_kernel<D, MINB>, dim3(grid), dim3(128), (size_t)(smem), stream, p, window));
   PG_LAUNCH_CHECK();
   return PG_OK;
+}
+
+template <int D>
+int launch_prefill(const AttnParams& p, int q_tiles, int window, cudaStream_t stream) {
+  if (g_prefill_ctas == 0) {
+    const char* e = getenv("PEGAINFER_PREFILL_CTAS");
+    g_prefill_ctas = (e && e[0] == '3') ? 3 : 2;
+  }
+  if constexpr (D <= 128) {
+    if (g_prefill_ctas == 3) return launch_prefill_b<D, 3>(p, q_tiles, window, stream);
+  }
+  return launch_prefill_b<D, (D <= 128 ? 2 : 1)>(p, q_tiles, window, stream);
 }
 
 }  // namespace
