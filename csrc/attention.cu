@@ -643,17 +643,32 @@ __global__ void __launch_bounds__(128, MINB) prefill_attn_kernel(const AttnParam
       }
     }
     float mx[2] = {NEG_BIG, NEG_BIG};
+    // every key of the tile is visible to every row of this warp (all but the tiles on the
+    // diagonal of a causal prompt): no per-element position tests
+    const bool full_tile = window <= 0 && tok_base + BKV - 1 <= pos_base + warp * 16 && tok_base + BKV <= kv_end;
+    if (full_tile) {
 #pragma unroll
-    for (int n = 0; n < BKV / 8; ++n) {
+      for (int n = 0; n < BKV / 8; ++n) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int tok = tok_base + n * 8 + 2 * t4 + (e & 1);
-        const int qp = qpos0 + (e >> 1) * 8;
-        bool ok = tok <= qp && tok < kv_end;
-        if (window > 0) ok = ok && tok > qp - window;
-        const float v = ok ? s_acc[n][e] * p.scale_log2 : NEG_BIG;
-        s_acc[n][e] = v;
-        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+        for (int e = 0; e < 4; ++e) {
+          const float v = s_acc[n][e] * p.scale_log2;
+          s_acc[n][e] = v;
+          mx[e >> 1] = fmaxf(mx[e >> 1], v);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int n = 0; n < BKV / 8; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int tok = tok_base + n * 8 + 2 * t4 + (e & 1);
+          const int qp = qpos0 + (e >> 1) * 8;
+          bool ok = tok <= qp && tok < kv_end;
+          if (window > 0) ok = ok && tok > qp - window;
+          const float v = ok ? s_acc[n][e] * p.scale_log2 : NEG_BIG;
+          s_acc[n][e] = v;
+          mx[e >> 1] = fmaxf(mx[e >> 1], v);
+        }
       }
     }
     float corr[2];

@@ -188,17 +188,32 @@ __global__ void __launch_bounds__(128) mla_attn_kernel(const MlaParams p) {
   for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
   float m_run[2] = {NEG_BIG, NEG_BIG}, l_run[2] = {0.f, 0.f};
 
+  // A 32-token tile starts at a multiple of 32 and pages hold 16, 32 or 64 tokens: at most two
+  // page-table entries per tile, read once; a thread's 18 chunks follow by stepping (row, chunk)
+  // instead of dividing by 72 and by the page size for every 16 bytes.
+  const int ps_shift = __ffs(p.page_size) - 1;
+  const int c0_r = threadIdx.x / CHUNKS, c0_ch = threadIdx.x % CHUNKS;
   auto issue = [&](int tile, int stage) {
     bf16* dst = tile_sm + stage * TILE * W;
     if (tile < t_end) {
-      for (int c = threadIdx.x; c < TILE * CHUNKS; c += 128) {
-        const int r = c / CHUNKS, ch = c % CHUNKS;
-        const int tok = tile * TILE + r;
-        const bool valid = tok < kv_end;
-        const int tk = valid ? tok : 0;
-        const int page = table_row[tk / p.page_size];
-        const bf16* src = p.latent + ((long long)page * p.page_size + tk % p.page_size) * W + ch * 8;
+      const int tok_base = tile * TILE;
+      const int pf = tok_base >> ps_shift;
+      const int pg0 = table_row[min(pf, p.table_stride - 1)];
+      const int pg1 = (1 << ps_shift) < TILE ? table_row[min(pf + 1, p.table_stride - 1)] : pg0;
+      int r = c0_r, ch = c0_ch;
+#pragma unroll
+      for (int i = 0; i < TILE * CHUNKS / 128; ++i) {
+        const bool valid = tok_base + r < kv_end;
+        const int rr = valid ? r : 0;
+        const int page = (rr >> ps_shift) ? pg1 : pg0;
+        const bf16* src = p.latent + ((long long)page * p.page_size + ((tok_base + rr) & (p.page_size - 1))) * W + ch * 8;
         cp_async16(dst + swz(r, ch), src, valid);
+        ch += 128 % CHUNKS;
+        r += 128 / CHUNKS;
+        if (ch >= CHUNKS) {
+          ch -= CHUNKS;
+          ++r;
+        }
       }
     }
     cp_async_commit();

@@ -309,6 +309,9 @@ def batch_invariant() -> bool:
     return _BATCH_INVARIANT
 
 
+_MIXED_DECODE_MIN = 4  # fewer trailing decode rows than this stay in the prefill kernel of a unified step
+
+
 def plan_decode_splits(num_seqs: int, hkv: int, max_kv_len: int, device) -> int:
     if _BATCH_INVARIANT:
         return INVARIANT_KV_SPLITS
@@ -325,29 +328,45 @@ def paged_attention(q, kv_layer, meta: AttnMeta, scale=None, window=0, out: Opti
         out = torch.empty((t, hq * d), dtype=q.dtype, device=q.device)
     c = ctx(q.device)
     table = meta.block_table
-    if meta.decode_only and window == 0:
-        splits = meta.plan if isinstance(meta.plan, int) else plan_decode_splits(meta.num_seqs, hkv, meta.max_kv_len, q.device)
-        need = meta.num_seqs * hq * splits * (d + 1) * 4
+
+    def decode_rows(first: int, n: int, plan=None):
+        """Decode kernel (one query row per sequence, the Q heads of a KV head packed into one MMA
+        tile, split KV) over sequences ``first .. first + n``; rows are found through q_indptr."""
+        splits = plan if isinstance(plan, int) else plan_decode_splits(n, hkv, meta.max_kv_len, q.device)
+        need = n * hq * splits * (d + 1) * 4
         if need > c.attn_part.numel():
-            splits = max(1, c.attn_part.numel() // (meta.num_seqs * hq * (d + 1) * 4))
-        part_o = c.attn_part
-        lse_off = meta.num_seqs * hq * splits * d * 4
-        part_lse = c.attn_part[lse_off:]
+            splits = max(1, c.attn_part.numel() // (n * hq * (d + 1) * 4))
+        lse_off = n * hq * splits * d * 4
         rc = lib().pg_paged_attention(
-            _ptr(q), _ptr(kv_layer), _ptr(out), _ptr(meta.q_indptr), _ptr(meta.kv_lens), _ptr(table), _ci(table.stride(0)), _ci(meta.num_seqs),
-            _ci(hq), _ci(hkv), _ci(d), _ci(page_size), _ll(kv_layer.shape[0]), _cf(scale), _ci(0), _ci(splits), _ptr(part_o), _ptr(part_lse),
+            _ptr(q), _ptr(kv_layer), _ptr(out), _ptr(meta.q_indptr[first:]), _ptr(meta.kv_lens[first:]), _ptr(table[first:]), _ci(table.stride(0)), _ci(n),
+            _ci(hq), _ci(hkv), _ci(d), _ci(page_size), _ll(kv_layer.shape[0]), _cf(scale), _ci(0), _ci(splits), _ptr(c.attn_part), _ptr(c.attn_part[lse_off:]),
             _ci(0), _ci(0), _ptr(c.status), _stream(),
         )
         _check(rc, c, 2 if splits > 1 else 1)
+
+    if meta.decode_only and window == 0:
+        decode_rows(0, meta.num_seqs, meta.plan)
         return out
     qi = meta.h_q_indptr if meta.h_q_indptr is not None else meta.q_indptr.tolist()
-    q_tiles = sum((qi[b + 1] - qi[b] + 63) // 64 for b in range(meta.num_seqs))
-    rc = lib().pg_paged_attention(
-        _ptr(q), _ptr(kv_layer), _ptr(out), _ptr(meta.q_indptr), _ptr(meta.kv_lens), _ptr(table), _ci(table.stride(0)), _ci(meta.num_seqs),
-        _ci(hq), _ci(hkv), _ci(d), _ci(page_size), _ll(kv_layer.shape[0]), _cf(scale), _ci(1), _ci(1), _vp(0), _vp(0), _ci(q_tiles), _ci(window),
-        _ptr(c.status), _stream(),
-    )
-    _check(rc, c)
+    n_pf = meta.num_seqs
+    if window == 0:
+        # A unified step lists its prompt chunks first and its decode rows last.  Through the prefill
+        # kernel a decode row is a 64-row query tile with one live row per Q head, and 63 of them cost
+        # several times the chunk itself; the trailing single-row sequences take the decode kernel.
+        while n_pf > 0 and qi[n_pf] - qi[n_pf - 1] == 1:
+            n_pf -= 1
+        if meta.num_seqs - n_pf < _MIXED_DECODE_MIN:
+            n_pf = meta.num_seqs
+    if n_pf > 0:
+        q_tiles = sum((qi[b + 1] - qi[b] + 63) // 64 for b in range(n_pf))
+        rc = lib().pg_paged_attention(
+            _ptr(q), _ptr(kv_layer), _ptr(out), _ptr(meta.q_indptr), _ptr(meta.kv_lens), _ptr(table), _ci(table.stride(0)), _ci(n_pf),
+            _ci(hq), _ci(hkv), _ci(d), _ci(page_size), _ll(kv_layer.shape[0]), _cf(scale), _ci(1), _ci(1), _vp(0), _vp(0), _ci(q_tiles), _ci(window),
+            _ptr(c.status), _stream(),
+        )
+        _check(rc, c)
+    if n_pf < meta.num_seqs:
+        decode_rows(n_pf, meta.num_seqs - n_pf)
     return out
 
 

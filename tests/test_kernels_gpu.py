@@ -191,6 +191,27 @@ def test_prefill_attention_ragged_and_mixed(d, hq, hkv, page):
     status_clean()
 
 
+@pytest.mark.parametrize("d,hq,hkv,page", [(128, 32, 8, 16), (256, 24, 4, 64)])
+def test_unified_step_attention_splits_chunks_and_decode_rows(d, hq, hkv, page):
+    """A unified step (prompt chunks first, decode rows last): the trailing single-row sequences take
+    the decode kernel, the chunks the prefill kernel, and together they match the reference; with
+    fewer than four decode rows everything stays in the prefill kernel."""
+    torch.manual_seed(d + 1)
+    for q_lens, kv_lens in (([130, 64, 1, 1, 1, 1, 1, 1], [130, 300, 40, 1025, 1, 333, 16, 17]), ([70, 1, 1], [200, 90, 5]), ([1, 1, 1, 1, 1, 90], [9, 8, 7, 6, 5, 90])):
+        kv, meta = make_batch(q_lens, kv_lens, page, hkv, d)
+        q = torch.randn(meta.num_tokens, hq, d, device=DEV).bfloat16()
+        ref = R.paged_attention(q, kv, meta)
+        before = cu().launch_count(DEV)
+        out = cu().paged_attention(q, kv, meta)
+        launches = cu().launch_count(DEV) - before
+        bf16_close(out, ref, rel=2 ** -6, abs_=6e-3)
+        trailing = 0
+        while trailing < len(q_lens) and q_lens[len(q_lens) - 1 - trailing] == 1:
+            trailing += 1
+        assert (launches >= 2) == (trailing >= 4), (q_lens, launches)
+    status_clean()
+
+
 @pytest.mark.parametrize("d,rot,gated,offset", [(128, 128, False, False), (64, 64, False, False), (256, 64, True, True)])
 def test_qk_norm_rope_append(d, rot, gated, offset):
     torch.manual_seed(rot)
