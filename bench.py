@@ -114,7 +114,7 @@ def hard_exit(code: int = 0):
 def reference_arm(args):
     # The reference is a Rust workspace (Cargo.toml, no setup.py / pyproject.toml); pip cannot
     # install it, there is no cargo here, and its kernel submodules are empty.
-    print(json.dumps({"impl": "reference", "unavailable": "reference is a Rust/cargo workspace: `pip install /root/reference` fails (neither setup.py nor pyproject.toml), no Rust toolchain in the image"}))
+    print(json.dumps({"impl": "reference", "unavailable": "reference is a Rust/cargo workspace: pip install of its tree fails (neither setup.py nor pyproject.toml), no Rust toolchain in the image"}))
     return 0
 
 
