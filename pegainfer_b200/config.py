@@ -254,14 +254,15 @@ def from_hf(cfg: dict, model_dir: Optional[str] = None) -> ModelConfig:
         norm_topk_prob=bool(cfg.get("norm_topk_prob", False)),
         routed_scaling_factor=cfg.get("routed_scaling_factor", 1.0),
     )
+    q = cfg.get("quantization_config") or top.get("quantization_config") or {}
+    quant = "bf16"
+    if q.get("quant_method") == "compressed-tensors" or q.get("format") == "pack-quantized":
+        quant = "int4_g32"
+    elif q.get("quant_method") == "fp8":
+        quant = "fp8_block128"
+    mla.update(expert_quant=quant)
     if family == "kimi_k2":
-        q = cfg.get("quantization_config") or top.get("quantization_config") or {}
-        quant = "bf16"
-        if q.get("quant_method") == "compressed-tensors" or q.get("format") == "pack-quantized":
-            quant = "int4_g32"
-        elif q.get("quant_method") == "fp8":
-            quant = "fp8_block128"
-        mla.update(router_bias=True, expert_quant=quant, num_mtp_layers=cfg.get("num_nextn_predict_layers", 0))
+        mla.update(router_bias=True, num_mtp_layers=cfg.get("num_nextn_predict_layers", 0))
     return ModelConfig(**common, **mla)
 
 

@@ -35,3 +35,13 @@ def build(cfg: ModelConfig, **kw):
     if cfg.family not in BUILDERS:
         raise ValueError(f"no model line for family {cfg.family!r}; known: {sorted(BUILDERS)}")
     return BUILDERS[cfg.family](cfg, **kw)
+
+
+def shapes_for(cfg: ModelConfig) -> dict:
+    """Full (unsharded) tensor shapes of a model family that has no entry in ``loader.export``."""
+    raise ValueError(f"no tensor-shape table for family {cfg.family!r}")
+
+
+def hf_config_extras(cfg: ModelConfig) -> dict:
+    """Family-specific ``config.json`` keys for ``loader.export.to_hf_config``."""
+    return {}

@@ -93,6 +93,13 @@ def logprobs_topk(logits, picked, k):
     return _impl(logits).logprobs_topk(logits, picked, k)
 
 
+# Load-time and test helpers that are plain tensor arithmetic on whatever device their inputs
+# live on (quantisers, repackers, RoPE tables, the dense-attention oracle): these have no kernel.
+_HOST_UTILS = frozenset(
+    ("rope_tables", "dense_causal_attention", "filtered_probs", "dequant_int4_g32", "quant_int4_g32", "repack_int4_pairs", "unrepack_int4_pairs", "plain_int4", "dequant_fp8_block", "quant_fp8_block")
+)
+
+
 def __getattr__(name):
     # ops added by later model families (MLA, MoE, GDN) resolve lazily
     if hasattr(reference, name):
@@ -101,7 +108,11 @@ def __getattr__(name):
 
             first = next((a for a in args if isinstance(a, torch.Tensor)), None)
             impl = _impl(first) if first is not None else reference
-            fn = getattr(impl, name, None) or getattr(reference, name)
+            fn = getattr(impl, name, None)
+            if fn is None:
+                if name not in _HOST_UTILS:
+                    raise NotImplementedError(f"ops.{name}: no sm_100a kernel for this op; refusing to run the PyTorch restatement on a CUDA tensor (use ops.mode('library') for the comparison arm)")
+                fn = getattr(reference, name)
             return fn(*args, **kwargs)
 
         return _dispatch

@@ -166,9 +166,7 @@ def rms_norm(x, w, eps, offset=False):
     _bf16(x)
     x2 = _rows2d(x)
     if x2.shape[1] % 8 != 0:
-        from . import reference
-
-        return reference.rms_norm(x, w, eps, offset)
+        raise ValueError(f"rms_norm: the sm_100a kernel takes rows of a multiple of 8 elements, got {x2.shape[1]}")
     y = torch.empty((x2.shape[0], x2.shape[1]), dtype=x.dtype, device=x.device)
     c = ctx(x.device)
     _check(lib().pg_rms_norm(_ptr(x2), _vp(0), _ptr(w), _ptr(y), _ci(x2.shape[0]), _ci(x2.shape[1]), _cf(eps), _ci(int(offset)), _ci(0), _ll(x2.stride(0)), _ll(0), _ll(y.stride(0)), _stream()), c)
@@ -355,7 +353,9 @@ def paged_attention(q, kv_layer, meta: AttnMeta, scale=None, window=0, out: Opti
         # several times the chunk itself; the trailing single-row sequences take the decode kernel.
         while n_pf > 0 and qi[n_pf] - qi[n_pf - 1] == 1:
             n_pf -= 1
-        if meta.num_seqs - n_pf < _MIXED_DECODE_MIN:
+        # batch-invariant serving: a single-row sequence ALWAYS takes the decode kernel (same KV
+        # splits and merge order as in a pure decode step or a graph replay), however few there are
+        if meta.num_seqs - n_pf < (1 if _BATCH_INVARIANT else _MIXED_DECODE_MIN):
             n_pf = meta.num_seqs
     if n_pf > 0:
         q_tiles = sum((qi[b + 1] - qi[b] + 63) // 64 for b in range(n_pf))

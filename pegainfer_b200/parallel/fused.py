@@ -68,6 +68,9 @@ class FusedTP(TPContext):
         self.flags = self.buf.view(torch.int32, (MAX_SITES, FLAG_WORDS_PER_SITE), self._off_f)
         self._site = 0
         self._pending_site = -1
+        self._lib_sites = 0
+        self._rows = 0
+        self.sites_by_rows: dict = {}  # token rows of a step -> (fused sites, library all-reduce sites) of its last forward
         self.fused = self
         if world > 1:
             dist.barrier(group=group)
@@ -78,6 +81,23 @@ class FusedTP(TPContext):
             raise RuntimeError("fused TP needs an even number of row-parallel projections per step (partial buffers alternate)")
         self._site = 0
         self._pending_site = -1
+        self._lib_sites = 0
+
+    def describe(self, rows: int) -> dict:
+        """What the last forward pass of a step with ``rows`` token rows (or the next larger one
+        seen) actually ran: the fused kernels, the library all-reduce, or both."""
+        keys = sorted(k for k in self.sites_by_rows if k >= rows) or sorted(self.sites_by_rows)
+        fused, libs = self.sites_by_rows[keys[0]] if keys else (0, 0)
+        path = "fused" if fused and not libs else "nccl" if libs and not fused else "fused+nccl" if fused else "none"
+        return {"path": path, "fused_sites_per_step": fused, "library_sites_per_step": libs}
+
+    def close(self) -> None:
+        """Unmap the peers' buffers and free the local one.  Every rank must be past its last
+        kernel that touches them (callers put a barrier in front)."""
+        if self.buf is not None:
+            self.x = self.flags = None
+            self.buf.close()
+            self.buf = None
 
     def _flag_ptr(self, site: int) -> int:
         return self.buf.local_ptr + self._off_f + site * FLAG_WORDS_PER_SITE * 4
@@ -89,6 +109,8 @@ class FusedTP(TPContext):
 
             from .. import ops
 
+            self._lib_sites += 1
+            self._rows = t
             y = K.linear(a, w)
             dist.all_reduce(y, group=self.group)
             return ops.add_rms_norm(y, residual, norm_w, eps, offset)
@@ -98,6 +120,7 @@ class FusedTP(TPContext):
             a = a.contiguous()
         site = self._site
         self._site += 1
+        self._rows = t
         if self._site >= MAX_SITES:
             raise RuntimeError("too many fused collective sites in one step")
         one_shot = t * self.world <= self.one_shot_rows
@@ -132,6 +155,8 @@ class FusedTP(TPContext):
 
     def sync(self) -> None:
         """Make the last gathered rows safe to read by kernels that do not wait themselves."""
+        if self._rows:
+            self.sites_by_rows[self._rows] = (self._site, self._lib_sites)
         if self._pending_site < 0:
             return
         site, self._pending_site = self._pending_site, -1

@@ -73,9 +73,11 @@ def drive_replicated(scheduler, handle: SchedulerHandle, stop: threading.Event, 
             for rid, req, queued_at, target in new:
                 if target is not None and target != rank:
                     continue
-                q = tracked.get(rid) if rank == 0 else None
-                if q is None:
-                    q = QueuedRequest(id=rid, request=req, queued_at=queued_at)
+                # Every rank, rank 0 included, gives its scheduler a PRIVATE copy whose abort flag is set
+                # from the broadcast list only.  The client-facing request (whose flag an HTTP thread may
+                # set at any moment) stays in `tracked`; if the scheduler saw that flag directly, rank 0
+                # could retire a request one iteration before the other ranks and run a different batch.
+                q = QueuedRequest(id=rid, request=req, queued_at=queued_at)
                 mine[rid] = q
                 ledger.register(q)
                 scheduler.submit(q)

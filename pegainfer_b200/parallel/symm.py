@@ -30,6 +30,7 @@ class SymmetricBuffer:
         self.lib = _native.load()
         self.nbytes = int(nbytes)
         self.rank, self.world, self.device = rank, world, torch.device(device)
+        self.group = group
         with torch.cuda.device(self.device):
             p = ctypes.c_void_p()
             _native.check(self.lib.pg_symm_alloc(ctypes.c_longlong(self.nbytes), ctypes.byref(p)))
@@ -67,6 +68,21 @@ class SymmetricBuffer:
         return (ctypes.c_void_p * self.world)(*[p + byte_offset for p in self.ptrs])
 
     def close(self) -> None:
+        """Unmap the peers' buffers and free the local one (idempotent).  The caller makes sure no
+        kernel on any rank still touches them."""
         for p in self._imported:
             self.lib.pg_ipc_close(ctypes.c_void_p(p))
         self._imported = []
+        if self.local_ptr:
+            if self.world > 1:
+                # a buffer is freed only after every peer has unmapped it
+                import torch.distributed as dist
+
+                if dist.is_initialized():
+                    dist.barrier(group=self.group)
+            self.bytes = None
+            self._keep = None
+            with torch.cuda.device(self.device):
+                torch.cuda.synchronize(self.device)
+                self.lib.pg_symm_free(ctypes.c_void_p(self.local_ptr))
+            self.local_ptr = 0

@@ -43,6 +43,13 @@ class TPContext:
     def begin_step(self) -> None:
         """Called at the start of every forward pass (fused mode numbers its sites)."""
 
+    def describe(self, rows: int) -> dict:
+        """Which collective path a step of ``rows`` token rows takes on this context."""
+        return {"path": "none" if self.world == 1 else "nccl", "fused_sites_per_step": 0, "library_sites_per_step": 0}
+
+    def close(self) -> None:
+        """Release communication buffers (nothing to release for the library arm)."""
+
     def col_linear(self, x, w, out_dtype=None):
         """Column-parallel projection of (possibly just all-gathered) activations."""
         return ops.linear(x, w, out_dtype)

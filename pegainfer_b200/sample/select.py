@@ -37,8 +37,9 @@ def mix_seed(seed: int, step: int) -> int:
 
 
 def uniform_from_seed(seed64: int) -> float:
-    """Uniform in [0,1) from the top 53 bits of a mixed seed."""
-    return (splitmix64(seed64) >> 11) * (1.0 / (1 << 53))
+    """Uniform in [0,1) from the top 53 bits of a mixed seed.  Clamped so that the value is still
+    below 1 after the kernel's conversion to float32 (a double just under 1 rounds up to 1.0f)."""
+    return min((splitmix64(seed64) >> 11) * (1.0 / (1 << 53)), 1.0 - 2.0 ** -24)
 
 
 def select_batch(

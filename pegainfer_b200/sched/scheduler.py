@@ -429,6 +429,10 @@ class ContinuousScheduler:
         """Finish rules: a stop token is never emitted; ``max_tokens`` ends with Length."""
         rid = r.q.id
         req = r.q.request
+        if first:
+            # the token sampled at the end of the prompt used request-local step 0: the first decode
+            # step must draw with step 1, or a seeded request would reuse one random number
+            r.step_index += 1
         if self._is_stop(r, tok):
             ledger.finish(rid, FinishReason.STOP)
             self._retire(rid)

@@ -100,6 +100,14 @@ class DecodeGraphs:
         self.h_out[:1].copy_(self.out_tokens[:1], non_blocking=True)
         torch.cuda.synchronize(dev)
 
+    def release(self) -> None:
+        """Drop every captured graph (each pins its kernels' buffers and a share of the graph
+        memory pool), so that the process can unmap peer memory and exit in order."""
+        self.pending = None
+        self.graphs.clear()
+        self.logits.clear()
+        self.pool = None
+
     def invalidate_table(self) -> None:
         """Forget what ``stage`` knows about the block-table mirror (call after writing it directly)."""
         self._row_state = [(-1, 0)] * self.max_b

@@ -7,6 +7,9 @@ Modes
             lock-step executor; rank 0 routes requests and collects every rank's updates
   rank_loss like tp, but the last rank leaves between steps (no collective in flight): the
             others must fail their open requests on the host instead of hanging
+  abort     like tp with long outputs; a client thread on rank 0 aborts two requests in the
+            middle of decoding.  Every rank logs the composition of every batch it executes
+            (OUT for rank 0, OUT.rankN for the others): the logs must be identical
 """
 import json
 import os
@@ -41,8 +44,19 @@ def main():
     ecfg = EngineConfig(preset=name, kv_page_size=16, num_kv_blocks=128, cuda_graph=False, max_prefill_tokens=32)
     eng = build_replicated_engine(ecfg, preset(name), rank, world, "cpu", torch.float32, control, tp=tp, ep=ep)
     result = {"rank": rank}
+    batches = []
+    if mode == "abort":
+        ex = eng.scheduler.ex
+        inner = ex.execute
+
+        def logged(batch):
+            batches.append([batch.kind] + [[s.rid, s.start_pos, len(s.input_tokens)] for s in batch.seqs])
+            time.sleep(0.002)  # widen the window between the abort broadcast and the step
+            return inner(batch)
+
+        ex.execute = logged
     if rank == 0:
-        n_tok = 400 if mode == "rank_loss" else 6
+        n_tok = 400 if mode == "rank_loss" else 120 if mode == "abort" else 6
         streams = [eng.submit(Request(prompt_tokens=p, params=SamplingParams(temperature=0.0, ignore_eos=True), max_tokens=n_tok)) for p in prompts]
     if mode == "rank_loss" and rank == world - 1:
         # leave between steps: stop the local loop after a few iterations, then exit without telling anyone
@@ -50,8 +64,30 @@ def main():
         time.sleep(0.4)
         os._exit(0)
     eng.start()
-    if rank == 0:
+    if mode == "abort" and rank == 0:
+        def client():
+            # abort as soon as the request has produced a few tokens, from a thread of its own
+            for victim, after in ((streams[1], 5), (streams[3], 17)):
+                seen = 0
+                while seen < after:
+                    seen += len(victim.get(timeout=60).tokens)
+                victim.abort()
+
+        threading.Thread(target=client, daemon=True).start()
+        outs = []
+        for i, s in enumerate(streams):
+            if i in (1, 3):
+                # the client thread consumes these; wait for the stream to close
+                deadline = time.monotonic() + 60
+                while not s.closed and time.monotonic() < deadline:
+                    time.sleep(0.01)
+                outs.append(([], type("T", (), {"kind": "aborted" if s.closed else "open", "message": ""})(), []))
+            else:
+                outs.append(s.collect(60))
+        result["batches"] = batches
+    elif rank == 0:
         outs = [s.collect(60) for s in streams]
+    if rank == 0:
         result["tokens"] = [o[0] for o in outs]
         result["terminals"] = [o[1].kind if hasattr(o[1], "kind") else str(o[1]) for o in outs]
         result["messages"] = [getattr(o[1], "message", "") for o in outs]
@@ -63,6 +99,9 @@ def main():
         deadline = time.monotonic() + 90
         while eng.healthy() and time.monotonic() < deadline:
             time.sleep(0.05)
+        if mode == "abort":
+            with open(f"{out_path}.rank{rank}", "w") as f:
+                json.dump({"rank": rank, "batches": batches}, f)
     sys.stdout.flush()
     os._exit(0)  # a peer may be gone: skip the process-group teardown
 

@@ -210,6 +210,46 @@ def test_batch_invariant_policy_row_result_independent_of_batch():
         eng.shutdown()
 
 
+def test_batch_invariant_decode_row_is_bit_identical_alone_and_in_unified_steps():
+    """The reference's unified-step gate (pegainfer-qwen3/tests/batch_invariance_unified.rs): with
+    the batch-invariant policy a decode row gives bit-identical logits alone, co-batched with a
+    prompt chunk and one to three decode rows, and co-batched with a chunk and four or more."""
+    from pegainfer_b200.kv.request_kv import KvView
+    from pegainfer_b200.ops import cuda as K
+    from pegainfer_b200.sched.executor import SeqStep, build_meta
+
+    eng = engine(False, no_prefix_cache=True)
+    K.set_batch_invariant(True)
+    try:
+        page, nxt = 16, 1
+        ps = [p[:48 + 7 * i] for i, p in enumerate(prompts(7, seed=21))]
+        chunk_prompt = prompts(1, seed=22)[0][:96]
+        seqs = []
+        for i, p in enumerate(ps):
+            npg = (len(p) + 1 + page - 1) // page
+            seqs.append(SeqStep(rid=i, input_tokens=p, start_pos=0, view=KvView(list(range(nxt, nxt + npg)), len(p), page)))
+            nxt += npg
+        for sq in seqs:
+            tok, meta = build_meta([sq], page, "cuda:0")
+            eng.model.forward(tok, meta, eng.kv)
+        npg = (len(chunk_prompt) + page - 1) // page
+        chunk = SeqStep(rid=99, input_tokens=chunk_prompt, start_pos=0, view=KvView(list(range(nxt, nxt + npg)), len(chunk_prompt), page))
+        dec = [SeqStep(rid=s.rid, input_tokens=[23 + s.rid], start_pos=len(s.input_tokens), view=KvView(s.view.page_indices, len(s.input_tokens) + 1, page)) for s in seqs]
+        tok1, meta1 = build_meta([dec[0]], page, "cuda:0")
+        alone = eng.model.forward(tok1, meta1, eng.kv).float()[0]
+        for n_dec in (1, 3, 4, 7):  # below and above the row count at which the default policy switches kernels
+            step = [chunk] + dec[:n_dec]
+            tok, meta = build_meta(step, page, "cuda:0")
+            out = eng.model.forward(tok, meta, eng.kv).float()
+            row = len(chunk_prompt)  # first decode row follows the chunk's rows
+            assert torch.equal(out[row], alone), f"decode row differs when co-batched with a chunk and {n_dec} decode rows"
+        torch.cuda.synchronize()
+        assert K.read_status("cuda:0") == 0
+    finally:
+        K.set_batch_invariant(False)
+        eng.shutdown()
+
+
 def test_decode_overlap_second_stream_matches_plain_engine():
     """Prompt chunks on the prefill lane (second stream, own scratch buffers) while CUDA-graph decode
     steps continue: same tokens as the plain engine, and the lane was really used."""

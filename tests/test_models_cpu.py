@@ -129,3 +129,32 @@ def test_decode_overlap_prefill_lane_keeps_outputs():
     over, eng = gen("tiny-qwen3", ps, 10, max_prefill_tokens=24, decode_overlap=True)
     assert over == plain
     assert eng.scheduler.overlapped_chunks > 0
+
+
+def test_seeded_request_draws_a_distinct_random_number_for_every_token():
+    """A seeded request keys its random stream by (seed, request-local step).  The token sampled at
+    the end of the prompt and every later decode token must each use a different step."""
+    from pegainfer_b200.sample import select as sel
+
+    seen = []
+    inner = sel.mix_seed
+
+    def spy(seed, step):
+        if seed == 777:
+            seen.append(step)
+        return inner(seed, step)
+
+    sel.mix_seed = spy
+    try:
+        ecfg = EngineConfig(preset="tiny-qwen3", kv_page_size=16, num_kv_blocks=64, cuda_graph=False, max_prefill_tokens=32)
+        eng = build_engine(ecfg, preset("tiny-qwen3"), device="cpu", dtype=torch.float32)
+        try:
+            ps = prompts_for(2, 40, seed=3)  # longer than one prefill chunk: the prompt takes two steps
+            out = eng.generate(ps, SamplingParams(temperature=0.9, top_p=0.95, seed=777, ignore_eos=True), max_tokens=6, timeout=120)
+            assert all(len(o[0]) == 6 for o in out)
+        finally:
+            eng.shutdown()
+    finally:
+        sel.mix_seed = inner
+    # two requests x six tokens; per request the steps are 0..5, each exactly once
+    assert sorted(seen) == sorted(list(range(6)) * 2), seen

@@ -54,3 +54,18 @@ def test_lost_rank_fails_open_requests_instead_of_hanging(tmp_path):
     res = run_workers("rank_loss", tmp_path)
     assert all(t == "failed" for t in res["terminals"]), res
     assert all(("engine failure" in m) or ("step failed" in m) for m in res["messages"]), res
+
+
+def test_abort_from_a_client_thread_keeps_tensor_parallel_ranks_on_identical_batches(tmp_path):
+    """A client may set a request's abort flag at any moment.  Tensor-parallel ranks run one
+    replicated schedule, so the abort must reach every rank's scheduler in the same iteration:
+    each rank's log of executed batches (kind, request ids, positions) has to be identical."""
+    res = run_workers("abort", tmp_path)
+    other = json.loads((tmp_path / "abort.json.rank1").read_text())
+    assert res["terminals"][0] == "finished" and res["terminals"][2] == "finished", res["terminals"]
+    assert res["terminals"][1] == "aborted" and res["terminals"][3] == "aborted", res["terminals"]
+    assert len(res["batches"]) > 20
+    assert res["batches"] == other["batches"]
+    # the aborted requests really left the batch early: later batches no longer carry their ids
+    last = res["batches"][-1]
+    assert {row[0] for row in last[1:]} <= {1, 3}

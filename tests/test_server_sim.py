@@ -92,7 +92,7 @@ def test_unsupported_params_are_rejected_not_ignored():
 
 
 def test_metrics_gauges_and_partitions():
-    eng, c = make(SimConfig(base_ttft_s=0.4, tpot_s=0.05), partitions=2, declared=2)
+    eng, c = make(SimConfig(base_ttft_s=1.0, tpot_s=0.1), partitions=2, declared=2)
     try:
         out = {}
 
@@ -101,17 +101,23 @@ def test_metrics_gauges_and_partitions():
 
         t = threading.Thread(target=slow)
         t.start()
+        # deadlines, not iteration counts: on a loaded machine the poster thread may start late
         seen_running = False
-        for _ in range(60):
+        deadline = time.monotonic() + 20.0
+        while time.monotonic() < deadline and t.is_alive():
             m = c.get("/metrics").text
             if 'vllm:num_requests_running{engine="0",model_name="sim-model"} 1' in m or 'vllm:num_requests_running{engine="1",model_name="sim-model"} 1' in m:
                 seen_running = True
                 break
-            time.sleep(0.02)
+            time.sleep(0.01)
         t.join()
         assert seen_running and out["r"].status_code == 200
-        time.sleep(0.05)
+        idle = ['vllm:num_requests_running{engine="%d",model_name="sim-model"} 0' % i for i in (0, 1)]
+        deadline = time.monotonic() + 10.0
         m = c.get("/metrics").text
+        while not all(line in m for line in idle) and time.monotonic() < deadline:  # gauges are published once per driver iteration
+            time.sleep(0.02)
+            m = c.get("/metrics").text
         for eng_idx in (0, 1):
             assert f'vllm:num_requests_running{{engine="{eng_idx}",model_name="sim-model"}} 0' in m
             assert f'vllm:num_requests_waiting{{engine="{eng_idx}",model_name="sim-model"}}' in m

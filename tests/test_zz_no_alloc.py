@@ -37,7 +37,18 @@ def test_noalloc_gemm_matches_regular_entry_point_twice_in_a_row():
     dev = "cuda:0"
     torch.manual_seed(11)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
-    shapes = [(64, 4096, 4096), (48, 1000, 520)]  # split-K with partials, then a ragged one
+    # (128, 4096, 4096) and (200, 1000, 4104) take the workspace split-K path: their f32 partial
+    # sums and tile counters live in the library's built-in array, which is what this entry point
+    # is for.  The same shape runs twice in a row and two shapes alternate, so whatever one call
+    # leaves in the shared array must not disturb the next.  The narrow shapes reduce on chip.
+    scratch_shapes = [(128, 4096, 4096), (200, 1000, 4104)]
+    scratch_bytes = (8 << 20) - (64 << 10)
+    for t, m, k in scratch_shapes:
+        plan = K.gemm_plan(t, m, k)
+        tiles = ((m + 127) // 128) * ((t + plan["bn"] - 1) // plan["bn"])
+        assert plan["cluster"] == 1 and plan["splits"] > 1, f"{t}x{m}x{k} does not use the split-K workspace: {plan}"
+        assert tiles * 2 * plan["bn"] * 128 * 4 <= scratch_bytes, "at least two splits must fit the built-in scratch"
+    shapes = [scratch_shapes[0], scratch_shapes[0], scratch_shapes[1], scratch_shapes[0], (64, 4096, 4096), (48, 1000, 520), scratch_shapes[1]]
     for t, m, k in shapes:
         x = (torch.randn(t, k, device=dev) * 0.5).bfloat16()
         w = (torch.randn(m, k, device=dev) * 0.05).bfloat16()
