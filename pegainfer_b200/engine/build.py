@@ -76,6 +76,10 @@ def build_engine(ecfg: EngineConfig, mcfg: Optional[ModelConfig] = None, device=
     device = torch.device(device)
     if dtype is None:
         dtype = torch.bfloat16 if device.type == "cuda" else torch.float32
+    if ecfg.gemm == "cublas" and device.type == "cuda":
+        from .. import ops
+
+        ops.set_mode("cublas")  # --gemm cublas: library GEMMs, everything else unchanged
     if ecfg.batch_invariant and device.type == "cuda":
         from ..ops import cuda as K
 

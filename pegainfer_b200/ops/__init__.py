@@ -13,13 +13,18 @@ import contextlib
 from . import reference
 from .reference import AttnMeta  # noqa: F401
 
-_MODE = "sm100"  # sm100 | library
+_MODE = "sm100"  # sm100 | cublas | library
 
 
 def set_mode(mode: str) -> None:
+    """``sm100``: every op is a kernel of this repository.  ``cublas``: dense projections go
+    through ``torch.nn.functional.linear`` (cuBLAS) and everything else stays on this
+    repository's kernels; with NCCL all-reduce this is the library build of the GEMM ->
+    collective -> norm decomposition, and it can be captured in CUDA graphs.  ``library``:
+    every op is its PyTorch restatement (the oracle; host-synchronising, not capturable)."""
     global _MODE
-    if mode not in ("sm100", "library"):
-        raise ValueError("mode must be 'sm100' or 'library'")
+    if mode not in ("sm100", "cublas", "library"):
+        raise ValueError("mode must be 'sm100', 'cublas' or 'library'")
     _MODE = mode
 
 
@@ -38,7 +43,7 @@ def mode(m: str):
 
 
 def _impl(t):
-    if t.is_cuda and _MODE == "sm100":
+    if t.is_cuda and _MODE != "library":
         from . import cuda
 
         return cuda
@@ -66,6 +71,11 @@ def swiglu(gate_up):
 
 
 def linear(x, w, out_dtype=None):
+    if _MODE == "cublas" and x.is_cuda:
+        import torch
+
+        y = torch.nn.functional.linear(x, w)
+        return y if out_dtype is None or y.dtype == out_dtype else y.to(out_dtype)
     return _impl(x).linear(x, w, out_dtype)
 
 
