@@ -227,7 +227,7 @@ def mla_cases(iters):
 
 
 GEMM_PHASES = ["entry", "prologue done", "predecessor complete", "all loads issued", "first stage landed", "last MMA committed", "accumulator ready",
-               "partial pushed", "cluster partials in", "reduced + stored", "roles done", "cluster released"]
+               "partial pushed", "cluster partials in", "reduced + stored", "roles done", "cluster released", "token tiles issued", "second stage landed", "seventh stage landed"]
 
 
 def gemm_phase_timeline(t, m, k):
@@ -272,6 +272,52 @@ def gemm_phase_timeline(t, m, k):
         print(f"{name:26s} {a:8.2f} {b:8.2f} {c:8.2f}")
 
 
+def gemm_phase_timeline_steady(t, m, k, launches=8):
+    """The same stamps in steady state: a CUDA graph of ``launches`` back-to-back GEMMs (rotating
+    weights, programmatic dependent launch between them), every launch writing its own stamp
+    buffer.  Printed per phase: median over the CTAs, microseconds from the exit of the previous
+    launch's last CTA (negative = overlapped with the predecessor)."""
+    import ctypes
+
+    import numpy as np
+
+    from pegainfer_b200 import _native
+    from pegainfer_b200.ops import cuda as K
+
+    lib = _native.load()
+    x = (torch.randn(t, k, device=DEV) * 0.1).bfloat16()
+    nvar = max(2, min(16, int(300e6 // (m * k * 2)) + 1))
+    ws = [(torch.randn(m, k, device=DEV) * 0.02).bfloat16() for _ in range(nvar)]
+    out = torch.empty(t, m, device=DEV, dtype=torch.bfloat16)
+    timing = torch.zeros(launches, 148 * 16, dtype=torch.int64, device=DEV)
+    for w in ws[:3]:
+        K.linear(x, w, out=out)
+    torch.cuda.synchronize()
+    plan = K.gemm_plan(t, m, k)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(launches):
+            lib.pg_gemm_set_timing(ctypes.c_void_p(timing[i].data_ptr()))
+            K.linear(x, ws[i % nvar], out=out)
+    lib.pg_gemm_set_timing(ctypes.c_void_p(0))
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    tm = timing.view(launches, 148, 16).cpu().numpy().astype(np.float64)[:, : plan["grid"]]
+    print(f"gemm T{t} M{m} K{k}: plan {plan}; steady state, launch i relative to the exit of launch i-1")
+    print(f"{'phase':26s} " + " ".join(f"{'L%d' % i:>8s}" for i in range(2, launches)))
+    ends = [max(tm[i][:, 11].max(), tm[i][:, 10].max()) for i in range(launches)]
+    for j, name in enumerate(GEMM_PHASES):
+        vals = []
+        for i in range(2, launches):
+            col = tm[i][:, j]
+            col = col[col > 0]
+            vals.append((np.median(col) - ends[i - 1]) / 1e3 if len(col) else float("nan"))
+        print(f"{name:26s} " + " ".join(f"{v:8.2f}" for v in vals))
+    per = [(ends[i] - ends[i - 1]) / 1e3 for i in range(2, launches)]
+    print(f"{'exit to exit':26s} " + " ".join(f"{v:8.2f}" for v in per))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default=None)
@@ -280,11 +326,15 @@ def main():
     ap.add_argument("--single", default=None, help="e.g. gemm:64x4096x4096, attn:64x1152, prefill:4x1024, gdn:8x2048 (sequences x tokens)")
     ap.add_argument("--library", action="store_true", help="also time torch/cuBLAS for the GEMM rows")
     ap.add_argument("--phases", default=None, help="gemm:TxMxK: print the per-CTA phase timeline of one GEMM launch")
+    ap.add_argument("--phases-steady", default=None, help="gemm:TxMxK: the same stamps for back-to-back launches inside one CUDA graph")
     args = ap.parse_args()
     hbm, tf, src = peaks()
     rows = []
     if args.phases:
         gemm_phase_timeline(*[int(v) for v in args.phases.split(":")[1].split("x")])
+        return
+    if args.phases_steady:
+        gemm_phase_timeline_steady(*[int(v) for v in args.phases_steady.split(":")[1].split("x")])
         return
     if args.single:
         kind, shape = args.single.split(":")

@@ -36,6 +36,13 @@ int pg_tp_gemm_rs_norm_ag(const void* a, const void* w, int T, int hidden, int K
                           void* const* xout, void* const* flags, int rank, int world, int site, void* residual, long long ld_res,
                           const void* norm_w, float eps, int offset, int one_shot, long long part_offset, unsigned long long wait_ns, void* ws,
                           long long ws_bytes, void* counters, long long counter_bytes, void* status, cudaStream_t stream);
+// Decode-chain GEMM (T <= 64) with the deferred RMSNorm scale of its input rows and a fused epilogue
+// (0 plain, 1 SwiGLU over interleaved gate/up rows, 2 residual add + norm-weight product + per-tile sums
+// of squares); PG_ERR_UNSUPPORTED when the problem does not plan onto the on-chip split-K path.
+int pg_gemm_bf16_tn_fused(const void* x, const void* w, void* y, int T, int M, int K, long long ldx, long long ldw, long long ldy,
+                          const void* in_ssp, int in_parts, int in_width, float in_eps, int epi, void* residual, long long ld_res,
+                          const void* norm_w, int norm_offset, void* out_ssp, void* ws, long long ws_bytes, void* counters,
+                          long long counter_bytes, void* status, cudaStream_t stream);
 int pg_tp_wait(const void* wait_flags, int world, unsigned long long wait_ns, void* status, cudaStream_t stream);
 int pg_symm_alloc(long long bytes, void** out);
 int pg_symm_free(void* p);
@@ -55,7 +62,7 @@ int pg_gather_words(const void* src, const void* idx, void* dst, int n, int src_
 int pg_rms_norm(const void* x, void* residual, const void* w, void* y, int rows, int width, float eps, int offset, int round_before,
                 long long ldx, long long ldr, long long ldy, cudaStream_t stream);
 int pg_gated_rms_norm(const void* x, const void* gate, const void* w_f32, void* y, long long rows, int dim, float eps, cudaStream_t stream);
-int pg_swiglu(const void* gate_up, void* out, int rows, int inter, long long ldin, long long ldout, cudaStream_t stream);
+int pg_swiglu(const void* gate_up, void* out, int rows, int inter, long long ldin, long long ldout, int interleaved, cudaStream_t stream);
 int pg_sigmoid_gate_mul(void* x, const void* gate, long long n, cudaStream_t stream);
 int pg_qk_norm_rope_append(const void* qkv, long long ld, const void* q_w, const void* k_w, const void* cos, const void* sin,
                            const void* positions, const void* slots, void* q_out, void* gate_out, void* kv, int tokens, int hq, int hkv, int dim,

@@ -142,17 +142,30 @@ __global__ void gated_rms_norm_kernel(const bf16* __restrict__ x, const bf16* __
   }
 }
 
-__global__ void swiglu_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int rows, int inter, long long ldin, long long ldout) {
+// `interleaved` = 0: a row is [gate_0 .. gate_{I-1}, up_0 .. up_{I-1}]; 1: (gate_0, up_0, gate_1, up_1, ...).
+__global__ void swiglu_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int rows, int inter, long long ldin, long long ldout, int interleaved) {
   PG_PDL_ENTRY();
   const int nvec = inter / 8;
   const long long total = (long long)rows * nvec;
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
     const int row = (int)(idx / nvec), i = (int)(idx % nvec);
-    const bf16x8* g = reinterpret_cast<const bf16x8*>(gu + row * ldin) + i;
-    const bf16x8* u = reinterpret_cast<const bf16x8*>(gu + row * ldin + inter) + i;
     float gf[8], uf[8], o[8];
-    unpack8(*g, gf);
-    unpack8(*u, uf);
+    if (interleaved) {
+      const bf16x8* pr = reinterpret_cast<const bf16x8*>(gu + row * ldin) + 2 * i;
+      float a[8], b[8];
+      unpack8(pr[0], a);
+      unpack8(pr[1], b);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        gf[j] = a[2 * j], uf[j] = a[2 * j + 1];
+        gf[4 + j] = b[2 * j], uf[4 + j] = b[2 * j + 1];
+      }
+    } else {
+      const bf16x8* g = reinterpret_cast<const bf16x8*>(gu + row * ldin) + i;
+      const bf16x8* u = reinterpret_cast<const bf16x8*>(gu + row * ldin + inter) + i;
+      unpack8(*g, gf);
+      unpack8(*u, uf);
+    }
 #pragma unroll
     for (int j = 0; j < 8; ++j) o[j] = bf16_round(gf[j] / (1.f + __expf(-gf[j]))) * uf[j];
     reinterpret_cast<bf16x8*>(out + row * ldout)[i] = pack8(o);
@@ -303,13 +316,13 @@ extern "C" int pg_gated_rms_norm(const void* x, const void* gate, const void* w_
   return PG_OK;
 }
 
-extern "C" int pg_swiglu(const void* gate_up, void* out, int rows, int inter, long long ldin, long long ldout, cudaStream_t stream) {
+extern "C" int pg_swiglu(const void* gate_up, void* out, int rows, int inter, long long ldin, long long ldout, int interleaved, cudaStream_t stream) {
   PG_REQUIRE(inter % 8 == 0 && ldin % 8 == 0 && ldout % 8 == 0, "swiglu: sizes must be multiples of 8");
   if (rows == 0) return PG_OK;
   long long total = (long long)rows * (inter / 8);
   int blocks = (int)((total + 255) / 256);
   if (blocks > 148 * 16) blocks = 148 * 16;
-  PG_CUDA(launch_pdl(swiglu_kernel, dim3(blocks), dim3(256), (size_t)(0), stream, (const bf16*)gate_up, (bf16*)out, rows, inter, ldin, ldout));
+  PG_CUDA(launch_pdl(swiglu_kernel, dim3(blocks), dim3(256), (size_t)(0), stream, (const bf16*)gate_up, (bf16*)out, rows, inter, ldin, ldout, interleaved));
   PG_LAUNCH_CHECK();
   return PG_OK;
 }

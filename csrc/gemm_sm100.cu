@@ -68,15 +68,42 @@ struct WaitSpec {
   unsigned long long* timing;  // optional: [6] wait start, [7] wait end of the producing site's slot
 };
 
+// Work folded into the GEMM so that the decode chain needs no separate row kernels.
+//
+// Deferred RMSNorm: a row-parallel projection (EPI_RESID_NORMW) adds the residual, stores the new
+// residual h and the un-normalised product xw = h * norm_w, and leaves per-(weight tile, token)
+// sums of squares in `out_ssp`; the GEMM that consumes xw multiplies every output element of token
+// n by inv_rms[n] = rsqrt(sum_tiles ssp[tile][n] / H + eps) in its epilogue (a per-token scalar
+// commutes with the matrix product).  No kernel ever needs a whole row at once, so there is no
+// grid-wide dependency between the projection and the norm.
+//
+// EPI_SWIGLU: the weight rows are interleaved (gate_0, up_0, gate_1, up_1, ...); the epilogue
+// writes bf16(silu(g)) * u for every pair: out[n][m / 2].
+enum { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_RESID_NORMW = 2 };
+struct FuseSpec {
+  int epi;
+  const float* in_ssp;  // consumer side: [in_parts][T] sums of squares of the input rows (nullptr = input is already normalised)
+  int in_parts;
+  int in_width;         // H of the normalised vector
+  float in_eps;
+  bf16* residual;       // EPI_RESID_NORMW: [T, M] read, updated in place
+  long long ld_res;
+  const bf16* norm_w;   // EPI_RESID_NORMW: weight of the norm that the consumer completes
+  int norm_offset;      // (1 + w) form
+  float* out_ssp;       // EPI_RESID_NORMW: [m_tiles][T]
+};
+
 struct GemmParams {
   TpFuse tp;
   WaitSpec wait;
+  FuseSpec fuse;
   bf16* y;
   float* y_f32;
   long long ldy;
   int M, T, K;
   int bn;
   int m_tiles, n_tiles, kblocks, splits;
+  int rotate;   // 1: each weight-row tile starts its k walk at a different k-block (spreads the L2 reads of the shared token tiles)
   int cluster;  // > 1: the k-splits of one tile are the CTAs of one cluster and reduce through distributed shared memory
   int stages;
   uint32_t tmem_cols;
@@ -93,7 +120,8 @@ struct GemmParams {
 // [source rank][row][hidden] of the rank(s) that reduce this row, so that the transfer of a
 // tile overlaps the MMAs of the tiles still being computed and the reduction later reads
 // local memory only.
-__device__ __forceinline__ void store_out(const GemmParams& p, int n, int m, float v) {
+__device__ __forceinline__ void store_out(const GemmParams& p, int n, int m, float v, const float* s_inv = nullptr, int n_local = 0) {
+  if (s_inv) v *= s_inv[n_local];
   if (p.tp.enabled) {
     const TpFuse& tp = p.tp;
     if (tp.one_shot) {
@@ -170,14 +198,49 @@ __device__ __forceinline__ float tp_sum_rows(const float* src_row, size_t src_st
 }
 
 // Four consecutive output features m..m+3 of token row n (the vector form of store_out).
-__device__ __forceinline__ void store_out4(const GemmParams& p, int n, int m, float4 v) {
+// Returns this thread's contribution to the row's sum of squares (EPI_RESID_NORMW, else 0).
+__device__ __forceinline__ float store_out4(const GemmParams& p, int n, int m, float4 v, const float* s_inv = nullptr, int n_local = 0) {
+  if (s_inv) {
+    const float sc = s_inv[n_local];
+    v.x *= sc, v.y *= sc, v.z *= sc, v.w *= sc;
+  }
+  if (p.fuse.epi == EPI_SWIGLU) {
+    // rows (m, m+1) = (gate, up) of feature m / 2, rows (m+2, m+3) of the next one
+    if (m + 3 < p.M) {
+      const float g0 = bf16_round(v.x), u0 = bf16_round(v.y), g1 = bf16_round(v.z), u1 = bf16_round(v.w);
+      const bf162 o = __floats2bfloat162_rn(bf16_round(g0 / (1.f + __expf(-g0))) * u0, bf16_round(g1 / (1.f + __expf(-g1))) * u1);
+      *reinterpret_cast<bf162*>(p.y + (size_t)n * p.ldy + (m >> 1)) = o;
+    }
+    return 0.f;
+  }
+  if (p.fuse.epi == EPI_RESID_NORMW) {
+    if (m + 3 >= p.M) return 0.f;
+    bf16* rr = p.fuse.residual + (size_t)n * p.fuse.ld_res + m;
+    const uint2 rv = *reinterpret_cast<const uint2*>(rr);
+    const float2 r0 = __bfloat1622float2(*reinterpret_cast<const bf162*>(&rv.x)), r1 = __bfloat1622float2(*reinterpret_cast<const bf162*>(&rv.y));
+    const bf162 h0 = __floats2bfloat162_rn(v.x + r0.x, v.y + r0.y), h1 = __floats2bfloat162_rn(v.z + r1.x, v.w + r1.y);
+    uint2 hp;
+    hp.x = *reinterpret_cast<const uint32_t*>(&h0);
+    hp.y = *reinterpret_cast<const uint32_t*>(&h1);
+    *reinterpret_cast<uint2*>(rr) = hp;
+    const float2 f0 = __bfloat1622float2(h0), f1 = __bfloat1622float2(h1);  // the rounded sum is what gets normalised
+    const uint2 wv = *reinterpret_cast<const uint2*>(p.fuse.norm_w + m);
+    float2 w0 = __bfloat1622float2(*reinterpret_cast<const bf162*>(&wv.x)), w1 = __bfloat1622float2(*reinterpret_cast<const bf162*>(&wv.y));
+    if (p.fuse.norm_offset) w0.x += 1.f, w0.y += 1.f, w1.x += 1.f, w1.y += 1.f;
+    const bf162 x0 = __floats2bfloat162_rn(f0.x * w0.x, f0.y * w0.y), x1 = __floats2bfloat162_rn(f1.x * w1.x, f1.y * w1.y);
+    uint2 xp;
+    xp.x = *reinterpret_cast<const uint32_t*>(&x0);
+    xp.y = *reinterpret_cast<const uint32_t*>(&x1);
+    *reinterpret_cast<uint2*>(p.y + (size_t)n * p.ldy + m) = xp;
+    return f0.x * f0.x + f0.y * f0.y + f1.x * f1.x + f1.y * f1.y;
+  }
   const bool vec = (p.M & 3) == 0 && m + 3 < p.M;
   if (!vec) {
     const float f[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i)
       if (m + i < p.M) store_out(p, n, m + i, f[i]);
-    return;
+    return 0.f;
   }
   if (p.tp.enabled) {
     const TpFuse& tp = p.tp;
@@ -210,6 +273,7 @@ __device__ __forceinline__ void store_out4(const GemmParams& p, int n, int m, fl
       o[0] = lo.x, o[1] = lo.y, o[2] = hi.x, o[3] = hi.y;
     }
   }
+  return 0.f;
 }
 
 // Split-K reduction through distributed shared memory.  The k-splits of one output tile are
@@ -219,12 +283,13 @@ __device__ __forceinline__ void store_out4(const GemmParams& p, int n, int m, fl
 // mbarrier, so the reduction itself reads local shared memory only: this function sums the
 // S slots in split order (deterministic) and stores the result.  A thread takes 4 rows of
 // one column per pass, 4 columns per pass across the 128 epilogue threads.
-__device__ __forceinline__ void cluster_reduce_local(const GemmParams& p, const float* kred, int S, int w, uint32_t cr, int et, int n0, int m0) {
+__device__ __forceinline__ void cluster_reduce_local(const GemmParams& p, const float* kred, int S, int w, uint32_t cr, int et, int n0, int m0, int m_tile,
+                                                     const float* s_inv) {
   const int nmax = min(p.bn, p.T - n0);
   const int c_lo = (int)cr * w;
   const int ncols = min(nmax, c_lo + w) - c_lo;
   const int sub = et >> 5, r4 = (et & 31) * 4;
-  for (int j = sub; j < ncols; j += 4) {
+  for (int j = sub; j < ncols; j += 4) {  // one warp = one token column across all 128 weight rows of the tile
     const float* src = kred + (size_t)j * BM + r4;
     float4 a = *reinterpret_cast<const float4*>(src);
 #pragma unroll 4
@@ -235,7 +300,11 @@ __device__ __forceinline__ void cluster_reduce_local(const GemmParams& p, const 
       a.z += b.z;
       a.w += b.w;
     }
-    store_out4(p, n0 + c_lo + j, m0 + r4, a);
+    float ss = store_out4(p, n0 + c_lo + j, m0 + r4, a, s_inv, c_lo + j);
+    if (p.fuse.epi == EPI_RESID_NORMW) {
+      ss = warp_sum(ss);
+      if ((et & 31) == 0) p.fuse.out_ssp[(size_t)m_tile * p.T + n0 + c_lo + j] = ss;
+    }
   }
 }
 
@@ -287,6 +356,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   uint32_t* last_flag = tmem_slot + 2;
+  float* s_inv_buf = reinterpret_cast<float*>(tmem_slot + 4);  // [bn] inverse RMS of the input rows (deferred norm), epilogue threads only
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -350,6 +420,14 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         const int kb0 = (int)(((long long)p.kblocks * s) / p.splits);
         const int kb1 = (int)(((long long)p.kblocks * (s + 1)) / p.splits);
         int kb = kb0;
+        // Every CTA of one k-split walks the same token tiles X[:, kb]; if they all walked them in
+        // the same order, 32..192 SMs would ask L2 for the same few lines at the same moment and
+        // the tiles would trickle in (measured: 8 KB per 0.26 us per SM).  Each weight-row tile
+        // therefore starts its walk at a different k-block and wraps around (the order of the
+        // partial sums depends on the tile's position only, never on the batch).
+        const int nkb = kb1 - kb0;
+        const int rot = p.rotate ? (m_tile * 3) % nkb : 0;
+#define PG_KB(i) (kb0 + (((i) - kb0 + rot) % nkb))
         if (!x_ready) {
           // Weights never change, the token rows X come from the previous kernel (or, with the
           // all-gather fused into this GEMM, from peers): stream the first weight tiles, then
@@ -357,7 +435,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           const int pre = min(p.stages, kb1 - kb0);
           for (int i = 0; i < pre; ++i) {
             mbar_expect_tx(&full[i], (uint32_t)stage_bytes);
-            tma_load_2d(tiles + i * stage_bytes, &tm_w, &full[i], (kb0 + i) * BK, m_tile * BM, pol_w);
+            tma_load_2d(tiles + i * stage_bytes, &tm_w, &full[i], PG_KB(kb0 + i) * BK, m_tile * BM, pol_w);
             used[i] = true;
             last_phase[i] = 0;
           }
@@ -373,7 +451,8 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           }
           x_ready = true;
           for (int i = 0; i < pre; ++i)
-            tma_load_2d(tiles + i * stage_bytes + A_BYTES, &tm_x, &full[i], (kb0 + i) * BK, n_tile * p.bn, pol_x);
+            tma_load_2d(tiles + i * stage_bytes + A_BYTES, &tm_x, &full[i], PG_KB(kb0 + i) * BK, n_tile * p.bn, pol_x);
+          if (tstamp) tstamp[12] = globaltimer_ns();
           kb = kb0 + pre;
           stage = pre;
           if (stage == p.stages) {
@@ -388,8 +467,8 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           }
           uint8_t* a_dst = tiles + stage * stage_bytes;
           mbar_expect_tx(&full[stage], (uint32_t)stage_bytes);
-          tma_load_2d(a_dst, &tm_w, &full[stage], kb * BK, m_tile * BM, pol_w);
-          tma_load_2d(a_dst + A_BYTES, &tm_x, &full[stage], kb * BK, n_tile * p.bn, pol_x);
+          tma_load_2d(a_dst, &tm_w, &full[stage], PG_KB(kb) * BK, m_tile * BM, pol_w);
+          tma_load_2d(a_dst + A_BYTES, &tm_x, &full[stage], PG_KB(kb) * BK, n_tile * p.bn, pol_x);
           used[stage] = true;
           last_phase[stage] = phase;
           if (++stage == p.stages) {
@@ -442,6 +521,8 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             break;
           }
           if (tstamp && item == (int)blockIdx.x && kb == kb0) tstamp[4] = globaltimer_ns();
+          if (tstamp && item == (int)blockIdx.x && kb == kb0 + 1) tstamp[13] = globaltimer_ns();
+          if (tstamp && item == (int)blockIdx.x && kb == kb0 + 6) tstamp[14] = globaltimer_ns();
           tc_fence_after();
           const uint32_t a_addr = smem_u32(tiles + stage * stage_bytes);
           const uint32_t b_addr = a_addr + A_BYTES;
@@ -474,9 +555,24 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     const uint32_t cr = p.cluster > 1 ? cluster_ctarank() : 0u;
     const int kw = p.cluster > 1 ? (p.bn + p.cluster - 1) / p.cluster : p.bn;  // columns per slice
     bool cluster_arrived = false;
+    const float* s_inv = p.fuse.in_ssp ? s_inv_buf : nullptr;
+    int inv_tile = -1;
     for (int item = blockIdx.x; item < total; item += gridDim.x) {
       const int tile = item / p.splits, s = item - tile * p.splits;
       const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
+      if (s_inv && n_tile != inv_tile) {
+        // inverse RMS of this token tile's input rows, from the producer's per-tile sums of squares
+        // (fixed summation order); computed while the main loop runs
+        if (inv_tile >= 0) named_bar_all(1, 128, true);  // nobody still reads the previous tile's values
+        for (int nl = et; nl < p.bn; nl += 128) {
+          const int n = n_tile * p.bn + nl;
+          float ss = 0.f;
+          if (n < p.T)
+            for (int q = 0; q < p.fuse.in_parts; ++q) ss += __ldcg(p.fuse.in_ssp + (size_t)q * p.T + n);
+          s_inv_buf[nl] = rsqrtf(ss / (float)p.fuse.in_width + p.fuse.in_eps);
+        }
+        inv_tile = n_tile;
+      }
       bool ok = mbar_wait(&tfull[acc], acc_phase, abort_flag);
       // cluster mode: every owner must have reduced the previous item before its slots are overwritten
       if (p.cluster > 1) ok = mbar_wait_cluster(kfree, kphase ^ 1u, abort_flag) && ok;
@@ -525,7 +621,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
                 const int n = n0 + c + j;
-                if (n < p.T) store_out(p, n, m, __uint_as_float(v[j]));
+                if (n < p.T) store_out(p, n, m, __uint_as_float(v[j]), s_inv, c + j);
               }
             }
           } else {
@@ -554,7 +650,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         if (tstamp && et == 0) tstamp[7] = globaltimer_ns();
         const bool full_ok = named_bar_all(1, 128, mbar_wait_cluster(kfull, kphase, abort_flag));
         if (tstamp && et == 0) tstamp[8] = globaltimer_ns();
-        if (full_ok) cluster_reduce_local(p, kred, (int)S, kw, cr, et, n0, m_tile * BM);
+        if (full_ok) cluster_reduce_local(p, kred, (int)S, kw, cr, et, n0, m_tile * BM, m_tile, s_inv);
         if (tstamp && et == 0) tstamp[9] = globaltimer_ns();
         // this CTA's slots may be overwritten by the next item (also said on the abort path, so nobody waits in vain)
         if (!last_item) {
@@ -600,7 +696,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
                 const int n = c + j;
-                if (n < nmax) store_out(p, n0 + n, m, acc[j]);
+                if (n < nmax) store_out(p, n0 + n, m, acc[j], s_inv, n);
               }
             }
           }
@@ -916,7 +1012,7 @@ extern "C" int pg_gemm_workspace_bytes(int T, int M, int K, int device, long lon
 // `force_splits` > 0 pins the k-split count (batch-invariant serving); 0 = heuristic.
 static int gemm_impl(const void* x, const void* w, void* y, int y_is_f32, int T, int M, int K, long long ldx, long long ldw, long long ldy,
                      void* ws, long long ws_bytes, void* counters, long long counter_bytes, void* status, int force_splits,
-                     const TpFuse* tp, const WaitSpec* wait, cudaStream_t stream, int* plan_out = nullptr) {
+                     const TpFuse* tp, const WaitSpec* wait, cudaStream_t stream, int* plan_out = nullptr, const FuseSpec* fuse = nullptr) {
   PG_REQUIRE(T > 0 && M > 0 && K > 0, "gemm: empty problem %dx%dx%d", T, M, K);
   PG_REQUIRE(K % 8 == 0, "gemm: K=%d must be a multiple of 8 (16-byte TMA rows)", K);
   PG_REQUIRE(status != nullptr, "gemm: a device status word is required");
@@ -956,6 +1052,7 @@ static int gemm_impl(const void* x, const void* w, void* y, int y_is_f32, int T,
   memset(&p, 0, sizeof(p));
   if (tp) p.tp = *tp;
   if (wait) p.wait = *wait;
+  if (fuse) p.fuse = *fuse;
   p.bn = pick_bn(T, M, di.sms);
   p.m_tiles = ceil_div(M, BM);
   p.n_tiles = ceil_div(T, p.bn);
@@ -983,8 +1080,12 @@ static int gemm_impl(const void* x, const void* w, void* y, int y_is_f32, int T,
       PG_REQUIRE(counters != nullptr && counter_bytes >= (long long)tiles * 4, "gemm: counter buffer too small");
     }
   }
+  if (fuse && fuse->epi != EPI_PLAIN && p.cluster <= 1) {
+    pg_set_error("gemm: the fused epilogue needs the on-chip split-K path (T <= 64 and a cluster plan); T=%d M=%d K=%d plans cluster=%d", T, M, K, p.cluster);
+    return PG_ERR_UNSUPPORTED;
+  }
   const int stage_bytes = A_BYTES + p.bn * 128;
-  const int tail = (2 * MAX_STAGES + 6) * 8 + 64;
+  const int tail = (2 * MAX_STAGES + 6) * 8 + 64 + 1024;  // barriers, flags, 256 floats of per-token scales
   const int red_bytes = p.cluster > 1 ? (p.bn + 8) * BM * 4 : 0;  // S slots of ceil(bn / S) columns
   p.stages = (di.max_smem - 1024 - tail - red_bytes) / stage_bytes;
   if (p.stages > MAX_STAGES) p.stages = MAX_STAGES;
@@ -1002,6 +1103,14 @@ static int gemm_impl(const void* x, const void* w, void* y, int y_is_f32, int T,
   p.counters = (uint32_t*)counters;
   p.status = (uint32_t*)status;
   p.timing = g_gemm_timing;
+  {
+    static int rot = -1;
+    if (rot < 0) {
+      const char* e = getenv("PEGAINFER_GEMM_ROTATE");
+      rot = (e && e[0] == '0') ? 0 : 1;
+    }
+    p.rotate = rot;
+  }
   if (plan_out == nullptr) {
     p.pf_ptr = (const uint8_t*)t_pf_ptr;
     p.pf_bytes = (t_pf_ptr && T <= 256) ? t_pf_bytes : 0;  // only the weight-streaming regime has idle HBM time to fill
@@ -1147,6 +1256,40 @@ extern "C" int pg_tp_gemm_rs_norm_ag(const void* a, const void* w, int T, int hi
   tp.timing = g_tp_timing;
   g_tp_last_site = site;
   return gemm_impl(a, w, (float*)part[rank] + part_offset, 1, T, hidden, K, lda, ldw, hidden, ws, ws_bytes, counters, counter_bytes, status, 0, &tp, nullptr, stream);
+}
+
+// The decode-chain form of the GEMM (T <= 64): optional deferred-RMSNorm scaling of the input rows
+// (`in_ssp` [in_parts][T] sums of squares written by the producer, nullptr = none) and a fused
+// epilogue: 0 plain, 1 SwiGLU over interleaved (gate, up) weight rows (y is [T, M / 2]), 2 residual
+// add + norm-weight product (y = xw [T, M], `residual` updated in place, `out_ssp` [ceil(M / 128)][T]
+// written).  Returns PG_ERR_UNSUPPORTED when the problem does not plan onto the on-chip split-K path;
+// the caller then runs the separate kernels.
+extern "C" int pg_gemm_bf16_tn_fused(const void* x, const void* w, void* y, int T, int M, int K, long long ldx, long long ldw, long long ldy,
+                                     const void* in_ssp, int in_parts, int in_width, float in_eps, int epi, void* residual, long long ld_res,
+                                     const void* norm_w, int norm_offset, void* out_ssp, void* ws, long long ws_bytes, void* counters,
+                                     long long counter_bytes, void* status, cudaStream_t stream) {
+  PG_REQUIRE(epi >= EPI_PLAIN && epi <= EPI_RESID_NORMW, "gemm fused: unknown epilogue %d", epi);
+  PG_REQUIRE(T <= 64, "gemm fused: built for decode steps of at most 64 token rows, got %d", T);
+  PG_REQUIRE(in_ssp == nullptr || (in_parts > 0 && in_width > 0), "gemm fused: input scale needs its part count and width");
+  if (epi == EPI_SWIGLU) PG_REQUIRE(M % 4 == 0 && ldy % 2 == 0, "gemm fused: SwiGLU needs M %% 4 == 0");
+  if (epi == EPI_RESID_NORMW) {
+    PG_REQUIRE(M % BM == 0, "gemm fused: residual + norm epilogue needs M (%d) to be a multiple of %d", M, BM);
+    PG_REQUIRE(residual && norm_w && out_ssp && ld_res % 4 == 0 && ldy % 4 == 0 && ((uintptr_t)residual & 7) == 0 && ((uintptr_t)norm_w & 7) == 0 && ((uintptr_t)y & 7) == 0,
+               "gemm fused: residual, norm weight and output must be given and 8-byte aligned");
+  }
+  FuseSpec f;
+  memset(&f, 0, sizeof(f));
+  f.epi = epi;
+  f.in_ssp = (const float*)in_ssp;
+  f.in_parts = in_parts;
+  f.in_width = in_width;
+  f.in_eps = in_eps;
+  f.residual = (bf16*)residual;
+  f.ld_res = ld_res;
+  f.norm_w = (const bf16*)norm_w;
+  f.norm_offset = norm_offset;
+  f.out_ssp = (float*)out_ssp;
+  return gemm_impl(x, w, y, 0, T, M, K, ldx, ldw, ldy, ws, ws_bytes, counters, counter_bytes, status, 0, nullptr, nullptr, stream, nullptr, &f);
 }
 
 extern "C" int pg_tp_wait(const void* wait_flags, int world, unsigned long long wait_ns, void* status, cudaStream_t stream) {

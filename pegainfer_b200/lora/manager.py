@@ -93,6 +93,10 @@ class LoraManager:
                 self.A[(li, p)] = torch.zeros((max_loras, self.r_max, k_in), dtype=dt, device=dev)
                 self.B[(li, p)] = torch.zeros((max_loras, m_out, self.r_max), dtype=dt, device=dev)
         model.lora = self
+        if hasattr(model, "set_gate_up_layout"):
+            # adapter deltas address the gate and up halves of the fused projection
+            model.fused_decode = False
+            model.set_gate_up_layout(False)
         if self.engine is not None:
             self.engine.scheduler.lora = self
 

@@ -72,8 +72,33 @@ class Qwen3Model:
         self.q_heads = cfg.num_q_heads // tp.world
         self.kv_heads = cfg.num_kv_heads // tp.world
         source = source or RandomSource(qwen3_shapes(cfg), seed=seed, dtype=dtype)
+        self.gate_up_interleaved = False
         self._load(source)
         self.cos, self.sin = rope_tables(cfg.max_position, cfg.rotary_dim, cfg.rope_theta, dtype, self.device)
+        # Decode steps on one GPU run a fused chain: SwiGLU inside the gate_up GEMM (its weight rows
+        # interleaved as gate_0, up_0, gate_1, ...) and the residual add + RMSNorm folded into the
+        # row-parallel GEMMs and their consumers.  PEGAINFER_FUSED_DECODE=0 keeps the separate kernels.
+        import os
+
+        self.fused_decode = self.device.type == "cuda" and tp.world == 1 and dtype == torch.bfloat16 and os.environ.get("PEGAINFER_FUSED_DECODE", "1") != "0"
+        if self.fused_decode:
+            self.set_gate_up_layout(True)
+
+    def set_gate_up_layout(self, interleaved: bool) -> None:
+        """Reorder the rows of every fused gate_up weight in place: ``[gate; up]`` halves
+        (``interleaved=False``; what adapter deltas address) or alternating (gate_i, up_i) rows
+        (what the fused SwiGLU epilogue reads)."""
+        if interleaved == self.gate_up_interleaved:
+            return
+        for l in self.layers:
+            w = l.gate_up
+            i = w.shape[0] // 2
+            if interleaved:
+                l.gate_up = torch.stack((w[:i], w[i:]), 1).reshape(w.shape).contiguous()
+            else:
+                l.gate_up = torch.cat((w[0::2], w[1::2]), 0).contiguous()
+            del w
+        self.gate_up_interleaved = interleaved
 
     # -- loading ---------------------------------------------------------------
     def _load(self, src: WeightSource) -> None:
@@ -131,12 +156,19 @@ class Qwen3Model:
         x = ops.rms_norm(residual, self.layers[0].input_norm, eps)
         aux = []
         n = len(self.layers)
+        il = self.gate_up_interleaved
+        fused = self._fused_chain_ok(meta)
+        if fused:
+            from ..ops import cuda as K
         for i, l in enumerate(self.layers):
             ls = meta.lora_slots if self.lora is not None else None
             decode = ls is None and meta.num_tokens <= 256  # weight-streaming regime: chain L2 prefetches GEMM to GEMM
             if decode:
                 ops.prefetch_weights(l.o)
-            qkv = tp.col_linear(x, l.qkv)
+            if fused:
+                qkv = K.linear_fused(x, l.qkv)  # completes the previous layer's deferred norm, if any
+            else:
+                qkv = tp.col_linear(x, l.qkv)
             if ls is not None:
                 qs, ks = self.q_heads * cfg.head_dim, self.kv_heads * cfg.head_dim
                 self.lora.apply(i, "q_proj", x, qkv[:, :qs], ls)
@@ -145,13 +177,27 @@ class Qwen3Model:
             q = ops.qk_norm_rope_append(qkv, l.q_norm, l.k_norm, self.cos, self.sin, meta, kv.layer(i), self.q_heads, self.kv_heads, cfg.head_dim, eps)
             a = ops.paged_attention(q, kv.layer(i), meta)
             next_norm = self.layers[i + 1].input_norm if i + 1 < n else self.final_norm
-            if ls is None:
+            if fused:
+                # o_proj (+ residual, x post_norm weight) -> gate_up (x inverse RMS, SwiGLU) -> down (+ residual,
+                # x next norm weight); the next qkv GEMM (or the final norm kernel) completes the last norm
+                ops.prefetch_weights(l.gate_up)
+                xd = K.linear_fused(a, l.o, K.EPI_RESID_NORMW, residual=residual, norm_w=l.post_norm, eps=eps)
+                ops.prefetch_weights(l.down)
+                act = K.linear_fused(xd, l.gate_up, K.EPI_SWIGLU)
+                last = i + 1 == n or i in aux_layers
+                if last:
+                    ops.prefetch_weights(self.layers[i + 1].qkv if i + 1 < n else self.lm_head)
+                    x = ops.add_rms_norm(K.linear(act, l.down), residual, next_norm, eps)
+                else:
+                    ops.prefetch_weights(self.layers[i + 1].qkv)
+                    x = K.linear_fused(act, l.down, K.EPI_RESID_NORMW, residual=residual, norm_w=next_norm, eps=eps)
+            elif ls is None:
                 if decode:
                     ops.prefetch_weights(l.gate_up)
                 x = tp.row_linear_add_norm(a, l.o, residual, l.post_norm, eps)
                 if decode:
                     ops.prefetch_weights(l.down)
-                act = ops.swiglu(tp.col_linear(x, l.gate_up))
+                act = ops.swiglu(tp.col_linear(x, l.gate_up), il)
                 if decode:
                     ops.prefetch_weights(self.layers[i + 1].qkv if i + 1 < n else self.lm_head)
                 x = tp.row_linear_add_norm(act, l.down, residual, next_norm, eps)
@@ -172,6 +218,23 @@ class Qwen3Model:
         self.last_aux = aux
         tp.sync()
         return x
+
+    def _fused_chain_ok(self, meta: AttnMeta) -> bool:
+        """The fused decode chain serves steps of up to 64 token rows without adapter deltas, when every
+        projection plans onto the GEMM's on-chip split-K path (decided once per row count)."""
+        if not self.fused_decode or self.lora is not None or meta.num_tokens > 64 or ops.get_mode() != "sm100":
+            return False
+        from ..ops import cuda as K
+
+        t = int(meta.num_tokens)
+        ok = self._fused_ok.get(t) if hasattr(self, "_fused_ok") else None
+        if ok is None:
+            if not hasattr(self, "_fused_ok"):
+                self._fused_ok = {}
+            l = self.layers[0]
+            ok = all(K.fused_plan_ok(t, w.shape[0], w.shape[1]) for w in (l.qkv, l.o, l.gate_up, l.down)) and self.cfg.hidden_size % 128 == 0
+            self._fused_ok[t] = ok
+        return ok and not K.batch_invariant()
 
     def logits(self, hidden: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         if rows is not None:

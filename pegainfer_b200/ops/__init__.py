@@ -66,8 +66,8 @@ def gated_rms_norm(x, gate, w, eps):
     return _impl(x).gated_rms_norm(x, gate, w, eps)
 
 
-def swiglu(gate_up):
-    return _impl(gate_up).swiglu(gate_up)
+def swiglu(gate_up, interleaved=False):
+    return _impl(gate_up).swiglu(gate_up, interleaved)
 
 
 def linear(x, w, out_dtype=None):

@@ -195,14 +195,65 @@ def gated_rms_norm(x, gate, w, eps):
     return y
 
 
-def swiglu(gate_up):
+def swiglu(gate_up, interleaved: bool = False):
+    """``bf16(silu(gate)) * up``; ``interleaved``: columns are (gate_0, up_0, gate_1, up_1, ...)."""
     _bf16(gate_up)
     g2 = _rows2d(gate_up)
     inter = g2.shape[1] // 2
     out = torch.empty((g2.shape[0], inter), dtype=g2.dtype, device=g2.device)
     c = ctx(g2.device)
-    _check(lib().pg_swiglu(_ptr(g2), _ptr(out), _ci(g2.shape[0]), _ci(inter), _ll(g2.stride(0)), _ll(out.stride(0)), _stream()), c)
+    _check(lib().pg_swiglu(_ptr(g2), _ptr(out), _ci(g2.shape[0]), _ci(inter), _ll(g2.stride(0)), _ll(out.stride(0)), _ci(int(interleaved)), _stream()), c)
     return out.view(*gate_up.shape[:-1], inter)
+
+
+class DeferredNorm:
+    """Activations whose RMSNorm is still owed its per-token scale: ``xw = h * norm_w`` plus the
+    per-(weight tile, token) sums of squares of ``h``.  The GEMM that consumes ``xw`` applies
+    ``rsqrt(sum(ssp) / width + eps)`` to every output element of the token."""
+
+    __slots__ = ("xw", "ssp", "width", "eps")
+
+    def __init__(self, xw, ssp, width, eps):
+        self.xw, self.ssp, self.width, self.eps = xw, ssp, width, eps
+
+
+FUSED_MAX_ROWS = 64
+EPI_PLAIN, EPI_SWIGLU, EPI_RESID_NORMW = 0, 1, 2
+
+
+def fused_plan_ok(t: int, m: int, k: int) -> bool:
+    """Does ``linear_fused`` run this problem on the on-chip split-K path (fused epilogues live there)?"""
+    return t <= FUSED_MAX_ROWS and not _BATCH_INVARIANT and gemm_plan(t, m, k)["cluster"] > 1
+
+
+def linear_fused(x, w, epilogue: int = EPI_PLAIN, residual=None, norm_w=None, norm_offset: bool = False, eps: float = 0.0):
+    """Decode-chain GEMM.  ``x``: a bf16 ``[T, K]`` tensor or a ``DeferredNorm``.  ``epilogue``:
+    ``EPI_PLAIN`` -> ``[T, M]``; ``EPI_SWIGLU`` (interleaved gate/up weight rows) -> ``[T, M / 2]``;
+    ``EPI_RESID_NORMW`` -> updates ``residual`` in place and returns a ``DeferredNorm`` for the norm
+    with weight ``norm_w`` (its consumer completes it)."""
+    dn = x if isinstance(x, DeferredNorm) else None
+    xin = dn.xw if dn is not None else x
+    _bf16(xin)
+    _bf16(w)
+    t, k = xin.shape
+    m = w.shape[0]
+    assert w.shape[1] == k and xin.stride(-1) == 1 and w.stride(-1) == 1
+    c = ctx(xin.device)
+    out = torch.empty((t, m // 2 if epilogue == EPI_SWIGLU else m), dtype=torch.bfloat16, device=xin.device)
+    ssp = None
+    if epilogue == EPI_RESID_NORMW:
+        assert residual is not None and norm_w is not None and residual.stride(-1) == 1
+        ssp = torch.empty(((m + 127) // 128, t), dtype=torch.float32, device=xin.device)
+    rc = lib().pg_gemm_bf16_tn_fused(
+        _ptr(xin), _ptr(w), _ptr(out), _ci(t), _ci(m), _ci(k), _ll(xin.stride(0)), _ll(w.stride(0)), _ll(out.stride(0)),
+        _ptr(dn.ssp) if dn is not None else _vp(0), _ci(dn.ssp.shape[0] if dn is not None else 0), _ci(dn.width if dn is not None else 0), _cf(dn.eps if dn is not None else 0.0),
+        _ci(epilogue), _ptr(residual), _ll(residual.stride(0) if residual is not None else 0), _ptr(norm_w), _ci(int(norm_offset)), _ptr(ssp),
+        _ptr(c.gemm_ws), _ll(c.gemm_ws.numel()), _ptr(c.gemm_counters), _ll(c.gemm_counters.numel() * 4), _ptr(c.status), _stream(),
+    )
+    _check(rc, c)
+    if epilogue == EPI_RESID_NORMW:
+        return DeferredNorm(out, ssp, m, eps)
+    return out
 
 
 def linear(x, w, out_dtype=None, force_splits: int = 0, out: Optional[torch.Tensor] = None):

@@ -90,11 +90,16 @@ def gated_rms_norm(x, gate, w, eps):
     return (xf * inv * w.float() * (g * torch.sigmoid(g))).to(x.dtype)
 
 
-def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
-    """``round(silu(gate)) * up`` on a fused ``[T, 2I]`` buffer (gate first)."""
+def swiglu(gate_up: torch.Tensor, interleaved: bool = False) -> torch.Tensor:
+    """``round(silu(gate)) * up`` on a fused ``[T, 2I]`` buffer: gate half first, or with
+    ``interleaved`` the columns alternate (gate_0, up_0, gate_1, up_1, ...)."""
     i = gate_up.shape[-1] // 2
-    g = gate_up[..., :i].float()
-    u = gate_up[..., i:].float()
+    if interleaved:
+        g = gate_up[..., 0::2].float()
+        u = gate_up[..., 1::2].float()
+    else:
+        g = gate_up[..., :i].float()
+        u = gate_up[..., i:].float()
     s = (g * torch.sigmoid(g)).to(gate_up.dtype).float()
     return (s * u).to(gate_up.dtype)
 

@@ -228,6 +228,14 @@ class TorchExecutor(ModelExecutor):
                 toks = toks.tolist()
             return StepResult(tokens={s.rid: [toks[i]] for i, s in enumerate(seqs)}, elapsed_s=time.perf_counter() - t0)
         token_ids, meta = build_meta(seqs, self.page_size, self.device)
+        if meta.decode_only and self.device.type == "cuda" and self.max_blocks_per_seq:
+            # the same KV-split plan a captured graph of this batch size uses (it depends on the batch
+            # size and the longest sequence the engine admits, not on the live lengths), so an eager
+            # decode step and a graph replay of the same batch are bit-identical
+            from ..ops import cuda as K
+
+            geo = self.model.kv_geometry()
+            meta.plan = K.plan_decode_splits(len(seqs), geo["kv_heads"], min(self.max_blocks_per_seq * self.page_size, 2048), self.device)
         if any(s.lora_slot >= 0 for s in seqs):
             rows = []
             for s in seqs:

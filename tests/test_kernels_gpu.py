@@ -568,3 +568,71 @@ def test_lora_delta_kernel_mixed_slots(t, k, m, r, slots_n):
     assert torch.equal(y1[untouched], wide[untouched])
     assert torch.equal(y1[:, :128], wide[:, :128]) and torch.equal(y1[:, 128 + m :], wide[:, 128 + m :])
     status_clean()
+
+
+@pytest.mark.parametrize("t", [1, 7, 64])
+def test_fused_decode_chain_matches_separate_kernels(t):
+    K = cu()
+    """o_proj with the residual add and the norm-weight product in its epilogue, a consumer GEMM that
+    completes the RMSNorm with the per-token scale (and applies SwiGLU over interleaved gate/up rows),
+    against GEMM -> add + RMSNorm -> GEMM -> SwiGLU as separate kernels."""
+    torch.manual_seed(t)
+    h, kq, inter = 1024, 1024, 1536
+    eps = 1e-6
+    a = (torch.randn(t, kq, device=DEV) * 0.5).bfloat16()
+    wo = (torch.randn(h, kq, device=DEV) * 0.03).bfloat16()
+    res0 = torch.randn(t, h, device=DEV).bfloat16()
+    nw = (1.0 + 0.1 * torch.randn(h, device=DEV)).bfloat16()
+    wg = (torch.randn(inter, h, device=DEV) * 0.03).bfloat16()
+    wu = (torch.randn(inter, h, device=DEV) * 0.03).bfloat16()
+    w_il = torch.stack((wg, wu), 1).reshape(2 * inter, h).contiguous()
+    if not K.fused_plan_ok(t, h, kq) or not K.fused_plan_ok(t, 2 * inter, h):
+        pytest.skip("this shape does not plan onto the on-chip split-K path")
+    # separate kernels
+    res_ref = res0.clone()
+    x_ref = K.add_rms_norm(K.linear(a, wo), res_ref, nw, eps)
+    act_ref = K.swiglu(K.linear(x_ref, torch.cat((wg, wu), 0)))
+    plain_ref = K.linear(x_ref, wg)
+    # fused chain
+    res = res0.clone()
+    dn = K.linear_fused(a, wo, K.EPI_RESID_NORMW, residual=res, norm_w=nw, eps=eps)
+    act = K.linear_fused(dn, w_il, K.EPI_SWIGLU)
+    plain = K.linear_fused(dn, wg)
+    torch.cuda.synchronize()
+    # the fused epilogue adds the residual to the f32 accumulator; the separate kernels round the
+    # projection to bf16 first: at most one bf16 step apart, and the fused one is the closer of the two
+    exact = res0.float() + a.float() @ wo.float().t()
+    assert (res.float() - res_ref.float()).abs().max() <= 2 ** -7 * exact.abs().max()
+    assert (res.float() - exact).abs().max() <= (res_ref.float() - exact).abs().max() + 1e-6
+    # the normalised activations differ only by where the bf16 rounding sits (before or after the scale)
+    inv = torch.rsqrt(res.float().pow(2).mean(-1, keepdim=True) + eps)
+    assert torch.allclose(dn.ssp.sum(0), res.float().pow(2).sum(-1), rtol=1e-4)
+    x_exact = res.float() * inv * nw.float()
+    assert (dn.xw.float() * inv - x_exact).abs().max() <= 2 ** -7 * x_exact.abs().max()
+    for got, ref in ((plain, plain_ref), (act, act_ref)):
+        err = (got.float() - ref.float()).abs().max().item()
+        assert err <= 2e-2 * max(1.0, ref.float().abs().max().item()), err
+    # bit-reproducible
+    res2 = res0.clone()
+    dn2 = K.linear_fused(a, wo, K.EPI_RESID_NORMW, residual=res2, norm_w=nw, eps=eps)
+    assert torch.equal(K.linear_fused(dn2, w_il, K.EPI_SWIGLU), act) and torch.equal(dn2.ssp, dn.ssp)
+    # a row's result does not depend on how many padding rows ride along in the same token tile
+    if t < 16:
+        pad = 16 - t
+        a_p = torch.cat((a, torch.zeros(pad, kq, device=DEV, dtype=a.dtype)), 0)
+        res_p = torch.cat((res0, torch.zeros(pad, h, device=DEV, dtype=a.dtype)), 0)
+        dn_p = K.linear_fused(a_p, wo, K.EPI_RESID_NORMW, residual=res_p, norm_w=nw, eps=eps)
+        act_p = K.linear_fused(dn_p, w_il, K.EPI_SWIGLU)
+        assert torch.equal(res_p[:t], res) and torch.equal(act_p[:t], act)
+    assert K.read_status(DEV) == 0
+
+
+def test_swiglu_interleaved_layout():
+    K = cu()
+    torch.manual_seed(5)
+    g = torch.randn(33, 256, device=DEV).bfloat16()
+    u = torch.randn(33, 256, device=DEV).bfloat16()
+    halves = torch.cat((g, u), 1)
+    il = torch.stack((g, u), 2).reshape(33, 512).contiguous()
+    assert torch.equal(K.swiglu(il, True), K.swiglu(halves))
+    assert torch.equal(K.swiglu(il, True), R.swiglu(il, True))
