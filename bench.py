@@ -262,6 +262,18 @@ def kernel_only(args, eng, rank, world, device):
     from pegainfer_b200.ops import cuda as K
 
     assert K.read_status(device) == 0, f"device status word set: {K.read_status(device):#x}"
+    if K.GemmTrace.enabled and rank == 0:
+        # phase stamps of the GEMMs of the captured step (the capture was the last pass that armed them)
+        rows = K.GemmTrace.dump(*graphs.trace_range[(b, True)], detail=True)
+        names = ["", "", "x ready", "loads issued", "first MMA", "last MMA issued", "accumulator ready", "partial pushed", "cluster partials in", "reduced + stored", "roles done", "exit"]
+        for r in rows[4:8]:  # the four GEMMs of the second layer: per-CTA spread of every phase, us after the median 'x ready'
+            print(f"  {r[0]}: " + "; ".join(f"{names[j]} {v[0]}/{v[1]}/{v[2]}" for j, v in sorted(r[6].items())), file=sys.stderr)
+        rows = [r[:6] for r in rows]
+        prev_exit = None
+        print("gemm timeline of the last replay (us): label, entry, x ready, first MMA, last MMA issued, exit, gap since previous exit", file=sys.stderr)
+        for lab, a, b_, c, d, e in rows[: 4 * 3 + 1] + rows[-5:]:
+            print(f"  {lab:28s} {a:9.2f} {b_:9.2f} {c:9.2f} {d:9.2f} {e:9.2f}   {'' if prev_exit is None else round(a - prev_exit, 2)}", file=sys.stderr)
+            prev_exit = e
     return dict(ms_total=ms, clocks=clocks, prefill_s=prefill_s, kernels_per_step=graphs.kernels_per_graph.get((b, True), 0), last_tokens=last[:4], all_last_tokens=last)
 
 

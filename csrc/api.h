@@ -40,9 +40,11 @@ int pg_tp_gemm_rs_norm_ag(const void* a, const void* w, int T, int hidden, int K
 // (0 plain, 1 SwiGLU over interleaved gate/up rows, 2 residual add + norm-weight product + per-tile sums
 // of squares); PG_ERR_UNSUPPORTED when the problem does not plan onto the on-chip split-K path.
 int pg_gemm_bf16_tn_fused(const void* x, const void* w, void* y, int T, int M, int K, long long ldx, long long ldw, long long ldy,
-                          const void* in_ssp, int in_parts, int in_width, float in_eps, int epi, void* residual, long long ld_res,
-                          const void* norm_w, int norm_offset, void* out_ssp, void* ws, long long ws_bytes, void* counters,
+                          const void* in_ssp, int in_parts, int in_ld, int in_width, float in_eps, int epi, void* residual, long long ld_res,
+                          const void* norm_w, int norm_offset, void* out_ssp, int out_ld, void* ws, long long ws_bytes, void* counters,
                           long long counter_bytes, void* status, cudaStream_t stream);
+// Write a captured cudaGraph_t as Graphviz DOT (graph_export.cu); counts = {nodes, edges, kernel nodes, programmatic edges}.
+int pg_graph_export_dot(void* graph, const char* path, const char* title, long long* counts);
 int pg_tp_wait(const void* wait_flags, int world, unsigned long long wait_ns, void* status, cudaStream_t stream);
 int pg_symm_alloc(long long bytes, void** out);
 int pg_symm_free(void* p);

@@ -82,7 +82,8 @@ struct WaitSpec {
 enum { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_RESID_NORMW = 2 };
 struct FuseSpec {
   int epi;
-  const float* in_ssp;  // consumer side: [in_parts][T] sums of squares of the input rows (nullptr = input is already normalised)
+  const float* in_ssp;  // consumer side: [T][in_ld] sums of squares of the input rows, in_parts valid per row (nullptr = input is already normalised)
+  int in_ld;            // row pitch of in_ssp in floats (a multiple of 4: rows are read with 16-byte loads)
   int in_parts;
   int in_width;         // H of the normalised vector
   float in_eps;
@@ -90,7 +91,8 @@ struct FuseSpec {
   long long ld_res;
   const bf16* norm_w;   // EPI_RESID_NORMW: weight of the norm that the consumer completes
   int norm_offset;      // (1 + w) form
-  float* out_ssp;       // EPI_RESID_NORMW: [m_tiles][T]
+  float* out_ssp;       // EPI_RESID_NORMW: [T][out_ld], entry [n][m_tile]
+  int out_ld;
 };
 
 struct GemmParams {
@@ -199,12 +201,14 @@ __device__ __forceinline__ float tp_sum_rows(const float* src_row, size_t src_st
 
 // Four consecutive output features m..m+3 of token row n (the vector form of store_out).
 // Returns this thread's contribution to the row's sum of squares (EPI_RESID_NORMW, else 0).
-__device__ __forceinline__ float store_out4(const GemmParams& p, int n, int m, float4 v, const float* s_inv = nullptr, int n_local = 0) {
+template <int EPI = EPI_PLAIN>
+__device__ __forceinline__ float store_out4(const GemmParams& p, int n, int m, float4 v, const float* s_inv = nullptr, int n_local = 0,
+                                            bool have_pre = false, uint2 pre_res = make_uint2(0u, 0u), uint2 pre_w = make_uint2(0u, 0u)) {
   if (s_inv) {
     const float sc = s_inv[n_local];
     v.x *= sc, v.y *= sc, v.z *= sc, v.w *= sc;
   }
-  if (p.fuse.epi == EPI_SWIGLU) {
+  if (EPI == EPI_SWIGLU) {
     // rows (m, m+1) = (gate, up) of feature m / 2, rows (m+2, m+3) of the next one
     if (m + 3 < p.M) {
       const float g0 = bf16_round(v.x), u0 = bf16_round(v.y), g1 = bf16_round(v.z), u1 = bf16_round(v.w);
@@ -213,10 +217,10 @@ __device__ __forceinline__ float store_out4(const GemmParams& p, int n, int m, f
     }
     return 0.f;
   }
-  if (p.fuse.epi == EPI_RESID_NORMW) {
+  if (EPI == EPI_RESID_NORMW) {
     if (m + 3 >= p.M) return 0.f;
     bf16* rr = p.fuse.residual + (size_t)n * p.fuse.ld_res + m;
-    const uint2 rv = *reinterpret_cast<const uint2*>(rr);
+    const uint2 rv = have_pre ? pre_res : *reinterpret_cast<const uint2*>(rr);
     const float2 r0 = __bfloat1622float2(*reinterpret_cast<const bf162*>(&rv.x)), r1 = __bfloat1622float2(*reinterpret_cast<const bf162*>(&rv.y));
     const bf162 h0 = __floats2bfloat162_rn(v.x + r0.x, v.y + r0.y), h1 = __floats2bfloat162_rn(v.z + r1.x, v.w + r1.y);
     uint2 hp;
@@ -224,7 +228,7 @@ __device__ __forceinline__ float store_out4(const GemmParams& p, int n, int m, f
     hp.y = *reinterpret_cast<const uint32_t*>(&h1);
     *reinterpret_cast<uint2*>(rr) = hp;
     const float2 f0 = __bfloat1622float2(h0), f1 = __bfloat1622float2(h1);  // the rounded sum is what gets normalised
-    const uint2 wv = *reinterpret_cast<const uint2*>(p.fuse.norm_w + m);
+    const uint2 wv = have_pre ? pre_w : *reinterpret_cast<const uint2*>(p.fuse.norm_w + m);
     float2 w0 = __bfloat1622float2(*reinterpret_cast<const bf162*>(&wv.x)), w1 = __bfloat1622float2(*reinterpret_cast<const bf162*>(&wv.y));
     if (p.fuse.norm_offset) w0.x += 1.f, w0.y += 1.f, w1.x += 1.f, w1.y += 1.f;
     const bf162 x0 = __floats2bfloat162_rn(f0.x * w0.x, f0.y * w0.y), x1 = __floats2bfloat162_rn(f1.x * w1.x, f1.y * w1.y);
@@ -283,13 +287,25 @@ __device__ __forceinline__ float store_out4(const GemmParams& p, int n, int m, f
 // mbarrier, so the reduction itself reads local shared memory only: this function sums the
 // S slots in split order (deterministic) and stores the result.  A thread takes 4 rows of
 // one column per pass, 4 columns per pass across the 128 epilogue threads.
+// Residual values (4 bf16) of one token column of this thread's rows.
+__device__ __forceinline__ uint2 load_resid(const GemmParams& p, int n, int m) {
+  return (m + 3 < p.M) ? *reinterpret_cast<const uint2*>(p.fuse.residual + (size_t)n * p.fuse.ld_res + m) : make_uint2(0u, 0u);
+}
+
+// `first_res` / `norm_wv` (EPI_RESID_NORMW): the residual of this thread's first column and its norm
+// weights, loaded by the caller while the main loop still ran; the residual of column i + 1 is loaded
+// while column i is reduced, so no global load sits on the dependent path of the tail.
+template <int EPI>
 __device__ __forceinline__ void cluster_reduce_local(const GemmParams& p, const float* kred, int S, int w, uint32_t cr, int et, int n0, int m0, int m_tile,
-                                                     const float* s_inv) {
+                                                     const float* s_inv, uint2 first_res, uint2 norm_wv) {
   const int nmax = min(p.bn, p.T - n0);
   const int c_lo = (int)cr * w;
   const int ncols = min(nmax, c_lo + w) - c_lo;
   const int sub = et >> 5, r4 = (et & 31) * 4;
+  uint2 cur = first_res;
   for (int j = sub; j < ncols; j += 4) {  // one warp = one token column across all 128 weight rows of the tile
+    uint2 nxt = make_uint2(0u, 0u);
+    if (EPI == EPI_RESID_NORMW && j + 4 < ncols) nxt = load_resid(p, n0 + c_lo + j + 4, m0 + r4);
     const float* src = kred + (size_t)j * BM + r4;
     float4 a = *reinterpret_cast<const float4*>(src);
 #pragma unroll 4
@@ -300,10 +316,11 @@ __device__ __forceinline__ void cluster_reduce_local(const GemmParams& p, const 
       a.z += b.z;
       a.w += b.w;
     }
-    float ss = store_out4(p, n0 + c_lo + j, m0 + r4, a, s_inv, c_lo + j);
-    if (p.fuse.epi == EPI_RESID_NORMW) {
+    float ss = store_out4<EPI>(p, n0 + c_lo + j, m0 + r4, a, s_inv, c_lo + j, EPI == EPI_RESID_NORMW, cur, norm_wv);
+    if (EPI == EPI_RESID_NORMW) {
       ss = warp_sum(ss);
-      if ((et & 31) == 0) p.fuse.out_ssp[(size_t)m_tile * p.T + n0 + c_lo + j] = ss;
+      if ((et & 31) == 0) p.fuse.out_ssp[(size_t)(n0 + c_lo + j) * p.fuse.out_ld + m_tile] = ss;
+      cur = nxt;
     }
   }
 }
@@ -340,6 +357,9 @@ __device__ __forceinline__ bool wait_epochs(const uint32_t* flags, int n, uint32
   return true;
 }
 
+// EPI / INV are compile-time so that each variant carries only its own epilogue: EPI is the fused
+// epilogue (FuseSpec), INV says whether the input rows still owe their RMSNorm scale.
+template <int EPI, bool INV>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -555,23 +575,46 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     const uint32_t cr = p.cluster > 1 ? cluster_ctarank() : 0u;
     const int kw = p.cluster > 1 ? (p.bn + p.cluster - 1) / p.cluster : p.bn;  // columns per slice
     bool cluster_arrived = false;
-    const float* s_inv = p.fuse.in_ssp ? s_inv_buf : nullptr;
+    const float* s_inv = INV ? s_inv_buf : nullptr;
     int inv_tile = -1;
     for (int item = blockIdx.x; item < total; item += gridDim.x) {
       const int tile = item / p.splits, s = item - tile * p.splits;
       const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
-      if (s_inv && n_tile != inv_tile) {
+      if (INV && n_tile != inv_tile) {
         // inverse RMS of this token tile's input rows, from the producer's per-tile sums of squares
         // (fixed summation order); computed while the main loop runs
         if (inv_tile >= 0) named_bar_all(1, 128, true);  // nobody still reads the previous tile's values
+        // one thread per token: the row's per-tile sums are contiguous, read with 16-byte loads that are
+        // all in flight together, summed in ascending tile order
         for (int nl = et; nl < p.bn; nl += 128) {
           const int n = n_tile * p.bn + nl;
           float ss = 0.f;
-          if (n < p.T)
-            for (int q = 0; q < p.fuse.in_parts; ++q) ss += __ldcg(p.fuse.in_ssp + (size_t)q * p.T + n);
+          if (n < p.T) {
+            const float4* src = reinterpret_cast<const float4*>(p.fuse.in_ssp + (size_t)n * p.fuse.in_ld);
+            for (int q = 0; q < p.fuse.in_parts; q += 32) {
+              float4 v[8];
+#pragma unroll
+              for (int u = 0; u < 8; ++u) v[u] = (q + 4 * u < p.fuse.in_parts) ? __ldcg(src + (q >> 2) + u) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+              for (int u = 0; u < 8; ++u) {
+                const int b = q + 4 * u;
+                ss += (b < p.fuse.in_parts ? v[u].x : 0.f);
+                ss += (b + 1 < p.fuse.in_parts ? v[u].y : 0.f);
+                ss += (b + 2 < p.fuse.in_parts ? v[u].z : 0.f);
+                ss += (b + 3 < p.fuse.in_parts ? v[u].w : 0.f);
+              }
+            }
+          }
           s_inv_buf[nl] = rsqrtf(ss / (float)p.fuse.in_width + p.fuse.in_eps);
         }
         inv_tile = n_tile;
+      }
+      uint2 first_res = make_uint2(0u, 0u), norm_wv = make_uint2(0u, 0u);
+      if (EPI == EPI_RESID_NORMW && p.cluster > 1) {
+        // this thread's norm weights and the residual of its first column, fetched while the main loop runs
+        const int mm = m_tile * BM + (et & 31) * 4, n_first = n_tile * p.bn + (int)cr * kw + (et >> 5);
+        if (mm + 3 < p.M) norm_wv = *reinterpret_cast<const uint2*>(p.fuse.norm_w + mm);
+        if (n_first < p.T) first_res = load_resid(p, n_first, mm);
       }
       bool ok = mbar_wait(&tfull[acc], acc_phase, abort_flag);
       // cluster mode: every owner must have reduced the previous item before its slots are overwritten
@@ -650,7 +693,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         if (tstamp && et == 0) tstamp[7] = globaltimer_ns();
         const bool full_ok = named_bar_all(1, 128, mbar_wait_cluster(kfull, kphase, abort_flag));
         if (tstamp && et == 0) tstamp[8] = globaltimer_ns();
-        if (full_ok) cluster_reduce_local(p, kred, (int)S, kw, cr, et, n0, m_tile * BM, m_tile, s_inv);
+        if (full_ok) cluster_reduce_local<EPI>(p, kred, (int)S, kw, cr, et, n0, m_tile * BM, m_tile, s_inv, first_res, norm_wv);
         if (tstamp && et == 0) tstamp[9] = globaltimer_ns();
         // this CTA's slots may be overwritten by the next item (also said on the abort path, so nobody waits in vain)
         if (!last_item) {
@@ -1024,7 +1067,12 @@ static int gemm_impl(const void* x, const void* w, void* y, int y_is_f32, int T,
     if (!di.attr_set) {
       PG_CUDA(cudaDeviceGetAttribute(&di.sms, cudaDevAttrMultiProcessorCount, dev));
       PG_CUDA(cudaDeviceGetAttribute(&di.max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
-      PG_CUDA(cudaFuncSetAttribute(gemm_bf16_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem));
+      PG_CUDA(cudaFuncSetAttribute(gemm_bf16_tn_kernel<EPI_PLAIN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem));
+      PG_CUDA(cudaFuncSetAttribute(gemm_bf16_tn_kernel<EPI_PLAIN, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem));
+      PG_CUDA(cudaFuncSetAttribute(gemm_bf16_tn_kernel<EPI_SWIGLU, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem));
+      PG_CUDA(cudaFuncSetAttribute(gemm_bf16_tn_kernel<EPI_SWIGLU, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem));
+      PG_CUDA(cudaFuncSetAttribute(gemm_bf16_tn_kernel<EPI_RESID_NORMW, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem));
+      PG_CUDA(cudaFuncSetAttribute(gemm_bf16_tn_kernel<EPI_RESID_NORMW, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem));
       di.max_clusters[1] = di.sms;
       const char* env = getenv("PEGAINFER_GEMM_CLUSTER");
       const bool use_clusters = !(env && env[0] == '0');
@@ -1042,7 +1090,7 @@ static int gemm_impl(const void* x, const void* w, void* y, int y_is_f32, int T,
         cfg.attrs = at;
         cfg.numAttrs = 1;
         int n = 0;
-        if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_tn_kernel, &cfg) == cudaSuccess) di.max_clusters[s] = n;
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_tn_kernel<EPI_PLAIN, false>, &cfg) == cudaSuccess) di.max_clusters[s] = n;
         else (void)cudaGetLastError();
       }
       di.attr_set = true;
@@ -1159,7 +1207,17 @@ static int gemm_impl(const void* x, const void* w, void* y, int y_is_f32, int T,
     ++na;
   }
   cfg.numAttrs = (unsigned)na;
-  PG_CUDA(cudaLaunchKernelEx(&cfg, gemm_bf16_tn_kernel, tm_w, tm_x, p));
+  const bool inv = p.fuse.in_ssp != nullptr;
+  cudaError_t le;
+  switch (p.fuse.epi * 2 + (inv ? 1 : 0)) {
+    case 1: le = cudaLaunchKernelEx(&cfg, gemm_bf16_tn_kernel<EPI_PLAIN, true>, tm_w, tm_x, p); break;
+    case 2: le = cudaLaunchKernelEx(&cfg, gemm_bf16_tn_kernel<EPI_SWIGLU, false>, tm_w, tm_x, p); break;
+    case 3: le = cudaLaunchKernelEx(&cfg, gemm_bf16_tn_kernel<EPI_SWIGLU, true>, tm_w, tm_x, p); break;
+    case 4: le = cudaLaunchKernelEx(&cfg, gemm_bf16_tn_kernel<EPI_RESID_NORMW, false>, tm_w, tm_x, p); break;
+    case 5: le = cudaLaunchKernelEx(&cfg, gemm_bf16_tn_kernel<EPI_RESID_NORMW, true>, tm_w, tm_x, p); break;
+    default: le = cudaLaunchKernelEx(&cfg, gemm_bf16_tn_kernel<EPI_PLAIN, false>, tm_w, tm_x, p); break;
+  }
+  PG_CUDA(le);
   PG_LAUNCH_CHECK();
   return PG_OK;
 }
@@ -1265,15 +1323,17 @@ extern "C" int pg_tp_gemm_rs_norm_ag(const void* a, const void* w, int T, int hi
 // written).  Returns PG_ERR_UNSUPPORTED when the problem does not plan onto the on-chip split-K path;
 // the caller then runs the separate kernels.
 extern "C" int pg_gemm_bf16_tn_fused(const void* x, const void* w, void* y, int T, int M, int K, long long ldx, long long ldw, long long ldy,
-                                     const void* in_ssp, int in_parts, int in_width, float in_eps, int epi, void* residual, long long ld_res,
-                                     const void* norm_w, int norm_offset, void* out_ssp, void* ws, long long ws_bytes, void* counters,
+                                     const void* in_ssp, int in_parts, int in_ld, int in_width, float in_eps, int epi, void* residual, long long ld_res,
+                                     const void* norm_w, int norm_offset, void* out_ssp, int out_ld, void* ws, long long ws_bytes, void* counters,
                                      long long counter_bytes, void* status, cudaStream_t stream) {
   PG_REQUIRE(epi >= EPI_PLAIN && epi <= EPI_RESID_NORMW, "gemm fused: unknown epilogue %d", epi);
   PG_REQUIRE(T <= 64, "gemm fused: built for decode steps of at most 64 token rows, got %d", T);
-  PG_REQUIRE(in_ssp == nullptr || (in_parts > 0 && in_width > 0), "gemm fused: input scale needs its part count and width");
+  PG_REQUIRE(in_ssp == nullptr || (in_parts > 0 && in_width > 0 && in_ld >= in_parts && in_ld % 4 == 0 && ((uintptr_t)in_ssp & 15) == 0),
+             "gemm fused: input scale needs its part count, width and a 16-byte aligned row pitch that is a multiple of 4");
   if (epi == EPI_SWIGLU) PG_REQUIRE(M % 4 == 0 && ldy % 2 == 0, "gemm fused: SwiGLU needs M %% 4 == 0");
   if (epi == EPI_RESID_NORMW) {
     PG_REQUIRE(M % BM == 0, "gemm fused: residual + norm epilogue needs M (%d) to be a multiple of %d", M, BM);
+    PG_REQUIRE(out_ld >= M / BM, "gemm fused: out_ssp rows hold %d entries, %d weight tiles", out_ld, M / BM);
     PG_REQUIRE(residual && norm_w && out_ssp && ld_res % 4 == 0 && ldy % 4 == 0 && ((uintptr_t)residual & 7) == 0 && ((uintptr_t)norm_w & 7) == 0 && ((uintptr_t)y & 7) == 0,
                "gemm fused: residual, norm weight and output must be given and 8-byte aligned");
   }
@@ -1282,6 +1342,7 @@ extern "C" int pg_gemm_bf16_tn_fused(const void* x, const void* w, void* y, int 
   f.epi = epi;
   f.in_ssp = (const float*)in_ssp;
   f.in_parts = in_parts;
+  f.in_ld = in_ld;
   f.in_width = in_width;
   f.in_eps = in_eps;
   f.residual = (bf16*)residual;
@@ -1289,6 +1350,7 @@ extern "C" int pg_gemm_bf16_tn_fused(const void* x, const void* w, void* y, int 
   f.norm_w = (const bf16*)norm_w;
   f.norm_offset = norm_offset;
   f.out_ssp = (float*)out_ssp;
+  f.out_ld = out_ld;
   return gemm_impl(x, w, y, 0, T, M, K, ldx, ldw, ldy, ws, ws_bytes, counters, counter_bytes, status, 0, nullptr, nullptr, stream, nullptr, &f);
 }
 

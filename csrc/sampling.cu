@@ -3,7 +3,8 @@
 //  * argmax: split partial/finalize, ties resolve to the lowest index; writes int32
 //    tokens straight into the caller's buffer (the next decode step's input under a
 //    CUDA graph).
-//  * sample: one CTA per row.  Online softmax at the row's temperature, then the
+//  * sample: one thread-block cluster per row (sample_cluster_kernel, below); the one-CTA kernel
+//    described here serves vocabularies too large for eight CTAs' shared memory.  Online softmax at the row's temperature, then the
 //    keep-set {top-k AND top-p AND min-p} is found as a threshold on the scaled logit
 //    by a 4-level byte-radix descent carrying (count, mass) of everything above, and
 //    the token is drawn by inverse CDF in vocabulary order from one uniform per row,
@@ -219,7 +220,8 @@ __global__ void __launch_bounds__(ST) sample_kernel(const T* __restrict__ logits
   if (local > 0.f && before <= target && target < s_scan[tid]) atomicMin(&s_owner, tid);
   __syncthreads();
   int owner = s_owner;
-  if (owner == ST) {
+  __syncthreads();  // every thread has read the owner before anyone may change it below
+  if (owner == ST) {  // uniform across the CTA
     // rounding pushed the target past the end: the last thread holding mass owns it
     if (local > 0.f) atomicMax(&s_owner, tid + ST);
     __syncthreads();
@@ -241,6 +243,279 @@ __global__ void __launch_bounds__(ST) sample_kernel(const T* __restrict__ logits
     }
     out[row] = pick >= 0 ? pick : last_kept;
   }
+}
+
+// ---------------------------------------------------------------------------------
+// Cluster sampler: one thread-block cluster per row.  Each CTA of the cluster reads its slice
+// of the row ONCE into shared memory (as tempered f32 logits) and every later pass -- the
+// normaliser, the four radix levels of the threshold search, the inverse-CDF walk -- runs out
+// of shared memory, with the per-CTA partial results combined across the cluster through
+// distributed shared memory.  Probability mass is carried as 2^-40 fixed point in 64-bit
+// integers, so every sum is exact and independent of the order in which threads add to it:
+// the same (logits, controls, uniform) always pick the same token, and the CDF target
+// floor(u * total) is always strictly inside the kept mass (no rounding fallback).
+// ---------------------------------------------------------------------------------
+constexpr int SC_THREADS = 512;
+constexpr int SC_MAX_CLUSTER = 8;
+constexpr float SC_FX = 1099511627776.f;  // 2^40
+
+__device__ __forceinline__ unsigned long long ld_dsmem_u64(uint32_t cluster_addr) {
+  unsigned long long v;
+  asm volatile("ld.shared::cluster.u64 %0, [%1];" : "=l"(v) : "r"(cluster_addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_dsmem_u32(uint32_t cluster_addr) {
+  uint32_t v;
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(cluster_addr) : "memory");
+  return v;
+}
+
+struct ScShared {
+  unsigned long long h_mass[2][256];  // per-CTA histogram of the level being searched (double buffered)
+  uint32_t h_cnt[2][256];
+  unsigned long long m_mass[256];     // histogram merged over the cluster (every CTA computes the same)
+  uint32_t m_cnt[256];
+  unsigned long long x_u64;           // this CTA's contribution to a cluster-wide sum
+  float x_f32;                        // this CTA's contribution to a cluster-wide max
+  uint32_t prefix, cnt_above;
+  unsigned long long mass_above;
+  unsigned long long warp_tot[SC_THREADS / 32];
+  int owner;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(SC_THREADS) sample_cluster_kernel(const T* __restrict__ logits, long long ld, int vocab, int slice,
+                                                                    const float* __restrict__ temperature, const int* __restrict__ top_k,
+                                                                    const float* __restrict__ top_p, const float* __restrict__ min_p,
+                                                                    const float* __restrict__ uniform, int* __restrict__ out, int csize) {
+  PG_PDL_ENTRY();
+  extern __shared__ __align__(16) uint8_t sc_raw[];
+  ScShared& sh = *reinterpret_cast<ScShared*>(sc_raw);
+  float* vals = reinterpret_cast<float*>(sc_raw + ((sizeof(ScShared) + 15) & ~size_t(15)));
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t cr = csize > 1 ? cluster_ctarank() : 0u;
+  const int row = blockIdx.x / csize;
+  const T* r = logits + row * ld;
+  const float inv_t = 1.f / fmaxf(temperature[row], 1e-6f);
+  const int i0 = min(vocab, (int)cr * slice), i1 = min(vocab, i0 + slice);
+  const int n = i1 - i0;
+  const int n_pad = (n + SC_THREADS - 1) / SC_THREADS * SC_THREADS;
+  __shared__ float red[32];
+
+  // the slice, tempered, into shared memory; local max
+  float m = -FLT_MAX;
+  for (int i = tid; i < n; i += SC_THREADS) {
+    const float s = ldf(r, (long long)i0 + i) * inv_t;
+    vals[i] = s;
+    m = fmaxf(m, s);
+  }
+  m = block_max_f(m, red);
+  if (tid == 0) {
+    sh.x_f32 = m;
+    sh.prefix = 0u;
+    sh.cnt_above = 0u;
+    sh.mass_above = 0ull;
+  }
+  for (int b = tid; b < 256; b += SC_THREADS) {
+    sh.h_cnt[0][b] = 0u;
+    sh.h_mass[0][b] = 0ull;
+  }
+  if (csize > 1) cluster_sync_all(); else __syncthreads();
+  if (csize > 1) {
+    float mm = -FLT_MAX;
+    for (int q = 0; q < csize; ++q) mm = fmaxf(mm, ld_dsmem_f32(dsmem_addr(smem_u32(&sh.x_f32), (uint32_t)q)));
+    m = mm;
+  }
+
+  const int kk = top_k[row] > 0 ? min(top_k[row], vocab) : vocab;
+  const float tp = top_p[row];
+  const float mp = min_p[row];
+
+  // From here on a token is represented by e = exp(s - max) in (0, 1]: the exponential is taken
+  // once, when the first radix level walks the slice, and stored over the tempered logit.  e
+  // orders the tokens exactly as s does, so the threshold search runs on the bits of e; the
+  // first level's histogram masses also add up to the normaliser.
+  unsigned long long p_lim = ~0ull;
+  for (int level = 0; level < 4; ++level) {
+    const int shift = 24 - 8 * level;
+    const uint32_t hi_mask = level == 0 ? 0u : (0xffffffffu << (shift + 8));
+    const int hb = level & 1;
+    const uint32_t prefix = sh.prefix;
+    for (int i = tid; i < n_pad; i += SC_THREADS) {
+      uint32_t bin = 256u;
+      unsigned long long fx = 0ull;
+      if (i < n) {
+        float e = vals[i];
+        if (level == 0) {
+          e = __expf(e - m);
+          vals[i] = e;
+        }
+        const uint32_t key = __float_as_uint(e);  // e >= 0: the bit pattern is already order preserving
+        if ((key & hi_mask) == prefix) {
+          bin = (key >> shift) & 255u;
+          fx = (unsigned long long)(e * SC_FX);
+        }
+      }
+      if (!__any_sync(0xffffffffu, bin < 256u)) continue;  // below the first level most warps have no candidate left
+      // one shared-memory atomic per distinct bin of the warp
+      const uint32_t peers = __match_any_sync(0xffffffffu, bin);
+      if (bin < 256u) {
+        const uint32_t lo = __reduce_add_sync(peers, (uint32_t)(fx & 0xFFFFFull));
+        const uint32_t hi = __reduce_add_sync(peers, (uint32_t)(fx >> 20));
+        if (lane == __ffs(peers) - 1) {
+          atomicAdd(&sh.h_cnt[hb][bin], (uint32_t)__popc(peers));
+          atomicAdd(&sh.h_mass[hb][bin], ((unsigned long long)hi << 20) + (unsigned long long)lo);
+        }
+      }
+    }
+    if (csize > 1) cluster_sync_all(); else __syncthreads();
+    for (int b = tid; b < 256; b += SC_THREADS) {
+      // The other buffer is free now: peers read it (the previous level's merge) before they arrived
+      // at the barrier above.  The next level adds into it after the __syncthreads below.
+      sh.h_cnt[hb ^ 1][b] = 0u;
+      sh.h_mass[hb ^ 1][b] = 0ull;
+      uint32_t c = 0u;
+      unsigned long long ms = 0ull;
+      if (csize > 1) {
+        for (int q = 0; q < csize; ++q) {
+          c += ld_dsmem_u32(dsmem_addr(smem_u32(&sh.h_cnt[hb][b]), (uint32_t)q));
+          ms += ld_dsmem_u64(dsmem_addr(smem_u32(&sh.h_mass[hb][b]), (uint32_t)q));
+        }
+      } else {
+        c = sh.h_cnt[hb][b];
+        ms = sh.h_mass[hb][b];
+      }
+      sh.m_cnt[b] = c;
+      sh.m_mass[b] = ms;
+    }
+    __syncthreads();
+    if (warp == 0) {
+      // Warp-parallel threshold step.  Lane l owns bins 8l .. 8l+7.  Walking the bins from the top, a
+      // bin is kept while (count above < k) and (mass above < top-p limit); both grow as the bin index
+      // falls, so the chosen bin is the LOWEST non-empty bin that still satisfies them.
+      uint32_t c8[8];
+      unsigned long long m8[8];
+      uint32_t csum = 0u;
+      unsigned long long msum = 0ull;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        c8[j] = sh.m_cnt[lane * 8 + j];
+        m8[j] = sh.m_mass[lane * 8 + j];
+        csum += c8[j];
+        msum += m8[j];
+      }
+      // totals of the lanes above this one (exclusive suffix sum)
+      uint32_t c_hi = csum;
+      unsigned long long m_hi = msum;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t cu = __shfl_down_sync(0xffffffffu, c_hi, o);
+        const unsigned long long mu = __shfl_down_sync(0xffffffffu, m_hi, o);
+        if (lane + o < 32) {
+          c_hi += cu;
+          m_hi += mu;
+        }
+      }
+      if (level == 0) {
+        const unsigned long long z = __shfl_sync(0xffffffffu, m_hi, 0);  // exact, whatever order the threads added in
+        if (lane == 0) sh.x_u64 = tp >= 1.f ? ~0ull : (unsigned long long)((double)tp * (double)z);
+        __syncwarp();
+      }
+      const unsigned long long lim = sh.x_u64;
+      uint32_t cnt = sh.cnt_above + (c_hi - csum);
+      unsigned long long mass = sh.mass_above + (m_hi - msum);
+      int chosen = 256;
+      uint32_t c_cnt = 0u;
+      unsigned long long c_mass = 0ull;
+#pragma unroll
+      for (int j = 7; j >= 0; --j) {
+        if (c8[j] != 0u && cnt < (uint32_t)kk && mass < lim) {
+          chosen = lane * 8 + j;
+          c_cnt = cnt;
+          c_mass = mass;
+        }
+        cnt += c8[j];
+        mass += m8[j];
+      }
+      int best = chosen;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) best = min(best, __shfl_xor_sync(0xffffffffu, best, o));
+      __syncwarp();
+      if (best == 256) {  // cannot happen (the top element is always kept); keep the top bin
+        if (lane == 31) {
+          sh.prefix = prefix | (255u << shift);
+        }
+      } else if (chosen == best) {  // exactly one lane owns the chosen bin
+        sh.prefix = prefix | ((uint32_t)best << shift);
+        sh.cnt_above = c_cnt;
+        sh.mass_above = c_mass;
+      }
+    }
+    __syncthreads();
+  }
+  (void)p_lim;
+  // min-p: e >= min_p (e is relative to the row maximum, whose e is 1)
+  const uint32_t thr_key = max(sh.prefix, mp > 0.f ? __float_as_uint(fminf(mp, 1.f)) : 0u);
+  __syncthreads();  // every thread has read the threshold before x_u64 is reused below
+
+  // inverse CDF in vocabulary order over the kept set: a contiguous chunk per thread
+  const int chunk = (n + SC_THREADS - 1) / SC_THREADS;
+  const int c0 = min(n, tid * chunk), c1 = min(n, c0 + chunk);
+  unsigned long long local = 0ull;
+  for (int i = c0; i < c1; ++i) {
+    const float e = vals[i];
+    if (__float_as_uint(e) >= thr_key) local += (unsigned long long)(e * SC_FX);
+  }
+  unsigned long long incl = local;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned long long up = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += up;
+  }
+  if (lane == 31) sh.warp_tot[warp] = incl;
+  __syncthreads();
+  unsigned long long warp_before = 0ull, cta_total = 0ull;
+  for (int w = 0; w < SC_THREADS / 32; ++w) {
+    const unsigned long long t = sh.warp_tot[w];
+    if (w < warp) warp_before += t;
+    cta_total += t;
+  }
+  const unsigned long long before = warp_before + incl - local;
+  if (tid == 0) {
+    sh.x_u64 = cta_total;
+    sh.owner = -1;
+  }
+  // x_u64 held the top-p limit, which only this CTA's thread 0 read (every CTA computes its own copy)
+  if (csize > 1) cluster_sync_all(); else __syncthreads();
+  unsigned long long total = 0ull, cta_before = 0ull;
+  for (int q = 0; q < csize; ++q) {
+    const unsigned long long t = csize > 1 ? ld_dsmem_u64(dsmem_addr(smem_u32(&sh.x_u64), (uint32_t)q)) : sh.x_u64;
+    if (q < (int)cr) cta_before += t;
+    total += t;
+  }
+  // u < 1, so the target lies strictly inside [0, total)
+  const float u = fminf(fmaxf(uniform[row], 0.f), 0.99999994f);
+  unsigned long long target = (unsigned long long)((double)u * (double)total);
+  if (target >= total) target = total - 1ull;
+  const bool mine = total > 0ull && target >= cta_before && target < cta_before + cta_total;
+  if (mine) {
+    const unsigned long long tl = target - cta_before;
+    if (local > 0ull && before <= tl && tl < before + local) {
+      unsigned long long acc = before;
+      int pick = -1;
+      for (int i = c0; i < c1; ++i) {
+        const float e = vals[i];
+        if (__float_as_uint(e) >= thr_key) {
+          acc += (unsigned long long)(e * SC_FX);
+          pick = i;
+          if (acc > tl) break;
+        }
+      }
+      out[row] = i0 + pick;
+    }
+  }
+  // a CTA must not exit while a peer may still read its shared memory
+  if (csize > 1) cluster_sync_all();
 }
 
 template <typename T>
@@ -303,9 +578,83 @@ extern "C" int pg_argmax(const void* logits, int is_f32, int rows, int vocab, lo
   return PG_OK;
 }
 
+static int g_force_cluster = 0;
+// Test hook: pin the cluster size of the cluster sampler (1, 2, 4 or 8; 0 = chosen from the vocabulary).
+extern "C" void pg_sample_force_cluster(int c) { g_force_cluster = c; }
+
+// Cluster size and slice length of the cluster sampler for a vocabulary, or 0 when the row does
+// not fit the shared memory of eight CTAs (the one-CTA kernel serves those).
+static int sampler_cluster_plan(int vocab, int max_smem, int* slice_out) {
+  const int room = (max_smem - 2048 - (int)sizeof(ScShared) - 64) / 4;  // floats per CTA (2 KB left for static shared memory)
+  int c = 1;
+  while (c < SC_MAX_CLUSTER && (ceil_div(vocab, c) > 24 * 1024 || ceil_div(vocab, c) > room)) c *= 2;
+  if (g_force_cluster > 0) c = g_force_cluster;
+  const int slice = (ceil_div(vocab, c) + 3) & ~3;
+  if (slice > room) return 0;
+  *slice_out = slice;
+  return c;
+}
+
+template <typename T>
+static int launch_sample_cluster(const T* logits, long long ld, int rows, int vocab, int c, int slice, const float* temperature, const int* top_k,
+                                 const float* top_p, const float* min_p, const float* uniform, int* out, cudaStream_t stream) {
+  const size_t smem = ((sizeof(ScShared) + 15) & ~size_t(15)) + (size_t)slice * 4;
+  static bool attr_done[2] = {false, false};
+  const int which = sizeof(T) == 4 ? 1 : 0;
+  if (!attr_done[which]) {
+    int max_smem = 0, dev = 0;
+    PG_CUDA(cudaGetDevice(&dev));
+    PG_CUDA(cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    PG_CUDA(cudaFuncSetAttribute(sample_cluster_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem - 2048));
+    attr_done[which] = true;
+  }
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)(rows * c));
+  cfg.blockDim = dim3(SC_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute at[2];
+  int na = 0;
+  if (c > 1) {
+    at[na].id = cudaLaunchAttributeClusterDimension;
+    at[na].val.clusterDim.x = (unsigned)c;
+    at[na].val.clusterDim.y = 1;
+    at[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  if (pdl_enabled()) {
+    at[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = at;
+  cfg.numAttrs = (unsigned)na;
+  PG_CUDA(cudaLaunchKernelEx(&cfg, sample_cluster_kernel<T>, logits, ld, vocab, slice, temperature, top_k, top_p, min_p, uniform, out, c));
+  PG_LAUNCH_CHECK();
+  return PG_OK;
+}
+
 extern "C" int pg_sample(const void* logits, int is_f32, int rows, int vocab, long long ld, const void* temperature, const void* top_k,
                          const void* top_p, const void* min_p, const void* uniform, void* out, cudaStream_t stream) {
   if (rows == 0) return PG_OK;
+  static int use_cluster = -1, max_smem = 0;
+  if (use_cluster < 0) {
+    const char* e = getenv("PEGAINFER_SAMPLER_CLUSTER");
+    int dev = 0;
+    PG_CUDA(cudaGetDevice(&dev));
+    PG_CUDA(cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    use_cluster = (e && e[0] == '0') ? 0 : 1;
+  }
+  int slice = 0;
+  const int c = use_cluster ? sampler_cluster_plan(vocab, max_smem, &slice) : 0;
+  if (c > 0) {
+    if (is_f32)
+      return launch_sample_cluster<float>((const float*)logits, ld, rows, vocab, c, slice, (const float*)temperature, (const int*)top_k, (const float*)top_p,
+                                          (const float*)min_p, (const float*)uniform, (int*)out, stream);
+    return launch_sample_cluster<bf16>((const bf16*)logits, ld, rows, vocab, c, slice, (const float*)temperature, (const int*)top_k, (const float*)top_p,
+                                       (const float*)min_p, (const float*)uniform, (int*)out, stream);
+  }
   if (is_f32)
     PG_CUDA(launch_pdl(sample_kernel<float>, dim3(rows), dim3(ST), (size_t)(0), stream, (const float*)logits, ld, vocab, (const float*)temperature, (const int*)top_k, (const float*)top_p,
                                                   (const float*)min_p, (const float*)uniform, (int*)out));

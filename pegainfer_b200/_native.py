@@ -115,7 +115,7 @@ def load():
     global _lib
     if _lib is not None:
         return _lib
-    if not is_current():
+    if not os.environ.get("PEGAINFER_LIB_PATH") and not is_current():
         # several ranks of one box may get here together: one builds, the others wait on the lock
         import fcntl
 
@@ -127,7 +127,8 @@ def load():
                     build()
             finally:
                 fcntl.flock(lk, fcntl.LOCK_UN)
-    _lib = ctypes.CDLL(LIB_PATH)
+    # PEGAINFER_LIB_PATH loads another build of the library as is (A/B timing of kernel changes)
+    _lib = ctypes.CDLL(os.environ.get("PEGAINFER_LIB_PATH") or LIB_PATH)
     _lib.pg_last_error.restype = ctypes.c_char_p
     return _lib
 

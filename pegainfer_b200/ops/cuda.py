@@ -208,13 +208,13 @@ def swiglu(gate_up, interleaved: bool = False):
 
 class DeferredNorm:
     """Activations whose RMSNorm is still owed its per-token scale: ``xw = h * norm_w`` plus the
-    per-(weight tile, token) sums of squares of ``h``.  The GEMM that consumes ``xw`` applies
-    ``rsqrt(sum(ssp) / width + eps)`` to every output element of the token."""
+    per-(token, weight tile) sums of squares of ``h`` (``ssp[:, :parts]``).  The GEMM that consumes
+    ``xw`` applies ``rsqrt(sum(ssp[n, :parts]) / width + eps)`` to every output element of token n."""
 
-    __slots__ = ("xw", "ssp", "width", "eps")
+    __slots__ = ("xw", "ssp", "parts", "width", "eps")
 
-    def __init__(self, xw, ssp, width, eps):
-        self.xw, self.ssp, self.width, self.eps = xw, ssp, width, eps
+    def __init__(self, xw, ssp, parts, width, eps):
+        self.xw, self.ssp, self.parts, self.width, self.eps = xw, ssp, parts, width, eps
 
 
 FUSED_MAX_ROWS = 64
@@ -243,17 +243,76 @@ def linear_fused(x, w, epilogue: int = EPI_PLAIN, residual=None, norm_w=None, no
     ssp = None
     if epilogue == EPI_RESID_NORMW:
         assert residual is not None and norm_w is not None and residual.stride(-1) == 1
-        ssp = torch.empty(((m + 127) // 128, t), dtype=torch.float32, device=xin.device)
+        parts = (m + 127) // 128
+        ssp = torch.empty((t, (parts + 3) // 4 * 4), dtype=torch.float32, device=xin.device)
+    GemmTrace.arm(f"fused{epilogue} {t}x{m}x{k}")
     rc = lib().pg_gemm_bf16_tn_fused(
         _ptr(xin), _ptr(w), _ptr(out), _ci(t), _ci(m), _ci(k), _ll(xin.stride(0)), _ll(w.stride(0)), _ll(out.stride(0)),
-        _ptr(dn.ssp) if dn is not None else _vp(0), _ci(dn.ssp.shape[0] if dn is not None else 0), _ci(dn.width if dn is not None else 0), _cf(dn.eps if dn is not None else 0.0),
-        _ci(epilogue), _ptr(residual), _ll(residual.stride(0) if residual is not None else 0), _ptr(norm_w), _ci(int(norm_offset)), _ptr(ssp),
+        _ptr(dn.ssp) if dn is not None else _vp(0), _ci(dn.parts if dn is not None else 0), _ci(dn.ssp.stride(0) if dn is not None else 0), _ci(dn.width if dn is not None else 0),
+        _cf(dn.eps if dn is not None else 0.0),
+        _ci(epilogue), _ptr(residual), _ll(residual.stride(0) if residual is not None else 0), _ptr(norm_w), _ci(int(norm_offset)), _ptr(ssp), _ci(ssp.stride(0) if ssp is not None else 0),
         _ptr(c.gemm_ws), _ll(c.gemm_ws.numel()), _ptr(c.gemm_counters), _ll(c.gemm_counters.numel() * 4), _ptr(c.status), _stream(),
     )
     _check(rc, c)
     if epilogue == EPI_RESID_NORMW:
-        return DeferredNorm(out, ssp, m, eps)
+        return DeferredNorm(out, ssp, parts, m, eps)
     return out
+
+
+class GemmTrace:
+    """Debug aid (``PEGAINFER_GEMM_TRACE=1``): every GEMM launch gets its own slot of a device
+    buffer for the kernel's globaltimer phase stamps, so a captured decode step can be read back
+    as one timeline (``dump``).  Off by default; the stamps cost a few stores per CTA."""
+
+    enabled = os.environ.get("PEGAINFER_GEMM_TRACE") == "1"
+    slots = 1024
+    buf = None
+    names: list = []
+
+    @classmethod
+    def arm(cls, label: str) -> None:
+        if not cls.enabled:
+            return
+        if cls.buf is None:
+            cls.buf = torch.zeros((cls.slots, 148 * 16), dtype=torch.int64, device="cuda")
+        i = len(cls.names) % cls.slots
+        cls.names.append(label)
+        lib().pg_gemm_set_timing(_vp(cls.buf[i].data_ptr()))
+
+    @classmethod
+    def reset(cls) -> None:
+        cls.names = []
+        if cls.buf is not None:
+            cls.buf.zero_()
+
+    @classmethod
+    def dump(cls, first: int, end: int, detail: bool = False) -> list:
+        """(label, entry, x ready, first MMA, last MMA, exit) in microseconds from the first entry,
+        medians over the CTAs, for the armed launches ``first .. end``."""
+        import numpy as np
+
+        torch.cuda.synchronize()
+        rows = []
+        t0 = None
+        for i in range(first, end):
+            tm = cls.buf[i % cls.slots].view(148, 16).cpu().numpy().astype(np.float64)
+            tm = tm[tm[:, 0] > 0]
+            if not len(tm):
+                continue
+            if t0 is None:
+                t0 = tm[:, 0].min()
+            med = lambda j: (np.median(tm[:, j][tm[:, j] > 0]) - t0) / 1e3 if (tm[:, j] > 0).any() else float("nan")
+            rows.append((cls.names[i], (tm[:, 0].min() - t0) / 1e3, med(2), med(4), med(5), (max(tm[:, 10].max(), tm[:, 11].max()) - t0) / 1e3))
+            if detail:
+                base = np.median(tm[:, 2][tm[:, 2] > 0])
+                det = {}
+                for j in range(2, 12):
+                    col = tm[:, j][tm[:, j] >= base - 1e6]
+                    col = col[col > 0]
+                    if len(col):
+                        det[j] = (round((col.min() - base) / 1e3, 2), round((np.median(col) - base) / 1e3, 2), round((col.max() - base) / 1e3, 2))
+                rows[-1] = rows[-1] + (det,)
+        return rows
 
 
 def linear(x, w, out_dtype=None, force_splits: int = 0, out: Optional[torch.Tensor] = None):
@@ -274,6 +333,7 @@ def linear(x, w, out_dtype=None, force_splits: int = 0, out: Optional[torch.Tens
     if _BATCH_INVARIANT and force_splits == 0:
         force_splits = 1
     c = ctx(x.device)
+    GemmTrace.arm(f"linear {t}x{m}x{k}")
     rc = lib().pg_gemm_bf16_tn(
         _ptr(x2), _ptr(w), _ptr(out), _ci(int(f32)), _ci(t), _ci(m), _ci(k), _ll(x2.stride(0)), _ll(w.stride(0)), _ll(out.stride(0)),
         _ptr(c.gemm_ws), _ll(c.gemm_ws.numel()), _ptr(c.gemm_counters), _ll(c.gemm_counters.numel() * 4), _ptr(c.status), _ci(force_splits), _stream(),

@@ -276,20 +276,24 @@ def argmax(logits: torch.Tensor) -> torch.Tensor:
 
 def filtered_probs(logits, temperature, top_k, top_p, min_p):
     """Temperature softmax followed by top-k, top-p and min-p filtering, renormalised.
-    All controls are per-row tensors."""
+    All controls are per-row tensors.  The keep-set is a threshold on the probability: every
+    token at least as likely as the k-th most likely one, and at least as likely as the token
+    at which the descending cumulative mass crosses ``top_p`` (so tokens that tie with the
+    last kept one are all kept, as in threshold-based samplers), and at least ``min_p`` times
+    the most likely one."""
     lf = logits.float() / temperature.clamp_min(1e-6).unsqueeze(-1)
     probs = torch.softmax(lf, dim=-1)
     sp, si = probs.sort(dim=-1, descending=True)
     v = probs.shape[-1]
-    rank = torch.arange(v, device=probs.device).unsqueeze(0)
-    k = torch.where(top_k > 0, top_k, torch.full_like(top_k, v)).unsqueeze(-1)
-    keep = rank < k
-    csum = sp.cumsum(-1)
-    keep &= (csum - sp) < top_p.unsqueeze(-1)
-    keep &= sp >= (min_p.unsqueeze(-1) * sp[:, :1])
-    keep[:, 0] = True
-    sp = sp * keep
-    out = torch.zeros_like(probs).scatter_(-1, si, sp)
+    k = torch.where(top_k > 0, top_k, torch.full_like(top_k, v)).clamp(max=v).long().unsqueeze(-1)
+    thr_k = sp.gather(-1, k - 1)
+    csum = sp.double().cumsum(-1)
+    before = csum - sp.double()
+    crossing = ((before < top_p.double().unsqueeze(-1)).sum(-1, keepdim=True) - 1).clamp_min(0)  # last position still below top_p
+    thr_p = sp.gather(-1, crossing)
+    keep = (probs >= thr_k) & (probs >= thr_p) & (probs >= min_p.unsqueeze(-1) * sp[:, :1])
+    keep |= probs >= sp[:, :1]
+    out = probs * keep
     return out / out.sum(-1, keepdim=True)
 
 

@@ -92,6 +92,7 @@ class DecodeGraphs:
         self.d2h_bytes = 0
         self.replays = 0
         self.kernels_per_graph: dict = {}
+        self.trace_range: dict = {}
         self.invalidate_table()
         # first use of a framework kernel loads its module (tens of milliseconds): do that now for the
         # two copies the run-ahead path issues between replays, not on a live decode step
@@ -170,11 +171,13 @@ class DecodeGraphs:
             g = torch.cuda.CUDAGraph()
             if self.pool is None:
                 self.pool = torch.cuda.graph_pool_handle()
+            trace0 = len(_K().GemmTrace.names)
             g.capture_begin(pool=self.pool)
             try:
                 logits = self._forward(b, greedy, splits)
             finally:
                 g.capture_end()
+            self.trace_range[key] = (trace0, len(_K().GemmTrace.names))  # GEMM trace slots of this graph (debug aid)
             # The first launch of an instantiated graph uploads it to the device (measured: 50 - 70 ms
             # for a whole-step graph).  Pay that here, on the padding inputs the capture ran on, and not
             # on the first decode step that lands in this bucket.
@@ -372,14 +375,41 @@ class DecodeGraphs:
         host = cur.host.tolist()
         return [host[cur.rows[s.rid]] for s in seqs]
 
-    def dump_dot(self, path: str, b: Optional[int] = None, greedy: bool = True) -> str:
-        """Write the captured graph of bucket ``b`` as Graphviz DOT text."""
+    def dump_dot(self, path: str, b: Optional[int] = None, greedy: bool = True, png: bool = False) -> dict:
+        """Write the decode graph of bucket ``b`` as Graphviz DOT text: every kernel node with its
+        name and launch shape, every dependency edge (programmatic-launch edges dashed) and a
+        per-kernel launch count in the header.  The bucket is captured once more into a graph
+        object that keeps its ``cudaGraph_t``, which the C library walks.  With ``png`` and a
+        ``dot`` binary on the PATH a PNG is rendered beside it.  Returns the node / edge counts."""
+        import ctypes
+        import shutil
+        import subprocess
+
+        from .. import _native
+
         b = b if b is not None else self.buckets[0]
-        g = self.graphs.get((b, greedy)) or self.capture(b, greedy)
-        g.enable_debug_mode() if hasattr(g, "enable_debug_mode") else None
-        try:
-            g.debug_dump(path)
-        except Exception:
-            with open(path, "w") as f:
-                f.write("digraph decode { /* this torch build cannot export graph nodes */ }\n")
-        return path
+        splits = self._splits_for(b)
+        self.d_small.zero_()
+        self.d_slots.zero_()
+        s = torch.cuda.Stream(self.device)
+        s.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(s):
+            self._forward(b, greedy, splits)
+            s.synchronize()
+            g = torch.cuda.CUDAGraph(keep_graph=True)
+            g.capture_begin()
+            try:
+                self._forward(b, greedy, splits)
+            finally:
+                g.capture_end()
+        torch.cuda.current_stream(self.device).wait_stream(s)
+        counts = (ctypes.c_longlong * 4)()
+        lib = _native.load()
+        _native.check(lib.pg_graph_export_dot(ctypes.c_void_p(g.raw_cuda_graph()), path.encode(), f"decode step, batch bucket {b}".encode(), counts))
+        out = dict(path=path, nodes=counts[0], edges=counts[1], kernels=counts[2], programmatic_edges=counts[3], png=None)
+        if png and shutil.which("dot"):
+            target = os.path.splitext(path)[0] + ".png"
+            if subprocess.run(["dot", "-Tpng", path, "-o", target], capture_output=True).returncode == 0:
+                out["png"] = target
+        del g
+        return out

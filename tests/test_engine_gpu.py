@@ -331,3 +331,22 @@ def test_run_ahead_decode_matches_step_by_step_engine():
     assert l1 > 20 and c1 > 20, (l1, c1)
     assert len(plain[0][0]) <= 20 and len(plain[4][0]) <= 11
     assert ahead == plain
+
+
+def test_decode_graph_exports_dot_with_kernel_names(tmp_path):
+    """The captured decode step written as Graphviz text: kernel nodes by name with launch shapes,
+    dependency edges, programmatic-launch edges marked, launch counts in the header."""
+    eng = engine(True)
+    try:
+        path = str(tmp_path / "decode.dot")
+        info = eng.executor._graphs.dump_dot(path, b=4)
+        text = open(path).read()
+        assert info["kernels"] > 10 and info["nodes"] >= info["kernels"] and info["edges"] >= info["kernels"] - 1
+        assert "gemm_bf16_tn_kernel" in text and "decode_attn" in text and "qk_norm_rope_append_kernel" in text
+        assert text.count("->") == info["edges"] and text.rstrip().endswith("}")
+        assert info["programmatic_edges"] > 0 and "style=dashed" in text
+        # the engine still decodes after the extra capture
+        out = eng.generate(prompts(2), max_tokens=4)
+        assert all(len(o[0]) == 4 for o in out)
+    finally:
+        eng.shutdown()

@@ -249,7 +249,7 @@ def test_position_out_of_range_sets_status_not_trap():
     status_clean()
 
 
-@pytest.mark.parametrize("vocab", [1024, 151936])
+@pytest.mark.parametrize("vocab", [1024, 40000, 151936, 248320])  # one CTA, and clusters of 2, 8 and 8 CTAs per row
 def test_argmax_sample_logprobs(vocab):
     torch.manual_seed(vocab)
     rows = 9
@@ -278,7 +278,9 @@ def test_argmax_sample_logprobs(vocab):
     c1, tv1, ti1 = cu().logprobs_topk(logits, picked, 5)
     c2, tv2, ti2 = R.logprobs_topk(logits, picked, 5)
     assert (c1 - c2).abs().max().item() < 1e-3 and (tv1 - tv2).abs().max().item() < 1e-3
-    assert torch.equal(ti1[1:, 0].long(), ti2[1:, 0])
+    # same best alternative, up to ties between equal bf16 logits (a large vocabulary has many)
+    lf = logits.float()
+    assert torch.equal(lf[1:].gather(-1, ti1[1:, :1].long()), lf[1:].gather(-1, ti2[1:, :1]))
     status_clean()
 
 
@@ -606,7 +608,7 @@ def test_fused_decode_chain_matches_separate_kernels(t):
     assert (res.float() - exact).abs().max() <= (res_ref.float() - exact).abs().max() + 1e-6
     # the normalised activations differ only by where the bf16 rounding sits (before or after the scale)
     inv = torch.rsqrt(res.float().pow(2).mean(-1, keepdim=True) + eps)
-    assert torch.allclose(dn.ssp.sum(0), res.float().pow(2).sum(-1), rtol=1e-4)
+    assert torch.allclose(dn.ssp[:, : dn.parts].sum(1), res.float().pow(2).sum(-1), rtol=1e-4)
     x_exact = res.float() * inv * nw.float()
     assert (dn.xw.float() * inv - x_exact).abs().max() <= 2 ** -7 * x_exact.abs().max()
     for got, ref in ((plain, plain_ref), (act, act_ref)):
@@ -615,7 +617,7 @@ def test_fused_decode_chain_matches_separate_kernels(t):
     # bit-reproducible
     res2 = res0.clone()
     dn2 = K.linear_fused(a, wo, K.EPI_RESID_NORMW, residual=res2, norm_w=nw, eps=eps)
-    assert torch.equal(K.linear_fused(dn2, w_il, K.EPI_SWIGLU), act) and torch.equal(dn2.ssp, dn.ssp)
+    assert torch.equal(K.linear_fused(dn2, w_il, K.EPI_SWIGLU), act) and torch.equal(dn2.ssp[:, : dn.parts], dn.ssp[:, : dn.parts])
     # a row's result does not depend on how many padding rows ride along in the same token tile
     if t < 16:
         pad = 16 - t
