@@ -43,6 +43,12 @@ int pg_gemm_bf16_tn_fused(const void* x, const void* w, void* y, int T, int M, i
                           const void* in_ssp, int in_parts, int in_ld, int in_width, float in_eps, int epi, void* residual, long long ld_res,
                           const void* norm_w, int norm_offset, void* out_ssp, int out_ld, void* ws, long long ws_bytes, void* counters,
                           long long counter_bytes, void* status, cudaStream_t stream);
+// Decode chain (decode_chain.cu): up to four dependent GEMMs of a layer in one persistent kernel for
+// steps of at most 64 rows.  One PgChainPhase per GEMM; see decode_chain.cu for the fields.
+struct PgChainPhase;
+long long pg_decode_chain_ws_bytes(int device);
+int pg_decode_chain(const struct PgChainPhase* phases, int nphase, int T, void* residual, long long ld_res, float eps, void* ws, long long ws_bytes,
+                    void* counters, void* status, cudaStream_t stream);
 // Write a captured cudaGraph_t as Graphviz DOT (graph_export.cu); counts = {nodes, edges, kernel nodes, programmatic edges}.
 int pg_graph_export_dot(void* graph, const char* path, const char* title, long long* counts);
 int pg_tp_wait(const void* wait_flags, int world, unsigned long long wait_ns, void* status, cudaStream_t stream);

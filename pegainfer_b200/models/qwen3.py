@@ -160,6 +160,9 @@ class Qwen3Model:
         fused = self._fused_chain_ok(meta)
         if fused:
             from ..ops import cuda as K
+
+            if self._chain_ok(meta):
+                return self._forward_chain(x, residual, meta, kv, aux_layers, K)
         for i, l in enumerate(self.layers):
             ls = meta.lora_slots if self.lora is not None else None
             decode = ls is None and meta.num_tokens <= 256  # weight-streaming regime: chain L2 prefetches GEMM to GEMM
@@ -219,6 +222,46 @@ class Qwen3Model:
         tp.sync()
         return x
 
+    def _chain_ok(self, meta: AttnMeta) -> bool:
+        """One persistent kernel per layer for the four projections behind attention (o_proj, gate_up,
+        down, the next layer's qkv): steps of up to 64 rows, hidden size a multiple of 128 up to 8192."""
+        import os
+
+        h = self.cfg.hidden_size
+        return os.environ.get("PEGAINFER_DECODE_CHAIN", "1") != "0" and h % 128 == 0 and h <= 8192 and self.gate_up_interleaved
+
+    def _forward_chain(self, x, residual, meta, kv, aux_layers, K):
+        cfg, eps, n = self.cfg, self.cfg.rms_eps, len(self.layers)
+        aux = []
+        # 128-wide heads with full rotary: QK-norm, RoPE and the KV append run in the epilogue of the qkv phase
+        rope_fused = cfg.head_dim == 128 and cfg.rotary_dim == 128
+
+        def qkv_phase(i):
+            l = self.layers[i]
+            if not rope_fused:
+                return (l.qkv, K.CH_PLAIN, None, False)
+            spec = dict(q_norm=l.q_norm, k_norm=l.k_norm, cos=self.cos, sin=self.sin, meta=meta, kv_layer=kv.layer(i), hq=self.q_heads, hkv=self.kv_heads, eps=eps)
+            return (l.qkv, K.CH_QKV_ROPE, spec, False)
+
+        q = K.decode_chain(x, [qkv_phase(0)])[0]
+        for i, l in enumerate(self.layers):
+            if not rope_fused:
+                q = ops.qk_norm_rope_append(q, l.q_norm, l.k_norm, self.cos, self.sin, meta, kv.layer(i), self.q_heads, self.kv_heads, cfg.head_dim, eps)
+            a = ops.paged_attention(q, kv.layer(i), meta)
+            phases = [(l.o, K.CH_RESID_NORM, l.post_norm, False), (l.gate_up, K.CH_SWIGLU, None, False)]
+            if i + 1 < n:
+                phases += [(l.down, K.CH_RESID_NORM, self.layers[i + 1].input_norm, False), qkv_phase(i + 1)]
+                outs = K.decode_chain(a, phases, residual=residual, eps=eps)
+                q = outs[3]
+            else:
+                phases += [(l.down, K.CH_RESID_NORM, self.final_norm, False)]
+                outs = K.decode_chain(a, phases, residual=residual, eps=eps)
+            x = outs[2]  # final-norm weight applied, per-token scale still owed: the lm_head GEMM completes it
+            if i in aux_layers:
+                aux.append(residual.clone())
+        self.last_aux = aux
+        return x
+
     def _fused_chain_ok(self, meta: AttnMeta) -> bool:
         """The fused decode chain serves steps of up to 64 token rows without adapter deltas, when every
         projection plans onto the GEMM's on-chip split-K path (decided once per row count)."""
@@ -236,7 +279,13 @@ class Qwen3Model:
             self._fused_ok[t] = ok
         return ok and not K.batch_invariant()
 
-    def logits(self, hidden: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def logits(self, hidden, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if not isinstance(hidden, torch.Tensor):  # rows from the decode chain whose final RMSNorm scale is still owed
+            from ..ops import cuda as K
+
+            if rows is not None:
+                hidden = K.DeferredNorm(ops.gather_rows(hidden.xw, rows), hidden.ssp.index_select(0, rows.long()), hidden.parts, hidden.width, hidden.eps)
+            return K.linear_fused(hidden, self.lm_head)
         if rows is not None:
             hidden = ops.gather_rows(hidden, rows)
         return ops.linear(hidden, self.lm_head)

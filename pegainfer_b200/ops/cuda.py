@@ -360,6 +360,86 @@ def linear_2sm(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return out.view(*x.shape[:-1], m)
 
 
+class _ChainPhase(ctypes.Structure):
+    _fields_ = [("x", _vp), ("ldx", _ll), ("w", _vp), ("ldw", _ll), ("M", _ci), ("K", _ci), ("epi", _ci), ("out", _vp), ("ld_out", _ll), ("norm_w", _vp), ("norm_offset", _ci),
+                ("in_ssp", _vp), ("in_parts", _ci), ("in_ld", _ci), ("in_width", _ci), ("in_eps", _cf), ("out_ssp", _vp), ("out_ld", _ci),
+                ("q_w", _vp), ("k_w", _vp), ("cos", _vp), ("sin", _vp), ("positions", _vp), ("slots", _vp), ("kv", _vp), ("hq", _ci), ("hkv", _ci), ("rot", _ci), ("page_size", _ci),
+                ("max_pos", _ci), ("num_slots", _ll), ("qk_eps", _cf)]
+
+
+CHAIN_MAX_ROWS = 64
+CH_PLAIN, CH_SWIGLU, CH_RESID_NORM, CH_QKV_ROPE = 0, 1, 2, 3
+
+
+def decode_chain(x, phases, residual=None, eps: float = 0.0):
+    """Up to four dependent GEMMs of a decode step (at most 64 rows) in one persistent kernel.
+
+    ``x``: bf16 ``[T, K0]`` or a ``DeferredNorm``; it feeds the first phase, each later phase reads
+    the previous phase's output.  ``phases``: list of ``(weight [M, K], epilogue, norm_weight_or_None,
+    norm_offset)`` with epilogue ``CH_PLAIN`` (output [T, M]), ``CH_SWIGLU`` (weight rows interleaved
+    gate/up; output [T, M / 2]) or ``CH_RESID_NORM`` (``residual`` += GEMM; the output is a
+    ``DeferredNorm``: ``residual * norm_weight`` plus the sums of squares from which the next phase, or
+    a later ``linear_fused`` / ``decode_chain``, takes the per-token RMSNorm scale).  A last phase
+    ``(qkv_weight, CH_QKV_ROPE, spec, norm_offset)`` finishes the fused qkv projection of a model with
+    128-wide heads: per-head QK RMSNorm, rotary embedding and the paged KV append happen in its epilogue;
+    ``spec`` is a dict with ``q_norm``, ``k_norm`` (or None), ``cos``, ``sin``, ``meta`` (positions, slot
+    mapping), ``kv_layer``, ``hq``, ``hkv``, ``eps``; the output is q ``[T, hq, 128]``.
+    Returns the list of phase outputs."""
+    dn = x if isinstance(x, DeferredNorm) else None
+    cur = dn.xw if dn is not None else x
+    _bf16(cur)
+    t = cur.shape[0]
+    assert 1 <= t <= CHAIN_MAX_ROWS and 1 <= len(phases) <= 4 and cur.stride(-1) == 1
+    c = ctx(cur.device)
+    if not hasattr(c, "chain_ws"):
+        c.chain_ws = torch.empty(int(lib().pg_decode_chain_ws_bytes(_ci(c.device.index or 0))), dtype=torch.uint8, device=cur.device)
+        c.chain_counters = torch.zeros(16, dtype=torch.int32, device=cur.device)
+    arr = (_ChainPhase * len(phases))()
+    results = []
+    for i, (w, epi, norm_w, norm_offset) in enumerate(phases):
+        _bf16(w)
+        m, k = w.shape
+        assert cur.shape[1] == k and w.stride(-1) == 1, f"chain phase {i}: input has {cur.shape[1]} features, weight wants {k}"
+        width = m // 2 if epi == CH_SWIGLU else m
+        spec = norm_w if epi == CH_QKV_ROPE else None
+        if spec is not None:
+            norm_w = None
+            out = torch.empty((t, spec["hq"], 128), dtype=torch.bfloat16, device=cur.device)
+        else:
+            out = torch.empty((t, width), dtype=torch.bfloat16, device=cur.device)
+        ph = _ChainPhase()
+        ph.x, ph.ldx, ph.w, ph.ldw, ph.M, ph.K, ph.epi, ph.out, ph.ld_out = cur.data_ptr(), cur.stride(0), w.data_ptr(), w.stride(0), m, k, epi, out.data_ptr(), out.stride(0)
+        ph.norm_w, ph.norm_offset = (norm_w.data_ptr() if norm_w is not None else 0), int(bool(norm_offset))
+        if dn is not None:
+            ph.in_ssp, ph.in_parts, ph.in_ld, ph.in_width, ph.in_eps = dn.ssp.data_ptr(), dn.parts, dn.ssp.stride(0), dn.width, dn.eps
+        dn = None
+        if spec is not None:
+            meta, kvl = spec["meta"], spec["kv_layer"]
+            assert kvl.is_contiguous() and kvl.shape[-1] == 128 and spec["cos"].shape[-1] * 2 == 128, "the fused qkv epilogue is built for 128-wide heads with full rotary"
+            ph.q_w = spec["q_norm"].data_ptr() if spec.get("q_norm") is not None else 0
+            ph.k_w = spec["k_norm"].data_ptr() if spec.get("k_norm") is not None else 0
+            ph.cos, ph.sin = spec["cos"].data_ptr(), spec["sin"].data_ptr()
+            ph.positions, ph.slots, ph.kv = meta.positions.data_ptr(), meta.slot_mapping.data_ptr(), kvl.data_ptr()
+            ph.hq, ph.hkv, ph.rot, ph.page_size, ph.max_pos = spec["hq"], spec["hkv"], spec["cos"].shape[-1] * 2, kvl.shape[2], spec["cos"].shape[0]
+            ph.num_slots, ph.qk_eps = kvl.shape[0] * kvl.shape[2], spec["eps"]
+        if epi == CH_RESID_NORM:
+            assert residual is not None and norm_w is not None and residual.shape == (t, m) and residual.stride(-1) == 1
+            parts = (m + 127) // 128
+            ssp = torch.empty((t, (parts + 3) // 4 * 4), dtype=torch.float32, device=cur.device)
+            ph.out_ssp, ph.out_ld = ssp.data_ptr(), ssp.stride(0)
+            dn = DeferredNorm(out, ssp, parts, m, eps)
+            results.append(dn)
+        else:
+            results.append(out)
+        arr[i] = ph
+        cur = out
+    GemmTrace.arm(f"chain x{len(phases)} T{t}")
+    rc = lib().pg_decode_chain(arr, _ci(len(phases)), _ci(t), _ptr(residual), _ll(residual.stride(0) if residual is not None else 0), _cf(eps), _ptr(c.chain_ws), _ll(c.chain_ws.numel()),
+                               _ptr(c.chain_counters), _ptr(c.status), _stream())
+    _check(rc, c)
+    return results
+
+
 _PREFETCH_CAP = int(float(os.environ.get("PEGAINFER_GEMM_PREFETCH_MB", "8")) * (1 << 20))
 
 

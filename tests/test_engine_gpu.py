@@ -342,7 +342,7 @@ def test_decode_graph_exports_dot_with_kernel_names(tmp_path):
         info = eng.executor._graphs.dump_dot(path, b=4)
         text = open(path).read()
         assert info["kernels"] > 10 and info["nodes"] >= info["kernels"] and info["edges"] >= info["kernels"] - 1
-        assert "gemm_bf16_tn_kernel" in text and "decode_attn" in text and "qk_norm_rope_append_kernel" in text
+        assert "decode_chain_kernel" in text and "decode_attn" in text and "gemm_bf16_tn_kernel" in text  # per-layer chain, attention, lm_head
         assert text.count("->") == info["edges"] and text.rstrip().endswith("}")
         assert info["programmatic_edges"] > 0 and "style=dashed" in text
         # the engine still decodes after the extra capture

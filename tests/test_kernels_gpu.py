@@ -638,3 +638,87 @@ def test_swiglu_interleaved_layout():
     il = torch.stack((g, u), 2).reshape(33, 512).contiguous()
     assert torch.equal(K.swiglu(il, True), K.swiglu(halves))
     assert torch.equal(K.swiglu(il, True), R.swiglu(il, True))
+
+
+@pytest.mark.parametrize("t,h,kq,inter,qkv", [(64, 1024, 1024, 1536, 1536), (5, 1024, 1024, 1536, 1536), (64, 4096, 4096, 12288, 6144), (1, 2048, 2048, 5504, 2560), (33, 1024, 2048, 19200, 1024)])
+def test_decode_chain_matches_separate_kernels(t, h, kq, inter, qkv):
+    """o_proj -> +residual, RMSNorm -> gate_up + SwiGLU -> down -> +residual, RMSNorm -> qkv in one
+    persistent kernel (stream-K split, grid barriers) against the same chain as separate kernels."""
+    K = cu()
+    torch.manual_seed(t + h)
+    eps = 1e-6
+    a = (torch.randn(t, kq, device=DEV) * 0.5).bfloat16()
+    wo = (torch.randn(h, kq, device=DEV) * 0.03).bfloat16()
+    wg = (torch.randn(inter, h, device=DEV) * 0.03).bfloat16()
+    wu = (torch.randn(inter, h, device=DEV) * 0.03).bfloat16()
+    wd = (torch.randn(h, inter, device=DEV) * 0.02).bfloat16()
+    wq = (torch.randn(qkv, h, device=DEV) * 0.03).bfloat16()
+    n1 = (1.0 + 0.1 * torch.randn(h, device=DEV)).bfloat16()
+    n2 = (1.0 + 0.1 * torch.randn(h, device=DEV)).bfloat16()
+    res0 = torch.randn(t, h, device=DEV).bfloat16()
+    w_il = torch.stack((wg, wu), 1).reshape(2 * inter, h).contiguous()
+    # separate kernels
+    res_ref = res0.clone()
+    x1 = K.add_rms_norm(K.linear(a, wo), res_ref, n1, eps)
+    act = K.swiglu(K.linear(x1, torch.cat((wg, wu), 0)))
+    x2 = K.add_rms_norm(K.linear(act, wd), res_ref, n2, eps)
+    q_ref = K.linear(x2, wq)
+    # one kernel
+    chain = [(wo, K.CH_RESID_NORM, n1, False), (w_il, K.CH_SWIGLU, None, False), (wd, K.CH_RESID_NORM, n2, False), (wq, K.CH_PLAIN, None, False)]
+    res = res0.clone()
+    outs = K.decode_chain(a, chain, residual=res, eps=eps)
+    torch.cuda.synchronize()
+    assert K.read_status(DEV) == 0
+    scale = lambda r: max(1.0, r.float().abs().max().item())
+
+    def normed(dn):  # complete the deferred RMSNorm on the host side of the test
+        inv = torch.rsqrt(dn.ssp[:, : dn.parts].sum(1) / dn.width + dn.eps)
+        return dn.xw.float() * inv[:, None]
+
+    for name, got, ref, tol in (("x1", normed(outs[0]), x1, 2e-2), ("act", outs[1], act, 3e-2), ("x2", normed(outs[2]), x2, 3e-2), ("qkv", outs[3], q_ref, 4e-2), ("residual", res, res_ref, 3e-2)):
+        err = (got.float() - ref.float()).abs().max().item()
+        assert err <= tol * scale(ref), f"{name}: max err {err}"
+    # bit-reproducible, and the counters were left re-armed: run it twice more
+    for _ in range(2):
+        res2 = res0.clone()
+        outs2 = K.decode_chain(a, chain, residual=res2, eps=eps)
+        same = lambda x, y: torch.equal(x.xw, y.xw) and torch.equal(x.ssp[:, : x.parts], y.ssp[:, : y.parts]) if isinstance(x, K.DeferredNorm) else torch.equal(x, y)
+        assert all(same(x, y) for x, y in zip(outs, outs2)) and torch.equal(res, res2)
+    # a chain that starts from rows whose norm is still owed, and a single-phase chain on finished rows
+    one = K.decode_chain(outs[2], [(wq, K.CH_PLAIN, None, False)])[0]  # the scale's epsilon travels with the rows
+    assert torch.equal(one, outs[3])
+    plain = K.decode_chain(x2, [(wq, K.CH_PLAIN, None, False)])[0]
+    assert (plain.float() - q_ref.float()).abs().max().item() <= 2e-2 * scale(q_ref)
+    # the separate GEMM kernel completes a deferred norm the same way (lm_head after the last layer)
+    lf = K.linear_fused(outs[2], wq)
+    assert (lf.float() - q_ref.float()).abs().max().item() <= 4e-2 * scale(q_ref)
+    assert K.read_status(DEV) == 0
+
+
+@pytest.mark.parametrize("t,hq,hkv,page", [(64, 8, 2, 16), (7, 4, 4, 32)])
+def test_decode_chain_qkv_rope_append_epilogue(t, hq, hkv, page):
+    """The qkv phase with per-head QK RMSNorm, RoPE and the paged KV append in its epilogue, against the
+    GEMM followed by the separate norm / rope / append kernel."""
+    K = cu()
+    torch.manual_seed(hq * 100 + t)
+    d, hidden, eps = 128, 1024, 1e-6
+    x = (torch.randn(t, hidden, device=DEV) * 0.5).bfloat16()
+    wqkv = (torch.randn((hq + 2 * hkv) * d, hidden, device=DEV) * 0.03).bfloat16()
+    qn = (1.0 + 0.1 * torch.randn(d, device=DEV)).bfloat16()
+    kn = (1.0 + 0.1 * torch.randn(d, device=DEV)).bfloat16()
+    cos, sin = R.rope_tables(512, d, 1e6, torch.bfloat16, DEV)
+    pages = 40
+    positions = torch.randint(0, 500, (t,), device=DEV, dtype=torch.int32)
+    slots = torch.randperm(pages * page, device=DEV)[:t].to(torch.int32)
+    meta = R.AttnMeta(q_indptr=torch.arange(t + 1, dtype=torch.int32, device=DEV), kv_lens=positions + 1, block_table=torch.zeros((t, 1), dtype=torch.int32, device=DEV), slot_mapping=slots,
+                      positions=positions, page_size=page, num_seqs=t, num_tokens=t, max_q_len=1, max_kv_len=512, decode_only=True)
+    kv_ref = torch.zeros((pages, 2, page, hkv, d), dtype=torch.bfloat16, device=DEV)
+    kv_got = torch.zeros_like(kv_ref)
+    q_ref = K.qk_norm_rope_append(K.linear(x, wqkv), qn, kn, cos, sin, meta, kv_ref, hq, hkv, d, eps)
+    spec = dict(q_norm=qn, k_norm=kn, cos=cos, sin=sin, meta=meta, kv_layer=kv_got, hq=hq, hkv=hkv, eps=eps)
+    q_got = K.decode_chain(x, [(wqkv, K.CH_QKV_ROPE, spec, False)])[0]
+    torch.cuda.synchronize()
+    assert K.read_status(DEV) == 0
+    assert (q_got.float() - q_ref.float().view(t, hq, d)).abs().max().item() <= 3e-2 * max(1.0, q_ref.float().abs().max().item())
+    assert (kv_got.float() - kv_ref.float()).abs().max().item() <= 3e-2 * max(1.0, kv_ref.float().abs().max().item())
+    assert torch.equal(kv_got != 0, kv_ref != 0)  # exactly the same slots were written
