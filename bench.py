@@ -264,9 +264,11 @@ def kernel_only(args, eng, rank, world, device):
     assert K.read_status(device) == 0, f"device status word set: {K.read_status(device):#x}"
     if K.GemmTrace.enabled and rank == 0:
         # phase stamps of the GEMMs of the captured step (the capture was the last pass that armed them)
+        for lab, med, last in K.GemmTrace.chain_rows(*graphs.trace_range[(b, True)])[:5]:
+            print(f"  {lab}: " + " ".join(f"{v:8.2f}" for v in med) + f"  | last stamp {last:8.2f}", file=sys.stderr)
         rows = K.GemmTrace.dump(*graphs.trace_range[(b, True)], detail=True)
         names = ["", "", "x ready", "loads issued", "first MMA", "last MMA issued", "accumulator ready", "partial pushed", "cluster partials in", "reduced + stored", "roles done", "exit"]
-        for r in rows[4:8]:  # the four GEMMs of the second layer: per-CTA spread of every phase, us after the median 'x ready'
+        for r in [x for x in rows if len(x) > 6][4:8]:  # the four GEMMs of the second layer: per-CTA spread of every phase, us after the median 'x ready'
             print(f"  {r[0]}: " + "; ".join(f"{names[j]} {v[0]}/{v[1]}/{v[2]}" for j, v in sorted(r[6].items())), file=sys.stderr)
         rows = [r[:6] for r in rows]
         prev_exit = None
@@ -371,9 +373,10 @@ def run_arm(args, impl, comm, rank, local, world, device, with_e2e):
         mcfg.num_layers = args.layers
     tp = TPContext(rank, world, comm="nccl")
     if world > 1 and comm == "fused":
-        from pegainfer_b200.parallel.fused import make_fused_tp
+        # decode steps: the chain kernel with its in-switch (multimem) reduction; prompt chunks: library all-reduce
+        from pegainfer_b200.parallel.chain_tp import ChainTP
 
-        tp = make_fused_tp(rank, world, device, mcfg, max_tokens=4096 + args.conc)
+        tp = ChainTP(rank, world, device, mcfg.hidden_size)
     page = args.page_size
     ramp = (args.conc + max(1, 4096 // args.prompt_len) - 1) // max(1, 4096 // args.prompt_len)
     total_len = args.prompt_len + args.warmup + args.steps + ramp + 2 * page

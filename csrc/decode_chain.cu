@@ -85,6 +85,30 @@ struct Phase {
   float qk_eps;
 };
 
+// Tensor parallelism: the row-parallel phases (residual + norm epilogue) sum their result over the
+// ranks.  Every rank first reduces its own stream-K partials to a bf16 [T, M] partial in a buffer that
+// is mapped on all ranks and bound to an NVSwitch multicast object; after a flag exchange each rank
+// reads the sum over ranks with multimem.ld_reduce (reduced inside the switch, f32 accumulation) and
+// finishes the epilogue on its own replicated copy of the residual.  Two partial buffers alternate
+// between consecutive exchanges; exchange numbers (epochs) live in device memory, so CUDA-graph
+// replays need no reset.
+constexpr int TP_MAX_RANKS = 8;
+struct ChainTp {
+  int world, rank;
+  bf16* y_local[2];            // this rank's partial buffers [T, M]
+  const bf16* y_mc[2];         // the same buffers through the multicast mapping
+  uint32_t* flags_local;       // [TP_MAX_RANKS] latest exchange number announced by each rank
+  uint32_t* flags_peer[TP_MAX_RANKS];  // every rank's flag block (peer mapped)
+  uint32_t* epoch;             // local word: exchanges completed by previous launches
+  unsigned long long wait_ns;
+};
+
+__device__ __forceinline__ uint2 multimem_ld_reduce_bf16x4(const bf16* mc_addr) {
+  uint2 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v2.bf16x2 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(mc_addr) : "memory");
+  return v;
+}
+
 struct ChainParams {
   Phase ph[MAX_PHASES];
   int nphase;
@@ -94,7 +118,8 @@ struct ChainParams {
   long long ld_res;
   float eps;
   float* ws;           // [G][2][SLOT_FLOATS]
-  uint32_t* counters;  // [2 * MAX_PHASES + 1], zero before the first launch, left zero by every launch
+  uint32_t* counters;  // [3 * MAX_PHASES + 1], zero before the first launch, left zero by every launch
+  ChainTp tp;
   uint32_t* status;
   unsigned long long* timing;  // optional profiling: 16 globaltimer stamps per CTA (nullptr = off)
 };
@@ -164,6 +189,10 @@ __device__ __forceinline__ bool grid_wait(const uint32_t* ctr, uint32_t G, uint3
     if (ld_acquire_gpu(ctr) >= G) return true;
     if ((++spins & 31u) == 0u) {
       if (*abort_flag) return false;
+      if (*((volatile uint32_t*)status) != PG_ST_OK) {  // another CTA already gave up: do not wait out a second limit
+        *abort_flag = 1;
+        return false;
+      }
       if (globaltimer_ns() - t0 > PG_WAIT_LIMIT_NS) {
         atomicCAS(status, PG_ST_OK, PG_ST_TIMEOUT | (site << 8));
         *abort_flag = 1;
@@ -223,11 +252,11 @@ __device__ __forceinline__ void fix_load(const ChainParams& p, const Phase& P, i
     for (int q = lane; q < P.in_parts; q += 32) f.part += __ldcg(P.in_ssp + (size_t)n * P.in_ld + q);
 }
 
-__device__ __forceinline__ void fix_finish(const ChainParams& p, const Phase& P, int u, int rem0, int lane, const FixIn& f) {
+__device__ __forceinline__ void fix_finish(const ChainParams& p, const Phase& P, int u, int rem0, int lane, const FixIn& f, bool scale_input = true) {
   const int rt = u / p.T, n = u - rt * p.T;
   const int mcol = (rem0 + rt) * BM + lane * 4;
   float4 a = f.a;
-  if (P.in_ssp != nullptr) {
+  if (P.in_ssp != nullptr && scale_input) {
     // the token's inverse RMS: the lanes split the per-tile sums, the shuffle tree adds them in a fixed order
     const float inv = rsqrtf(warp_sum(f.part) / (float)P.in_width + P.in_eps);
     a.x *= inv, a.y *= inv, a.z *= inv, a.w *= inv;
@@ -408,7 +437,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_chain_kernel(const __grid_c
       for (int ph = 0; ph < p.nphase && ok; ++ph) {
         const Phase& P = p.ph[ph];
         if (ph > 0) {
-          ok = grid_wait(p.counters + 2 * (ph - 1) + 1, (uint32_t)G, p.status, abort_flag, 20u + (uint32_t)ph);
+          ok = grid_wait(p.counters + 3 * (ph - 1) + 2, (uint32_t)G, p.status, abort_flag, 20u + (uint32_t)ph);
           fence_proxy_async_all();  // rows written by other SMs' ordinary stores, read by the bulk-copy engine
         }
         Item it;
@@ -487,6 +516,9 @@ __global__ void __launch_bounds__(THREADS, 1) decode_chain_kernel(const __grid_c
     unsigned long long* ts = (p.timing && et == 0) ? p.timing + (size_t)c * 16 : nullptr;
     if (ts) ts[0] = globaltimer_ns();
     pdl_wait();
+    // tensor parallel: exchanges completed before this launch (written by the previous launch's last CTA)
+    const uint32_t tp_epoch = p.tp.world > 1 ? *((volatile uint32_t*)p.tp.epoch) : 0u;
+    int tp_sites = 0;
     if (ts) ts[1] = globaltimer_ns();
     for (int ph = 0; ph < p.nphase; ++ph) {
       const Phase& P = p.ph[ph];
@@ -495,7 +527,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_chain_kernel(const __grid_c
         // whole-tile epilogues need every token's inverse RMS: the sums of squares come from the previous
         // phase's fix-up on other CTAs, complete once its second barrier is full
         bool w_ok = true;
-        if (et == 0 && ph > 0) w_ok = grid_wait(p.counters + 2 * (ph - 1) + 1, (uint32_t)G, p.status, abort_flag, 30u + (uint32_t)ph);
+        if (et == 0 && ph > 0) w_ok = grid_wait(p.counters + 3 * (ph - 1) + 2, (uint32_t)G, p.status, abort_flag, 30u + (uint32_t)ph);
         ok = bar128(w_ok);
         if (ok && et < 2 * BN) {
           const int n = et >> 1, half = et & 1;  // two threads per token
@@ -574,8 +606,9 @@ __global__ void __launch_bounds__(THREADS, 1) decode_chain_kernel(const __grid_c
         if (acc == 0) acc_phase ^= 1u;
       }
       // ---- all tiles / partials of this CTA are stored: first grid barrier of the phase ----
-      uint32_t* bar_a = p.counters + 2 * ph;
-      uint32_t* bar_b = bar_a + 1;
+      uint32_t* bar_a = p.counters + 3 * ph;  // [3ph] partials stored, [3ph + 1] rank partial stored (tensor parallel), [3ph + 2] output complete
+      uint32_t* bar_a2 = bar_a + 1;
+      uint32_t* bar_b = bar_a + 2;
       ok = bar128(ok);
       if (ts) ts[2 + 3 * ph] = globaltimer_ns();  // this CTA's tiles and partials are stored
       if (et == 0) grid_arrive(bar_a);
@@ -587,7 +620,96 @@ __global__ void __launch_bounds__(THREADS, 1) decode_chain_kernel(const __grid_c
         ok = bar128(ok && w_ok);
       }
       if (ts) ts[3 + 3 * ph] = globaltimer_ns();  // every CTA's partials are visible
-      if (ok && need_fix) {
+      const bool tp_reduce = p.tp.world > 1 && P.epi == CH_RESID_NORM;
+      if (ok && need_fix && tp_reduce) {
+        // ---- tensor parallel row phase: local partials -> this rank's bf16 partial -> sum over ranks in the switch ----
+        const int par = (int)((tp_epoch + (uint32_t)tp_sites) & 1u);
+        const uint32_t e = tp_epoch + (uint32_t)tp_sites + 1u;
+        bf16* y_loc = p.tp.y_local[par];
+        const int units = P.rem_tiles * p.T;
+        for (int u = c * EW + ew; u < units; u += 2 * EW * G) {
+          const int u2 = u + EW * G;
+          const bool two = u2 < units;
+          FixIn f1, f2;
+          fix_load(p, P, u, rem0, lane, f1);
+          if (two) fix_load(p, P, u2, rem0, lane, f2);
+#pragma unroll
+          for (int k = 0; k < 2; ++k) {
+            if (k == 1 && !two) break;
+            const int uu = k ? u2 : u;
+            const FixIn& f = k ? f2 : f1;
+            const int rt = uu / p.T, n = uu - rt * p.T;
+            const int mcol = (rem0 + rt) * BM + lane * 4;
+            float4 a = f.a;
+            if (P.in_ssp != nullptr) {
+              const float inv = rsqrtf(warp_sum(f.part) / (float)P.in_width + P.in_eps);
+              a.x *= inv, a.y *= inv, a.z *= inv, a.w *= inv;
+            }
+            const bf162 lo = __floats2bfloat162_rn(a.x, a.y), hi = __floats2bfloat162_rn(a.z, a.w);
+            uint2 pk;
+            pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+            pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+            if (mcol + 3 < P.M) *reinterpret_cast<uint2*>(y_loc + (size_t)n * P.M + mcol) = pk;
+          }
+        }
+        // every CTA's share of the rank partial is stored -> tell the other ranks -> wait for all of them
+        ok = bar128(ok);
+        if (et == 0) {
+          __threadfence_system();
+          atomicAdd(bar_a2, 1u);
+          bool w_ok = true;
+          if (c == 0) {
+            w_ok = grid_wait(bar_a2, (uint32_t)G, p.status, abort_flag, 40u + (uint32_t)ph);
+            __threadfence_system();
+            if (w_ok)
+              for (int q = 0; q < p.tp.world; ++q) st_release_sys(p.tp.flags_peer[q] + p.tp.rank, e);
+          }
+          if (w_ok) {
+            const uint64_t t0 = globaltimer_ns();
+            for (int q = 0; q < p.tp.world && w_ok; ++q) {
+              uint32_t spins = 0;
+              while ((int32_t)(ld_acquire_sys(p.tp.flags_local + q) - e) < 0) {
+                if ((++spins & 15u) == 0u) {
+                  if (*abort_flag || *((volatile uint32_t*)p.status) != PG_ST_OK) {
+                    *abort_flag = 1;
+                    w_ok = false;
+                    break;
+                  }
+                  if (globaltimer_ns() - t0 > p.tp.wait_ns) {
+                    atomicCAS(p.status, PG_ST_OK, PG_ST_TIMEOUT | ((50u + (uint32_t)ph) << 8) | ((uint32_t)q << 16));
+                    *abort_flag = 1;
+                    w_ok = false;
+                    break;
+                  }
+                }
+              }
+            }
+          }
+          ok = w_ok;
+        }
+        ok = bar128(ok);
+        if (ok) {
+          const bf16* y_mc = p.tp.y_mc[par];
+          for (int u = c * EW + ew; u < units; u += EW * G) {
+            const int rt = u / p.T, n = u - rt * p.T;
+            const int mcol = (rem0 + rt) * BM + lane * 4;
+            FixIn f;
+            f.part = 0.f;
+            f.a = make_float4(0.f, 0.f, 0.f, 0.f);
+            f.rv = make_uint2(0u, 0u);
+            f.wv = make_uint2(0u, 0u);
+            if (mcol + 3 < P.M) {
+              const uint2 sum = multimem_ld_reduce_bf16x4(y_mc + (size_t)n * P.M + mcol);
+              const float2 s0 = __bfloat1622float2(*reinterpret_cast<const bf162*>(&sum.x)), s1 = __bfloat1622float2(*reinterpret_cast<const bf162*>(&sum.y));
+              f.a = make_float4(s0.x, s0.y, s1.x, s1.y);
+              f.rv = __ldcg(reinterpret_cast<const uint2*>(p.residual + (size_t)n * p.ld_res + mcol));
+              f.wv = *reinterpret_cast<const uint2*>(P.norm_w + mcol);
+            }
+            fix_finish(p, P, u, rem0, lane, f, false);
+          }
+        }
+        ++tp_sites;
+      } else if (ok && need_fix) {
         // units (remainder tile, token): one warp each, a lane finishes 4 consecutive weight rows.  Two
         // units are in flight per warp: all loads of both are issued before the first value is used.
         const int units = P.rem_tiles * p.T;
@@ -610,13 +732,14 @@ __global__ void __launch_bounds__(THREADS, 1) decode_chain_kernel(const __grid_c
     // last CTA through re-arms the counters for the next launch (every CTA is past every wait by then:
     // a CTA arrives here only after it passed all of them)
     if (et == 0) {
-      uint32_t* fin = p.counters + 2 * MAX_PHASES;
+      uint32_t* fin = p.counters + 3 * MAX_PHASES;
       __threadfence();
       const uint32_t old = atomicAdd(fin, 1u);
       if (old == (uint32_t)G - 1u) {
         // nobody waits on `fin`; the token producers of other CTAs may still poll the last bar_b only if a
         // later phase existed, which it does not
-        for (int i = 0; i <= 2 * MAX_PHASES; ++i) p.counters[i] = 0u;
+        for (int i = 0; i <= 3 * MAX_PHASES; ++i) p.counters[i] = 0u;
+        if (p.tp.world > 1) *p.tp.epoch = tp_epoch + (uint32_t)tp_sites;  // the next launch numbers its exchanges from here
         __threadfence();
       }
     }
@@ -692,8 +815,38 @@ extern "C" long long pg_decode_chain_ws_bytes(int device) {
 // `residual` [T, hidden] is updated in place by every epi-2 phase.  `ws` holds
 // pg_decode_chain_ws_bytes() bytes; `counters` holds 16 uint32 that are zero before the first
 // launch (every completed launch leaves them zero).
+// Tensor-parallel description for pg_decode_chain_tp: `y_local` / `y_mc` are this rank's two partial buffers
+// (each at least 64 x max M bf16) and the same buffers through the multicast mapping; `flags_peer[q]` is rank
+// q's flag block (8 uint32 arrival words + the exchange counter at word 16, all zero at start), `flags_peer[rank]`
+// the local one.
+struct PgChainTp {
+  int world, rank;
+  void* y_local[2];
+  const void* y_mc[2];
+  void* flags_peer[8];
+  unsigned long long wait_ns;
+};
+
+static int decode_chain_impl(const PgChainPhase* phases, int nphase, int T, void* residual, long long ld_res, float eps, void* ws, long long ws_bytes, void* counters,
+                             void* status, const PgChainTp* tp, cudaStream_t stream);
+
 extern "C" int pg_decode_chain(const PgChainPhase* phases, int nphase, int T, void* residual, long long ld_res, float eps, void* ws, long long ws_bytes,
                                void* counters, void* status, cudaStream_t stream) {
+  return decode_chain_impl(phases, nphase, T, residual, ld_res, eps, ws, ws_bytes, counters, status, nullptr, stream);
+}
+
+// The same chain on one rank of a tensor-parallel group: every residual + norm phase sums its result over the
+// ranks through NVSwitch multicast memory (see ChainTp).  All ranks must launch the same sequence of chains.
+extern "C" int pg_decode_chain_tp(const PgChainPhase* phases, int nphase, int T, void* residual, long long ld_res, float eps, void* ws, long long ws_bytes,
+                                  void* counters, void* status, const PgChainTp* tp, cudaStream_t stream) {
+  PG_REQUIRE(tp != nullptr && tp->world >= 2 && tp->world <= TP_MAX_RANKS && tp->rank >= 0 && tp->rank < tp->world, "decode chain: bad tensor-parallel description");
+  for (int i = 0; i < 2; ++i) PG_REQUIRE(tp->y_local[i] && tp->y_mc[i] && ((uintptr_t)tp->y_local[i] & 15) == 0 && ((uintptr_t)tp->y_mc[i] & 15) == 0, "decode chain: partial buffers must be given and 16-byte aligned");
+  for (int q = 0; q < tp->world; ++q) PG_REQUIRE(tp->flags_peer[q] != nullptr, "decode chain: flag block of rank %d is missing", q);
+  return decode_chain_impl(phases, nphase, T, residual, ld_res, eps, ws, ws_bytes, counters, status, tp, stream);
+}
+
+static int decode_chain_impl(const PgChainPhase* phases, int nphase, int T, void* residual, long long ld_res, float eps, void* ws, long long ws_bytes, void* counters,
+                             void* status, const PgChainTp* tp, cudaStream_t stream) {
   PG_REQUIRE(nphase >= 1 && nphase <= MAX_PHASES, "decode chain: %d phases (1..%d)", nphase, MAX_PHASES);
   PG_REQUIRE(T >= 1 && T <= BN, "decode chain: built for steps of 1..%d token rows, got %d", BN, T);
   PG_REQUIRE(status != nullptr && counters != nullptr && ws != nullptr, "decode chain: scratch, counters and status word are required");
@@ -726,6 +879,18 @@ extern "C" int pg_decode_chain(const PgChainPhase* phases, int nphase, int T, vo
   p.counters = (uint32_t*)counters;
   p.status = (uint32_t*)status;
   p.timing = g_chain_timing;
+  if (tp) {
+    p.tp.world = tp->world;
+    p.tp.rank = tp->rank;
+    for (int i = 0; i < 2; ++i) {
+      p.tp.y_local[i] = (bf16*)tp->y_local[i];
+      p.tp.y_mc[i] = (const bf16*)tp->y_mc[i];
+    }
+    for (int q = 0; q < tp->world; ++q) p.tp.flags_peer[q] = (uint32_t*)tp->flags_peer[q];
+    p.tp.flags_local = (uint32_t*)tp->flags_peer[tp->rank];
+    p.tp.epoch = p.tp.flags_local + 16;
+    p.tp.wait_ns = tp->wait_ns ? tp->wait_ns : PG_WAIT_LIMIT_NS;
+  }
   for (int i = 0; i < nphase; ++i) {
     const PgChainPhase& s = phases[i];
     Phase& P = p.ph[i];

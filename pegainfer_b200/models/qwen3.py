@@ -80,9 +80,17 @@ class Qwen3Model:
         # row-parallel GEMMs and their consumers.  PEGAINFER_FUSED_DECODE=0 keeps the separate kernels.
         import os
 
-        self.fused_decode = self.device.type == "cuda" and tp.world == 1 and dtype == torch.bfloat16 and os.environ.get("PEGAINFER_FUSED_DECODE", "1") != "0"
+        chain_tp = tp.world > 1 and tp.comm == "chain"
+        self.fused_decode = self.device.type == "cuda" and (tp.world == 1 or chain_tp) and dtype == torch.bfloat16 and os.environ.get("PEGAINFER_FUSED_DECODE", "1") != "0"
         if self.fused_decode:
             self.set_gate_up_layout(True)
+        # With the chain collective the output projection is sharded by vocabulary as well: each rank
+        # streams 1 / world of lm_head and the ranks exchange (best value, index) pairs or logits.
+        self.vocab_sharded = chain_tp and cfg.vocab_size % tp.world == 0
+        if self.vocab_sharded:
+            v0, v1 = shard_range(cfg.vocab_size, tp.rank, tp.world)
+            self.vocab_range = (v0, v1)
+            self.lm_head = self.lm_head[v0:v1] if self.lm_head is self.embed else self.lm_head[v0:v1].contiguous()
 
     def set_gate_up_layout(self, interleaved: bool) -> None:
         """Reorder the rows of every fused gate_up weight in place: ``[gate; up]`` halves
@@ -243,6 +251,7 @@ class Qwen3Model:
             spec = dict(q_norm=l.q_norm, k_norm=l.k_norm, cos=self.cos, sin=self.sin, meta=meta, kv_layer=kv.layer(i), hq=self.q_heads, hkv=self.kv_heads, eps=eps)
             return (l.qkv, K.CH_QKV_ROPE, spec, False)
 
+        tpc = self.tp if self.tp.world > 1 else None
         q = K.decode_chain(x, [qkv_phase(0)])[0]
         for i, l in enumerate(self.layers):
             if not rope_fused:
@@ -251,15 +260,17 @@ class Qwen3Model:
             phases = [(l.o, K.CH_RESID_NORM, l.post_norm, False), (l.gate_up, K.CH_SWIGLU, None, False)]
             if i + 1 < n:
                 phases += [(l.down, K.CH_RESID_NORM, self.layers[i + 1].input_norm, False), qkv_phase(i + 1)]
-                outs = K.decode_chain(a, phases, residual=residual, eps=eps)
+                outs = K.decode_chain(a, phases, residual=residual, eps=eps, tp=tpc)
                 q = outs[3]
             else:
                 phases += [(l.down, K.CH_RESID_NORM, self.final_norm, False)]
-                outs = K.decode_chain(a, phases, residual=residual, eps=eps)
+                outs = K.decode_chain(a, phases, residual=residual, eps=eps, tp=tpc)
             x = outs[2]  # final-norm weight applied, per-token scale still owed: the lm_head GEMM completes it
             if i in aux_layers:
                 aux.append(residual.clone())
         self.last_aux = aux
+        if tpc is not None:
+            tpc.sites_by_rows[int(meta.num_tokens)] = (2 * n, 0)
         return x
 
     def _fused_chain_ok(self, meta: AttnMeta) -> bool:
@@ -267,6 +278,10 @@ class Qwen3Model:
         projection plans onto the GEMM's on-chip split-K path (decided once per row count)."""
         if not self.fused_decode or self.lora is not None or meta.num_tokens > 64 or ops.get_mode() != "sm100":
             return False
+        if self.tp.world > 1:  # tensor parallel: only the chain kernel carries a collective
+            from ..ops import cuda as K
+
+            return self._chain_ok(meta) and not K.batch_invariant()
         from ..ops import cuda as K
 
         t = int(meta.num_tokens)
@@ -290,5 +305,48 @@ class Qwen3Model:
             hidden = ops.gather_rows(hidden, rows)
         return ops.linear(hidden, self.lm_head)
 
+    def full_logits(self, logits: torch.Tensor) -> torch.Tensor:
+        """All-gather vocabulary-sharded logits ``[T, V / world]`` into ``[T, V]`` (a no-op otherwise)."""
+        if not getattr(self, "vocab_sharded", False):
+            return logits
+        import torch.distributed as dist
+
+        t, vs = logits.shape
+        out = torch.empty((self.tp.world, t, vs), dtype=logits.dtype, device=logits.device)
+        dist.all_gather_into_tensor(out, logits.contiguous(), group=self.tp.group)
+        return out.permute(1, 0, 2).reshape(t, self.tp.world * vs)
+
+    def greedy_tokens(self, logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Row-wise argmax (ties -> lowest index).  With vocabulary-sharded logits every rank finds
+        its local best and the ranks exchange (value, index) pairs: 8 bytes per row and rank
+        instead of the logits (reference: pegainfer-kernels csrc/shared/argmax.cu sharded argmax)."""
+        if not getattr(self, "vocab_sharded", False):
+            if out is not None and logits.is_cuda and ops.get_mode() != "library":
+                from ..ops import cuda as K
+
+                return K.argmax(logits, out=out)
+            res = ops.argmax(logits)
+            if out is not None:
+                out.copy_(res)
+                return out
+            return res
+        import torch.distributed as dist
+
+        w = self.tp.world
+        idx = ops.argmax(logits)  # local index, ties -> lowest
+        val = logits.float().gather(1, idx.long().unsqueeze(1)).squeeze(1)
+        pair = torch.stack((val, (idx + self.vocab_range[0]).float()), 1)  # indices below 2^24 are exact in f32
+        allp = torch.empty((w,) + tuple(pair.shape), dtype=torch.float32, device=logits.device)
+        dist.all_gather_into_tensor(allp, pair, group=self.tp.group)
+        vals, ids = allp[:, :, 0], allp[:, :, 1]
+        best = vals.max(0, keepdim=True).values
+        ranks = torch.arange(w, device=logits.device).unsqueeze(1).expand_as(vals)
+        first = torch.where(vals == best, ranks, torch.full_like(ranks, w)).min(0).values  # lowest rank = lowest index on ties
+        tok = ids.gather(0, first.unsqueeze(0)).squeeze(0).to(torch.int32)
+        if out is not None:
+            out.copy_(tok)
+            return out
+        return tok
+
     def forward(self, token_ids, meta, kv, logits_rows=None):
-        return self.logits(self.forward_hidden(token_ids, meta, kv), logits_rows)
+        return self.full_logits(self.logits(self.forward_hidden(token_ids, meta, kv), logits_rows))

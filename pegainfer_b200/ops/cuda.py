@@ -277,7 +277,30 @@ class GemmTrace:
             cls.buf = torch.zeros((cls.slots, 148 * 16), dtype=torch.int64, device="cuda")
         i = len(cls.names) % cls.slots
         cls.names.append(label)
-        lib().pg_gemm_set_timing(_vp(cls.buf[i].data_ptr()))
+        if label.startswith("chain"):
+            lib().pg_decode_chain_set_timing(_vp(cls.buf[i].data_ptr()))
+        else:
+            lib().pg_gemm_set_timing(_vp(cls.buf[i].data_ptr()))
+
+    @classmethod
+    def chain_rows(cls, first: int, end: int) -> list:
+        """Stamps of the decode-chain launches among the armed launches ``first .. end``: per launch the
+        medians over the CTAs of [entry, predecessor complete, then per phase: tiles stored, partials
+        visible, fix-up done], microseconds from the first launch's entry, and the last CTA's last stamp."""
+        import numpy as np
+
+        torch.cuda.synchronize()
+        rows, t0 = [], None
+        for i in range(first, end):
+            if not cls.names[i].startswith("chain"):
+                continue
+            tm = cls.buf[i % cls.slots].view(148, 16).cpu().numpy().astype(np.float64)
+            if t0 is None:
+                t0 = np.median(tm[:, 0])
+            med = [(np.median(tm[:, j]) - t0) / 1e3 if (tm[:, j] > 0).all() else float("nan") for j in range(14)]
+            last = (tm[:, :14].max() - t0) / 1e3
+            rows.append((cls.names[i], med, last))
+        return rows
 
     @classmethod
     def reset(cls) -> None:
@@ -371,7 +394,7 @@ CHAIN_MAX_ROWS = 64
 CH_PLAIN, CH_SWIGLU, CH_RESID_NORM, CH_QKV_ROPE = 0, 1, 2, 3
 
 
-def decode_chain(x, phases, residual=None, eps: float = 0.0):
+def decode_chain(x, phases, residual=None, eps: float = 0.0, tp=None):
     """Up to four dependent GEMMs of a decode step (at most 64 rows) in one persistent kernel.
 
     ``x``: bf16 ``[T, K0]`` or a ``DeferredNorm``; it feeds the first phase, each later phase reads
@@ -384,7 +407,8 @@ def decode_chain(x, phases, residual=None, eps: float = 0.0):
     128-wide heads: per-head QK RMSNorm, rotary embedding and the paged KV append happen in its epilogue;
     ``spec`` is a dict with ``q_norm``, ``k_norm`` (or None), ``cos``, ``sin``, ``meta`` (positions, slot
     mapping), ``kv_layer``, ``hq``, ``hkv``, ``eps``; the output is q ``[T, hq, 128]``.
-    Returns the list of phase outputs."""
+    ``tp``: a ``parallel.chain_tp.ChainTP``; the residual + norm phases then sum over the ranks
+    through NVSwitch multicast memory.  Returns the list of phase outputs."""
     dn = x if isinstance(x, DeferredNorm) else None
     cur = dn.xw if dn is not None else x
     _bf16(cur)
@@ -434,8 +458,12 @@ def decode_chain(x, phases, residual=None, eps: float = 0.0):
         arr[i] = ph
         cur = out
     GemmTrace.arm(f"chain x{len(phases)} T{t}")
-    rc = lib().pg_decode_chain(arr, _ci(len(phases)), _ci(t), _ptr(residual), _ll(residual.stride(0) if residual is not None else 0), _cf(eps), _ptr(c.chain_ws), _ll(c.chain_ws.numel()),
-                               _ptr(c.chain_counters), _ptr(c.status), _stream())
+    if tp is not None and tp.world > 1:
+        rc = lib().pg_decode_chain_tp(arr, _ci(len(phases)), _ci(t), _ptr(residual), _ll(residual.stride(0) if residual is not None else 0), _cf(eps), _ptr(c.chain_ws), _ll(c.chain_ws.numel()),
+                                      _ptr(c.chain_counters), _ptr(c.status), ctypes.byref(tp.spec), _stream())
+    else:
+        rc = lib().pg_decode_chain(arr, _ci(len(phases)), _ci(t), _ptr(residual), _ll(residual.stride(0) if residual is not None else 0), _cf(eps), _ptr(c.chain_ws), _ll(c.chain_ws.numel()),
+                                   _ptr(c.chain_counters), _ptr(c.status), _stream())
     _check(rc, c)
     return results
 

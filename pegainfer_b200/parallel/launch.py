@@ -204,6 +204,11 @@ def launch_distributed(ecfg, mcfg, ns) -> int:
             from .ep import EPContext
 
             ep = EPContext(rank, world, comm="nccl", tokens="dp")
+    elif ecfg.comm == "fused" and mcfg.family == "qwen3":
+        # decode: one chain kernel per layer that sums over the ranks inside the NVSwitch (multimem)
+        from .chain_tp import ChainTP
+
+        tp = ChainTP(rank, world, device, mcfg.hidden_size)
     elif ecfg.comm == "fused":
         from .fused import make_fused_tp
 

@@ -258,6 +258,8 @@ class TorchExecutor(ModelExecutor):
         if rows:
             idx = torch.tensor(rows, dtype=torch.int32, device=self.device)
             logits = self.model.logits(hidden, idx)
+            if hasattr(self.model, "full_logits"):
+                logits = self.model.full_logits(logits)  # vocabulary-sharded output projection: gather before sampling
             toks, lps = self._sample(logits, sample_seqs, rows_per_seq)
             toks = toks.tolist()
             k = 0
@@ -302,7 +304,8 @@ class TorchExecutor(ModelExecutor):
             keep = [token_ids, meta, hidden]
             if rows:
                 idx = torch.tensor(rows, dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
-                toks = ops.argmax(self.model.logits(hidden, idx))
+                lg = self.model.logits(hidden, idx)
+                toks = self.model.greedy_tokens(lg) if hasattr(self.model, "greedy_tokens") else ops.argmax(lg)
                 host = torch.empty(len(rows), dtype=toks.dtype).pin_memory()
                 host.copy_(toks, non_blocking=True)
                 keep += [idx, toks]

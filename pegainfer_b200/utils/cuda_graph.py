@@ -143,10 +143,15 @@ class DecodeGraphs:
         tok = self._views(b)[0]
         meta = self._meta(b, splits)
         hidden = self.ex.model.forward_hidden(tok, meta, self.ex.kv)
-        logits = self.ex.model.logits(hidden)
+        model = self.ex.model
+        logits = model.logits(hidden)
         if greedy:
-            _K().argmax(logits, out=self.out_tokens[:b])
-        return logits
+            if hasattr(model, "greedy_tokens"):
+                model.greedy_tokens(logits, out=self.out_tokens[:b])
+            else:
+                _K().argmax(logits, out=self.out_tokens[:b])
+            return logits
+        return model.full_logits(logits) if hasattr(model, "full_logits") else logits
 
     def _splits_for(self, b: int) -> int:
         geo = self.ex.model.kv_geometry()

@@ -22,6 +22,18 @@ def test_fused_tp_matches_single_gpu(world):
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
+def test_chain_tp_multimem_matches_single_gpu(world):
+    """The decode-chain kernel with its in-switch reduction (multimem.ld_reduce on NVSwitch multicast
+    memory), the vocabulary-sharded lm_head and the sharded argmax, against NCCL and one GPU."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1", "--master-port", str(29540 + world), os.path.join(ROOT, "tests", "chain_tp_worker.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=420, env=env, cwd=ROOT)
+    assert r.returncode == 0 and "CHAIN_TP_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_fused_ep_matches_single_gpu(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
