@@ -86,22 +86,33 @@ struct Phase {
 };
 
 // Tensor parallelism: the row-parallel phases (residual + norm epilogue) sum their result over the
-// ranks.  Every rank first reduces its own stream-K partials to a bf16 [T, M] partial in a buffer that
+// ranks (either inside the switch with multimem.ld_reduce, or by pulling every rank's copy with plain peer
+// loads over NVLink and adding in rank order; the pull has the lower latency for these 0.5 MB exchanges).  Every rank first reduces its own stream-K partials to a bf16 [T, M] partial in a buffer that
 // is mapped on all ranks and bound to an NVSwitch multicast object; after a flag exchange each rank
 // reads the sum over ranks with multimem.ld_reduce (reduced inside the switch, f32 accumulation) and
 // finishes the epilogue on its own replicated copy of the residual.  Two partial buffers alternate
 // between consecutive exchanges; exchange numbers (epochs) live in device memory, so CUDA-graph
 // replays need no reset.
 constexpr int TP_MAX_RANKS = 8;
+constexpr int TP_FLAG_STRIDE = 160;  // flag words per source rank (one per CTA; at least the SM count)
+constexpr int TP_EPOCH_WORD = TP_MAX_RANKS * TP_FLAG_STRIDE;
 struct ChainTp {
   int world, rank;
   bf16* y_local[2];            // this rank's partial buffers [T, M]
   const bf16* y_mc[2];         // the same buffers through the multicast mapping
-  uint32_t* flags_local;       // [TP_MAX_RANKS] latest exchange number announced by each rank
+  const bf16* y_peer[TP_MAX_RANKS][2];  // every rank's partial buffers (peer mapped)
+  int use_multimem;            // 1: sum with multimem.ld_reduce in the switch; 0: pull every rank's copy with plain peer loads and add in rank order
+  uint32_t* flags_local;       // [TP_MAX_RANKS][TP_FLAG_STRIDE] latest exchange number announced by CTA c of each rank
   uint32_t* flags_peer[TP_MAX_RANKS];  // every rank's flag block (peer mapped)
   uint32_t* epoch;             // local word: exchanges completed by previous launches
   unsigned long long wait_ns;
 };
+
+__device__ __forceinline__ uint2 ld_relaxed_sys_u32x2(const void* addr) {
+  uint2 v;
+  asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(addr) : "memory");
+  return v;
+}
 
 __device__ __forceinline__ uint2 multimem_ld_reduce_bf16x4(const bf16* mc_addr) {
   uint2 v;
@@ -606,8 +617,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_chain_kernel(const __grid_c
         if (acc == 0) acc_phase ^= 1u;
       }
       // ---- all tiles / partials of this CTA are stored: first grid barrier of the phase ----
-      uint32_t* bar_a = p.counters + 3 * ph;  // [3ph] partials stored, [3ph + 1] rank partial stored (tensor parallel), [3ph + 2] output complete
-      uint32_t* bar_a2 = bar_a + 1;
+      uint32_t* bar_a = p.counters + 3 * ph;  // [3ph] partials stored, [3ph + 1] spare, [3ph + 2] output complete
       uint32_t* bar_b = bar_a + 2;
       ok = bar128(ok);
       if (ts) ts[2 + 3 * ph] = globaltimer_ns();  // this CTA's tiles and partials are stored
@@ -652,60 +662,85 @@ __global__ void __launch_bounds__(THREADS, 1) decode_chain_kernel(const __grid_c
             if (mcol + 3 < P.M) *reinterpret_cast<uint2*>(y_loc + (size_t)n * P.M + mcol) = pk;
           }
         }
-        // every CTA's share of the rank partial is stored -> tell the other ranks -> wait for all of them
+        // This CTA's units of the rank partial are stored.  The same CTA index owns the same units on
+        // every rank (same shapes, same grid), so the exchange is CTA to CTA: announce to CTA c of every
+        // rank, wait for CTA c of every rank, no grid-wide step in between.
         ok = bar128(ok);
         if (et == 0) {
-          __threadfence_system();
-          atomicAdd(bar_a2, 1u);
-          bool w_ok = true;
-          if (c == 0) {
-            w_ok = grid_wait(bar_a2, (uint32_t)G, p.status, abort_flag, 40u + (uint32_t)ph);
-            __threadfence_system();
-            if (w_ok)
-              for (int q = 0; q < p.tp.world; ++q) st_release_sys(p.tp.flags_peer[q] + p.tp.rank, e);
-          }
-          if (w_ok) {
-            const uint64_t t0 = globaltimer_ns();
-            for (int q = 0; q < p.tp.world && w_ok; ++q) {
-              uint32_t spins = 0;
-              while ((int32_t)(ld_acquire_sys(p.tp.flags_local + q) - e) < 0) {
-                if ((++spins & 15u) == 0u) {
-                  if (*abort_flag || *((volatile uint32_t*)p.status) != PG_ST_OK) {
-                    *abort_flag = 1;
-                    w_ok = false;
-                    break;
-                  }
-                  if (globaltimer_ns() - t0 > p.tp.wait_ns) {
-                    atomicCAS(p.status, PG_ST_OK, PG_ST_TIMEOUT | ((50u + (uint32_t)ph) << 8) | ((uint32_t)q << 16));
-                    *abort_flag = 1;
-                    w_ok = false;
-                    break;
-                  }
+          bool w_ok = ok;
+          if (ts) ts[13] = globaltimer_ns();  // rank partial of this CTA stored
+          __threadfence_system();              // one fence for all flag stores below (a release store each would pay it per peer)
+          for (int q = 0; q < p.tp.world; ++q)
+            asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.tp.flags_peer[q] + p.tp.rank * TP_FLAG_STRIDE + c), "r"(e) : "memory");
+          if (ts) ts[14] = globaltimer_ns();  // announced
+          const uint64_t t0 = globaltimer_ns();
+          for (int q = 0; q < p.tp.world && w_ok; ++q) {
+            uint32_t spins = 0;
+            // relaxed polls (one acquire fence after the last flag): a poll is a plain L2 read of local memory
+            while ((int32_t)(*((volatile const uint32_t*)(p.tp.flags_local + q * TP_FLAG_STRIDE + c)) - e) < 0) {
+              if ((++spins & 15u) == 0u) {
+                if (*abort_flag || *((volatile uint32_t*)p.status) != PG_ST_OK) {
+                  *abort_flag = 1;
+                  w_ok = false;
+                  break;
+                }
+                if (globaltimer_ns() - t0 > p.tp.wait_ns) {
+                  atomicCAS(p.status, PG_ST_OK, PG_ST_TIMEOUT | ((50u + (uint32_t)ph) << 8) | ((uint32_t)q << 16));
+                  *abort_flag = 1;
+                  w_ok = false;
+                  break;
                 }
               }
             }
           }
+          asm volatile("fence.acq_rel.sys;" ::: "memory");
+          if (ts) ts[15] = globaltimer_ns();  // every rank's partial of these units has arrived
           ok = w_ok;
         }
         ok = bar128(ok);
         if (ok) {
           const bf16* y_mc = p.tp.y_mc[par];
-          for (int u = c * EW + ew; u < units; u += EW * G) {
-            const int rt = u / p.T, n = u - rt * p.T;
-            const int mcol = (rem0 + rt) * BM + lane * 4;
-            FixIn f;
-            f.part = 0.f;
-            f.a = make_float4(0.f, 0.f, 0.f, 0.f);
-            f.rv = make_uint2(0u, 0u);
-            f.wv = make_uint2(0u, 0u);
-            if (mcol + 3 < P.M) {
-              const uint2 sum = multimem_ld_reduce_bf16x4(y_mc + (size_t)n * P.M + mcol);
-              const float2 s0 = __bfloat1622float2(*reinterpret_cast<const bf162*>(&sum.x)), s1 = __bfloat1622float2(*reinterpret_cast<const bf162*>(&sum.y));
-              f.a = make_float4(s0.x, s0.y, s1.x, s1.y);
-              f.rv = __ldcg(reinterpret_cast<const uint2*>(p.residual + (size_t)n * p.ld_res + mcol));
-              f.wv = *reinterpret_cast<const uint2*>(P.norm_w + mcol);
+          for (int u = c * EW + ew; u < units; u += 2 * EW * G) {
+            // both units' sums over the ranks are requested from the switch before either is used
+            const int uu[2] = {u, u + EW * G};
+            FixIn f[2];
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+              f[k].part = 0.f;
+              f[k].a = make_float4(0.f, 0.f, 0.f, 0.f);
+              f[k].rv = make_uint2(0u, 0u);
+              f[k].wv = make_uint2(0u, 0u);
+              const int rt = uu[k] / p.T, n = uu[k] - rt * p.T;
+              const int mcol = (rem0 + rt) * BM + lane * 4;
+              if (uu[k] < units && mcol + 3 < P.M) {
+                const size_t off = (size_t)n * P.M + mcol;
+                if (p.tp.use_multimem) {
+                  const uint2 sum = multimem_ld_reduce_bf16x4(y_mc + off);
+                  const float2 s0 = __bfloat1622float2(*reinterpret_cast<const bf162*>(&sum.x)), s1 = __bfloat1622float2(*reinterpret_cast<const bf162*>(&sum.y));
+                  f[k].a = make_float4(s0.x, s0.y, s1.x, s1.y);
+                } else {
+                  // every rank's copy over NVLink, all loads in flight, added in rank order (the same order on every rank)
+                  uint2 part[TP_MAX_RANKS];
+#pragma unroll
+                  for (int q = 0; q < TP_MAX_RANKS; ++q)
+                    part[q] = q < p.tp.world ? ld_relaxed_sys_u32x2(p.tp.y_peer[q][par] + off) : make_uint2(0u, 0u);
+#pragma unroll
+                  for (int q = 0; q < TP_MAX_RANKS; ++q) {
+                    if (q < p.tp.world) {
+                      const float2 s0 = __bfloat1622float2(*reinterpret_cast<const bf162*>(&part[q].x)), s1 = __bfloat1622float2(*reinterpret_cast<const bf162*>(&part[q].y));
+                      f[k].a.x += s0.x;
+                      f[k].a.y += s0.y;
+                      f[k].a.z += s1.x;
+                      f[k].a.w += s1.y;
+                    }
+                  }
+                }
+                f[k].rv = __ldcg(reinterpret_cast<const uint2*>(p.residual + (size_t)n * p.ld_res + mcol));
+                f[k].wv = *reinterpret_cast<const uint2*>(P.norm_w + mcol);
+              }
             }
-            fix_finish(p, P, u, rem0, lane, f, false);
+            fix_finish(p, P, uu[0], rem0, lane, f[0], false);
+            if (uu[1] < units) fix_finish(p, P, uu[1], rem0, lane, f[1], false);
           }
         }
         ++tp_sites;
@@ -817,7 +852,7 @@ extern "C" long long pg_decode_chain_ws_bytes(int device) {
 // launch (every completed launch leaves them zero).
 // Tensor-parallel description for pg_decode_chain_tp: `y_local` / `y_mc` are this rank's two partial buffers
 // (each at least 64 x max M bf16) and the same buffers through the multicast mapping; `flags_peer[q]` is rank
-// q's flag block (8 uint32 arrival words + the exchange counter at word 16, all zero at start), `flags_peer[rank]`
+// q's flag block (8 x 160 uint32 arrival words, one per source rank and CTA, + the exchange counter at word 1280; 8 KiB, all zero at start), `flags_peer[rank]`
 // the local one.
 struct PgChainTp {
   int world, rank;
@@ -825,6 +860,8 @@ struct PgChainTp {
   const void* y_mc[2];
   void* flags_peer[8];
   unsigned long long wait_ns;
+  const void* y_peer[8][2];  // every rank's two partial buffers (peer mapped; [rank] = y_local)
+  int use_multimem;          // 1: multimem.ld_reduce; 0: plain peer loads added in rank order
 };
 
 static int decode_chain_impl(const PgChainPhase* phases, int nphase, int T, void* residual, long long ld_res, float eps, void* ws, long long ws_bytes, void* counters,
@@ -886,9 +923,17 @@ static int decode_chain_impl(const PgChainPhase* phases, int nphase, int T, void
       p.tp.y_local[i] = (bf16*)tp->y_local[i];
       p.tp.y_mc[i] = (const bf16*)tp->y_mc[i];
     }
-    for (int q = 0; q < tp->world; ++q) p.tp.flags_peer[q] = (uint32_t*)tp->flags_peer[q];
+    for (int q = 0; q < tp->world; ++q) {
+      p.tp.flags_peer[q] = (uint32_t*)tp->flags_peer[q];
+      for (int i = 0; i < 2; ++i) {
+        p.tp.y_peer[q][i] = (const bf16*)tp->y_peer[q][i];
+        PG_REQUIRE(tp->use_multimem || tp->y_peer[q][i] != nullptr, "decode chain: partial buffer %d of rank %d is missing", i, q);
+      }
+    }
+    p.tp.use_multimem = tp->use_multimem;
     p.tp.flags_local = (uint32_t*)tp->flags_peer[tp->rank];
-    p.tp.epoch = p.tp.flags_local + 16;
+    p.tp.epoch = p.tp.flags_local + TP_EPOCH_WORD;
+    PG_REQUIRE(G <= TP_FLAG_STRIDE, "decode chain: %d SMs exceed the per-rank flag stride", G);
     p.tp.wait_ns = tp->wait_ns ? tp->wait_ns : PG_WAIT_LIMIT_NS;
   }
   for (int i = 0; i < nphase; ++i) {

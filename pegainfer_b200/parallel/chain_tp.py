@@ -28,7 +28,7 @@ MAX_ROWS = 64
 
 
 class _ChainTpSpec(ctypes.Structure):
-    _fields_ = [("world", _ci), ("rank", _ci), ("y_local", _vp * 2), ("y_mc", _vp * 2), ("flags_peer", _vp * 8), ("wait_ns", _ull)]
+    _fields_ = [("world", _ci), ("rank", _ci), ("y_local", _vp * 2), ("y_mc", _vp * 2), ("flags_peer", _vp * 8), ("wait_ns", _ull), ("y_peer", (_vp * 2) * 8), ("use_multimem", _ci)]
 
 
 class ChainTP(TPContext):
@@ -42,7 +42,7 @@ class ChainTP(TPContext):
         grp = group if group is not None else dist.group.WORLD
         y_bytes = (MAX_ROWS * hidden * 2 + 255) // 256 * 256
         self._off_flags = 2 * y_bytes
-        nbytes = self._off_flags + 256
+        nbytes = self._off_flags + 8192  # 8 x 160 arrival words (source rank x CTA) and the exchange counter
         self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
         self.buf.zero_()
         torch.cuda.synchronize(self.device)
@@ -54,8 +54,16 @@ class ChainTP(TPContext):
         for i in range(2):
             spec.y_local[i] = self.handle.buffer_ptrs[rank] + i * y_bytes
             spec.y_mc[i] = self.handle.multicast_ptr + i * y_bytes
+        import os
+
+        # how the partial sums meet: "pull" = every rank reads every rank's copy with plain peer loads and adds in
+        # rank order; "multimem" = multimem.ld_reduce, the NVSwitch adds the copies
+        self.mode = os.environ.get("PEGAINFER_CHAIN_TP", "pull")
+        spec.use_multimem = int(self.mode == "multimem")
         for q in range(world):
             spec.flags_peer[q] = self.handle.buffer_ptrs[q] + self._off_flags
+            for i in range(2):
+                spec.y_peer[q][i] = self.handle.buffer_ptrs[q] + i * y_bytes
         self.spec = spec
         self.sites_by_rows: dict = {}
         dist.barrier(group=grp)
@@ -66,7 +74,7 @@ class ChainTP(TPContext):
         the in-switch reduction (two exchanges per layer), larger steps the library all-reduce."""
         keys = sorted(k for k in self.sites_by_rows if k >= rows) or sorted(self.sites_by_rows)
         fused, libs = self.sites_by_rows[keys[0]] if keys else (0, 0)
-        path = "fused-multimem" if fused and not libs else "nccl" if libs and not fused else "fused+nccl" if fused else "none"
+        path = f"fused-{self.mode}" if fused and not libs else "nccl" if libs and not fused else "fused+nccl" if fused else "none"
         return {"path": path, "fused_sites_per_step": fused, "library_sites_per_step": libs}
 
     def close(self) -> None:
