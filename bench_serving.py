@@ -3,6 +3,7 @@
 
     python bench_serving.py --url http://127.0.0.1:8000 --num-prompts 256 --input-len 1024 --output-len 256 --concurrency 64
     python bench_serving.py --url ... --request-rate 8            # open loop, Poisson arrivals
+    python bench_serving.py --url ... --qps-sweep 1,2,4,8,16      # one open-loop run per rate, one table row each
     python bench_serving.py --spawn sim --num-prompts 64           # self-contained: serves the CPU fake engine
 
 Prompts are uniform-random token ids sent as ``prompt: [int, ...]`` (no tokenizer in the
@@ -194,6 +195,7 @@ def main(argv=None) -> int:
     ap.add_argument("--output-len", type=int, default=256)
     ap.add_argument("--concurrency", type=int, default=64)
     ap.add_argument("--request-rate", type=float, default=0.0, help="requests/s, Poisson arrivals (0 = closed loop)")
+    ap.add_argument("--qps-sweep", default=None, help="comma-separated request rates: run the open-loop benchmark once per rate (fresh prompts each) and print one row per rate")
     ap.add_argument("--vocab", type=int, default=32000, help="prompt token ids are drawn from [0, vocab)")
     ap.add_argument("--shared-prefix", type=int, default=0, help="leading tokens shared by all prompts (prefix-cache runs)")
     ap.add_argument("--warmup", type=int, default=2, help="untimed requests sent first")
@@ -214,6 +216,29 @@ def main(argv=None) -> int:
     if args.warmup > 0:
         warm = make_prompts(args.warmup, min(args.input_len, 64), args.vocab, args.seed + 1)
         asyncio.run(run_load(args.url, args.model, warm, min(args.output_len, 4), args.warmup, 0.0, args.seed, extra))
+    if args.qps_sweep:
+        # the reference's QPS sweep (tools/bench/run_serving_bench.sh, scripts/qps_sweep.sh): Poisson arrivals at each
+        # rate, different prompts per rate so that the prefix cache of one run does not serve the next
+        rows = []
+        for i, rate in enumerate(float(v) for v in args.qps_sweep.split(",")):
+            ps = make_prompts(args.num_prompts, args.input_len, args.vocab, args.seed + 100 * (i + 1), args.shared_prefix)
+            traces, wall = asyncio.run(run_load(args.url, args.model, ps, args.output_len, args.concurrency, rate, args.seed + i, extra))
+            r = summarize(traces, wall)
+            r["request_rate"] = rate
+            rows.append(r)
+        print(f"{'QPS':>6s} {'out tok/s':>10s} {'TTFT p50':>9s} {'TTFT p99':>9s} {'TPOT p50':>9s} {'TPOT p99':>9s} {'failed':>6s}   (ms)")
+        for r in rows:
+            ms = lambda d, k: "-" if d.get(k) is None else f"{d[k]:.1f}"
+            print(f"{r['request_rate']:6.1f} {r['output_tok_s']:10.1f} {ms(r['ttft_ms'], 'p50'):>9s} {ms(r['ttft_ms'], 'p99'):>9s} {ms(r['tpot_ms'], 'p50'):>9s} {ms(r['tpot_ms'], 'p99'):>9s} {r['failed']:6d}")
+        res = {"sweep": rows, "config": {"url": args.url, "num_prompts": args.num_prompts, "input_len": args.input_len, "output_len": args.output_len, "concurrency": args.concurrency}}
+        print(json.dumps(res))
+        if args.json:
+            os.makedirs(os.path.dirname(os.path.abspath(args.json)) or ".", exist_ok=True)
+            with open(args.json, "w") as f:
+                json.dump(res, f, indent=1)
+        if server is not None:
+            server.should_exit = True
+        return 0 if all(r["failed"] == 0 for r in rows) else 1
     traces, wall = asyncio.run(run_load(args.url, args.model, prompts, args.output_len, args.concurrency, args.request_rate, args.seed, extra))
     res = summarize(traces, wall)
     res["config"] = {"url": args.url, "num_prompts": args.num_prompts, "input_len": args.input_len, "output_len": args.output_len,

@@ -143,5 +143,18 @@ def check(rc: int) -> None:
         raise NativeError(f"libpegainfer_b200 error {rc}: {msg}")
 
 
+def build_api_counter() -> str:
+    """Compile the LD_PRELOAD CUDA API counter (utils/cuda_api_counter.c) next to the main library."""
+    src = os.path.join(ROOT, "pegainfer_b200", "utils", "cuda_api_counter.c")
+    out = os.path.join(LIB_DIR, "libcuda_api_counter.so")
+    os.makedirs(LIB_DIR, exist_ok=True)
+    if not os.path.exists(out) or os.path.getmtime(out) < os.path.getmtime(src):
+        r = subprocess.run(["gcc", "-O2", "-shared", "-fPIC", "-o", out, src, "-ldl"], capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"gcc failed for {src}:\n{r.stderr}")
+    return out
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_api_counter())

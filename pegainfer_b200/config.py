@@ -295,6 +295,8 @@ class EngineConfig:
     kv_offload: bool = False
     kv_offload_host_gib: float = 4.0
     kv_offload_l1_disabled: bool = False  # test mode: evict idle GPU blocks before every probe
+    kv_offload_disk_dir: Optional[str] = None  # third tier: blocks evicted from host memory go to files here
+    kv_offload_disk_gib: float = 0.0
     max_prefill_tokens: int = 1024
     max_decode_batch: int = 256
     max_model_len: Optional[int] = None

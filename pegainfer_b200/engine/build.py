@@ -120,7 +120,8 @@ def build_engine(ecfg: EngineConfig, mcfg: Optional[ModelConfig] = None, device=
     if ecfg.kv_offload:
         from ..kv.host_tier import HostTier
 
-        host_tier = HostTier(kv, pool, int(ecfg.kv_offload_host_gib * (1 << 30)), l1_retention_disabled=ecfg.kv_offload_l1_disabled)
+        host_tier = HostTier(kv, pool, int(ecfg.kv_offload_host_gib * (1 << 30)), l1_retention_disabled=ecfg.kv_offload_l1_disabled,
+                             disk_dir=ecfg.kv_offload_disk_dir, disk_bytes=int(ecfg.kv_offload_disk_gib * (1 << 30)))
     spec = None
     if ecfg.spec_method:
         from ..spec.speculative import build_spec

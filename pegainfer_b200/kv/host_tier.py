@@ -62,7 +62,8 @@ class TierStats:
 
 
 class HostTier:
-    def __init__(self, kv, pool, host_bytes: int, reserve_floor: int = 2, l1_retention_disabled: bool = False, load_deadline_s: float = 15.0):
+    def __init__(self, kv, pool, host_bytes: int, reserve_floor: int = 2, l1_retention_disabled: bool = False, load_deadline_s: float = 15.0,
+                 disk_dir: Optional[str] = None, disk_bytes: int = 0):
         self.kv, self.pool = kv, pool
         self.data = kv.data
         self.device = self.data.device
@@ -86,16 +87,42 @@ class HostTier:
         self.load_deadline_s = load_deadline_s
         self.stats = TierStats()
         self._probed: set = set()
+        # optional third tier: blocks evicted from the pinned slab go to files, see kv/disk_tier.py
+        self.disk = None
+        if disk_dir and disk_bytes > 0:
+            from .disk_tier import DiskTier
+
+            self.disk = DiskTier(disk_dir, disk_bytes, self.block_bytes)
 
     # -- save path ---------------------------------------------------------------------
-    def _take_slot(self) -> Optional[int]:
+    def _take_slot(self, protect=()) -> Optional[int]:
+        """A free slot, else the least recently used entry that is not in ``protect``."""
         if self.free_slots:
             return self.free_slots.pop()
-        if self.by_hash:
-            _, slot = self.by_hash.popitem(last=False)
+        if self.saving:
+            self.poll()  # saves that have landed become evictable entries
+        victim = next((h for h in self.by_hash if h not in protect), None)
+        if victim is not None:
+            h, slot = victim, self.by_hash.pop(victim)
             self.stats.evictions += 1
+            if self.disk is not None:
+                self.disk.offer(h, self.slab[slot])  # copied out before the slot is reused
             return slot
         return None
+
+    def _promote_from_disk(self, h: bytes, protect=()) -> bool:
+        """Bring a block that only the disk tier holds back into a host slot (never at the cost of a
+        block in ``protect``: the run being assembled must stay resident until it is copied)."""
+        if self.disk is None or not self.disk.contains(h):
+            return False
+        slot = self._take_slot(protect)
+        if slot is None:
+            return False
+        if not self.disk.read_into(h, self.slab[slot]):
+            self.free_slots.append(slot)
+            return False
+        self.by_hash[h] = slot
+        return True
 
     def on_blocks_sealed(self, r, sched) -> None:
         """Offer every newly registered block of request ``r`` to the host tier."""
@@ -146,9 +173,11 @@ class HostTier:
     # -- query / load path -----------------------------------------------------------------
     def host_hit_run(self, hashes: list, start: int) -> int:
         n = 0
+        run = set()
         for h in hashes[start:]:
-            if h not in self.by_hash:
+            if h not in self.by_hash and not self._promote_from_disk(h, run):
                 break
+            run.add(h)
             n += 1
         return n
 

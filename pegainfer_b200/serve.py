@@ -28,7 +28,7 @@ log = logging.getLogger("pegainfer_b200.serve")
 
 SHARED_FLAGS = {
     "model_path", "preset", "served_model_name", "port", "host", "cuda_graph", "precapture_graphs", "dump_graph_dot", "device_ordinal", "tp_size", "dp_size", "ep_size",
-    "kv_offload", "kv_offload_host_gib", "no_prefix_cache", "max_prefill_tokens", "max_model_len", "num_kv_blocks", "gpu_memory_utilization",
+    "kv_offload", "kv_offload_host_gib", "kv_offload_disk_dir", "kv_offload_disk_gib", "no_prefix_cache", "max_prefill_tokens", "max_model_len", "num_kv_blocks", "gpu_memory_utilization",
     "kv_cache_memory_margin_mib", "kv_page_size", "max_decode_batch", "seed", "comm", "gemm", "tokenizer",
 }
 
@@ -92,6 +92,8 @@ def build_parser() -> argparse.ArgumentParser:
     k.add_argument("--no-prefix-cache", action="store_true")
     k.add_argument("--kv-offload", action="store_true", help="spill sealed KV blocks to a pinned host tier and restore them by content hash")
     k.add_argument("--kv-offload-host-gib", type=float, default=4.0)
+    k.add_argument("--kv-offload-disk-dir", default=None, help="third KV tier: blocks evicted from host memory are kept as files in this directory")
+    k.add_argument("--kv-offload-disk-gib", type=float, default=0.0)
     k.add_argument("--max-prefill-tokens", type=int, default=1024)
     k.add_argument("--max-decode-batch", type=int, default=256)
     k.add_argument("--max-model-len", type=int)
@@ -145,7 +147,7 @@ def engine_config_from(ns: argparse.Namespace) -> EngineConfig:
         dump_graph_dot=ns.dump_graph_dot, device_ordinal=ns.device_ordinal, tp_size=ns.tp_size, dp_size=ns.dp_size, ep_size=ns.ep_size,
         kv_page_size=ns.kv_page_size, num_kv_blocks=ns.num_kv_blocks, gpu_memory_utilization=ns.gpu_memory_utilization,
         kv_cache_memory_margin_mib=ns.kv_cache_memory_margin_mib, no_prefix_cache=ns.no_prefix_cache, kv_offload=ns.kv_offload,
-        kv_offload_host_gib=ns.kv_offload_host_gib, max_prefill_tokens=ns.max_prefill_tokens, max_decode_batch=ns.max_decode_batch,
+        kv_offload_host_gib=ns.kv_offload_host_gib, kv_offload_disk_dir=ns.kv_offload_disk_dir, kv_offload_disk_gib=ns.kv_offload_disk_gib, max_prefill_tokens=ns.max_prefill_tokens, max_decode_batch=ns.max_decode_batch,
         max_model_len=ns.max_model_len, batch_invariant=ns.batch_invariant, decode_overlap=ns.decode_overlap, run_ahead=not ns.no_run_ahead, tune_gc=not ns.no_gc_tuning, decode_sm_pct=ns.decode_sm_pct,
         enable_lora=ns.enable_lora, max_loras=ns.max_loras, max_lora_rank=ns.max_lora_rank, lora_modules=tuple(ns.lora_modules), spec_method=ns.spec_method,
         spec_draft_len=ns.spec_draft_len, draft_model_path=ns.draft_model_path, comm=ns.ep_backend or ns.comm, gemm=ns.gemm, seed=ns.seed,
