@@ -140,7 +140,7 @@ __global__ void __launch_bounds__(128) gdn_recurrent_kernel(const bf16* __restri
       }
       qs = warp_sum(qs);
       ks = warp_sum(ks);
-      const float qn = rsqrtf(qs + 1e-12f) * q_scale, kn = rsqrtf(ks + 1e-12f);
+      const float qn = rsqrtf(qs + 1e-6f) * q_scale, kn = rsqrtf(ks + 1e-6f);
 #pragma unroll
       for (int i = 0; i < QL; ++i) {
         const int e = lane + 32 * i;

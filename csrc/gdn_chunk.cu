@@ -191,7 +191,7 @@ gdn_chunk_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, long lo
       ks += __shfl_xor_sync(0xffffffffu, ks, 2);
       qs += __shfl_xor_sync(0xffffffffu, qs, 1);
       qs += __shfl_xor_sync(0xffffffffu, qs, 2);
-      const float kn = rsqrtf(ks + 1e-12f), qn = rsqrtf(qs + 1e-12f) * q_scale;
+      const float kn = rsqrtf(ks + 1e-6f), qn = rsqrtf(qs + 1e-6f) * q_scale;
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
         kf[i] *= kn;

@@ -74,7 +74,7 @@ def to_hf_config(cfg: ModelConfig) -> dict:
         out["head_dim"] = cfg.head_dim
     elif cfg.family == "qwen35":
         out.update(head_dim=cfg.head_dim, partial_rotary_factor=cfg.partial_rotary_factor, layer_types=list(cfg.layer_types), linear_num_key_heads=cfg.gdn_num_k_heads,
-                   linear_num_value_heads=cfg.gdn_num_v_heads, linear_key_head_dim=cfg.gdn_head_dim, linear_conv_kernel_dim=cfg.gdn_conv_kernel)
+                   linear_num_value_heads=cfg.gdn_num_v_heads, linear_key_head_dim=cfg.gdn_head_dim, linear_value_head_dim=cfg.gdn_head_dim, linear_conv_kernel_dim=cfg.gdn_conv_kernel)
     elif cfg.family in ("deepseek_v2", "kimi_k2"):
         out.update(q_lora_rank=cfg.q_lora_rank or None, kv_lora_rank=cfg.kv_lora_rank, qk_nope_head_dim=cfg.qk_nope_head_dim, qk_rope_head_dim=cfg.qk_rope_head_dim, v_head_dim=cfg.v_head_dim,
                    rope_scaling=cfg.rope_scaling, n_routed_experts=cfg.n_routed_experts, n_shared_experts=cfg.n_shared_experts, num_experts_per_tok=cfg.num_experts_per_tok,
@@ -88,6 +88,11 @@ def to_hf_config(cfg: ModelConfig) -> dict:
         from ..models import registry
 
         out.update(registry.hf_config_extras(cfg))
+    if cfg.family == "qwen35":
+        # the released checkpoints are multimodal wrappers: the language model's keys sit in text_config
+        text = dict(out, model_type="qwen3_5_text")
+        text.pop("architectures")
+        return {"model_type": "qwen3_5", "architectures": ["Qwen3_5ForConditionalGeneration"], "tie_word_embeddings": cfg.tie_word_embeddings, "text_config": text}
     return out
 
 

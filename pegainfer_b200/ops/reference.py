@@ -599,8 +599,8 @@ def gdn_recurrent(q, k, v, g, beta, state, meta: AttnMeta):
     rep = hv // hk
     qf = q.float()
     kf = k.float()
-    qf = qf * torch.rsqrt(qf.pow(2).sum(-1, keepdim=True) + 1e-12) * (dk ** -0.5)
-    kf = kf * torch.rsqrt(kf.pow(2).sum(-1, keepdim=True) + 1e-12)
+    qf = qf * torch.rsqrt(qf.pow(2).sum(-1, keepdim=True) + 1e-6) * (dk ** -0.5)
+    kf = kf * torch.rsqrt(kf.pow(2).sum(-1, keepdim=True) + 1e-6)
     qf = qf.repeat_interleave(rep, dim=1)
     kf = kf.repeat_interleave(rep, dim=1)
     vf = v.float()

@@ -350,3 +350,34 @@ def test_decode_graph_exports_dot_with_kernel_names(tmp_path):
         assert all(len(o[0]) == 4 for o in out)
     finally:
         eng.shutdown()
+
+
+def test_host_tier_on_gpu_saves_evicts_and_restores_prefix():
+    """The pinned host slab, the copy stream and the keep-alive on a real GPU: a prompt's blocks are
+    saved to host memory, evicted from the GPU pool, and restored for a second request with the same
+    prefix, which must then decode the same tokens as an engine without the tier."""
+    mk = lambda **kw: engine(False, **kw)
+    g = torch.Generator().manual_seed(31)
+    base = torch.randint(0, 8192, (200,), generator=g).tolist()
+    plain = mk()
+    off = mk(kv_offload=True, kv_offload_host_gib=0.25, kv_offload_l1_disabled=True)
+    try:
+        a1 = plain.generate([base + [1, 2]], max_tokens=6)[0][0]
+        a2 = plain.generate([base + [3, 4, 5]], max_tokens=6)[0][0]
+        b1 = off.generate([base + [1, 2]], max_tokens=6)[0][0]
+        ht = off.host_tier
+        assert ht.cuda and ht.slab.is_pinned()
+        ht.flush_saves_then(lambda: None)
+        assert ht.stats.saves >= 12  # 200 tokens = 12 full blocks of 16
+        b2, _, upd = off.generate([base + [3, 4, 5]], max_tokens=6)[0]
+        assert (b1, b2) == (a1, a2)
+        cached = [u.cached_tokens for u in upd if u.cached_tokens is not None]
+        assert cached == [192] and ht.stats.loads == 1 and ht.stats.host_hits == 12 and ht.stats.load_failures == 0
+        off.pool.check_invariants()
+        from pegainfer_b200.ops import cuda as K
+
+        torch.cuda.synchronize()
+        assert K.read_status("cuda:0") == 0
+    finally:
+        plain.shutdown()
+        off.shutdown()
