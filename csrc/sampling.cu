@@ -93,6 +93,41 @@ __global__ void __launch_bounds__(128) argmax_final_kernel(const ArgPair* __rest
   if (threadIdx.x == 0) out[row] = best.i;
 }
 
+// One step of a low-rank Markov head over block-drafted logits: row r scores token v with
+// base[(r * block + step) * ld + v] + bias[r * ldb + v] (bias = w2 . w1[previous token]); the best
+// token becomes the row's previous token for the next step and entry (r, step) of the drafts.
+template <typename T>
+__global__ void __launch_bounds__(256) markov_partial_kernel(const T* __restrict__ base, long long ld, int block, int step, const T* __restrict__ bias,
+                                                              long long ldb, int vocab, ArgPair* __restrict__ partial, int tiles) {
+  PG_PDL_ENTRY();
+  __shared__ ArgPair red[32];
+  const int row = blockIdx.y, tile = blockIdx.x;
+  const T* r = base + ((long long)row * block + step) * ld;
+  const T* b = bias + (long long)row * ldb;
+  ArgPair best{-FLT_MAX, 0x7fffffff};
+  const int end = min(vocab, (tile + 1) * ARG_TILE);
+  for (int i = tile * ARG_TILE + threadIdx.x; i < end; i += 256) {
+    float v = ldf(r, i) + ldf(b, i);
+    if (v > best.v) best = ArgPair{v, i};
+  }
+  best = block_argmax(best, red);
+  if (threadIdx.x == 0) partial[(long long)row * tiles + tile] = best;
+}
+
+__global__ void __launch_bounds__(128) markov_final_kernel(const ArgPair* __restrict__ partial, int tiles, int* __restrict__ next, int* __restrict__ drafts,
+                                                            int block, int step) {
+  PG_PDL_ENTRY();
+  __shared__ ArgPair red[32];
+  const int row = blockIdx.x;
+  ArgPair best{-FLT_MAX, 0x7fffffff};
+  for (int i = threadIdx.x; i < tiles; i += 128) best = arg_better(best, partial[(long long)row * tiles + i]);
+  best = block_argmax(best, red);
+  if (threadIdx.x == 0) {
+    next[row] = best.i;
+    drafts[(long long)row * block + step] = best.i;
+  }
+}
+
 // order-preserving float -> uint
 __device__ __forceinline__ uint32_t fkey(float f) {
   uint32_t u = __float_as_uint(f);
@@ -574,6 +609,25 @@ extern "C" int pg_argmax(const void* logits, int is_f32, int rows, int vocab, lo
     PG_CUDA(launch_pdl(argmax_partial_kernel<bf16>, dim3(grid), dim3(256), (size_t)(0), stream, (const bf16*)logits, ld, vocab, (ArgPair*)scratch, tiles));
   PG_LAUNCH_CHECK();
   PG_CUDA(launch_pdl(argmax_final_kernel, dim3(rows), dim3(128), (size_t)(0), stream, (const ArgPair*)scratch, tiles, (int*)out));
+  PG_LAUNCH_CHECK();
+  return PG_OK;
+}
+
+extern "C" int pg_markov_step_argmax(const void* base, int is_f32, int rows, int block, int step, int vocab, long long ld, const void* bias, long long ldb,
+                                    void* scratch, long long scratch_bytes, void* next, void* drafts, cudaStream_t stream) {
+  if (rows == 0) return PG_OK;
+  const int tiles = ceil_div(vocab, ARG_TILE);
+  PG_REQUIRE(step >= 0 && step < block, "markov step: step outside the block");
+  PG_REQUIRE(scratch_bytes >= pg_argmax_scratch_bytes(rows, vocab), "markov step: scratch too small");
+  dim3 grid(tiles, rows);
+  if (is_f32)
+    PG_CUDA(launch_pdl(markov_partial_kernel<float>, dim3(grid), dim3(256), (size_t)(0), stream, (const float*)base, ld, block, step, (const float*)bias, ldb,
+                       vocab, (ArgPair*)scratch, tiles));
+  else
+    PG_CUDA(launch_pdl(markov_partial_kernel<bf16>, dim3(grid), dim3(256), (size_t)(0), stream, (const bf16*)base, ld, block, step, (const bf16*)bias, ldb, vocab,
+                       (ArgPair*)scratch, tiles));
+  PG_LAUNCH_CHECK();
+  PG_CUDA(launch_pdl(markov_final_kernel, dim3(rows), dim3(128), (size_t)(0), stream, (const ArgPair*)scratch, tiles, (int*)next, (int*)drafts, block, step));
   PG_LAUNCH_CHECK();
   return PG_OK;
 }

@@ -309,7 +309,7 @@ class EngineConfig:
     max_loras: int = 4
     max_lora_rank: int = 64
     lora_modules: tuple = ()
-    spec_method: Optional[str] = None  # None | "mtp" | "draft"
+    spec_method: Optional[str] = None  # None | "mtp" | "draft" | "dflash" | "dspark" | "eagle3"
     spec_draft_len: int = 1
     draft_model_path: Optional[str] = None
     comm: str = "fused"  # fused | nccl

@@ -91,6 +91,14 @@ def build_engine(ecfg: EngineConfig, mcfg: Optional[ModelConfig] = None, device=
         from ..spec.draft_model import load_draft_model
 
         model.draft_model = load_draft_model(ecfg, model)
+    if ecfg.spec_method in ("dflash", "dspark") and getattr(model, "draft_model", None) is None:
+        from ..spec.dflash import DFlashDraftModel
+
+        model.draft_model = DFlashDraftModel.load(ecfg.draft_model_path or "random", model, seed=ecfg.seed + 1)
+    if ecfg.spec_method == "eagle3" and getattr(model, "draft_model", None) is None:
+        from ..spec.eagle3 import Eagle3DraftModel
+
+        model.draft_model = Eagle3DraftModel.load(ecfg.draft_model_path or "random", model, seed=ecfg.seed + 1)
     page = ecfg.kv_page_size
     nblocks = ecfg.num_kv_blocks or profile_kv_blocks(model, ecfg, page)
     if nblocks < 2:
@@ -102,8 +110,6 @@ def build_engine(ecfg: EngineConfig, mcfg: Optional[ModelConfig] = None, device=
     executor = (model.make_executor if hasattr(model, "make_executor") else TorchExecutor)(
         model, kv, page, cuda_graph=ecfg.cuda_graph, max_decode_batch=ecfg.max_decode_batch, max_blocks_per_seq=max_blocks_per_seq, seed=ecfg.seed
     )
-    if ecfg.precapture_graphs and getattr(executor, "_graphs", None) is not None:
-        executor._graphs.precapture(True, ecfg.max_decode_batch)
     scfg = SchedulerConfig(
         max_prefill_tokens=ecfg.max_prefill_tokens,
         max_decode_batch=ecfg.max_decode_batch,
@@ -127,6 +133,10 @@ def build_engine(ecfg: EngineConfig, mcfg: Optional[ModelConfig] = None, device=
         from ..spec.speculative import build_spec
 
         spec = build_spec(ecfg, model, executor)
+        if hasattr(executor, "enable_verify_graph"):
+            executor.enable_verify_graph(1 + int(getattr(spec, "draft_len", 1)))
+    if ecfg.precapture_graphs and getattr(executor, "_graphs", None) is not None:
+        executor._graphs.precapture(True, ecfg.max_decode_batch)
     sched = ContinuousScheduler(executor, pool, scfg, spec=spec, host_tier=host_tier)
     info = EngineInfo(
         model_name=ecfg.served_model_name or ecfg.preset or (ecfg.model_path or "model"),

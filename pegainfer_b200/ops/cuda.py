@@ -610,6 +610,20 @@ def argmax(logits, out: Optional[torch.Tensor] = None):
     return out
 
 
+def markov_step_argmax(base, bias, block: int, step: int, next_tokens, drafts):
+    """``next_tokens[r] = drafts[r, step] = argmax_v base[r * block + step, v] + bias[r, v]``."""
+    rows, vocab = bias.shape
+    assert base.shape[0] == rows * block and base.shape[1] == vocab and base.stride(-1) == 1 and bias.stride(-1) == 1 and base.dtype == bias.dtype
+    c = ctx(base.device)
+    f32 = base.dtype == torch.float32
+    if not f32:
+        _bf16(base)
+    rc = lib().pg_markov_step_argmax(_ptr(base), _ci(int(f32)), _ci(rows), _ci(block), _ci(step), _ci(vocab), _ll(base.stride(0)), _ptr(bias), _ll(bias.stride(0)),
+                                     _ptr(c.argmax_scratch), _ll(c.argmax_scratch.numel()), _ptr(next_tokens), _ptr(drafts), _stream())
+    _check(rc, c, 2)
+    return next_tokens
+
+
 def sample(logits, temperature, top_k, top_p, min_p, u):
     rows, vocab = logits.shape
     if logits.stride(-1) != 1:

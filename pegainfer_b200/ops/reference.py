@@ -621,6 +621,18 @@ def gdn_recurrent(q, k, v, g, beta, state, meta: AttnMeta):
     return out
 
 
+def markov_step_argmax(base, bias, block: int, step: int, next_tokens, drafts):
+    """One step of a low-rank Markov head over block-drafted logits (pegainfer-qwen3/src/dspark.rs:60-100):
+    row ``r`` scores with ``base[r * block + step] + bias[r]``; the argmax is written to ``next_tokens[r]``
+    and ``drafts[r, step]`` (``drafts`` is ``[rows * block]`` int32)."""
+    rows = bias.shape[0]
+    score = base.view(rows, block, -1)[:, step].float() + bias.float()
+    tok = score.argmax(-1).to(torch.int32)
+    next_tokens[:rows] = tok
+    drafts.view(rows, block)[:, step] = tok
+    return next_tokens
+
+
 def sigmoid_gate_mul(x, gate):
     return (x.float() * torch.sigmoid(gate.float())).to(x.dtype)
 

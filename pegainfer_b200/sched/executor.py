@@ -164,6 +164,7 @@ class TorchExecutor(ModelExecutor):
         self.max_decode_batch = max_decode_batch
         self.max_blocks_per_seq = max_blocks_per_seq
         self.mtp = None  # set by spec.MtpSpec
+        self.aux_sink = None  # set by drafters that read target hidden states: .aux_layers, .observe(kind, seqs, meta, aux)
         self._lane_stream = None  # second stream of the decode-overlap prefill lane
         self._graphs = None
         if self.use_graph:
@@ -194,7 +195,41 @@ class TorchExecutor(ModelExecutor):
 
     def _graph_decode(self, batch: StepBatch) -> bool:
         seqs = batch.seqs
-        return self._graphs is not None and self.mtp is None and batch.is_decode() and len(seqs) <= self.max_decode_batch and all(s.sample and s.logprobs == 0 and s.lora_slot < 0 for s in seqs)
+        return (self._graphs is not None and self.mtp is None and self.aux_sink is None and batch.is_decode() and len(seqs) <= self.max_decode_batch
+                and all(s.sample and s.logprobs == 0 and s.lora_slot < 0 for s in seqs))
+
+    def enable_verify_graph(self, span: int) -> None:
+        """Size the decode graphs for verify steps of ``span`` rows per request (speculative decoding):
+        a verify step replays the decode graph of ``requests * span`` rows."""
+        self.verify_span = span
+        if self._graphs is None or self._graphs.uses_state:
+            return
+        from ..utils.cuda_graph import DecodeGraphs
+
+        want = min(DECODE_BUCKETS[-1], self.max_decode_batch * span)
+        if want > self._graphs.max_b:
+            self._graphs.release()
+            self._graphs = DecodeGraphs(self, want, self.max_blocks_per_seq)
+        if self.aux_sink is not None:
+            self._graphs.aux_layers = tuple(self.aux_sink.aux_layers)
+
+    def _graph_verify(self, batch: StepBatch) -> bool:
+        g, seqs = self._graphs, batch.seqs
+        return (batch.kind == "verify" and g is not None and not g.uses_state and self.mtp is None and getattr(self, "verify_span", 0) > 0
+                and batch.num_tokens <= g.max_b and all(s.sample and s.all_rows and s.logprobs == 0 and s.lora_slot < 0 and s.params.effectively_greedy(self.vocab_size) for s in seqs))
+
+    def _execute_verify_graph(self, batch: StepBatch, t0: float) -> StepResult:
+        from types import SimpleNamespace
+
+        rows, indptr = [], [0]
+        for s in batch.seqs:
+            for j, tok in enumerate(s.input_tokens):
+                rows.append(SeqStep(rid=s.rid, input_tokens=[tok], start_pos=s.start_pos + j, view=s.view))
+            indptr.append(len(rows))
+        toks, aux = self._graphs.run_rows(rows)
+        if self.aux_sink is not None:
+            self.aux_sink.observe("verify", batch.seqs, SimpleNamespace(num_tokens=len(rows), h_q_indptr=indptr), aux)
+        return StepResult(tokens={s.rid: toks[indptr[i] : indptr[i + 1]] for i, s in enumerate(batch.seqs)}, elapsed_s=time.perf_counter() - t0)
 
     def execute(self, batch: StepBatch) -> StepResult:
         g = self._graphs
@@ -218,6 +253,8 @@ class TorchExecutor(ModelExecutor):
         t0 = time.perf_counter()
         self.steps += 1
         seqs = batch.seqs
+        if self._graph_verify(batch):
+            return self._execute_verify_graph(batch, t0)
         if self._graph_decode(batch):
             all_greedy = all(s.params.effectively_greedy(self.vocab_size) for s in seqs)
             out = self._graphs.run(seqs, greedy=all_greedy, ahead=batch.run_ahead and all_greedy)
@@ -243,7 +280,11 @@ class TorchExecutor(ModelExecutor):
             rows += [-1] * (meta.num_tokens - len(rows))
             meta.lora_slots = torch.tensor(rows, dtype=torch.int32, device=self.device)
         self.prepare_meta(seqs, meta)
-        hidden = self.model.forward_hidden(token_ids, meta, self.kv)
+        if self.aux_sink is not None:
+            hidden = self.model.forward_hidden(token_ids, meta, self.kv, aux_layers=self.aux_sink.aux_layers)
+            self.aux_sink.observe(batch.kind, seqs, meta, self.model.last_aux)
+        else:
+            hidden = self.model.forward_hidden(token_ids, meta, self.kv)
         # rows that need logits
         rows, rows_per_seq, sample_seqs = [], [], []
         for i, s in enumerate(seqs):

@@ -454,6 +454,7 @@ class ContinuousScheduler:
 
         seqs = []
         propose = getattr(self.spec, "propose", None)
+        on_accept = getattr(self.spec, "on_accept", None)
         all_drafts = {}
         try:
             if propose is not None:
@@ -480,6 +481,8 @@ class ContinuousScheduler:
             accepted = accept_prefix_match(drafts, result.tokens[rid])
             self._metrics.spec_decode.record(len(drafts), len(accepted) - 1)
             r.kv.apply_speculative(len(accepted), accepted)
+            if on_accept is not None:
+                on_accept(rid, len(accepted))
             nd = result.drafts.get(rid)
             r.spec_state = [nd[len(accepted) - 1]] if nd else None
             emitted, finished = [], None

@@ -103,7 +103,7 @@ def build_parser() -> argparse.ArgumentParser:
     x.add_argument("--max-loras", type=int, default=4)
     x.add_argument("--max-lora-rank", type=int, default=64)
     x.add_argument("--batch-invariant", action="store_true")
-    x.add_argument("--spec-method", choices=["mtp", "draft"])
+    x.add_argument("--spec-method", choices=["mtp", "draft", "dflash", "dspark", "eagle3"])
     x.add_argument("--draft-model-path")
     x.add_argument("--spec-draft-len", type=int, default=1)
     x.add_argument("--decode-overlap", action="store_true")

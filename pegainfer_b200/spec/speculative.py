@@ -8,6 +8,10 @@ rejected positions is rolled back by ``RequestKv.apply_speculative``.
   per round; verification is a 2-row forward per request.
 * ``DraftModelSpec``: a smaller model of the same vocabulary drafts ``k`` tokens
   autoregressively (its own paged KV).
+* ``DFlashSpec`` (``spec.dflash``): a block drafter over the target's hidden states drafts a whole
+  block in one forward pass; with a Markov head (DSpark) the block is corrected left to right.
+* ``Eagle3Spec`` (``spec.eagle3``): one decoder layer over (next token, fused target feature) pairs
+  drafts a chain of three tokens.
 
 A round runs only when every running request is draft-ready, greedy, and wants no
 logprobs (pegainfer-qwen3/src/scheduler/plan.rs:153-164); prefix caching is off while
@@ -57,4 +61,15 @@ def build_spec(ecfg, model, executor):
         from .draft_model import DraftModelSpec
 
         return DraftModelSpec(ecfg, model, executor)
+    if ecfg.spec_method in ("dflash", "dspark"):
+        from .dflash import DFlashSpec
+
+        spec = DFlashSpec(ecfg, model, executor)
+        if ecfg.spec_method == "dspark" and spec.kind != "dspark":
+            raise ValueError("--spec-method dspark needs a drafter with a Markov head (markov_rank > 0)")
+        return spec
+    if ecfg.spec_method == "eagle3":
+        from .eagle3 import Eagle3Spec
+
+        return Eagle3Spec(ecfg, model, executor)
     raise ValueError(f"unknown speculative method {ecfg.spec_method!r}")

@@ -87,6 +87,8 @@ class DecodeGraphs:
         self.launch_s = 0.0  # host time spent staging and launching steps
         self.graphs: dict = {}
         self.logits: dict = {}
+        self.aux_layers: tuple = ()  # target layers whose residual stream every captured step also returns (drafters read them)
+        self.aux: dict = {}  # graph key -> the step's tapped hidden states (graph outputs, overwritten by the next replay)
         self.pool = None
         self.h2d_bytes = 0
         self.d2h_bytes = 0
@@ -107,6 +109,8 @@ class DecodeGraphs:
         self.pending = None
         self.graphs.clear()
         self.logits.clear()
+        self.aux.clear()
+        self._last_aux = None
         self.pool = None
 
     def invalidate_table(self) -> None:
@@ -142,8 +146,12 @@ class DecodeGraphs:
     def _forward(self, b: int, greedy: bool, splits: int):
         tok = self._views(b)[0]
         meta = self._meta(b, splits)
-        hidden = self.ex.model.forward_hidden(tok, meta, self.ex.kv)
         model = self.ex.model
+        if self.aux_layers:
+            hidden = model.forward_hidden(tok, meta, self.ex.kv, aux_layers=self.aux_layers)
+            self._last_aux = list(model.last_aux)
+        else:
+            hidden = model.forward_hidden(tok, meta, self.ex.kv)
         logits = model.logits(hidden)
         if greedy:
             if hasattr(model, "greedy_tokens"):
@@ -190,6 +198,8 @@ class DecodeGraphs:
         torch.cuda.current_stream(self.device).wait_stream(s)
         self.graphs[key] = g
         self.logits[key] = logits
+        if self.aux_layers:
+            self.aux[key] = self._last_aux
         return g
 
     def precapture(self, greedy: bool = True, max_batch: int = 0) -> int:
@@ -379,6 +389,30 @@ class DecodeGraphs:
         self.wait_s += time.perf_counter() - t0
         host = cur.host.tolist()
         return [host[cur.rows[s.rid]] for s in seqs]
+
+    def run_rows(self, rows):
+        """A verify step as a widened decode step.  ``rows``: one-token steps, several of them per request
+        (consecutive positions of the same block table).  Row ``j`` of a request is a sequence of its own
+        whose KV length ends at its position: the layer's K/V append runs over all rows before its
+        attention, so the row sees the request's earlier rows of the same step, and causality inside the
+        span needs no mask.  Returns ``(tokens, tapped hidden states or None)`` for the rows in order."""
+        from ..sched.executor import bucket_for
+
+        n = len(rows)
+        self.pending = None
+        b = bucket_for(n, self.buckets)
+        key = (b, True)
+        if key not in self.graphs:
+            self.capture(b, True)
+        self.invalidate_table()  # rows of one request share a request id: the per-row table cache does not apply
+        self.stage(rows, b)
+        self.graphs[key].replay()
+        self.replays += 1
+        self.invalidate_table()
+        self.h_out[:n].copy_(self.out_tokens[:n], non_blocking=True)
+        self.d2h_bytes += n * 4
+        torch.cuda.current_stream(self.device).synchronize()
+        return self.h_out[:n].tolist(), self.aux.get(key)
 
     def dump_dot(self, path: str, b: Optional[int] = None, greedy: bool = True, png: bool = False) -> dict:
         """Write the decode graph of bucket ``b`` as Graphviz DOT text: every kernel node with its

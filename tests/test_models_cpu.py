@@ -158,3 +158,82 @@ def test_seeded_request_draws_a_distinct_random_number_for_every_token():
         sel.mix_seed = inner
     # two requests x six tokens; per request the steps are 0..5, each exactly once
     assert sorted(seen) == sorted(list(range(6)) * 2), seen
+
+
+def _spec_lossless(method, path, rounds_attr="rounds"):
+    ps = prompts_for(3, 21, seed=6)
+    plain, _ = gen("tiny-qwen3", ps, 14)
+    spec, eng = gen("tiny-qwen3", ps, 14, spec_method=method, draft_model_path=path, max_prefill_tokens=16)
+    assert spec == plain
+    c = eng.scheduler._metrics.spec_decode
+    assert c.num_drafts > 0 and getattr(eng.scheduler.spec, rounds_attr) > 0
+    return eng, c
+
+
+def test_dflash_block_drafter_is_lossless_anchor_drop_and_anchor_first():
+    """A random block drafter proposes garbage: the output must still equal plain greedy decoding, with
+    chunked prefill feeding the draft cache and verify rows joining the next round's context."""
+    eng, c = _spec_lossless("dflash", "random:layers=2,block=4")
+    assert eng.scheduler.spec.draft_len == 3 and c.num_draft_tokens == 3 * c.num_drafts
+    eng, c = _spec_lossless("dflash", "random:layers=1,block=3,anchor_first=1")
+    assert eng.scheduler.spec.draft_len == 3
+
+
+def test_dspark_markov_head_is_lossless_and_sequential():
+    eng, c = _spec_lossless("dspark", "random:layers=1,block=3,markov=8")
+    assert eng.scheduler.spec.kind == "dspark" and eng.scheduler.spec.draft_len == 3
+
+
+def test_dflash_drafter_that_knows_the_answer_is_accepted():
+    """Acceptance accounting: a drafter whose picks are replaced by the target's own continuation gets every
+    draft accepted, and the request finishes in about max_tokens / (drafts + 1) verify rounds."""
+    ps = prompts_for(2, 19, seed=8)
+    plain, _ = gen("tiny-qwen3", ps, 13)
+    from pegainfer_b200.spec import dflash
+
+    truth = {tuple(p): o for p, o in zip(ps, plain)}
+    orig = dflash.DFlashSpec.propose
+
+    def oracle(self, decoders):
+        out = orig(self, decoders)  # still runs the drafter (cache bookkeeping), then overrides its picks
+        for r in decoders:
+            toks = r.kv.tokens
+            for p, o in truth.items():
+                if tuple(toks[: len(p)]) == p:
+                    done = len(toks) - len(p)
+                    want = o[done : done + self.draft_len]
+                    out[r.q.id] = want + [0] * (self.draft_len - len(want))
+        return out
+
+    dflash.DFlashSpec.propose = oracle
+    try:
+        spec, eng = gen("tiny-qwen3", ps, 13, spec_method="dflash", draft_model_path="random:layers=1,block=4")
+    finally:
+        dflash.DFlashSpec.propose = orig
+    assert spec == plain
+    c = eng.scheduler._metrics.spec_decode
+    assert c.num_accepted_tokens >= c.num_draft_tokens - 2 * 3  # all but each request's last, truncated round
+    assert eng.scheduler.spec.rounds <= 5
+
+
+def test_eagle3_chain_drafter_is_lossless():
+    import dataclasses
+
+    cfg = dataclasses.replace(preset("tiny-qwen3"), num_layers=8)
+    ps = prompts_for(3, 21, seed=7)
+
+    def run(**kw):
+        ecfg = EngineConfig(preset="tiny-qwen3", kv_page_size=16, num_kv_blocks=128, cuda_graph=False, **kw)
+        eng = build_engine(ecfg, cfg, device="cpu", dtype=torch.float32)
+        try:
+            return [o[0] for o in eng.generate(ps, SamplingParams(temperature=0.0, ignore_eos=True), max_tokens=12, timeout=300)], eng
+        finally:
+            eng.shutdown()
+
+    plain, _ = run()
+    spec, eng = run(spec_method="eagle3", draft_model_path="random:draft_vocab=512", max_prefill_tokens=16)
+    assert spec == plain
+    s = eng.scheduler.spec
+    assert s.draft_len == 3 and s.rounds > 0 and s.draft.aux_layers == (1, 3, 4)
+    c = eng.scheduler._metrics.spec_decode
+    assert c.num_draft_tokens == 3 * c.num_drafts
