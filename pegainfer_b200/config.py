@@ -20,7 +20,7 @@ from typing import Optional
 
 @dataclass
 class ModelConfig:
-    family: str = "qwen3"  # qwen3 | qwen35 | deepseek_v2 | kimi_k2
+    family: str = "qwen3"  # qwen3 | qwen35 | deepseek_v2 | kimi_k2 | glm_dsa
     vocab_size: int = 1024
     hidden_size: int = 256
     num_layers: int = 2
@@ -66,6 +66,10 @@ class ModelConfig:
     quant_group_size: int = 32
     # MTP
     num_mtp_layers: int = 0
+    # sparse attention indexer (GLM-5 line): every query keeps its index_topk best-scoring keys
+    index_topk: int = 0
+    index_head_dim: int = 128
+    index_n_heads: int = 0
 
     # -- derived ---------------------------------------------------------------
     @property
@@ -154,6 +158,16 @@ PRESETS = {
     "kimi-k2": ModelConfig(family="kimi_k2", vocab_size=163840, hidden_size=7168, num_layers=61, num_q_heads=64, num_kv_heads=64, head_dim=192, intermediate_size=18432, qk_norm=False, q_lora_rank=1536, kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, n_routed_experts=384, n_shared_experts=1, num_experts_per_tok=8, moe_intermediate_size=2048, first_k_dense_replace=1, scoring_func="sigmoid", n_group=1, topk_group=1, norm_topk_prob=True, routed_scaling_factor=2.827, router_bias=True, expert_quant="int4_g32", rope_theta=50000.0, rope_scaling=dict(_YARN_KIMI), rms_eps=1e-5, max_position=131072, num_mtp_layers=1),
 }
 # the DeepSeek-V2 shapes with block-scaled FP8 e4m3 experts (128x128 scale blocks)
+PRESETS["tiny-glm"] = ModelConfig(family="glm_dsa", vocab_size=1024, hidden_size=256, num_layers=3, num_q_heads=4, num_kv_heads=4, head_dim=48, intermediate_size=512, qk_norm=False, q_lora_rank=96,
+                                  kv_lora_rank=64, qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=48, n_routed_experts=8, n_shared_experts=1, num_experts_per_tok=2, moe_intermediate_size=128,
+                                  first_k_dense_replace=1, scoring_func="sigmoid", n_group=1, topk_group=1, norm_topk_prob=True, routed_scaling_factor=2.5, router_bias=True, rope_theta=10000.0,
+                                  rms_eps=1e-5, index_topk=24, index_head_dim=32, index_n_heads=4, num_mtp_layers=1)
+PRESETS["small-glm"] = replace(PRESETS["tiny-glm"], vocab_size=4096, hidden_size=1024, num_q_heads=16, num_kv_heads=16, head_dim=256, intermediate_size=2048, q_lora_rank=512, kv_lora_rank=512,
+                               qk_nope_head_dim=192, qk_rope_head_dim=64, v_head_dim=256, n_routed_experts=16, num_experts_per_tok=4, moe_intermediate_size=256, index_topk=256, index_head_dim=128,
+                               index_n_heads=32, max_position=8192)
+# GLM-5 (zai-org/GLM-5): 78 layers, 256 routed experts, MLA with 192 + 64 query dims and 256 value dims, 32-head indexer keeping 2048 keys
+PRESETS["glm-5"] = replace(PRESETS["small-glm"], vocab_size=154880, hidden_size=6144, num_layers=78, num_q_heads=64, num_kv_heads=64, intermediate_size=12288, q_lora_rank=2048, n_routed_experts=256,
+                           num_experts_per_tok=8, moe_intermediate_size=2048, first_k_dense_replace=3, index_topk=2048, max_position=202752, rope_theta=1e6, expert_quant="fp8_block128")
 for _name in ("tiny-dsv2", "small-dsv2", "dsv2-lite"):
     if _name in PRESETS:
         PRESETS[_name + "-fp8"] = replace(PRESETS[_name], expert_quant="fp8_block128")
@@ -175,6 +189,8 @@ def detect_family(cfg: dict) -> str:
         return "qwen35"
     if mt == "deepseek_v2" or "DeepseekV2" in archs:
         return "deepseek_v2"
+    if mt == "glm_moe_dsa" or "GlmMoeDsa" in archs:
+        return "glm_dsa"
     if mt in ("kimi_k2", "deepseek_v3", "kimi_k25") or "DeepseekV3" in archs or "Kimi" in archs:
         return "kimi_k2"
     raise ValueError(f"no model line recognises model_type={mt!r} architectures={archs!r}")
@@ -241,7 +257,7 @@ def from_hf(cfg: dict, model_dir: Optional[str] = None) -> ModelConfig:
         qk_rope_head_dim=cfg["qk_rope_head_dim"],
         v_head_dim=cfg["v_head_dim"],
         head_dim=cfg["qk_nope_head_dim"] + cfg["qk_rope_head_dim"],
-        rope_theta=cfg.get("rope_theta", 10000.0),
+        rope_theta=cfg.get("rope_theta") or (cfg.get("rope_parameters") or {}).get("rope_theta", 10000.0),
         rope_scaling=cfg.get("rope_scaling"),
         n_routed_experts=cfg.get("n_routed_experts", 0),
         n_shared_experts=cfg.get("n_shared_experts", 0),
@@ -263,6 +279,11 @@ def from_hf(cfg: dict, model_dir: Optional[str] = None) -> ModelConfig:
     mla.update(expert_quant=quant)
     if family == "kimi_k2":
         mla.update(router_bias=True, num_mtp_layers=cfg.get("num_nextn_predict_layers", 0))
+    if family == "glm_dsa":
+        types = cfg.get("mlp_layer_types")
+        dense = cfg.get("first_k_dense_replace", 3) if types is None else next((i for i, t in enumerate(types) if t == "sparse"), len(types))
+        mla.update(router_bias=True, scoring_func="sigmoid", first_k_dense_replace=dense, num_mtp_layers=cfg.get("num_nextn_predict_layers", 0),
+                   index_topk=cfg.get("index_topk", 2048), index_head_dim=cfg.get("index_head_dim", 128), index_n_heads=cfg.get("index_n_heads", 32))
     return ModelConfig(**common, **mla)
 
 

@@ -46,6 +46,10 @@ def default_source(cfg: ModelConfig, seed: int = 0, dtype=torch.bfloat16):
     from ..models import registry
 
     shapes = registry.shapes_for(cfg)
+    if cfg.is_moe:
+        from ..models.mla_moe import _QuantRandomSource
+
+        return _QuantRandomSource(shapes, seed=seed, dtype=dtype)
     return RandomSource(shapes, seed=seed, dtype=dtype)
 
 

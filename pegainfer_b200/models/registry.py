@@ -28,7 +28,13 @@ def _mla_moe(cfg, **kw):
     return MlaMoeModel(cfg, **kw)
 
 
-BUILDERS = {"qwen3": _qwen3, "qwen35": _qwen35, "deepseek_v2": _mla_moe, "kimi_k2": _mla_moe}
+def _glm_dsa(cfg, **kw):
+    from .glm_dsa import GlmDsaModel
+
+    return GlmDsaModel(cfg, **kw)
+
+
+BUILDERS = {"glm_dsa": _glm_dsa, "qwen3": _qwen3, "qwen35": _qwen35, "deepseek_v2": _mla_moe, "kimi_k2": _mla_moe}
 
 
 def build(cfg: ModelConfig, **kw):
@@ -39,9 +45,20 @@ def build(cfg: ModelConfig, **kw):
 
 def shapes_for(cfg: ModelConfig) -> dict:
     """Full (unsharded) tensor shapes of a model family that has no entry in ``loader.export``."""
+    if cfg.family == "glm_dsa":
+        from .glm_dsa import glm_dsa_shapes
+
+        return glm_dsa_shapes(cfg)
     raise ValueError(f"no tensor-shape table for family {cfg.family!r}")
 
 
 def hf_config_extras(cfg: ModelConfig) -> dict:
     """Family-specific ``config.json`` keys for ``loader.export.to_hf_config``."""
+    if cfg.family == "glm_dsa":
+        return dict(model_type="glm_moe_dsa", architectures=["GlmMoeDsaForCausalLM"], q_lora_rank=cfg.q_lora_rank, kv_lora_rank=cfg.kv_lora_rank, qk_nope_head_dim=cfg.qk_nope_head_dim,
+                    qk_rope_head_dim=cfg.qk_rope_head_dim, v_head_dim=cfg.v_head_dim, n_routed_experts=cfg.n_routed_experts, n_shared_experts=cfg.n_shared_experts,
+                    num_experts_per_tok=cfg.num_experts_per_tok, moe_intermediate_size=cfg.moe_intermediate_size, n_group=cfg.n_group, topk_group=cfg.topk_group,
+                    norm_topk_prob=cfg.norm_topk_prob, routed_scaling_factor=cfg.routed_scaling_factor, num_nextn_predict_layers=cfg.num_mtp_layers,
+                    mlp_layer_types=["dense" if i < cfg.first_k_dense_replace else "sparse" for i in range(cfg.num_layers)], first_k_dense_replace=cfg.first_k_dense_replace,
+                    index_topk=cfg.index_topk, index_head_dim=cfg.index_head_dim, index_n_heads=cfg.index_n_heads, rope_parameters=dict(rope_theta=cfg.rope_theta, rope_type="default"))
     return {}

@@ -503,6 +503,91 @@ def mla_attention(q, w_uk, w_uv, latent_layer, meta: AttnMeta, scale, kv_lora):
     return out.reshape(t, h * v)
 
 
+# ----------------------------------------------------------------------------------
+# Sparse-attention indexer (GLM-5 / DeepSeek-V3.2 style): a light multi-head scorer picks, for every
+# query, the keys the main attention may look at
+# ----------------------------------------------------------------------------------
+def dsa_index_append(k, norm_w, norm_b, cos, sin, meta: AttnMeta, index_layer, eps=1e-6):
+    """Index keys ``[T, D]``: LayerNorm (weight and bias), half-split rotation of the leading
+    ``2 * cos.shape[-1]`` dims, then append to the paged index cache ``[pages, page_size, D]``."""
+    kf = torch.nn.functional.layer_norm(k.float(), (k.shape[-1],), norm_w.float(), norm_b.float(), eps).to(k.dtype)
+    pos = meta.positions.long()
+    kf = _rope_half(kf.unsqueeze(1), cos[pos], sin[pos]).squeeze(1)
+    ps = meta.page_size
+    slots = meta.slot_mapping.long()
+    index_layer[slots // ps, slots % ps] = kf
+
+
+def dsa_rope_q(q, cos, sin, meta: AttnMeta):
+    """Index queries ``[T, H, D]``: half-split rotation of the leading rope dims."""
+    pos = meta.positions.long()
+    return _rope_half(q, cos[pos], sin[pos])
+
+
+def dsa_index_scores(q, w, index_layer, meta: AttnMeta):
+    """``score[t, j] = sum_h w[t, h] * relu(q[t, h] . k[j])`` over the keys of row ``t``'s sequence
+    that are not in its future; everything else is ``-inf``.  ``q`` [T, H, D] (rotated), ``w`` [T, H]
+    f32 (head weights with every constant factor folded in).  Returns ``[T, max_kv_len]`` f32."""
+    t = q.shape[0]
+    qi = meta.h_q_indptr if meta.h_q_indptr is not None else meta.q_indptr.tolist()
+    kl = meta.h_kv_lens if meta.h_kv_lens is not None else meta.kv_lens.tolist()
+    width = max([kl[b] for b in range(meta.num_seqs)] + [1])
+    out = torch.full((t, width), float("-inf"), dtype=torch.float32, device=q.device)
+    ps = meta.page_size
+    for b in range(meta.num_seqs):
+        q0, q1 = qi[b], qi[b + 1]
+        if q1 == q0 or kl[b] == 0:
+            continue
+        pages = meta.block_table[b, : (kl[b] + ps - 1) // ps].long()
+        keys = index_layer[pages].reshape(-1, index_layer.shape[-1])[: kl[b]].float()
+        s = torch.relu(torch.einsum("qhd,kd->qhk", q[q0:q1].float(), keys))
+        sc = torch.einsum("qhk,qh->qk", s, w[q0:q1].float())
+        n = q1 - q0
+        qpos = torch.arange(kl[b] - n, kl[b], device=q.device).view(n, 1)
+        kpos = torch.arange(kl[b], device=q.device).view(1, -1)
+        out[q0:q1, : kl[b]] = sc.masked_fill(kpos > qpos, float("-inf"))
+    return out
+
+
+def dsa_topk(scores, k: int):
+    """Positions of each row's ``k`` best finite scores, ``-1`` where a row has fewer; among equal scores the
+    earlier position wins (``relu`` makes exact ties common), so the choice does not depend on how wide the
+    score matrix of a step happens to be.  ``[T, min(k, width)]`` int32."""
+    k = min(k, scores.shape[1])
+    val, idx = torch.sort(scores, dim=-1, descending=True, stable=True)
+    val, idx = val[:, :k], idx[:, :k]
+    return torch.where(torch.isfinite(val), idx, torch.full_like(idx, -1)).to(torch.int32)
+
+
+def mla_attention_sparse(q, w_uk, w_uv, latent_layer, meta: AttnMeta, scale, kv_lora, select):
+    """``mla_attention`` restricted, per query row, to the key positions listed in ``select`` [T, k]
+    (``-1`` entries are skipped; the listed positions are already causal)."""
+    t, h, _ = q.shape
+    nope, v = w_uk.shape[1], w_uv.shape[1]
+    q_abs = torch.einsum("thn,hnc->thc", q[..., :nope].float(), w_uk.float()).to(q.dtype)
+    q_pe = q[..., nope:]
+    out = torch.zeros(t, h, v, dtype=q.dtype, device=q.device)
+    qi = meta.h_q_indptr if meta.h_q_indptr is not None else meta.q_indptr.tolist()
+    kl = meta.h_kv_lens if meta.h_kv_lens is not None else meta.kv_lens.tolist()
+    ps = meta.page_size
+    for b in range(meta.num_seqs):
+        q0, q1 = qi[b], qi[b + 1]
+        if q1 == q0 or kl[b] == 0:
+            continue
+        pages = meta.block_table[b, : (kl[b] + ps - 1) // ps].long()
+        lat = latent_layer[pages].reshape(-1, latent_layer.shape[-1])[: kl[b]].float()
+        ckv, kpe = lat[:, :kv_lora], lat[:, kv_lora:]
+        s = (torch.einsum("qhc,kc->hqk", q_abs[q0:q1].float(), ckv) + torch.einsum("qhr,kr->hqk", q_pe[q0:q1].float(), kpe)) * scale
+        sel = select[q0:q1].long()
+        keep = torch.zeros(q1 - q0, kl[b] + 1, dtype=torch.bool, device=q.device)
+        keep.scatter_(1, torch.where(sel < 0, torch.full_like(sel, kl[b]), sel), True)
+        s = s.masked_fill(~keep[:, : kl[b]].unsqueeze(0), float("-inf"))
+        p = torch.softmax(s, -1)
+        lo = torch.einsum("hqk,kc->qhc", p, ckv).to(q.dtype)
+        out[q0:q1] = torch.einsum("qhc,hvc->qhv", lo.float(), w_uv.float()).to(q.dtype)
+    return out.reshape(t, h * v)
+
+
 def moe_experts_int4(x, ids, weights, w13_packed, w13_scale, w2_packed, w2_scale, expert_offset=0, group=32):
     """``moe_experts`` over INT4 group-quantised weights (dequantised per expert)."""
     t, h = x.shape

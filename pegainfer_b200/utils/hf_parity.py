@@ -137,7 +137,7 @@ def hf_prompt_logits(model_dir: str, tokens: Sequence[int], dtype=torch.float32)
             m = _qwen35_text_model(model_dir, cfg, dtype)
         else:
             path = _as_deepseek_v3_dir(model_dir, cfg, tmp) if cfg.get("model_type") == "kimi_k2" else model_dir
-            m = AutoModelForCausalLM.from_pretrained(path, dtype=dtype)
+            m = AutoModelForCausalLM.from_pretrained(path, dtype=dtype, attn_implementation="eager")  # an explicit causal mask in every family
     m.eval()
     if cfg.get("model_type") == "deepseek_v2":
         # transformers' own DeepSeek-V2 leaves the YaRN mscale^2 off the softmax scale; DeepSeek's

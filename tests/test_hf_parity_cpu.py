@@ -15,7 +15,7 @@ from pegainfer_b200.utils.hf_parity import compare
 pytest.importorskip("transformers")
 
 
-@pytest.mark.parametrize("name,atol", [("tiny-qwen3", 2e-5), ("tiny-qwen35", 2e-5), ("tiny-dsv2", 2e-5), ("tiny-kimi", 5e-4)])
+@pytest.mark.parametrize("name,atol", [("tiny-qwen3", 2e-5), ("tiny-qwen35", 2e-5), ("tiny-dsv2", 2e-5), ("tiny-kimi", 5e-4), ("tiny-glm", 5e-4)])
 def test_prompt_logits_match_hugging_face(name, atol):
     cfg = preset(name)
     g = torch.Generator().manual_seed(3)

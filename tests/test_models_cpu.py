@@ -237,3 +237,13 @@ def test_eagle3_chain_drafter_is_lossless():
     assert s.draft_len == 3 and s.rounds > 0 and s.draft.aux_layers == (1, 3, 4)
     c = eng.scheduler._metrics.spec_decode
     assert c.num_draft_tokens == 3 * c.num_drafts
+
+
+def test_glm_sparse_indexer_chunking_invariance_and_mtp():
+    """tiny-glm keeps 24 keys per query: prompts of 40+ tokens run the indexer and the sparse latent attention.
+    Chunked, batched and one-at-a-time generation must agree, and the MTP head must stay lossless."""
+    _chunking_invariance("tiny-glm")
+    ps = prompts_for(2, 33, seed=12)
+    plain, _ = gen("tiny-glm", ps, 10)
+    spec, eng = gen("tiny-glm", ps, 10, spec_method="mtp")
+    assert spec == plain and eng.scheduler._metrics.spec_decode.num_drafts > 0
