@@ -77,6 +77,18 @@ int pg_qk_norm_rope_append(const void* qkv, long long ld, const void* q_w, const
                            int rot, int page_size, long long num_pages, int max_pos, int gated, int offset, float eps, void* status,
                            cudaStream_t stream);
 
+// ---- sparse-attention indexer (dsa.cu) ----------------------------------------------------
+int pg_dsa_k_append(const void* k, long long ld, const void* norm_w, const void* norm_b, const void* cos, const void* sin, const void* positions,
+                    const void* slots, void* cache, int tokens, int d, int rope, int max_pos, long long num_slots, float eps, void* status,
+                    cudaStream_t stream);
+int pg_dsa_q_rope(void* q, const void* cos, const void* sin, const void* positions, int tokens, int heads, int d, int rope, int max_pos, cudaStream_t stream);
+int pg_dsa_scores(const void* q, const void* w, const void* cache, const void* unit_seq, const void* q_indptr, const void* kv_lens, const void* table,
+                  int table_stride, int page_size, long long num_pages, int tokens, int heads, int d, void* scores, int width, void* status,
+                  cudaStream_t stream);
+int pg_dsa_topk(const void* scores, int rows, int width, int k, void* out, void* counts, cudaStream_t stream);
+int pg_dsa_gather(const void* latent, const void* select, int k, const void* unit_seq, const void* table, int table_stride, int page_size,
+                  long long num_pages, int row_bytes, int rows, void* out, int slots_per_row, void* status, cudaStream_t stream);
+
 // ---- multi-head latent attention (mla.cu) ------------------------------------------
 int pg_mla_append(const void* kv_a, long long ld, const void* norm_w, const void* cos, const void* sin, const void* positions, const void* slots,
                   void* latent, int tokens, int c, int rope, int max_pos, long long num_slots, float eps, void* status, cudaStream_t stream);

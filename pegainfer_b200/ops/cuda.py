@@ -923,6 +923,99 @@ def mla_attention(q: "_MlaQ", w_uk, w_uv, latent_layer, meta: AttnMeta, scale, k
     return out
 
 
+# ---- sparse-attention indexer (csrc/dsa.cu) ---------------------------------------------------------
+def dsa_index_append(k, norm_w, norm_b, cos, sin, meta: AttnMeta, index_layer, eps=1e-6):
+    _bf16(k)
+    assert k.stride(-1) == 1 and index_layer.is_contiguous() and norm_w.dtype == torch.float32 and norm_b.dtype == torch.float32
+    t, d = k.shape
+    c = ctx(k.device)
+    num_slots = index_layer.shape[0] * index_layer.shape[1]
+    rc = lib().pg_dsa_k_append(_ptr(k), _ll(k.stride(0)), _ptr(norm_w), _ptr(norm_b), _ptr(cos), _ptr(sin), _ptr(meta.positions), _ptr(meta.slot_mapping), _ptr(index_layer),
+                               _ci(t), _ci(d), _ci(cos.shape[-1] * 2), _ci(cos.shape[0]), _ll(num_slots), _cf(eps), _ptr(c.status), _stream())
+    _check(rc, c)
+
+
+def dsa_rope_q(q, cos, sin, meta: AttnMeta):
+    _bf16(q)
+    q = q.contiguous()
+    t, h, d = q.shape
+    _check(lib().pg_dsa_q_rope(_ptr(q), _ptr(cos), _ptr(sin), _ptr(meta.positions), _ci(t), _ci(h), _ci(d), _ci(cos.shape[-1] * 2), _ci(cos.shape[0]), _stream()), ctx(q.device))
+    return q
+
+
+def _unit_seq(meta: AttnMeta, device):
+    """Sequence index of every query row."""
+    if meta.decode_only:
+        return meta.q_indptr  # one row per sequence: q_indptr[i] == i
+    qi = meta.h_q_indptr if meta.h_q_indptr is not None else meta.q_indptr.tolist()
+    seq_of = []
+    for b in range(meta.num_seqs):
+        seq_of.extend([b] * (qi[b + 1] - qi[b]))
+    return torch.tensor(seq_of, dtype=torch.int32, device=device)
+
+
+def dsa_index_scores(q, w, index_layer, meta: AttnMeta):
+    """``[T, width]`` f32 with ``width`` = the step's longest sequence rounded up to the 128-key tile."""
+    _bf16(q)
+    t, h, d = q.shape
+    assert q.is_contiguous() and w.dtype == torch.float32 and w.is_contiguous() and index_layer.is_contiguous()
+    dev = q.device
+    c = ctx(dev)
+    width = (max(meta.max_kv_len, 1) + 127) // 128 * 128
+    scores = torch.empty((t, width), dtype=torch.float32, device=dev)
+    rc = lib().pg_dsa_scores(_ptr(q), _ptr(w), _ptr(index_layer), _ptr(_unit_seq(meta, dev)), _ptr(meta.q_indptr), _ptr(meta.kv_lens), _ptr(meta.block_table),
+                             _ci(meta.block_table.stride(0)), _ci(index_layer.shape[1]), _ll(index_layer.shape[0]), _ci(t), _ci(h), _ci(d), _ptr(scores), _ci(width),
+                             _ptr(c.status), _stream())
+    _check(rc, c)
+    return scores
+
+
+def dsa_topk(scores, k: int):
+    """``[T, k]`` int32 positions in increasing order, ``-1`` padded; the number of live entries per row rides
+    along as ``._pg_counts``."""
+    t, width = scores.shape
+    assert scores.is_contiguous() and scores.dtype == torch.float32
+    k = min(k, width)
+    out = torch.empty((t, k), dtype=torch.int32, device=scores.device)
+    counts = torch.empty((t,), dtype=torch.int32, device=scores.device)
+    _check(lib().pg_dsa_topk(_ptr(scores), _ci(t), _ci(width), _ci(k), _ptr(out), _ptr(counts), _stream()), ctx(scores.device))
+    out._pg_counts = counts
+    return out
+
+
+def mla_attention_sparse(q: "_MlaQ", w_uk, w_uv, latent_layer, meta: AttnMeta, scale, kv_lora, select):
+    """Latent attention over the selected keys only: the chosen latent rows of every query are copied into pages
+    of a scratch cache (row ``t`` owns pages ``t * kp .. (t + 1) * kp``) and the dense kernel runs with every
+    query as a sequence of its own.  Key order does not matter to attention, and the rotary phase is part of
+    the cached key.  Long steps go through in slices so that the scratch stays under 1 GiB."""
+    t, k = select.shape
+    dev = latent_layer.device
+    c = ctx(dev)
+    ps, width = latent_layer.shape[1], latent_layer.shape[2]
+    kp = (k + ps - 1) // ps
+    counts = getattr(select, "_pg_counts", None)
+    if counts is None:
+        counts = (select >= 0).sum(1, dtype=torch.int32)
+    unit = _unit_seq(meta, dev)
+    per = max(1, min(t, (1 << 30) // (kp * ps * width * 2)))
+    outs = []
+    for r0 in range(0, t, per):
+        n = min(per, t - r0)
+        scratch = torch.empty((n * kp, ps, width), dtype=latent_layer.dtype, device=dev)
+        rc = lib().pg_dsa_gather(_ptr(latent_layer), _ptr(select[r0:]), _ci(k), _ptr(unit[r0:]), _ptr(meta.block_table), _ci(meta.block_table.stride(0)), _ci(ps),
+                                 _ll(latent_layer.shape[0]), _ci(width * 2), _ci(n), _ptr(scratch), _ci(kp * ps), _ptr(c.status), _stream())
+        _check(rc, c)
+        ar = torch.arange(n * kp + 1, dtype=torch.int32, device=dev)
+        sub = AttnMeta(q_indptr=ar[: n + 1], kv_lens=counts[r0 : r0 + n], block_table=ar[: n * kp].view(n, kp), slot_mapping=None, positions=None, page_size=ps, num_seqs=n,
+                       num_tokens=n, max_q_len=1, max_kv_len=k, decode_only=True)
+        if n == t:
+            subq = q
+        else:
+            subq = _MlaQ(q.nope_hm[:, r0 : r0 + n].contiguous(), q.pe[r0 : r0 + n], n, q.heads, q.nope)
+        outs.append(mla_attention(subq, w_uk, w_uv, scratch, sub, scale, kv_lora))
+    return outs[0] if len(outs) == 1 else torch.cat(outs)
+
+
 def lora_delta_(y, x, A, B, scale, slots):
     """In place: ``y[t] += scale[s] * B[s] @ (A[s] @ x[t])`` with ``s = slots[t]`` (negative = skip)."""
     _bf16(x)

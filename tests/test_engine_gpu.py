@@ -96,7 +96,7 @@ def _family_engine(name, cuda_graph, **kw):
     return build_engine(ecfg, preset(name), device="cuda:0", dtype=torch.bfloat16)
 
 
-def _family_logits_close(name, mean_tol=0.03, max_tol=0.5):
+def _family_logits_close(name, mean_tol=0.03, max_tol=0.5, lens=(50, 17, 33)):
     """Kernel path vs PyTorch library path of the same weights, one ragged prefill step."""
     from pegainfer_b200.kv.request_kv import KvView
     from pegainfer_b200.sched.executor import SeqStep, build_meta
@@ -104,7 +104,7 @@ def _family_logits_close(name, mean_tol=0.03, max_tol=0.5):
     eng = _family_engine(name, False)
     try:
         g = torch.Generator().manual_seed(2)
-        ps = [torch.randint(0, 4096, (n,), generator=g).tolist() for n in (50, 17, 33)]
+        ps = [torch.randint(0, 4096, (n,), generator=g).tolist() for n in lens]
         seqs, page, nxt = [], 16, 1
         for i, p in enumerate(ps):
             npg = (len(p) + page - 1) // page
@@ -139,6 +139,27 @@ def test_kimi_shape_int4_kernels_vs_library():
 
 def test_dsv2_shape_fp8_block_scaled_experts_kernels_vs_library():
     _family_logits_close("small-dsv2-fp8")
+
+
+def test_glm_dense_and_sparse_indexer_kernels_vs_library():
+    """small-glm keeps 256 keys per query: short prompts take the dense latent path, prompts past 256 tokens run the
+    tcgen05 index scores, the radix top-k and the gathered sparse attention."""
+    _family_logits_close("small-glm")
+    _family_logits_close("small-glm", lens=(300, 90, 420))
+
+
+def test_glm_generate_graph_equals_eager_past_the_selection_width():
+    e1, e2 = _family_engine("small-glm", False), _family_engine("small-glm", True)
+    try:
+        g = torch.Generator().manual_seed(8)
+        ps = [torch.randint(0, 4096, (n,), generator=g).tolist() for n in (270, 40)]
+        o1 = e1.generate(ps, max_tokens=8)
+        o2 = e2.generate(ps, max_tokens=8)
+        assert [x[0] for x in o1] == [x[0] for x in o2]
+        assert e2.executor._graphs.replays > 0
+    finally:
+        e1.shutdown()
+        e2.shutdown()
 
 
 def test_qwen35_hybrid_kernels_vs_library():
