@@ -77,6 +77,12 @@ int pg_qk_norm_rope_append(const void* qkv, long long ld, const void* q_w, const
                            int rot, int page_size, long long num_pages, int max_pos, int gated, int offset, float eps, void* status,
                            cudaStream_t stream);
 
+// ---- block-scaled FP8 GEMM on tcgen05 kind::f8f6f4 (gemm_fp8_sm100.cu) --------------------
+long long pg_gemm_fp8_ws_bytes(int T, int M);
+int pg_gemm_fp8_block(const void* xq, long long ldx, const void* x_scale, long long ldxs, const void* wq, long long ldw, const void* w_scale, void* y,
+                      long long ldy, int T, int M, int K, void* ws, long long ws_bytes, void* status, cudaStream_t stream);
+int pg_quant_fp8_1x128(const void* x, long long ldx, int T, int K, void* xq, long long ldq, void* scale, long long lds, cudaStream_t stream);
+
 // ---- sparse-attention indexer (dsa.cu) ----------------------------------------------------
 int pg_dsa_k_append(const void* k, long long ld, const void* norm_w, const void* norm_b, const void* cos, const void* sin, const void* positions,
                     const void* slots, void* cache, int tokens, int d, int rope, int max_pos, long long num_slots, float eps, void* status,

@@ -130,6 +130,9 @@ def load():
     # PEGAINFER_LIB_PATH loads another build of the library as is (A/B timing of kernel changes)
     _lib = ctypes.CDLL(os.environ.get("PEGAINFER_LIB_PATH") or LIB_PATH)
     _lib.pg_last_error.restype = ctypes.c_char_p
+    for name in ("pg_gemm_fp8_ws_bytes", "pg_decode_chain_ws_bytes", "pg_argmax_scratch_bytes"):
+        if hasattr(_lib, name):
+            getattr(_lib, name).restype = ctypes.c_longlong
     return _lib
 
 

@@ -923,6 +923,47 @@ def mla_attention(q: "_MlaQ", w_uk, w_uv, latent_layer, meta: AttnMeta, scale, k
     return out
 
 
+# ---- block-scaled FP8 GEMM (csrc/gemm_fp8_sm100.cu) -------------------------------------------------
+def quant_fp8_1x128(x):
+    """bf16 ``[T, K]`` -> (e4m3 ``[T, K]``, f32 scales ``[K / 128, T padded to 64]``): one scale per token and 128-wide k group."""
+    _bf16(x)
+    assert x.stride(-1) == 1
+    t, k = x.shape
+    xq = torch.empty((t, k), dtype=torch.float8_e4m3fn, device=x.device)
+    lds = (t + 63) // 64 * 64
+    scale = torch.zeros((k // 128, lds), dtype=torch.float32, device=x.device)
+    _check(lib().pg_quant_fp8_1x128(_ptr(x), _ll(x.stride(0)), _ci(t), _ci(k), _ptr(xq), _ll(k), _ptr(scale), _ll(lds), _stream()), ctx(x.device))
+    return xq, scale
+
+
+_FP8_WS: dict = {}
+
+
+def linear_fp8_block(x, wq, w_scale, xq=None, x_scale=None):
+    """``x [T, K]`` bf16 (quantised here per token and k group, unless ``xq`` / ``x_scale`` are given) times the
+    block-scaled e4m3 weight ``wq [M, K]`` with ``w_scale [M / 128, K / 128]``; bf16 ``[T, M]``.  Steps of more
+    than 64 rows run in slices of 64 (the kernel is the decode-shape one)."""
+    if xq is None:
+        xq, x_scale = quant_fp8_1x128(x)
+    t, k = xq.shape
+    m = wq.shape[0]
+    assert wq.is_contiguous() and w_scale.is_contiguous() and w_scale.dtype == torch.float32 and w_scale.shape == (m // 128, k // 128)
+    dev = xq.device
+    c = ctx(dev)
+    y = torch.empty((t, m), dtype=torch.bfloat16, device=dev)
+    ws = _FP8_WS.get(dev.index)
+    need = lib().pg_gemm_fp8_ws_bytes(_ci(min(t, 64)), _ci(m))
+    if ws is None or ws.numel() < need:
+        ws = torch.empty(int(need), dtype=torch.uint8, device=dev)
+        _FP8_WS[dev.index] = ws
+    for t0 in range(0, t, 64):
+        n = min(64, t - t0)
+        rc = lib().pg_gemm_fp8_block(_ptr(xq[t0:]), _ll(k), _ptr(x_scale[:, t0:]), _ll(x_scale.stride(0)), _ptr(wq), _ll(k), _ptr(w_scale), _ptr(y[t0:]), _ll(m),
+                                     _ci(n), _ci(m), _ci(k), _ptr(ws), _ll(ws.numel()), _ptr(c.status), _stream())
+        _check(rc, c, 3)
+    return y
+
+
 # ---- sparse-attention indexer (csrc/dsa.cu) ---------------------------------------------------------
 def dsa_index_append(k, norm_w, norm_b, cos, sin, meta: AttnMeta, index_layer, eps=1e-6):
     _bf16(k)

@@ -503,6 +503,27 @@ def mla_attention(q, w_uk, w_uv, latent_layer, meta: AttnMeta, scale, kv_lora):
     return out.reshape(t, h * v)
 
 
+def quant_fp8_1x128(x):
+    """Per token and 128-wide k group: ``scale = amax / 448``, values rounded to e4m3.  Returns the e4m3 matrix and
+    the f32 scales as ``[K / 128, T]`` (pegainfer-kernels/csrc/glm52/glm52_moe_quant.cu, plain float scales)."""
+    t, k = x.shape
+    g = x.float().view(t, k // 128, 128)
+    scale = (g.abs().amax(-1) / 448.0).clamp_min(1e-10 / 448.0)
+    q = (g / scale.unsqueeze(-1)).clamp_(-448.0, 448.0).to(torch.float8_e4m3fn).view(t, k)
+    return q, scale.t().contiguous()
+
+
+def linear_fp8_block(x, wq, w_scale, xq=None, x_scale=None):
+    """``Y = dequant(Xq) . dequant(Wq)^T`` with 1 x 128 activation groups and 128 x 128 weight blocks, accumulated in f32."""
+    if xq is None:
+        xq, x_scale = quant_fp8_1x128(x)
+    t, k = xq.shape
+    xf = xq.float().view(t, k // 128, 128) * x_scale[:, :t].t().unsqueeze(-1)
+    m = wq.shape[0]
+    wf = wq.float() * w_scale.float().repeat_interleave(128, 0)[:m].repeat_interleave(128, 1)[:, :k]
+    return (xf.view(t, k) @ wf.t()).to(torch.bfloat16)
+
+
 # ----------------------------------------------------------------------------------
 # Sparse-attention indexer (GLM-5 / DeepSeek-V3.2 style): a light multi-head scorer picks, for every
 # query, the keys the main attention may look at

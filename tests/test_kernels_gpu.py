@@ -779,3 +779,31 @@ def test_dsa_indexer_kernels_match_reference():
     err = (out_k.float() - out_r.float()).abs()
     assert err.max().item() < 0.03 and err.mean().item() < 0.003, (err.max().item(), err.mean().item())
     assert K.read_status(dev) == 0
+
+
+@pytest.mark.parametrize("t,m,k", [(1, 256, 512), (7, 1024, 2048), (64, 4096, 4096), (100, 2048, 7168), (16, 12288, 4096)])
+def test_fp8_block_scaled_gemm_matches_reference(t, m, k):
+    """tcgen05 kind::f8f6f4 GEMM with per-k-group promotion against the dequantised f32 product of the same e4m3 data."""
+    K = cu()
+    g = torch.Generator(device=DEV).manual_seed(t + m)
+    x = (torch.randn(t, k, device=DEV, generator=g) * (1 + torch.rand(t, 1, device=DEV, generator=g) * 3)).to(torch.bfloat16)
+    w = torch.randn(m, k, device=DEV, generator=g) * 0.05
+    tensors = {"w": w.cpu()}
+    from pegainfer_b200.loader.export import quantize_dense_to_fp8
+
+    quantize_dense_to_fp8(tensors, ["w"])
+    wq, ws = tensors["w"].to(DEV).contiguous(), tensors["w_scale_inv"].to(DEV).contiguous()
+    xq_k, xs_k = K.quant_fp8_1x128(x)
+    xq_r, xs_r = R.quant_fp8_1x128(x)
+    torch.cuda.synchronize()
+    assert torch.equal(xs_k[:, :t], xs_r) or (xs_k[:, :t] - xs_r).abs().max().item() < 1e-6 * xs_r.abs().max().item()
+    assert (xq_k.float() - xq_r.float()).abs().max().item() <= 32.0  # at most one e4m3 step at the top of the range
+    y = K.linear_fp8_block(x, wq, ws, xq_k, xs_k)
+    ref = R.linear_fp8_block(x, wq, ws, xq_k, xs_k)
+    torch.cuda.synchronize()
+    bf16_close(y, ref, rel=2 ** -6, abs_=2e-2)
+    # and the quantised product stays close to the bf16 one
+    full = (x.float() @ R.dequant_fp8_block(wq, ws).float().t())
+    rel = (y.float() - full).norm() / full.norm()
+    assert rel.item() < 0.05, rel.item()
+    status_clean()
