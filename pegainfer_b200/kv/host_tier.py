@@ -61,23 +61,56 @@ class TierStats:
     evictions: int = 0
 
 
+class TierStore:
+    """The slab of a KV tier and its hash index, as an object of its own so that two engines can share it:
+    a prefill engine publishes the blocks it seals, a decode engine finds them by hash (prefill / decode
+    disaggregation inside one process).  ``device`` is where the slab lives: pinned host memory (``cpu``), or
+    the decode engine's GPU, in which case a published block crosses NVLink once, as a peer copy from the
+    prefill GPU, and the decode engine's restore is a local copy.  ``busy`` counts the loads reading a slot:
+    such an entry is never chosen for eviction."""
+
+    def __init__(self, block_shape, dtype, num_slots: int, device="cpu", pin: bool = False):
+        import threading
+
+        self.lock = threading.RLock()
+        self.slab = torch.empty((num_slots,) + tuple(block_shape), dtype=dtype, device=device)
+        if pin and torch.device(device).type == "cpu":
+            self.slab = self.slab.pin_memory()
+        self.by_hash: "OrderedDict[bytes, int]" = OrderedDict()  # LRU: oldest first
+        self.free_slots = list(range(num_slots - 1, -1, -1))
+        self.busy: dict = {}
+        self.num_slots = num_slots
+
+    @classmethod
+    def for_kv(cls, kv, nbytes: int, device="cpu") -> "TierStore":
+        one = kv.data[:, 0]
+        slots = max(1, nbytes // (one.numel() * one.element_size()))
+        return cls(tuple(one.shape), kv.data.dtype, slots, device, pin=kv.data.device.type == "cuda")
+
+
 class HostTier:
     def __init__(self, kv, pool, host_bytes: int, reserve_floor: int = 2, l1_retention_disabled: bool = False, load_deadline_s: float = 15.0,
-                 disk_dir: Optional[str] = None, disk_bytes: int = 0):
+                 disk_dir: Optional[str] = None, disk_bytes: int = 0, store: Optional[TierStore] = None, flush_on_finish: bool = False):
         self.kv, self.pool = kv, pool
         self.data = kv.data
         self.device = self.data.device
         one = self.data[:, 0]
         self.block_shape = tuple(one.shape)
         self.block_bytes = one.numel() * one.element_size()
-        self.num_slots = max(1, host_bytes // self.block_bytes)
-        self.slab = torch.empty((self.num_slots,) + self.block_shape, dtype=self.data.dtype)
         self.cuda = self.device.type == "cuda"
+        if store is None:
+            store = TierStore(self.block_shape, self.data.dtype, max(1, host_bytes // self.block_bytes), "cpu", pin=self.cuda)
+        elif tuple(store.slab.shape[1:]) != self.block_shape or store.slab.dtype != self.data.dtype:
+            raise ValueError("the shared KV store holds blocks of another shape: both engines must run the same model and page size")
+        self.store = store
+        self.lock = store.lock
+        self.num_slots = store.num_slots
+        self.slab = store.slab
         if self.cuda:
-            self.slab = self.slab.pin_memory()
             self.stream = torch.cuda.Stream(self.device)
-        self.by_hash: "OrderedDict[bytes, int]" = OrderedDict()  # LRU: oldest first
-        self.free_slots = list(range(self.num_slots - 1, -1, -1))
+        self.by_hash = store.by_hash
+        self.free_slots = store.free_slots
+        self.flush_on_finish = flush_on_finish  # a finish is reported only after the request's sealed blocks are in the store
         self.saving: list = []
         self.loading: dict = {}
         self.ready: list = []
@@ -101,7 +134,7 @@ class HostTier:
             return self.free_slots.pop()
         if self.saving:
             self.poll()  # saves that have landed become evictable entries
-        victim = next((h for h in self.by_hash if h not in protect), None)
+        victim = next((h for h in self.by_hash if h not in protect and not self.store.busy.get(h)), None)
         if victim is not None:
             h, slot = victim, self.by_hash.pop(victim)
             self.stats.evictions += 1
@@ -142,6 +175,10 @@ class HostTier:
         self.saved_upto[r.q.id] = upto
 
     def _save_block(self, bid: int, h: bytes) -> None:
+        with self.lock:
+            self._save_block_locked(bid, h)
+
+    def _save_block_locked(self, bid: int, h: bytes) -> None:
         if h in self.by_hash or any(s.h == h for s in self.saving):
             self.stats.save_skips += 1
             return
@@ -172,6 +209,10 @@ class HostTier:
 
     # -- query / load path -----------------------------------------------------------------
     def host_hit_run(self, hashes: list, start: int) -> int:
+        with self.lock:
+            return self._host_hit_run_locked(hashes, start)
+
+    def _host_hit_run_locked(self, hashes: list, start: int) -> int:
         n = 0
         run = set()
         for h in hashes[start:]:
@@ -205,20 +246,22 @@ class HostTier:
             parent = chain_hash(parent, req.prompt_tokens[i * bs : (i + 1) * bs], salt)
             hashes.append(parent)
         gpu_hit = self.pool.probe(hashes)
-        n = self.host_hit_run(hashes, gpu_hit)
-        if n == 0:
-            return False
-        blocks = self.pool.reserve(n, floor=self.reserve_floor + sched._future_blocks())
-        if blocks is None:
-            return False  # no room: recompute instead
-        self.stats.host_hits += n
-        want = hashes[gpu_hit : gpu_hit + n]
-        ev = None
-        try:
+        with self.lock:
+            n = self._host_hit_run_locked(hashes, gpu_hit)
+            if n == 0:
+                return False
+            blocks = self.pool.reserve(n, floor=self.reserve_floor + sched._future_blocks())
+            if blocks is None:
+                return False  # no room: recompute instead
+            self.stats.host_hits += n
+            want = hashes[gpu_hit : gpu_hit + n]
             slots = []
             for h in want:
                 self.by_hash.move_to_end(h)
                 slots.append(self.by_hash[h])
+                self.store.busy[h] = self.store.busy.get(h, 0) + 1  # not evictable while the copy reads it
+        ev = None
+        try:
             if self.cuda:
                 with torch.cuda.stream(self.stream):
                     for bid, slot in zip(blocks, slots):
@@ -229,6 +272,7 @@ class HostTier:
                 for bid, slot in zip(blocks, slots):
                     self.data[:, bid].copy_(self.slab[slot])
         except Exception:
+            self._unbusy(want)
             self.pool.free_unregistered_tail(blocks)
             self.stats.load_failures += 1
             return False
@@ -236,17 +280,27 @@ class HostTier:
         self.stats.loads += 1
         return True
 
+    def _unbusy(self, hashes) -> None:
+        with self.lock:
+            for h in hashes:
+                n = self.store.busy.get(h, 0) - 1
+                if n > 0:
+                    self.store.busy[h] = n
+                else:
+                    self.store.busy.pop(h, None)
+
     def poll(self, sched=None) -> None:
         # completed saves: publish hash -> slot, drop the keep-alive
         still = []
-        for s in self.saving:
-            if s.event is None or s.event.query():
-                self.by_hash[s.h] = s.slot
-                self.by_hash.move_to_end(s.h)
-                self.pool.release([s.bid])
-                self.stats.saves += 1
-            else:
-                still.append(s)
+        with self.lock:
+            for s in self.saving:
+                if s.event is None or s.event.query():
+                    self.by_hash[s.h] = s.slot
+                    self.by_hash.move_to_end(s.h)
+                    self.pool.release([s.bid])
+                    self.stats.saves += 1
+                else:
+                    still.append(s)
         self.saving = still
         # completed loads: the blocks join the prefix cache, the request may be admitted
         for rid in list(self.loading):
@@ -255,12 +309,14 @@ class HostTier:
                 if self.cuda:
                     torch.cuda.current_stream(self.device).wait_event(ld.event)
                 self.pool.commit_reserved(ld.blocks, ld.hashes, ld.parent)
+                self._unbusy(ld.hashes)
                 del self.loading[rid]
                 self.ready.append(rid)
             elif time.monotonic() - ld.started > self.load_deadline_s:
                 # give up: the reservation is returned once the copy can no longer write
                 ld.event.synchronize()
                 self.pool.free_unregistered_tail(ld.blocks)
+                self._unbusy(ld.hashes)
                 del self.loading[rid]
                 self.stats.load_failures += 1
                 self.ready.append(rid)
@@ -275,6 +331,7 @@ class HostTier:
             if ld.event is not None:
                 ld.event.synchronize()
             self.pool.free_unregistered_tail(ld.blocks)
+            self._unbusy(ld.hashes)
 
     def on_retire(self, r, sched) -> None:
         self.saved_upto.pop(r.q.id, None)
@@ -290,4 +347,5 @@ class HostTier:
         cb()
 
     def contains(self, h: bytes) -> bool:
-        return h in self.by_hash
+        with self.lock:
+            return h in self.by_hash

@@ -444,6 +444,11 @@ class ContinuousScheduler:
         if r.t_first is None:
             r.t_first = time.monotonic()
         if r.out_tokens >= req.max_tokens or r.kv.committed + 1 >= self.cfg.max_model_len:
+            if self.host_tier is not None and self.host_tier.flush_on_finish:
+                # prefill side of a disaggregated pair: the finish is the peer's cue to look the blocks up,
+                # so it goes out only once they have landed in the shared store
+                self.host_tier.on_blocks_sealed(r, self)
+                self.host_tier.flush_saves_then(lambda: None)
             ledger.finish(rid, FinishReason.LENGTH)
             self._retire(rid)
 

@@ -29,7 +29,7 @@ log = logging.getLogger("pegainfer_b200.serve")
 SHARED_FLAGS = {
     "model_path", "preset", "served_model_name", "port", "host", "cuda_graph", "precapture_graphs", "dump_graph_dot", "device_ordinal", "tp_size", "dp_size", "ep_size",
     "kv_offload", "kv_offload_host_gib", "kv_offload_disk_dir", "kv_offload_disk_gib", "no_prefix_cache", "max_prefill_tokens", "max_model_len", "num_kv_blocks", "gpu_memory_utilization",
-    "kv_cache_memory_margin_mib", "kv_page_size", "max_decode_batch", "seed", "comm", "gemm", "tokenizer",
+    "kv_cache_memory_margin_mib", "kv_page_size", "max_decode_batch", "seed", "comm", "gemm", "tokenizer", "pd_prefill_device", "pd_store",
 }
 
 
@@ -94,6 +94,8 @@ def build_parser() -> argparse.ArgumentParser:
     k.add_argument("--kv-offload-host-gib", type=float, default=4.0)
     k.add_argument("--kv-offload-disk-dir", default=None, help="third KV tier: blocks evicted from host memory are kept as files in this directory")
     k.add_argument("--kv-offload-disk-gib", type=float, default=0.0)
+    k.add_argument("--pd-prefill-device", type=int, help="prefill / decode disaggregation: run prompts on this GPU and decode on --device-ordinal; KV blocks move by content hash")
+    k.add_argument("--pd-store", choices=["peer", "host"], default="peer", help="where the handoff store lives: the decode GPU (one NVLink hop) or pinned host memory")
     k.add_argument("--max-prefill-tokens", type=int, default=1024)
     k.add_argument("--max-decode-batch", type=int, default=256)
     k.add_argument("--max-model-len", type=int)
@@ -203,6 +205,21 @@ def main(argv: Optional[list] = None) -> int:
         return launch_distributed(ecfg, mcfg, ns)
     tok_dir = None if (ns.tokenizer == "none" or not ecfg.model_path) else ecfg.model_path
     tokenizer = load_tokenizer(tok_dir, mcfg.vocab_size)  # fails early when tokenizer.json is missing
+    if ns.pd_prefill_device is not None:
+        from .engine.pd import build_pd_engine
+
+        if ecfg.enable_lora or ecfg.spec_method:
+            raise SystemExit("--pd-prefill-device does not combine with LoRA or speculative decoding")
+        dec = f"cuda:{ecfg.device_ordinal}" if torch.cuda.is_available() else "cpu"
+        pre = f"cuda:{ns.pd_prefill_device}" if torch.cuda.is_available() else "cpu"
+        eng = build_pd_engine(ecfg, mcfg, prefill_device=pre, decode_device=dec, store_device="cpu" if ns.pd_store == "host" else None)
+        log.info("prefill on %s, decode on %s, %d store slots on %s", pre, dec, eng.store.num_slots, eng.store.slab.device)
+        name = ecfg.served_model_name or ecfg.preset or os.path.basename(os.path.normpath(ecfg.model_path))
+        try:
+            serve(eng, tokenizer, name, ecfg.host, ecfg.port)
+        finally:
+            eng.shutdown()
+        return 0
     eng = build_engine(ecfg, mcfg)
     eng.scheduler.tracer = tracer_from_env()
     if ecfg.dump_graph_dot and getattr(eng.executor, "_graphs", None) is not None:

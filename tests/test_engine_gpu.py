@@ -402,3 +402,32 @@ def test_host_tier_on_gpu_saves_evicts_and_restores_prefix():
     finally:
         plain.shutdown()
         off.shutdown()
+
+
+def test_pd_pair_on_gpu_hands_blocks_over_by_hash():
+    """Two engines on the GPU(s) of the box (the second GPU when there is one) joined by a device-resident store:
+    the decode engine restores the prompt's full blocks instead of recomputing them."""
+    from pegainfer_b200.engine.pd import build_pd_engine
+
+    mcfg = preset("qwen3-0.6b", num_layers=3, vocab_size=8192)
+    ecfg = EngineConfig(preset="qwen3-0.6b", num_kv_blocks=256, cuda_graph=True, max_decode_batch=8, max_model_len=1024, max_prefill_tokens=256)
+    single = build_engine(ecfg, mcfg, device="cuda:0", dtype=torch.bfloat16)
+    ps = prompts(3, seed=9)
+    try:
+        want = [o[0] for o in single.generate(ps, max_tokens=8)]
+        model = single.model
+    finally:
+        single.shutdown()
+    two = torch.cuda.device_count() > 1
+    pd = build_pd_engine(ecfg, mcfg, prefill_device="cuda:0", decode_device="cuda:1" if two else "cuda:0", dtype=torch.bfloat16, store_bytes=256 << 20,
+                         prefill_model=model, decode_model=None if two else model)
+    try:
+        got = [o[0] for o in pd.generate(ps, max_tokens=8)]
+        full = sum((len(p) - 1) // 16 for p in ps)
+        assert pd.decode.host_tier.stats.host_hits == full and pd.prefill.host_tier.stats.saves >= full and pd.handoffs == 3
+        assert pd.store.slab.device.type == "cuda"
+        # the decode engine recomputes only the last partial block, with other kernels than a whole-prompt prefill:
+        # the first tokens must agree, later ones may drift on near-ties of a random-weight model
+        assert [g[:2] for g in got] == [w[:2] for w in want]
+    finally:
+        pd.shutdown()
