@@ -64,6 +64,7 @@ class ModelConfig:
     router_bias: bool = False
     expert_quant: str = "bf16"  # bf16 | int4_g32 | fp8_block128
     quant_group_size: int = 32
+    dense_quant: str = "bf16"  # bf16 | fp8_block128: projections outside the experts stay FP8 and run the FP8 GEMM
     # MTP
     num_mtp_layers: int = 0
     # sparse attention indexer (GLM-5 line): every query keeps its index_topk best-scoring keys
@@ -168,6 +169,7 @@ PRESETS["small-glm"] = replace(PRESETS["tiny-glm"], vocab_size=4096, hidden_size
 # GLM-5 (zai-org/GLM-5): 78 layers, 256 routed experts, MLA with 192 + 64 query dims and 256 value dims, 32-head indexer keeping 2048 keys
 PRESETS["glm-5"] = replace(PRESETS["small-glm"], vocab_size=154880, hidden_size=6144, num_layers=78, num_q_heads=64, num_kv_heads=64, intermediate_size=12288, q_lora_rank=2048, n_routed_experts=256,
                            num_experts_per_tok=8, moe_intermediate_size=2048, first_k_dense_replace=3, index_topk=2048, max_position=202752, rope_theta=1e6, expert_quant="fp8_block128")
+PRESETS["small-glm-fp8"] = replace(PRESETS["small-glm"], expert_quant="fp8_block128", dense_quant="fp8_block128")
 for _name in ("tiny-dsv2", "small-dsv2", "dsv2-lite"):
     if _name in PRESETS:
         PRESETS[_name + "-fp8"] = replace(PRESETS[_name], expert_quant="fp8_block128")
@@ -282,7 +284,7 @@ def from_hf(cfg: dict, model_dir: Optional[str] = None) -> ModelConfig:
     if family == "glm_dsa":
         types = cfg.get("mlp_layer_types")
         dense = cfg.get("first_k_dense_replace", 3) if types is None else next((i for i, t in enumerate(types) if t == "sparse"), len(types))
-        mla.update(router_bias=True, scoring_func="sigmoid", first_k_dense_replace=dense, num_mtp_layers=cfg.get("num_nextn_predict_layers", 0),
+        mla.update(dense_quant="fp8_block128" if quant == "fp8_block128" else "bf16", router_bias=True, scoring_func="sigmoid", first_k_dense_replace=dense, num_mtp_layers=cfg.get("num_nextn_predict_layers", 0),
                    index_topk=cfg.get("index_topk", 2048), index_head_dim=cfg.get("index_head_dim", 128), index_n_heads=cfg.get("index_n_heads", 32))
     return ModelConfig(**common, **mla)
 

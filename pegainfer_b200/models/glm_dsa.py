@@ -30,7 +30,7 @@ from ..config import ModelConfig
 from ..kv.buffer import LatentKvBuffer
 from ..loader.sources import WeightSource
 from ..ops.reference import AttnMeta
-from .mla_moe import MlaLayer, MlaMoeModel, mla_moe_shapes
+from .mla_moe import MlaLayer, MlaMoeModel, load_dense, mla_moe_shapes
 
 
 def glm_dsa_shapes(cfg: ModelConfig) -> dict:
@@ -40,11 +40,20 @@ def glm_dsa_shapes(cfg: ModelConfig) -> dict:
         p = f"model.layers.{i}.self_attn.indexer."
         s.update({p + "wq_b.weight": (hi * di, cfg.q_lora_rank), p + "wk.weight": (di, cfg.hidden_size), p + "k_norm.weight": (di,), p + "k_norm.bias": (di,),
                   p + "weights_proj.weight": (hi, cfg.hidden_size)})
+        if cfg.dense_quant == "fp8_block128" and (hi * di) % 128 == 0 and cfg.q_lora_rank % 128 == 0:
+            s[p + "wq_b.weight_scale_inv"] = (hi * di // 128, cfg.q_lora_rank // 128)
     return s
 
 
-def _pairs_from_halves(w: torch.Tensor, start: int, width: int) -> None:
-    """In place: rows ``start .. start + width`` go from half-split order (i, i + width/2) to adjacent pairs."""
+def _pairs_from_halves(w, start: int, width: int) -> None:
+    """In place: rows ``start .. start + width`` go from half-split order (i, i + width/2) to adjacent pairs.
+    An FP8 matrix is reordered in its e4m3 rows; the rows of one rotary block share one 128-row scale block."""
+    if isinstance(w, ops.Fp8Weight):
+        if start // 128 != (start + width - 1) // 128:
+            raise ValueError("rotary rows straddle two FP8 scale blocks")
+        q = w.q.view(torch.uint8)
+        _pairs_from_halves(q, start, width)
+        return
     blk = w[start : start + width]
     half = width // 2
     w[start : start + width] = torch.stack((blk[:half], blk[half:]), 1).reshape(blk.shape)
@@ -79,7 +88,7 @@ class GlmDsaModel(MlaMoeModel):
         _pairs_from_halves(L.kv_a, cfg.kv_lora_rank, rope)
         p = f"{self.P}layers.{i}.self_attn.indexer."
         L.layer_index = i
-        L.idx_wq_b = src.get(p + "wq_b.weight", dev, dt)
+        L.idx_wq_b = load_dense(src, p + "wq_b.weight", dev, dt, cfg)
         L.idx_wk = src.get(p + "wk.weight", dev, dt)
         L.idx_k_norm_w = src.get(p + "k_norm.weight", dev, torch.float32)
         L.idx_k_norm_b = src.get(p + "k_norm.bias", dev, torch.float32)

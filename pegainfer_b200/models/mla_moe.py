@@ -86,7 +86,34 @@ def mla_moe_shapes(cfg: ModelConfig) -> dict:
             s[m + "gate_proj.weight"] = (cfg.intermediate_size, h)
             s[m + "up_proj.weight"] = (cfg.intermediate_size, h)
             s[m + "down_proj.weight"] = (h, cfg.intermediate_size)
+    if cfg.dense_quant == "fp8_block128":
+        for name, shp in list(s.items()):
+            if _fp8_dense_name(name) and len(shp) == 2 and shp[0] % 128 == 0 and shp[1] % 128 == 0:
+                s[name + "_scale_inv"] = (shp[0] // 128, shp[1] // 128)
     return s
+
+
+_FP8_DENSE = ("q_a_proj.weight", "q_b_proj.weight", "q_proj.weight", "o_proj.weight", "mlp.gate_proj.weight", "mlp.up_proj.weight", "mlp.down_proj.weight",
+              "shared_experts.gate_proj.weight", "shared_experts.up_proj.weight", "shared_experts.down_proj.weight", "indexer.wq_b.weight")
+
+
+def _fp8_dense_name(name: str) -> bool:
+    return name.endswith(_FP8_DENSE) and ".experts." not in name
+
+
+def load_dense(src, name, dev, dt, cfg):
+    """A projection matrix: bf16, or kept as block-scaled FP8 when the checkpoint stores it that way and the
+    model runs its dense projections in FP8."""
+    if cfg.dense_quant == "fp8_block128" and dev.type == "cuda" or cfg.dense_quant == "fp8_block128" and dt == torch.float32:
+        if src.has(name + "_scale_inv"):
+            shp = src.shape(name)
+            if len(shp) == 2 and shp[0] % 128 == 0 and shp[1] % 128 == 0:
+                return ops.Fp8Weight(src.get(name, dev, torch.float8_e4m3fn), src.get(name + "_scale_inv", dev, torch.float32))
+    return src.get(name, dev, dt)
+
+
+def cat_rows(parts):
+    return ops.Fp8Weight.cat(parts) if isinstance(parts[0], ops.Fp8Weight) else torch.cat(parts, 0)
 
 
 class _QuantRandomSource(RandomSource):
@@ -176,26 +203,26 @@ class MlaMoeModel:
         L = MlaLayer(
             input_norm=src.get(p + "input_layernorm.weight", dev, dt),
             post_norm=src.get(p + "post_attention_layernorm.weight", dev, dt),
-            q_a=src.get(a + "q_a_proj.weight", dev, dt) if cfg.q_lora_rank else None,
+            q_a=load_dense(src, a + "q_a_proj.weight", dev, dt, cfg) if cfg.q_lora_rank else None,
             q_a_norm=src.get(a + "q_a_layernorm.weight", dev, dt) if cfg.q_lora_rank else None,
-            q_b=src.get(a + ("q_b_proj.weight" if cfg.q_lora_rank else "q_proj.weight"), dev, dt),
+            q_b=load_dense(src, a + ("q_b_proj.weight" if cfg.q_lora_rank else "q_proj.weight"), dev, dt, cfg),
             kv_a=src.get(a + "kv_a_proj_with_mqa.weight", dev, dt),
             kv_a_norm=src.get(a + "kv_a_layernorm.weight", dev, dt),
             w_uk=kv_b[:, :nope].contiguous(),
             w_uv=kv_b[:, nope:].contiguous(),
-            o=src.get(a + "o_proj.weight", dev, dt),
+            o=load_dense(src, a + "o_proj.weight", dev, dt, cfg),
         )
         m = p + "mlp."
         if not cfg.layer_is_moe(i):
-            L.dense_gate_up = torch.cat([src.get(m + "gate_proj.weight", dev, dt), src.get(m + "up_proj.weight", dev, dt)], 0)
-            L.dense_down = src.get(m + "down_proj.weight", dev, dt)
+            L.dense_gate_up = cat_rows([load_dense(src, m + "gate_proj.weight", dev, dt, cfg), load_dense(src, m + "up_proj.weight", dev, dt, cfg)])
+            L.dense_down = load_dense(src, m + "down_proj.weight", dev, dt, cfg)
             return L
         L.router = src.get(m + "gate.weight", dev, dt)
         if cfg.router_bias:
             L.router_bias = src.get(m + "gate.e_score_correction_bias", dev, torch.float32)
         if cfg.n_shared_experts:
-            L.shared_gate_up = torch.cat([src.get(m + "shared_experts.gate_proj.weight", dev, dt), src.get(m + "shared_experts.up_proj.weight", dev, dt)], 0)
-            L.shared_down = src.get(m + "shared_experts.down_proj.weight", dev, dt)
+            L.shared_gate_up = cat_rows([load_dense(src, m + "shared_experts.gate_proj.weight", dev, dt, cfg), load_dense(src, m + "shared_experts.up_proj.weight", dev, dt, cfg)])
+            L.shared_down = load_dense(src, m + "shared_experts.down_proj.weight", dev, dt, cfg)
         e0, e1 = shard_range(cfg.n_routed_experts, self.ep.rank, self.ep.world)
         ex: dict = {"offset": e0}
         if cfg.expert_quant == "int4_g32":

@@ -70,7 +70,34 @@ def swiglu(gate_up, interleaved=False):
     return _impl(gate_up).swiglu(gate_up, interleaved)
 
 
+class Fp8Weight:
+    """A dense matrix kept as block-scaled FP8: ``q`` e4m3 ``[M, K]`` and one f32 scale per 128 x 128 block.
+    ``linear`` quantises the activations per token and 128-wide k group and runs the FP8 tensor-core GEMM."""
+
+    __slots__ = ("q", "scale")
+
+    def __init__(self, q, scale):
+        self.q, self.scale = q.contiguous(), scale.float().contiguous()
+
+    @property
+    def shape(self):
+        return self.q.shape
+
+    def numel(self):
+        return self.q.numel()
+
+    @staticmethod
+    def cat(parts):
+        """Stack matrices by rows (each part's rows a multiple of 128, so its scale rows stack too)."""
+        import torch
+
+        return Fp8Weight(torch.cat([p.q for p in parts], 0), torch.cat([p.scale for p in parts], 0))
+
+
 def linear(x, w, out_dtype=None):
+    if isinstance(w, Fp8Weight):
+        y = _impl(x).linear_fp8_block(x, w.q, w.scale)
+        return y if out_dtype is None or y.dtype == out_dtype else y.to(out_dtype)
     if _MODE == "cublas" and x.is_cuda:
         import torch
 

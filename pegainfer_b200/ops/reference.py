@@ -521,7 +521,7 @@ def linear_fp8_block(x, wq, w_scale, xq=None, x_scale=None):
     xf = xq.float().view(t, k // 128, 128) * x_scale[:, :t].t().unsqueeze(-1)
     m = wq.shape[0]
     wf = wq.float() * w_scale.float().repeat_interleave(128, 0)[:m].repeat_interleave(128, 1)[:, :k]
-    return (xf.view(t, k) @ wf.t()).to(torch.bfloat16)
+    return (xf.view(t, k) @ wf.t()).to(torch.bfloat16 if x is None else x.dtype)
 
 
 # ----------------------------------------------------------------------------------

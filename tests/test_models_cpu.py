@@ -247,3 +247,30 @@ def test_glm_sparse_indexer_chunking_invariance_and_mtp():
     plain, _ = gen("tiny-glm", ps, 10)
     spec, eng = gen("tiny-glm", ps, 10, spec_method="mtp")
     assert spec == plain and eng.scheduler._metrics.spec_decode.num_drafts > 0
+
+
+def test_glm_fp8_dense_projections_load_as_fp8_and_generate():
+    """With FP8 dense weights the projections outside the experts stay e4m3 + block scales and go through the
+    quantise-activations + FP8 GEMM path; chunked and whole-prompt generation must still agree."""
+    import dataclasses
+
+    from pegainfer_b200 import ops
+
+    cfg = dataclasses.replace(preset("small-glm-fp8"), hidden_size=256, num_q_heads=4, num_kv_heads=4, q_lora_rank=128, kv_lora_rank=128, qk_nope_head_dim=64, qk_rope_head_dim=64,
+                              v_head_dim=64, intermediate_size=256, moe_intermediate_size=128, n_routed_experts=8, num_experts_per_tok=2, index_n_heads=4, index_head_dim=128, index_topk=24,
+                              vocab_size=1024, max_position=4096, num_mtp_layers=0)
+    ps = prompts_for(2, 41, seed=3)
+
+    def run(chunk):
+        eng = build_engine(EngineConfig(preset="small-glm-fp8", kv_page_size=16, num_kv_blocks=64, cuda_graph=False, max_prefill_tokens=chunk), cfg, device="cpu", dtype=torch.float32)
+        try:
+            L = eng.model.layers
+            assert isinstance(L[0].q_b, ops.Fp8Weight) and isinstance(L[0].dense_gate_up, ops.Fp8Weight) and isinstance(L[1].shared_down, ops.Fp8Weight) and isinstance(L[1].idx_wq_b, ops.Fp8Weight)
+            assert not isinstance(L[0].kv_a, ops.Fp8Weight)  # 128 + 64 output rows: not a whole number of scale blocks
+            outs = eng.generate(ps, SamplingParams(temperature=0.0, ignore_eos=True), max_tokens=6, timeout=300)
+            assert all(o[1].kind == "finished" for o in outs)
+            return [o[0] for o in outs]
+        finally:
+            eng.shutdown()
+
+    assert run(512) == run(24)
