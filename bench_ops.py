@@ -230,6 +230,60 @@ GEMM_PHASES = ["entry", "prologue done", "predecessor complete", "all loads issu
                "partial pushed", "cluster partials in", "reduced + stored", "roles done", "cluster released", "token tiles issued", "second stage landed", "seventh stage landed"]
 
 
+def fp8_cases(iters):
+    """Block-scaled FP8 GEMM (kind::f8f6f4) on decode shapes, with and without the activation quantiser; bytes
+    count the e4m3 weights once."""
+    from pegainfer_b200.loader.export import quantize_dense_to_fp8
+    from pegainfer_b200.ops import cuda as K
+
+    rows = []
+    for t, m, k in ((64, 6144, 4096), (64, 24576, 4096), (64, 4096, 12288), (16, 24576, 4096), (64, 12288, 6144)):
+        nvar = max(2, min(16, int(300e6 // (m * k)) + 1))
+        ws = []
+        for i in range(nvar):
+            d = {"w": torch.randn(m, k) * 0.05}
+            quantize_dense_to_fp8(d, ["w"])
+            ws.append((d["w"].to(DEV).contiguous(), d["w_scale_inv"].to(DEV).contiguous()))
+        x = torch.randn(t, k, device=DEV).bfloat16()
+        xq, xs = K.quant_fp8_1x128(x)
+        ms = time_graph(lambda i: K.linear_fp8_block(x, ws[i][0], ws[i][1], xq, xs), nvar, iters)
+        rows.append((f"fp8 gemm T{t} M{m} K{k} (pre-quantised x)", ms, m * k + t * k + t * m * 2, 2.0 * t * m * k))
+        ms = time_graph(lambda i: K.linear_fp8_block(x, ws[i][0], ws[i][1]), nvar, iters)
+        rows.append((f"  with activation quantiser", ms, m * k + t * k * 3 + t * m * 2, 2.0 * t * m * k))
+    return rows
+
+
+def dsa_cases(iters):
+    """Sparse-attention indexer on GLM-5 shapes (32 index heads x 128, keep 2048): tcgen05 scores, radix top-k, and the
+    gathered sparse latent attention (64 heads, latent 512 + 64) at one decode row per sequence."""
+    from pegainfer_b200.ops import cuda as K
+
+    rows = []
+    page, heads, d = 64, 32, 128
+    for bs, ctx in ((16, 16384), (64, 8192), (64, 32768)):
+        meta, npages = _meta_for([1] * bs, [ctx] * bs, page)
+        cache = (torch.randn(npages, page, d, device=DEV) * 0.5).bfloat16()
+        q = (torch.randn(bs, heads, d, device=DEV) * 0.3).bfloat16()
+        w = (torch.randn(bs, heads, device=DEV) * 0.2).float()
+        ms = time_graph(lambda i: K.dsa_index_scores(q, w, cache, meta), 1, iters)
+        rows.append((f"dsa index scores bs{bs} ctx{ctx} 32h x 128", ms, bs * ctx * d * 2 + bs * ctx * 4, 2.0 * bs * ctx * heads * d))
+        sc = K.dsa_index_scores(q, w, cache, meta)
+        ms = time_graph(lambda i: K.dsa_topk(sc, 2048), 1, iters)
+        rows.append((f"dsa top-2048 bs{bs} ctx{ctx}", ms, bs * ctx * 4 * 5, 0))
+        sel = K.dsa_topk(sc, 2048)
+        H, nope, vdim, c, rope = 64, 192, 256, 512, 64
+        latent = (torch.randn(npages, page, c + rope, device=DEV) * 0.3).bfloat16()
+        cos, sin = __import__("pegainfer_b200.ops.reference", fromlist=["rope_tables"]).rope_tables(ctx + 8, rope, 1e4, torch.bfloat16, DEV)
+        qm = K.mla_rope_q((torch.randn(bs, H, nope + rope, device=DEV) * 0.3).bfloat16(), cos, sin, meta, nope)
+        w_uk, w_uv = (torch.randn(H, nope, c, device=DEV) * 0.05).bfloat16(), (torch.randn(H, vdim, c, device=DEV) * 0.05).bfloat16()
+        ms = time_graph(lambda i: K.mla_attention_sparse(qm, w_uk, w_uv, latent, meta, 0.0625, c, sel), 1, max(2, iters // 2))
+        rows.append((f"sparse mla decode (gather + attn) bs{bs} keep 2048 of {ctx}", ms, bs * 2048 * (c + rope) * 2 * 3, 2.0 * bs * 2048 * H * (c + rope + c)))
+        ms = time_graph(lambda i: K.mla_attention(qm, w_uk, w_uv, latent, meta, 0.0625, c), 1, max(2, iters // 4))
+        rows.append((f"  dense mla decode over all {ctx} keys", ms, bs * ctx * (c + rope) * 2, 2.0 * bs * ctx * H * (c + rope + c)))
+        del cache, latent
+    return rows
+
+
 def gemm_phase_timeline(t, m, k):
     """Per-CTA globaltimer stamps of one eager GEMM launch with cold L2 (profiling hook of the
     GEMM kernel): min / median / max over the CTAs, microseconds from the first CTA's entry."""
@@ -381,6 +435,10 @@ def main():
             rows.extend(moe_cases(args.iters))
         if args.only in (None, "mla"):
             rows.extend(mla_cases(args.iters))
+        if args.only in (None, "fp8"):
+            rows.extend(fp8_cases(args.iters))
+        if args.only in (None, "dsa"):
+            rows.extend(dsa_cases(args.iters))
     out = []
     print(f"{'op':58s} {'us':>9s} {'GB/s':>8s} {'%HBM':>6s} {'TFLOP/s':>8s} {'%bf16':>6s}   (peaks: {src} {hbm:.0f} GB/s, {tf:.0f} TFLOP/s)")
     for name, ms, by, fl in rows:

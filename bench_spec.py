@@ -5,7 +5,9 @@ per arm: output tokens per second over the decode phase, draft rounds, mean acce
 share of verify steps that were CUDA-graph replays.  Weights are random (there is no checkpoint here), so the
 block / chain drafters propose tokens the target almost never accepts: those arms show what a round costs.
 ``draft-self`` drafts with a copy of the target itself (every draft is accepted): it shows the acceptance
-accounting and the upper end of the tokens-per-verify-step range.
+accounting and the upper end of the tokens-per-verify-step range.  Token-for-token equality with plain decoding is
+what the tests check (under the batch-invariant policy); with random weights the logits are nearly flat, so the arms
+here, which run different kernel shapes, need not pick the same tokens.
 
     python bench_spec.py --preset qwen3-8b --conc 16 --prompt-len 512 --max-tokens 96
 """
@@ -25,7 +27,7 @@ def run(args, method, path, draft_len):
 
     kw = {}
     if method:
-        kw = dict(spec_method=method, draft_model_path=path, spec_draft_len=draft_len, seed=-1 if path and path.startswith("preset:") else 0)
+        kw = dict(spec_method=method, draft_model_path=path, spec_draft_len=draft_len)
     mcfg = preset(args.preset)
     ecfg = EngineConfig(preset=args.preset, cuda_graph=True, max_decode_batch=args.conc, max_model_len=args.prompt_len + args.max_tokens + 64, max_prefill_tokens=4096,
                         num_kv_blocks=args.conc * ((args.prompt_len + args.max_tokens + 64) // 16 + 2) + 8, **kw)
@@ -70,14 +72,13 @@ def main():
     a = ap.parse_args()
     arms = {
         "none": (None, None, 0),
-        "draft-self": ("draft", f"preset:{a.preset}", 3),
+        "draft-self": ("draft", f"preset:{a.preset}:seed=0", 3),  # the target's own weights (engine seed 0): every draft is accepted
         "dflash": ("dflash", "random:layers=2,block=4", 3),
         "dspark": ("dspark", "random:layers=2,block=4,markov=64", 4),
         "eagle3": ("eagle3", "random:draft_vocab=32768", 3),
     }
-    rows = [run(a, *arms[name]) for name in a.arms.split(",")]
-    base = rows[0]["first_tokens"]
-    print(json.dumps({"lossless": all(r["first_tokens"] == base for r in rows)}))
+    for name in a.arms.split(","):
+        run(a, *arms[name])
 
 
 if __name__ == "__main__":

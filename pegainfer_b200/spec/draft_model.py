@@ -35,8 +35,11 @@ def load_draft_model(ecfg, model):
     if not path:
         raise ValueError("--spec-method draft needs --draft-model-path")
     if path.startswith("preset:"):
-        dcfg = preset(path.split(":", 1)[1])
-        decfg = EngineConfig(preset=path.split(":", 1)[1], seed=ecfg.seed + 1)
+        # preset:NAME[:seed=K]: random weights of a named shape; the default seed differs from the target's
+        parts = path.split(":")
+        seed = next((int(p[5:]) for p in parts[2:] if p.startswith("seed=")), ecfg.seed + 1)
+        dcfg = preset(parts[1])
+        decfg = EngineConfig(preset=parts[1], seed=seed)
     else:
         dcfg = load_model_config(path)
         decfg = EngineConfig(model_path=path, seed=ecfg.seed)
