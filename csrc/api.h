@@ -77,6 +77,12 @@ int pg_qk_norm_rope_append(const void* qkv, long long ld, const void* q_w, const
                            int rot, int page_size, long long num_pages, int max_pos, int gated, int offset, float eps, void* status,
                            cudaStream_t stream);
 
+// ---- prefill attention on tcgen05 (attention_tc.cu) ----------------------------------------
+int pg_prefill_attention_tc(const void* q, const void* kv_layer, void* out, const void* q_indptr, const void* kv_lens, const void* table, int table_stride,
+                            int num_seqs, int tokens, int hq, int hkv, int dim, int page_size, long long num_pages, float scale, int q_tiles, void* status,
+                            cudaStream_t stream);
+void pg_prefill_attention_tc_variant(int v);
+
 // ---- block-scaled FP8 GEMM on tcgen05 kind::f8f6f4 (gemm_fp8_sm100.cu) --------------------
 long long pg_gemm_fp8_ws_bytes(int T, int M);
 int pg_gemm_fp8_block(const void* xq, long long ldx, const void* x_scale, long long ldxs, const void* wq, long long ldw, const void* w_scale, void* y,

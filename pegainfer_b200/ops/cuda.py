@@ -509,6 +509,8 @@ def qk_norm_rope_append(qkv, q_norm_w, k_norm_w, cos, sin, meta: AttnMeta, kv_la
 
 _BATCH_INVARIANT = False
 INVARIANT_KV_SPLITS = 4
+_PREFILL_TC = os.environ.get("PEGAINFER_PREFILL_TC", "1") != "0"  # tcgen05 prefill attention for head dim 128
+_PREFILL_TC_MIN_ROWS = int(os.environ.get("PEGAINFER_PREFILL_TC_MIN_ROWS", "64"))  # shorter chunks keep the 64-row mma.sync tiles
 
 
 def set_batch_invariant(on: bool) -> None:
@@ -576,7 +578,13 @@ def paged_attention(q, kv_layer, meta: AttnMeta, scale=None, window=0, out: Opti
         # splits and merge order as in a pure decode step or a graph replay), however few there are
         if meta.num_seqs - n_pf < (1 if _BATCH_INVARIANT else _MIXED_DECODE_MIN):
             n_pf = meta.num_seqs
-    if n_pf > 0:
+    if n_pf > 0 and d == 128 and window == 0 and _PREFILL_TC and 128 % page_size == 0 and q.is_contiguous() and max(qi[b + 1] - qi[b] for b in range(n_pf)) >= _PREFILL_TC_MIN_ROWS:
+        # tcgen05 kernel: 128 query rows of one head per CTA, S and P V on the tensor cores, accumulators in TMEM
+        q_tiles = sum((qi[b + 1] - qi[b] + 127) // 128 for b in range(n_pf))
+        rc = lib().pg_prefill_attention_tc(_ptr(q), _ptr(kv_layer), _ptr(out), _ptr(meta.q_indptr), _ptr(meta.kv_lens), _ptr(table), _ci(table.stride(0)), _ci(n_pf), _ci(qi[n_pf]),
+                                           _ci(hq), _ci(hkv), _ci(d), _ci(page_size), _ll(kv_layer.shape[0]), _cf(scale), _ci(q_tiles), _ptr(c.status), _stream())
+        _check(rc, c)
+    elif n_pf > 0:
         q_tiles = sum((qi[b + 1] - qi[b] + 63) // 64 for b in range(n_pf))
         rc = lib().pg_paged_attention(
             _ptr(q), _ptr(kv_layer), _ptr(out), _ptr(meta.q_indptr), _ptr(meta.kv_lens), _ptr(table), _ci(table.stride(0)), _ci(n_pf),

@@ -807,3 +807,38 @@ def test_fp8_block_scaled_gemm_matches_reference(t, m, k):
     rel = (y.float() - full).norm() / full.norm()
     assert rel.item() < 0.05, rel.item()
     status_clean()
+
+
+@pytest.mark.parametrize("page", [16, 64])
+def test_tcgen05_prefill_attention_matches_reference(page):
+    """Ragged prefill (whole prompts, a chunk behind a cached prefix, a short tail) through the tcgen05 kernel."""
+    from pegainfer_b200.kv.request_kv import KvView
+    from pegainfer_b200.sched.executor import SeqStep, build_meta
+
+    K = cu()
+    hq, hkv, d = 8, 2, 128
+    g = torch.Generator(device=DEV).manual_seed(3)
+    cases = [(300, 300), (700, 257), (128, 128), (1000, 130), (90, 70)]  # (kv_len, query rows)
+    seqs, nxt = [], 1
+    for i, (kl, nq) in enumerate(cases):
+        npg = (kl + page - 1) // page
+        seqs.append(SeqStep(rid=i, input_tokens=[0] * nq, start_pos=kl - nq, view=KvView(list(range(nxt, nxt + npg)), kl, page)))
+        nxt += npg
+    _, meta = build_meta(seqs, page, DEV)
+    t = meta.num_tokens
+    kv = (torch.randn(nxt, 2, page, hkv, d, device=DEV, generator=g) * 0.8).to(torch.bfloat16)
+    q = (torch.randn(t, hq, d, device=DEV, generator=g) * 0.8).to(torch.bfloat16)
+    ref = R.paged_attention(q, kv, meta).float()
+    import ctypes
+
+    from pegainfer_b200 import _native
+
+    errs = {}
+    for variant in (1, 0):
+        _native.load().pg_prefill_attention_tc_variant(ctypes.c_int(variant))
+        out = K.paged_attention(q, kv, meta).float()
+        torch.cuda.synchronize()
+        errs[variant] = (out - ref).abs().max().item()
+    _native.load().pg_prefill_attention_tc_variant(ctypes.c_int(-1))
+    assert errs[1] < 0.03, errs
+    status_clean()
