@@ -230,14 +230,35 @@ GEMM_PHASES = ["entry", "prologue done", "predecessor complete", "all loads issu
                "partial pushed", "cluster partials in", "reduced + stored", "roles done", "cluster released", "token tiles issued", "second stage landed", "seventh stage landed"]
 
 
-def fp8_cases(iters):
+def chain_case(t, h, inter, qkv, iters):
+    """The four projections behind attention of one dense layer (o_proj + residual + norm weight, gate_up + SwiGLU,
+    down + residual + norm weight, next qkv) as ONE persistent kernel; bytes = the four weight matrices."""
+    from pegainfer_b200.ops import cuda as K
+
+    nvar = 6
+    ws = [dict(wo=(torch.randn(h, h, device=DEV) * 0.03).bfloat16(), gu=(torch.randn(2 * inter, h, device=DEV) * 0.03).bfloat16(), wd=(torch.randn(h, inter, device=DEV) * 0.02).bfloat16(),
+               wq=(torch.randn(qkv, h, device=DEV) * 0.03).bfloat16()) for _ in range(nvar)]
+    a = (torch.randn(t, h, device=DEV) * 0.5).bfloat16()
+    n1 = torch.ones(h, device=DEV).bfloat16()
+    res = torch.randn(t, h, device=DEV).bfloat16()
+
+    def fn(i):
+        w = ws[i]
+        return K.decode_chain(a, [(w["wo"], K.CH_RESID_NORM, n1, False), (w["gu"], K.CH_SWIGLU, None, False), (w["wd"], K.CH_RESID_NORM, n1, False), (w["wq"], K.CH_PLAIN, None, False)],
+                              residual=res, eps=1e-6)
+
+    ms = time_graph(fn, nvar, iters)
+    return ms, (h * h + 2 * inter * h + h * inter + qkv * h) * 2, 2.0 * t * (h * h + 2 * inter * h + h * inter + qkv * h)
+
+
+def fp8_cases(iters, only=None):
     """Block-scaled FP8 GEMM (kind::f8f6f4) on decode shapes, with and without the activation quantiser; bytes
     count the e4m3 weights once."""
     from pegainfer_b200.loader.export import quantize_dense_to_fp8
     from pegainfer_b200.ops import cuda as K
 
     rows = []
-    for t, m, k in ((64, 6144, 4096), (64, 24576, 4096), (64, 4096, 12288), (16, 24576, 4096), (64, 12288, 6144)):
+    for t, m, k in only or ((64, 6144, 4096), (64, 24576, 4096), (64, 4096, 12288), (16, 24576, 4096), (64, 12288, 6144)):
         nvar = max(2, min(16, int(300e6 // (m * k)) + 1))
         ws = []
         for i in range(nvar):
@@ -253,14 +274,14 @@ def fp8_cases(iters):
     return rows
 
 
-def dsa_cases(iters):
+def dsa_cases(iters, only=None):
     """Sparse-attention indexer on GLM-5 shapes (32 index heads x 128, keep 2048): tcgen05 scores, radix top-k, and the
     gathered sparse latent attention (64 heads, latent 512 + 64) at one decode row per sequence."""
     from pegainfer_b200.ops import cuda as K
 
     rows = []
     page, heads, d = 64, 32, 128
-    for bs, ctx in ((16, 16384), (64, 8192), (64, 32768)):
+    for bs, ctx in only or ((16, 16384), (64, 8192), (64, 32768)):
         meta, npages = _meta_for([1] * bs, [ctx] * bs, page)
         cache = (torch.randn(npages, page, d, device=DEV) * 0.5).bfloat16()
         q = (torch.randn(bs, heads, d, device=DEV) * 0.3).bfloat16()
@@ -377,7 +398,8 @@ def main():
     ap.add_argument("--only", default=None)
     ap.add_argument("--iters", type=int, default=16)
     ap.add_argument("--json", default=None)
-    ap.add_argument("--single", default=None, help="e.g. gemm:64x4096x4096, attn:64x1152, prefill:4x1024, gdn:8x2048 (sequences x tokens)")
+    ap.add_argument("--single", default=None, help="e.g. gemm:64x4096x4096, attn:64x1152, prefill:4x1024, gdn:8x2048 (sequences x tokens), chain:64x4096x12288x6144 (tokens x hidden x ffn x qkv), "
+                    "fp8:64x24576x4096, dsa:16x16384 (sequences x context)")
     ap.add_argument("--library", action="store_true", help="also time torch/cuBLAS for the GEMM rows")
     ap.add_argument("--phases", default=None, help="gemm:TxMxK: print the per-CTA phase timeline of one GEMM launch")
     ap.add_argument("--phases-steady", default=None, help="gemm:TxMxK: the same stamps for back-to-back launches inside one CUDA graph")
@@ -397,12 +419,22 @@ def main():
             ms, by, fl = gemm_case(*dims, iters=args.iters, mode={"gemm": "auto", "gemm2sm": "two_sm", "gemm1cta": "one_cta"}[kind])
         elif kind == "gdn":
             name, ms, by, fl = gdn_cases(args.iters, only=[("single", [dims[1]] * dims[0])])[0]
+        elif kind == "chain":
+            ms, by, fl = chain_case(dims[0], dims[1], dims[2], dims[3], args.iters)
+        elif kind == "fp8":
+            name, ms, by, fl = [r for r in fp8_cases(args.iters, only=[tuple(dims)])][0]
+        elif kind == "dsa":
+            name, ms, by, fl = dsa_cases(args.iters, only=[tuple(dims)])[0]
         elif kind == "attn":
             ms, by, fl = attn_decode_case(dims[0], dims[1], 32, 8, 128, 16, args.iters)
         else:
             ms, by, fl = attn_prefill_case(dims[0], dims[1], 32, 8, 128, 16, args.iters)
         rows.append((args.single, ms, by, fl))
     else:
+        if args.only in (None, "chain"):
+            for t in (64, 16):
+                ms, by, fl = chain_case(t, 4096, 12288, 6144, args.iters)
+                rows.append((f"decode chain T{t} (o, gate_up, down, qkv of Qwen3-8B)", ms, by, fl))
         if args.only in (None, "gemm"):
             shapes = [(64, 6144, 4096), (64, 4096, 4096), (64, 24576, 4096), (64, 4096, 12288), (64, 151936, 4096), (1, 4096, 4096), (16, 24576, 4096), (256, 24576, 4096),
                       (1024, 6144, 4096), (1024, 24576, 4096), (4096, 6144, 4096), (4096, 4096, 4096), (4096, 24576, 4096), (4096, 4096, 12288), (8192, 8192, 8192)]

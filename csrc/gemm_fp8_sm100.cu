@@ -36,7 +36,7 @@ struct Fp8Params {
   bf16* y;
   long long ldy;
   float* ws;  // [splits, T, M] f32 when splits > 1
-  int M, T, kgroups, bn, stages, splits, m_tiles, n_tiles;
+  int M, T, kgroups, bn, stages, splits, m_tiles, n_tiles, kg_cap;
   uint32_t* status;
 };
 
@@ -64,6 +64,8 @@ __global__ void __launch_bounds__(192) gemm_fp8_block_kernel(const __grid_consta
   uint64_t* tempty = tfull + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* s_ws = reinterpret_cast<float*>(tmem_slot + 4);  // [k groups of this CTA] weight-block scales
+  float* s_xs = s_ws + p.kg_cap;                           // [k groups of this CTA][BN] activation scales (0 past T)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
 
@@ -145,11 +147,20 @@ __global__ void __launch_bounds__(192) gemm_fp8_block_kernel(const __grid_consta
     float acc[BN];
 #pragma unroll
     for (int j = 0; j < BN; ++j) acc[j] = 0.f;
+    // this CTA's scales go to shared memory once: read per k group from global memory they would put a memory
+    // latency and BN loads per thread on the critical path of every k group
+    const int et = threadIdx.x - 64;  // 0..127
+    for (int i = et; i < kg1 - kg0; i += 128) s_ws[i] = p.w_scale[(long long)m_tile * p.kgroups + kg0 + i];
+    for (int i = et; i < (kg1 - kg0) * BN; i += 128) {
+      const int g = i / BN, j = i % BN;
+      s_xs[i] = (n0 + j < p.T) ? p.x_scale[(long long)(kg0 + g) * p.ldxs + n0 + j] : 0.f;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
     bool ok = true;
     for (int kg = kg0; kg < kg1 && ok; ++kg) {
       const int i = kg - kg0, buf = i & 1;
-      const float sw = p.w_scale[(long long)m_tile * p.kgroups + kg];
-      const float* sx = p.x_scale + (long long)kg * p.ldxs + n0;
+      const float sw = s_ws[i];
+      const float4* sx = reinterpret_cast<const float4*>(s_xs + i * BN);
       ok = mbar_wait(&tfull[buf], (uint32_t)((i >> 1) & 1), abort_flag);
       if (!ok) break;
       tc_fence_after();
@@ -160,9 +171,12 @@ __global__ void __launch_bounds__(192) gemm_fp8_block_kernel(const __grid_consta
         tmem_ld16(t_row + c, v);
         tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const float s = n0 + c + j < p.T ? sw * sx[c + j] : 0.f;
-          acc[c + j] = fmaf(__uint_as_float(v[j]), s, acc[c + j]);
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const float4 s4 = sx[(c >> 2) + q4];
+          acc[c + q4 * 4 + 0] = fmaf(__uint_as_float(v[q4 * 4 + 0]), sw * s4.x, acc[c + q4 * 4 + 0]);
+          acc[c + q4 * 4 + 1] = fmaf(__uint_as_float(v[q4 * 4 + 1]), sw * s4.y, acc[c + q4 * 4 + 1]);
+          acc[c + q4 * 4 + 2] = fmaf(__uint_as_float(v[q4 * 4 + 2]), sw * s4.z, acc[c + q4 * 4 + 2]);
+          acc[c + q4 * 4 + 3] = fmaf(__uint_as_float(v[q4 * 4 + 3]), sw * s4.w, acc[c + q4 * 4 + 3]);
         }
       }
       tc_fence_before();
@@ -254,7 +268,7 @@ int make_tmap_u8_2d(CUtensorMap* out, const void* ptr, long long rows, long long
 
 template <int BN>
 int launch_fp8(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const Fp8Params& p, cudaStream_t stream) {
-  const size_t smem = 1024 + (size_t)p.stages * (A_BYTES + BN * BKB) + (2 * MAX_STAGES + 4) * 8 + 64;
+  const size_t smem = 1024 + (size_t)p.stages * (A_BYTES + BN * BKB) + (2 * MAX_STAGES + 4) * 8 + 64 + (size_t)p.kg_cap * (BN + 1) * 4;
   static bool attr_done = false;
   if (!attr_done) {
     PG_CUDA(cudaFuncSetAttribute(gemm_fp8_block_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
@@ -297,7 +311,9 @@ extern "C" int pg_gemm_fp8_block(const void* xq, long long ldx, const void* x_sc
   if ((long long)splits * T * M * 4 > ws_bytes) splits = 1;
   p.splits = splits;
   const int per = ceil_div(p.kgroups, splits);
-  p.stages = min(MAX_STAGES, max(2, min(per, (int)((180 * 1024) / (A_BYTES + p.bn * BKB)))));
+  p.kg_cap = (per + 4) & ~3;  // k groups of one CTA, rounded for the float4 reads of the staged scales
+  // four stages leave room for two CTAs per SM (a grid of 150 - 296 CTAs then runs as one wave)
+  p.stages = min(4, max(2, per));
   CUtensorMap tm_w, tm_x;
   int rc = make_tmap_u8_2d(&tm_w, wq, M, K, ldw, BM);
   if (rc != PG_OK) return rc;

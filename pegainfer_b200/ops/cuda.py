@@ -511,6 +511,15 @@ _BATCH_INVARIANT = False
 INVARIANT_KV_SPLITS = 4
 _PREFILL_TC = os.environ.get("PEGAINFER_PREFILL_TC", "1") != "0"  # tcgen05 prefill attention for head dim 128
 _PREFILL_TC_MIN_ROWS = int(os.environ.get("PEGAINFER_PREFILL_TC_MIN_ROWS", "64"))  # shorter chunks keep the 64-row mma.sync tiles
+# the tcgen05 kernel wins once a sequence is a few thousand keys long (measured 1.37x at 4096, 1.58x at 16384, 0.98x at 1024)
+_PREFILL_TC_MIN_KV = int(os.environ.get("PEGAINFER_PREFILL_TC_MIN_KV", "2048"))
+
+
+def set_prefill_tc(min_kv: int) -> int:
+    """KV length from which prefill attention of head dim 128 takes the tcgen05 kernel; returns the previous value."""
+    global _PREFILL_TC_MIN_KV
+    prev, _PREFILL_TC_MIN_KV = _PREFILL_TC_MIN_KV, int(min_kv)
+    return prev
 
 
 def set_batch_invariant(on: bool) -> None:
@@ -578,7 +587,9 @@ def paged_attention(q, kv_layer, meta: AttnMeta, scale=None, window=0, out: Opti
         # splits and merge order as in a pure decode step or a graph replay), however few there are
         if meta.num_seqs - n_pf < (1 if _BATCH_INVARIANT else _MIXED_DECODE_MIN):
             n_pf = meta.num_seqs
-    if n_pf > 0 and d == 128 and window == 0 and _PREFILL_TC and 128 % page_size == 0 and q.is_contiguous() and max(qi[b + 1] - qi[b] for b in range(n_pf)) >= _PREFILL_TC_MIN_ROWS:
+    # (not under the batch-invariant policy: which kernel runs would depend on the other sequences of the step)
+    if (n_pf > 0 and d == 128 and window == 0 and _PREFILL_TC and not _BATCH_INVARIANT and 128 % page_size == 0 and q.is_contiguous() and max(qi[b + 1] - qi[b] for b in range(n_pf)) >= _PREFILL_TC_MIN_ROWS
+            and (meta.h_kv_lens is None or max(meta.h_kv_lens[:n_pf]) >= _PREFILL_TC_MIN_KV)):
         # tcgen05 kernel: 128 query rows of one head per CTA, S and P V on the tensor cores, accumulators in TMEM
         q_tiles = sum((qi[b + 1] - qi[b] + 127) // 128 for b in range(n_pf))
         rc = lib().pg_prefill_attention_tc(_ptr(q), _ptr(kv_layer), _ptr(out), _ptr(meta.q_indptr), _ptr(meta.kv_lens), _ptr(table), _ci(table.stride(0)), _ci(n_pf), _ci(qi[n_pf]),

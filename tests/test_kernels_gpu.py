@@ -834,11 +834,16 @@ def test_tcgen05_prefill_attention_matches_reference(page):
     from pegainfer_b200 import _native
 
     errs = {}
-    for variant in (1, 0):
-        _native.load().pg_prefill_attention_tc_variant(ctypes.c_int(variant))
-        out = K.paged_attention(q, kv, meta).float()
-        torch.cuda.synchronize()
-        errs[variant] = (out - ref).abs().max().item()
-    _native.load().pg_prefill_attention_tc_variant(ctypes.c_int(-1))
+    prev = K.set_prefill_tc(0)  # every length through the tcgen05 kernel
+    try:
+        before = K.launch_count(DEV)
+        for variant in (1, 0):
+            _native.load().pg_prefill_attention_tc_variant(ctypes.c_int(variant))
+            out = K.paged_attention(q, kv, meta).float()
+            torch.cuda.synchronize()
+            errs[variant] = (out - ref).abs().max().item()
+    finally:
+        K.set_prefill_tc(prev)
+        _native.load().pg_prefill_attention_tc_variant(ctypes.c_int(-1))
     assert errs[1] < 0.03, errs
     status_clean()
