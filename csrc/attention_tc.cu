@@ -1,20 +1,23 @@
 // Prefill attention on tcgen05 for sm_100a: causal GQA attention of ragged query rows over a paged KV cache,
 // head dim 128.
 //
-// One CTA owns 128 query rows of one query head and walks the KV of its sequence in tiles of 128 keys:
+// One CTA owns 256 query rows of one query head as two tiles of 128 (two softmax groups) and walks the KV of its
+// sequence in tiles of 128 keys that both tiles share:
 //
-//   S = Q K^T          tcgen05.mma, both operands K-major in shared memory (TMA, 128-byte swizzle), accumulator in TMEM
-//   P = softmax tile   eight warps, two threads per query row (64 key columns each): tcgen05.ld of the half row, the two
-//                      halves' maxima meet through shared memory, running max / sum in registers, P written as bf16
-//                      into the swizzled A-operand layout
-//   O_j = P V          tcgen05.mma with V as an MN-major B operand (the cache stores keys as rows, which is what the
-//                      contraction over keys needs transposed), fresh TMEM accumulator per tile (two, ping-pong)
-//   O += ...           each thread reads its 64 output columns of O_j back and folds them into f32 registers with the
-//                      rescale factor of the next tile
+//   S_g = Q_g K^T      tcgen05.mma, both operands K-major in shared memory (TMA, 128-byte swizzle), accumulator in TMEM
+//   P_g = softmax tile four warps per group, one query row per thread: two passes over the row in TMEM (maximum, then
+//                      exponentials with packed f32x2 arithmetic), P written back as bf16 INTO TENSOR MEMORY over the
+//                      score columns already consumed (two values per 32-bit column)
+//   O_g += P_g V       tcgen05.mma with A = P_g read from tensor memory and V as an MN-major B operand (the cache stores
+//                      keys as rows, which is what the contraction over keys needs transposed); O_g stays in TMEM for
+//                      the whole walk.  It is rescaled (tcgen05.ld / multiply / tcgen05.st) only when a row's maximum
+//                      grew by more than 2^8 since the value its exponentials refer to; the row sum follows the same
+//                      reference, so the result is exact.
 //
-// Roles: warp 0 = TMA producer (Q once, then K and V tiles through the page table, a ring of four tiles), warp 1 = MMA
-// issuer (S of tile j + 1 is issued before P V of tile j, so the tensor core works during the softmax), warps 2-9 =
-// softmax and output.  TMEM: S twice 128 columns, O_j twice 128 columns.  Every wait is bounded and reports through
+// Roles: warp 0 = TMA producer (Q once, then K and V tiles through the page table, two stages each), warp 1 = MMA
+// issuer, in the order  P V of group a, next S of group a, P V of group b, next S of group b : while one group's
+// softmax runs the tensor core has the other group's work, warps 2-5 / 6-9 = softmax groups a / b and output.
+// TMEM: S / P of group g at columns 128 g, O of group g at 256 + 128 g.  Every wait is bounded and reports through
 // the status word.
 //
 // Reference parity: the reference's prefill attention is FlashInfer's BatchPrefillWithPagedKVCache
@@ -27,7 +30,7 @@
 
 namespace {
 
-constexpr int BQ = 128, BKV = 128, D = 128;
+constexpr int BQ2 = 256, BKV = 128, D = 128;
 constexpr int TILE_BYTES = 128 * D * 2;  // 32 KB: [2 blocks of 64 columns][128 rows][128 B]
 constexpr int HALF_BYTES = TILE_BYTES / 2;
 
@@ -43,14 +46,12 @@ struct TcAttnParams {
   uint32_t* status;
 };
 
-constexpr int RING = 4;           // K / V tiles in flight: K_j, V_j, K_{j+1}, V_{j+1} share one ring
-constexpr int SM_WARPS = 8;       // softmax warps: two per TMEM lane quadrant, each thread owns half of a row
-constexpr int THREADS = 64 + SM_WARPS * 32;
+constexpr int GROUPS = 2;          // query tiles of 128 rows per CTA; their softmax groups alternate on the tensor core
+constexpr int THREADS = 64 + GROUPS * 128;
+constexpr float RESCALE_LOG2 = 8.f;  // O and the row sum move to a new maximum only when it grew by more than 2^8
 
 struct TcSmem {
-  uint64_t q_full, kv_full[RING], kv_empty[RING], s_full[2], s_empty[2], p_ready[2], o_full[2], o_empty[2];
-  float xmax[2][2][BQ];  // [tile parity][column half][row]: the halves' row maxima
-  float xsum[2][BQ];
+  uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[GROUPS], p_ready[GROUPS], o_full[GROUPS];
   uint32_t tmem_slot;
   int abort_flag;
 };
@@ -75,32 +76,49 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
   tmem_ld16(taddr, r);
   tmem_ld16(taddr + 16, r + 16);
 }
+// Each thread of the warp writes 16 consecutive 32-bit columns of its own TMEM lane.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]),
+        "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// D[tmem] (+)= A[tmem] * B[smem]: A is a 128-row matrix in tensor memory (row = lane, two bf16 per 32-bit column).
+__device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-__device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, %0;" ::"n"(SM_WARPS * 32) : "memory"); }
 
 __global__ void __launch_bounds__(THREADS) prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv, const TcAttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = smem_u32(smem_raw);
   uint8_t* tiles = smem_raw + (((base + 1023u) & ~1023u) - base);
-  uint8_t* q_tile = tiles;                       // 32 KB
-  uint8_t* p_tile = tiles + TILE_BYTES;          // 32 KB
-  uint8_t* ring = tiles + 2 * TILE_BYTES;        // RING x 32 KB
-  TcSmem* sh = reinterpret_cast<TcSmem*>(tiles + (2 + RING) * TILE_BYTES);
+  uint8_t* q_tile = tiles;                            // GROUPS x 32 KB
+  uint8_t* k_tile = tiles + GROUPS * TILE_BYTES;      // 2 x 32 KB
+  uint8_t* v_tile = k_tile + 2 * TILE_BYTES;          // 2 x 32 KB
+  TcSmem* sh = reinterpret_cast<TcSmem*>(v_tile + 2 * TILE_BYTES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int hq = blockIdx.y;
   const int h = hq / (p.hq / p.hkv);
 
-  // (sequence, query tile) of this CTA: late tiles (most keys) first
+  // (sequence, query tile of 256 rows) of this CTA: late tiles (most keys) first
   int b = 0, tile_in_seq = 0;
   {
     int rem = (int)gridDim.x - 1 - (int)blockIdx.x;
     for (; b < p.num_seqs; ++b) {
       const int n = p.q_indptr[b + 1] - p.q_indptr[b];
-      const int nt = (n + BQ - 1) / BQ;
+      const int nt = (n + BQ2 - 1) / BQ2;
       if (rem < nt) {
         tile_in_seq = rem;
         break;
@@ -111,16 +129,16 @@ __global__ void __launch_bounds__(THREADS) prefill_attn_tc_kernel(const __grid_c
   }
   if (threadIdx.x == 0) {
     mbar_init(&sh->q_full, 1);
-    for (int s = 0; s < RING; ++s) {
-      mbar_init(&sh->kv_full[s], 1);
-      mbar_init(&sh->kv_empty[s], 1);
+    for (int s2 = 0; s2 < 2; ++s2) {
+      mbar_init(&sh->k_full[s2], 1);
+      mbar_init(&sh->k_empty[s2], 1);
+      mbar_init(&sh->v_full[s2], 1);
+      mbar_init(&sh->v_empty[s2], 1);
     }
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&sh->s_full[s], 1);
-      mbar_init(&sh->s_empty[s], SM_WARPS);
-      mbar_init(&sh->p_ready[s], SM_WARPS);
-      mbar_init(&sh->o_full[s], 1);
-      mbar_init(&sh->o_empty[s], SM_WARPS);
+    for (int g = 0; g < GROUPS; ++g) {
+      mbar_init(&sh->s_full[g], 1);
+      mbar_init(&sh->p_ready[g], 4);
+      mbar_init(&sh->o_full[g], 1);
     }
     sh->abort_flag = 0;
     mbar_fence_init();
@@ -134,53 +152,68 @@ __global__ void __launch_bounds__(THREADS) prefill_attn_tc_kernel(const __grid_c
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem = sh->tmem_slot;  // columns: S0 0..127, S1 128..255, O0 256..383, O1 384..511
+  const uint32_t tmem = sh->tmem_slot;  // columns: S of group g at 128 g (P overwrites its first 64), O of group g at 256 + 128 g
   volatile int* abort_flag = &sh->abort_flag;
   PG_PDL_ENTRY();
 
   const int q0 = p.q_indptr[b], q_len = p.q_indptr[b + 1] - q0;
   const int kv_len = p.kv_lens[b];
-  const int row_base = tile_in_seq * BQ;
-  const int rows_here = min(BQ, q_len - row_base);
-  const int pos_base = kv_len - q_len + row_base;                 // position of the tile's first row
-  const int last_pos = pos_base + rows_here - 1;                  // last key any row of the tile may see
-  const int n_tiles = kv_len > 0 ? min(last_pos, kv_len - 1) / BKV + 1 : 0;
+  const int row_base = tile_in_seq * BQ2;
+  const int rows_here = min(BQ2, q_len - row_base);
+  const int pos_base = kv_len - q_len + row_base;  // position of the CTA's first row
+  // tiles of 128 keys each group needs: up to its last row's position
+  int n_g[GROUPS];
+#pragma unroll
+  for (int g = 0; g < GROUPS; ++g) {
+    const int rows_of_g = min(128, rows_here - g * 128);
+    n_g[g] = (rows_of_g > 0 && kv_len > 0) ? min(pos_base + g * 128 + rows_of_g - 1, kv_len - 1) / BKV + 1 : 0;
+  }
+  const int n_tiles = max(n_g[0], n_g[1]);
   const int* table_row = p.table + (long long)b * p.table_stride;
 
   if (warp == 0) {
     if (lane == 0 && n_tiles > 0) {
       const uint64_t pol = l2_policy_evict_normal();
-      mbar_expect_tx(&sh->q_full, TILE_BYTES);
-      tma_load_3d(q_tile, &tm_q, &sh->q_full, 0, hq, q0 + row_base, pol);
-      tma_load_3d(q_tile + HALF_BYTES, &tm_q, &sh->q_full, 64, hq, q0 + row_base, pol);
+      mbar_expect_tx(&sh->q_full, GROUPS * TILE_BYTES);
+#pragma unroll
+      for (int g = 0; g < GROUPS; ++g) {
+        tma_load_3d(q_tile + g * TILE_BYTES, &tm_q, &sh->q_full, 0, hq, q0 + row_base + g * 128, pol);
+        tma_load_3d(q_tile + g * TILE_BYTES + HALF_BYTES, &tm_q, &sh->q_full, 64, hq, q0 + row_base + g * 128, pol);
+      }
       const int ppt = BKV / p.page_size;  // pages per key tile
-      // load n = 2 j (K of tile j) or 2 j + 1 (V of tile j) goes to ring slot n % RING.  The tile's page ids are
-      // read in one unrolled burst (independent loads in flight together); read one by one between the TMA issues,
-      // each would cost a full memory latency and the page walk alone would take longer than the tile's MMAs.
+      // The tile's page ids are read in one unrolled burst (independent loads in flight together); read one by one
+      // between the TMA issues, each would cost a full memory latency.
       int pages[16];
-      for (int n = 0; n < 2 * n_tiles; ++n) {
-        const int j = n >> 1, kvsel = n & 1, slot = n % RING, use = n / RING;
-        if (kvsel == 0) {
-          const int pages_live = min(ppt, (kv_len - j * BKV + p.page_size - 1) / p.page_size);
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int pages_live = min(ppt, (kv_len - j * BKV + p.page_size - 1) / p.page_size);
 #pragma unroll
-          for (int pg = 0; pg < 16; ++pg) pages[pg] = (pg < pages_live) ? __ldg(table_row + j * ppt + pg) : 0;  // past the end: the padding page, keys masked
-#pragma unroll
-          for (int pg = 0; pg < 16; ++pg) {
-            if (pages[pg] < 0 || pages[pg] >= p.num_pages) {
-              atomicCAS(p.status, PG_ST_OK, PG_ST_BOUNDS | (41u << 8));
-              pages[pg] = 0;
-            }
-          }
-        }
-        if (use >= 1 && !mbar_wait(&sh->kv_empty[slot], (uint32_t)((use - 1) & 1), abort_flag)) break;
-        mbar_expect_tx(&sh->kv_full[slot], TILE_BYTES);
-        uint8_t* dst = ring + slot * TILE_BYTES;
+        for (int pg = 0; pg < 16; ++pg) pages[pg] = (pg < pages_live) ? __ldg(table_row + j * ppt + pg) : 0;  // past the end: the padding page, keys masked
 #pragma unroll
         for (int pg = 0; pg < 16; ++pg) {
-          if (pg < ppt) {
-            const int z = (pages[pg] * 2 + kvsel) * p.page_size;
-            tma_load_3d(dst + pg * p.page_size * 128, &tm_kv, &sh->kv_full[slot], 0, h, z, pol);
-            tma_load_3d(dst + HALF_BYTES + pg * p.page_size * 128, &tm_kv, &sh->kv_full[slot], 64, h, z, pol);
+          if (pages[pg] < 0 || pages[pg] >= p.num_pages) {
+            atomicCAS(p.status, PG_ST_OK, PG_ST_BOUNDS | (41u << 8));
+            pages[pg] = 0;
+          }
+        }
+        const int st = j & 1;
+#pragma unroll
+        for (int kvsel = 0; kvsel < 2; ++kvsel) {
+          uint64_t* full = kvsel ? &sh->v_full[st] : &sh->k_full[st];
+          uint64_t* empty = kvsel ? &sh->v_empty[st] : &sh->k_empty[st];
+          uint8_t* dst = (kvsel ? v_tile : k_tile) + st * TILE_BYTES;
+          if (j >= 2 && !mbar_wait(empty, (uint32_t)(((j >> 1) - 1) & 1), abort_flag)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(full, TILE_BYTES);
+#pragma unroll
+          for (int pg = 0; pg < 16; ++pg) {
+            if (pg < ppt) {
+              const int z = (pages[pg] * 2 + kvsel) * p.page_size;
+              tma_load_3d(dst + pg * p.page_size * 128, &tm_kv, full, 0, h, z, pol);
+              tma_load_3d(dst + HALF_BYTES + pg * p.page_size * 128, &tm_kv, full, 64, h, z, pol);
+            }
           }
         }
       }
@@ -189,167 +222,180 @@ __global__ void __launch_bounds__(THREADS) prefill_attn_tc_kernel(const __grid_c
     if (lane == 0 && n_tiles > 0) {
       constexpr uint32_t idesc_s = idesc_bf16(128, 128, 0);
       constexpr uint32_t idesc_o = idesc_bf16(128, 128, 1);
-      const uint32_t qa = smem_u32(q_tile);
       const uint32_t lbo = p.mn_lbo_first ? (uint32_t)HALF_BYTES : 1024u, sbo = p.mn_lbo_first ? 1024u : (uint32_t)HALF_BYTES;
       bool ok = mbar_wait(&sh->q_full, 0, abort_flag);
-      auto issue_s = [&](int j) {
-        const int s = j & 1, n = 2 * j, slot = n % RING, use = n / RING;
-        if (!mbar_wait(&sh->kv_full[slot], (uint32_t)(use & 1), abort_flag)) return false;
-        if (j >= 2 && !mbar_wait(&sh->s_empty[s], (uint32_t)(((j >> 1) - 1) & 1), abort_flag)) return false;
+      int k_seen = -1, v_seen = -1;  // tiles whose K / V arrival this thread has already observed
+      // S of group g, tile j.  K_j is released once the last group that needs it has issued its S.  S of tile j
+      // overwrites the group's previous S and P: the tensor core runs this thread's instructions in order, and the
+      // product that read that P was issued before.
+      auto issue_s = [&](int g, int j) {
+        if (j >= n_g[g]) return true;
+        const int st = j & 1;
+        if (k_seen < j) {
+          if (!mbar_wait(&sh->k_full[st], (uint32_t)((j >> 1) & 1), abort_flag)) return false;
+          k_seen = j;
+        }
         tc_fence_after();
-        const uint32_t ka = smem_u32(ring + slot * TILE_BYTES);
+        const uint32_t qa = smem_u32(q_tile + g * TILE_BYTES), ka = smem_u32(k_tile + st * TILE_BYTES);
 #pragma unroll
         for (int kb = 0; kb < 2; ++kb)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            umma_bf16_ss(tmem + (uint32_t)(s * 128), umma_desc_k_sw128(qa + kb * HALF_BYTES + k * 32), umma_desc_k_sw128(ka + kb * HALF_BYTES + k * 32), idesc_s,
+            umma_bf16_ss(tmem + (uint32_t)(g * 128), umma_desc_k_sw128(qa + kb * HALF_BYTES + k * 32), umma_desc_k_sw128(ka + kb * HALF_BYTES + k * 32), idesc_s,
                          (kb | k) ? 1u : 0u);
-        umma_commit(&sh->s_full[s]);
-        umma_commit(&sh->kv_empty[slot]);  // the K tile is free once S is done
+        umma_commit(&sh->s_full[g]);
+        const bool last_user = (g == GROUPS - 1) || j >= n_g[GROUPS - 1];
+        if (last_user) umma_commit(&sh->k_empty[st]);
         return true;
       };
-      ok = ok && issue_s(0);
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int s = j & 1, n = 2 * j + 1, slot = n % RING, use = n / RING;
-        if (j + 1 < n_tiles) ok = issue_s(j + 1);
-        if (!ok) break;
-        ok = mbar_wait(&sh->p_ready[s], (uint32_t)((j >> 1) & 1), abort_flag) && mbar_wait(&sh->kv_full[slot], (uint32_t)(use & 1), abort_flag);
-        if (ok && j >= 2) ok = mbar_wait(&sh->o_empty[s], (uint32_t)(((j >> 1) - 1) & 1), abort_flag);
-        if (!ok) break;
+      // O_g (+)= P_g V_j with P_g read from tensor memory.  V_j is released once the last group that needs it has
+      // issued its product.
+      auto issue_pv = [&](int g, int j) {
+        if (j >= n_g[g]) return true;
+        const int st = j & 1;
+        if (!mbar_wait(&sh->p_ready[g], (uint32_t)(j & 1), abort_flag)) return false;
+        if (v_seen < j) {
+          if (!mbar_wait(&sh->v_full[st], (uint32_t)((j >> 1) & 1), abort_flag)) return false;
+          v_seen = j;
+        }
         tc_fence_after();
-        const uint32_t va = smem_u32(ring + slot * TILE_BYTES), pa = smem_u32(p_tile);
+        const uint32_t va = smem_u32(v_tile + st * TILE_BYTES);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
-          umma_bf16_ss(tmem + 256u + (uint32_t)(s * 128), umma_desc_k_sw128(pa + (ks >> 2) * HALF_BYTES + (ks & 3) * 32), umma_desc_mn_sw128(va + ks * 2048, lbo, sbo), idesc_o,
-                       ks ? 1u : 0u);
-        umma_commit(&sh->o_full[s]);
-        umma_commit(&sh->kv_empty[slot]);
+          umma_bf16_ts(tmem + 256u + (uint32_t)(g * 128), tmem + (uint32_t)(g * 128) + (uint32_t)(ks * 8), umma_desc_mn_sw128(va + ks * 2048, lbo, sbo), idesc_o,
+                       (j | ks) ? 1u : 0u);
+        umma_commit(&sh->o_full[g]);
+        const bool last_user = (g == GROUPS - 1) || j >= n_g[GROUPS - 1];
+        if (last_user) umma_commit(&sh->v_empty[st]);
+        return true;
+      };
+      ok = ok && issue_s(0, 0) && issue_s(1, 0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        // while one group's softmax runs, the tensor core has the other group's product and next scores to do
+        ok = issue_pv(0, j) && issue_s(0, j + 1) && issue_pv(1, j) && issue_s(1, j + 1);
       }
     }
   } else {
-    // softmax / output warps.  TMEM lanes 32 * (warp % 4) ..: warps w and w + 4 share a quadrant; the first takes key
-    // (and output) columns 0..63 of its rows, the second 64..127.
-    const int wq = warp & 3, half = (warp - 2) >> 2;
+    // softmax / output warps: group g = one query tile, one row per thread (TMEM lane 32 * (warp % 4) + lane)
+    const int g = (warp - 2) >> 2, wq = warp & 3;
     const int r = wq * 32 + lane;
-    const int my_pos = pos_base + r;  // rows past rows_here compute garbage that is never stored
-    const uint32_t lane_base = tmem + ((uint32_t)(wq * 32) << 16) + (uint32_t)(half * 64);
-    float2 o[32];  // packed pairs: the fold and the rescale are f32x2 instructions
-#pragma unroll
-    for (int i = 0; i < 32; ++i) o[i] = make_float2(0.f, 0.f);
-    float m = -INFINITY, l = 0.f;
+    const int my_n = n_g[g];
+    const int pos0 = pos_base + g * 128;  // position of the group's first row
+    const int my_pos = pos0 + r;          // rows past the sequence compute garbage that is never stored
+    const uint32_t s_row = tmem + ((uint32_t)(wq * 32) << 16) + (uint32_t)(g * 128);
+    const uint32_t o_row = s_row + 256u;
+    float m = -INFINITY, l = 0.f;  // m: the maximum the exponentials refer to (may lag the true maximum by up to 2^8)
     bool ok = true;
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      const int s = j & 1;
-      ok = mbar_wait(&sh->s_full[s], (uint32_t)((j >> 1) & 1), abort_flag);
+    for (int j = 0; j < my_n && ok; ++j) {
+      ok = mbar_wait(&sh->s_full[g], (uint32_t)(j & 1), abort_flag);
       if (!ok) break;
       tc_fence_after();
-      const int key0 = j * BKV + half * 64;
-      const bool need_mask = j * BKV + BKV - 1 > min(pos_base, kv_len - 1);
-      const int limit = min(my_pos, kv_len - 1) - key0;  // columns 0 .. limit of this thread's half are visible
-      uint32_t v[64];
-      tmem_ld32(lane_base + (uint32_t)(s * 128), v);
-      tmem_ld32(lane_base + (uint32_t)(s * 128) + 32, v + 32);
-      tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sh->s_empty[s]);  // S is in registers
+      const int key0 = j * BKV;
+      const bool need_mask = key0 + BKV - 1 > min(pos0, kv_len - 1);
+      const int limit = min(my_pos, kv_len - 1) - key0;  // columns 0 .. limit are visible to this row
+      // pass 1: row maximum of the raw scores
       float mx_raw = -INFINITY;
-      if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < 64; ++i)
-          if (i <= limit) mx_raw = fmaxf(mx_raw, __uint_as_float(v[i]));
-      } else {
+      for (int c = 0; c < BKV; c += 64) {
+        uint32_t v[64];
+        tmem_ld32(s_row + c, v);
+        tmem_ld32(s_row + c + 32, v + 32);
+        tmem_ld_wait();
+        if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) mx_raw = fmaxf(mx_raw, __uint_as_float(v[i]));
+          for (int i = 0; i < 64; ++i)
+            if (c + i <= limit) mx_raw = fmaxf(mx_raw, __uint_as_float(v[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) mx_raw = fmaxf(mx_raw, __uint_as_float(v[i]));
+        }
       }
-      sh->xmax[s][half][r] = mx_raw;
-      softmax_bar();
-      const float mx = fmaxf(m, fmaxf(sh->xmax[s][0][r], sh->xmax[s][1][r]) * p.scale_log2);
-      const float alpha = (mx == -INFINITY) ? 1.f : ex2_approx(m - mx);
-      const float neg = (mx == -INFINITY) ? 0.f : -mx;
-      // fold in the previous tile's P V product and move to the new maximum; its completion also frees the P tile
+      const float mx = mx_raw * p.scale_log2;
+      // the previous product of this group must be complete before O is rescaled
       if (j >= 1) {
-        const int sp = (j - 1) & 1;
-        ok = mbar_wait(&sh->o_full[sp], (uint32_t)(((j - 1) >> 1) & 1), abort_flag);
+        ok = mbar_wait(&sh->o_full[g], (uint32_t)((j - 1) & 1), abort_flag);
         if (!ok) break;
         tc_fence_after();
-#pragma unroll
-        for (int c = 0; c < 64; c += 32) {
-          uint32_t w[32];
-          tmem_ld32(lane_base + 256u + (uint32_t)(sp * 128) + c, w);
-          tmem_ld_wait();
-          if (alpha == 1.f) {
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) o[(c + i) >> 1] = __fadd2_rn(o[(c + i) >> 1], make_float2(__uint_as_float(w[i]), __uint_as_float(w[i + 1])));
-          } else {
-            const float2 a2 = make_float2(alpha, alpha);
-#pragma unroll
-            for (int i = 0; i < 32; i += 2)
-              o[(c + i) >> 1] = __fmul2_rn(__fadd2_rn(o[(c + i) >> 1], make_float2(__uint_as_float(w[i]), __uint_as_float(w[i + 1]))), a2);
-          }
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sh->o_empty[sp]);
       }
-      // P = exp2(S * scale - max) as bf16 into this half's 64-key block of the swizzled A tile
-      uint8_t* p_row = p_tile + half * HALF_BYTES + r * 128;
+      // move to a new maximum only when it grew by more than the threshold (or there was none yet)
+      float alpha = 1.f;
+      if (mx > m + RESCALE_LOG2 || (m == -INFINITY && mx > -INFINITY)) {
+        alpha = (m == -INFINITY) ? 0.f : ex2_approx(m - mx);
+        m = mx;
+      }
+      if (j >= 1 && __any_sync(0xFFFFFFFFu, alpha != 1.f)) {
+        const float2 a2 = make_float2(alpha, alpha);
+#pragma unroll
+        for (int c = 0; c < D; c += 32) {
+          uint32_t w[32];
+          tmem_ld32(o_row + c, w);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float2 t2 = __fmul2_rn(make_float2(__uint_as_float(w[i]), __uint_as_float(w[i + 1])), a2);
+            w[i] = __float_as_uint(t2.x);
+            w[i + 1] = __float_as_uint(t2.y);
+          }
+          tmem_st16(o_row + c, w);
+          tmem_st16(o_row + c + 16, w + 16);
+        }
+      }
+      l *= alpha;
+      const float neg = (m == -INFINITY) ? 0.f : -m;
+      // pass 2: P = exp2(S * scale - m) as bf16, two per 32-bit column, over the columns of S already consumed
+      // (scores 0..63 become P columns 0..31 before scores 64..127 are read); row sum
       float2 sum2 = make_float2(0.f, 0.f);
       const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), ng2 = make_float2(neg, neg);
 #pragma unroll
-      for (int c8 = 0; c8 < 8; ++c8) {
-        uint32_t packed[4];
+      for (int c = 0; c < BKV; c += 64) {
+        uint32_t v[64];
+        tmem_ld32(s_row + c, v);
+        tmem_ld32(s_row + c + 32, v + 32);
+        tmem_ld_wait();
+        uint32_t packed[32];
 #pragma unroll
-        for (int i = 0; i < 8; i += 2) {
-          const int col = c8 * 8 + i;
-          const float2 t2 = __ffma2_rn(make_float2(__uint_as_float(v[col]), __uint_as_float(v[col + 1])), sc2, ng2);
+        for (int i = 0; i < 64; i += 2) {
+          const float2 t2 = __ffma2_rn(make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), sc2, ng2);
           float2 e = make_float2(ex2_approx(t2.x), ex2_approx(t2.y));
           if (need_mask) {
-            if (col > limit) e.x = 0.f;
-            if (col + 1 > limit) e.y = 0.f;
+            if (c + i > limit) e.x = 0.f;
+            if (c + i + 1 > limit) e.y = 0.f;
           }
           sum2 = __fadd2_rn(sum2, e);
           const bf162 pr = __floats2bfloat162_rn(e.x, e.y);
           packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&pr);
         }
-        *reinterpret_cast<uint4*>(p_row + ((c8 ^ (r & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        tmem_st16(s_row + (c >> 1), packed);
+        tmem_st16(s_row + (c >> 1) + 16, packed + 16);
       }
-      l = l * alpha + sum2.x + sum2.y;
-      m = mx;
-      fence_proxy_async_smem();
+      tmem_st_wait();
+      l += sum2.x + sum2.y;
+      tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&sh->p_ready[s]);
+      if (lane == 0) mbar_arrive(&sh->p_ready[g]);
     }
-    if (ok && n_tiles > 0) {
-      const int sp = (n_tiles - 1) & 1;
-      ok = mbar_wait(&sh->o_full[sp], (uint32_t)(((n_tiles - 1) >> 1) & 1), abort_flag);
-      if (ok) {
-        tc_fence_after();
+    const int rows_g = min(128, rows_here - g * 128);
+    if (ok && my_n > 0) {
+      ok = mbar_wait(&sh->o_full[g], (uint32_t)((my_n - 1) & 1), abort_flag);
+      tc_fence_after();
+    }
+    const float inv = (ok && l > 0.f) ? 1.f / l : 0.f;
+    bf16* dst = p.out + ((long long)(q0 + row_base + g * 128 + r) * p.hq + hq) * D;
 #pragma unroll
-        for (int c = 0; c < 64; c += 32) {
-          uint32_t w[32];
-          tmem_ld32(lane_base + 256u + (uint32_t)(sp * 128) + c, w);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) o[(c + i) >> 1] = __fadd2_rn(o[(c + i) >> 1], make_float2(__uint_as_float(w[i]), __uint_as_float(w[i + 1])));
-        }
+    for (int c = 0; c < D; c += 32) {
+      uint32_t w[32];
+      if (my_n > 0) {  // uniform per group
+        tmem_ld32(o_row + c, w);
+        tmem_ld_wait();
       }
-    }
-    sh->xsum[half][r] = l;
-    softmax_bar();
-    if (r < rows_here) {
-      const float lt = sh->xsum[0][r] + sh->xsum[1][r];
-      const float inv = (ok && lt > 0.f) ? 1.f / lt : 0.f;
-      bf16* dst = p.out + ((long long)(q0 + row_base + r) * p.hq + hq) * D + half * 64;
+      if (r < rows_g) {
 #pragma unroll
-      for (int c = 0; c < 64; c += 8) {
-        float f[8];
+        for (int c8 = 0; c8 < 32; c8 += 8) {
+          float f[8];
 #pragma unroll
-        for (int i = 0; i < 8; i += 2) {
-          f[i] = o[(c + i) >> 1].x * inv;
-          f[i + 1] = o[(c + i) >> 1].y * inv;
+          for (int i = 0; i < 8; ++i) f[i] = my_n > 0 ? __uint_as_float(w[c8 + i]) * inv : 0.f;
+          *reinterpret_cast<bf16x8*>(dst + c + c8) = pack8(f);
         }
-        *reinterpret_cast<bf16x8*>(dst + c) = pack8(f);
       }
     }
   }
@@ -401,7 +447,7 @@ int g_mn_variant = -1;
 extern "C" void pg_prefill_attention_tc_variant(int v) { g_mn_variant = v; }
 
 // q [T, hq, 128] bf16 (contiguous), kv_layer [pages, 2, page_size, hkv, 128], out [T, hq * 128].  `q_tiles` = sum over the
-// sequences of ceil(query rows / 128).
+// sequences of ceil(query rows / 256).
 extern "C" int pg_prefill_attention_tc(const void* q, const void* kv_layer, void* out, const void* q_indptr, const void* kv_lens, const void* table, int table_stride,
                                        int num_seqs, int tokens, int hq, int hkv, int dim, int page_size, long long num_pages, float scale, int q_tiles, void* status,
                                        cudaStream_t stream) {
@@ -411,7 +457,7 @@ extern "C" int pg_prefill_attention_tc(const void* q, const void* kv_layer, void
   PG_REQUIRE(hq % hkv == 0, "query heads %d are not a multiple of the KV heads %d", hq, hkv);
   if (q_tiles == 0 || tokens == 0) return PG_OK;
   CUtensorMap tm_q, tm_kv;
-  int rc = make_tmap_rows_heads(&tm_q, q, tokens, hq, BQ);
+  int rc = make_tmap_rows_heads(&tm_q, q, tokens, hq, 128);
   if (rc != PG_OK) return rc;
   rc = make_tmap_rows_heads(&tm_kv, kv_layer, num_pages * 2 * page_size, hkv, page_size);
   if (rc != PG_OK) return rc;
@@ -429,7 +475,7 @@ extern "C" int pg_prefill_attention_tc(const void* q, const void* kv_layer, void
   p.scale_log2 = scale * 1.4426950408889634f;
   p.mn_lbo_first = g_mn_variant < 0 ? 1 : g_mn_variant;
   p.status = (uint32_t*)status;
-  const size_t smem = 1024 + (2 + RING) * (size_t)TILE_BYTES + sizeof(TcSmem) + 64;
+  const size_t smem = 1024 + (GROUPS + 4) * (size_t)TILE_BYTES + sizeof(TcSmem) + 64;
   static bool attr_done = false;
   if (!attr_done) {
     PG_CUDA(cudaFuncSetAttribute(prefill_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

@@ -591,7 +591,7 @@ def paged_attention(q, kv_layer, meta: AttnMeta, scale=None, window=0, out: Opti
     if (n_pf > 0 and d == 128 and window == 0 and _PREFILL_TC and not _BATCH_INVARIANT and 128 % page_size == 0 and q.is_contiguous() and max(qi[b + 1] - qi[b] for b in range(n_pf)) >= _PREFILL_TC_MIN_ROWS
             and (meta.h_kv_lens is None or max(meta.h_kv_lens[:n_pf]) >= _PREFILL_TC_MIN_KV)):
         # tcgen05 kernel: 128 query rows of one head per CTA, S and P V on the tensor cores, accumulators in TMEM
-        q_tiles = sum((qi[b + 1] - qi[b] + 127) // 128 for b in range(n_pf))
+        q_tiles = sum((qi[b + 1] - qi[b] + 255) // 256 for b in range(n_pf))
         rc = lib().pg_prefill_attention_tc(_ptr(q), _ptr(kv_layer), _ptr(out), _ptr(meta.q_indptr), _ptr(meta.kv_lens), _ptr(table), _ci(table.stride(0)), _ci(n_pf), _ci(qi[n_pf]),
                                            _ci(hq), _ci(hkv), _ci(d), _ci(page_size), _ll(kv_layer.shape[0]), _cf(scale), _ci(q_tiles), _ptr(c.status), _stream())
         _check(rc, c)
