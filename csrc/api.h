@@ -77,6 +77,8 @@ int pg_qk_norm_rope_append(const void* qkv, long long ld, const void* q_w, const
                            int rot, int page_size, long long num_pages, int max_pos, int gated, int offset, float eps, void* status,
                            cudaStream_t stream);
 
+int pg_repack_int4_pairs(const void* in, void* out, long long words, cudaStream_t stream);
+
 // ---- prefill attention on tcgen05 (attention_tc.cu) ----------------------------------------
 int pg_prefill_attention_tc(const void* q, const void* kv_layer, void* out, const void* q_indptr, const void* kv_lens, const void* table, int table_stride,
                             int num_seqs, int tokens, int hq, int hkv, int dim, int page_size, long long num_pages, float scale, int q_tiles, void* status,

@@ -372,3 +372,43 @@ extern "C" int pg_qk_norm_rope_append(const void* qkv, long long ld, const void*
   PG_LAUNCH_CHECK();
   return PG_OK;
 }
+
+
+// ---------------------------------------------------------------------------------
+// Load-time repack of compressed-tensors INT4 words: nibble j of the output word holds element
+// (0, 2, 4, 6, 1, 3, 5, 7)[j] of the input word, so that the grouped GEMM gets two consecutive elements as one
+// bf16 pair from a shift and a mask.  One 16-byte vector (32 weights) per thread.
+// ---------------------------------------------------------------------------------
+namespace {
+__device__ __forceinline__ uint32_t pair_nibbles(uint32_t w) {
+  // even elements to the low half, odd elements to the high half, order kept inside each half
+  uint32_t lo = 0, hi = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    lo |= ((w >> (8 * i)) & 0xFu) << (4 * i);
+    hi |= ((w >> (8 * i + 4)) & 0xFu) << (4 * i);
+  }
+  return lo | (hi << 16);
+}
+__global__ void __launch_bounds__(256) repack_int4_pairs_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, long long vecs, const uint32_t* __restrict__ tail_in,
+                                                                uint32_t* __restrict__ tail_out, int tail) {
+  const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (i < vecs) {
+    const uint4 v = in[i];
+    out[i] = make_uint4(pair_nibbles(v.x), pair_nibbles(v.y), pair_nibbles(v.z), pair_nibbles(v.w));
+  }
+  if (i < tail) tail_out[i] = pair_nibbles(tail_in[i]);
+}
+}  // namespace
+
+extern "C" int pg_repack_int4_pairs(const void* in, void* out, long long words, cudaStream_t stream) {
+  if (words == 0) return PG_OK;
+  PG_REQUIRE((((uintptr_t)in | (uintptr_t)out) & 15) == 0, "repack_int4_pairs: buffers must be 16-byte aligned");
+  const long long vecs = words / 4;
+  const int tail = (int)(words - vecs * 4);
+  const long long threads = vecs > tail ? vecs : tail;
+  repack_int4_pairs_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>((const uint4*)in, (uint4*)out, vecs, (const uint32_t*)in + vecs * 4,
+                                                                                 (uint32_t*)out + vecs * 4, tail);
+  PG_LAUNCH_CHECK();
+  return PG_OK;
+}

@@ -328,6 +328,7 @@ class EngineConfig:
     run_ahead: bool = True  # greedy graph decode launches the next step before reading this one's tokens
     tune_gc: bool = False  # freeze start-up objects and raise the collector thresholds (utils/runtime.py); the server and the benches turn it on
     decode_sm_pct: int = 50
+    decode_sm_split: bool = False  # --decode-sm-pct given: the prefill lane gets its own SM partition (green contexts)
     enable_lora: bool = False
     max_loras: int = 4
     max_lora_rank: int = 64

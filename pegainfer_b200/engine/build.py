@@ -135,6 +135,8 @@ def build_engine(ecfg: EngineConfig, mcfg: Optional[ModelConfig] = None, device=
         spec = build_spec(ecfg, model, executor)
         if hasattr(executor, "enable_verify_graph"):
             executor.enable_verify_graph(1 + int(getattr(spec, "draft_len", 1)))
+    if ecfg.decode_overlap and getattr(ecfg, "decode_sm_split", False) and device.type == "cuda" and hasattr(executor, "enable_sm_split"):
+        executor.enable_sm_split(ecfg.decode_sm_pct)
     if ecfg.precapture_graphs and getattr(executor, "_graphs", None) is not None:
         executor._graphs.precapture(True, ecfg.max_decode_batch)
     sched = ContinuousScheduler(executor, pool, scfg, spec=spec, host_tier=host_tier)

@@ -229,8 +229,8 @@ class MlaMoeModel:
             for key, names in (("w13", ("gate_proj", "up_proj")), ("w2", ("down_proj",))):
                 pk = torch.stack([torch.cat([src.get(f"{m}experts.{e}.{n}.weight_packed", dev, torch.int32) for n in names], 0) for e in range(e0, e1)])
                 sc = torch.stack([torch.cat([src.get(f"{m}experts.{e}.{n}.weight_scale", dev, dt) for n in names], 0) for e in range(e0, e1)])
-                if dev.type == "cuda":  # nibble order of the sm_100a grouped GEMM (load-time repack)
-                    from ..ops.reference import repack_int4_pairs
+                if dev.type == "cuda":  # nibble order of the sm_100a grouped GEMM (load-time repack kernel)
+                    from ..ops.cuda import repack_int4_pairs
 
                     pk = repack_int4_pairs(pk)
                 ex[key + "_packed"], ex[key + "_scale"] = pk, sc

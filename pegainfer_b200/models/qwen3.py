@@ -235,8 +235,12 @@ class Qwen3Model:
         down, the next layer's qkv): steps of up to 64 rows, hidden size a multiple of 128 up to 8192."""
         import os
 
+        from ..ops import cuda as K
+
         h = self.cfg.hidden_size
-        return os.environ.get("PEGAINFER_DECODE_CHAIN", "1") != "0" and h % 128 == 0 and h <= 8192 and self.gate_up_interleaved
+        # never on the prefill lane: the chain kernel's grid barriers need all of its CTAs resident at once, which a
+        # second chain kernel on the main stream, or a lane confined to part of the SMs, does not allow
+        return os.environ.get("PEGAINFER_DECODE_CHAIN", "1") != "0" and h % 128 == 0 and h <= 8192 and self.gate_up_interleaved and K._LANE[0] == 0
 
     def _forward_chain(self, x, residual, meta, kv, aux_layers, K):
         cfg, eps, n = self.cfg, self.cfg.rms_eps, len(self.layers)

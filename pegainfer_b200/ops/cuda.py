@@ -788,11 +788,20 @@ def paired_int4(w):
         return w
     cp = getattr(w, "_pg_paired_copy", None)
     if cp is None:
-        from .reference import repack_int4_pairs
-
         cp = repack_int4_pairs(w)
         w._pg_paired_copy = cp
     return cp
+
+
+def repack_int4_pairs(packed):
+    """Load-time repack of compressed-tensors INT4 words (int32, eight nibbles each) into the pair-interleaved nibble
+    order of the grouped GEMM, on the device."""
+    assert packed.dtype == torch.int32 and packed.is_cuda
+    src = packed.contiguous()
+    out = torch.empty_like(src)
+    _check(lib().pg_repack_int4_pairs(_ptr(src), _ptr(out), _ll(src.numel()), _stream()), ctx(src.device))
+    out._pg_nibbles = "paired"
+    return out
 
 
 def grouped_gemm(xs, offsets, w, scales=None, bn: int = 16):

@@ -166,6 +166,7 @@ class TorchExecutor(ModelExecutor):
         self.mtp = None  # set by spec.MtpSpec
         self.aux_sink = None  # set by drafters that read target hidden states: .aux_layers, .observe(kind, seqs, meta, aux)
         self._lane_stream = None  # second stream of the decode-overlap prefill lane
+        self.sm_split = None  # utils.green_ctx.SmSplit when the lane is confined to its own SM partition
         self._graphs = None
         if self.use_graph:
             from ..utils.cuda_graph import DecodeGraphs
@@ -197,6 +198,13 @@ class TorchExecutor(ModelExecutor):
         seqs = batch.seqs
         return (self._graphs is not None and self.mtp is None and self.aux_sink is None and batch.is_decode() and len(seqs) <= self.max_decode_batch
                 and all(s.sample and s.logprobs == 0 and s.lora_slot < 0 for s in seqs))
+
+    def enable_sm_split(self, decode_pct: int) -> None:
+        """Confine the prefill lane to ``100 - decode_pct`` percent of the SMs (green contexts)."""
+        from ..utils.green_ctx import SmSplit
+
+        self.sm_split = SmSplit(self.device, decode_pct)
+        self._lane_stream = self.sm_split.prefill_stream
 
     def enable_verify_graph(self, span: int) -> None:
         """Size the decode graphs for verify steps of ``span`` rows per request (speculative decoding):

@@ -50,9 +50,8 @@ def _qwen3_validate(ns, provided):
         log.warning("LoRA requests run outside CUDA graphs; graph replay stays on for adapter-free batches")
     if ns.decode_overlap and ns.tp_size > 1:
         raise SystemExit("--decode-overlap is not available together with tensor parallelism")
-    if "decode_sm_pct" in provided:
-        # the overlap lane shares the SMs between its two streams; a fixed SM split (green contexts) is not built
-        raise SystemExit("--decode-sm-pct is not supported: --decode-overlap runs prefill and decode on two streams that share the SMs")
+    if "decode_sm_pct" in provided and not ns.decode_overlap:
+        raise SystemExit("--decode-sm-pct splits the SMs between the decode stream and the prefill lane: it needs --decode-overlap")
 
 
 LINES = [
@@ -180,6 +179,7 @@ def resolve(argv: Optional[list] = None):
     provided = provided_flags(argv, parser)
     validate_flags(line, provided)
     ecfg = engine_config_from(ns)
+    ecfg.decode_sm_split = "decode_sm_pct" in provided
     ecfg.validate()
     line.validate(ns, provided)
     if mcfg.family == "qwen35":

@@ -433,3 +433,26 @@ def test_pd_pair_on_gpu_hands_blocks_over_by_hash():
         assert same >= 12, (got, want)  # 24 tokens in all
     finally:
         pd.shutdown()
+
+
+def test_decode_overlap_with_sm_split_matches_plain_engine():
+    """--decode-sm-pct: the prefill lane runs on a green-context stream that owns part of the SMs; results must not change."""
+    plain = engine(True)
+    split = engine(True, decode_overlap=True, decode_sm_split=True, decode_sm_pct=60, max_prefill_tokens=64)
+    try:
+        assert split.executor.sm_split is not None
+        sp = split.executor.sm_split
+        assert sp.decode_sms + sp.prefill_sms == torch.cuda.get_device_properties(0).multi_processor_count and sp.prefill_sms >= 8
+        ps = prompts(4, seed=21)
+        a = plain.generate(ps[:2], max_tokens=10) + plain.generate(ps, max_tokens=12)
+        b = split.generate(ps[:2], max_tokens=10) + split.generate(ps, max_tokens=12)
+        agree = sum(x == y for (ta, _, _), (tb, _, _) in zip(a, b) for x, y in zip(ta, tb))
+        total = sum(len(ta) for ta, _, _ in a)
+        assert [ta[0] for ta, _, _ in a] == [tb[0] for tb, _, _ in b] and agree >= 0.8 * total, (agree, total)
+        from pegainfer_b200.ops import cuda as K
+
+        torch.cuda.synchronize()
+        assert K.read_status("cuda:0") == 0
+    finally:
+        plain.shutdown()
+        split.shutdown()

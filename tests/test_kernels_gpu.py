@@ -847,3 +847,15 @@ def test_tcgen05_prefill_attention_matches_reference(page):
         _native.load().pg_prefill_attention_tc_variant(ctypes.c_int(-1))
     assert errs[1] < 0.03, errs
     status_clean()
+
+
+def test_int4_repack_kernel_matches_reference_nibble_order():
+    K = cu()
+    g = torch.Generator(device=DEV).manual_seed(2)
+    for shape in ((3, 256, 64), (5, 7), (1, 1, 1030)):
+        w = torch.randint(-(2 ** 31), 2 ** 31 - 1, shape, dtype=torch.int32, device=DEV, generator=g)
+        got = K.repack_int4_pairs(w)
+        want = R.repack_int4_pairs(w)
+        torch.cuda.synchronize()
+        assert torch.equal(got, want) and got._pg_nibbles == "paired"
+        assert torch.equal(R.unrepack_int4_pairs(got), w)
