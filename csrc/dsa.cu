@@ -96,7 +96,7 @@ __global__ void __launch_bounds__(128) dsa_q_rope_kernel(bf16* __restrict__ q, c
 }
 
 // ---------------------------------------------------------------------------------------------
-// scores on tcgen05: one CTA = (key tile of 128, query row)
+// scores on tcgen05: one CTA = (strip of key tiles of 128, query row)
 // ---------------------------------------------------------------------------------------------
 constexpr int SC_KEYS = 128;
 constexpr int SC_D = 128;           // index head dim
@@ -107,6 +107,8 @@ struct ScoreSmem {
   int abort_flag;
 };
 
+constexpr int SC_STRIP = 8;  // key tiles per CTA: set-up (TMEM, barrier, Q staging) once per strip, loads of the next tile under the current one
+
 __global__ void __launch_bounds__(128) dsa_scores_kernel(const bf16* __restrict__ q, const float* __restrict__ w, const bf16* __restrict__ cache,
                                                           const int* __restrict__ unit_seq, const int* __restrict__ q_indptr, const int* __restrict__ kv_lens,
                                                           const int* __restrict__ table, int table_stride, int page_size, long long num_pages, int heads,
@@ -114,11 +116,11 @@ __global__ void __launch_bounds__(128) dsa_scores_kernel(const bf16* __restrict_
   extern __shared__ uint8_t smem_raw[];
   // tiles want 1024-byte alignment (128-byte swizzle atoms of 8 rows)
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* k_tile = tiles;                       // [2 k-blocks][128 keys][128 B]
-  uint8_t* q_tile = tiles + 2 * SC_KEYS * 128;   // [2 k-blocks][heads][128 B]
+  uint8_t* k_tile = tiles;                           // 2 buffers x [2 k-blocks][128 keys][128 B]
+  uint8_t* q_tile = tiles + 2 * 2 * SC_KEYS * 128;   // [2 k-blocks][heads][128 B]
   ScoreSmem* sh = reinterpret_cast<ScoreSmem*>(q_tile + 2 * SC_MAX_HEADS * 128);
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int t = blockIdx.y, kt = blockIdx.x;
+  const int t = blockIdx.y, strip = blockIdx.x;
   if (tid == 0) {
     mbar_init(&sh->done, 1);
     sh->abort_flag = 0;
@@ -128,77 +130,99 @@ __global__ void __launch_bounds__(128) dsa_scores_kernel(const bf16* __restrict_
   const int b = unit_seq[t];
   const int kv_len = kv_lens[b];
   const int qpos = kv_len - (q_indptr[b + 1] - t);  // rows of a sequence end at its last key
-  const int key0 = kt * SC_KEYS;
-  float* out = scores + (long long)t * width + key0;
-  const int live = min(min(kv_len, qpos + 1) - key0, SC_KEYS);  // keys of this tile the row may see
-  if (live <= 0) {  // whole tile in the row's future (or beyond its sequence)
-    if (key0 + tid < width) out[tid] = -INFINITY;
-    return;
-  }
+  const int visible = min(kv_len, qpos + 1);        // keys 0 .. visible - 1 may be seen by this row
+  const int tile0 = strip * SC_STRIP;
+  const int tiles_total = (width + SC_KEYS - 1) / SC_KEYS;
+  const int tile_end = min(tile0 + SC_STRIP, tiles_total);
+  const int live_tiles = min(tile_end, (visible + SC_KEYS - 1) / SC_KEYS) - tile0;  // tiles of the strip with a visible key
+  // tiles wholly in the row's future (or past its sequence): just the fill value
+  for (int jt = tile0 + max(live_tiles, 0); jt < tile_end; ++jt)
+    if (jt * SC_KEYS + tid < width) scores[(long long)t * width + jt * SC_KEYS + tid] = -INFINITY;
+  if (live_tiles <= 0) return;
   if (warp == 0) {
     tmem_alloc(&sh->tmem_slot, 64);
     tmem_relinquish();
   }
-  // stage K (keys x 128 dims) and Q (heads x 128 dims) as 128-byte-swizzled K-major tiles: 16-byte chunk c of row r
-  // lives at chunk (c & 7) ^ (r & 7) of row r in k-block c >> 3
-  for (int i = tid; i < SC_KEYS * 16; i += 128) {
-    const int r = i >> 4, c = i & 15;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (r < live) {
+  const int* table_row = table + (long long)b * table_stride;
+  // this thread's 16 chunks of a key tile: chunk i -> key row (i >> 4), 16-byte column (i & 15), i = tid + 128 n
+  auto load_tile = [&](int jt, uint4* regs) {
+    const int key0 = jt * SC_KEYS;
+#pragma unroll
+    for (int n = 0; n < 16; ++n) {
+      const int i = tid + 128 * n, r = i >> 4, c = i & 15;
       const int j = key0 + r;
-      const long long page = table[(long long)b * table_stride + j / page_size];
-      if (page >= 0 && page < num_pages) {
-        v = *reinterpret_cast<const uint4*>(cache + ((page * page_size + j % page_size) * SC_D + c * 8));
-      } else {
-        atomicCAS(status, PG_ST_OK, PG_ST_BOUNDS | (22u << 8));
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (j < visible) {
+        const long long page = table_row[j / page_size];
+        if (page >= 0 && page < num_pages) v = *reinterpret_cast<const uint4*>(cache + ((page * page_size + j % page_size) * SC_D + c * 8));
+        else atomicCAS(status, PG_ST_OK, PG_ST_BOUNDS | (22u << 8));
       }
+      regs[n] = v;
     }
-    *reinterpret_cast<uint4*>(k_tile + (c >> 3) * (SC_KEYS * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
-  }
+  };
+  // 16-byte chunk c of row r lives at chunk (c & 7) ^ (r & 7) of row r in k-block c >> 3 (128-byte swizzle, K-major)
+  auto store_tile = [&](uint8_t* dst, const uint4* regs) {
+#pragma unroll
+    for (int n = 0; n < 16; ++n) {
+      const int i = tid + 128 * n, r = i >> 4, c = i & 15;
+      *reinterpret_cast<uint4*>(dst + (c >> 3) * (SC_KEYS * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = regs[n];
+    }
+  };
+  uint4 regs[16];
+  load_tile(tile0, regs);
   for (int i = tid; i < heads * 16; i += 128) {
     const int r = i >> 4, c = i & 15;
     const uint4 v = *reinterpret_cast<const uint4*>(q + (((long long)t * heads + r) * SC_D + c * 8));
     *reinterpret_cast<uint4*>(q_tile + (c >> 3) * (SC_MAX_HEADS * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
   }
+  store_tile(k_tile, regs);
   fence_proxy_async_smem();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sh->tmem_slot;
-  if (tid == 0) {
-    const uint32_t idesc = umma_idesc_bf16_f32(128, (uint32_t)heads);
-    const uint32_t ka = smem_u32(k_tile), qa = smem_u32(q_tile);
+  const uint32_t idesc = umma_idesc_bf16_f32(128, (uint32_t)heads);
+  const uint32_t qa = smem_u32(q_tile);
+  const float* wt = w + (long long)t * heads;
+  bool ok = true;
+  for (int lt = 0; lt < live_tiles && ok; ++lt) {
+    const int jt = tile0 + lt, buf = lt & 1;
+    if (tid == 0) {
+      const uint32_t ka = smem_u32(k_tile + buf * (2 * SC_KEYS * 128));
 #pragma unroll
-    for (int kb = 0; kb < 2; ++kb)
+      for (int kb = 0; kb < 2; ++kb)
 #pragma unroll
-      for (int k = 0; k < 4; ++k)
-        umma_bf16_ss(tmem, umma_desc_k_sw128(ka + kb * (SC_KEYS * 128) + k * 32), umma_desc_k_sw128(qa + kb * (SC_MAX_HEADS * 128) + k * 32), idesc,
-                     (kb | k) ? 1u : 0u);
-    umma_commit(&sh->done);
-  }
-  const bool ok = mbar_wait(&sh->done, 0, &sh->abort_flag);
-  tc_fence_after();
-  if (ok) {
-    const uint32_t t_row = tmem + ((uint32_t)(warp * 32) << 16);
-    const float* wt = w + (long long)t * heads;
-    float acc = 0.f;
-    for (int c = 0; c < heads; c += 16) {
-      uint32_t v[16];
-      tmem_ld16(t_row + c, v);
-      tmem_ld_wait();
-#pragma unroll
-      for (int j = 0; j < 16; ++j) acc += wt[c + j] * fmaxf(__uint_as_float(v[j]), 0.f);
+        for (int k = 0; k < 4; ++k)
+          umma_bf16_ss(tmem, umma_desc_k_sw128(ka + kb * (SC_KEYS * 128) + k * 32), umma_desc_k_sw128(qa + kb * (SC_MAX_HEADS * 128) + k * 32), idesc, (kb | k) ? 1u : 0u);
+      umma_commit(&sh->done);
     }
-    if (key0 + tid < width) out[tid] = tid < live ? acc : -INFINITY;
-  } else if (tid == 0) {
-    atomicCAS(status, PG_ST_OK, PG_ST_TIMEOUT | (22u << 8));
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 0) {
+    const bool more = lt + 1 < live_tiles;
+    if (more) load_tile(jt + 1, regs);  // in flight while the tensor core and the read-back work on this tile
+    ok = mbar_wait(&sh->done, (uint32_t)(lt & 1), &sh->abort_flag);
     tc_fence_after();
-    tmem_dealloc(tmem, 64);
+    if (ok) {
+      const uint32_t t_row = tmem + ((uint32_t)(warp * 32) << 16);
+      float acc = 0.f;
+      for (int c = 0; c < heads; c += 16) {
+        uint32_t v[16];
+        tmem_ld16(t_row + c, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) acc += wt[c + j] * fmaxf(__uint_as_float(v[j]), 0.f);
+      }
+      const int key = jt * SC_KEYS + tid;
+      if (key < width) scores[(long long)t * width + key] = key < visible ? acc : -INFINITY;
+    }
+    if (more) {
+      store_tile(k_tile + (buf ^ 1) * (2 * SC_KEYS * 128), regs);
+      fence_proxy_async_smem();
+    }
+    tc_fence_before();
+    __syncthreads();  // the accumulator has been read by every warp and the next tile is staged
+    tc_fence_after();
   }
+  if (!ok && tid == 0) atomicCAS(status, PG_ST_OK, PG_ST_TIMEOUT | (22u << 8));
+  if (warp == 0) tmem_dealloc(tmem, 64);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -356,13 +380,13 @@ extern "C" int pg_dsa_scores(const void* q, const void* w, const void* cache, co
   PG_REQUIRE(d == SC_D, "dsa_scores: built for an index head dim of 128 (got %d)", d);
   PG_REQUIRE(heads % 16 == 0 && heads >= 16 && heads <= SC_MAX_HEADS, "dsa_scores: %d index heads (need a multiple of 16 up to 64)", heads);
   if (tokens == 0 || width == 0) return PG_OK;
-  const size_t smem = 1024 + 2 * SC_KEYS * 128 + 2 * SC_MAX_HEADS * 128 + sizeof(ScoreSmem);
+  const size_t smem = 1024 + 2 * 2 * SC_KEYS * 128 + 2 * SC_MAX_HEADS * 128 + sizeof(ScoreSmem);
   static bool attr_done = false;
   if (!attr_done) {
     PG_CUDA(cudaFuncSetAttribute(dsa_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attr_done = true;
   }
-  PG_CUDA(launch_pdl(dsa_scores_kernel, dim3((unsigned)ceil_div(width, SC_KEYS), (unsigned)tokens), dim3(128), smem, stream, (const bf16*)q, (const float*)w,
+  PG_CUDA(launch_pdl(dsa_scores_kernel, dim3((unsigned)ceil_div(ceil_div(width, SC_KEYS), SC_STRIP), (unsigned)tokens), dim3(128), smem, stream, (const bf16*)q, (const float*)w,
                      (const bf16*)cache, (const int*)unit_seq, (const int*)q_indptr, (const int*)kv_lens, (const int*)table, table_stride, page_size, num_pages,
                      heads, (float*)scores, width, (uint32_t*)status));
   PG_LAUNCH_CHECK();

@@ -969,8 +969,7 @@ _FP8_WS: dict = {}
 
 def linear_fp8_block(x, wq, w_scale, xq=None, x_scale=None):
     """``x [T, K]`` bf16 (quantised here per token and k group, unless ``xq`` / ``x_scale`` are given) times the
-    block-scaled e4m3 weight ``wq [M, K]`` with ``w_scale [M / 128, K / 128]``; bf16 ``[T, M]``.  Steps of more
-    than 64 rows run in slices of 64 (the kernel is the decode-shape one)."""
+    block-scaled e4m3 weight ``wq [M, K]`` with ``w_scale [M / 128, K / 128]``; bf16 ``[T, M]``."""
     if xq is None:
         xq, x_scale = quant_fp8_1x128(x)
     t, k = xq.shape
@@ -980,15 +979,14 @@ def linear_fp8_block(x, wq, w_scale, xq=None, x_scale=None):
     c = ctx(dev)
     y = torch.empty((t, m), dtype=torch.bfloat16, device=dev)
     ws = _FP8_WS.get(dev.index)
-    need = lib().pg_gemm_fp8_ws_bytes(_ci(min(t, 64)), _ci(m))
+    need = lib().pg_gemm_fp8_ws_bytes(_ci(min(t, 64)), _ci(m))  # split K only happens for one narrow token tile
     if ws is None or ws.numel() < need:
         ws = torch.empty(int(need), dtype=torch.uint8, device=dev)
         _FP8_WS[dev.index] = ws
-    for t0 in range(0, t, 64):
-        n = min(64, t - t0)
-        rc = lib().pg_gemm_fp8_block(_ptr(xq[t0:]), _ll(k), _ptr(x_scale[:, t0:]), _ll(x_scale.stride(0)), _ptr(wq), _ll(k), _ptr(w_scale), _ptr(y[t0:]), _ll(m),
-                                     _ci(n), _ci(m), _ci(k), _ptr(ws), _ll(ws.numel()), _ptr(c.status), _stream())
-        _check(rc, c, 3)
+    # one launch for any number of rows: token tiles of 64 are the grid's second dimension
+    rc = lib().pg_gemm_fp8_block(_ptr(xq), _ll(k), _ptr(x_scale), _ll(x_scale.stride(0)), _ptr(wq), _ll(k), _ptr(w_scale), _ptr(y), _ll(m), _ci(t), _ci(m), _ci(k), _ptr(ws),
+                                 _ll(ws.numel()), _ptr(c.status), _stream())
+    _check(rc, c, 3)
     return y
 
 
