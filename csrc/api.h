@@ -91,6 +91,9 @@ int pg_gemm_fp8_block(const void* xq, long long ldx, const void* x_scale, long l
                       long long ldy, int T, int M, int K, void* ws, long long ws_bytes, void* status, cudaStream_t stream);
 int pg_quant_fp8_1x128(const void* x, long long ldx, int T, int K, void* xq, long long ldq, void* scale, long long lds, cudaStream_t stream);
 
+int pg_moe_grouped_gemm_fp8(const void* xq, long long rows, const void* x_scale, long long ldxs, const void* wq, const void* w_scale, void* y, long long ldy,
+                            const void* offsets, int E, int M, int K, int bn, void* status, cudaStream_t stream);
+
 // ---- sparse-attention indexer (dsa.cu) ----------------------------------------------------
 int pg_dsa_k_append(const void* k, long long ld, const void* norm_w, const void* norm_b, const void* cos, const void* sin, const void* positions,
                     const void* slots, void* cache, int tokens, int d, int rope, int max_pos, long long num_slots, float eps, void* status,

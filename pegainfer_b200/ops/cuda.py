@@ -823,6 +823,23 @@ def grouped_gemm(xs, offsets, w, scales=None, bn: int = 16):
     return y
 
 
+_MOE_FP8_TC = os.environ.get("PEGAINFER_MOE_FP8_TC", "1") != "0"  # FP8 experts on the FP8 tensor-core path (activations quantised per token group)
+
+
+def grouped_gemm_fp8(xq, x_scale, offsets, w_fp8, w_scale, bn: int = 16):
+    """``xq`` e4m3 [rows, K] sorted by expert with ``x_scale`` [K / 128, ld] (``quant_fp8_1x128``), ``w_fp8`` e4m3 [E, M, K] with
+    f32 ``w_scale`` [E, M / 128, K / 128]; bf16 [rows, M] on tcgen05 kind::f8f6f4."""
+    rows, k = xq.shape
+    e, m = w_fp8.shape[0], w_fp8.shape[1]
+    assert w_fp8.is_contiguous() and w_scale.is_contiguous() and w_scale.dtype == torch.float32 and w_scale.shape == (e, m // 128, k // 128)
+    y = torch.empty((rows, m), dtype=torch.bfloat16, device=xq.device)
+    c = ctx(xq.device)
+    rc = lib().pg_moe_grouped_gemm_fp8(_ptr(xq), _ll(rows), _ptr(x_scale), _ll(x_scale.stride(0)), _ptr(w_fp8), _ptr(w_scale), _ptr(y), _ll(m), _ptr(offsets), _ci(e), _ci(m),
+                                       _ci(k), _ci(min(64, max(16, bn))), _ptr(c.status), _stream())
+    _check(rc, c)
+    return y
+
+
 def _moe_pipeline(x, ids, weights, w13, s13, w2, s2, expert_offset):
     _bf16(x)
     t, h = x.shape
@@ -834,9 +851,16 @@ def _moe_pipeline(x, ids, weights, w13, s13, w2, s2, expert_offset):
     xs = torch.empty((routes, h), dtype=x.dtype, device=x.device)
     _check(lib().pg_moe_gather(_ptr(x), _ll(x.stride(0)), _ptr(sorted_src), _ptr(offsets), _ci(e_local), _ci(k), _ptr(xs), _ci(h), _ci(routes), _stream()), c)
     bn = _token_tile(routes, e_local)
-    y1 = grouped_gemm(xs, offsets, w13, s13, bn)
-    act = swiglu(y1)
-    y2 = grouped_gemm(act, offsets, w2, s2, bn)
+    if quant_code(w13) == 2 and _MOE_FP8_TC and h % 128 == 0 and w13.shape[1] % 256 == 0 and w2.shape[1] % 128 == 0:
+        # both GEMMs on the FP8 tensor-core path: activations quantised per row and 128-wide k group
+        xq, xsc = quant_fp8_1x128(xs)
+        act = swiglu(grouped_gemm_fp8(xq, xsc, offsets, w13, s13, bn))
+        aq, asc = quant_fp8_1x128(act)
+        y2 = grouped_gemm_fp8(aq, asc, offsets, w2, s2, bn)
+    else:
+        y1 = grouped_gemm(xs, offsets, w13, s13, bn)
+        act = swiglu(y1)
+        y2 = grouped_gemm(act, offsets, w2, s2, bn)
     out = torch.empty((t, h), dtype=torch.float32, device=x.device)
     _check(lib().pg_moe_combine(_ptr(y2), _ll(y2.stride(0)), _ptr(route_pos), _ptr(weights.contiguous()), _ci(t), _ci(k), _ptr(out), _ci(h), _ci(0), _stream()), c)
     return out

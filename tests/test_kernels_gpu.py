@@ -859,3 +859,33 @@ def test_int4_repack_kernel_matches_reference_nibble_order():
         torch.cuda.synchronize()
         assert torch.equal(got, want) and got._pg_nibbles == "paired"
         assert torch.equal(R.unrepack_int4_pairs(got), w)
+
+
+@pytest.mark.parametrize("counts,m,k,bn", [([3, 0, 17, 1, 64, 9], 512, 1024, 16), ([70, 5, 0, 130], 256, 2048, 64), ([1] * 24, 1024, 512, 32)])
+def test_grouped_fp8_gemm_matches_dequantised_reference(counts, m, k, bn):
+    """Per-expert block-scaled FP8 GEMM on kind::f8f6f4: e4m3 activations (per row and k group) times e4m3 expert weights."""
+    from pegainfer_b200.loader.export import quantize_dense_to_fp8
+
+    K = cu()
+    g = torch.Generator(device=DEV).manual_seed(len(counts) + m)
+    e, rows = len(counts), sum(counts)
+    offsets = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32, device=DEV)
+    x = (torch.randn(rows, k, device=DEV, generator=g) * 2).to(torch.bfloat16)
+    wq, ws = [], []
+    for i in range(e):
+        d = {"w": torch.randn(m, k, generator=torch.Generator().manual_seed(i)) * 0.05}
+        quantize_dense_to_fp8(d, ["w"])
+        wq.append(d["w"])
+        ws.append(d["w_scale_inv"])
+    wq, ws = torch.stack(wq).to(DEV).contiguous(), torch.stack(ws).to(DEV).contiguous()
+    xq, xs = K.quant_fp8_1x128(x)
+    y = K.grouped_gemm_fp8(xq, xs, offsets, wq, ws, bn)
+    torch.cuda.synchronize()
+    xf = xq.float().view(rows, k // 128, 128) * xs[:, :rows].t().unsqueeze(-1)
+    ref = torch.empty(rows, m, device=DEV)
+    for i in range(e):
+        r0, r1 = int(offsets[i]), int(offsets[i + 1])
+        wf = wq[i].float() * ws[i].repeat_interleave(128, 0)[:m].repeat_interleave(128, 1)[:, :k]
+        ref[r0:r1] = xf[r0:r1].view(r1 - r0, k) @ wf.t()
+    bf16_close(y, ref, rel=2 ** -6, abs_=2e-2)
+    status_clean()
