@@ -63,6 +63,33 @@ class ClockSampler:
         self.path = None
 
     def start(self):
+        # NVML in a thread (read-only queries every 20 ms) gives a dozen samples even for a 250 ms region; the
+        # nvidia-smi loop below needs 100 - 200 ms before its first line and is the fallback
+        self._nvml = None
+        try:
+            import threading
+
+            import pynvml
+
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByIndex(self.gpu)
+            self._nvml = {"rows": [], "stop": threading.Event()}
+
+            def loop():
+                get_reasons = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+                mx = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+                while not self._nvml["stop"].is_set():
+                    try:
+                        self._nvml["rows"].append((pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM), mx, int(get_reasons(h))))
+                    except Exception:
+                        pass
+                    self._nvml["stop"].wait(0.02)
+
+            self._nvml["thread"] = threading.Thread(target=loop, daemon=True)
+            self._nvml["thread"].start()
+            return
+        except Exception:
+            self._nvml = None
         try:
             f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
             self.path = f.name
@@ -74,6 +101,17 @@ class ClockSampler:
 
     def stop(self) -> dict:
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if getattr(self, "_nvml", None) is not None:
+            self._nvml["stop"].set()
+            self._nvml["thread"].join(2)
+            rows = self._nvml["rows"]
+            if rows:
+                bits = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+                seen = set()
+                for _, _, r in rows:
+                    seen.update(name for bit, name in bits.items() if r & bit)
+                out.update(sm_mhz=statistics.median([r[0] for r in rows]), sm_max_mhz=float(rows[0][1]), reasons=sorted(seen), samples=len(rows), source="nvml")
+            return out
         if self.proc is None:
             return out
         time.sleep(0.15)

@@ -157,9 +157,22 @@ def main():
                        "parallelism": f"dp{world}xep{world}-{args.comm if world > 1 else 'local'}", "cuda_graph": graphs is not None, "prefill_s": round(prefill_s, 3), "load_s": round(load_s, 1)},
             "clocks": clocks, "gpu_launches": kernels * args.steps,
         }))
-    from bench import hard_exit
+    # orderly exit: the captured graphs pin kernels and buffers, peers' memory is unmapped only after every rank is past
+    # its last kernel, then the process group goes
+    import gc
 
-    hard_exit(0)
+    from bench import leave_group
+
+    if graphs is not None:
+        graphs.release()
+    gr = None
+    del ex, model, kv
+    gc.collect()
+    torch.cuda.synchronize(device)
+    barrier(world, device)
+    if hasattr(ep, "close"):
+        ep.close()
+    leave_group(world)
 
 
 if __name__ == "__main__":

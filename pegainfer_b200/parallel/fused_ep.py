@@ -109,7 +109,13 @@ class FusedEP(EPContext):
                                     _ci(max_rows), st)
         K._check(rc, c)
         bn = K._token_tile(max_rows, e_local)
-        y1 = K.grouped_gemm(xs, offsets, w13, s13, bn)
+        if mode == 2 and K._MOE_FP8_TC and h % 128 == 0 and w13.shape[1] % 256 == 0:
+            # FP8 experts: W13 on the FP8 tensor-core path (received rows quantised per row and k group); rows past the
+            # live routes are whatever the buffer held, and their products are never read
+            xq, xsc = K.quant_fp8_1x128(xs)
+            y1 = K.grouped_gemm_fp8(xq, xsc, offsets, w13, s13, bn)
+        else:
+            y1 = K.grouped_gemm(xs, offsets, w13, s13, bn)
         act = K.swiglu(y1)
         m = w2.shape[1]
         kk = act.shape[1]
