@@ -36,7 +36,8 @@ def run(args, method, path, draft_len):
         g = torch.Generator().manual_seed(1)
         prompts = [torch.randint(0, mcfg.vocab_size, (args.prompt_len,), generator=g).tolist() for _ in range(args.conc)]
         sp = SamplingParams(temperature=0.0, ignore_eos=True)
-        eng.generate(prompts[:2], sp, max_tokens=8)  # warm-up: graph capture, kernel modules
+        warm = [torch.randint(0, mcfg.vocab_size, (args.prompt_len,), generator=g).tolist() for _ in range(args.conc)]
+        eng.generate(warm, sp, max_tokens=8)  # warm-up with a full batch of other prompts: every graph bucket the timed run uses is captured here
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         first = eng.generate(prompts, sp, max_tokens=1)

@@ -257,6 +257,160 @@ class DFlashDraftModel:
         return drafts.view(n, B).tolist()
 
 
+class _DraftGraphs:
+    """The draft round as one CUDA graph per request-count bucket.
+
+    A round's shapes vary only through the number of context rows each request brings (the rows its last verify step
+    committed, at most ``span``), so every request gets ``span`` context slots: unused slots carry zero rows whose
+    K/V land in the padding page, and the block rows' KV lengths simply do not cover them.  Positions, slots, KV
+    lengths, block tables, current tokens and context rows live in pointer-stable buffers that are refreshed from
+    pinned mirrors before each replay; the picked drafts come back through one small copy."""
+
+    def __init__(self, draft: "DFlashDraftModel", kv, page_size: int, span: int, max_batch: int, width: int):
+        from ..sched.executor import DECODE_BUCKETS, bucket_for
+
+        self.draft, self.kv, self.page_size, self.span = draft, kv, page_size, span
+        c, dev = draft.cfg, draft.device
+        self.B, self.R = c.block_size, span + c.block_size
+        self.buckets = [b for b in DECODE_BUCKETS if b <= max(bucket_for(max_batch), 1)]
+        n, B, R, W = self.buckets[-1], self.B, self.R, max(width, 1)
+        self.nmax, self.W = n, W
+        self.ctx = torch.zeros((n * span, c.hidden_size), dtype=draft.dtype, device=dev)
+        words = n + 2 * n * R + n * B  # current tokens | tail positions | tail slots | block-row KV lengths
+        self.h_small = torch.zeros(words, dtype=torch.int32).pin_memory()
+        self.d_small = torch.zeros(words, dtype=torch.int32, device=dev)
+        self.h_table = torch.zeros((n, W), dtype=torch.int32).pin_memory()
+        self.d_table = torch.zeros((n, W), dtype=torch.int32, device=dev)
+        self.d_table_blk = torch.zeros((n * B, W), dtype=torch.int32, device=dev)
+        self.toks = torch.full((n * B,), c.mask_token_id, dtype=torch.int32, device=dev)
+        self.out = torch.zeros(n * B, dtype=torch.int32, device=dev)
+        self.h_out = torch.zeros(n * B, dtype=torch.int32).pin_memory()
+        self.prev = torch.zeros(n, dtype=torch.int32, device=dev)
+        self.nxt = torch.zeros(n, dtype=torch.int32, device=dev)
+        self.tail_ptr = torch.arange(n + 1, dtype=torch.int32, device=dev) * R
+        self.blk_ptr = torch.arange(n * B + 1, dtype=torch.int32, device=dev)
+        ar = torch.arange(n, device=dev).view(n, 1) * R
+        self.ctx_idx = (ar + torch.arange(span, device=dev).view(1, span)).reshape(-1)
+        self.blk_idx = (ar + span + torch.arange(B, device=dev).view(1, B)).reshape(-1)
+        self.graphs: dict = {}
+        self.pool = None
+        self.replays = 0
+
+    def _views(self, n: int):
+        N, R, B = self.nmax, self.R, self.B
+        s = self.d_small
+        return s[:n], s[N : N + n * R], s[N + N * R : N + N * R + n * R], s[N + 2 * N * R : N + 2 * N * R + n * B]
+
+    def _body(self, n: int) -> None:
+        from ..ops import cuda as K
+        from ..ops.reference import AttnMeta
+
+        d, c = self.draft, self.draft.cfg
+        B, R, S, eps = self.B, self.R, self.span, c.rms_eps
+        cur, pos, slot, kvl = self._views(n)
+        geo = d.kv_geometry()
+        plan = K.plan_decode_splits(n * B, geo["kv_heads"], min(self.W * self.page_size, 2048), d.device)
+        meta_tail = AttnMeta(q_indptr=self.tail_ptr[: n + 1], kv_lens=kvl, block_table=self.d_table[:n], slot_mapping=slot, positions=pos, page_size=self.page_size, num_seqs=n,
+                             num_tokens=n * R, max_q_len=R, max_kv_len=self.W * self.page_size)
+        self.d_table_blk[: n * B].copy_(self.d_table[:n].repeat_interleave(B, 0))
+        meta_blk = AttnMeta(q_indptr=self.blk_ptr[: n * B + 1], kv_lens=kvl, block_table=self.d_table_blk[: n * B], slot_mapping=slot, positions=pos, page_size=self.page_size,
+                            num_seqs=n * B, num_tokens=n * B, max_q_len=1, max_kv_len=self.W * self.page_size, decode_only=True, plan=plan)
+        self.toks.view(self.nmax, B)[:n, 0].copy_(cur)
+        ctx_idx, blk_idx = self.ctx_idx[: n * S], self.blk_idx[: n * B]
+        residual = ops.embedding(self.toks[: n * B], d.target.embed)
+        x = ops.rms_norm(residual, d.layers[0].input_norm, eps)
+        for i, l in enumerate(d.layers):
+            tail_in = torch.empty((n * R, c.hidden_size), dtype=x.dtype, device=x.device)
+            tail_in.index_copy_(0, ctx_idx, self.ctx[: n * S])
+            tail_in.index_copy_(0, blk_idx, x)
+            qkv = ops.linear(tail_in, l.qkv)
+            q = ops.qk_norm_rope_append(qkv, l.q_norm, l.k_norm, d.cos, d.sin, meta_tail, self.kv.layer(i), c.num_q_heads, c.num_kv_heads, c.head_dim, eps)
+            q = q.reshape(n * R, c.num_q_heads, c.head_dim).index_select(0, blk_idx)
+            a = ops.paged_attention(q, self.kv.layer(i), meta_blk)
+            x = ops.add_rms_norm(ops.linear(a, l.o), residual, l.post_norm, eps)
+            act = ops.swiglu(ops.linear(x, l.gate_up))
+            nxt_norm = d.layers[i + 1].input_norm if i + 1 < len(d.layers) else d.norm
+            x = ops.add_rms_norm(ops.linear(act, l.down), residual, nxt_norm, eps)
+        logits = d.target.logits(x)
+        if d.markov is None:
+            K.argmax(logits, out=self.out[: n * B])
+            return
+        w1, w2 = d.markov
+        self.prev[:n].copy_(cur)
+        a_, b_ = self.prev[:n], self.nxt[:n]
+        for step in range(B):
+            bias = ops.linear(ops.embedding(a_, w1), w2)
+            K.markov_step_argmax(logits, bias if bias.dtype == logits.dtype else bias.to(logits.dtype), B, step, b_, self.out[: n * B])
+            a_, b_ = b_, a_
+
+    def capture(self, n: int):
+        dev = self.draft.device
+        self.d_small.zero_()
+        self.d_table.zero_()
+        s = torch.cuda.Stream(dev)
+        s.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(s):
+            self._body(n)  # warm-up on padding inputs (page 0, KV length 0)
+            s.synchronize()
+            g = torch.cuda.CUDAGraph()
+            if self.pool is None:
+                self.pool = torch.cuda.graph_pool_handle()
+            g.capture_begin(pool=self.pool)
+            try:
+                self._body(n)
+            finally:
+                g.capture_end()
+            g.replay()
+        torch.cuda.current_stream(dev).wait_stream(s)
+        self.graphs[n] = g
+        return g
+
+    def run(self, reqs: list) -> list:
+        """``reqs`` as for ``DFlashDraftModel.block_logits``.  Returns the block's picks, ``block_size`` per request."""
+        from ..sched.executor import bucket_for
+
+        n, N, B, R, S, ps = len(reqs), self.nmax, self.B, self.R, self.span, self.page_size
+        b = bucket_for(n, self.buckets)
+        if b not in self.graphs:
+            self.capture(b)
+        sm = self.h_small.numpy()
+        tb = self.h_table.numpy()
+        sm[:] = 0
+        ctx_rows, ctx_at = [], []
+        for i, (view, base, ctx, cur) in enumerate(reqs):
+            nc = 0 if ctx is None else ctx.shape[0]
+            pages = view.page_indices
+            tb[i, : len(pages)] = pages
+            sm[i] = cur
+            p0, s0 = N + i * R, N + N * R + i * R
+            for j in range(nc):  # real context rows first; the unused context slots keep position 0 and slot 0 (padding page)
+                pos = base + j
+                sm[p0 + j] = pos
+                sm[s0 + j] = pages[pos // ps] * ps + pos % ps
+            for j in range(B):
+                pos = base + nc + j
+                sm[p0 + S + j] = pos
+                sm[s0 + S + j] = pages[pos // ps] * ps + pos % ps
+            sm[N + 2 * N * R + i * B : N + 2 * N * R + (i + 1) * B] = base + nc + B
+            if nc:
+                ctx_rows.append(ctx)
+                ctx_at.append((i * S, nc))
+        self.d_small.copy_(self.h_small, non_blocking=True)
+        self.d_table[:b].copy_(self.h_table[:b], non_blocking=True)
+        self.ctx[: b * S].zero_()
+        for (at, nc), rows in zip(ctx_at, ctx_rows):
+            self.ctx[at : at + nc].copy_(rows, non_blocking=True)
+        self.graphs[b].replay()
+        self.replays += 1
+        self.h_out[: n * B].copy_(self.out[: n * B], non_blocking=True)
+        torch.cuda.current_stream(self.draft.device).synchronize()
+        return self.h_out[: n * B].view(n, B).tolist()
+
+    def release(self) -> None:
+        self.graphs.clear()
+        self.pool = None
+
+
 @dataclass
 class _ReqState:
     valid: int = 0  # leading positions of the draft cache that hold committed context
@@ -286,6 +440,12 @@ class DFlashSpec:
         self.rounds = 0
         executor.aux_sink = self
         self.aux_layers = tuple(draft_model.cfg.target_layer_ids)
+        # the draft round as a CUDA graph (one GPU; with tensor parallelism the target's sharded output projection
+        # would put a collective into the graph)
+        self.graphs = None
+        tp = getattr(model, "tp", None)
+        if self.device.type == "cuda" and getattr(executor, "use_graph", False) and (tp is None or tp.world == 1) and os.environ.get("PEGAINFER_DRAFT_GRAPH", "1") != "0":
+            self.graphs = _DraftGraphs(draft_model, self.kv, self.page_size, 1 + self.draft_len, executor.max_decode_batch, executor.max_blocks_per_seq)
 
     # -- called by the executor after every target forward ---------------------------------
     def observe(self, kind: str, seqs, meta, aux: list) -> None:
@@ -343,8 +503,13 @@ class DFlashSpec:
             st = self.state[r.q.id]
             reqs.append((r.kv.view(), st.valid, st.pending, r.kv.tokens[-1]))
             cur.append(r.kv.tokens[-1])
-        logits = self.draft.block_logits(self.kv, self.page_size, reqs)
-        picked = self.draft.pick(logits, cur)
+        g = self.graphs
+        if g is not None and len(reqs) <= g.nmax and all(q[2] is None or q[2].shape[0] <= g.span for q in reqs):
+            blocks = g.run(reqs)
+            picked = blocks if (self.draft.markov is not None or self.draft.cfg.anchor_first) else [t[1:] for t in blocks]
+        else:
+            logits = self.draft.block_logits(self.kv, self.page_size, reqs)
+            picked = self.draft.pick(logits, cur)
         for r in decoders:
             st = self.state[r.q.id]
             if st.pending is not None:
