@@ -29,7 +29,7 @@ log = logging.getLogger("pegainfer_b200.serve")
 SHARED_FLAGS = {
     "model_path", "preset", "served_model_name", "port", "host", "cuda_graph", "precapture_graphs", "dump_graph_dot", "device_ordinal", "tp_size", "dp_size", "ep_size",
     "kv_offload", "kv_offload_host_gib", "kv_offload_disk_dir", "kv_offload_disk_gib", "no_prefix_cache", "max_prefill_tokens", "max_model_len", "num_kv_blocks", "gpu_memory_utilization",
-    "kv_cache_memory_margin_mib", "kv_page_size", "max_decode_batch", "seed", "comm", "gemm", "tokenizer", "pd_prefill_device", "pd_store",
+    "kv_cache_memory_margin_mib", "kv_page_size", "max_decode_batch", "seed", "comm", "gemm", "tokenizer", "pd_prefill_device", "pd_store", "engine_process",
 }
 
 
@@ -93,6 +93,7 @@ def build_parser() -> argparse.ArgumentParser:
     k.add_argument("--kv-offload-host-gib", type=float, default=4.0)
     k.add_argument("--kv-offload-disk-dir", default=None, help="third KV tier: blocks evicted from host memory are kept as files in this directory")
     k.add_argument("--kv-offload-disk-gib", type=float, default=0.0)
+    k.add_argument("--engine-process", action="store_true", help="run the engine in a process of its own, so that the HTTP frontend and the scheduler do not share one interpreter lock")
     k.add_argument("--pd-prefill-device", type=int, help="prefill / decode disaggregation: run prompts on this GPU and decode on --device-ordinal; KV blocks move by content hash")
     k.add_argument("--pd-store", choices=["peer", "host"], default="peer", help="where the handoff store lives: the decode GPU (one NVLink hop) or pinned host memory")
     k.add_argument("--max-prefill-tokens", type=int, default=1024)
@@ -215,6 +216,19 @@ def main(argv: Optional[list] = None) -> int:
         eng = build_pd_engine(ecfg, mcfg, prefill_device=pre, decode_device=dec, store_device="cpu" if ns.pd_store == "host" else None)
         log.info("prefill on %s, decode on %s, %d store slots on %s", pre, dec, eng.store.num_slots, eng.store.slab.device)
         name = ecfg.served_model_name or ecfg.preset or os.path.basename(os.path.normpath(ecfg.model_path))
+        try:
+            serve(eng, tokenizer, name, ecfg.host, ecfg.port)
+        finally:
+            eng.shutdown()
+        return 0
+    if ns.engine_process:
+        from .engine.remote import RemoteEngine
+
+        if ecfg.enable_lora or ecfg.dump_graph_dot:
+            raise SystemExit("--engine-process does not combine with LoRA routes or --dump-graph-dot")
+        eng = RemoteEngine(ecfg, mcfg)
+        name = ecfg.served_model_name or ecfg.preset or os.path.basename(os.path.normpath(ecfg.model_path))
+        log.info("engine process up: %d KV blocks of %d tokens, max_model_len %d", eng.info.kv_capacity.num_blocks, eng.info.kv_capacity.block_size, eng.info.max_model_len)
         try:
             serve(eng, tokenizer, name, ecfg.host, ecfg.port)
         finally:
