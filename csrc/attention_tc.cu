@@ -22,6 +22,7 @@
 //
 // Reference parity: the reference's prefill attention is FlashInfer's BatchPrefillWithPagedKVCache
 // (pegainfer-kernels/csrc/shared/flashinfer_prefill.cu), an mma.sync kernel on every architecture.
+#include <type_traits>
 #include "common.cuh"
 
 #include <cuda.h>
@@ -94,6 +95,11 @@ __device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, u
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float y;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+  return y;
+}
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -109,13 +115,15 @@ __global__ void __launch_bounds__(THREADS) prefill_attn_tc_kernel(const __grid_c
   uint8_t* v_tile = k_tile + 2 * TILE_BYTES;          // 2 x 32 KB
   TcSmem* sh = reinterpret_cast<TcSmem*>(v_tile + 2 * TILE_BYTES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int hq = blockIdx.y;
+  // one-dimensional grid, query tile slowest: every head's late tiles (most keys) are handed out before any early
+  // tile, so the long CTAs start first on all SMs and the short ones fill the tail
+  const int hq = (int)(blockIdx.x % (unsigned)p.hq);
   const int h = hq / (p.hq / p.hkv);
 
   // (sequence, query tile of 256 rows) of this CTA: late tiles (most keys) first
   int b = 0, tile_in_seq = 0;
   {
-    int rem = (int)gridDim.x - 1 - (int)blockIdx.x;
+    int rem = (int)(gridDim.x / (unsigned)p.hq) - 1 - (int)(blockIdx.x / (unsigned)p.hq);
     for (; b < p.num_seqs; ++b) {
       const int n = p.q_indptr[b + 1] - p.q_indptr[b];
       const int nt = (n + BQ2 - 1) / BQ2;
@@ -286,35 +294,49 @@ __global__ void __launch_bounds__(THREADS) prefill_attn_tc_kernel(const __grid_c
     const uint32_t o_row = s_row + 256u;
     float m = -INFINITY, l = 0.f;  // m: the maximum the exponentials refer to (may lag the true maximum by up to 2^8)
     bool ok = true;
-    for (int j = 0; j < my_n && ok; ++j) {
-      ok = mbar_wait(&sh->s_full[g], (uint32_t)(j & 1), abort_flag);
-      if (!ok) break;
+    // One key tile of this group.  MASK (a tile that the causal edge or the end of the keys crosses) is a compile-time
+    // property: the plain tiles, nearly all of them, carry no compare or select per element.
+    auto tile = [&](int j, auto mask_tag) -> bool {
+      constexpr bool MASK = decltype(mask_tag)::value;
+      if (!mbar_wait(&sh->s_full[g], (uint32_t)(j & 1), abort_flag)) return false;
       tc_fence_after();
-      const int key0 = j * BKV;
-      const bool need_mask = key0 + BKV - 1 > min(pos0, kv_len - 1);
-      const int limit = min(my_pos, kv_len - 1) - key0;  // columns 0 .. limit are visible to this row
-      // pass 1: row maximum of the raw scores
-      float mx_raw = -INFINITY;
+      const int limit = min(my_pos, kv_len - 1) - j * BKV;  // columns 0 .. limit are visible to this row
+      // the whole row of S goes to registers in one round trip (four loads in flight, one wait): both the maximum
+      // and the exponentials work from there, and S in tensor memory may be overwritten by P right away
+      uint32_t v[BKV];
+      tmem_ld32(s_row, v);
+      tmem_ld32(s_row + 32, v + 32);
+      tmem_ld32(s_row + 64, v + 64);
+      tmem_ld32(s_row + 96, v + 96);
+      tmem_ld_wait();
+      float mx_raw;
+      if constexpr (MASK) {
+        mx_raw = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < BKV; c += 64) {
-        uint32_t v[64];
-        tmem_ld32(s_row + c, v);
-        tmem_ld32(s_row + c + 32, v + 32);
-        tmem_ld_wait();
-        if (need_mask) {
+        for (int i = 0; i < BKV; ++i)
+          if (i <= limit) mx_raw = fmaxf(mx_raw, __uint_as_float(v[i]));
+      } else {
+        // three-input maximum, four chains instead of one long one
+        float m0 = max3(__uint_as_float(v[0]), __uint_as_float(v[1]), __uint_as_float(v[2]));
+        float m1 = max3(__uint_as_float(v[3]), __uint_as_float(v[4]), __uint_as_float(v[5]));
+        float m2 = max3(__uint_as_float(v[6]), __uint_as_float(v[7]), __uint_as_float(v[8]));
+        float m3 = max3(__uint_as_float(v[9]), __uint_as_float(v[10]), __uint_as_float(v[11]));
 #pragma unroll
-          for (int i = 0; i < 64; ++i)
-            if (c + i <= limit) mx_raw = fmaxf(mx_raw, __uint_as_float(v[i]));
-        } else {
-#pragma unroll
-          for (int i = 0; i < 64; ++i) mx_raw = fmaxf(mx_raw, __uint_as_float(v[i]));
+        for (int i = 12; i + 7 < BKV; i += 8) {
+          m0 = max3(m0, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+          m1 = max3(m1, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+          m2 = max3(m2, __uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+          m3 = max3(m3, __uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
         }
+        // 12 + 8 * 14 = 124: four columns left
+        m0 = max3(m0, __uint_as_float(v[124]), __uint_as_float(v[125]));
+        m1 = max3(m1, __uint_as_float(v[126]), __uint_as_float(v[127]));
+        mx_raw = fmaxf(max3(m0, m1, m2), m3);
       }
       const float mx = mx_raw * p.scale_log2;
       // the previous product of this group must be complete before O is rescaled
       if (j >= 1) {
-        ok = mbar_wait(&sh->o_full[g], (uint32_t)((j - 1) & 1), abort_flag);
-        if (!ok) break;
+        if (!mbar_wait(&sh->o_full[g], (uint32_t)((j - 1) & 1), abort_flag)) return false;
         tc_fence_after();
       }
       // move to a new maximum only when it grew by more than the threshold (or there was none yet)
@@ -325,7 +347,7 @@ __global__ void __launch_bounds__(THREADS) prefill_attn_tc_kernel(const __grid_c
       }
       if (j >= 1 && __any_sync(0xFFFFFFFFu, alpha != 1.f)) {
         const float2 a2 = make_float2(alpha, alpha);
-#pragma unroll
+#pragma unroll 1
         for (int c = 0; c < D; c += 32) {
           uint32_t w[32];
           tmem_ld32(o_row + c, w);
@@ -339,40 +361,46 @@ __global__ void __launch_bounds__(THREADS) prefill_attn_tc_kernel(const __grid_c
           tmem_st16(o_row + c, w);
           tmem_st16(o_row + c + 16, w + 16);
         }
+        l *= alpha;
       }
-      l *= alpha;
       const float neg = (m == -INFINITY) ? 0.f : -m;
-      // pass 2: P = exp2(S * scale - m) as bf16, two per 32-bit column, over the columns of S already consumed
-      // (scores 0..63 become P columns 0..31 before scores 64..127 are read); row sum
-      float2 sum2 = make_float2(0.f, 0.f);
+      // P = exp2(S * scale - m) as bf16, two per 32-bit column, over the first 64 columns of S; row sum
+      float2 sum2 = make_float2(0.f, 0.f), sum3 = make_float2(0.f, 0.f);
       const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), ng2 = make_float2(neg, neg);
 #pragma unroll
-      for (int c = 0; c < BKV; c += 64) {
-        uint32_t v[64];
-        tmem_ld32(s_row + c, v);
-        tmem_ld32(s_row + c + 32, v + 32);
-        tmem_ld_wait();
-        uint32_t packed[32];
+      for (int c = 0; c < BKV; c += 32) {
+        uint32_t packed[16];
 #pragma unroll
-        for (int i = 0; i < 64; i += 2) {
-          const float2 t2 = __ffma2_rn(make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), sc2, ng2);
+        for (int i = 0; i < 32; i += 4) {
+          const float2 t2 = __ffma2_rn(make_float2(__uint_as_float(v[c + i]), __uint_as_float(v[c + i + 1])), sc2, ng2);
+          const float2 t3 = __ffma2_rn(make_float2(__uint_as_float(v[c + i + 2]), __uint_as_float(v[c + i + 3])), sc2, ng2);
           float2 e = make_float2(ex2_approx(t2.x), ex2_approx(t2.y));
-          if (need_mask) {
+          float2 f = make_float2(ex2_approx(t3.x), ex2_approx(t3.y));
+          if constexpr (MASK) {
             if (c + i > limit) e.x = 0.f;
             if (c + i + 1 > limit) e.y = 0.f;
+            if (c + i + 2 > limit) f.x = 0.f;
+            if (c + i + 3 > limit) f.y = 0.f;
           }
           sum2 = __fadd2_rn(sum2, e);
-          const bf162 pr = __floats2bfloat162_rn(e.x, e.y);
-          packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&pr);
+          sum3 = __fadd2_rn(sum3, f);
+          const bf162 pe = __floats2bfloat162_rn(e.x, e.y), pf = __floats2bfloat162_rn(f.x, f.y);
+          packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&pe);
+          packed[(i >> 1) + 1] = *reinterpret_cast<const uint32_t*>(&pf);
         }
         tmem_st16(s_row + (c >> 1), packed);
-        tmem_st16(s_row + (c >> 1) + 16, packed + 16);
       }
+      sum2 = __fadd2_rn(sum2, sum3);
       tmem_st_wait();
       l += sum2.x + sum2.y;
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&sh->p_ready[g]);
+      return true;
+    };
+    for (int j = 0; j < my_n && ok; ++j) {
+      const bool need_mask = j * BKV + BKV - 1 > min(pos0, kv_len - 1);
+      ok = need_mask ? tile(j, std::true_type{}) : tile(j, std::false_type{});
     }
     const int rows_g = min(128, rows_here - g * 128);
     if (ok && my_n > 0) {
@@ -481,7 +509,7 @@ extern "C" int pg_prefill_attention_tc(const void* q, const void* kv_layer, void
     PG_CUDA(cudaFuncSetAttribute(prefill_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attr_done = true;
   }
-  PG_CUDA(launch_pdl(prefill_attn_tc_kernel, dim3((unsigned)q_tiles, (unsigned)hq), dim3(THREADS), smem, stream, tm_q, tm_kv, p));
+  PG_CUDA(launch_pdl(prefill_attn_tc_kernel, dim3((unsigned)q_tiles * (unsigned)hq), dim3(THREADS), smem, stream, tm_q, tm_kv, p));
   PG_LAUNCH_CHECK();
   return PG_OK;
 }
