@@ -106,7 +106,7 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
-__global__ void __launch_bounds__(THREADS) prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv, const TcAttnParams p) {
+__global__ void __launch_bounds__(THREADS, 1) prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv, const TcAttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = smem_u32(smem_raw);
   uint8_t* tiles = smem_raw + (((base + 1023u) & ~1023u) - base);
@@ -180,48 +180,60 @@ __global__ void __launch_bounds__(THREADS) prefill_attn_tc_kernel(const __grid_c
   const int* table_row = p.table + (long long)b * p.table_stride;
 
   if (warp == 0) {
-    if (lane == 0 && n_tiles > 0) {
+    // Producer warp.  A key tile and its value tile arrive as 4 * ppt small boxes (one per page, 64-column half and
+    // K or V); the lanes issue them side by side, slot = lane, lane + 32, and each lane reads the page ids of its own
+    // slots one tile ahead, so that neither the table's memory latency nor a serial run of TMA issues sits between
+    // two tiles.
+    if (n_tiles > 0) {
       const uint64_t pol = l2_policy_evict_normal();
-      mbar_expect_tx(&sh->q_full, GROUPS * TILE_BYTES);
+      if (lane == 0) {
+        mbar_expect_tx(&sh->q_full, GROUPS * TILE_BYTES);
 #pragma unroll
-      for (int g = 0; g < GROUPS; ++g) {
-        tma_load_3d(q_tile + g * TILE_BYTES, &tm_q, &sh->q_full, 0, hq, q0 + row_base + g * 128, pol);
-        tma_load_3d(q_tile + g * TILE_BYTES + HALF_BYTES, &tm_q, &sh->q_full, 64, hq, q0 + row_base + g * 128, pol);
+        for (int g = 0; g < GROUPS; ++g) {
+          tma_load_3d(q_tile + g * TILE_BYTES, &tm_q, &sh->q_full, 0, hq, q0 + row_base + g * 128, pol);
+          tma_load_3d(q_tile + g * TILE_BYTES + HALF_BYTES, &tm_q, &sh->q_full, 64, hq, q0 + row_base + g * 128, pol);
+        }
       }
-      const int ppt = BKV / p.page_size;  // pages per key tile
-      // The tile's page ids are read in one unrolled burst (independent loads in flight together); read one by one
-      // between the TMA issues, each would cost a full memory latency.
-      int pages[16];
+      const int ppt = BKV / p.page_size;  // pages per key tile (1 .. 16)
+      const int per_kv = 2 * ppt, slots = 4 * ppt;
+      auto page_of = [&](int j, int slot) -> int {
+        const int pg = (slot % per_kv) >> 1;
+        const int pages_live = min(ppt, (kv_len - j * BKV + p.page_size - 1) / p.page_size);
+        int page = (slot < slots && pg < pages_live) ? __ldg(table_row + j * ppt + pg) : 0;  // past the end: the padding page, keys masked
+        if (page < 0 || page >= p.num_pages) {
+          atomicCAS(p.status, PG_ST_OK, PG_ST_BOUNDS | (41u << 8));
+          page = 0;
+        }
+        return page;
+      };
+      int nxt0 = page_of(0, lane), nxt1 = page_of(0, lane + 32);
       bool ok = true;
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const int pages_live = min(ppt, (kv_len - j * BKV + p.page_size - 1) / p.page_size);
-#pragma unroll
-        for (int pg = 0; pg < 16; ++pg) pages[pg] = (pg < pages_live) ? __ldg(table_row + j * ppt + pg) : 0;  // past the end: the padding page, keys masked
-#pragma unroll
-        for (int pg = 0; pg < 16; ++pg) {
-          if (pages[pg] < 0 || pages[pg] >= p.num_pages) {
-            atomicCAS(p.status, PG_ST_OK, PG_ST_BOUNDS | (41u << 8));
-            pages[pg] = 0;
-          }
+        const int pg0 = nxt0, pg1 = nxt1;
+        if (j + 1 < n_tiles) {
+          nxt0 = page_of(j + 1, lane);
+          nxt1 = page_of(j + 1, lane + 32);
         }
         const int st = j & 1;
+        if (j >= 2) {
+          const uint32_t par = (uint32_t)(((j >> 1) - 1) & 1);
+          ok = mbar_wait(&sh->k_empty[st], par, abort_flag) && mbar_wait(&sh->v_empty[st], par, abort_flag);
+          ok = __all_sync(0xFFFFFFFFu, ok);
+          if (!ok) break;
+        }
+        if (lane == 0) {
+          mbar_expect_tx(&sh->k_full[st], TILE_BYTES);
+          mbar_expect_tx(&sh->v_full[st], TILE_BYTES);
+        }
+        __syncwarp();
 #pragma unroll
-        for (int kvsel = 0; kvsel < 2; ++kvsel) {
-          uint64_t* full = kvsel ? &sh->v_full[st] : &sh->k_full[st];
-          uint64_t* empty = kvsel ? &sh->v_empty[st] : &sh->k_empty[st];
-          uint8_t* dst = (kvsel ? v_tile : k_tile) + st * TILE_BYTES;
-          if (j >= 2 && !mbar_wait(empty, (uint32_t)(((j >> 1) - 1) & 1), abort_flag)) {
-            ok = false;
-            break;
-          }
-          mbar_expect_tx(full, TILE_BYTES);
-#pragma unroll
-          for (int pg = 0; pg < 16; ++pg) {
-            if (pg < ppt) {
-              const int z = (pages[pg] * 2 + kvsel) * p.page_size;
-              tma_load_3d(dst + pg * p.page_size * 128, &tm_kv, full, 0, h, z, pol);
-              tma_load_3d(dst + HALF_BYTES + pg * p.page_size * 128, &tm_kv, full, 64, h, z, pol);
-            }
+        for (int it = 0; it < 2; ++it) {
+          const int slot = lane + 32 * it;
+          if (slot < slots) {
+            const int kvsel = slot / per_kv, rem = slot % per_kv, pg = rem >> 1, half = rem & 1;
+            const int z = ((it ? pg1 : pg0) * 2 + kvsel) * p.page_size;
+            uint8_t* dst = (kvsel ? v_tile : k_tile) + st * TILE_BYTES + half * HALF_BYTES + pg * p.page_size * 128;
+            tma_load_3d(dst, &tm_kv, kvsel ? &sh->v_full[st] : &sh->k_full[st], half * 64, h, z, pol);
           }
         }
       }
