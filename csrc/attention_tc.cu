@@ -1,27 +1,32 @@
 // Prefill attention on tcgen05 for sm_100a: causal GQA attention of ragged query rows over a paged KV cache,
-// head dim 128.
+// head dims 128 and 256 (the second kernel, further down, has its own notes).
 //
-// One CTA owns 256 query rows of one query head as two tiles of 128 (two softmax groups) and walks the KV of its
-// sequence in tiles of 128 keys that both tiles share:
+// Head dim 128: one CTA owns 256 query rows of one query head as two tiles of 128 (two softmax groups) and walks the KV
+// of its sequence in tiles of 128 keys that both tiles share:
 //
 //   S_g = Q_g K^T      tcgen05.mma, both operands K-major in shared memory (TMA, 128-byte swizzle), accumulator in TMEM
-//   P_g = softmax tile four warps per group, one query row per thread: two passes over the row in TMEM (maximum, then
-//                      exponentials with packed f32x2 arithmetic), P written back as bf16 INTO TENSOR MEMORY over the
-//                      score columns already consumed (two values per 32-bit column)
+//   P_g = softmax tile four warps per group, one query row per thread: the row of S is read into registers in one round
+//                      trip (maximum with three-input max, exponentials with packed f32x2 arithmetic and ex2.approx),
+//                      P is written back as bf16 INTO TENSOR MEMORY over the first score columns (two values per 32-bit
+//                      column).  Whether a tile needs the causal / length mask is a compile-time property of the tile
+//                      body: the plain tiles carry no compare or select per element.
 //   O_g += P_g V       tcgen05.mma with A = P_g read from tensor memory and V as an MN-major B operand (the cache stores
 //                      keys as rows, which is what the contraction over keys needs transposed); O_g stays in TMEM for
 //                      the whole walk.  It is rescaled (tcgen05.ld / multiply / tcgen05.st) only when a row's maximum
 //                      grew by more than 2^8 since the value its exponentials refer to; the row sum follows the same
 //                      reference, so the result is exact.
 //
-// Roles: warp 0 = TMA producer (Q once, then K and V tiles through the page table, two stages each), warp 1 = MMA
-// issuer, in the order  P V of group a, next S of group a, P V of group b, next S of group b : while one group's
-// softmax runs the tensor core has the other group's work, warps 2-5 / 6-9 = softmax groups a / b and output.
-// TMEM: S / P of group g at columns 128 g, O of group g at 256 + 128 g.  Every wait is bounded and reports through
-// the status word.
+// Roles: warp 0 = TMA producer (Q once, then K and V tiles through the page table, two stages each; a tile is 4 x pages
+// small boxes, which the 32 lanes issue side by side, with the page ids read one tile ahead), warp 1 = MMA issuer, in the
+// order  P V of group a, next S of group a, P V of group b, next S of group b : while one group's softmax runs the
+// tensor core has the other group's work, warps 2-5 / 6-9 = softmax groups a / b and output.
+// TMEM: S / P of group g at columns 128 g, O of group g at 256 + 128 g.  The grid is one-dimensional with the query
+// tile slowest and late tiles first, so the CTAs with the most keys start first on every SM.  Every wait is bounded and
+// reports through the status word.
 //
 // Reference parity: the reference's prefill attention is FlashInfer's BatchPrefillWithPagedKVCache
-// (pegainfer-kernels/csrc/shared/flashinfer_prefill.cu), an mma.sync kernel on every architecture.
+// (pegainfer-kernels/csrc/shared/flashinfer_prefill.cu, hd256 instantiations in paged_attention.cu:977-1135), an
+// mma.sync kernel on every architecture.
 #include <type_traits>
 #include "common.cuh"
 
@@ -449,6 +454,321 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attn_tc_kernel(const __gri
   if (threadIdx.x == 0 && sh->abort_flag) atomicCAS(p.status, PG_ST_OK, PG_ST_TIMEOUT | (41u << 8));
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Head dim 256 (the gated full-attention layers of the hybrid models).  O of one 128-row query tile already takes 256 of
+// the 512 TMEM columns, so a CTA owns ONE query tile and keeps the tensor core busy the other way round: the scores are
+// double-buffered (tiles of 64 keys, S_j at columns 256 + 64 (j & 1)), and the MMA thread issues  P V of tile j, then S of
+// tile j + 2  while the softmax warps work on tile j + 1.  Shared memory: Q 64 KB, K and V two stages of 32 KB each.
+// The producer warp is split: lanes 0-15 feed K, lanes 16-31 feed V, each half with its own waits, because K runs two
+// tiles ahead of V.
+constexpr int D2 = 256, BKV2 = 64, BQ1 = 128;
+constexpr int Q2_BYTES = BQ1 * D2 * 2;     // 64 KB: [4 blocks of 64 columns][128 rows][128 B]
+constexpr int KV2_BYTES = BKV2 * D2 * 2;   // 32 KB: [4 blocks of 64 columns][64 rows][128 B]
+constexpr int KV2_BLOCK = BKV2 * 128;      // 8 KB
+constexpr int THREADS2 = 64 + 128;
+
+struct TcSmem2 {
+  uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_ready[2], o_full;
+  uint32_t tmem_slot;
+  int abort_flag;
+};
+
+__global__ void __launch_bounds__(THREADS2, 1) prefill_attn_tc256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv, const TcAttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = smem_u32(smem_raw);
+  uint8_t* tiles = smem_raw + (((base + 1023u) & ~1023u) - base);
+  uint8_t* q_tile = tiles;
+  uint8_t* k_tile = tiles + Q2_BYTES;
+  uint8_t* v_tile = k_tile + 2 * KV2_BYTES;
+  TcSmem2* sh = reinterpret_cast<TcSmem2*>(v_tile + 2 * KV2_BYTES);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int hq = (int)(blockIdx.x % (unsigned)p.hq);
+  const int h = hq / (p.hq / p.hkv);
+  int b = 0, tile_in_seq = 0;  // late tiles (most keys) first, every head's before any early tile
+  {
+    int rem = (int)(gridDim.x / (unsigned)p.hq) - 1 - (int)(blockIdx.x / (unsigned)p.hq);
+    for (; b < p.num_seqs; ++b) {
+      const int n = p.q_indptr[b + 1] - p.q_indptr[b];
+      const int nt = (n + BQ1 - 1) / BQ1;
+      if (rem < nt) {
+        tile_in_seq = rem;
+        break;
+      }
+      rem -= nt;
+    }
+    if (b >= p.num_seqs) return;
+  }
+  if (threadIdx.x == 0) {
+    mbar_init(&sh->q_full, 1);
+    for (int s2 = 0; s2 < 2; ++s2) {
+      mbar_init(&sh->k_full[s2], 1);
+      mbar_init(&sh->k_empty[s2], 1);
+      mbar_init(&sh->v_full[s2], 1);
+      mbar_init(&sh->v_empty[s2], 1);
+      mbar_init(&sh->s_full[s2], 1);
+      mbar_init(&sh->p_ready[s2], 4);
+    }
+    mbar_init(&sh->o_full, 1);
+    sh->abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_kv);
+  }
+  if (warp == 1) {
+    tmem_alloc(&sh->tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sh->tmem_slot;  // columns: O at 0 .. 255, S / P of tile j at 256 + 64 (j & 1)
+  volatile int* abort_flag = &sh->abort_flag;
+  PG_PDL_ENTRY();
+
+  const int q0 = p.q_indptr[b], q_len = p.q_indptr[b + 1] - q0;
+  const int kv_len = p.kv_lens[b];
+  const int row_base = tile_in_seq * BQ1;
+  const int rows_here = min(BQ1, q_len - row_base);
+  const int pos0 = kv_len - q_len + row_base;  // position of the tile's first row
+  const int n_tiles = (rows_here > 0 && kv_len > 0) ? min(pos0 + rows_here - 1, kv_len - 1) / BKV2 + 1 : 0;
+  const int* table_row = p.table + (long long)b * p.table_stride;
+
+  if (warp == 0) {
+    if (n_tiles > 0) {
+      const uint64_t pol = l2_policy_evict_normal();
+      if (lane == 0) {
+        mbar_expect_tx(&sh->q_full, Q2_BYTES);
+#pragma unroll
+        for (int cb = 0; cb < 4; ++cb) tma_load_3d(q_tile + cb * (BQ1 * 128), &tm_q, &sh->q_full, cb * 64, hq, q0 + row_base, pol);
+      }
+      // lanes 0-15: K boxes, lanes 16-31: V boxes; slot = (page of the tile, 64-column block), 4 * ppt slots per tile
+      const int kvsel = lane >> 4, sub = lane & 15;
+      const uint32_t half_mask = kvsel ? 0xFFFF0000u : 0x0000FFFFu;
+      const int ppt = BKV2 / p.page_size;  // 1 .. 8
+      const int slots = 4 * ppt;           // 4 .. 32: up to two per lane
+      uint64_t* full = kvsel ? sh->v_full : sh->k_full;
+      uint64_t* empty = kvsel ? sh->v_empty : sh->k_empty;
+      uint8_t* tile0 = kvsel ? v_tile : k_tile;
+      auto page_of = [&](int j, int slot) -> int {
+        const int pg = slot >> 2;
+        const int pages_live = min(ppt, (kv_len - j * BKV2 + p.page_size - 1) / p.page_size);
+        int page = (slot < slots && pg < pages_live) ? __ldg(table_row + j * ppt + pg) : 0;  // past the end: the padding page, keys masked
+        if (page < 0 || page >= p.num_pages) {
+          atomicCAS(p.status, PG_ST_OK, PG_ST_BOUNDS | (42u << 8));
+          page = 0;
+        }
+        return page;
+      };
+      int nxt0 = page_of(0, sub), nxt1 = page_of(0, sub + 16);
+      for (int j = 0; j < n_tiles; ++j) {
+        const int pg0 = nxt0, pg1 = nxt1;
+        if (j + 1 < n_tiles) {
+          nxt0 = page_of(j + 1, sub);
+          nxt1 = page_of(j + 1, sub + 16);
+        }
+        const int st = j & 1;
+        if (j >= 2) {
+          bool ok = mbar_wait(&empty[st], (uint32_t)(((j >> 1) - 1) & 1), abort_flag);
+          ok = __all_sync(half_mask, ok);
+          if (!ok) break;
+        }
+        if (sub == 0) mbar_expect_tx(&full[st], KV2_BYTES);
+        __syncwarp(half_mask);
+#pragma unroll
+        for (int it = 0; it < 2; ++it) {
+          const int slot = sub + 16 * it;
+          if (slot < slots) {
+            const int pg = slot >> 2, cb = slot & 3;
+            const int z = ((it ? pg1 : pg0) * 2 + kvsel) * p.page_size;
+            tma_load_3d(tile0 + st * KV2_BYTES + cb * KV2_BLOCK + pg * p.page_size * 128, &tm_kv, &full[st], cb * 64, h, z, pol);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_tiles > 0) {
+      constexpr uint32_t idesc_s = idesc_bf16(128, BKV2, 0);
+      constexpr uint32_t idesc_o = idesc_bf16(128, D2, 1);
+      const uint32_t lbo = p.mn_lbo_first ? (uint32_t)KV2_BLOCK : 1024u, sbo = p.mn_lbo_first ? 1024u : (uint32_t)KV2_BLOCK;
+      bool ok = mbar_wait(&sh->q_full, 0, abort_flag);
+      // S of tile j into buffer j & 1.  It overwrites S and P of tile j - 2: the product that read that P was issued
+      // before, and the tensor core runs this thread's instructions in order.
+      auto issue_s = [&](int j) {
+        if (j >= n_tiles) return true;
+        const int st = j & 1;
+        if (!mbar_wait(&sh->k_full[st], (uint32_t)((j >> 1) & 1), abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t qa = smem_u32(q_tile), ka = smem_u32(k_tile + st * KV2_BYTES);
+#pragma unroll
+        for (int cb = 0; cb < 4; ++cb)
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_bf16_ss(tmem + 256u + (uint32_t)(st * BKV2), umma_desc_k_sw128(qa + cb * (BQ1 * 128) + k * 32), umma_desc_k_sw128(ka + cb * KV2_BLOCK + k * 32), idesc_s,
+                         (cb | k) ? 1u : 0u);
+        umma_commit(&sh->s_full[st]);
+        umma_commit(&sh->k_empty[st]);
+        return true;
+      };
+      ok = ok && issue_s(0) && issue_s(1);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int st = j & 1;
+        ok = mbar_wait(&sh->p_ready[st], (uint32_t)((j >> 1) & 1), abort_flag) && mbar_wait(&sh->v_full[st], (uint32_t)((j >> 1) & 1), abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t va = smem_u32(v_tile + st * KV2_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < BKV2 / 16; ++ks)
+          umma_bf16_ts(tmem, tmem + 256u + (uint32_t)(st * BKV2) + (uint32_t)(ks * 8), umma_desc_mn_sw128(va + ks * 2048, lbo, sbo), idesc_o, (j | ks) ? 1u : 0u);
+        umma_commit(&sh->o_full);
+        umma_commit(&sh->v_empty[st]);
+        ok = issue_s(j + 2);
+      }
+    }
+  } else {
+    // softmax / output warps: one query row per thread (TMEM lane 32 * (warp % 4) + lane)
+    const int wq = warp & 3;
+    const int r = wq * 32 + lane;
+    const int my_pos = pos0 + r;  // rows past the sequence compute garbage that is never stored
+    const uint32_t lane_base = tmem + ((uint32_t)(wq * 32) << 16);
+    const uint32_t o_row = lane_base;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    auto tile = [&](int j, auto mask_tag) -> bool {
+      constexpr bool MASK = decltype(mask_tag)::value;
+      const int st = j & 1;
+      const uint32_t s_row = lane_base + 256u + (uint32_t)(st * BKV2);
+      if (!mbar_wait(&sh->s_full[st], (uint32_t)((j >> 1) & 1), abort_flag)) return false;
+      tc_fence_after();
+      const int limit = min(my_pos, kv_len - 1) - j * BKV2;  // columns 0 .. limit are visible to this row
+      uint32_t v[BKV2];
+      tmem_ld32(s_row, v);
+      tmem_ld32(s_row + 32, v + 32);
+      tmem_ld_wait();
+      float mx_raw;
+      if constexpr (MASK) {
+        mx_raw = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < BKV2; ++i)
+          if (i <= limit) mx_raw = fmaxf(mx_raw, __uint_as_float(v[i]));
+      } else {
+        float m0 = max3(__uint_as_float(v[0]), __uint_as_float(v[1]), __uint_as_float(v[2]));
+        float m1 = max3(__uint_as_float(v[3]), __uint_as_float(v[4]), __uint_as_float(v[5]));
+        float m2 = max3(__uint_as_float(v[6]), __uint_as_float(v[7]), __uint_as_float(v[8]));
+        float m3 = max3(__uint_as_float(v[9]), __uint_as_float(v[10]), __uint_as_float(v[11]));
+#pragma unroll
+        for (int i = 12; i + 7 < BKV2; i += 8) {
+          m0 = max3(m0, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+          m1 = max3(m1, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+          m2 = max3(m2, __uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+          m3 = max3(m3, __uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
+        }
+        // 12 + 8 * 6 = 60: four columns left
+        m0 = max3(m0, __uint_as_float(v[60]), __uint_as_float(v[61]));
+        m1 = max3(m1, __uint_as_float(v[62]), __uint_as_float(v[63]));
+        mx_raw = fmaxf(max3(m0, m1, m2), m3);
+      }
+      const float mx = mx_raw * p.scale_log2;
+      // the previous product must be complete before O is rescaled
+      if (j >= 1) {
+        if (!mbar_wait(&sh->o_full, (uint32_t)((j - 1) & 1), abort_flag)) return false;
+        tc_fence_after();
+      }
+      float alpha = 1.f;
+      if (mx > m + RESCALE_LOG2 || (m == -INFINITY && mx > -INFINITY)) {
+        alpha = (m == -INFINITY) ? 0.f : ex2_approx(m - mx);
+        m = mx;
+      }
+      if (j >= 1 && __any_sync(0xFFFFFFFFu, alpha != 1.f)) {
+        const float2 a2 = make_float2(alpha, alpha);
+#pragma unroll 1
+        for (int c = 0; c < D2; c += 32) {
+          uint32_t w[32];
+          tmem_ld32(o_row + c, w);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float2 t2 = __fmul2_rn(make_float2(__uint_as_float(w[i]), __uint_as_float(w[i + 1])), a2);
+            w[i] = __float_as_uint(t2.x);
+            w[i + 1] = __float_as_uint(t2.y);
+          }
+          tmem_st16(o_row + c, w);
+          tmem_st16(o_row + c + 16, w + 16);
+        }
+        l *= alpha;
+      }
+      const float neg = (m == -INFINITY) ? 0.f : -m;
+      float2 sum2 = make_float2(0.f, 0.f), sum3 = make_float2(0.f, 0.f);
+      const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), ng2 = make_float2(neg, neg);
+#pragma unroll
+      for (int c = 0; c < BKV2; c += 32) {
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          const float2 t2 = __ffma2_rn(make_float2(__uint_as_float(v[c + i]), __uint_as_float(v[c + i + 1])), sc2, ng2);
+          const float2 t3 = __ffma2_rn(make_float2(__uint_as_float(v[c + i + 2]), __uint_as_float(v[c + i + 3])), sc2, ng2);
+          float2 e = make_float2(ex2_approx(t2.x), ex2_approx(t2.y));
+          float2 f = make_float2(ex2_approx(t3.x), ex2_approx(t3.y));
+          if constexpr (MASK) {
+            if (c + i > limit) e.x = 0.f;
+            if (c + i + 1 > limit) e.y = 0.f;
+            if (c + i + 2 > limit) f.x = 0.f;
+            if (c + i + 3 > limit) f.y = 0.f;
+          }
+          sum2 = __fadd2_rn(sum2, e);
+          sum3 = __fadd2_rn(sum3, f);
+          const bf162 pe = __floats2bfloat162_rn(e.x, e.y), pf = __floats2bfloat162_rn(f.x, f.y);
+          packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&pe);
+          packed[(i >> 1) + 1] = *reinterpret_cast<const uint32_t*>(&pf);
+        }
+        tmem_st16(s_row + (c >> 1), packed);
+      }
+      sum2 = __fadd2_rn(sum2, sum3);
+      tmem_st_wait();
+      l += sum2.x + sum2.y;
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->p_ready[st]);
+      return true;
+    };
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const bool need_mask = j * BKV2 + BKV2 - 1 > min(pos0, kv_len - 1);
+      ok = need_mask ? tile(j, std::true_type{}) : tile(j, std::false_type{});
+    }
+    if (ok && n_tiles > 0) {
+      ok = mbar_wait(&sh->o_full, (uint32_t)((n_tiles - 1) & 1), abort_flag);
+      tc_fence_after();
+    }
+    const float inv = (ok && l > 0.f) ? 1.f / l : 0.f;
+    bf16* dst = p.out + ((long long)(q0 + row_base + r) * p.hq + hq) * D2;
+#pragma unroll 1
+    for (int c = 0; c < D2; c += 32) {
+      uint32_t w[32];
+      if (n_tiles > 0) {
+        tmem_ld32(o_row + c, w);
+        tmem_ld_wait();
+      }
+      if (r < rows_here) {
+#pragma unroll
+        for (int c8 = 0; c8 < 32; c8 += 8) {
+          float f[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) f[i] = n_tiles > 0 ? __uint_as_float(w[c8 + i]) * inv : 0.f;
+          *reinterpret_cast<bf16x8*>(dst + c + c8) = pack8(f);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+  if (threadIdx.x == 0 && sh->abort_flag) atomicCAS(p.status, PG_ST_OK, PG_ST_TIMEOUT | (42u << 8));
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
@@ -464,13 +784,13 @@ EncodeTiledFn get_encode_attn() {
   return fn;
 }
 
-// [rows, heads, 128] bf16, contiguous; box = 64 columns x 1 head x box_rows rows, 128-byte swizzle
-int make_tmap_rows_heads(CUtensorMap* out, const void* ptr, long long rows, int heads, int box_rows) {
+// [rows, heads, dim] bf16, contiguous; box = 64 columns x 1 head x box_rows rows, 128-byte swizzle
+int make_tmap_rows_heads(CUtensorMap* out, const void* ptr, long long rows, int heads, int box_rows, int dim = D) {
   EncodeTiledFn enc = get_encode_attn();
   PG_REQUIRE(enc != nullptr, "cuTensorMapEncodeTiled is not available from this driver");
   PG_REQUIRE(((uintptr_t)ptr & 15) == 0, "TMA base address must be 16-byte aligned");
-  cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)heads, (cuuint64_t)rows};
-  cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)heads * D * 2};
+  cuuint64_t dims[3] = {(cuuint64_t)dim, (cuuint64_t)heads, (cuuint64_t)rows};
+  cuuint64_t strides[2] = {(cuuint64_t)dim * 2, (cuuint64_t)heads * dim * 2};
   cuuint32_t box[3] = {64u, 1u, (cuuint32_t)box_rows};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -486,20 +806,21 @@ int g_mn_variant = -1;
 // Test hook: which of the two stride fields of the MN-major descriptor carries the 64-column block stride.
 extern "C" void pg_prefill_attention_tc_variant(int v) { g_mn_variant = v; }
 
-// q [T, hq, 128] bf16 (contiguous), kv_layer [pages, 2, page_size, hkv, 128], out [T, hq * 128].  `q_tiles` = sum over the
-// sequences of ceil(query rows / 256).
+// q [T, hq, d] bf16 (contiguous), kv_layer [pages, 2, page_size, hkv, d], out [T, hq * d], d = 128 or 256.  `q_tiles` = sum
+// over the sequences of ceil(query rows / 256) for d = 128 and of ceil(query rows / 128) for d = 256.
 extern "C" int pg_prefill_attention_tc(const void* q, const void* kv_layer, void* out, const void* q_indptr, const void* kv_lens, const void* table, int table_stride,
                                        int num_seqs, int tokens, int hq, int hkv, int dim, int page_size, long long num_pages, float scale, int q_tiles, void* status,
                                        cudaStream_t stream) {
-  PG_REQUIRE(dim == D, "tcgen05 prefill attention is built for head dim 128 (got %d)", dim);
-  PG_REQUIRE(page_size >= 8 && page_size <= 128 && BKV % page_size == 0, "page size %d does not tile 128 keys", page_size);
+  PG_REQUIRE(dim == D || dim == D2, "tcgen05 prefill attention is built for head dims 128 and 256 (got %d)", dim);
+  const int key_tile = dim == D ? BKV : BKV2;
+  PG_REQUIRE(page_size >= 8 && page_size <= key_tile && key_tile % page_size == 0, "page size %d does not tile %d keys", page_size, key_tile);
   PG_REQUIRE(num_pages * 2 * page_size < (1ll << 31), "KV cache of %lld pages is too large for 32-bit TMA row coordinates", num_pages);
   PG_REQUIRE(hq % hkv == 0, "query heads %d are not a multiple of the KV heads %d", hq, hkv);
   if (q_tiles == 0 || tokens == 0) return PG_OK;
   CUtensorMap tm_q, tm_kv;
-  int rc = make_tmap_rows_heads(&tm_q, q, tokens, hq, 128);
+  int rc = make_tmap_rows_heads(&tm_q, q, tokens, hq, 128, dim);
   if (rc != PG_OK) return rc;
-  rc = make_tmap_rows_heads(&tm_kv, kv_layer, num_pages * 2 * page_size, hkv, page_size);
+  rc = make_tmap_rows_heads(&tm_kv, kv_layer, num_pages * 2 * page_size, hkv, page_size, dim);
   if (rc != PG_OK) return rc;
   TcAttnParams p;
   p.out = (bf16*)out;
@@ -515,6 +836,17 @@ extern "C" int pg_prefill_attention_tc(const void* q, const void* kv_layer, void
   p.scale_log2 = scale * 1.4426950408889634f;
   p.mn_lbo_first = g_mn_variant < 0 ? 1 : g_mn_variant;
   p.status = (uint32_t*)status;
+  if (dim == D2) {
+    const size_t smem2 = 1024 + (size_t)Q2_BYTES + 4 * (size_t)KV2_BYTES + sizeof(TcSmem2) + 64;
+    static bool attr2_done = false;
+    if (!attr2_done) {
+      PG_CUDA(cudaFuncSetAttribute(prefill_attn_tc256_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2));
+      attr2_done = true;
+    }
+    PG_CUDA(launch_pdl(prefill_attn_tc256_kernel, dim3((unsigned)q_tiles * (unsigned)hq), dim3(THREADS2), smem2, stream, tm_q, tm_kv, p));
+    PG_LAUNCH_CHECK();
+    return PG_OK;
+  }
   const size_t smem = 1024 + (GROUPS + 4) * (size_t)TILE_BYTES + sizeof(TcSmem) + 64;
   static bool attr_done = false;
   if (!attr_done) {

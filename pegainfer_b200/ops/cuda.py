@@ -509,10 +509,11 @@ def qk_norm_rope_append(qkv, q_norm_w, k_norm_w, cos, sin, meta: AttnMeta, kv_la
 
 _BATCH_INVARIANT = False
 INVARIANT_KV_SPLITS = 4
-_PREFILL_TC = os.environ.get("PEGAINFER_PREFILL_TC", "1") != "0"  # tcgen05 prefill attention for head dim 128
+_PREFILL_TC = os.environ.get("PEGAINFER_PREFILL_TC", "1") != "0"  # tcgen05 prefill attention for head dims 128 and 256
 _PREFILL_TC_MIN_ROWS = int(os.environ.get("PEGAINFER_PREFILL_TC_MIN_ROWS", "64"))  # shorter chunks keep the 64-row mma.sync tiles
-# the tcgen05 kernel wins once a sequence is a few thousand keys long (measured 1.37x at 4096, 1.58x at 16384, 0.98x at 1024)
-_PREFILL_TC_MIN_KV = int(os.environ.get("PEGAINFER_PREFILL_TC_MIN_KV", "2048"))
+# the tcgen05 kernel wins from a few hundred keys on (head dim 128, against the mma.sync kernel: 1.0x at 256 keys, 1.3x at 512,
+# 1.9x at 1024, 3.2x at 4096, 3.8x at 16384)
+_PREFILL_TC_MIN_KV = int(os.environ.get("PEGAINFER_PREFILL_TC_MIN_KV", "512"))
 
 
 def set_prefill_tc(min_kv: int) -> int:
@@ -588,10 +589,12 @@ def paged_attention(q, kv_layer, meta: AttnMeta, scale=None, window=0, out: Opti
         if meta.num_seqs - n_pf < (1 if _BATCH_INVARIANT else _MIXED_DECODE_MIN):
             n_pf = meta.num_seqs
     # (not under the batch-invariant policy: which kernel runs would depend on the other sequences of the step)
-    if (n_pf > 0 and d == 128 and window == 0 and _PREFILL_TC and not _BATCH_INVARIANT and 128 % page_size == 0 and q.is_contiguous() and max(qi[b + 1] - qi[b] for b in range(n_pf)) >= _PREFILL_TC_MIN_ROWS
+    if (n_pf > 0 and d in (128, 256) and window == 0 and _PREFILL_TC and not _BATCH_INVARIANT and (128 if d == 128 else 64) % page_size == 0 and q.is_contiguous() and max(qi[b + 1] - qi[b] for b in range(n_pf)) >= _PREFILL_TC_MIN_ROWS
             and (meta.h_kv_lens is None or max(meta.h_kv_lens[:n_pf]) >= _PREFILL_TC_MIN_KV)):
-        # tcgen05 kernel: 128 query rows of one head per CTA, S and P V on the tensor cores, accumulators in TMEM
-        q_tiles = sum((qi[b + 1] - qi[b] + 255) // 256 for b in range(n_pf))
+        # tcgen05 kernel: 256 (head dim 128) or 128 (head dim 256) query rows of one head per CTA, S and P V on the
+        # tensor cores, accumulators in TMEM
+        rows_per_cta = 256 if d == 128 else 128
+        q_tiles = sum((qi[b + 1] - qi[b] + rows_per_cta - 1) // rows_per_cta for b in range(n_pf))
         rc = lib().pg_prefill_attention_tc(_ptr(q), _ptr(kv_layer), _ptr(out), _ptr(meta.q_indptr), _ptr(meta.kv_lens), _ptr(table), _ci(table.stride(0)), _ci(n_pf), _ci(qi[n_pf]),
                                            _ci(hq), _ci(hkv), _ci(d), _ci(page_size), _ll(kv_layer.shape[0]), _cf(scale), _ci(q_tiles), _ptr(c.status), _stream())
         _check(rc, c)

@@ -809,14 +809,15 @@ def test_fp8_block_scaled_gemm_matches_reference(t, m, k):
     status_clean()
 
 
-@pytest.mark.parametrize("page", [16, 64])
-def test_tcgen05_prefill_attention_matches_reference(page):
-    """Ragged prefill (whole prompts, a chunk behind a cached prefix, a short tail) through the tcgen05 kernel."""
+@pytest.mark.parametrize("page,d", [(16, 128), (64, 128), (16, 256), (64, 256), (32, 256)])
+def test_tcgen05_prefill_attention_matches_reference(page, d):
+    """Ragged prefill (whole prompts, a chunk behind a cached prefix, a short tail) through the tcgen05 kernels
+    (head dim 128: two query tiles per CTA; head dim 256: one query tile, double-buffered scores)."""
     from pegainfer_b200.kv.request_kv import KvView
     from pegainfer_b200.sched.executor import SeqStep, build_meta
 
     K = cu()
-    hq, hkv, d = 8, 2, 128
+    hq, hkv = 8, 2
     g = torch.Generator(device=DEV).manual_seed(3)
     cases = [(300, 300), (700, 257), (128, 128), (1000, 130), (90, 70)]  # (kv_len, query rows)
     seqs, nxt = [], 1
