@@ -226,6 +226,51 @@ def mla_cases(iters):
     return rows
 
 
+def time_eager(fn, iters, warm=3):
+    """ms per call of a host-driven op (not graph-capturable: it uploads small index tensors), CUDA events around `iters` calls."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def mla_prefill_cases(iters, only=None):
+    """MLA prefill, whole op (query absorb or K / V expansion included): the expanded form on the tcgen05 kernel against
+    the absorbed form on the mma.sync kernel.  FLOPs counted in the expanded form: causal 4 x (192 + 128) / 2 per pair."""
+    from pegainfer_b200.ops import cuda as K
+    from pegainfer_b200.ops import reference as R
+
+    rows = []
+    c, rope, nope, vd = 512, 64, 128, 128
+    for heads, ns, ql in only or ((16, 4, 1024), (16, 1, 4096), (16, 1, 8192), (64, 1, 4096)):
+        meta, npages = _meta_for([ql] * ns, [ql] * ns, 16)
+        latent = torch.randn(npages, 16, c + rope, device=DEV).bfloat16() * 0.5
+        q = torch.randn(ns * ql, heads, nope + rope, device=DEV).bfloat16() * 0.5
+        w_uk = torch.randn(heads, nope, c, device=DEV).bfloat16() * 0.05
+        w_uv = torch.randn(heads, vd, c, device=DEV).bfloat16() * 0.05
+        cos, sin = R.rope_tables(max(4096, ql), rope, 10000.0, torch.bfloat16, DEV)
+        qq = K.mla_rope_q(q, cos, sin, meta, nope)
+        scale = (nope + rope) ** -0.5
+        fl = 2.0 * ns * (ql * ql / 2) * heads * (nope + rope + vd)
+        by = ns * ql * (c + rope) * 2
+        ms = time_eager(lambda: K.mla_attention(qq, w_uk, w_uv, latent, meta, scale, c), max(2, iters // 2))
+        rows.append((f"mla prefill {heads}h {ns}x{ql}, expanded on tcgen05 (gather + expand GEMMs + attention)", ms, by, fl))
+        prev = K._PREFILL_TC
+        K._PREFILL_TC = False
+        try:
+            ms = time_eager(lambda: K.mla_attention(qq, w_uk, w_uv, latent, meta, scale, c), max(2, iters // 4))
+        finally:
+            K._PREFILL_TC = prev
+        rows.append((f"  absorbed on mma.sync (absorb GEMM + attention over 576 / 512 + v_up)", ms, by, fl))
+    return rows
+
+
 GEMM_PHASES = ["entry", "prologue done", "predecessor complete", "all loads issued", "first stage landed", "last MMA committed", "accumulator ready",
                "partial pushed", "cluster partials in", "reduced + stored", "roles done", "cluster released", "token tiles issued", "second stage landed", "seventh stage landed"]
 
@@ -427,6 +472,11 @@ def main():
             name, ms, by, fl = dsa_cases(args.iters, only=[tuple(dims)])[0]
         elif kind == "attn":
             ms, by, fl = attn_decode_case(dims[0], dims[1], 32, 8, 128, 16, args.iters)
+        elif kind == "mlaprefill":  # heads x sequences x tokens
+            r2 = mla_prefill_cases(args.iters, only=[tuple(dims)])
+            rows.extend(r2[:-1])
+            name, ms, by, fl = r2[-1]
+            args.single = name
         elif kind == "prefill256":  # the gated full-attention layers of Qwen3.5-27B: 24 query / 4 KV heads of 256
             ms, by, fl = attn_prefill_case(dims[0], dims[1], 24, 4, 256, 16, args.iters)
         else:

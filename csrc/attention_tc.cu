@@ -468,6 +468,106 @@ constexpr int KV2_BYTES = BKV2 * D2 * 2;   // 32 KB: [4 blocks of 64 columns][64
 constexpr int KV2_BLOCK = BKV2 * 128;      // 8 KB
 constexpr int THREADS2 = 64 + 128;
 
+// One tile of 64 keys for one query row per thread (the head-dim-256 and MLA kernels): S of the tile -> registers ->
+// maximum -> lazy rescale of O (`o_cols` columns at `o_row`) -> P as bf16 over the first 32 columns of S -> `p_ready`.
+// `o_full` / `o_parity` name the completion of the previous product into the same O (ignored for j == 0).
+template <bool MASK>
+__device__ __forceinline__ bool softmax_tile64(uint64_t* s_full, uint32_t s_parity, uint32_t s_row, uint32_t o_row, int o_cols, uint64_t* o_full, uint32_t o_parity, int j, int limit,
+                                               float scale_log2, float& m, float& l, uint64_t* p_ready, int lane, volatile int* abort_flag) {
+  if (!mbar_wait(s_full, s_parity, abort_flag)) return false;
+  tc_fence_after();
+  uint32_t v[BKV2];
+  tmem_ld32(s_row, v);
+  tmem_ld32(s_row + 32, v + 32);
+  tmem_ld_wait();
+  float mx_raw;
+  if constexpr (MASK) {
+    mx_raw = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < BKV2; ++i)
+      if (i <= limit) mx_raw = fmaxf(mx_raw, __uint_as_float(v[i]));
+  } else {
+    float m0 = max3(__uint_as_float(v[0]), __uint_as_float(v[1]), __uint_as_float(v[2]));
+    float m1 = max3(__uint_as_float(v[3]), __uint_as_float(v[4]), __uint_as_float(v[5]));
+    float m2 = max3(__uint_as_float(v[6]), __uint_as_float(v[7]), __uint_as_float(v[8]));
+    float m3 = max3(__uint_as_float(v[9]), __uint_as_float(v[10]), __uint_as_float(v[11]));
+#pragma unroll
+    for (int i = 12; i + 7 < BKV2; i += 8) {
+      m0 = max3(m0, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+      m1 = max3(m1, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+      m2 = max3(m2, __uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+      m3 = max3(m3, __uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
+    }
+    // 12 + 8 * 6 = 60: four columns left
+    m0 = max3(m0, __uint_as_float(v[60]), __uint_as_float(v[61]));
+    m1 = max3(m1, __uint_as_float(v[62]), __uint_as_float(v[63]));
+    mx_raw = fmaxf(max3(m0, m1, m2), m3);
+  }
+  const float mx = mx_raw * scale_log2;
+  // the previous product must be complete before O is rescaled
+  if (j >= 1) {
+    if (!mbar_wait(o_full, o_parity, abort_flag)) return false;
+    tc_fence_after();
+  }
+  float alpha = 1.f;
+  if (mx > m + RESCALE_LOG2 || (m == -INFINITY && mx > -INFINITY)) {
+    alpha = (m == -INFINITY) ? 0.f : ex2_approx(m - mx);
+    m = mx;
+  }
+  if (j >= 1 && __any_sync(0xFFFFFFFFu, alpha != 1.f)) {
+    const float2 a2 = make_float2(alpha, alpha);
+#pragma unroll 1
+    for (int c = 0; c < o_cols; c += 32) {
+      uint32_t w[32];
+      tmem_ld32(o_row + c, w);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        const float2 t2 = __fmul2_rn(make_float2(__uint_as_float(w[i]), __uint_as_float(w[i + 1])), a2);
+        w[i] = __float_as_uint(t2.x);
+        w[i + 1] = __float_as_uint(t2.y);
+      }
+      tmem_st16(o_row + c, w);
+      tmem_st16(o_row + c + 16, w + 16);
+    }
+    l *= alpha;
+  }
+  const float neg = (m == -INFINITY) ? 0.f : -m;
+  float2 sum2 = make_float2(0.f, 0.f), sum3 = make_float2(0.f, 0.f);
+  const float2 sc2 = make_float2(scale_log2, scale_log2), ng2 = make_float2(neg, neg);
+#pragma unroll
+  for (int c = 0; c < BKV2; c += 32) {
+    uint32_t packed[16];
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+      const float2 t2 = __ffma2_rn(make_float2(__uint_as_float(v[c + i]), __uint_as_float(v[c + i + 1])), sc2, ng2);
+      const float2 t3 = __ffma2_rn(make_float2(__uint_as_float(v[c + i + 2]), __uint_as_float(v[c + i + 3])), sc2, ng2);
+      float2 e = make_float2(ex2_approx(t2.x), ex2_approx(t2.y));
+      float2 f = make_float2(ex2_approx(t3.x), ex2_approx(t3.y));
+      if constexpr (MASK) {
+        if (c + i > limit) e.x = 0.f;
+        if (c + i + 1 > limit) e.y = 0.f;
+        if (c + i + 2 > limit) f.x = 0.f;
+        if (c + i + 3 > limit) f.y = 0.f;
+      }
+      sum2 = __fadd2_rn(sum2, e);
+      sum3 = __fadd2_rn(sum3, f);
+      const bf162 pe = __floats2bfloat162_rn(e.x, e.y), pf = __floats2bfloat162_rn(f.x, f.y);
+      packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&pe);
+      packed[(i >> 1) + 1] = *reinterpret_cast<const uint32_t*>(&pf);
+    }
+    tmem_st16(s_row + (c >> 1), packed);
+  }
+  sum2 = __fadd2_rn(sum2, sum3);
+  tmem_st_wait();
+  l += sum2.x + sum2.y;
+  tc_fence_before();
+  __syncwarp();
+  if (lane == 0) mbar_arrive(p_ready);
+  return true;
+}
+
+
 struct TcSmem2 {
   uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_ready[2], o_full;
   uint32_t tmem_slot;
@@ -634,106 +734,14 @@ __global__ void __launch_bounds__(THREADS2, 1) prefill_attn_tc256_kernel(const _
     const uint32_t o_row = lane_base;
     float m = -INFINITY, l = 0.f;
     bool ok = true;
-    auto tile = [&](int j, auto mask_tag) -> bool {
-      constexpr bool MASK = decltype(mask_tag)::value;
-      const int st = j & 1;
-      const uint32_t s_row = lane_base + 256u + (uint32_t)(st * BKV2);
-      if (!mbar_wait(&sh->s_full[st], (uint32_t)((j >> 1) & 1), abort_flag)) return false;
-      tc_fence_after();
-      const int limit = min(my_pos, kv_len - 1) - j * BKV2;  // columns 0 .. limit are visible to this row
-      uint32_t v[BKV2];
-      tmem_ld32(s_row, v);
-      tmem_ld32(s_row + 32, v + 32);
-      tmem_ld_wait();
-      float mx_raw;
-      if constexpr (MASK) {
-        mx_raw = -INFINITY;
-#pragma unroll
-        for (int i = 0; i < BKV2; ++i)
-          if (i <= limit) mx_raw = fmaxf(mx_raw, __uint_as_float(v[i]));
-      } else {
-        float m0 = max3(__uint_as_float(v[0]), __uint_as_float(v[1]), __uint_as_float(v[2]));
-        float m1 = max3(__uint_as_float(v[3]), __uint_as_float(v[4]), __uint_as_float(v[5]));
-        float m2 = max3(__uint_as_float(v[6]), __uint_as_float(v[7]), __uint_as_float(v[8]));
-        float m3 = max3(__uint_as_float(v[9]), __uint_as_float(v[10]), __uint_as_float(v[11]));
-#pragma unroll
-        for (int i = 12; i + 7 < BKV2; i += 8) {
-          m0 = max3(m0, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
-          m1 = max3(m1, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
-          m2 = max3(m2, __uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
-          m3 = max3(m3, __uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
-        }
-        // 12 + 8 * 6 = 60: four columns left
-        m0 = max3(m0, __uint_as_float(v[60]), __uint_as_float(v[61]));
-        m1 = max3(m1, __uint_as_float(v[62]), __uint_as_float(v[63]));
-        mx_raw = fmaxf(max3(m0, m1, m2), m3);
-      }
-      const float mx = mx_raw * p.scale_log2;
-      // the previous product must be complete before O is rescaled
-      if (j >= 1) {
-        if (!mbar_wait(&sh->o_full, (uint32_t)((j - 1) & 1), abort_flag)) return false;
-        tc_fence_after();
-      }
-      float alpha = 1.f;
-      if (mx > m + RESCALE_LOG2 || (m == -INFINITY && mx > -INFINITY)) {
-        alpha = (m == -INFINITY) ? 0.f : ex2_approx(m - mx);
-        m = mx;
-      }
-      if (j >= 1 && __any_sync(0xFFFFFFFFu, alpha != 1.f)) {
-        const float2 a2 = make_float2(alpha, alpha);
-#pragma unroll 1
-        for (int c = 0; c < D2; c += 32) {
-          uint32_t w[32];
-          tmem_ld32(o_row + c, w);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float2 t2 = __fmul2_rn(make_float2(__uint_as_float(w[i]), __uint_as_float(w[i + 1])), a2);
-            w[i] = __float_as_uint(t2.x);
-            w[i + 1] = __float_as_uint(t2.y);
-          }
-          tmem_st16(o_row + c, w);
-          tmem_st16(o_row + c + 16, w + 16);
-        }
-        l *= alpha;
-      }
-      const float neg = (m == -INFINITY) ? 0.f : -m;
-      float2 sum2 = make_float2(0.f, 0.f), sum3 = make_float2(0.f, 0.f);
-      const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), ng2 = make_float2(neg, neg);
-#pragma unroll
-      for (int c = 0; c < BKV2; c += 32) {
-        uint32_t packed[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          const float2 t2 = __ffma2_rn(make_float2(__uint_as_float(v[c + i]), __uint_as_float(v[c + i + 1])), sc2, ng2);
-          const float2 t3 = __ffma2_rn(make_float2(__uint_as_float(v[c + i + 2]), __uint_as_float(v[c + i + 3])), sc2, ng2);
-          float2 e = make_float2(ex2_approx(t2.x), ex2_approx(t2.y));
-          float2 f = make_float2(ex2_approx(t3.x), ex2_approx(t3.y));
-          if constexpr (MASK) {
-            if (c + i > limit) e.x = 0.f;
-            if (c + i + 1 > limit) e.y = 0.f;
-            if (c + i + 2 > limit) f.x = 0.f;
-            if (c + i + 3 > limit) f.y = 0.f;
-          }
-          sum2 = __fadd2_rn(sum2, e);
-          sum3 = __fadd2_rn(sum3, f);
-          const bf162 pe = __floats2bfloat162_rn(e.x, e.y), pf = __floats2bfloat162_rn(f.x, f.y);
-          packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&pe);
-          packed[(i >> 1) + 1] = *reinterpret_cast<const uint32_t*>(&pf);
-        }
-        tmem_st16(s_row + (c >> 1), packed);
-      }
-      sum2 = __fadd2_rn(sum2, sum3);
-      tmem_st_wait();
-      l += sum2.x + sum2.y;
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sh->p_ready[st]);
-      return true;
-    };
     for (int j = 0; j < n_tiles && ok; ++j) {
       const bool need_mask = j * BKV2 + BKV2 - 1 > min(pos0, kv_len - 1);
-      ok = need_mask ? tile(j, std::true_type{}) : tile(j, std::false_type{});
+      const int st = j & 1;
+      const uint32_t s_row = lane_base + 256u + (uint32_t)(st * BKV2);
+      const int limit = min(my_pos, kv_len - 1) - j * BKV2;  // columns 0 .. limit are visible to this row
+      const uint32_t sp = (uint32_t)((j >> 1) & 1), op = (uint32_t)((j - 1) & 1);
+      ok = need_mask ? softmax_tile64<true>(&sh->s_full[st], sp, s_row, o_row, D2, &sh->o_full, op, j, limit, p.scale_log2, m, l, &sh->p_ready[st], lane, abort_flag)
+                     : softmax_tile64<false>(&sh->s_full[st], sp, s_row, o_row, D2, &sh->o_full, op, j, limit, p.scale_log2, m, l, &sh->p_ready[st], lane, abort_flag);
     }
     if (ok && n_tiles > 0) {
       ok = mbar_wait(&sh->o_full, (uint32_t)((n_tiles - 1) & 1), abort_flag);
@@ -769,6 +777,253 @@ __global__ void __launch_bounds__(THREADS2, 1) prefill_attn_tc256_kernel(const _
   if (threadIdx.x == 0 && sh->abort_flag) atomicCAS(p.status, PG_ST_OK, PG_ST_TIMEOUT | (42u << 8));
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Multi-head latent attention, prefill, in the expanded (not absorbed) form: per head, queries and keys of 128 + 64
+// (rotary part, one key row shared by all heads) and values of 128, keys and values dense rows [sum of kv lengths, heads,
+// 128] that the caller expanded from the gathered latent rows with the up-projection GEMMs.  The absorbed form the decode
+// kernel uses would contract over 576 and accumulate 512 columns per row; expanded, a prefill chunk costs a quarter of
+// the FLOPs and O fits tensor memory.  Structure as for head dim 128 (two query tiles of 128 rows per CTA whose softmax
+// groups alternate on the tensor core, P in tensor memory), with key tiles of 64 so that Q (2 x 48 KB) and two stages of
+// K (24 KB) and V (16 KB) fit shared memory.  The rotary block of Q and K comes through tensor maps of its own.
+//
+// Reference parity: pegainfer-kernels/csrc/k3/k3_flash_mla_prefill.cu (gather / expand, then a dense SM100 FMHA).
+constexpr int MQ_BYTES = 128 * 192 * 2;  // 48 KB: [3 blocks of 64 columns][128 rows][128 B]
+constexpr int MK_BYTES = BKV2 * 192 * 2; // 24 KB: [3 blocks][64 rows][128 B]
+constexpr int MV_BYTES = BKV2 * 128 * 2; // 16 KB: [2 blocks][64 rows][128 B]
+
+struct MlaTcParams {
+  bf16* out;             // [T, heads * 128]
+  const int* q_indptr;   // [num_seqs + 1]
+  const int* kv_indptr;  // [num_seqs + 1] rows of the dense K / V
+  const int* kv_lens;    // [num_seqs]
+  int num_seqs, heads;
+  float scale_log2;
+  int mn_lbo_first;
+  uint32_t* status;
+};
+
+__global__ void __launch_bounds__(THREADS, 1) mla_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_qn, const __grid_constant__ CUtensorMap tm_qpe,
+                                                                    const __grid_constant__ CUtensorMap tm_kn, const __grid_constant__ CUtensorMap tm_kpe,
+                                                                    const __grid_constant__ CUtensorMap tm_v, const MlaTcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = smem_u32(smem_raw);
+  uint8_t* tiles = smem_raw + (((base + 1023u) & ~1023u) - base);
+  uint8_t* q_tile = tiles;                    // GROUPS x 48 KB
+  uint8_t* k_tile = tiles + GROUPS * MQ_BYTES;  // 2 x 24 KB
+  uint8_t* v_tile = k_tile + 2 * MK_BYTES;    // 2 x 16 KB
+  TcSmem* sh = reinterpret_cast<TcSmem*>(v_tile + 2 * MV_BYTES);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = (int)(blockIdx.x % (unsigned)p.heads);
+  int b = 0, tile_in_seq = 0;  // late tiles (most keys) first, every head's before any early tile
+  {
+    int rem = (int)(gridDim.x / (unsigned)p.heads) - 1 - (int)(blockIdx.x / (unsigned)p.heads);
+    for (; b < p.num_seqs; ++b) {
+      const int n = p.q_indptr[b + 1] - p.q_indptr[b];
+      const int nt = (n + BQ2 - 1) / BQ2;
+      if (rem < nt) {
+        tile_in_seq = rem;
+        break;
+      }
+      rem -= nt;
+    }
+    if (b >= p.num_seqs) return;
+  }
+  if (threadIdx.x == 0) {
+    mbar_init(&sh->q_full, 1);
+    for (int s2 = 0; s2 < 2; ++s2) {
+      mbar_init(&sh->k_full[s2], 1);
+      mbar_init(&sh->k_empty[s2], 1);
+      mbar_init(&sh->v_full[s2], 1);
+      mbar_init(&sh->v_empty[s2], 1);
+    }
+    for (int g = 0; g < GROUPS; ++g) {
+      mbar_init(&sh->s_full[g], 1);
+      mbar_init(&sh->p_ready[g], 4);
+      mbar_init(&sh->o_full[g], 1);
+    }
+    sh->abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tm_qn);
+    tma_prefetch_desc(&tm_qpe);
+    tma_prefetch_desc(&tm_kn);
+    tma_prefetch_desc(&tm_kpe);
+    tma_prefetch_desc(&tm_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(&sh->tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sh->tmem_slot;  // columns: S / P of group g at 128 g (64 used), O of group g at 256 + 128 g
+  volatile int* abort_flag = &sh->abort_flag;
+  PG_PDL_ENTRY();
+
+  const int q0 = p.q_indptr[b], q_len = p.q_indptr[b + 1] - q0;
+  const int kv_len = p.kv_lens[b], kv0 = p.kv_indptr[b];
+  const int row_base = tile_in_seq * BQ2;
+  const int rows_here = min(BQ2, q_len - row_base);
+  const int pos_base = kv_len - q_len + row_base;
+  int n_g[GROUPS];
+#pragma unroll
+  for (int g = 0; g < GROUPS; ++g) {
+    const int rows_of_g = min(128, rows_here - g * 128);
+    n_g[g] = (rows_of_g > 0 && kv_len > 0) ? min(pos_base + g * 128 + rows_of_g - 1, kv_len - 1) / BKV2 + 1 : 0;
+  }
+  const int n_tiles = max(n_g[0], n_g[1]);
+
+  if (warp == 0) {
+    if (n_tiles > 0) {
+      const uint64_t pol = l2_policy_evict_normal();
+      if (lane == 0) {
+        mbar_expect_tx(&sh->q_full, GROUPS * MQ_BYTES);
+#pragma unroll
+        for (int g = 0; g < GROUPS; ++g) {
+          const int row = q0 + row_base + g * 128;
+          tma_load_3d(q_tile + g * MQ_BYTES, &tm_qn, &sh->q_full, 0, row, h, pol);            // nope columns 0 .. 63   ([heads, T, 128])
+          tma_load_3d(q_tile + g * MQ_BYTES + 16384, &tm_qn, &sh->q_full, 64, row, h, pol);   // nope columns 64 .. 127
+          tma_load_3d(q_tile + g * MQ_BYTES + 32768, &tm_qpe, &sh->q_full, 0, h, row, pol);   // rotary part            ([T, heads, 64])
+        }
+      }
+      // five boxes per tile, one lane each: K nope (2), K rotary, V (2)
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int st = j & 1;
+        const int row = kv0 + j * BKV2;  // rows past the sequence belong to the next one (or are filled with zeros): masked
+        if (j >= 2) {
+          const uint32_t par = (uint32_t)(((j >> 1) - 1) & 1);
+          ok = mbar_wait(&sh->k_empty[st], par, abort_flag) && mbar_wait(&sh->v_empty[st], par, abort_flag);
+          ok = __all_sync(0xFFFFFFFFu, ok);
+          if (!ok) break;
+        }
+        if (lane == 0) {
+          mbar_expect_tx(&sh->k_full[st], MK_BYTES);
+          mbar_expect_tx(&sh->v_full[st], MV_BYTES);
+        }
+        __syncwarp();
+        if (lane < 2) tma_load_3d(k_tile + st * MK_BYTES + lane * 8192, &tm_kn, &sh->k_full[st], lane * 64, h, row, pol);
+        else if (lane == 2) tma_load_2d(k_tile + st * MK_BYTES + 16384, &tm_kpe, &sh->k_full[st], 0, row, pol);
+        else if (lane < 5) tma_load_3d(v_tile + st * MV_BYTES + (lane - 3) * 8192, &tm_v, &sh->v_full[st], (lane - 3) * 64, h, row, pol);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_tiles > 0) {
+      constexpr uint32_t idesc_s = idesc_bf16(128, BKV2, 0);
+      constexpr uint32_t idesc_o = idesc_bf16(128, 128, 1);
+      const uint32_t lbo = p.mn_lbo_first ? 8192u : 1024u, sbo = p.mn_lbo_first ? 1024u : 8192u;
+      bool ok = mbar_wait(&sh->q_full, 0, abort_flag);
+      int k_seen = -1, v_seen = -1;
+      auto issue_s = [&](int g, int j) {
+        if (j >= n_g[g]) return true;
+        const int st = j & 1;
+        if (k_seen < j) {
+          if (!mbar_wait(&sh->k_full[st], (uint32_t)((j >> 1) & 1), abort_flag)) return false;
+          k_seen = j;
+        }
+        tc_fence_after();
+        const uint32_t qa = smem_u32(q_tile + g * MQ_BYTES), ka = smem_u32(k_tile + st * MK_BYTES);
+#pragma unroll
+        for (int cb = 0; cb < 3; ++cb)
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_bf16_ss(tmem + (uint32_t)(g * 128), umma_desc_k_sw128(qa + cb * 16384 + k * 32), umma_desc_k_sw128(ka + cb * 8192 + k * 32), idesc_s, (cb | k) ? 1u : 0u);
+        umma_commit(&sh->s_full[g]);
+        const bool last_user = (g == GROUPS - 1) || j >= n_g[GROUPS - 1];
+        if (last_user) umma_commit(&sh->k_empty[st]);
+        return true;
+      };
+      auto issue_pv = [&](int g, int j) {
+        if (j >= n_g[g]) return true;
+        const int st = j & 1;
+        if (!mbar_wait(&sh->p_ready[g], (uint32_t)(j & 1), abort_flag)) return false;
+        if (v_seen < j) {
+          if (!mbar_wait(&sh->v_full[st], (uint32_t)((j >> 1) & 1), abort_flag)) return false;
+          v_seen = j;
+        }
+        tc_fence_after();
+        const uint32_t va = smem_u32(v_tile + st * MV_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < BKV2 / 16; ++ks)
+          umma_bf16_ts(tmem + 256u + (uint32_t)(g * 128), tmem + (uint32_t)(g * 128) + (uint32_t)(ks * 8), umma_desc_mn_sw128(va + ks * 2048, lbo, sbo), idesc_o, (j | ks) ? 1u : 0u);
+        umma_commit(&sh->o_full[g]);
+        const bool last_user = (g == GROUPS - 1) || j >= n_g[GROUPS - 1];
+        if (last_user) umma_commit(&sh->v_empty[st]);
+        return true;
+      };
+      ok = ok && issue_s(0, 0) && issue_s(1, 0);
+      for (int j = 0; j < n_tiles && ok; ++j) ok = issue_pv(0, j) && issue_s(0, j + 1) && issue_pv(1, j) && issue_s(1, j + 1);
+    }
+  } else {
+    const int g = (warp - 2) >> 2, wq = warp & 3;
+    const int r = wq * 32 + lane;
+    const int my_n = n_g[g];
+    const int pos0 = pos_base + g * 128;
+    const int my_pos = pos0 + r;
+    const uint32_t s_row = tmem + ((uint32_t)(wq * 32) << 16) + (uint32_t)(g * 128);
+    const uint32_t o_row = s_row + 256u;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < my_n && ok; ++j) {
+      const bool need_mask = j * BKV2 + BKV2 - 1 > min(pos0, kv_len - 1);
+      const int limit = min(my_pos, kv_len - 1) - j * BKV2;
+      const uint32_t sp = (uint32_t)(j & 1), op = (uint32_t)((j - 1) & 1);
+      ok = need_mask ? softmax_tile64<true>(&sh->s_full[g], sp, s_row, o_row, 128, &sh->o_full[g], op, j, limit, p.scale_log2, m, l, &sh->p_ready[g], lane, abort_flag)
+                     : softmax_tile64<false>(&sh->s_full[g], sp, s_row, o_row, 128, &sh->o_full[g], op, j, limit, p.scale_log2, m, l, &sh->p_ready[g], lane, abort_flag);
+    }
+    const int rows_g = min(128, rows_here - g * 128);
+    if (ok && my_n > 0) {
+      ok = mbar_wait(&sh->o_full[g], (uint32_t)((my_n - 1) & 1), abort_flag);
+      tc_fence_after();
+    }
+    const float inv = (ok && l > 0.f) ? 1.f / l : 0.f;
+    bf16* dst = p.out + ((long long)(q0 + row_base + g * 128 + r) * p.heads + h) * 128;
+#pragma unroll 1
+    for (int c = 0; c < 128; c += 32) {
+      uint32_t w[32];
+      if (my_n > 0) {  // uniform per group
+        tmem_ld32(o_row + c, w);
+        tmem_ld_wait();
+      }
+      if (r < rows_g) {
+#pragma unroll
+        for (int c8 = 0; c8 < 32; c8 += 8) {
+          float f[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) f[i] = my_n > 0 ? __uint_as_float(w[c8 + i]) * inv : 0.f;
+          *reinterpret_cast<bf16x8*>(dst + c + c8) = pack8(f);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+  if (threadIdx.x == 0 && sh->abort_flag) atomicCAS(p.status, PG_ST_OK, PG_ST_TIMEOUT | (43u << 8));
+}
+
+// Latent rows of every key of the step's sequences, through the page table, as dense rows [sum of kv lengths, width].
+__global__ void __launch_bounds__(128) mla_gather_latent_kernel(const bf16* __restrict__ latent, int page_size, long long num_pages, int width, const int* __restrict__ table,
+                                                                int table_stride, const int* __restrict__ kv_indptr, int num_seqs, bf16* __restrict__ out, uint32_t* status) {
+  const int row = blockIdx.x;
+  int b = 0;
+  while (b + 1 < num_seqs && kv_indptr[b + 1] <= row) ++b;
+  const int pos = row - kv_indptr[b];
+  int page = table[(long long)b * table_stride + pos / page_size];
+  if (page < 0 || page >= num_pages) {
+    if (threadIdx.x == 0) atomicCAS(status, PG_ST_OK, PG_ST_BOUNDS | (44u << 8));
+    page = 0;
+  }
+  const uint4* src = reinterpret_cast<const uint4*>(latent + ((long long)page * page_size + pos % page_size) * width);
+  uint4* dst = reinterpret_cast<uint4*>(out + (long long)row * width);
+  for (int i = threadIdx.x; i < width / 8; i += blockDim.x) dst[i] = src[i];
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
@@ -795,6 +1050,20 @@ int make_tmap_rows_heads(CUtensorMap* out, const void* ptr, long long rows, int 
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  PG_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return PG_OK;
+}
+
+
+// generic tiled tensor map over bf16 with the 128-byte swizzle (inner box = 64 elements)
+int make_tmap_bf16(CUtensorMap* out, const void* ptr, int rank, const cuuint64_t* dims, const cuuint64_t* strides_bytes, const cuuint32_t* box) {
+  EncodeTiledFn enc = get_encode_attn();
+  PG_REQUIRE(enc != nullptr, "cuTensorMapEncodeTiled is not available from this driver");
+  PG_REQUIRE(((uintptr_t)ptr & 15) == 0, "TMA base address must be 16-byte aligned");
+  for (int i = 0; i + 1 < rank; ++i) PG_REQUIRE(strides_bytes[i] % 16 == 0, "TMA stride %d of %llu bytes is not a multiple of 16", i, (unsigned long long)strides_bytes[i]);
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(ptr), dims, strides_bytes, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   PG_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code %d", (int)r);
   return PG_OK;
 }
@@ -854,6 +1123,69 @@ extern "C" int pg_prefill_attention_tc(const void* q, const void* kv_layer, void
     attr_done = true;
   }
   PG_CUDA(launch_pdl(prefill_attn_tc_kernel, dim3((unsigned)q_tiles * (unsigned)hq), dim3(THREADS), smem, stream, tm_q, tm_kv, p));
+  PG_LAUNCH_CHECK();
+  return PG_OK;
+}
+
+// Dense latent rows of the step's keys: latent_layer [pages, page_size, width] -> out [total_kv, width].
+extern "C" int pg_mla_gather_latent(const void* latent_layer, int page_size, long long num_pages, int width, const void* table, int table_stride, const void* kv_indptr,
+                                    int num_seqs, int total_kv, void* out, void* status, cudaStream_t stream) {
+  PG_REQUIRE(width % 8 == 0, "latent width %d is not a multiple of 8", width);
+  if (total_kv == 0) return PG_OK;
+  PG_CUDA(launch_pdl(mla_gather_latent_kernel, dim3((unsigned)total_kv), dim3(128), 0, stream, (const bf16*)latent_layer, page_size, num_pages, width, (const int*)table,
+                     table_stride, (const int*)kv_indptr, num_seqs, (bf16*)out, (uint32_t*)status));
+  PG_LAUNCH_CHECK();
+  return PG_OK;
+}
+
+// Expanded-form MLA prefill on tcgen05.  q_nope_hm [heads, T, 128], q_pe [T, heads, 64], k_nope and v [total_kv, heads, 128],
+// k_pe = column `pe_col` of the dense latent rows [total_kv, pe_ld]; out [T, heads * 128].  `q_tiles` = sum over the
+// sequences of ceil(query rows / 256).
+extern "C" int pg_mla_prefill_tc(const void* q_nope_hm, const void* q_pe, const void* k_nope, const void* k_pe_rows, int pe_ld, int pe_col, const void* v, void* out,
+                                 const void* q_indptr, const void* kv_indptr, const void* kv_lens, int num_seqs, int tokens, int total_kv, int heads, int nope, int rope, int vdim,
+                                 float scale, int q_tiles, void* status, cudaStream_t stream) {
+  PG_REQUIRE(nope == 128 && rope == 64 && vdim == 128, "tcgen05 MLA prefill is built for 128 + 64 query / key and 128 value columns (got %d + %d, %d)", nope, rope, vdim);
+  if (q_tiles == 0 || tokens == 0 || total_kv == 0) return PG_OK;
+  CUtensorMap tm_qn, tm_qpe, tm_kn, tm_kpe, tm_v;
+  {
+    cuuint64_t dims[3] = {128, (cuuint64_t)tokens, (cuuint64_t)heads}, st[2] = {128 * 2, (cuuint64_t)tokens * 128 * 2};
+    cuuint32_t box[3] = {64, 128, 1};
+    int rc = make_tmap_bf16(&tm_qn, q_nope_hm, 3, dims, st, box);
+    if (rc != PG_OK) return rc;
+  }
+  {
+    cuuint64_t dims[3] = {64, (cuuint64_t)heads, (cuuint64_t)tokens}, st[2] = {64 * 2, (cuuint64_t)heads * 64 * 2};
+    cuuint32_t box[3] = {64, 1, 128};
+    int rc = make_tmap_bf16(&tm_qpe, q_pe, 3, dims, st, box);
+    if (rc != PG_OK) return rc;
+  }
+  int rc = make_tmap_rows_heads(&tm_kn, k_nope, total_kv, heads, BKV2, 128);
+  if (rc != PG_OK) return rc;
+  rc = make_tmap_rows_heads(&tm_v, v, total_kv, heads, BKV2, 128);
+  if (rc != PG_OK) return rc;
+  {
+    cuuint64_t dims[2] = {64, (cuuint64_t)total_kv}, st[1] = {(cuuint64_t)pe_ld * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)BKV2};
+    rc = make_tmap_bf16(&tm_kpe, (const bf16*)k_pe_rows + pe_col, 2, dims, st, box);
+    if (rc != PG_OK) return rc;
+  }
+  MlaTcParams p;
+  p.out = (bf16*)out;
+  p.q_indptr = (const int*)q_indptr;
+  p.kv_indptr = (const int*)kv_indptr;
+  p.kv_lens = (const int*)kv_lens;
+  p.num_seqs = num_seqs;
+  p.heads = heads;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.mn_lbo_first = g_mn_variant < 0 ? 1 : g_mn_variant;
+  p.status = (uint32_t*)status;
+  const size_t smem = 1024 + GROUPS * (size_t)MQ_BYTES + 2 * (size_t)MK_BYTES + 2 * (size_t)MV_BYTES + sizeof(TcSmem) + 64;
+  static bool attr_done = false;
+  if (!attr_done) {
+    PG_CUDA(cudaFuncSetAttribute(mla_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr_done = true;
+  }
+  PG_CUDA(launch_pdl(mla_prefill_tc_kernel, dim3((unsigned)q_tiles * (unsigned)heads), dim3(THREADS), smem, stream, tm_qn, tm_qpe, tm_kn, tm_kpe, tm_v, p));
   PG_LAUNCH_CHECK();
   return PG_OK;
 }

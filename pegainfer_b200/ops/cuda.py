@@ -930,6 +930,54 @@ def _head_offsets(heads: int, tokens: int, device):
     return o
 
 
+def _mla_expanded_ok(q: "_MlaQ", w_uk, w_uv, meta: AttnMeta, kv_lora) -> bool:
+    """A step of prefill chunks only (every sequence brings at least two rows), of the 128 + 64 / 128 head shape, long
+    enough for the tensor-core kernel to pay for expanding K and V."""
+    if meta.decode_only or not _PREFILL_TC or _BATCH_INVARIANT or meta.h_q_indptr is None or meta.h_kv_lens is None:
+        return False
+    if not (isinstance(w_uk, torch.Tensor) and isinstance(w_uv, torch.Tensor)) or w_uk.dtype != torch.bfloat16 or w_uv.dtype != torch.bfloat16:
+        return False
+    if q.nope != 128 or q.pe.shape[-1] != 64 or w_uv.shape[1] != 128:
+        return False
+    qi = meta.h_q_indptr
+    rows = [qi[b + 1] - qi[b] for b in range(meta.num_seqs)]
+    return min(rows) >= 2 and max(rows) >= _PREFILL_TC_MIN_ROWS and max(meta.h_kv_lens[: meta.num_seqs]) >= _PREFILL_TC_MIN_KV
+
+
+def _mla_prefill_expanded(q: "_MlaQ", w_uk, w_uv, latent_layer, meta: AttnMeta, scale, kv_lora):
+    """Prefill in the expanded form: the latent rows of every key of the step are gathered through the page table,
+    K (nope part) and V are expanded per head with the two up-projection GEMMs, and attention runs on the tcgen05
+    kernel with 128 + 64 query / key and 128 value columns per head (a quarter of the absorbed form's FLOPs).
+    Reference: pegainfer-kernels/csrc/k3/k3_flash_mla_prefill.cu (gather / expand + dense FMHA)."""
+    t, h = q.tokens, q.heads
+    dev = latent_layer.device
+    c = ctx(dev)
+    n = meta.num_seqs
+    kvl = [int(x) for x in meta.h_kv_lens[:n]]
+    kv_ind = [0]
+    for x in kvl:
+        kv_ind.append(kv_ind[-1] + x)
+    total = kv_ind[-1]
+    kv_indptr = torch.tensor(kv_ind, dtype=torch.int32).pin_memory().to(dev, non_blocking=True)
+    width = latent_layer.shape[-1]
+    page_size = latent_layer.shape[1]
+    dense = torch.empty((total, width), dtype=torch.bfloat16, device=dev)
+    _check(lib().pg_mla_gather_latent(_ptr(latent_layer), _ci(page_size), _ll(latent_layer.shape[0]), _ci(width), _ptr(meta.block_table), _ci(meta.block_table.stride(0)),
+                                      _ptr(kv_indptr), _ci(n), _ci(total), _ptr(dense), _ptr(c.status), _stream()), c)
+    nope, vdim = q.nope, w_uv.shape[1]
+    c_lat = dense[:, :kv_lora]
+    k_nope = linear(c_lat, w_uk.reshape(h * nope, kv_lora))   # [total, h * 128]
+    v = linear(c_lat, w_uv.reshape(h * vdim, kv_lora))         # [total, h * 128]
+    out = torch.empty((t, h * vdim), dtype=torch.bfloat16, device=dev)
+    qi = meta.h_q_indptr
+    q_tiles = sum((qi[b + 1] - qi[b] + 255) // 256 for b in range(n))
+    rc = lib().pg_mla_prefill_tc(_ptr(q.nope_hm), _ptr(q.pe), _ptr(k_nope), _ptr(dense), _ci(width), _ci(kv_lora), _ptr(v), _ptr(out), _ptr(meta.q_indptr), _ptr(kv_indptr),
+                                 _ptr(meta.kv_lens), _ci(n), _ci(t), _ci(total), _ci(h), _ci(nope), _ci(q.pe.shape[-1]), _ci(vdim), _cf(scale), _ci(q_tiles), _ptr(c.status),
+                                 _stream())
+    _check(rc, c)
+    return out
+
+
 def mla_attention(q: "_MlaQ", w_uk, w_uv, latent_layer, meta: AttnMeta, scale, kv_lora):
     """``w_uk`` [H, nope, kv_lora], ``w_uv`` [H, v, kv_lora].  The absorb GEMM wants W_UK as
     an [out = kv_lora, in = nope] weight per head; that transposed copy is made once per
@@ -943,6 +991,8 @@ def mla_attention(q: "_MlaQ", w_uk, w_uv, latent_layer, meta: AttnMeta, scale, k
     c = ctx(dev)
     if t == 0:
         return torch.empty((0, h * w_uv.shape[1]), dtype=torch.bfloat16, device=dev)
+    if _mla_expanded_ok(q, w_uk, w_uv, meta, kv_lora):
+        return _mla_prefill_expanded(q, w_uk, w_uv, latent_layer, meta, scale, kv_lora)
     offs = _head_offsets(h, t, dev)
     bn = _token_tile(h * t, h)
     q_abs = grouped_gemm(q.nope_hm.view(h * t, q.nope), offs, w_uk_t, None, bn)  # [H*T, kv_lora]

@@ -446,7 +446,10 @@ def test_moe_pipeline_fp8_block_scaled_experts(t, h, inter, e, k):
     torch.cuda.synchronize()
     status_clean()
     err = (got - ref).abs()
-    assert err.max().item() < 2e-2 * max(1.0, ref.abs().max().item()), (err.max().item(), ref.abs().max().item())
+    # the tensor-core path quantises the activations to e4m3 per token and 128-wide k group (3 mantissa bits); the
+    # reference keeps them in bf16: single elements may be off by a few percent of the largest value, the mean far less
+    assert err.max().item() < 4e-2 * max(1.0, ref.abs().max().item()), (err.max().item(), ref.abs().max().item())
+    assert err.mean().item() < 4e-3 * max(1.0, ref.abs().max().item()), err.mean().item()
     assert torch.equal(got, cu().moe_experts_fp8(x, ids, w, q13, s13, q2, s2, off))
     # one-hot rows read single weights back: the in-kernel dequantisation is exact
     m, kk = 256, 256
@@ -504,6 +507,29 @@ def test_mla_decode_and_prefill_match_reference(heads):
         status_clean()
         err = (got.float() - ref.float()).abs()
         assert err.max().item() < 3e-2 * max(1.0, ref.float().abs().max().item()), (q_lens, err.max().item(), ref.float().abs().max().item())
+
+
+@pytest.mark.parametrize("heads", [16, 64])
+def test_mla_prefill_expanded_tcgen05_matches_reference(heads):
+    """Prefill chunks (whole prompts, a chunk behind a cached prefix, ragged tails) through the expanded-form tcgen05
+    kernel: gather of the latent rows, K / V expansion, 192 / 128 attention."""
+    K = cu()
+    q_lens, kv_lens = [300, 257, 130, 70], [300, 700, 1000, 90]
+    meta, latent, q, w_uk, w_uv, cos, sin, c, nope = _mla_setup(q_lens, kv_lens, heads, seed=heads + 1)
+    scale = 0.1
+    q_ref = R.mla_rope_q(q, cos, sin, meta, nope)
+    ref = R.mla_attention(q_ref, w_uk, w_uv, latent, meta, scale, c)
+    q_cu = K.mla_rope_q(q, cos, sin, meta, nope)
+    prev = K.set_prefill_tc(0)
+    try:
+        assert K._mla_expanded_ok(q_cu, w_uk, w_uv, meta, c)
+        got = K.mla_attention(q_cu, w_uk, w_uv, latent, meta, scale, c)
+        torch.cuda.synchronize()
+    finally:
+        K.set_prefill_tc(prev)
+    status_clean()
+    err = (got.float() - ref.float()).abs()
+    assert err.max().item() < 3e-2 * max(1.0, ref.float().abs().max().item()), (err.max().item(), ref.float().abs().max().item())
 
 
 def test_mla_append_matches_reference():
