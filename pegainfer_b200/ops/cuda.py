@@ -516,6 +516,10 @@ _PREFILL_TC_MIN_ROWS = int(os.environ.get("PEGAINFER_PREFILL_TC_MIN_ROWS", "64")
 _PREFILL_TC_MIN_KV = int(os.environ.get("PEGAINFER_PREFILL_TC_MIN_KV", "512"))
 
 
+# how often each tcgen05 prefill kernel was chosen (tests assert that long prompts really take them)
+PREFILL_TC_CALLS = {"hd128": 0, "hd256": 0, "mla": 0}
+
+
 def set_prefill_tc(min_kv: int) -> int:
     """KV length from which prefill attention of head dim 128 takes the tcgen05 kernel; returns the previous value."""
     global _PREFILL_TC_MIN_KV
@@ -594,6 +598,7 @@ def paged_attention(q, kv_layer, meta: AttnMeta, scale=None, window=0, out: Opti
         # tcgen05 kernel: 256 (head dim 128) or 128 (head dim 256) query rows of one head per CTA, S and P V on the
         # tensor cores, accumulators in TMEM
         rows_per_cta = 256 if d == 128 else 128
+        PREFILL_TC_CALLS["hd128" if d == 128 else "hd256"] += 1
         q_tiles = sum((qi[b + 1] - qi[b] + rows_per_cta - 1) // rows_per_cta for b in range(n_pf))
         rc = lib().pg_prefill_attention_tc(_ptr(q), _ptr(kv_layer), _ptr(out), _ptr(meta.q_indptr), _ptr(meta.kv_lens), _ptr(table), _ci(table.stride(0)), _ci(n_pf), _ci(qi[n_pf]),
                                            _ci(hq), _ci(hkv), _ci(d), _ci(page_size), _ll(kv_layer.shape[0]), _cf(scale), _ci(q_tiles), _ptr(c.status), _stream())
@@ -949,6 +954,7 @@ def _mla_prefill_expanded(q: "_MlaQ", w_uk, w_uv, latent_layer, meta: AttnMeta, 
     K (nope part) and V are expanded per head with the two up-projection GEMMs, and attention runs on the tcgen05
     kernel with 128 + 64 query / key and 128 value columns per head (a quarter of the absorbed form's FLOPs).
     Reference: pegainfer-kernels/csrc/k3/k3_flash_mla_prefill.cu (gather / expand + dense FMHA)."""
+    PREFILL_TC_CALLS["mla"] += 1
     t, h = q.tokens, q.heads
     dev = latent_layer.device
     c = ctx(dev)

@@ -162,6 +162,18 @@ def test_glm_generate_graph_equals_eager_past_the_selection_width():
         e2.shutdown()
 
 
+def test_long_prompts_take_the_tcgen05_prefill_kernels():
+    """Prompts past the gate (512 keys) run the expanded-form MLA prefill (DeepSeek-V2 shape) and the head-dim-256
+    kernel (the hybrid model's full-attention layers); logits stay close to the PyTorch library path."""
+    from pegainfer_b200.ops import cuda as K
+
+    before = dict(K.PREFILL_TC_CALLS)
+    _family_logits_close("small-dsv2", lens=(700, 530))
+    assert K.PREFILL_TC_CALLS["mla"] > before["mla"]
+    _family_logits_close("small-qwen35", lens=(700, 530))
+    assert K.PREFILL_TC_CALLS["hd256"] > before["hd256"]
+
+
 def test_qwen35_hybrid_kernels_vs_library():
     _family_logits_close("small-qwen35")
 
