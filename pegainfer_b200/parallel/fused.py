@@ -33,17 +33,19 @@ _vp, _ll, _ci, _cf, _ull = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, cty
 
 
 class FusedTP(TPContext):
-    def __init__(self, rank: int, world: int, device, hidden: int, max_tokens: int, group=None, wait_s: float = 5.0, fused_max_rows: int = 256):
+    def __init__(self, rank: int, world: int, device, hidden: int, max_tokens: int, group=None, wait_s: float = 5.0, fused_max_rows: int = 256, site_max_world: int = 4):
         super().__init__(rank, world, group, comm="fused")
         # Steps with more token rows than this (prefill chunks) take the library all-reduce:
         # measured at 1024 rows on 2 GPUs the fused site is ~30 us slower than GEMM + NCCL +
         # norm, while up to a few hundred rows (decode) it is at parity or ahead.
         self.fused_max_rows = int(os.environ.get("PEGAINFER_TP_FUSED_MAX_ROWS", fused_max_rows))
-        # Measured on Qwen3-8B decode (64 rows): the fused site is within 1-2 % of GEMM + NCCL +
-        # norm on 2 and 4 GPUs, but 27 % behind on 8, where NCCL reduces inside the switch (NVLS)
-        # and the two-hop peer-store protocol pays the skew of eight ranks twice.  Above this
-        # world size every step takes the library all-reduce.
-        self.fused_max_world = int(os.environ.get("PEGAINFER_TP_FUSED_MAX_WORLD", "4"))
+        # This class is the PER-SITE fused kernel (GEMM + peer-store reduce-scatter + norm + all-gather), which the
+        # models that do not run on the decode-chain kernel use (the chain kernel carries its own cross-GPU reduction,
+        # peer pull or multimem, at every world size).  Measured at 64 rows the site kernel is within 1-2 % of GEMM +
+        # NCCL + norm on 2 and 4 GPUs but 27 % behind on 8, where NCCL reduces inside the switch and the two-hop
+        # peer-store protocol pays the skew of eight ranks twice: above `site_max_world` ranks a site takes the
+        # library all-reduce.
+        self.fused_max_world = int(site_max_world)
         import torch.distributed as dist
 
         self.device = torch.device(device)
@@ -165,5 +167,5 @@ class FusedTP(TPContext):
         K._check(rc, c)
 
 
-def make_fused_tp(rank: int, world: int, device, mcfg, max_tokens: int, group=None, wait_s: float = 5.0) -> FusedTP:
-    return FusedTP(rank, world, device, mcfg.hidden_size, max_tokens, group, wait_s)
+def make_fused_tp(rank: int, world: int, device, mcfg, max_tokens: int, group=None, wait_s: float = 5.0, site_max_world: int = 4) -> FusedTP:
+    return FusedTP(rank, world, device, mcfg.hidden_size, max_tokens, group, wait_s, site_max_world=site_max_world)

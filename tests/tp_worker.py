@@ -9,8 +9,6 @@ import torch.distributed as dist
 
 
 def main():
-    os.environ["PEGAINFER_TP_FUSED_MAX_WORLD"] = "8"  # exercise the fused kernels at every world size
-
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
@@ -26,7 +24,7 @@ def main():
 
     mcfg = preset("qwen3-0.6b", num_layers=3, vocab_size=4096)
     page, npages = 16, 64
-    tp_f = make_fused_tp(rank, world, dev, mcfg, max_tokens=512, wait_s=20.0)
+    tp_f = make_fused_tp(rank, world, dev, mcfg, max_tokens=512, wait_s=20.0, site_max_world=8)  # exercise the site kernels at every world size
     models = {
         "single": Qwen3Model(mcfg, device=dev, tp=SINGLE),
         "nccl": Qwen3Model(mcfg, device=dev, tp=TPContext(rank, world, comm="nccl")),
