@@ -1138,17 +1138,18 @@ extern "C" int pg_mla_gather_latent(const void* latent_layer, int page_size, lon
   return PG_OK;
 }
 
-// Expanded-form MLA prefill on tcgen05.  q_nope_hm [heads, T, 128], q_pe [T, heads, 64], k_nope and v [total_kv, heads, 128],
+// Expanded-form MLA prefill on tcgen05.  q_nope_hm [heads, T, 128] with `q_nope_head_stride` elements between heads (the rows may be
+// a prefix of a longer step), q_pe [T, heads, 64], k_nope and v [total_kv, heads, 128],
 // k_pe = column `pe_col` of the dense latent rows [total_kv, pe_ld]; out [T, heads * 128].  `q_tiles` = sum over the
 // sequences of ceil(query rows / 256).
-extern "C" int pg_mla_prefill_tc(const void* q_nope_hm, const void* q_pe, const void* k_nope, const void* k_pe_rows, int pe_ld, int pe_col, const void* v, void* out,
+extern "C" int pg_mla_prefill_tc(const void* q_nope_hm, long long q_nope_head_stride, const void* q_pe, const void* k_nope, const void* k_pe_rows, int pe_ld, int pe_col, const void* v, void* out,
                                  const void* q_indptr, const void* kv_indptr, const void* kv_lens, int num_seqs, int tokens, int total_kv, int heads, int nope, int rope, int vdim,
                                  float scale, int q_tiles, void* status, cudaStream_t stream) {
   PG_REQUIRE(nope == 128 && rope == 64 && vdim == 128, "tcgen05 MLA prefill is built for 128 + 64 query / key and 128 value columns (got %d + %d, %d)", nope, rope, vdim);
   if (q_tiles == 0 || tokens == 0 || total_kv == 0) return PG_OK;
   CUtensorMap tm_qn, tm_qpe, tm_kn, tm_kpe, tm_v;
   {
-    cuuint64_t dims[3] = {128, (cuuint64_t)tokens, (cuuint64_t)heads}, st[2] = {128 * 2, (cuuint64_t)tokens * 128 * 2};
+    cuuint64_t dims[3] = {128, (cuuint64_t)tokens, (cuuint64_t)heads}, st[2] = {128 * 2, (cuuint64_t)q_nope_head_stride * 2};
     cuuint32_t box[3] = {64, 128, 1};
     int rc = make_tmap_bf16(&tm_qn, q_nope_hm, 3, dims, st, box);
     if (rc != PG_OK) return rc;

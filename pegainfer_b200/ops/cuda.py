@@ -935,18 +935,52 @@ def _head_offsets(heads: int, tokens: int, device):
     return o
 
 
-def _mla_expanded_ok(q: "_MlaQ", w_uk, w_uv, meta: AttnMeta, kv_lora) -> bool:
-    """A step of prefill chunks only (every sequence brings at least two rows), of the 128 + 64 / 128 head shape, long
-    enough for the tensor-core kernel to pay for expanding K and V."""
+def _mla_expanded_seqs(q: "_MlaQ", w_uk, w_uv, meta: AttnMeta, kv_lora) -> int:
+    """How many leading sequences of the step take the expanded-form tcgen05 prefill: the prefill chunks (at least
+    two rows each) in front of the step's single-row decodes, when they have the 128 + 64 / 128 head shape and are
+    long enough for the tensor-core kernel to pay for expanding K and V; 0 when the step stays on the absorbed kernel."""
     if meta.decode_only or not _PREFILL_TC or _BATCH_INVARIANT or meta.h_q_indptr is None or meta.h_kv_lens is None:
-        return False
+        return 0
     if not (isinstance(w_uk, torch.Tensor) and isinstance(w_uv, torch.Tensor)) or w_uk.dtype != torch.bfloat16 or w_uv.dtype != torch.bfloat16:
-        return False
+        return 0
     if q.nope != 128 or q.pe.shape[-1] != 64 or w_uv.shape[1] != 128:
-        return False
+        return 0
     qi = meta.h_q_indptr
-    rows = [qi[b + 1] - qi[b] for b in range(meta.num_seqs)]
-    return min(rows) >= 2 and max(rows) >= _PREFILL_TC_MIN_ROWS and max(meta.h_kv_lens[: meta.num_seqs]) >= _PREFILL_TC_MIN_KV
+    n_pf = meta.num_seqs
+    while n_pf > 0 and qi[n_pf] - qi[n_pf - 1] == 1:
+        n_pf -= 1
+    if n_pf == 0:
+        return 0
+    rows = [qi[b + 1] - qi[b] for b in range(n_pf)]
+    if min(rows) < 2 or max(rows) < _PREFILL_TC_MIN_ROWS or max(meta.h_kv_lens[:n_pf]) < _PREFILL_TC_MIN_KV:
+        return 0
+    return n_pf
+
+
+def _mla_expanded_ok(q: "_MlaQ", w_uk, w_uv, meta: AttnMeta, kv_lora) -> bool:
+    return _mla_expanded_seqs(q, w_uk, w_uv, meta, kv_lora) > 0
+
+
+def _mla_split_step(q: "_MlaQ", w_uk, w_uv, latent_layer, meta: AttnMeta, scale, kv_lora, n_pf: int):
+    """A unified step: the leading prefill chunks through the expanded form, the single-row decodes behind them
+    through the absorbed kernel, each on its own slice of the step."""
+    from dataclasses import replace
+
+    qi, kvl = meta.h_q_indptr, meta.h_kv_lens
+    n, t, h = meta.num_seqs, q.tokens, q.heads
+    t_pf, n_dec = qi[n_pf], n - n_pf
+    vdim = w_uv.shape[1]
+    out = torch.empty((t, h * vdim), dtype=torch.bfloat16, device=latent_layer.device)
+    meta_pf = replace(meta, q_indptr=meta.q_indptr[: n_pf + 1], kv_lens=meta.kv_lens[:n_pf], block_table=meta.block_table[:n_pf], num_seqs=n_pf, num_tokens=t_pf,
+                      max_q_len=max(qi[b + 1] - qi[b] for b in range(n_pf)), max_kv_len=max(kvl[:n_pf]), decode_only=False, h_q_indptr=list(qi[: n_pf + 1]), h_kv_lens=list(kvl[:n_pf]),
+                      plan=None)
+    q_pf = _MlaQ(q.nope_hm[:, :t_pf], q.pe[:t_pf], t_pf, h, q.nope)
+    out[:t_pf] = _mla_prefill_expanded(q_pf, w_uk, w_uv, latent_layer, meta_pf, scale, kv_lora)
+    meta_dec = replace(meta, q_indptr=(meta.q_indptr[n_pf : n + 1] - t_pf).contiguous(), kv_lens=meta.kv_lens[n_pf:n], block_table=meta.block_table[n_pf:n], num_seqs=n_dec,
+                       num_tokens=n_dec, max_q_len=1, max_kv_len=max(kvl[n_pf:n]), decode_only=True, h_q_indptr=list(range(n_dec + 1)), h_kv_lens=list(kvl[n_pf:n]), plan=None)
+    q_dec = _MlaQ(q.nope_hm[:, t_pf:].contiguous(), q.pe[t_pf:], n_dec, h, q.nope)
+    out[t_pf:] = mla_attention(q_dec, w_uk, w_uv, latent_layer, meta_dec, scale, kv_lora)
+    return out
 
 
 def _mla_prefill_expanded(q: "_MlaQ", w_uk, w_uv, latent_layer, meta: AttnMeta, scale, kv_lora):
@@ -977,7 +1011,8 @@ def _mla_prefill_expanded(q: "_MlaQ", w_uk, w_uv, latent_layer, meta: AttnMeta, 
     out = torch.empty((t, h * vdim), dtype=torch.bfloat16, device=dev)
     qi = meta.h_q_indptr
     q_tiles = sum((qi[b + 1] - qi[b] + 255) // 256 for b in range(n))
-    rc = lib().pg_mla_prefill_tc(_ptr(q.nope_hm), _ptr(q.pe), _ptr(k_nope), _ptr(dense), _ci(width), _ci(kv_lora), _ptr(v), _ptr(out), _ptr(meta.q_indptr), _ptr(kv_indptr),
+    assert q.nope_hm.stride(2) == 1 and q.nope_hm.stride(1) == nope and q.pe.is_contiguous()
+    rc = lib().pg_mla_prefill_tc(_ptr(q.nope_hm), _ll(q.nope_hm.stride(0)), _ptr(q.pe), _ptr(k_nope), _ptr(dense), _ci(width), _ci(kv_lora), _ptr(v), _ptr(out), _ptr(meta.q_indptr), _ptr(kv_indptr),
                                  _ptr(meta.kv_lens), _ci(n), _ci(t), _ci(total), _ci(h), _ci(nope), _ci(q.pe.shape[-1]), _ci(vdim), _cf(scale), _ci(q_tiles), _ptr(c.status),
                                  _stream())
     _check(rc, c)
@@ -997,8 +1032,11 @@ def mla_attention(q: "_MlaQ", w_uk, w_uv, latent_layer, meta: AttnMeta, scale, k
     c = ctx(dev)
     if t == 0:
         return torch.empty((0, h * w_uv.shape[1]), dtype=torch.bfloat16, device=dev)
-    if _mla_expanded_ok(q, w_uk, w_uv, meta, kv_lora):
+    n_pf = _mla_expanded_seqs(q, w_uk, w_uv, meta, kv_lora)
+    if n_pf == meta.num_seqs:
         return _mla_prefill_expanded(q, w_uk, w_uv, latent_layer, meta, scale, kv_lora)
+    if n_pf > 0:
+        return _mla_split_step(q, w_uk, w_uv, latent_layer, meta, scale, kv_lora, n_pf)
     offs = _head_offsets(h, t, dev)
     bn = _token_tile(h * t, h)
     q_abs = grouped_gemm(q.nope_hm.view(h * t, q.nope), offs, w_uk_t, None, bn)  # [H*T, kv_lora]

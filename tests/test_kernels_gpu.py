@@ -514,22 +514,23 @@ def test_mla_prefill_expanded_tcgen05_matches_reference(heads):
     """Prefill chunks (whole prompts, a chunk behind a cached prefix, ragged tails) through the expanded-form tcgen05
     kernel: gather of the latent rows, K / V expansion, 192 / 128 attention."""
     K = cu()
-    q_lens, kv_lens = [300, 257, 130, 70], [300, 700, 1000, 90]
-    meta, latent, q, w_uk, w_uv, cos, sin, c, nope = _mla_setup(q_lens, kv_lens, heads, seed=heads + 1)
-    scale = 0.1
-    q_ref = R.mla_rope_q(q, cos, sin, meta, nope)
-    ref = R.mla_attention(q_ref, w_uk, w_uv, latent, meta, scale, c)
-    q_cu = K.mla_rope_q(q, cos, sin, meta, nope)
-    prev = K.set_prefill_tc(0)
-    try:
-        assert K._mla_expanded_ok(q_cu, w_uk, w_uv, meta, c)
-        got = K.mla_attention(q_cu, w_uk, w_uv, latent, meta, scale, c)
-        torch.cuda.synchronize()
-    finally:
-        K.set_prefill_tc(prev)
-    status_clean()
-    err = (got.float() - ref.float()).abs()
-    assert err.max().item() < 3e-2 * max(1.0, ref.float().abs().max().item()), (err.max().item(), ref.float().abs().max().item())
+    # prefill chunks only, then a unified step: chunks in front (expanded form), single-row decodes behind (absorbed kernel)
+    for q_lens, kv_lens, n_expanded in (([300, 257, 130, 70], [300, 700, 1000, 90], 4), ([300, 257, 1, 1, 1], [300, 700, 90, 1000, 33], 2)):
+        meta, latent, q, w_uk, w_uv, cos, sin, c, nope = _mla_setup(q_lens, kv_lens, heads, seed=heads + 1)
+        scale = 0.1
+        q_ref = R.mla_rope_q(q, cos, sin, meta, nope)
+        ref = R.mla_attention(q_ref, w_uk, w_uv, latent, meta, scale, c)
+        q_cu = K.mla_rope_q(q, cos, sin, meta, nope)
+        prev = K.set_prefill_tc(0)
+        try:
+            assert K._mla_expanded_seqs(q_cu, w_uk, w_uv, meta, c) == n_expanded
+            got = K.mla_attention(q_cu, w_uk, w_uv, latent, meta, scale, c)
+            torch.cuda.synchronize()
+        finally:
+            K.set_prefill_tc(prev)
+        status_clean()
+        err = (got.float() - ref.float()).abs()
+        assert err.max().item() < 3e-2 * max(1.0, ref.float().abs().max().item()), (q_lens, err.max().item(), ref.float().abs().max().item())
 
 
 def test_mla_append_matches_reference():
