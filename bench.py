@@ -47,6 +47,7 @@ def parse():
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (marks the result invalid)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--prefill-chunk", type=int, default=4096, help="token budget of one prefill step (max_prefill_tokens)")
     ap.add_argument("--profile-host", default=None, help="write a cProfile of the scheduler thread during the e2e phase to this path")
     ap.add_argument("--no-library-arm", action="store_true", help="skip the cuBLAS + NCCL arm that is timed after the main arm and reported as `library_arm`")
     return ap.parse_args()
@@ -238,8 +239,8 @@ def kernel_only(args, eng, rank, world, device):
     g = torch.Generator().manual_seed(1234)
     prompts = torch.randint(0, eng.model.cfg.vocab_size, (n, plen), generator=g)
     pages = [pool.allocate(need_pages) for _ in range(n)]
-    # prefill through the executor (chunks of up to 4096 tokens per forward)
-    per = max(1, 4096 // plen)
+    # prefill through the executor (chunks of up to --prefill-chunk tokens per forward)
+    per = max(1, args.prefill_chunk // plen)
     first_tokens = [0] * n
     t0 = time.perf_counter()
     for i in range(0, n, per):
@@ -419,7 +420,7 @@ def run_arm(args, impl, comm, rank, local, world, device, with_e2e):
     ramp = (args.conc + max(1, 4096 // args.prompt_len) - 1) // max(1, 4096 // args.prompt_len)
     total_len = args.prompt_len + args.warmup + args.steps + ramp + 2 * page
     blocks = 2 * args.conc * ((total_len + page - 1) // page + 2) + 8
-    ecfg = EngineConfig(preset=args.model, num_kv_blocks=blocks, kv_page_size=page, cuda_graph=True, precapture_graphs=True, max_decode_batch=max(args.conc, 8), max_model_len=total_len + page, max_prefill_tokens=4096, no_prefix_cache=True, tune_gc=True)
+    ecfg = EngineConfig(preset=args.model, num_kv_blocks=blocks, kv_page_size=page, cuda_graph=True, precapture_graphs=True, max_decode_batch=max(args.conc, 8), max_model_len=total_len + page, max_prefill_tokens=args.prefill_chunk, no_prefix_cache=True, tune_gc=True)
     eng = None
     try:
         eng = build_engine(ecfg, mcfg, device=device, dtype=torch.bfloat16, tp=tp, start=False)

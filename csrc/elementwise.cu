@@ -279,6 +279,103 @@ __global__ void __launch_bounds__(128) qk_norm_rope_append_kernel(const RopePara
   }
 }
 
+// Same operation for head dims whose 32 lanes each hold VEC = D / 32 contiguous elements (one 4-, 8- or 16-byte access
+// per lane and row, no shared memory): the rotation partner of a lane is lane ^ (rot / 2 / VEC), which needs
+// rot / 2 to be a multiple of VEC and rot / 2 / VEC a power of two (full rotary of 64 / 128 / 256, a quarter of 256).
+// A warp takes ROPE_G consecutive heads of one token: their rows are loaded together (independent loads in flight), and the
+// token's slot, position and cos / sin row are read once for all of them.
+constexpr int ROPE_G = 8;
+template <int VEC>
+__global__ void __launch_bounds__(128) qk_norm_rope_append_vec_kernel(const RopeParams p) {
+  PG_PDL_ENTRY();
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = p.hq + 2 * p.hkv;
+  const int groups = (heads + ROPE_G - 1) / ROPE_G;
+  const long long unit = (long long)blockIdx.x * 4 + w;
+  if (unit >= (long long)p.tokens * groups) return;
+  const int t = (int)(unit / groups), h0 = (int)(unit % groups) * ROPE_G;
+  constexpr int D = VEC * 32;
+  const int qstride = p.gated ? 2 * D : D;
+  struct alignas(VEC * 2) Pack {
+    bf16 v[VEC];
+  };
+  const bf16* row = p.qkv + t * p.ld;
+  auto src_of = [&](int h) { return h < p.hq ? row + (long long)h * qstride : row + (long long)p.hq * qstride + (long long)(h - p.hq) * D; };
+  Pack in[ROPE_G];
+#pragma unroll
+  for (int g = 0; g < ROPE_G; ++g)
+    if (h0 + g < heads) in[g] = *reinterpret_cast<const Pack*>(src_of(h0 + g) + lane * VEC);
+  long long slot = p.slots[t];
+  const bool slot_ok = slot >= 0 && slot < p.num_slots;
+  if (!slot_ok && h0 + ROPE_G > p.hq && lane == 0) atomicCAS(p.status, PG_ST_OK, PG_ST_BOUNDS | (3u << 8));
+  const long long page = slot / p.page_size, off = slot % p.page_size;
+  int pos = p.positions[t];
+  if (pos < 0 || pos >= p.max_pos) {
+    if (lane == 0 && h0 < p.hq + p.hkv) atomicCAS(p.status, PG_ST_OK, PG_ST_BOUNDS | (4u << 8));
+    pos = pos < 0 ? 0 : p.max_pos - 1;
+  }
+  const int half = p.rot / 2, half_lanes = half / VEC;
+  const bool rotated = lane < 2 * half_lanes;
+  const bool low = lane < half_lanes;
+  const int e0 = (low ? lane : lane - half_lanes) * VEC;  // index into the cos / sin row (valid when rotated)
+  float cs[VEC], sn[VEC];
+  if (rotated) {
+    const Pack c = *reinterpret_cast<const Pack*>(p.cos + (long long)pos * half + e0);
+    const Pack s2 = *reinterpret_cast<const Pack*>(p.sin + (long long)pos * half + e0);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      cs[i] = __bfloat162float(c.v[i]);
+      sn[i] = low ? -__bfloat162float(s2.v[i]) : __bfloat162float(s2.v[i]);
+    }
+  }
+  float qw[VEC], kw[VEC];
+  if (p.has_norm) {
+    const Pack a = *reinterpret_cast<const Pack*>(p.q_w + lane * VEC), b2 = *reinterpret_cast<const Pack*>(p.k_w + lane * VEC);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      qw[i] = __bfloat162float(a.v[i]) + (p.offset ? 1.f : 0.f);
+      kw[i] = __bfloat162float(b2.v[i]) + (p.offset ? 1.f : 0.f);
+    }
+  }
+#pragma unroll
+  for (int g = 0; g < ROPE_G; ++g) {
+    const int h = h0 + g;
+    if (h >= heads) break;
+    const int kind = h < p.hq ? 0 : h < p.hq + p.hkv ? 1 : 2;
+    if (kind != 0 && !slot_ok) continue;
+    if (kind == 2) {
+      bf16* dst = p.kv + (((page * 2 + 1) * p.page_size + off) * p.hkv + (h - p.hq - p.hkv)) * D;
+      *reinterpret_cast<Pack*>(dst + lane * VEC) = in[g];
+      continue;
+    }
+    float x[VEC];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      x[i] = __bfloat162float(in[g].v[i]);
+      ss += x[i] * x[i];
+    }
+    if (p.has_norm) {
+      ss = warp_sum(ss);
+      const float inv = rsqrtf(ss / (float)D + p.eps);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) x[i] = bf16_round(x[i] * inv * (kind == 0 ? qw[i] : kw[i]));
+    }
+    Pack out;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      const float partner = __shfl_xor_sync(0xFFFFFFFFu, x[i], half_lanes);
+      out.v[i] = __float2bfloat16(rotated ? x[i] * cs[i] + partner * sn[i] : x[i]);
+    }
+    bf16* dst = kind == 0 ? p.q_out + ((long long)t * p.hq + h) * D : p.kv + (((page * 2 + 0) * p.page_size + off) * p.hkv + (h - p.hq)) * D;
+    *reinterpret_cast<Pack*>(dst + lane * VEC) = out;
+    if (kind == 0 && p.gated) {
+      bf16* gdst = p.gate_out + ((long long)t * p.hq + h) * D;
+      *reinterpret_cast<Pack*>(gdst + lane * VEC) = *reinterpret_cast<const Pack*>(src_of(h) + D + lane * VEC);
+    }
+  }
+}
+
 }  // namespace
 
 extern "C" int pg_gather_rows(const void* table, const void* ids, void* out, int rows, int width, long long table_rows, void* status,
@@ -368,6 +465,17 @@ extern "C" int pg_qk_norm_rope_append(const void* qkv, long long ld, const void*
   p.eps = eps;
   p.status = (uint32_t*)status;
   long long units = (long long)tokens * (hq + 2 * hkv);
+  const int vec = dim / 32, half_lanes = (dim == 64 || dim == 128 || dim == 256) && rot >= 2 * vec && (rot / 2) % vec == 0 ? rot / 2 / vec : 0;
+  const bool vec_ok = half_lanes > 0 && (half_lanes & (half_lanes - 1)) == 0 && ld % 8 == 0 && ((uintptr_t)qkv & 15) == 0;
+  if (vec_ok) {
+    const long long vunits = (long long)tokens * ((hq + 2 * hkv + ROPE_G - 1) / ROPE_G);
+    const dim3 grid((unsigned)((vunits + 3) / 4));
+    if (dim == 64) PG_CUDA(launch_pdl(qk_norm_rope_append_vec_kernel<2>, grid, dim3(128), (size_t)(0), stream, p));
+    else if (dim == 128) PG_CUDA(launch_pdl(qk_norm_rope_append_vec_kernel<4>, grid, dim3(128), (size_t)(0), stream, p));
+    else PG_CUDA(launch_pdl(qk_norm_rope_append_vec_kernel<8>, grid, dim3(128), (size_t)(0), stream, p));
+    PG_LAUNCH_CHECK();
+    return PG_OK;
+  }
   PG_CUDA(launch_pdl(qk_norm_rope_append_kernel, dim3((unsigned)((units + 3) / 4)), dim3(128), (size_t)(0), stream, p));
   PG_LAUNCH_CHECK();
   return PG_OK;

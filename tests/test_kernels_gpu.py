@@ -212,7 +212,7 @@ def test_unified_step_attention_splits_chunks_and_decode_rows(d, hq, hkv, page):
     status_clean()
 
 
-@pytest.mark.parametrize("d,rot,gated,offset", [(128, 128, False, False), (64, 64, False, False), (256, 64, True, True)])
+@pytest.mark.parametrize("d,rot,gated,offset", [(128, 128, False, False), (64, 64, False, False), (256, 64, True, True), (256, 256, False, False), (128, 32, False, True), (96, 48, False, False)])
 def test_qk_norm_rope_append(d, rot, gated, offset):
     torch.manual_seed(rot)
     hq, hkv, page = 8, 2, 16
