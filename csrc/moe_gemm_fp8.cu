@@ -35,6 +35,12 @@ struct MoeFp8Params {
   const int* offsets;  // [E + 1]
   int M, E, kgroups, m_tiles, stages, kg_cap;
   uint32_t* status;
+  // expert-parallel return path (as in the bf16 grouped kernel): output row r goes to rank (scatter_src[r] / cap), slot
+  // (scatter_src[r] % cap) of that rank's combine buffer (row stride ldy); the tail raises the "returned" epoch
+  const int* scatter_src;
+  bf16* peer_out[8];
+  uint32_t* peer_flags[8];
+  int cap, rank, world, site;
 };
 
 __host__ __device__ constexpr uint32_t idesc_e4m3(uint32_t m, uint32_t n) { return (1u << 4) | ((n >> 3) << 17) | ((m >> 4) << 24); }
@@ -111,6 +117,8 @@ __global__ void __launch_bounds__(192) moe_gemm_fp8_kernel(const __grid_constant
     tmem_relinquish();
   }
   PG_PDL_ENTRY();
+  uint32_t ep_epoch = 0;
+  if (p.scatter_src != nullptr) ep_epoch = *((volatile uint32_t*)(p.peer_flags[p.rank] + p.site * 32 + 16));
   for (int e = threadIdx.x; e < p.E; e += blockDim.x) s_tiles[e] = p.m_tiles * ((p.offsets[e + 1] - p.offsets[e] + BN - 1) / BN);
   tc_fence_before();
   __syncthreads();
@@ -235,9 +243,20 @@ __global__ void __launch_bounds__(192) moe_gemm_fp8_kernel(const __grid_constant
       if (!ok) break;
       const int m = it.m_tile * BM + r;
       if (m < p.M) {
+        if (p.scatter_src == nullptr) {
 #pragma unroll
-        for (int j = 0; j < BN; ++j)
-          if (j < it.rows) p.y[(long long)(it.row0 + j) * p.ldy + m] = __float2bfloat16(acc[j]);
+          for (int j = 0; j < BN; ++j)
+            if (j < it.rows) p.y[(long long)(it.row0 + j) * p.ldy + m] = __float2bfloat16(acc[j]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < BN; ++j) {
+            if (j < it.rows) {
+              const int idx = p.scatter_src[it.row0 + j];
+              const int dst_rank = idx / p.cap, slot = idx - dst_rank * p.cap;
+              p.peer_out[dst_rank][(size_t)slot * p.ldy + m] = __float2bfloat16(acc[j]);
+            }
+          }
+        }
       }
     }
   }
@@ -249,6 +268,17 @@ __global__ void __launch_bounds__(192) moe_gemm_fp8_kernel(const __grid_constant
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
   if (threadIdx.x == 0 && *abort_flag) atomicCAS(p.status, PG_ST_OK, PG_ST_TIMEOUT | (32u << 8));
+  if (p.scatter_src != nullptr && threadIdx.x == 0) {
+    // every output row of this CTA is on its way to its source rank (the barrier above orders the other threads'
+    // stores before this fence): the last CTA of this GPU raises the "returned" epoch on all ranks
+    uint32_t* myflags = p.peer_flags[p.rank] + p.site * 32;
+    __threadfence_system();
+    const uint32_t old = atomicAdd(&myflags[17], 1u);
+    if (old == gridDim.x - 1) {
+      myflags[17] = 0u;
+      for (int q = 0; q < p.world; ++q) st_release_sys(p.peer_flags[q] + p.site * 32 + 8 + p.rank, ep_epoch + 1u);
+    }
+  }
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
@@ -283,12 +313,14 @@ int launch(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const MoeFp8Params&
 
 // xq [rows, K] e4m3 (row stride K), x_scale [K / 128, ldxs] f32, wq [E, M, K] e4m3, w_scale [E, M / 128, K / 128] f32,
 // y [rows, M] bf16, offsets [E + 1] int32 (device).  `bn`: token tile, 16, 32 or 64.
-extern "C" int pg_moe_grouped_gemm_fp8(const void* xq, long long rows, const void* x_scale, long long ldxs, const void* wq, const void* w_scale, void* y, long long ldy,
-                                       const void* offsets, int E, int M, int K, int bn, void* status, cudaStream_t stream) {
+static int moe_fp8_impl(const void* xq, long long rows, const void* x_scale, long long ldxs, const void* wq, const void* w_scale, void* y, long long ldy, const void* offsets,
+                        int E, int M, int K, int bn, void* status, const void* scatter_src, void* const* peer_out, void* const* peer_flags, int cap, int rank, int world,
+                        int site, cudaStream_t stream) {
   PG_REQUIRE(K % 128 == 0 && M % 128 == 0, "fp8 grouped gemm: K %d and M %d must be multiples of the 128 x 128 scale block", K, M);
   PG_REQUIRE(E >= 1 && E <= MAX_EXPERTS, "fp8 grouped gemm: %d experts (at most %d)", E, MAX_EXPERTS);
   PG_REQUIRE(bn == 16 || bn == 32 || bn == 64, "fp8 grouped gemm: token tile %d", bn);
-  if (rows == 0) return PG_OK;
+  if (rows == 0 && scatter_src == nullptr) return PG_OK;
+  PG_REQUIRE(rows > 0, "fp8 grouped gemm: the return path needs a non-empty row buffer");
   EncodeTiledFn enc = get_encode();
   PG_REQUIRE(enc != nullptr, "cuTensorMapEncodeTiled is not available from this driver");
   PG_REQUIRE((((uintptr_t)xq | (uintptr_t)wq) & 15) == 0, "TMA base addresses must be 16-byte aligned");
@@ -325,10 +357,36 @@ extern "C" int pg_moe_grouped_gemm_fp8(const void* xq, long long rows, const voi
   p.kg_cap = (p.kgroups + 4) & ~3;
   p.stages = 4;
   p.status = (uint32_t*)status;
+  p.scatter_src = (const int*)scatter_src;
+  p.cap = p.rank = p.world = p.site = 0;
+  if (scatter_src) {
+    for (int q = 0; q < world; ++q) {
+      p.peer_out[q] = (bf16*)peer_out[q];
+      p.peer_flags[q] = (uint32_t*)peer_flags[q];
+    }
+    p.cap = cap;
+    p.rank = rank;
+    p.world = world;
+    p.site = site;
+  }
   int dev = 0, sms = 148;
   PG_CUDA(cudaGetDevice(&dev));
   PG_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   if (bn == 16) return launch<16>(tm_w, tm_x, p, sms, stream);
   if (bn == 32) return launch<32>(tm_w, tm_x, p, sms, stream);
   return launch<64>(tm_w, tm_x, p, sms, stream);
+}
+
+extern "C" int pg_moe_grouped_gemm_fp8(const void* xq, long long rows, const void* x_scale, long long ldxs, const void* wq, const void* w_scale, void* y, long long ldy,
+                                       const void* offsets, int E, int M, int K, int bn, void* status, cudaStream_t stream) {
+  return moe_fp8_impl(xq, rows, x_scale, ldxs, wq, w_scale, y, ldy, offsets, E, M, K, bn, status, nullptr, nullptr, nullptr, 0, 0, 1, 0, stream);
+}
+
+// Expert-parallel W2 on the FP8 tensor-core path: output rows are stored straight into their source ranks' combine
+// buffers (row stride ldy) and the kernel's tail raises this rank's "returned" epoch.
+extern "C" int pg_moe_grouped_gemm_fp8_return(const void* xq, long long rows, const void* x_scale, long long ldxs, const void* wq, const void* w_scale, long long ldy,
+                                              const void* offsets, int E, int M, int K, int bn, void* status, const void* scatter_src, void* const* peer_out,
+                                              void* const* peer_flags, int cap, int rank, int world, int site, cudaStream_t stream) {
+  PG_REQUIRE(scatter_src != nullptr && world >= 1 && world <= 8, "fp8 grouped gemm return: needs the sorted-source table and 1..8 ranks");
+  return moe_fp8_impl(xq, rows, x_scale, ldxs, wq, w_scale, nullptr, ldy, offsets, E, M, K, bn, status, scatter_src, peer_out, peer_flags, cap, rank, world, site, stream);
 }

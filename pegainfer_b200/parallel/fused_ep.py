@@ -119,9 +119,17 @@ class FusedEP(EPContext):
         act = K.swiglu(y1)
         m = w2.shape[1]
         kk = act.shape[1]
-        rc = self.lib.pg_moe_grouped_gemm_return(_vp(act.data_ptr()), _ll(act.stride(0)), _ll(max_rows), _vp(w2.data_ptr()), _vp(s2.data_ptr()) if s2 is not None else _vp(0),
-                                                 _ci(mode), _ll(h), _vp(offsets.data_ptr()), _ci(e_local), _ci(m), _ci(kk), _ci(bn), _vp(c.status.data_ptr()),
-                                                 _vp(sorted_src.data_ptr()), self.comb_table, self.flag_table, _ci(self.cap), _ci(self.rank), _ci(self.world), _ci(site), st)
+        if mode == 2 and K._MOE_FP8_TC and kk % 128 == 0 and m % 128 == 0:
+            bn8 = 16 if bn <= 16 else 32 if bn <= 32 else 64
+            # W2 on the FP8 tensor-core path as well, with the same scatter-return epilogue
+            aq, asc = K.quant_fp8_1x128(act)
+            rc = self.lib.pg_moe_grouped_gemm_fp8_return(_vp(aq.data_ptr()), _ll(max_rows), _vp(asc.data_ptr()), _ll(asc.stride(0)), _vp(w2.data_ptr()), _vp(s2.data_ptr()), _ll(h),
+                                                         _vp(offsets.data_ptr()), _ci(e_local), _ci(m), _ci(kk), _ci(bn8), _vp(c.status.data_ptr()), _vp(sorted_src.data_ptr()),
+                                                         self.comb_table, self.flag_table, _ci(self.cap), _ci(self.rank), _ci(self.world), _ci(site), st)
+        else:
+            rc = self.lib.pg_moe_grouped_gemm_return(_vp(act.data_ptr()), _ll(act.stride(0)), _ll(max_rows), _vp(w2.data_ptr()), _vp(s2.data_ptr()) if s2 is not None else _vp(0),
+                                                     _ci(mode), _ll(h), _vp(offsets.data_ptr()), _ci(e_local), _ci(m), _ci(kk), _ci(bn), _vp(c.status.data_ptr()),
+                                                     _vp(sorted_src.data_ptr()), self.comb_table, self.flag_table, _ci(self.cap), _ci(self.rank), _ci(self.world), _ci(site), st)
         K._check(rc, c)
         out = torch.empty((t, h), dtype=torch.float32, device=dev)
         wts = wts.contiguous()
