@@ -235,6 +235,34 @@ __global__ void __launch_bounds__(128) quant_fp8_1x128_kernel(const bf16* __rest
   if (lane == 0) scale[(long long)g * lds + t] = s;
 }
 
+// SwiGLU and the quantiser in one pass: gu [T, 2 K] bf16 (gate half first) -> e4m3 of round_bf16(round_bf16(silu(gate)) * up)
+// with the same per-token, per-k-group scales; bit-identical to the swiglu kernel followed by the quantiser.
+__global__ void __launch_bounds__(128) swiglu_quant_fp8_1x128_kernel(const bf16* __restrict__ gu, long long ldx, int T, int kgroups, uint8_t* __restrict__ xq, long long ldq,
+                                                                      float* __restrict__ scale, long long lds) {
+  PG_PDL_ENTRY();
+  const long long u = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (u >= (long long)T * kgroups) return;
+  const int t = (int)(u / kgroups), g = (int)(u % kgroups), lane = threadIdx.x & 31;
+  const bf16* src = gu + (long long)t * ldx + g * 128 + lane * 4;
+  const uint2 rg = *reinterpret_cast<const uint2*>(src), ru = *reinterpret_cast<const uint2*>(src + (long long)kgroups * 128);
+  const bf16* pg = reinterpret_cast<const bf16*>(&rg);
+  const bf16* pu = reinterpret_cast<const bf16*>(&ru);
+  float v[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float gf = __bfloat162float(pg[i]);
+    const float sg = __bfloat162float(__float2bfloat16(gf / (1.f + __expf(-gf))));
+    v[i] = __bfloat162float(__float2bfloat16(sg * __bfloat162float(pu[i])));
+  }
+  const float amax = fmaxf(warp_max(fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])))), 1e-10f);
+  const float s = amax / 448.f, inv = 448.f / amax;
+  uint32_t out = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) out |= (uint32_t)__nv_cvt_float_to_fp8(v[i] * inv, __NV_SATFINITE, __NV_E4M3) << (8 * i);
+  *reinterpret_cast<uint32_t*>(xq + (long long)t * ldq + g * 128 + lane * 4) = out;
+  if (lane == 0) scale[(long long)g * lds + t] = s;
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
@@ -337,6 +365,17 @@ extern "C" int pg_quant_fp8_1x128(const void* x, long long ldx, int T, int K, vo
   const long long units = (long long)T * (K / 128);
   if (units == 0) return PG_OK;
   PG_CUDA(launch_pdl(quant_fp8_1x128_kernel, dim3((unsigned)((units + 3) / 4)), dim3(128), (size_t)0, stream, (const bf16*)x, ldx, T, K / 128, (uint8_t*)xq, ldq,
+                     (float*)scale, lds));
+  PG_LAUNCH_CHECK();
+  return PG_OK;
+}
+
+// gu [T, 2 K] bf16 (gate half first) -> xq [T, K] e4m3 of SwiGLU(gu) + scale [K / 128, lds] f32.
+extern "C" int pg_swiglu_quant_fp8_1x128(const void* gu, long long ldx, int T, int K, void* xq, long long ldq, void* scale, long long lds, cudaStream_t stream) {
+  PG_REQUIRE(K % 128 == 0 && ldx % 4 == 0 && ldq % 4 == 0, "fp8 swiglu quant: K %d must be a multiple of 128", K);
+  const long long units = (long long)T * (K / 128);
+  if (units == 0) return PG_OK;
+  PG_CUDA(launch_pdl(swiglu_quant_fp8_1x128_kernel, dim3((unsigned)((units + 3) / 4)), dim3(128), (size_t)0, stream, (const bf16*)gu, ldx, T, K / 128, (uint8_t*)xq, ldq,
                      (float*)scale, lds));
   PG_LAUNCH_CHECK();
   return PG_OK;

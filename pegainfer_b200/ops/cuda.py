@@ -862,8 +862,7 @@ def _moe_pipeline(x, ids, weights, w13, s13, w2, s2, expert_offset):
     if quant_code(w13) == 2 and _MOE_FP8_TC and h % 128 == 0 and w13.shape[1] % 256 == 0 and w2.shape[1] % 128 == 0:
         # both GEMMs on the FP8 tensor-core path: activations quantised per row and 128-wide k group
         xq, xsc = quant_fp8_1x128(xs)
-        act = swiglu(grouped_gemm_fp8(xq, xsc, offsets, w13, s13, bn))
-        aq, asc = quant_fp8_1x128(act)
+        aq, asc = swiglu_quant_fp8_1x128(grouped_gemm_fp8(xq, xsc, offsets, w13, s13, bn))
         y2 = grouped_gemm_fp8(aq, asc, offsets, w2, s2, bn)
     else:
         y1 = grouped_gemm(xs, offsets, w13, s13, bn)
@@ -1082,6 +1081,20 @@ def quant_fp8_1x128(x):
     lds = (t + 63) // 64 * 64
     scale = torch.zeros((k // 128, lds), dtype=torch.float32, device=x.device)
     _check(lib().pg_quant_fp8_1x128(_ptr(x), _ll(x.stride(0)), _ci(t), _ci(k), _ptr(xq), _ll(k), _ptr(scale), _ll(lds), _stream()), ctx(x.device))
+    return xq, scale
+
+
+def swiglu_quant_fp8_1x128(gate_up):
+    """SwiGLU of a fused ``[T, 2 K]`` buffer (gate half first) and the per-token, per-k-group e4m3 quantiser in one kernel;
+    the same values as ``quant_fp8_1x128(swiglu(gate_up))``."""
+    _bf16(gate_up)
+    assert gate_up.stride(-1) == 1
+    t, k2 = gate_up.shape
+    k = k2 // 2
+    xq = torch.empty((t, k), dtype=torch.float8_e4m3fn, device=gate_up.device)
+    lds = (t + 63) // 64 * 64
+    scale = torch.zeros((k // 128, lds), dtype=torch.float32, device=gate_up.device)
+    _check(lib().pg_swiglu_quant_fp8_1x128(_ptr(gate_up), _ll(gate_up.stride(0)), _ci(t), _ci(k), _ptr(xq), _ll(k), _ptr(scale), _ll(lds), _stream()), ctx(gate_up.device))
     return xq, scale
 
 

@@ -116,13 +116,15 @@ class FusedEP(EPContext):
             y1 = K.grouped_gemm_fp8(xq, xsc, offsets, w13, s13, bn)
         else:
             y1 = K.grouped_gemm(xs, offsets, w13, s13, bn)
-        act = K.swiglu(y1)
         m = w2.shape[1]
-        kk = act.shape[1]
-        if mode == 2 and K._MOE_FP8_TC and kk % 128 == 0 and m % 128 == 0:
+        kk = y1.shape[1] // 2
+        fp8_w2 = mode == 2 and K._MOE_FP8_TC and kk % 128 == 0 and m % 128 == 0
+        act = None if fp8_w2 else K.swiglu(y1)
+        if fp8_w2:
             bn8 = 16 if bn <= 16 else 32 if bn <= 32 else 64
-            # W2 on the FP8 tensor-core path as well, with the same scatter-return epilogue
-            aq, asc = K.quant_fp8_1x128(act)
+            # W2 on the FP8 tensor-core path as well (SwiGLU and the quantiser in one kernel), with the same
+            # scatter-return epilogue
+            aq, asc = K.swiglu_quant_fp8_1x128(y1)
             rc = self.lib.pg_moe_grouped_gemm_fp8_return(_vp(aq.data_ptr()), _ll(max_rows), _vp(asc.data_ptr()), _ll(asc.stride(0)), _vp(w2.data_ptr()), _vp(s2.data_ptr()), _ll(h),
                                                          _vp(offsets.data_ptr()), _ci(e_local), _ci(m), _ci(kk), _ci(bn8), _vp(c.status.data_ptr()), _vp(sorted_src.data_ptr()),
                                                          self.comb_table, self.flag_table, _ci(self.cap), _ci(self.rank), _ci(self.world), _ci(site), st)

@@ -808,6 +808,19 @@ def test_dsa_indexer_kernels_match_reference():
     assert K.read_status(dev) == 0
 
 
+def test_swiglu_quant_fp8_equals_swiglu_then_quant():
+    """The fused SwiGLU + e4m3 quantiser writes the same bytes and scales as the two kernels one after the other."""
+    K = cu()
+    g = torch.Generator(device=DEV).manual_seed(11)
+    for t, k in ((5, 256), (130, 1408 // 128 * 128), (64, 2048)):
+        gu = (torch.randn(t, 2 * k, device=DEV, generator=g) * 2).bfloat16()
+        q1, s1 = K.quant_fp8_1x128(K.swiglu(gu))
+        q2, s2 = K.swiglu_quant_fp8_1x128(gu)
+        torch.cuda.synchronize()
+        assert torch.equal(q1.view(torch.uint8), q2.view(torch.uint8)) and torch.equal(s1, s2)
+    status_clean()
+
+
 @pytest.mark.parametrize("t,m,k", [(1, 256, 512), (7, 1024, 2048), (64, 4096, 4096), (100, 2048, 7168), (16, 12288, 4096)])
 def test_fp8_block_scaled_gemm_matches_reference(t, m, k):
     """tcgen05 kind::f8f6f4 GEMM with per-k-group promotion against the dequantised f32 product of the same e4m3 data."""
