@@ -125,8 +125,9 @@ def trace_calls(module=None):
         trace.finalize()
 
 
-def model_report(preset_name: str, batch: int = 8, context: int = 256, device: Optional[str] = None, **overrides) -> str:
-    """Kernel table of one prefill step (``batch`` prompts of ``context`` tokens) and one decode step."""
+def model_report(preset_name: str, batch: int = 8, context: int = 256, device: Optional[str] = None, kernels: bool = False, **overrides) -> str:
+    """Kernel table of one prefill step (``batch`` prompts of ``context`` tokens) and one decode step; with ``kernels`` also
+    the GPU kernels of each step by name (CUPTI activity records, ``utils.range_profiler``)."""
     from ..config import EngineConfig, preset
     from ..engine.build import build_engine
     from ..kv.request_kv import KvView
@@ -153,6 +154,12 @@ def model_report(preset_name: str, batch: int = 8, context: int = 256, device: O
             with trace_calls() as tr:
                 eng.model.forward(tok, meta, eng.kv)
             out.append(tr.report(title))
+            if kernels:
+                from ..utils.range_profiler import RangeProfiler
+
+                with RangeProfiler(title + " (GPU kernels by name)") as rp:
+                    eng.model.forward(tok, meta, eng.kv)
+                out.append(rp.report())
         return "\n\n".join(out)
     finally:
         eng.shutdown()
@@ -166,9 +173,10 @@ def main(argv=None) -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=256)
     ap.add_argument("--layers", type=int, default=0, help="truncate the model (0 = as configured)")
+    ap.add_argument("--kernels", action="store_true", help="also list the GPU kernels of each step by name (range profiler)")
     a = ap.parse_args(argv)
     kw = {"num_layers": a.layers} if a.layers else {}
-    print(model_report(a.preset, a.batch, a.context, **kw))
+    print(model_report(a.preset, a.batch, a.context, kernels=a.kernels, **kw))
     return 0
 
 
