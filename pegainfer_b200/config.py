@@ -71,6 +71,16 @@ class ModelConfig:
     index_topk: int = 0
     index_head_dim: int = 128
     index_n_heads: int = 0
+    # Gemma 4 line: sliding-window layers (head_dim, num_kv_heads, rope_theta_local, full rotary) interleaved with global
+    # layers (global_head_dim, num_global_kv_heads, rope_theta, partial_rotary_factor of the head rotated); layer_types
+    # holds "sliding_attention" | "full_attention"
+    sliding_window: int = 0
+    global_head_dim: int = 0
+    num_global_kv_heads: int = 0
+    attention_k_eq_v: bool = False  # global layers have no v_proj: V is the key projection (before key norm and RoPE)
+    final_logit_softcapping: float = 0.0
+    rope_theta_local: float = 10000.0
+    hidden_act: str = "silu"  # "silu" | "gelu_tanh"
 
     # -- derived ---------------------------------------------------------------
     @property
@@ -169,6 +179,16 @@ PRESETS["small-glm"] = replace(PRESETS["tiny-glm"], vocab_size=4096, hidden_size
 # GLM-5 (zai-org/GLM-5): 78 layers, 256 routed experts, MLA with 192 + 64 query dims and 256 value dims, 32-head indexer keeping 2048 keys
 PRESETS["glm-5"] = replace(PRESETS["small-glm"], vocab_size=154880, hidden_size=6144, num_layers=78, num_q_heads=64, num_kv_heads=64, intermediate_size=12288, q_lora_rank=2048, n_routed_experts=256,
                            num_experts_per_tok=8, moe_intermediate_size=2048, first_k_dense_replace=3, index_topk=2048, max_position=202752, rope_theta=1e6, expert_quant="fp8_block128")
+def _gemma_pattern(n: int) -> tuple:
+    return tuple("sliding_attention" if (i + 1) % 6 else "full_attention" for i in range(n))
+
+
+PRESETS["tiny-gemma4"] = ModelConfig(family="gemma4", vocab_size=1024, hidden_size=256, num_layers=6, num_q_heads=4, num_kv_heads=2, head_dim=64, global_head_dim=128, num_global_kv_heads=1,
+                                     attention_k_eq_v=True, intermediate_size=512, sliding_window=32, layer_types=_gemma_pattern(6), rope_theta=1e6, rope_theta_local=1e4,
+                                     partial_rotary_factor=0.25, final_logit_softcapping=30.0, hidden_act="gelu_tanh", tie_word_embeddings=True, max_position=4096)
+# head dims of the released dense model (256 sliding, 512 global, 5 : 1), two global KV heads of 512 as wide as four local ones of 256
+PRESETS["small-gemma4"] = replace(PRESETS["tiny-gemma4"], vocab_size=4096, hidden_size=1024, num_q_heads=8, num_kv_heads=4, head_dim=256, global_head_dim=512, num_global_kv_heads=2,
+                                  intermediate_size=2048, sliding_window=128, max_position=8192)
 PRESETS["small-glm-fp8"] = replace(PRESETS["small-glm"], expert_quant="fp8_block128", dense_quant="fp8_block128")
 for _name in ("tiny-dsv2", "small-dsv2", "dsv2-lite"):
     if _name in PRESETS:
@@ -193,6 +213,8 @@ def detect_family(cfg: dict) -> str:
         return "deepseek_v2"
     if mt == "glm_moe_dsa" or "GlmMoeDsa" in archs:
         return "glm_dsa"
+    if mt.startswith("gemma4") or "Gemma4" in archs:
+        return "gemma4"
     if mt in ("kimi_k2", "deepseek_v3", "kimi_k25") or "DeepseekV3" in archs or "Kimi" in archs:
         return "kimi_k2"
     raise ValueError(f"no model line recognises model_type={mt!r} architectures={archs!r}")
@@ -221,6 +243,8 @@ def from_hf(cfg: dict, model_dir: Optional[str] = None) -> ModelConfig:
         cfg = cfg["text_config"]
     if family == "kimi_k2" and "text_config" in cfg:
         cfg = cfg["text_config"]
+    if family == "gemma4" and "text_config" in cfg:
+        cfg = cfg["text_config"]
     common = dict(
         family=family,
         vocab_size=cfg["vocab_size"],
@@ -234,6 +258,32 @@ def from_hf(cfg: dict, model_dir: Optional[str] = None) -> ModelConfig:
         tie_word_embeddings=bool(top.get("tie_word_embeddings", cfg.get("tie_word_embeddings", False))),
         eos_token_ids=_eos_ids(model_dir, top),
     )
+    if family == "gemma4":
+        for key in ("hidden_size_per_layer_input", "num_kv_shared_layers"):
+            if cfg.get(key, 0):
+                raise ValueError(f"gemma4: {key}={cfg[key]} (per-layer input embeddings / cross-layer KV sharing of the small variants) is not supported")
+        if cfg.get("enable_moe_block"):
+            raise ValueError("gemma4: the mixture-of-experts variant is not supported")
+        rp = cfg.get("rope_parameters") or {}
+        full, local = rp.get("full_attention", {}), rp.get("sliding_attention", {})
+        n = cfg["num_hidden_layers"]
+        types = cfg.get("layer_types") or ["sliding_attention" if (i + 1) % 6 else "full_attention" for i in range(n)]
+        common["tie_word_embeddings"] = bool(top.get("tie_word_embeddings", cfg.get("tie_word_embeddings", True)))
+        return ModelConfig(
+            head_dim=cfg.get("head_dim", 256),
+            global_head_dim=cfg.get("global_head_dim", 512) or cfg.get("head_dim", 256),
+            num_global_kv_heads=cfg.get("num_global_key_value_heads") or common["num_kv_heads"],
+            attention_k_eq_v=bool(cfg.get("attention_k_eq_v", False)),
+            sliding_window=cfg.get("sliding_window", 512),
+            layer_types=tuple(types),
+            rope_theta=full.get("rope_theta", 1e6),
+            partial_rotary_factor=full.get("partial_rotary_factor", 0.25),
+            rope_theta_local=local.get("rope_theta", 1e4),
+            final_logit_softcapping=cfg.get("final_logit_softcapping") or 0.0,
+            hidden_act="gelu_tanh",
+            qk_norm=True,
+            **common,
+        )
     if family == "qwen3":
         return ModelConfig(head_dim=cfg.get("head_dim", cfg["hidden_size"] // cfg["num_attention_heads"]), rope_theta=cfg.get("rope_theta", 1e6), **common)
     if family == "qwen35":

@@ -90,7 +90,7 @@ class RandomSource(WeightSource):
 
     @staticmethod
     def _default_kind(name: str) -> str:
-        if name.endswith("norm.weight") or "layernorm" in name or name.endswith("_norm.weight"):
+        if name.endswith("norm.weight") or "layernorm" in name or name.endswith("_norm.weight") or name.endswith("layer_scalar"):
             return "ones"
         if name.endswith("A_log") or name.endswith("dt_bias") or name.endswith("e_score_correction_bias"):
             return "small"

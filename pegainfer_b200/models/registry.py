@@ -34,7 +34,14 @@ def _glm_dsa(cfg, **kw):
     return GlmDsaModel(cfg, **kw)
 
 
-BUILDERS = {"glm_dsa": _glm_dsa, "qwen3": _qwen3, "qwen35": _qwen35, "deepseek_v2": _mla_moe, "kimi_k2": _mla_moe}
+def _gemma4(cfg, **kw):
+    from .gemma4 import Gemma4Model
+
+    kw.pop("ep", None)
+    return Gemma4Model(cfg, **kw)
+
+
+BUILDERS = {"gemma4": _gemma4, "glm_dsa": _glm_dsa, "qwen3": _qwen3, "qwen35": _qwen35, "deepseek_v2": _mla_moe, "kimi_k2": _mla_moe}
 
 
 def build(cfg: ModelConfig, **kw):
@@ -49,6 +56,10 @@ def shapes_for(cfg: ModelConfig) -> dict:
         from .glm_dsa import glm_dsa_shapes
 
         return glm_dsa_shapes(cfg)
+    if cfg.family == "gemma4":
+        from .gemma4 import gemma4_shapes
+
+        return gemma4_shapes(cfg)
     raise ValueError(f"no tensor-shape table for family {cfg.family!r}")
 
 
@@ -61,4 +72,11 @@ def hf_config_extras(cfg: ModelConfig) -> dict:
                     norm_topk_prob=cfg.norm_topk_prob, routed_scaling_factor=cfg.routed_scaling_factor, num_nextn_predict_layers=cfg.num_mtp_layers,
                     mlp_layer_types=["dense" if i < cfg.first_k_dense_replace else "sparse" for i in range(cfg.num_layers)], first_k_dense_replace=cfg.first_k_dense_replace,
                     index_topk=cfg.index_topk, index_head_dim=cfg.index_head_dim, index_n_heads=cfg.index_n_heads, rope_parameters=dict(rope_theta=cfg.rope_theta, rope_type="default"))
+    if cfg.family == "gemma4":
+        return dict(model_type="gemma4_text", architectures=["Gemma4ForCausalLM"], head_dim=cfg.head_dim, global_head_dim=cfg.global_head_dim or cfg.head_dim,
+                    num_global_key_value_heads=cfg.num_global_kv_heads or cfg.num_kv_heads, attention_k_eq_v=cfg.attention_k_eq_v, sliding_window=cfg.sliding_window,
+                    layer_types=list(cfg.layer_types), final_logit_softcapping=cfg.final_logit_softcapping or None, hidden_activation="gelu_pytorch_tanh",
+                    hidden_size_per_layer_input=0, vocab_size_per_layer_input=cfg.vocab_size, num_kv_shared_layers=0, enable_moe_block=False, use_double_wide_mlp=False,
+                    rope_parameters={"sliding_attention": {"rope_type": "default", "rope_theta": cfg.rope_theta_local},
+                                     "full_attention": {"rope_type": "proportional", "partial_rotary_factor": cfg.partial_rotary_factor, "rope_theta": cfg.rope_theta}})
     return {}

@@ -110,7 +110,9 @@ def gather_rows(x, idx):
     return _impl(x).gather_rows(x, idx)
 
 
-def qk_norm_rope_append(qkv, q_norm_w, k_norm_w, cos, sin, meta, kv_layer, num_q_heads, num_kv_heads, head_dim, eps, offset=False, gated=False):
+def qk_norm_rope_append(qkv, q_norm_w, k_norm_w, cos, sin, meta, kv_layer, num_q_heads, num_kv_heads, head_dim, eps, offset=False, gated=False, v_norm=False):
+    if v_norm:
+        return _impl(qkv).qk_norm_rope_append(qkv, q_norm_w, k_norm_w, cos, sin, meta, kv_layer, num_q_heads, num_kv_heads, head_dim, eps, offset, gated, True)
     return _impl(qkv).qk_norm_rope_append(qkv, q_norm_w, k_norm_w, cos, sin, meta, kv_layer, num_q_heads, num_kv_heads, head_dim, eps, offset, gated)
 
 

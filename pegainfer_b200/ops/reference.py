@@ -82,6 +82,20 @@ def add_rms_norm(x, residual, w, eps, offset=False, round_before_norm=True):
     return (src * inv * wf).to(x.dtype)
 
 
+def geglu(gate_up: torch.Tensor) -> torch.Tensor:
+    """``round(gelu_tanh(gate)) * up`` on a fused ``[T, 2I]`` buffer, gate half first."""
+    i = gate_up.shape[-1] // 2
+    g = gate_up[..., :i].float()
+    u = gate_up[..., i:].float()
+    a = torch.nn.functional.gelu(g, approximate="tanh").to(gate_up.dtype).float()
+    return (a * u).to(gate_up.dtype)
+
+
+def softcap(logits: torch.Tensor, cap: float) -> torch.Tensor:
+    """``cap * tanh(logits / cap)`` (final-logit soft-capping)."""
+    return (torch.tanh(logits.float() / cap) * cap).to(logits.dtype)
+
+
 def gated_rms_norm(x, gate, w, eps):
     """Per-head ``rms_norm(x, w_f32) * silu(gate)``; x, gate: [T, H, D]."""
     xf = x.float()
@@ -176,9 +190,9 @@ def _rope_interleaved_in(x, cos, sin):
     return torch.cat([o1, o2], dim=-1)
 
 
-def qk_norm_rope_append(qkv, q_norm_w, k_norm_w, cos, sin, meta: AttnMeta, kv_layer, num_q_heads, num_kv_heads, head_dim, eps, offset=False, gated=False):
+def qk_norm_rope_append(qkv, q_norm_w, k_norm_w, cos, sin, meta: AttnMeta, kv_layer, num_q_heads, num_kv_heads, head_dim, eps, offset=False, gated=False, v_norm=False):
     """Split fused qkv rows, per-head RMSNorm on q/k (optional), rotate, append k/v
-    to the paged cache.  Returns ``q [T, Hq, D]`` (and ``gate [T, Hq, D]`` if gated:
+    to the paged cache (``v_norm``: the value rows get a weightless per-head RMSNorm first).  Returns ``q [T, Hq, D]`` (and ``gate [T, Hq, D]`` if gated:
     q_proj rows are then per-head ``[q(D), gate(D)]``)."""
     t = qkv.shape[0]
     qw = num_q_heads * head_dim * (2 if gated else 1)
@@ -198,6 +212,9 @@ def qk_norm_rope_append(qkv, q_norm_w, k_norm_w, cos, sin, meta: AttnMeta, kv_la
     c, s = cos[pos], sin[pos]
     q = _rope_half(q, c, s)
     k = _rope_half(k, c, s)
+    if v_norm:
+        vf = v.float()
+        v = (vf * torch.rsqrt(vf.pow(2).mean(-1, keepdim=True) + eps)).to(v.dtype)
     ps = meta.page_size
     slots = meta.slot_mapping.long()
     kv_layer[slots // ps, 0, slots % ps] = k

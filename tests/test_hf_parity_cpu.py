@@ -15,11 +15,11 @@ from pegainfer_b200.utils.hf_parity import compare
 pytest.importorskip("transformers")
 
 
-@pytest.mark.parametrize("name,atol", [("tiny-qwen3", 2e-5), ("tiny-qwen35", 2e-5), ("tiny-dsv2", 2e-5), ("tiny-kimi", 5e-4), ("tiny-glm", 5e-4)])
+@pytest.mark.parametrize("name,atol", [("tiny-qwen3", 2e-5), ("tiny-qwen35", 2e-5), ("tiny-dsv2", 2e-5), ("tiny-kimi", 5e-4), ("tiny-glm", 5e-4), ("tiny-gemma4", 5e-4)])
 def test_prompt_logits_match_hugging_face(name, atol):
     cfg = preset(name)
     g = torch.Generator().manual_seed(3)
-    toks = torch.randint(0, cfg.vocab_size, (40,), generator=g).tolist()
+    toks = torch.randint(0, cfg.vocab_size, (40,), generator=g).tolist()  # past tiny-gemma4's sliding window of 32
     with tempfile.TemporaryDirectory() as tmp:
         export_checkpoint(cfg, tmp, dtype=torch.float32)
         whole = compare(tmp, toks)

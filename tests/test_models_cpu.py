@@ -239,6 +239,20 @@ def test_eagle3_chain_drafter_is_lossless():
     assert c.num_draft_tokens == 3 * c.num_drafts
 
 
+def test_gemma4_sliding_and_global_layers_chunking_invariance():
+    """tiny-gemma4: five sliding-window layers (window 32, head dim 64) and one global layer (head dim 128, one KV head, V
+    from the key projection) over prompts past the window; chunked, batched and one-at-a-time generation must agree."""
+    _chunking_invariance("tiny-gemma4")
+    from pegainfer_b200.models.gemma4 import Gemma4Model, proportional_rope_tables
+
+    m = Gemma4Model(preset("tiny-gemma4"), device="cpu", dtype=torch.float32)
+    assert [l.head_dim for l in m.layers] == [64] * 5 + [128] and [l.kv_heads for l in m.layers] == [2] * 5 + [1]
+    assert m.kv_geometry() == dict(num_layers=6, kv_heads=1, head_dim=128) and m.allows_prefix_cache  # 2 x 64 == 1 x 128
+    assert torch.equal(m.layers[5].qkv[4 * 128 : 5 * 128], m.layers[5].qkv[5 * 128 :])  # V rows are the K rows
+    cos, sin = proportional_rope_tables(64, 128, 0.25, 1e6, torch.float32, "cpu")
+    assert cos.shape == (64, 64) and torch.all(cos[:, 16:] == 1) and torch.all(sin[:, 16:] == 0) and sin[5, 0] != 0
+
+
 def test_glm_sparse_indexer_chunking_invariance_and_mtp():
     """tiny-glm keeps 24 keys per query: prompts of 40+ tokens run the indexer and the sparse latent attention.
     Chunked, batched and one-at-a-time generation must agree, and the MTP head must stay lossless."""
