@@ -74,8 +74,9 @@ int pg_swiglu(const void* gate_up, void* out, int rows, int inter, long long ldi
 int pg_sigmoid_gate_mul(void* x, const void* gate, long long n, cudaStream_t stream);
 int pg_qk_norm_rope_append(const void* qkv, long long ld, const void* q_w, const void* k_w, const void* cos, const void* sin,
                            const void* positions, const void* slots, void* q_out, void* gate_out, void* kv, int tokens, int hq, int hkv, int dim,
-                           int rot, int page_size, long long num_pages, int max_pos, int gated, int offset, float eps, void* status,
+                           int rot, int page_size, long long num_pages, int max_pos, int gated, int offset, float eps, int v_norm, void* status,
                            cudaStream_t stream);
+int pg_softcap(const void* x, void* y, long long n, float cap, cudaStream_t stream);
 
 int pg_repack_int4_pairs(const void* in, void* out, long long words, cudaStream_t stream);
 

@@ -143,8 +143,10 @@ __global__ void gated_rms_norm_kernel(const bf16* __restrict__ x, const bf16* __
 }
 
 // `interleaved` = 0: a row is [gate_0 .. gate_{I-1}, up_0 .. up_{I-1}]; 1: (gate_0, up_0, gate_1, up_1, ...).
-__global__ void swiglu_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int rows, int inter, long long ldin, long long ldout, int interleaved) {
+// `flags`: bit 0 = gate / up columns interleaved, bit 1 = tanh GELU instead of SiLU on the gate (GeGLU)
+__global__ void swiglu_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int rows, int inter, long long ldin, long long ldout, int flags) {
   PG_PDL_ENTRY();
+  const int interleaved = flags & 1, gelu = flags & 2;
   const int nvec = inter / 8;
   const long long total = (long long)rows * nvec;
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
@@ -167,9 +169,20 @@ __global__ void swiglu_kernel(const bf16* __restrict__ gu, bf16* __restrict__ ou
       unpack8(*u, uf);
     }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) o[j] = bf16_round(gf[j] / (1.f + __expf(-gf[j]))) * uf[j];
+    for (int j = 0; j < 8; ++j) {
+      const float g = gf[j];
+      const float a = gelu ? 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) : g / (1.f + __expf(-g));
+      o[j] = bf16_round(a) * uf[j];
+    }
     reinterpret_cast<bf16x8*>(out + row * ldout)[i] = pack8(o);
   }
+}
+
+__global__ void softcap_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, long long n, float cap) {
+  PG_PDL_ENTRY();
+  const float inv = 1.f / cap;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    y[i] = __float2bfloat16(tanhf(__bfloat162float(x[i]) * inv) * cap);
 }
 
 __global__ void sigmoid_gate_mul_kernel(bf16* __restrict__ x, const bf16* __restrict__ gate, long long n) {
@@ -195,6 +208,7 @@ struct RopeParams {
   bf16* gate_out;
   bf16* kv;  // [pages, 2, page_size, Hkv, D]
   int tokens, hq, hkv, dim, rot, page_size, max_pos, gated, offset, has_norm;
+  int v_norm;  // value rows get a weightless RMSNorm over the head before they are stored
   long long num_slots;
   float eps;
   uint32_t* status;
@@ -230,6 +244,17 @@ __global__ void __launch_bounds__(128) qk_norm_rope_append_kernel(const RopePara
   const long long page = slot / p.page_size, off = slot % p.page_size;
   if (kind == 2) {
     bf16* dst = p.kv + (((page * 2 + 1) * p.page_size + off) * p.hkv + (h - p.hq - p.hkv)) * D;
+    if (p.v_norm) {
+      float ss = 0.f;
+      for (int i = lane; i < D; i += 32) {
+        const float v = __bfloat162float(src[i]);
+        ss += v * v;
+      }
+      ss = warp_sum(ss);
+      const float inv = rsqrtf(ss / (float)D + p.eps);
+      for (int i = lane; i < D; i += 32) dst[i] = __float2bfloat16(__bfloat162float(src[i]) * inv);
+      return;
+    }
     for (int i = lane; i < D / 8; i += 32) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
     return;
   }
@@ -345,6 +370,21 @@ __global__ void __launch_bounds__(128) qk_norm_rope_append_vec_kernel(const Rope
     if (kind != 0 && !slot_ok) continue;
     if (kind == 2) {
       bf16* dst = p.kv + (((page * 2 + 1) * p.page_size + off) * p.hkv + (h - p.hq - p.hkv)) * D;
+      if (p.v_norm) {
+        float vv[VEC], ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+          vv[i] = __bfloat162float(in[g].v[i]);
+          ss += vv[i] * vv[i];
+        }
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss / (float)D + p.eps);
+        Pack vo;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) vo.v[i] = __float2bfloat16(vv[i] * inv);
+        *reinterpret_cast<Pack*>(dst + lane * VEC) = vo;
+        continue;
+      }
       *reinterpret_cast<Pack*>(dst + lane * VEC) = in[g];
       continue;
     }
@@ -424,6 +464,16 @@ extern "C" int pg_swiglu(const void* gate_up, void* out, int rows, int inter, lo
   return PG_OK;
 }
 
+extern "C" int pg_softcap(const void* x, void* y, long long n, float cap, cudaStream_t stream) {
+  PG_REQUIRE(cap > 0.f, "softcap: the cap must be positive");
+  if (n == 0) return PG_OK;
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  PG_CUDA(launch_pdl(softcap_kernel, dim3((int)blocks), dim3(256), (size_t)(0), stream, (const bf16*)x, (bf16*)y, n, cap));
+  PG_LAUNCH_CHECK();
+  return PG_OK;
+}
+
 extern "C" int pg_sigmoid_gate_mul(void* x, const void* gate, long long n, cudaStream_t stream) {
   if (n == 0) return PG_OK;
   long long blocks = (n + 255) / 256;
@@ -436,8 +486,8 @@ extern "C" int pg_sigmoid_gate_mul(void* x, const void* gate, long long n, cudaS
 extern "C" int pg_qk_norm_rope_append(const void* qkv, long long ld, const void* q_w, const void* k_w, const void* cos, const void* sin,
                                       const void* positions, const void* slots, void* q_out, void* gate_out, void* kv, int tokens, int hq, int hkv,
                                       int dim, int rot, int page_size, long long num_pages, int max_pos, int gated, int offset, float eps,
-                                      void* status, cudaStream_t stream) {
-  PG_REQUIRE(dim % 8 == 0 && dim <= 256 && rot <= dim && rot % 2 == 0, "qk_norm_rope: unsupported head_dim %d / rotary %d", dim, rot);
+                                      int v_norm, void* status, cudaStream_t stream) {
+  PG_REQUIRE(dim % 8 == 0 && (dim <= 256 || dim == 512) && rot <= dim && rot % 2 == 0, "qk_norm_rope: unsupported head_dim %d / rotary %d", dim, rot);
   if (tokens == 0) return PG_OK;
   RopeParams p;
   p.qkv = (const bf16*)qkv;
@@ -461,18 +511,21 @@ extern "C" int pg_qk_norm_rope_append(const void* qkv, long long ld, const void*
   p.gated = gated;
   p.offset = offset;
   p.has_norm = q_w != nullptr;
+  p.v_norm = v_norm;
   p.num_slots = num_pages * page_size;
   p.eps = eps;
   p.status = (uint32_t*)status;
   long long units = (long long)tokens * (hq + 2 * hkv);
-  const int vec = dim / 32, half_lanes = (dim == 64 || dim == 128 || dim == 256) && rot >= 2 * vec && (rot / 2) % vec == 0 ? rot / 2 / vec : 0;
-  const bool vec_ok = half_lanes > 0 && (half_lanes & (half_lanes - 1)) == 0 && ld % 8 == 0 && ((uintptr_t)qkv & 15) == 0;
+  const int vec = dim / 32, half_lanes = (dim == 64 || dim == 128 || dim == 256 || dim == 512) && rot >= 2 * vec && (rot / 2) % vec == 0 ? rot / 2 / vec : 0;
+  const bool vec_ok = half_lanes > 0 && (half_lanes & (half_lanes - 1)) == 0 && ld % (dim == 512 ? 16 : 8) == 0 && ((uintptr_t)qkv & (dim == 512 ? 31 : 15)) == 0;
+  PG_REQUIRE(dim <= 256 || vec_ok, "qk_norm_rope: head dim 512 needs a rotary width whose half is a power-of-two multiple of 16 and 32-byte aligned rows");
   if (vec_ok) {
     const long long vunits = (long long)tokens * ((hq + 2 * hkv + ROPE_G - 1) / ROPE_G);
     const dim3 grid((unsigned)((vunits + 3) / 4));
     if (dim == 64) PG_CUDA(launch_pdl(qk_norm_rope_append_vec_kernel<2>, grid, dim3(128), (size_t)(0), stream, p));
     else if (dim == 128) PG_CUDA(launch_pdl(qk_norm_rope_append_vec_kernel<4>, grid, dim3(128), (size_t)(0), stream, p));
-    else PG_CUDA(launch_pdl(qk_norm_rope_append_vec_kernel<8>, grid, dim3(128), (size_t)(0), stream, p));
+    else if (dim == 256) PG_CUDA(launch_pdl(qk_norm_rope_append_vec_kernel<8>, grid, dim3(128), (size_t)(0), stream, p));
+    else PG_CUDA(launch_pdl(qk_norm_rope_append_vec_kernel<16>, grid, dim3(128), (size_t)(0), stream, p));
     PG_LAUNCH_CHECK();
     return PG_OK;
   }

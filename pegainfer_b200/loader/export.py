@@ -43,6 +43,10 @@ def default_source(cfg: ModelConfig, seed: int = 0, dtype=torch.bfloat16):
         from ..models.mla_moe import _QuantRandomSource, mla_moe_shapes
 
         return _QuantRandomSource(mla_moe_shapes(cfg), seed=seed, dtype=dtype)
+    if cfg.family == "gemma4":
+        from ..models.gemma4 import gemma4_source
+
+        return gemma4_source(cfg, seed=seed, dtype=dtype)
     from ..models import registry
 
     shapes = registry.shapes_for(cfg)

@@ -79,7 +79,7 @@ class DictSource(WeightSource):
 class RandomSource(WeightSource):
     """Deterministic synthetic weights.  ``shapes`` maps tensor name -> shape; a
     callable ``kind(name)`` picks the distribution: ``"normal"`` (std 0.02),
-    ``"ones"``, ``"zeros"`` or ``"small"`` (N(0, 0.02) vectors, e.g. biases)."""
+    ``"ones"``, ``"zeros"``, ``"const:<value>"`` or ``"small"`` (N(0, 0.02) vectors, e.g. biases)."""
 
     def __init__(self, shapes: dict, seed: int = 0, std: float = 0.02, kind: Optional[Callable[[str], str]] = None, dtype=torch.bfloat16):
         self.shapes = shapes
@@ -119,6 +119,8 @@ class RandomSource(WeightSource):
             t = torch.ones(shape, dtype=dtype, device=device)
         elif kind == "zeros":
             t = torch.zeros(shape, dtype=dtype, device=device)
+        elif kind.startswith("const:"):
+            t = torch.full(shape, float(kind[6:]), dtype=dtype, device=device)
         else:
             dev = torch.device(device)
             g = torch.Generator(device=dev)

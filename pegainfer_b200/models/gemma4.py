@@ -72,6 +72,19 @@ def gemma4_shapes(cfg: ModelConfig) -> dict:
     return s
 
 
+def _kind(name: str) -> str:
+    """Random-weight distributions.  The softmax scale of this line is 1 and Q / K are RMS-normalised per head, so
+    unit norm weights would give scores of standard deviation sqrt(head_dim) and a softmax that is an argmax; the
+    released checkpoints carry learned norm weights well below one."""
+    if name.endswith("q_norm.weight") or name.endswith("k_norm.weight"):
+        return "const:0.25"
+    return RandomSource._default_kind(name)
+
+
+def gemma4_source(cfg: ModelConfig, seed: int = 0, dtype=torch.bfloat16) -> RandomSource:
+    return RandomSource(gemma4_shapes(cfg), seed=seed, dtype=dtype, kind=_kind)
+
+
 def proportional_rope_tables(max_pos: int, head_dim: int, fraction: float, theta: float, dtype, device):
     """cos / sin ``[max_pos, head_dim / 2]`` of the global layers: ``int(fraction * head_dim // 2)`` rotating pairs with
     ``theta ** (-2 i / head_dim)``, angle zero (the identity) for the other pairs."""
@@ -113,7 +126,7 @@ class Gemma4Model:
         self.dtype = dtype
         self.tp = tp
         self.lora = None
-        source = source or RandomSource(gemma4_shapes(cfg), seed=seed, dtype=dtype)
+        source = source or gemma4_source(cfg, seed=seed, dtype=dtype)
         self._load(source)
         dg = cfg.global_head_dim or cfg.head_dim
         self.cos_l, self.sin_l = rope_tables(cfg.max_position, cfg.head_dim, cfg.rope_theta_local, dtype, self.device)

@@ -206,6 +206,25 @@ def swiglu(gate_up, interleaved: bool = False):
     return out.view(*gate_up.shape[:-1], inter)
 
 
+def geglu(gate_up):
+    """``bf16(gelu_tanh(gate)) * up`` on a fused ``[T, 2 I]`` buffer, gate half first."""
+    _bf16(gate_up)
+    g2 = _rows2d(gate_up)
+    inter = g2.shape[1] // 2
+    out = torch.empty((g2.shape[0], inter), dtype=g2.dtype, device=g2.device)
+    _check(lib().pg_swiglu(_ptr(g2), _ptr(out), _ci(g2.shape[0]), _ci(inter), _ll(g2.stride(0)), _ll(out.stride(0)), _ci(2), _stream()), ctx(g2.device))
+    return out.view(*gate_up.shape[:-1], inter)
+
+
+def softcap(logits, cap: float):
+    """``cap * tanh(logits / cap)``."""
+    _bf16(logits)
+    x = logits.contiguous()
+    y = torch.empty_like(x)
+    _check(lib().pg_softcap(_ptr(x), _ptr(y), _ll(x.numel()), _cf(cap), _stream()), ctx(x.device))
+    return y
+
+
 class DeferredNorm:
     """Activations whose RMSNorm is still owed its per-token scale: ``xw = h * norm_w`` plus the
     per-(token, weight tile) sums of squares of ``h`` (``ssp[:, :parts]``).  The GEMM that consumes
@@ -489,7 +508,7 @@ def gemm_plan(t: int, m: int, k: int, force_splits: int = 0) -> dict:
     return dict(zip(("bn", "splits", "cluster", "grid", "stages", "max_clusters"), list(out)))
 
 
-def qk_norm_rope_append(qkv, q_norm_w, k_norm_w, cos, sin, meta: AttnMeta, kv_layer, num_q_heads, num_kv_heads, head_dim, eps, offset=False, gated=False):
+def qk_norm_rope_append(qkv, q_norm_w, k_norm_w, cos, sin, meta: AttnMeta, kv_layer, num_q_heads, num_kv_heads, head_dim, eps, offset=False, gated=False, v_norm=False):
     _bf16(qkv)
     t = qkv.shape[0]
     assert qkv.stride(-1) == 1
@@ -501,7 +520,7 @@ def qk_norm_rope_append(qkv, q_norm_w, k_norm_w, cos, sin, meta: AttnMeta, kv_la
     rc = lib().pg_qk_norm_rope_append(
         _ptr(qkv), _ll(qkv.stride(0)), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(cos), _ptr(sin), _ptr(meta.positions), _ptr(meta.slot_mapping),
         _ptr(q), _ptr(gate), _ptr(kv_layer), _ci(t), _ci(num_q_heads), _ci(num_kv_heads), _ci(head_dim), _ci(cos.shape[-1] * 2), _ci(page_size),
-        _ll(num_pages), _ci(cos.shape[0]), _ci(int(gated)), _ci(int(offset)), _cf(eps), _ptr(c.status), _stream(),
+        _ll(num_pages), _ci(cos.shape[0]), _ci(int(gated)), _ci(int(offset)), _cf(eps), _ci(int(v_norm)), _ptr(c.status), _stream(),
     )
     _check(rc, c)
     return (q, gate) if gated else q
@@ -561,6 +580,14 @@ def paged_attention(q, kv_layer, meta: AttnMeta, scale=None, window=0, out: Opti
         out = torch.empty((t, hq * d), dtype=q.dtype, device=q.device)
     c = ctx(q.device)
     table = meta.block_table
+    if d == 512:
+        # wide heads (global layers of the Gemma 4 line): one block per (query row, KV head), csrc/attention_wide.cu
+        assert q.is_contiguous() and kv_layer.is_contiguous()
+        rc = lib().pg_attention_wide(_ptr(q), _ptr(kv_layer), _ptr(out), _ptr(_unit_seq(meta, q.device)), _ptr(meta.q_indptr), _ptr(meta.kv_lens), _ptr(table),
+                                     _ci(table.stride(0)), _ci(t), _ci(hq), _ci(hkv), _ci(d), _ci(page_size), _ll(kv_layer.shape[0]), _cf(scale), _ci(window), _ptr(c.status),
+                                     _stream())
+        _check(rc, c)
+        return out
 
     def decode_rows(first: int, n: int, plan=None):
         """Decode kernel (one query row per sequence, the Q heads of a KV head packed into one MMA
@@ -580,7 +607,12 @@ def paged_attention(q, kv_layer, meta: AttnMeta, scale=None, window=0, out: Opti
     if meta.decode_only and window == 0:
         decode_rows(0, meta.num_seqs, meta.plan)
         return out
-    qi = meta.h_q_indptr if meta.h_q_indptr is not None else meta.q_indptr.tolist()
+    if meta.h_q_indptr is not None:
+        qi = meta.h_q_indptr
+    elif meta.decode_only:  # one row per sequence (a captured decode step has no host copies)
+        qi = list(range(meta.num_seqs + 1))
+    else:
+        qi = meta.q_indptr.tolist()
     n_pf = meta.num_seqs
     if window == 0:
         # A unified step lists its prompt chunks first and its decode rows last.  Through the prefill

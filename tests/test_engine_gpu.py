@@ -174,11 +174,17 @@ def test_long_prompts_take_the_tcgen05_prefill_kernels():
     assert K.PREFILL_TC_CALLS["hd256"] > before["hd256"]
 
 
+def test_gemma4_sliding_window_and_wide_global_layers_kernels_vs_library():
+    """small-gemma4: sliding-window layers of head dim 256 (window 128) and a global layer of head dim 512 with two KV
+    heads, V from the key projection; prompts past the window, logits close to the PyTorch library path."""
+    _family_logits_close("small-gemma4", lens=(200, 90, 150))
+
+
 def test_qwen35_hybrid_kernels_vs_library():
     _family_logits_close("small-qwen35")
 
 
-@pytest.mark.parametrize("name", ["small-dsv2", "small-kimi", "small-qwen35"])
+@pytest.mark.parametrize("name", ["small-dsv2", "small-kimi", "small-qwen35", "small-gemma4"])
 def test_family_generate_graph_equals_eager(name):
     e1, e2 = _family_engine(name, False), _family_engine(name, True)
     try:

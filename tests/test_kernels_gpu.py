@@ -160,6 +160,46 @@ def make_batch(q_lens, kv_lens, page_size, hkv, d, extra_pages=3, pad=0):
     return kv, meta
 
 
+@pytest.mark.parametrize("hq,hkv,page", [(8, 2, 16), (8, 1, 64), (4, 4, 16)])
+def test_wide_head_attention_hd512(hq, hkv, page):
+    """Head dim 512 (the global layers of the Gemma 4 line): prefill chunks, decode rows and padding rows through the
+    one-block-per-(row, KV head) kernel, with scale 1 on normalised rows and with a sliding window."""
+    torch.manual_seed(hq)
+    d = 512
+    q_lens = [1, 64, 65, 130, 1, 17]
+    kv_lens = [40, 64, 200, 130, 1, 300]
+    kv, meta = make_batch(q_lens, kv_lens, page, hkv, d, pad=2)
+    kv = (kv.float() * 0.05).bfloat16()
+    q = (torch.randn(meta.num_tokens, hq, d, device=DEV) * 0.5).bfloat16()
+    for scale, window in ((None, 0), (1.0, 0), (None, 48)):
+        ref = R.paged_attention(q, kv, meta, scale, window)
+        out = cu().paged_attention(q, kv, meta, scale, window)
+        bf16_close(out, ref, rel=2 ** -6, abs_=6e-3)
+    status_clean()
+
+
+def test_geglu_softcap_and_value_norm_kernels():
+    K = cu()
+    g = torch.Generator(device=DEV).manual_seed(5)
+    gu = (torch.randn(70, 2 * 1024, device=DEV, generator=g) * 2).bfloat16()
+    bf16_close(K.geglu(gu), R.geglu(gu), rel=2 ** -6, abs_=4e-3)
+    lg = (torch.randn(9, 4096, device=DEV, generator=g) * 40).bfloat16()
+    bf16_close(K.softcap(lg, 30.0), R.softcap(lg, 30.0), rel=2 ** -6, abs_=4e-3)
+    # weightless RMSNorm of the value rows inside the fused norm + RoPE + append kernels (vector and scalar variants)
+    for d, rot in ((256, 256), (512, 512), (96, 48)):
+        hq, hkv, page = 4, 2, 16
+        kv, meta = make_batch([5, 1, 20], [21, 33, 20], page, hkv, d)
+        kv2 = kv.clone()
+        qkv = torch.randn(meta.num_tokens, (hq + 2 * hkv) * d, device=DEV, generator=g).bfloat16()
+        w = (torch.randn(d, device=DEV, generator=g) * 0.1 + 1).bfloat16()
+        cos, sin = R.rope_tables(512, rot, 1e4, torch.bfloat16, DEV)
+        a = K.qk_norm_rope_append(qkv, w, w, cos, sin, meta, kv, hq, hkv, d, 1e-6, False, False, True)
+        b = R.qk_norm_rope_append(qkv, w, w, cos, sin, meta, kv2, hq, hkv, d, 1e-6, False, False, True)
+        bf16_close(a, b, rel=2 ** -7, abs_=2e-3)
+        bf16_close(kv, kv2, rel=2 ** -7, abs_=2e-3)
+    status_clean()
+
+
 @pytest.mark.parametrize("d,hq,hkv,page", [(128, 32, 8, 16), (64, 4, 2, 16), (256, 24, 4, 64), (128, 8, 8, 32), (128, 6, 1, 16)])
 def test_decode_attention(d, hq, hkv, page):
     torch.manual_seed(d + hq)
