@@ -443,7 +443,7 @@ def main():
     ap.add_argument("--only", default=None)
     ap.add_argument("--iters", type=int, default=16)
     ap.add_argument("--json", default=None)
-    ap.add_argument("--single", default=None, help="e.g. gemm:64x4096x4096, attn:64x1152, prefill:4x1024, prefill256:1x4096, gdn:8x2048 (sequences x tokens), chain:64x4096x12288x6144 (tokens x hidden x ffn x qkv), "
+    ap.add_argument("--single", default=None, help="e.g. gemm:64x4096x4096, attn:64x1152, prefill:4x1024, prefill256:1x4096, prefill512:4x1024, decode512:64x1152, gdn:8x2048 (sequences x tokens), chain:64x4096x12288x6144 (tokens x hidden x ffn x qkv), "
                     "fp8:64x24576x4096, dsa:16x16384 (sequences x context)")
     ap.add_argument("--library", action="store_true", help="also time torch/cuBLAS for the GEMM rows")
     ap.add_argument("--phases", default=None, help="gemm:TxMxK: print the per-CTA phase timeline of one GEMM launch")
@@ -477,6 +477,10 @@ def main():
             rows.extend(r2[:-1])
             name, ms, by, fl = r2[-1]
             args.single = name
+        elif kind == "prefill512":  # global layers of the Gemma 4 line: 32 query / 4 KV heads of 512 (plain CUDA cores)
+            ms, by, fl = attn_prefill_case(dims[0], dims[1], 32, 4, 512, 16, args.iters)
+        elif kind == "decode512":
+            ms, by, fl = attn_decode_case(dims[0], dims[1], 32, 4, 512, 16, args.iters)
         elif kind == "prefill256":  # the gated full-attention layers of Qwen3.5-27B: 24 query / 4 KV heads of 256
             ms, by, fl = attn_prefill_case(dims[0], dims[1], 24, 4, 256, 16, args.iters)
         else:

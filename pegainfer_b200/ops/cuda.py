@@ -1180,11 +1180,19 @@ def _unit_seq(meta: AttnMeta, device):
     """Sequence index of every query row."""
     if meta.decode_only:
         return meta.q_indptr  # one row per sequence: q_indptr[i] == i
+    cached = getattr(meta, "_pg_unit_seq", None)  # one upload per step, shared by the layers (and made before any capture)
+    if cached is not None:
+        return cached
     qi = meta.h_q_indptr if meta.h_q_indptr is not None else meta.q_indptr.tolist()
     seq_of = []
     for b in range(meta.num_seqs):
         seq_of.extend([b] * (qi[b + 1] - qi[b]))
-    return torch.tensor(seq_of, dtype=torch.int32, device=device)
+    out = torch.tensor(seq_of, dtype=torch.int32).pin_memory().to(device, non_blocking=True) if torch.device(device).type == "cuda" else torch.tensor(seq_of, dtype=torch.int32)
+    try:
+        meta._pg_unit_seq = out
+    except Exception:
+        pass
+    return out
 
 
 def dsa_index_scores(q, w, index_layer, meta: AttnMeta):
