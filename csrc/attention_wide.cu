@@ -1,12 +1,13 @@
 // Causal GQA attention over the paged KV cache for wide heads (head dim 512: the global layers of the Gemma 4 line),
-// prefill chunks and decode rows alike.
+// prefill chunks and decode rows alike.  Head dim 512 leaves no room in tensor memory for the accumulators of the tcgen05
+// kernels (O alone would take all 512 columns), so this head dim runs on `mma.sync` with the head split over the warps
+// of a block (second kernel below); the first kernel is the plain CUDA-core form, kept for query-head groups that do not
+// divide 16 and as the oracle-like fallback (`PEGAINFER_WIDE_MMA=0`).
 //
-// One block per (query row, KV head): its warps are the query heads that share the KV head, so a tile of keys and values
-// is fetched through the page table once and used by all of them from shared memory.  A lane holds D / 32 consecutive
-// elements of its head's query row and of the output row; per tile of 16 keys a warp computes the 16 scores (dot
-// products reduced over the warp), one running-maximum update, and the weighted sum of the 16 value rows.  Plain CUDA
-// cores: these layers are one in six of the model, and head dim 512 leaves no room in tensor memory for the accumulators
-// of the tcgen05 kernels (O alone would take all 512 columns).
+// CUDA-core kernel: one block per (query row, KV head): its warps are the query heads that share the KV head, so a tile
+// of keys and values is fetched through the page table once and used by all of them from shared memory.  A lane holds
+// D / 32 consecutive elements of its head's query row and of the output row; per tile of 16 keys a warp computes the 16
+// scores (dot products reduced over the warp), one running-maximum update, and the weighted sum of the 16 value rows.
 //
 // Reference parity: pegainfer-kernels/csrc/shared/prefill_attention_hd512.cu:64-540, paged_attention_hd512.cu:71-224.
 #include "api.h"
@@ -134,12 +135,288 @@ __global__ void __launch_bounds__(256) attn_wide_kernel(const WideParams p) {
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// Tensor-core variant (mma.sync m16n8k16, bf16 in, f32 accumulate).  A block of eight warps owns two MMA row tiles of 16
+// rows: 32 / G consecutive query tokens of a sequence times the G query heads of one KV head, so prefill chunks and
+// decode rows alike fetch a key / value tile once for the whole group.  The head dim is split over the four warps of a
+// row tile: warp w multiplies Q[:, 128 w : 128 w + 128] with the same slice of the 32 keys of a tile, the four partial
+// score tiles are summed through shared memory, every warp runs the (identical) online softmax, and accumulates its own
+// 128 columns of O.  K / V tiles of 32 keys x 512 are double-buffered by cp.async through the page table.
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const int sz = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  bf162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+// Swizzled offset (in bf16 elements) of 16-byte chunk `ch` of row `r` in a [rows][D] tile.
+template <int D>
+__device__ __forceinline__ int swz(int r, int ch) {
+  return r * D + ((ch ^ (r & 7)) << 3);
+}
+
+constexpr float NEG_BIG = -1e30f;
+
+constexpr int WIDE_ROWS = 32;  // query rows (tokens x heads of the group) per block: two MMA row tiles
+
+template <int D>
+__global__ void __launch_bounds__(256, 1) attn_wide_mma_kernel(const WideParams p, int num_seqs) {
+  PG_PDL_ENTRY();
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  constexpr int BKV = 32;
+  constexpr int CH = D / 8;    // 16-byte chunks per row
+  constexpr int SL = D / 4;    // columns of one warp's slice (128)
+  constexpr int KS = SL / 16;  // k-steps of the slice in Q K^T
+  constexpr int NT = SL / 8;   // n-tiles of the slice in P V
+  constexpr int TILE_ELEMS = BKV * D;
+  bf16* sm = reinterpret_cast<bf16*>(smem_raw);                             // [2 stages][K | V][32][D]; the Q tile is staged in stage 0 first
+  float* s_part = reinterpret_cast<float*>(sm + 2 * 2 * TILE_ELEMS);        // [8 warps][BKV / 8][32 lanes][4]
+  const int warp_id = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rt = warp_id >> 2, warp = warp_id & 3;  // row tile of 16 rows, slice of the head dim
+  const int g = lane >> 2, t4 = lane & 3;
+  const int hk = blockIdx.y;
+  const int G = p.hq / p.hkv;
+  const int TPT = WIDE_ROWS / G;  // query tokens per block
+
+  int b = 0, tile_in_seq = 0;
+  {
+    int rem = (int)gridDim.x - 1 - (int)blockIdx.x;  // late tiles (most keys) first
+    for (; b < num_seqs; ++b) {
+      const int n = p.q_indptr[b + 1] - p.q_indptr[b];
+      const int nt = (n + TPT - 1) / TPT;
+      if (rem < nt) {
+        tile_in_seq = rem;
+        break;
+      }
+      rem -= nt;
+    }
+    if (b >= num_seqs) return;
+  }
+  const int q0 = p.q_indptr[b], q_len = p.q_indptr[b + 1] - q0;
+  const int kv_len = p.kv_lens[b];
+  const int* table_row = p.table + (long long)b * p.table_stride;
+  const int tok_base_q = tile_in_seq * TPT;  // first query token of this tile within the sequence
+  const int toks_here = min(TPT, q_len - tok_base_q);
+  const int pos_base = kv_len - q_len + tok_base_q;
+  if (kv_len <= 0 || pos_base + toks_here - 1 < 0) {  // padding rows of a graph bucket attend to nothing
+    for (int idx = threadIdx.x; idx < toks_here * G * CH; idx += 256) {
+      const int r = idx / CH, ch = idx % CH;
+      *reinterpret_cast<uint4*>(p.out + ((long long)(q0 + tok_base_q + r / G) * p.hq + hk * G + r % G) * D + ch * 8) = make_uint4(0, 0, 0, 0);
+    }
+    return;
+  }
+
+  // stage the Q tile [32][D] (row r = token r / G, head hk G + r % G), then the warp's A fragments of its slice
+  for (int c = threadIdx.x; c < WIDE_ROWS * CH; c += 256) {
+    const int r = c / CH, ch = c % CH;
+    const bool valid = r / G < toks_here;
+    const bf16* src = p.q + ((long long)(q0 + tok_base_q + (valid ? r / G : 0)) * p.hq + hk * G + r % G) * D + ch * 8;
+    cp_async16(sm + swz<D>(r, ch), src, valid);
+  }
+  cp_async_commit();
+  cp_async_wait<0>();
+  __syncthreads();
+  uint32_t qf[KS][4];
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks) {
+    const int j = lane >> 3, r = lane & 7;
+    const int row = rt * 16 + (j & 1) * 8 + r;
+    const int ch = warp * (SL / 8) + ks * 2 + (j >> 1);
+    ldsm_x4(smem_u32(sm + swz<D>(row, ch)), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+  }
+  __syncthreads();
+
+  float o[NT][4];
+#pragma unroll
+  for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float m_run[2] = {NEG_BIG, NEG_BIG}, l_run[2] = {0.f, 0.f};
+
+  const int max_pos = pos_base + toks_here - 1;
+  int kv_start = 0;
+  if (p.window > 0) kv_start = max(0, pos_base - p.window + 1) / BKV * BKV;
+  const int kv_end = min(kv_len, max_pos + 1);
+  const int n_kv_tiles = (kv_end - kv_start + BKV - 1) / BKV;
+
+  constexpr int RPT = BKV * CH / 256, RSTEP = 256 / CH;
+  const long long row_stride = (long long)p.hkv * D;
+  const long long v_plane = (long long)p.page_size * row_stride;
+  const int my_ch = threadIdx.x % CH, my_r0 = threadIdx.x / CH;
+  const bf16* kv_head = p.kv + (long long)hk * D + my_ch * 8;
+  auto issue = [&](int kt, int stage) {
+    bf16* ks_ = sm + stage * 2 * TILE_ELEMS;
+    bf16* vs_ = ks_ + TILE_ELEMS;
+    if (kt < n_kv_tiles) {
+      const int tok_base = kv_start + kt * BKV;
+#pragma unroll 4
+      for (int i = 0; i < RPT; ++i) {
+        const int r = my_r0 + i * RSTEP;
+        const bool valid = tok_base + r < kv_end;
+        const int tok = valid ? tok_base + r : kv_start;
+        int page = table_row[tok / p.page_size];
+        if (page < 0 || page >= p.num_pages) {
+          atomicCAS(p.status, PG_ST_OK, PG_ST_BOUNDS | (47u << 8));
+          page = 0;
+        }
+        const bf16* src = kv_head + ((long long)page * 2 * p.page_size + tok % p.page_size) * row_stride;
+        cp_async16(ks_ + swz<D>(r, my_ch), src, valid);
+        cp_async16(vs_ + swz<D>(r, my_ch), src + v_plane, valid);
+      }
+    }
+    cp_async_commit();
+  };
+
+  issue(0, 0);
+  const float scale_log2 = p.scale * 1.4426950408889634f;
+  for (int kt = 0; kt < n_kv_tiles; ++kt) {
+    issue(kt + 1, (kt + 1) & 1);
+    cp_async_wait<1>();
+    __syncthreads();
+    const bf16* ks_ = sm + (kt & 1) * 2 * TILE_ELEMS;
+    const bf16* vs_ = ks_ + TILE_ELEMS;
+    const int tok_base = kv_start + kt * BKV;
+    float s_acc[BKV / 8][4];
+#pragma unroll
+    for (int n = 0; n < BKV / 8; ++n) s_acc[n][0] = s_acc[n][1] = s_acc[n][2] = s_acc[n][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+      for (int n2 = 0; n2 < BKV / 16; ++n2) {
+        const int j = lane >> 3, r = lane & 7;
+        const int row = n2 * 16 + (j >> 1) * 8 + r;
+        const int ch = warp * (SL / 8) + ks * 2 + (j & 1);
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4(smem_u32(ks_ + swz<D>(row, ch)), b0, b1, b2, b3);
+        mma16816(s_acc[2 * n2], qf[ks], b0, b1);
+        mma16816(s_acc[2 * n2 + 1], qf[ks], b2, b3);
+      }
+    }
+    // sum the four warps' partial scores (each over its 128 columns of the head)
+#pragma unroll
+    for (int n = 0; n < BKV / 8; ++n)
+      *reinterpret_cast<float4*>(s_part + ((warp_id * (BKV / 8) + n) * 32 + lane) * 4) = make_float4(s_acc[n][0], s_acc[n][1], s_acc[n][2], s_acc[n][3]);
+    __syncthreads();
+#pragma unroll
+    for (int n = 0; n < BKV / 8; ++n) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float4 v = *reinterpret_cast<const float4*>(s_part + (((rt * 4 + w) * (BKV / 8) + n) * 32 + lane) * 4);
+        acc.x += v.x;
+        acc.y += v.y;
+        acc.z += v.z;
+        acc.w += v.w;
+      }
+      s_acc[n][0] = acc.x;
+      s_acc[n][1] = acc.y;
+      s_acc[n][2] = acc.z;
+      s_acc[n][3] = acc.w;
+    }
+    float mx[2] = {NEG_BIG, NEG_BIG};
+#pragma unroll
+    for (int n = 0; n < BKV / 8; ++n) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int tok = tok_base + n * 8 + 2 * t4 + (e & 1);
+        const int tq = (rt * 16 + g + (e >> 1) * 8) / G;
+        const int qp = pos_base + tq;
+        bool ok = tq < toks_here && tok <= qp && tok < kv_end;
+        if (p.window > 0) ok = ok && tok > qp - p.window;
+        const float v = ok ? s_acc[n][e] * scale_log2 : NEG_BIG;
+        s_acc[n][e] = v;
+        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+      }
+    }
+    float corr[2];
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+      mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 1));
+      mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 2));
+      const float m_new = fmaxf(m_run[rr], mx[rr]);
+      corr[rr] = exp2f(m_run[rr] - m_new);
+      m_run[rr] = m_new;
+    }
+    float ps[2] = {0.f, 0.f};
+    uint32_t pa[BKV / 16][4];
+#pragma unroll
+    for (int n = 0; n < BKV / 8; ++n) {
+      float pvv[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        pvv[e] = s_acc[n][e] <= NEG_BIG ? 0.f : exp2f(s_acc[n][e] - m_run[e >> 1]);
+        ps[e >> 1] += pvv[e];
+      }
+      pa[n >> 1][(n & 1) * 2 + 0] = pack_bf16(pvv[0], pvv[1]);
+      pa[n >> 1][(n & 1) * 2 + 1] = pack_bf16(pvv[2], pvv[3]);
+    }
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+      ps[rr] += __shfl_xor_sync(0xffffffffu, ps[rr], 1);
+      ps[rr] += __shfl_xor_sync(0xffffffffu, ps[rr], 2);
+      l_run[rr] = l_run[rr] * corr[rr] + ps[rr];
+    }
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      o[n][0] *= corr[0];
+      o[n][1] *= corr[0];
+      o[n][2] *= corr[1];
+      o[n][3] *= corr[1];
+    }
+#pragma unroll
+    for (int kk = 0; kk < BKV / 16; ++kk) {
+#pragma unroll
+      for (int n2 = 0; n2 < NT / 2; ++n2) {
+        const int j = lane >> 3, r = lane & 7;
+        const int row = kk * 16 + (j & 1) * 8 + r;
+        const int ch = warp * (SL / 8) + n2 * 2 + (j >> 1);
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4_t(smem_u32(vs_ + swz<D>(row, ch)), b0, b1, b2, b3);
+        mma16816(o[2 * n2], pa[kk], b0, b1);
+        mma16816(o[2 * n2 + 1], pa[kk], b2, b3);
+      }
+    }
+    __syncthreads();  // the tile and the partial-score buffer are free again
+  }
+  cp_async_wait<0>();
+
+#pragma unroll
+  for (int rr = 0; rr < 2; ++rr) {
+    const int r = rt * 16 + g + rr * 8;
+    const int tq = r / G;
+    if (tq < toks_here) {
+      const float inv = l_run[rr] > 0.f ? 1.f / l_run[rr] : 0.f;
+      bf16* dst = p.out + ((long long)(q0 + tok_base_q + tq) * p.hq + hk * G + r % G) * D + warp * SL;
+#pragma unroll
+      for (int n = 0; n < NT; ++n) *reinterpret_cast<uint32_t*>(dst + n * 8 + 2 * t4) = pack_bf16(o[n][rr * 2] * inv, o[n][rr * 2 + 1] * inv);
+    }
+  }
+}
+
 }  // namespace
 
 // q [T, hq, dim] bf16, kv_layer [pages, 2, page_size, hkv, dim], out [T, hq * dim]; `unit_seq[t]` = sequence of row t.
+// `q_tiles` = sum over the sequences of ceil(query rows / (32 / (hq / hkv))) selects the tensor-core kernel (hq / hkv a
+// divisor of 32); 0 selects the CUDA-core kernel.
 extern "C" int pg_attention_wide(const void* q, const void* kv_layer, void* out, const void* unit_seq, const void* q_indptr, const void* kv_lens, const void* table,
-                                 int table_stride, int tokens, int hq, int hkv, int dim, int page_size, long long num_pages, float scale, int window, void* status,
-                                 cudaStream_t stream) {
+                                 int table_stride, int tokens, int num_seqs, int q_tiles, int hq, int hkv, int dim, int page_size, long long num_pages, float scale, int window,
+                                 void* status, cudaStream_t stream) {
   PG_REQUIRE(dim == 512, "wide attention is built for head dim 512 (got %d)", dim);
   PG_REQUIRE(hq % hkv == 0 && hq / hkv >= 1 && hq / hkv <= 8, "wide attention: %d query heads per KV head (1 .. 8)", hkv ? hq / hkv : 0);
   if (tokens == 0) return PG_OK;
@@ -160,6 +437,18 @@ extern "C" int pg_attention_wide(const void* q, const void* kv_layer, void* out,
   p.num_pages = num_pages;
   p.scale = scale;
   p.status = (uint32_t*)status;
+  const int group = hq / hkv;
+  if (q_tiles > 0 && WIDE_ROWS % group == 0) {
+    const size_t smem_mma = (size_t)2 * 2 * 32 * 512 * 2 + (size_t)8 * 4 * 32 * 4 * 4;
+    static bool attr_done = false;
+    if (!attr_done) {
+      PG_CUDA(cudaFuncSetAttribute(attn_wide_mma_kernel<512>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_mma));
+      attr_done = true;
+    }
+    PG_CUDA(launch_pdl(attn_wide_mma_kernel<512>, dim3((unsigned)q_tiles, (unsigned)hkv), dim3(256), smem_mma, stream, p, num_seqs));
+    PG_LAUNCH_CHECK();
+    return PG_OK;
+  }
   const size_t smem = 2 * (size_t)TK * 512 * 2;
   PG_CUDA(launch_pdl(attn_wide_kernel<512>, dim3((unsigned)tokens, (unsigned)hkv), dim3((unsigned)(32 * (hq / hkv))), smem, stream, p));
   PG_LAUNCH_CHECK();

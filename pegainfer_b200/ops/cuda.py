@@ -528,6 +528,7 @@ def qk_norm_rope_append(qkv, q_norm_w, k_norm_w, cos, sin, meta: AttnMeta, kv_la
 
 _BATCH_INVARIANT = False
 INVARIANT_KV_SPLITS = 4
+_WIDE_MMA = os.environ.get("PEGAINFER_WIDE_MMA", "1") != "0"  # head dim 512 on the mma.sync kernel (0: the CUDA-core kernel)
 _PREFILL_TC = os.environ.get("PEGAINFER_PREFILL_TC", "1") != "0"  # tcgen05 prefill attention for head dims 128 and 256
 _PREFILL_TC_MIN_ROWS = int(os.environ.get("PEGAINFER_PREFILL_TC_MIN_ROWS", "64"))  # shorter chunks keep the 64-row mma.sync tiles
 # the tcgen05 kernel wins from a few hundred keys on (head dim 128, against the mma.sync kernel: 1.0x at 256 keys, 1.3x at 512,
@@ -583,9 +584,18 @@ def paged_attention(q, kv_layer, meta: AttnMeta, scale=None, window=0, out: Opti
     if d == 512:
         # wide heads (global layers of the Gemma 4 line): one block per (query row, KV head), csrc/attention_wide.cu
         assert q.is_contiguous() and kv_layer.is_contiguous()
+        group = hq // hkv
+        q_tiles = 0
+        if _WIDE_MMA and 32 % group == 0:  # tensor-core kernel: 32 / group query tokens of a sequence x the group's heads per block
+            tpt = 32 // group
+            if meta.decode_only:
+                q_tiles = meta.num_seqs
+            else:
+                qh = meta.h_q_indptr if meta.h_q_indptr is not None else meta.q_indptr.tolist()
+                q_tiles = sum((qh[b + 1] - qh[b] + tpt - 1) // tpt for b in range(meta.num_seqs))
         rc = lib().pg_attention_wide(_ptr(q), _ptr(kv_layer), _ptr(out), _ptr(_unit_seq(meta, q.device)), _ptr(meta.q_indptr), _ptr(meta.kv_lens), _ptr(table),
-                                     _ci(table.stride(0)), _ci(t), _ci(hq), _ci(hkv), _ci(d), _ci(page_size), _ll(kv_layer.shape[0]), _cf(scale), _ci(window), _ptr(c.status),
-                                     _stream())
+                                     _ci(table.stride(0)), _ci(t), _ci(meta.num_seqs), _ci(q_tiles), _ci(hq), _ci(hkv), _ci(d), _ci(page_size), _ll(kv_layer.shape[0]), _cf(scale),
+                                     _ci(window), _ptr(c.status), _stream())
         _check(rc, c)
         return out
 
