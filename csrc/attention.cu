@@ -77,6 +77,7 @@ struct AttnParams {
   float* part_lse;  // [B, Hq, splits]
   long long num_pages;
   uint32_t* status;
+  int window;  // decode: a row sees its last `window` keys only (0: all of them)
 };
 
 // Row address of token `tok` of sequence b, kv head h (kvsel 0 = K, 1 = V).
@@ -116,10 +117,12 @@ __global__ void __launch_bounds__(128, (STAGES == 2 && D <= 128) ? 3 : 1) decode
   const int* table_row = p.table + (long long)b * p.table_stride;
   bf16* wsm = reinterpret_cast<bf16*>(smem_raw) + warp * STAGES * STAGE_ELEMS;
 
-  const int n_tiles = (kv_len + TILE - 1) / TILE;
+  const int kv_lo = p.window > 0 ? max(0, kv_len - p.window) : 0;  // first key the row (position kv_len - 1) may see
+  const int first_tile = kv_lo / TILE;
+  const int n_tiles = (kv_len + TILE - 1) / TILE - first_tile;
   const int tps = (n_tiles + p.splits - 1) / p.splits;
-  const int t_begin = split * tps;
-  const int t_end = min(n_tiles, t_begin + tps);
+  const int t_begin = first_tile + split * tps;
+  const int t_end = min(first_tile + n_tiles, t_begin + tps);
 
   // Q fragments: rows 0..G-1 of the A operand are the group's heads, the rest zero.
   uint32_t qf[KS][2];
@@ -195,10 +198,10 @@ __global__ void __launch_bounds__(128, (STAGES == 2 && D <= 128) ? 3 : 1) decode
     // online softmax for row g (rows g+8 are padding)
     float sv[4];
     const int tok0 = tile * TILE + 2 * t4;
-    sv[0] = (tok0 < kv_len) ? s_acc[0][0] * p.scale_log2 : NEG_BIG;
-    sv[1] = (tok0 + 1 < kv_len) ? s_acc[0][1] * p.scale_log2 : NEG_BIG;
-    sv[2] = (tok0 + 8 < kv_len) ? s_acc[1][0] * p.scale_log2 : NEG_BIG;
-    sv[3] = (tok0 + 9 < kv_len) ? s_acc[1][1] * p.scale_log2 : NEG_BIG;
+    sv[0] = (tok0 < kv_len && tok0 >= kv_lo) ? s_acc[0][0] * p.scale_log2 : NEG_BIG;
+    sv[1] = (tok0 + 1 < kv_len && tok0 + 1 >= kv_lo) ? s_acc[0][1] * p.scale_log2 : NEG_BIG;
+    sv[2] = (tok0 + 8 < kv_len && tok0 + 8 >= kv_lo) ? s_acc[1][0] * p.scale_log2 : NEG_BIG;
+    sv[3] = (tok0 + 9 < kv_len && tok0 + 9 >= kv_lo) ? s_acc[1][1] * p.scale_log2 : NEG_BIG;
     float mx = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
@@ -283,7 +286,7 @@ __global__ void __launch_bounds__(128, (STAGES == 2 && D <= 128) ? 3 : 1) decode
 // scratch is separate from the pipeline buffers, because loads of the next unit are in
 // flight while the four warps of a CTA combine their partials of the current one.
 struct DecodeUnit {
-  int b, h, split, kv_len, qrow, t_begin, t_end;
+  int b, h, split, kv_len, kv_lo, qrow, t_begin, t_end;
   const int* table_row;
 };
 
@@ -295,10 +298,12 @@ __device__ __forceinline__ bool load_decode_unit(const AttnParams& p, int u, Dec
   o.kv_len = p.kv_lens[o.b];
   o.qrow = p.q_indptr[o.b];
   o.table_row = p.table + (long long)o.b * p.table_stride;
-  const int n_tiles = (o.kv_len + 15) / 16;
+  o.kv_lo = p.window > 0 ? max(0, o.kv_len - p.window) : 0;  // first key the row (position kv_len - 1) may see
+  const int first_tile = o.kv_lo / 16;
+  const int n_tiles = (o.kv_len + 15) / 16 - first_tile;
   const int tps = (n_tiles + p.splits - 1) / p.splits;
-  o.t_begin = o.split * tps;
-  o.t_end = min(n_tiles, o.t_begin + tps);
+  o.t_begin = first_tile + o.split * tps;
+  o.t_end = min(first_tile + n_tiles, o.t_begin + tps);
   return true;
 }
 
@@ -403,10 +408,10 @@ __global__ void __launch_bounds__(128, D <= 128 ? 2 : 1) decode_attn_persistent_
       }
       float sv[4];
       const int tok0 = tile * TILE + 2 * t4;
-      sv[0] = (tok0 < uc.kv_len) ? s_acc[0][0] * p.scale_log2 : NEG_BIG;
-      sv[1] = (tok0 + 1 < uc.kv_len) ? s_acc[0][1] * p.scale_log2 : NEG_BIG;
-      sv[2] = (tok0 + 8 < uc.kv_len) ? s_acc[1][0] * p.scale_log2 : NEG_BIG;
-      sv[3] = (tok0 + 9 < uc.kv_len) ? s_acc[1][1] * p.scale_log2 : NEG_BIG;
+      sv[0] = (tok0 < uc.kv_len && tok0 >= uc.kv_lo) ? s_acc[0][0] * p.scale_log2 : NEG_BIG;
+      sv[1] = (tok0 + 1 < uc.kv_len && tok0 + 1 >= uc.kv_lo) ? s_acc[0][1] * p.scale_log2 : NEG_BIG;
+      sv[2] = (tok0 + 8 < uc.kv_len && tok0 + 8 >= uc.kv_lo) ? s_acc[1][0] * p.scale_log2 : NEG_BIG;
+      sv[3] = (tok0 + 9 < uc.kv_len && tok0 + 9 >= uc.kv_lo) ? s_acc[1][1] * p.scale_log2 : NEG_BIG;
       float mx = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
@@ -878,6 +883,7 @@ extern "C" int pg_paged_attention(const void* q, const void* kv, void* out, cons
   p.part_lse = (float*)part_lse;
   p.num_pages = num_pages;
   p.status = (uint32_t*)status;
+  p.window = mode == 0 ? window : 0;
   if (mode == 0) {
     PG_REQUIRE(p.splits == 1 || (part_o && part_lse), "paged_attention: split-KV decode needs partial buffers");
     if (dim == 64) return launch_decode<64>(p, stream);

@@ -189,6 +189,10 @@ PRESETS["tiny-gemma4"] = ModelConfig(family="gemma4", vocab_size=1024, hidden_si
 # head dims of the released dense model (256 sliding, 512 global, 5 : 1), two global KV heads of 512 as wide as four local ones of 256
 PRESETS["small-gemma4"] = replace(PRESETS["tiny-gemma4"], vocab_size=4096, hidden_size=1024, num_q_heads=8, num_kv_heads=4, head_dim=256, global_head_dim=512, num_global_kv_heads=2,
                                   intermediate_size=2048, sliding_window=128, max_position=8192)
+# a 10 B-parameter shape of the line for benchmarks (not a released configuration): 30 sliding + 6 global layers, 16 local
+# KV heads of 256 against 4 global KV heads of 512 (the narrower global layers pack their pages at the front of their slab)
+PRESETS["gemma4-10b-shape"] = replace(PRESETS["small-gemma4"], vocab_size=262144, hidden_size=4096, num_layers=36, layer_types=_gemma_pattern(36), num_q_heads=32, num_kv_heads=16,
+                                      num_global_kv_heads=4, intermediate_size=14336, sliding_window=1024, max_position=131072)
 PRESETS["small-glm-fp8"] = replace(PRESETS["small-glm"], expert_quant="fp8_block128", dense_quant="fp8_block128")
 for _name in ("tiny-dsv2", "small-dsv2", "dsv2-lite"):
     if _name in PRESETS:

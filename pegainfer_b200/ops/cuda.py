@@ -610,30 +610,24 @@ def paged_attention(q, kv_layer, meta: AttnMeta, scale=None, window=0, out: Opti
         rc = lib().pg_paged_attention(
             _ptr(q), _ptr(kv_layer), _ptr(out), _ptr(meta.q_indptr[first:]), _ptr(meta.kv_lens[first:]), _ptr(table[first:]), _ci(table.stride(0)), _ci(n),
             _ci(hq), _ci(hkv), _ci(d), _ci(page_size), _ll(kv_layer.shape[0]), _cf(scale), _ci(0), _ci(splits), _ptr(c.attn_part), _ptr(c.attn_part[lse_off:]),
-            _ci(0), _ci(0), _ptr(c.status), _stream(),
+            _ci(0), _ci(window), _ptr(c.status), _stream(),
         )
         _check(rc, c, 2 if splits > 1 else 1)
 
-    if meta.decode_only and window == 0:
+    if meta.decode_only:  # with a sliding window the decode kernel walks the last `window` keys of every sequence
         decode_rows(0, meta.num_seqs, meta.plan)
         return out
-    if meta.h_q_indptr is not None:
-        qi = meta.h_q_indptr
-    elif meta.decode_only:  # one row per sequence (a captured decode step has no host copies)
-        qi = list(range(meta.num_seqs + 1))
-    else:
-        qi = meta.q_indptr.tolist()
+    qi = meta.h_q_indptr if meta.h_q_indptr is not None else meta.q_indptr.tolist()
     n_pf = meta.num_seqs
-    if window == 0:
-        # A unified step lists its prompt chunks first and its decode rows last.  Through the prefill
-        # kernel a decode row is a 64-row query tile with one live row per Q head, and 63 of them cost
-        # several times the chunk itself; the trailing single-row sequences take the decode kernel.
-        while n_pf > 0 and qi[n_pf] - qi[n_pf - 1] == 1:
-            n_pf -= 1
-        # batch-invariant serving: a single-row sequence ALWAYS takes the decode kernel (same KV
-        # splits and merge order as in a pure decode step or a graph replay), however few there are
-        if meta.num_seqs - n_pf < (1 if _BATCH_INVARIANT else _MIXED_DECODE_MIN):
-            n_pf = meta.num_seqs
+    # A unified step lists its prompt chunks first and its decode rows last.  Through the prefill
+    # kernel a decode row is a 64-row query tile with one live row per Q head, and 63 of them cost
+    # several times the chunk itself; the trailing single-row sequences take the decode kernel.
+    while n_pf > 0 and qi[n_pf] - qi[n_pf - 1] == 1:
+        n_pf -= 1
+    # batch-invariant serving: a single-row sequence ALWAYS takes the decode kernel (same KV
+    # splits and merge order as in a pure decode step or a graph replay), however few there are
+    if meta.num_seqs - n_pf < (1 if _BATCH_INVARIANT else _MIXED_DECODE_MIN):
+        n_pf = meta.num_seqs
     # (not under the batch-invariant policy: which kernel runs would depend on the other sequences of the step)
     if (n_pf > 0 and d in (128, 256) and window == 0 and _PREFILL_TC and not _BATCH_INVARIANT and (128 if d == 128 else 64) % page_size == 0 and q.is_contiguous() and max(qi[b + 1] - qi[b] for b in range(n_pf)) >= _PREFILL_TC_MIN_ROWS
             and (meta.h_kv_lens is None or max(meta.h_kv_lens[:n_pf]) >= _PREFILL_TC_MIN_KV)):

@@ -212,6 +212,12 @@ def test_decode_attention(d, hq, hkv, page):
         out = cu().paged_attention(q, kv, meta)
         bf16_close(out, ref, rel=2 ** -6, abs_=6e-3)
         assert out[len(kv_lens):].abs().max().item() == 0  # padding rows are inert
+    # sliding window: the decode kernel walks only the last `window` keys (split over the same partial buffers)
+    for window in (48, 200):
+        refw = R.paged_attention(q, kv, meta, None, window)
+        for splits in (1, 3, None):
+            meta.plan = splits
+            bf16_close(cu().paged_attention(q, kv, meta, None, window), refw, rel=2 ** -6, abs_=6e-3)
     status_clean()
 
 
