@@ -255,6 +255,10 @@ def test_unified_step_attention_splits_chunks_and_decode_rows(d, hq, hkv, page):
         while trailing < len(q_lens) and q_lens[len(q_lens) - 1 - trailing] == 1:
             trailing += 1
         assert (launches >= 2) == (trailing >= 4), (q_lens, launches)
+        # the same step under a sliding window: chunks through the windowed prefill kernel, decode rows through the
+        # windowed decode kernel
+        refw = R.paged_attention(q, kv, meta, None, 100)
+        bf16_close(cu().paged_attention(q, kv, meta, None, 100), refw, rel=2 ** -6, abs_=6e-3)
     status_clean()
 
 
