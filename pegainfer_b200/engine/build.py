@@ -124,6 +124,8 @@ def build_engine(ecfg: EngineConfig, mcfg: Optional[ModelConfig] = None, device=
     )
     host_tier = None
     if ecfg.kv_offload:
+        if not getattr(model, "supports_prefix_cache", True):
+            raise ValueError("KV offload needs whole pages per layer slab: this model's layers have different KV row widths (or keep recurrent state)")
         from ..kv.host_tier import HostTier
 
         host_tier = HostTier(kv, pool, int(ecfg.kv_offload_host_gib * (1 << 30)), l1_retention_disabled=ecfg.kv_offload_l1_disabled,

@@ -116,7 +116,7 @@ class Gemma4Layer:
 
 class Gemma4Model:
     family = "gemma4"
-    allows_prefix_cache = True
+    supports_prefix_cache = True
 
     def __init__(self, cfg: ModelConfig, source: Optional[WeightSource] = None, device="cpu", dtype=torch.bfloat16, tp: TPContext = SINGLE, seed: int = 0):
         if tp.world != 1:
@@ -135,7 +135,7 @@ class Gemma4Model:
         self.kv_width = max(widths)
         # one width for all layers: a layer's slab is exactly its pages; otherwise narrower layers pack their pages at
         # the front of the slab and block-wise copies (prefix cache, KV offload) do not see whole pages
-        self.allows_prefix_cache = len(widths) == 1
+        self.supports_prefix_cache = len(widths) == 1
 
     def _load(self, src: WeightSource) -> None:
         cfg, dev, dt = self.cfg, self.device, self.dtype

@@ -247,7 +247,7 @@ def test_gemma4_sliding_and_global_layers_chunking_invariance():
 
     m = Gemma4Model(preset("tiny-gemma4"), device="cpu", dtype=torch.float32)
     assert [l.head_dim for l in m.layers] == [64] * 5 + [128] and [l.kv_heads for l in m.layers] == [2] * 5 + [1]
-    assert m.kv_geometry() == dict(num_layers=6, kv_heads=1, head_dim=128) and m.allows_prefix_cache  # 2 x 64 == 1 x 128
+    assert m.kv_geometry() == dict(num_layers=6, kv_heads=1, head_dim=128) and m.supports_prefix_cache  # 2 x 64 == 1 x 128
     assert torch.equal(m.layers[5].qkv[4 * 128 : 5 * 128], m.layers[5].qkv[5 * 128 :])  # V rows are the K rows
     cos, sin = proportional_rope_tables(64, 128, 0.25, 1e6, torch.float32, "cpu")
     assert cos.shape == (64, 64) and torch.all(cos[:, 16:] == 1) and torch.all(sin[:, 16:] == 0) and sin[5, 0] != 0
