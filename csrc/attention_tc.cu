@@ -48,6 +48,7 @@ struct TcAttnParams {
   int table_stride, num_seqs, hq, hkv, page_size;
   long long num_pages;
   float scale_log2;       // softmax scale * log2(e)
+  int window;             // head dim 256 only: a row sees its last `window` keys (0: all of them)
   int mn_lbo_first;       // descriptor variant of the MN-major operand (1: LBO = stride between 64-column blocks)
   uint32_t* status;
 };
@@ -472,7 +473,7 @@ constexpr int THREADS2 = 64 + 128;
 // maximum -> lazy rescale of O (`o_cols` columns at `o_row`) -> P as bf16 over the first 32 columns of S -> `p_ready`.
 // `o_full` / `o_parity` name the completion of the previous product into the same O (ignored for j == 0).
 template <bool MASK>
-__device__ __forceinline__ bool softmax_tile64(uint64_t* s_full, uint32_t s_parity, uint32_t s_row, uint32_t o_row, int o_cols, uint64_t* o_full, uint32_t o_parity, int j, int limit,
+__device__ __forceinline__ bool softmax_tile64(uint64_t* s_full, uint32_t s_parity, uint32_t s_row, uint32_t o_row, int o_cols, uint64_t* o_full, uint32_t o_parity, int j, int limit, int lo,
                                                float scale_log2, float& m, float& l, uint64_t* p_ready, int lane, volatile int* abort_flag) {
   if (!mbar_wait(s_full, s_parity, abort_flag)) return false;
   tc_fence_after();
@@ -485,7 +486,7 @@ __device__ __forceinline__ bool softmax_tile64(uint64_t* s_full, uint32_t s_pari
     mx_raw = -INFINITY;
 #pragma unroll
     for (int i = 0; i < BKV2; ++i)
-      if (i <= limit) mx_raw = fmaxf(mx_raw, __uint_as_float(v[i]));
+      if (i <= limit && i > lo) mx_raw = fmaxf(mx_raw, __uint_as_float(v[i]));
   } else {
     float m0 = max3(__uint_as_float(v[0]), __uint_as_float(v[1]), __uint_as_float(v[2]));
     float m1 = max3(__uint_as_float(v[3]), __uint_as_float(v[4]), __uint_as_float(v[5]));
@@ -545,10 +546,10 @@ __device__ __forceinline__ bool softmax_tile64(uint64_t* s_full, uint32_t s_pari
       float2 e = make_float2(ex2_approx(t2.x), ex2_approx(t2.y));
       float2 f = make_float2(ex2_approx(t3.x), ex2_approx(t3.y));
       if constexpr (MASK) {
-        if (c + i > limit) e.x = 0.f;
-        if (c + i + 1 > limit) e.y = 0.f;
-        if (c + i + 2 > limit) f.x = 0.f;
-        if (c + i + 3 > limit) f.y = 0.f;
+        if (c + i > limit || c + i <= lo) e.x = 0.f;
+        if (c + i + 1 > limit || c + i + 1 <= lo) e.y = 0.f;
+        if (c + i + 2 > limit || c + i + 2 <= lo) f.x = 0.f;
+        if (c + i + 3 > limit || c + i + 3 <= lo) f.y = 0.f;
       }
       sum2 = __fadd2_rn(sum2, e);
       sum3 = __fadd2_rn(sum3, f);
@@ -631,7 +632,10 @@ __global__ void __launch_bounds__(THREADS2, 1) prefill_attn_tc256_kernel(const _
   const int row_base = tile_in_seq * BQ1;
   const int rows_here = min(BQ1, q_len - row_base);
   const int pos0 = kv_len - q_len + row_base;  // position of the tile's first row
-  const int n_tiles = (rows_here > 0 && kv_len > 0) ? min(pos0 + rows_here - 1, kv_len - 1) / BKV2 + 1 : 0;
+  // key tiles j0 .. last the rows of this tile can see (a sliding window drops the tiles in front of the first row's
+  // window); the loops below count tiles from j0
+  const int j0 = (p.window > 0 && rows_here > 0) ? max(0, pos0 - p.window + 1) / BKV2 : 0;
+  const int n_tiles = (rows_here > 0 && kv_len > 0) ? min(pos0 + rows_here - 1, kv_len - 1) / BKV2 + 1 - j0 : 0;
   const int* table_row = p.table + (long long)b * p.table_stride;
 
   if (warp == 0) {
@@ -660,12 +664,12 @@ __global__ void __launch_bounds__(THREADS2, 1) prefill_attn_tc256_kernel(const _
         }
         return page;
       };
-      int nxt0 = page_of(0, sub), nxt1 = page_of(0, sub + 16);
+      int nxt0 = page_of(j0, sub), nxt1 = page_of(j0, sub + 16);
       for (int j = 0; j < n_tiles; ++j) {
         const int pg0 = nxt0, pg1 = nxt1;
         if (j + 1 < n_tiles) {
-          nxt0 = page_of(j + 1, sub);
-          nxt1 = page_of(j + 1, sub + 16);
+          nxt0 = page_of(j0 + j + 1, sub);
+          nxt1 = page_of(j0 + j + 1, sub + 16);
         }
         const int st = j & 1;
         if (j >= 2) {
@@ -735,13 +739,17 @@ __global__ void __launch_bounds__(THREADS2, 1) prefill_attn_tc256_kernel(const _
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
-      const bool need_mask = j * BKV2 + BKV2 - 1 > min(pos0, kv_len - 1);
+      const int key0 = (j0 + j) * BKV2;
+      // a tile needs the mask when the causal edge or the end of the keys crosses it, or (sliding window) when its first
+      // key lies in front of the window of the tile's last row
+      const bool need_mask = key0 + BKV2 - 1 > min(pos0, kv_len - 1) || (p.window > 0 && key0 <= pos0 + BQ1 - 1 - p.window);
       const int st = j & 1;
       const uint32_t s_row = lane_base + 256u + (uint32_t)(st * BKV2);
-      const int limit = min(my_pos, kv_len - 1) - j * BKV2;  // columns 0 .. limit are visible to this row
+      const int limit = min(my_pos, kv_len - 1) - key0;                          // columns lo + 1 .. limit are visible to this row
+      const int lo = p.window > 0 ? my_pos - p.window - key0 : -(1 << 30);
       const uint32_t sp = (uint32_t)((j >> 1) & 1), op = (uint32_t)((j - 1) & 1);
-      ok = need_mask ? softmax_tile64<true>(&sh->s_full[st], sp, s_row, o_row, D2, &sh->o_full, op, j, limit, p.scale_log2, m, l, &sh->p_ready[st], lane, abort_flag)
-                     : softmax_tile64<false>(&sh->s_full[st], sp, s_row, o_row, D2, &sh->o_full, op, j, limit, p.scale_log2, m, l, &sh->p_ready[st], lane, abort_flag);
+      ok = need_mask ? softmax_tile64<true>(&sh->s_full[st], sp, s_row, o_row, D2, &sh->o_full, op, j, limit, lo, p.scale_log2, m, l, &sh->p_ready[st], lane, abort_flag)
+                     : softmax_tile64<false>(&sh->s_full[st], sp, s_row, o_row, D2, &sh->o_full, op, j, limit, lo, p.scale_log2, m, l, &sh->p_ready[st], lane, abort_flag);
     }
     if (ok && n_tiles > 0) {
       ok = mbar_wait(&sh->o_full, (uint32_t)((n_tiles - 1) & 1), abort_flag);
@@ -969,8 +977,8 @@ __global__ void __launch_bounds__(THREADS, 1) mla_prefill_tc_kernel(const __grid
       const bool need_mask = j * BKV2 + BKV2 - 1 > min(pos0, kv_len - 1);
       const int limit = min(my_pos, kv_len - 1) - j * BKV2;
       const uint32_t sp = (uint32_t)(j & 1), op = (uint32_t)((j - 1) & 1);
-      ok = need_mask ? softmax_tile64<true>(&sh->s_full[g], sp, s_row, o_row, 128, &sh->o_full[g], op, j, limit, p.scale_log2, m, l, &sh->p_ready[g], lane, abort_flag)
-                     : softmax_tile64<false>(&sh->s_full[g], sp, s_row, o_row, 128, &sh->o_full[g], op, j, limit, p.scale_log2, m, l, &sh->p_ready[g], lane, abort_flag);
+      ok = need_mask ? softmax_tile64<true>(&sh->s_full[g], sp, s_row, o_row, 128, &sh->o_full[g], op, j, limit, -(1 << 30), p.scale_log2, m, l, &sh->p_ready[g], lane, abort_flag)
+                     : softmax_tile64<false>(&sh->s_full[g], sp, s_row, o_row, 128, &sh->o_full[g], op, j, limit, -(1 << 30), p.scale_log2, m, l, &sh->p_ready[g], lane, abort_flag);
     }
     const int rows_g = min(128, rows_here - g * 128);
     if (ok && my_n > 0) {
@@ -1078,8 +1086,9 @@ extern "C" void pg_prefill_attention_tc_variant(int v) { g_mn_variant = v; }
 // q [T, hq, d] bf16 (contiguous), kv_layer [pages, 2, page_size, hkv, d], out [T, hq * d], d = 128 or 256.  `q_tiles` = sum
 // over the sequences of ceil(query rows / 256) for d = 128 and of ceil(query rows / 128) for d = 256.
 extern "C" int pg_prefill_attention_tc(const void* q, const void* kv_layer, void* out, const void* q_indptr, const void* kv_lens, const void* table, int table_stride,
-                                       int num_seqs, int tokens, int hq, int hkv, int dim, int page_size, long long num_pages, float scale, int q_tiles, void* status,
-                                       cudaStream_t stream) {
+                                       int num_seqs, int tokens, int hq, int hkv, int dim, int page_size, long long num_pages, float scale, int q_tiles, int window,
+                                       void* status, cudaStream_t stream) {
+  PG_REQUIRE(window == 0 || dim == D2, "tcgen05 prefill attention: a sliding window is built for head dim 256 only");
   PG_REQUIRE(dim == D || dim == D2, "tcgen05 prefill attention is built for head dims 128 and 256 (got %d)", dim);
   const int key_tile = dim == D ? BKV : BKV2;
   PG_REQUIRE(page_size >= 8 && page_size <= key_tile && key_tile % page_size == 0, "page size %d does not tile %d keys", page_size, key_tile);
@@ -1103,6 +1112,7 @@ extern "C" int pg_prefill_attention_tc(const void* q, const void* kv_layer, void
   p.page_size = page_size;
   p.num_pages = num_pages;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.window = window;
   p.mn_lbo_first = g_mn_variant < 0 ? 1 : g_mn_variant;
   p.status = (uint32_t*)status;
   if (dim == D2) {

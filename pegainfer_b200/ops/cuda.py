@@ -614,6 +614,8 @@ def paged_attention(q, kv_layer, meta: AttnMeta, scale=None, window=0, out: Opti
         )
         _check(rc, c, 2 if splits > 1 else 1)
 
+    if window > 0 and meta.h_kv_lens is not None and max(meta.h_kv_lens[: meta.num_seqs], default=0) <= window:
+        window = 0  # no sequence of this step is longer than the window: plain causal attention (and its faster kernels)
     if meta.decode_only:  # with a sliding window the decode kernel walks the last `window` keys of every sequence
         decode_rows(0, meta.num_seqs, meta.plan)
         return out
@@ -629,7 +631,7 @@ def paged_attention(q, kv_layer, meta: AttnMeta, scale=None, window=0, out: Opti
     if meta.num_seqs - n_pf < (1 if _BATCH_INVARIANT else _MIXED_DECODE_MIN):
         n_pf = meta.num_seqs
     # (not under the batch-invariant policy: which kernel runs would depend on the other sequences of the step)
-    if (n_pf > 0 and d in (128, 256) and window == 0 and _PREFILL_TC and not _BATCH_INVARIANT and (128 if d == 128 else 64) % page_size == 0 and q.is_contiguous() and max(qi[b + 1] - qi[b] for b in range(n_pf)) >= _PREFILL_TC_MIN_ROWS
+    if (n_pf > 0 and (d == 256 or (d == 128 and window == 0)) and _PREFILL_TC and not _BATCH_INVARIANT and (128 if d == 128 else 64) % page_size == 0 and q.is_contiguous() and max(qi[b + 1] - qi[b] for b in range(n_pf)) >= _PREFILL_TC_MIN_ROWS
             and (meta.h_kv_lens is None or max(meta.h_kv_lens[:n_pf]) >= _PREFILL_TC_MIN_KV)):
         # tcgen05 kernel: 256 (head dim 128) or 128 (head dim 256) query rows of one head per CTA, S and P V on the
         # tensor cores, accumulators in TMEM
@@ -637,7 +639,7 @@ def paged_attention(q, kv_layer, meta: AttnMeta, scale=None, window=0, out: Opti
         PREFILL_TC_CALLS["hd128" if d == 128 else "hd256"] += 1
         q_tiles = sum((qi[b + 1] - qi[b] + rows_per_cta - 1) // rows_per_cta for b in range(n_pf))
         rc = lib().pg_prefill_attention_tc(_ptr(q), _ptr(kv_layer), _ptr(out), _ptr(meta.q_indptr), _ptr(meta.kv_lens), _ptr(table), _ci(table.stride(0)), _ci(n_pf), _ci(qi[n_pf]),
-                                           _ci(hq), _ci(hkv), _ci(d), _ci(page_size), _ll(kv_layer.shape[0]), _cf(scale), _ci(q_tiles), _ptr(c.status), _stream())
+                                           _ci(hq), _ci(hkv), _ci(d), _ci(page_size), _ll(kv_layer.shape[0]), _cf(scale), _ci(q_tiles), _ci(window), _ptr(c.status), _stream())
         _check(rc, c)
     elif n_pf > 0:
         q_tiles = sum((qi[b + 1] - qi[b] + 63) // 64 for b in range(n_pf))

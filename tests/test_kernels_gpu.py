@@ -937,6 +937,18 @@ def test_tcgen05_prefill_attention_matches_reference(page, d):
         K.set_prefill_tc(prev)
         _native.load().pg_prefill_attention_tc_variant(ctypes.c_int(-1))
     assert errs[1] < 0.03, errs
+    if d == 256:  # sliding window on the head-dim-256 kernel: tiles in front of the window are skipped, the edge tiles masked
+        prev = K.set_prefill_tc(0)
+        try:
+            calls = K.PREFILL_TC_CALLS["hd256"]
+            for window in (100, 64, 300):
+                outw = K.paged_attention(q, kv, meta, None, window).float()
+                refw = R.paged_attention(q, kv, meta, None, window).float()
+                torch.cuda.synchronize()
+                assert (outw - refw).abs().max().item() < 0.03, window
+            assert K.PREFILL_TC_CALLS["hd256"] == calls + 3
+        finally:
+            K.set_prefill_tc(prev)
     status_clean()
 
 
