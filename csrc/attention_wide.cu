@@ -248,6 +248,7 @@ __global__ void __launch_bounds__(256, 1) attn_wide_mma_kernel(const WideParams 
 #pragma unroll
   for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
   float m_run[2] = {NEG_BIG, NEG_BIG}, l_run[2] = {0.f, 0.f};
+  const bool rt_active = (rt * 16) / G < toks_here;
 
   const int max_pos = pos_base + toks_here - 1;
   int kv_start = 0;
@@ -295,6 +296,8 @@ __global__ void __launch_bounds__(256, 1) attn_wide_mma_kernel(const WideParams 
     float s_acc[BKV / 8][4];
 #pragma unroll
     for (int n = 0; n < BKV / 8; ++n) s_acc[n][0] = s_acc[n][1] = s_acc[n][2] = s_acc[n][3] = 0.f;
+    // a row tile without live rows (decode: one token per sequence fills at most the first tile) only copies and waits
+    if (rt_active) {
 #pragma unroll
     for (int ks = 0; ks < KS; ++ks) {
 #pragma unroll
@@ -312,7 +315,9 @@ __global__ void __launch_bounds__(256, 1) attn_wide_mma_kernel(const WideParams 
 #pragma unroll
     for (int n = 0; n < BKV / 8; ++n)
       *reinterpret_cast<float4*>(s_part + ((warp_id * (BKV / 8) + n) * 32 + lane) * 4) = make_float4(s_acc[n][0], s_acc[n][1], s_acc[n][2], s_acc[n][3]);
+    }
     __syncthreads();
+    if (rt_active) {
 #pragma unroll
     for (int n = 0; n < BKV / 8; ++n) {
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -391,6 +396,7 @@ __global__ void __launch_bounds__(256, 1) attn_wide_mma_kernel(const WideParams 
         mma16816(o[2 * n2], pa[kk], b0, b1);
         mma16816(o[2 * n2 + 1], pa[kk], b2, b3);
       }
+    }
     }
     __syncthreads();  // the tile and the partial-score buffer are free again
   }
