@@ -29,6 +29,11 @@ struct WideParams {
   long long num_pages;
   float scale;
   uint32_t* status;
+  // split KV (decode steps of few long sequences): split s of a block's key tiles writes its unnormalised O and (m, l)
+  // per row; attn_wide_merge_kernel combines them
+  int splits;
+  float* part_o;   // [T * hq, splits, D]
+  float* part_ml;  // [T * hq, splits, 2]
 };
 
 template <int D>
@@ -198,7 +203,7 @@ __global__ void __launch_bounds__(256, 1) attn_wide_mma_kernel(const WideParams 
 
   int b = 0, tile_in_seq = 0;
   {
-    int rem = (int)gridDim.x - 1 - (int)blockIdx.x;  // late tiles (most keys) first
+    int rem = (int)(gridDim.x / (unsigned)p.splits) - 1 - (int)(blockIdx.x / (unsigned)p.splits);  // late tiles (most keys) first
     for (; b < num_seqs; ++b) {
       const int n = p.q_indptr[b + 1] - p.q_indptr[b];
       const int nt = (n + TPT - 1) / TPT;
@@ -217,6 +222,14 @@ __global__ void __launch_bounds__(256, 1) attn_wide_mma_kernel(const WideParams 
   const int toks_here = min(TPT, q_len - tok_base_q);
   const int pos_base = kv_len - q_len + tok_base_q;
   if (kv_len <= 0 || pos_base + toks_here - 1 < 0) {  // padding rows of a graph bucket attend to nothing
+    if (p.splits > 1) {  // the merge kernel writes the zeros: every split reports an empty partial
+      for (int r = threadIdx.x; r < toks_here * G; r += 256) {
+        const long long row = (long long)(q0 + tok_base_q + r / G) * p.hq + hk * G + r % G;
+        p.part_ml[(row * p.splits + (int)(blockIdx.x % (unsigned)p.splits)) * 2] = NEG_BIG;
+        p.part_ml[(row * p.splits + (int)(blockIdx.x % (unsigned)p.splits)) * 2 + 1] = 0.f;
+      }
+      return;
+    }
     for (int idx = threadIdx.x; idx < toks_here * G * CH; idx += 256) {
       const int r = idx / CH, ch = idx % CH;
       *reinterpret_cast<uint4*>(p.out + ((long long)(q0 + tok_base_q + r / G) * p.hq + hk * G + r % G) * D + ch * 8) = make_uint4(0, 0, 0, 0);
@@ -254,7 +267,11 @@ __global__ void __launch_bounds__(256, 1) attn_wide_mma_kernel(const WideParams 
   int kv_start = 0;
   if (p.window > 0) kv_start = max(0, pos_base - p.window + 1) / BKV * BKV;
   const int kv_end = min(kv_len, max_pos + 1);
-  const int n_kv_tiles = (kv_end - kv_start + BKV - 1) / BKV;
+  const int split = (int)(blockIdx.x % (unsigned)p.splits);
+  const int all_tiles = (kv_end - kv_start + BKV - 1) / BKV;
+  const int tps = (all_tiles + p.splits - 1) / p.splits;  // key tiles per split
+  kv_start += split * tps * BKV;
+  const int n_kv_tiles = max(0, min(tps, all_tiles - split * tps));
 
   constexpr int RPT = BKV * CH / 256, RSTEP = 256 / CH;
   const long long row_stride = (long long)p.hkv * D;
@@ -407,11 +424,62 @@ __global__ void __launch_bounds__(256, 1) attn_wide_mma_kernel(const WideParams 
     const int r = rt * 16 + g + rr * 8;
     const int tq = r / G;
     if (tq < toks_here) {
+      const long long row = (long long)(q0 + tok_base_q + tq) * p.hq + hk * G + r % G;
+      if (p.splits > 1) {  // unnormalised partial of this split and its (running maximum in the log2 domain, sum)
+        float* po = p.part_o + (row * p.splits + split) * D + warp * SL;
+#pragma unroll
+        for (int n = 0; n < NT; ++n) *reinterpret_cast<float2*>(po + n * 8 + 2 * t4) = make_float2(o[n][rr * 2], o[n][rr * 2 + 1]);
+        if (warp == 0 && t4 == 0) {
+          p.part_ml[(row * p.splits + split) * 2] = m_run[rr];
+          p.part_ml[(row * p.splits + split) * 2 + 1] = l_run[rr];
+        }
+        continue;
+      }
       const float inv = l_run[rr] > 0.f ? 1.f / l_run[rr] : 0.f;
-      bf16* dst = p.out + ((long long)(q0 + tok_base_q + tq) * p.hq + hk * G + r % G) * D + warp * SL;
+      bf16* dst = p.out + row * D + warp * SL;
 #pragma unroll
       for (int n = 0; n < NT; ++n) *reinterpret_cast<uint32_t*>(dst + n * 8 + 2 * t4) = pack_bf16(o[n][rr * 2] * inv, o[n][rr * 2 + 1] * inv);
     }
+  }
+}
+
+// One warp per output row: combine the splits' partials.
+template <int D>
+__global__ void __launch_bounds__(128) attn_wide_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out, long long rows, int splits) {
+  PG_PDL_ENTRY();
+  const long long row = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  float mx = NEG_BIG;
+  for (int s2 = 0; s2 < splits; ++s2) mx = fmaxf(mx, part_ml[(row * splits + s2) * 2]);
+  float l = 0.f;
+  constexpr int E = D / 32;
+  float acc[E];
+#pragma unroll
+  for (int e = 0; e < E; ++e) acc[e] = 0.f;
+  for (int s2 = 0; s2 < splits; ++s2) {
+    const float m = part_ml[(row * splits + s2) * 2], ls = part_ml[(row * splits + s2) * 2 + 1];
+    if (ls <= 0.f) continue;
+    const float w = exp2f(m - mx);
+    l += w * ls;
+    const float* po = part_o + (row * splits + s2) * D + lane * E;
+#pragma unroll
+    for (int e = 0; e < E; e += 4) {
+      const float4 v = *reinterpret_cast<const float4*>(po + e);
+      acc[e] += w * v.x;
+      acc[e + 1] += w * v.y;
+      acc[e + 2] += w * v.z;
+      acc[e + 3] += w * v.w;
+    }
+  }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  bf16* dst = out + row * D + lane * E;
+#pragma unroll
+  for (int e = 0; e < E; e += 8) {
+    float f[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = acc[e + i] * inv;
+    *reinterpret_cast<bf16x8*>(dst + e) = pack8(f);
   }
 }
 
@@ -422,7 +490,7 @@ __global__ void __launch_bounds__(256, 1) attn_wide_mma_kernel(const WideParams 
 // divisor of 32); 0 selects the CUDA-core kernel.
 extern "C" int pg_attention_wide(const void* q, const void* kv_layer, void* out, const void* unit_seq, const void* q_indptr, const void* kv_lens, const void* table,
                                  int table_stride, int tokens, int num_seqs, int q_tiles, int hq, int hkv, int dim, int page_size, long long num_pages, float scale, int window,
-                                 void* status, cudaStream_t stream) {
+                                 int splits, void* part_o, void* part_ml, void* status, cudaStream_t stream) {
   PG_REQUIRE(dim == 512, "wide attention is built for head dim 512 (got %d)", dim);
   PG_REQUIRE(hq % hkv == 0 && hq / hkv >= 1 && hq / hkv <= 8, "wide attention: %d query heads per KV head (1 .. 8)", hkv ? hq / hkv : 0);
   if (tokens == 0) return PG_OK;
@@ -443,6 +511,10 @@ extern "C" int pg_attention_wide(const void* q, const void* kv_layer, void* out,
   p.num_pages = num_pages;
   p.scale = scale;
   p.status = (uint32_t*)status;
+  p.splits = splits < 1 ? 1 : splits;
+  p.part_o = (float*)part_o;
+  p.part_ml = (float*)part_ml;
+  PG_REQUIRE(p.splits == 1 || (part_o && part_ml && q_tiles > 0), "wide attention: split KV needs the partial buffers and the tensor-core kernel");
   const int group = hq / hkv;
   if (q_tiles > 0 && WIDE_ROWS % group == 0) {
     const size_t smem_mma = (size_t)2 * 2 * 32 * 512 * 2 + (size_t)8 * 4 * 32 * 4 * 4;
@@ -451,8 +523,13 @@ extern "C" int pg_attention_wide(const void* q, const void* kv_layer, void* out,
       PG_CUDA(cudaFuncSetAttribute(attn_wide_mma_kernel<512>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_mma));
       attr_done = true;
     }
-    PG_CUDA(launch_pdl(attn_wide_mma_kernel<512>, dim3((unsigned)q_tiles, (unsigned)hkv), dim3(256), smem_mma, stream, p, num_seqs));
+    PG_CUDA(launch_pdl(attn_wide_mma_kernel<512>, dim3((unsigned)(q_tiles * p.splits), (unsigned)hkv), dim3(256), smem_mma, stream, p, num_seqs));
     PG_LAUNCH_CHECK();
+    if (p.splits > 1) {
+      const long long rows = (long long)tokens * hq;
+      PG_CUDA(launch_pdl(attn_wide_merge_kernel<512>, dim3((unsigned)((rows + 3) / 4)), dim3(128), (size_t)0, stream, (const float*)p.part_o, (const float*)p.part_ml, p.out, rows, p.splits));
+      PG_LAUNCH_CHECK();
+    }
     return PG_OK;
   }
   const size_t smem = 2 * (size_t)TK * 512 * 2;

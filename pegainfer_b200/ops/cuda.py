@@ -593,10 +593,17 @@ def paged_attention(q, kv_layer, meta: AttnMeta, scale=None, window=0, out: Opti
             else:
                 qh = meta.h_q_indptr if meta.h_q_indptr is not None else meta.q_indptr.tolist()
                 q_tiles = sum((qh[b + 1] - qh[b] + tpt - 1) // tpt for b in range(meta.num_seqs))
+        # decode steps: split the keys of a sequence over several blocks until the launch fills the GPU about twice
+        splits = 1
+        if q_tiles > 0 and meta.decode_only:
+            splits = max(1, min(8, (2 * c.sms) // max(1, q_tiles * hkv), (max(meta.max_kv_len, 1) + 255) // 256))
+            while splits > 1 and t * hq * splits * (d + 2) * 4 > c.attn_part.numel():
+                splits -= 1
+        ml_off = t * hq * splits * d * 4
         rc = lib().pg_attention_wide(_ptr(q), _ptr(kv_layer), _ptr(out), _ptr(_unit_seq(meta, q.device)), _ptr(meta.q_indptr), _ptr(meta.kv_lens), _ptr(table),
                                      _ci(table.stride(0)), _ci(t), _ci(meta.num_seqs), _ci(q_tiles), _ci(hq), _ci(hkv), _ci(d), _ci(page_size), _ll(kv_layer.shape[0]), _cf(scale),
-                                     _ci(window), _ptr(c.status), _stream())
-        _check(rc, c)
+                                     _ci(window), _ci(splits), _ptr(c.attn_part), _ptr(c.attn_part[ml_off:]), _ptr(c.status), _stream())
+        _check(rc, c, 2 if splits > 1 else 1)
         return out
 
     def decode_rows(first: int, n: int, plan=None):

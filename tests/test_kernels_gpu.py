@@ -175,6 +175,19 @@ def test_wide_head_attention_hd512(hq, hkv, page):
         ref = R.paged_attention(q, kv, meta, scale, window)
         out = cu().paged_attention(q, kv, meta, scale, window)
         bf16_close(out, ref, rel=2 ** -6, abs_=6e-3)
+    # a decode step of few sequences: the keys of a sequence are split over several blocks and merged
+    kv_lens = [1, 15, 300, 1025, 2000]
+    kv, meta = make_batch([1] * len(kv_lens), kv_lens, page, hkv, d, pad=2)
+    kv = (kv.float() * 0.05).bfloat16()
+    q = (torch.randn(meta.num_tokens, hq, d, device=DEV) * 0.5).bfloat16()
+    assert meta.decode_only
+    for window in (0, 200):
+        ref = R.paged_attention(q, kv, meta, None, window)
+        before = cu().launch_count(DEV)
+        out = cu().paged_attention(q, kv, meta, None, window)
+        assert cu().launch_count(DEV) - before == 2  # split kernel + merge
+        bf16_close(out, ref, rel=2 ** -6, abs_=6e-3)
+        assert out[len(kv_lens):].abs().max().item() == 0  # padding rows are inert
     status_clean()
 
 
