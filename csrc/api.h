@@ -143,7 +143,7 @@ int pg_ep_combine(const void* comb, const void* ids, const void* weights, int to
 
 // ---- LoRA (lora.cu) -----------------------------------------------------------------
 int pg_lora_delta(const void* x, long long ldx, const void* A, const void* B, const void* scale, const void* slots, void* y, long long ldy,
-                  int tokens, int K, int M, int r_max, int num_slots, cudaStream_t stream);
+                  int tokens, int K, int M, int r_max, int num_slots, void* tvec, cudaStream_t stream);
 
 // ---- Gated DeltaNet (gdn.cu) ------------------------------------------------------
 int pg_gdn_conv1d(const void* x, long long ldx, const void* w, void* state, void* out, long long ldo, const void* q_indptr, const void* slots,

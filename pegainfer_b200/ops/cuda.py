@@ -1277,7 +1277,8 @@ def lora_delta_(y, x, A, B, scale, slots):
     t, k = x.shape
     m = y.shape[1]
     c = ctx(x.device)
+    tvec = torch.empty((t, A.shape[1]), dtype=torch.float32, device=x.device)  # A x per token, between the shrink and the expand kernel
     rc = lib().pg_lora_delta(_ptr(x), _ll(x.stride(0)), _ptr(A), _ptr(B), _ptr(scale), _ptr(slots), _ptr(y), _ll(y.stride(0)), _ci(t), _ci(k), _ci(m), _ci(A.shape[1]),
-                             _ci(A.shape[0]), _stream())
-    _check(rc, c)
+                             _ci(A.shape[0]), _ptr(tvec), _stream())
+    _check(rc, c, 2)
     return y

@@ -199,6 +199,22 @@ class TorchExecutor(ModelExecutor):
         return (self._graphs is not None and self.mtp is None and self.aux_sink is None and batch.is_decode() and len(seqs) <= self.max_decode_batch
                 and all(s.sample and s.logprobs == 0 and s.lora_slot < 0 for s in seqs))
 
+    def _graph_lora_decode(self, batch: StepBatch) -> bool:
+        """A greedy decode step in which at least one request uses an adapter: replayed from the adapter-aware graphs
+        (the adapter slot of every row is a graph input), not run kernel by kernel."""
+        seqs = batch.seqs
+        return (self._graphs is not None and not self._graphs.uses_state and self.mtp is None and self.aux_sink is None and getattr(self.model, "lora", None) is not None
+                and batch.is_decode() and len(seqs) <= self.max_decode_batch and any(s.lora_slot >= 0 for s in seqs)
+                and all(s.sample and s.logprobs == 0 and s.params.effectively_greedy(self.vocab_size) for s in seqs))
+
+    def _lora_graphs(self):
+        g = getattr(self, "_graphs_lora", None)
+        if g is None:
+            from ..utils.cuda_graph import DecodeGraphs
+
+            g = self._graphs_lora = DecodeGraphs(self, self.max_decode_batch, self.max_blocks_per_seq, with_lora=True)
+        return g
+
     def enable_sm_split(self, decode_pct: int) -> None:
         """Confine the prefill lane to ``100 - decode_pct`` percent of the SMs (green contexts)."""
         from ..utils.green_ctx import SmSplit
@@ -263,6 +279,9 @@ class TorchExecutor(ModelExecutor):
         seqs = batch.seqs
         if self._graph_verify(batch):
             return self._execute_verify_graph(batch, t0)
+        if self._graph_lora_decode(batch):
+            toks, _ = self._lora_graphs().run_rows(batch.seqs)
+            return StepResult(tokens={s.rid: [toks[i]] for i, s in enumerate(batch.seqs)}, elapsed_s=time.perf_counter() - t0)
         if self._graph_decode(batch):
             all_greedy = all(s.params.effectively_greedy(self.vocab_size) for s in seqs)
             out = self._graphs.run(seqs, greedy=all_greedy, ahead=batch.run_ahead and all_greedy)

@@ -53,7 +53,7 @@ class _InFlight:
 
 
 class DecodeGraphs:
-    def __init__(self, executor, max_batch: int, max_blocks_per_seq: int):
+    def __init__(self, executor, max_batch: int, max_blocks_per_seq: int, with_lora: bool = False):
         from ..sched.executor import DECODE_BUCKETS, bucket_for
 
         self.ex = executor
@@ -75,6 +75,11 @@ class DecodeGraphs:
         self.h_slots = torch.zeros(B, dtype=torch.int32).pin_memory()
         self.d_slots = torch.zeros(B, dtype=torch.int32, device=dev)
         self.uses_state = hasattr(executor.model, "rec")
+        # graphs whose steps carry an adapter slot per row (-1: no adapter); a separate set from the adapter-free graphs,
+        # which keep the fused decode path
+        self.with_lora = with_lora
+        self.h_lora = torch.full((B,), -1, dtype=torch.int32).pin_memory()
+        self.d_lora = torch.full((B,), -1, dtype=torch.int32, device=dev)
         self.h_out = torch.zeros(B, dtype=torch.int32).pin_memory()
         self.h_out2 = torch.zeros(B, dtype=torch.int32).pin_memory()
         self.pending: Optional[_InFlight] = None  # the step that is running ahead, if any
@@ -141,6 +146,7 @@ class DecodeGraphs:
             decode_only=True,
             plan=splits,
             state_slots=self.d_slots[:b] if self.uses_state else None,
+            lora_slots=self.d_lora[:b] if self.with_lora else None,
         )
 
     def _forward(self, b: int, greedy: bool, splits: int):
@@ -406,6 +412,11 @@ class DecodeGraphs:
             self.capture(b, True)
         self.invalidate_table()  # rows of one request share a request id: the per-row table cache does not apply
         self.stage(rows, b)
+        if self.with_lora:
+            self.h_lora[:n] = torch.tensor([getattr(r, "lora_slot", -1) for r in rows], dtype=torch.int32)
+            self.h_lora[n:b] = -1
+            self.d_lora[:b].copy_(self.h_lora[:b], non_blocking=True)
+            self.h2d_bytes += b * 4
         self.graphs[key].replay()
         self.replays += 1
         self.invalidate_table()

@@ -474,3 +474,39 @@ def test_decode_overlap_with_sm_split_matches_plain_engine():
     finally:
         plain.shutdown()
         split.shutdown()
+
+
+def test_lora_decode_steps_replay_adapter_aware_graphs(tmp_path):
+    """Greedy decode steps with adapters run from the adapter-aware CUDA graphs (the adapter slot of every row is a graph
+    input) and produce the tokens of the kernel-by-kernel path; adapter-free requests in the same batch keep theirs."""
+    import os
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    if root not in sys.path:
+        sys.path.insert(0, root)
+    from bench_lora import write_adapter
+    from pegainfer_b200.engine.contract import Request, SamplingParams
+    from pegainfer_b200.lora.manager import LoraManager
+
+    mcfg = preset("qwen3-0.6b", num_layers=3, vocab_size=4096)
+    for i in range(2):
+        write_adapter(str(tmp_path / f"a{i}"), mcfg, 8, 16, seed=i)
+    g = torch.Generator().manual_seed(4)
+    ps = [torch.randint(0, 4096, (20 + 5 * i,), generator=g).tolist() for i in range(5)]
+    adapters = ["a0", None, "a1", "a0", None]
+    outs = {}
+    for graph in (False, True):
+        ecfg = EngineConfig(preset="qwen3-0.6b", num_kv_blocks=256, cuda_graph=graph, max_decode_batch=8, max_model_len=512, enable_lora=True, max_loras=2, max_lora_rank=8)
+        eng = build_engine(ecfg, mcfg, device="cuda:0", dtype=torch.bfloat16)
+        try:
+            mgr = LoraManager(eng, max_loras=2, max_rank=8)
+            for i in range(2):
+                mgr.load(f"a{i}", str(tmp_path / f"a{i}"))
+            streams = [eng.submit(Request(prompt_tokens=p, params=SamplingParams(temperature=0.0, ignore_eos=True), max_tokens=10, lora_adapter=a)) for p, a in zip(ps, adapters)]
+            outs[graph] = [s.collect(120)[0] for s in streams]
+            if graph:
+                assert eng.executor._lora_graphs().replays > 0
+        finally:
+            eng.shutdown()
+    assert outs[True] == outs[False]
