@@ -47,7 +47,7 @@ class ModelLine:
 
 def _qwen3_validate(ns, provided):
     if ns.enable_lora and ns.cuda_graph:
-        log.warning("LoRA requests run outside CUDA graphs; graph replay stays on for adapter-free batches")
+        log.info("greedy decode steps with adapters replay adapter-aware CUDA graphs (the adapter slot of every row is a graph input); sampled or logprob steps with adapters run kernel by kernel")
     if ns.decode_overlap and ns.tp_size > 1:
         raise SystemExit("--decode-overlap is not available together with tensor parallelism")
     if "decode_sm_pct" in provided and not ns.decode_overlap:
