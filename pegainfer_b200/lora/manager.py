@@ -169,6 +169,12 @@ class LoraManager:
             self._free.append(slot)
 
     # -- application ------------------------------------------------------------------------
+    def apply_shared(self, layer: int, projs, x: torch.Tensor, ys, slots: Optional[torch.Tensor]) -> None:
+        """``apply`` for projections that read the same ``x`` (q / k / v, gate / up): one pair of launches for all."""
+        if slots is None:
+            return
+        ops.lora_delta_multi_(list(ys), x, [self.A[(layer, p)] for p in projs], [self.B[(layer, p)] for p in projs], self.scale, slots)
+
     def apply(self, layer: int, proj: str, x: torch.Tensor, y: torch.Tensor, slots: Optional[torch.Tensor]) -> None:
         """``y += scale * B (A x)`` for rows whose request uses an adapter; ``y`` may be a column slice."""
         if slots is None:

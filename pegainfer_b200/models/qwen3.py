@@ -182,9 +182,7 @@ class Qwen3Model:
                 qkv = tp.col_linear(x, l.qkv)
             if ls is not None:
                 qs, ks = self.q_heads * cfg.head_dim, self.kv_heads * cfg.head_dim
-                self.lora.apply(i, "q_proj", x, qkv[:, :qs], ls)
-                self.lora.apply(i, "k_proj", x, qkv[:, qs : qs + ks], ls)
-                self.lora.apply(i, "v_proj", x, qkv[:, qs + ks :], ls)
+                self.lora.apply_shared(i, ("q_proj", "k_proj", "v_proj"), x, (qkv[:, :qs], qkv[:, qs : qs + ks], qkv[:, qs + ks :]), ls)
             q = ops.qk_norm_rope_append(qkv, l.q_norm, l.k_norm, self.cos, self.sin, meta, kv.layer(i), self.q_heads, self.kv_heads, cfg.head_dim, eps)
             a = ops.paged_attention(q, kv.layer(i), meta)
             next_norm = self.layers[i + 1].input_norm if i + 1 < n else self.final_norm
@@ -218,8 +216,7 @@ class Qwen3Model:
                 x = ops.add_rms_norm(tp.all_reduce(y), residual, l.post_norm, eps)
                 gu = ops.linear(x, l.gate_up)
                 ff = gu.shape[1] // 2
-                self.lora.apply(i, "gate_proj", x, gu[:, :ff], ls)
-                self.lora.apply(i, "up_proj", x, gu[:, ff:], ls)
+                self.lora.apply_shared(i, ("gate_proj", "up_proj"), x, (gu[:, :ff], gu[:, ff:]), ls)
                 act = ops.swiglu(gu)
                 y = ops.linear(act, l.down)
                 self.lora.apply(i, "down_proj", act, y, ls)

@@ -1270,6 +1270,25 @@ def mla_attention_sparse(q: "_MlaQ", w_uk, w_uv, latent_layer, meta: AttnMeta, s
     return outs[0] if len(outs) == 1 else torch.cat(outs)
 
 
+def lora_delta_multi_(ys, x, As, Bs, scale, slots):
+    """``lora_delta_`` for up to three projections that read the same ``x`` (q / k / v, gate / up): one shrink and one
+    expand launch for all of them."""
+    import ctypes
+
+    _bf16(x)
+    n = len(ys)
+    assert 1 <= n <= 3 and x.stride(-1) == 1 and all(y.stride(-1) == 1 for y in ys) and all(a.is_contiguous() for a in As) and all(b.is_contiguous() for b in Bs)
+    t, k = x.shape
+    r = As[0].shape[1]
+    tvec = torch.empty((n, t, r), dtype=torch.float32, device=x.device)
+    vp = ctypes.c_void_p * n
+    rc = lib().pg_lora_delta_multi(_ptr(x), _ll(x.stride(0)), _ci(n), vp(*[a.data_ptr() for a in As]), vp(*[b.data_ptr() for b in Bs]), vp(*[y.data_ptr() for y in ys]),
+                                   (ctypes.c_longlong * n)(*[y.stride(0) for y in ys]), (ctypes.c_int * n)(*[y.shape[1] for y in ys]), _ptr(scale), _ptr(slots), _ci(t), _ci(k), _ci(r),
+                                   _ci(As[0].shape[0]), _ptr(tvec), _stream())
+    _check(rc, ctx(x.device), 2)
+    return ys
+
+
 def lora_delta_(y, x, A, B, scale, slots):
     """In place: ``y[t] += scale[s] * B[s] @ (A[s] @ x[t])`` with ``s = slots[t]`` (negative = skip)."""
     _bf16(x)

@@ -760,6 +760,13 @@ def sigmoid_gate_mul(x, gate):
     return (x.float() * torch.sigmoid(gate.float())).to(x.dtype)
 
 
+def lora_delta_multi_(ys, x, As, Bs, scale, slots):
+    """``lora_delta_`` for several projections that read the same ``x``."""
+    for y, a, b in zip(ys, As, Bs):
+        lora_delta_(y, x, a, b, scale, slots)
+    return ys
+
+
 def lora_delta_(y, x, A, B, scale, slots):
     """In place: ``y[t] += scale[s] * B[s] @ (A[s] @ x[t])`` with ``s = slots[t]`` (negative = skip)."""
     sl = slots.tolist()
