@@ -59,6 +59,8 @@ LINES = [
     ModelLine("qwen35", ("qwen35",), frozenset({"max_batch"})),
     ModelLine("deepseek-v2-lite", ("deepseek_v2",), frozenset({"ep_backend"})),
     ModelLine("kimi-k2", ("kimi_k2",), frozenset({"ep_backend", "spec_method"})),
+    ModelLine("glm-5", ("glm_dsa",), frozenset({"ep_backend", "spec_method"})),
+    ModelLine("gemma4", ("gemma4",), frozenset()),
 ]
 LINES[0].validate = _qwen3_validate  # type: ignore[method-assign]
 

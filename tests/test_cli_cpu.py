@@ -45,3 +45,11 @@ def test_percentiles_and_affinity_plan():
     assert parse_cpulist("0-3,8,10-11") == [0, 1, 2, 3, 8, 10, 11]
     assert plan_affinity(list(range(16)), 1, 4) == [4, 5, 6, 7]
     assert plan_affinity([], 0, 1) == []
+
+
+def test_every_registered_family_has_exactly_one_model_line():
+    from pegainfer_b200.models.registry import BUILDERS
+    from pegainfer_b200.serve import detect_line
+
+    for family in BUILDERS:
+        assert detect_line(family).name
