@@ -47,6 +47,7 @@ def parse():
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (marks the result invalid)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--decode-overlap", action="store_true", help="end-to-end arm: prompts are prefilled on a second stream while the admitted requests keep decoding (1 GPU)")
     ap.add_argument("--prefill-chunk", type=int, default=4096, help="token budget of one prefill step (max_prefill_tokens)")
     ap.add_argument("--profile-host", default=None, help="write a cProfile of the scheduler thread during the e2e phase to this path")
     ap.add_argument("--no-library-arm", action="store_true", help="skip the cuBLAS + NCCL arm that is timed after the main arm and reported as `library_arm`")
@@ -420,7 +421,7 @@ def run_arm(args, impl, comm, rank, local, world, device, with_e2e):
     ramp = (args.conc + max(1, 4096 // args.prompt_len) - 1) // max(1, 4096 // args.prompt_len)
     total_len = args.prompt_len + args.warmup + args.steps + ramp + 2 * page
     blocks = 2 * args.conc * ((total_len + page - 1) // page + 2) + 8
-    ecfg = EngineConfig(preset=args.model, num_kv_blocks=blocks, kv_page_size=page, cuda_graph=True, precapture_graphs=True, max_decode_batch=max(args.conc, 8), max_model_len=total_len + page, max_prefill_tokens=args.prefill_chunk, no_prefix_cache=True, tune_gc=True)
+    ecfg = EngineConfig(preset=args.model, num_kv_blocks=blocks, kv_page_size=page, cuda_graph=True, precapture_graphs=True, max_decode_batch=max(args.conc, 8), max_model_len=total_len + page, max_prefill_tokens=args.prefill_chunk, no_prefix_cache=True, tune_gc=True, decode_overlap=bool(args.decode_overlap))
     eng = None
     try:
         eng = build_engine(ecfg, mcfg, device=device, dtype=torch.bfloat16, tp=tp, start=False)
