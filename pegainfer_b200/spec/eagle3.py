@@ -146,6 +146,116 @@ class Eagle3DraftModel:
         return self.d2t[draft.long()], ops.gather_rows(residual, rows)
 
 
+class _ChainGraphs:
+    """The chain steps of a draft round (every step after the first) as one CUDA graph per request-count bucket.
+
+    The first step of a round takes a ragged number of (token, feature) pairs per request and stays kernel by kernel; the
+    ``steps`` steps behind it are decode-shaped (one row per request, positions one further each time), so their
+    positions, slots, KV lengths and block tables live in pointer-stable buffers that are refreshed from pinned mirrors
+    before a replay, the first step's drafts and features are copied in, and the drafts of all steps come back through
+    one small copy."""
+
+    def __init__(self, draft: "Eagle3DraftModel", kv, page_size: int, steps: int, max_batch: int, width: int):
+        from ..sched.executor import DECODE_BUCKETS, bucket_for
+
+        self.draft, self.kv, self.page_size, self.steps = draft, kv, page_size, steps
+        dev = draft.device
+        self.buckets = [b for b in DECODE_BUCKETS if b <= max(bucket_for(max_batch), 1)]
+        n, W = self.buckets[-1], max(width, 1)
+        self.nmax, self.W = n, W
+        self.h_small = torch.zeros(3 * steps * n, dtype=torch.int32).pin_memory()  # positions | slots | kv lengths, [steps, n] each
+        self.d_small = torch.zeros(3 * steps * n, dtype=torch.int32, device=dev)
+        self.h_table = torch.zeros((n, W), dtype=torch.int32).pin_memory()
+        self.d_table = torch.zeros((n, W), dtype=torch.int32, device=dev)
+        self.tok = torch.zeros(n, dtype=torch.int32, device=dev)
+        self.feat = torch.zeros((n, draft.cfg.hidden_size), dtype=draft.dtype, device=dev)
+        self.out = torch.zeros((steps, n), dtype=torch.int32, device=dev)
+        self.h_out = torch.zeros((steps, n), dtype=torch.int32).pin_memory()
+        self.q_indptr = torch.arange(n + 1, dtype=torch.int32, device=dev)
+        self.rows = torch.arange(n, dtype=torch.int32, device=dev)
+        self.graphs: dict = {}
+        self.pool = None
+        self.replays = 0
+
+    def _views(self, j: int, n: int):
+        N, S = self.nmax, self.steps
+        s = self.d_small
+        return s[j * N : j * N + n], s[(S + j) * N : (S + j) * N + n], s[(2 * S + j) * N : (2 * S + j) * N + n]
+
+    def _body(self, n: int) -> None:
+        from ..ops import cuda as K
+        from ..ops.reference import AttnMeta
+
+        d = self.draft
+        geo = d.kv_geometry()
+        plan = K.plan_decode_splits(n, geo["kv_heads"], min(self.W * self.page_size, 2048), d.device)
+        tok, feat = self.tok[:n], self.feat[:n]
+        for j in range(self.steps):
+            pos, slot, kvl = self._views(j, n)
+            meta = AttnMeta(q_indptr=self.q_indptr[: n + 1], kv_lens=kvl, block_table=self.d_table[:n], slot_mapping=slot, positions=pos, page_size=self.page_size, num_seqs=n,
+                            num_tokens=n, max_q_len=1, max_kv_len=self.W * self.page_size, decode_only=True, plan=plan)
+            draft, feat = d.step(tok, feat, meta, self.kv, self.rows[:n])
+            tok = draft.to(torch.int32)
+            self.out[j, :n].copy_(tok)
+
+    def capture(self, n: int):
+        dev = self.draft.device
+        self.d_small.zero_()
+        self.d_table.zero_()
+        s = torch.cuda.Stream(dev)
+        s.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(s):
+            self._body(n)  # warm-up on padding inputs (page 0, KV length 0)
+            s.synchronize()
+            g = torch.cuda.CUDAGraph()
+            if self.pool is None:
+                self.pool = torch.cuda.graph_pool_handle()
+            g.capture_begin(pool=self.pool)
+            try:
+                self._body(n)
+            finally:
+                g.capture_end()
+            g.replay()
+        torch.cuda.current_stream(dev).wait_stream(s)
+        self.graphs[n] = g
+        return g
+
+    def run(self, decoders, first_draft: torch.Tensor, first_feat: torch.Tensor) -> list:
+        """Drafts of the chain steps, ``[steps][requests]``.  ``decoders``: the scheduler's request states;
+        ``first_draft`` / ``first_feat``: what the round's first step produced for them."""
+        from ..sched.executor import bucket_for
+
+        n, N, S, ps = len(decoders), self.nmax, self.steps, self.page_size
+        b = bucket_for(n, self.buckets)
+        if b not in self.graphs:
+            self.capture(b)
+        sm, tb = self.h_small.numpy(), self.h_table.numpy()
+        sm[:] = 0
+        tb[:] = 0
+        for i, r in enumerate(decoders):
+            pages = r.kv.view().page_indices
+            tb[i, : len(pages)] = pages
+            c = r.kv.committed
+            for j in range(S):
+                pos = c + j  # chain step j + 1 appends at position committed + j
+                sm[j * N + i] = pos
+                sm[(S + j) * N + i] = pages[pos // ps] * ps + pos % ps
+                sm[(2 * S + j) * N + i] = pos + 1
+        self.d_small.copy_(self.h_small, non_blocking=True)
+        self.d_table.copy_(self.h_table, non_blocking=True)
+        self.tok[:n].copy_(first_draft.to(torch.int32))
+        self.feat[:n].copy_(first_feat)
+        self.graphs[b].replay()
+        self.replays += 1
+        self.h_out.copy_(self.out, non_blocking=True)
+        torch.cuda.current_stream(self.draft.device).synchronize()
+        return [self.h_out[j, :n].tolist() for j in range(S)]
+
+    def release(self) -> None:
+        self.graphs.clear()
+        self.pool = None
+
+
 class Eagle3Spec:
     allows_prefix_cache = False
     kind = "eagle3"
@@ -165,6 +275,13 @@ class Eagle3Spec:
         self.pending: dict = {}  # rid -> [feature rows] of committed positions valid .. committed - 1
         self.staged: dict = {}
         self.rounds = 0
+        import os
+
+        # the chain steps of a round as one CUDA graph per bucket (PEGAINFER_DRAFT_GRAPH=0: kernel by kernel)
+        self._use_graph = self.device.type == "cuda" and os.environ.get("PEGAINFER_DRAFT_GRAPH", "1") != "0"
+        self._chain = None
+        self._max_batch = int(getattr(executor, "max_decode_batch", 64))
+        self._width = int(getattr(executor, "max_blocks_per_seq", 0) or 1)
         executor.aux_sink = self
 
     def observe(self, kind: str, seqs, meta, aux: list) -> None:
@@ -210,6 +327,15 @@ class Eagle3Spec:
         tok, meta = build_meta(seqs, self.page_size, dev)
         rows = torch.tensor([meta.h_q_indptr[i + 1] - 1 for i in range(len(seqs))], dtype=torch.int32, device=dev)
         draft, feat = self.draft.step(tok, torch.cat(feats) if len(feats) > 1 else feats[0], meta, self.kv, rows)
+        if self._use_graph and self.draft_len > 1 and len(decoders) <= self._max_batch:
+            if self._chain is None:
+                self._chain = _ChainGraphs(self.draft, self.kv, self.page_size, self.draft_len - 1, self._max_batch, self._width)
+            chain = self._chain.run(decoders, draft, feat)
+            first = draft.tolist()
+            for r in decoders:
+                self.valid[r.q.id], self.pending[r.q.id] = r.kv.committed, []
+            self.rounds += 1
+            return {r.q.id: [int(first[i])] + [int(step[i]) for step in chain] for i, r in enumerate(decoders)}
         out = [draft]
         one = torch.arange(len(seqs), dtype=torch.int32, device=dev)
         for j in range(1, self.draft_len):

@@ -67,3 +67,24 @@ def test_drafters_are_lossless_with_the_verify_graph(method, path, layers, draft
     finally:
         plain.shutdown()
         spec.shutdown()
+
+
+def test_eagle3_chain_graph_gives_the_drafts_of_the_kernel_by_kernel_chain(monkeypatch):
+    """The chain steps of an EAGLE-3 round replayed as a CUDA graph propose the same tokens as the eager chain: the two
+    engines accept the same number of draft tokens and emit the same text."""
+    ps = _prompts(3, 9)
+    stats = {}
+    for mode in ("1", "0"):
+        monkeypatch.setenv("PEGAINFER_DRAFT_GRAPH", mode)
+        eng = _engine(8, spec_method="eagle3", draft_model_path="random:draft_vocab=4096")
+        try:
+            out = eng.generate(ps, max_tokens=24)
+            s, c = eng.scheduler.spec, eng.scheduler._metrics.spec_decode
+            stats[mode] = ([x[0] for x in out], c.num_drafts, c.num_accepted_tokens)
+            if mode == "1":
+                assert s._chain is not None and s._chain.replays == s.rounds > 0
+            else:
+                assert s._chain is None
+        finally:
+            eng.shutdown()
+    assert stats["1"] == stats["0"]
