@@ -5,7 +5,9 @@ Kineto tracer that ships inside PyTorch) records every kernel launch with its de
 afterwards ``kernels()`` gives one row per kernel name (launches, total / mean / min / max microseconds,
 grid and block of the last launch) and ``sol()`` turns the algorithmic bytes or FLOPs of the range into
 achieved GB/s and TFLOP/s against given peaks.  No hardware counters are collected and nothing is
-replayed, so the range runs once, at its own speed, and the clocks are left alone.
+replayed, so the range runs once, at its own speed, and the clocks are left alone.  A kernel launched with programmatic
+dependent launch starts while its predecessor still runs and waits inside: its record covers that wait, so per-kernel times
+of such chains overlap and add up to more than the span (the span itself is exact).
 
 On a machine without a GPU (or when the tracer cannot start) the range still runs; ``kernels()`` is then
 empty and ``available`` is False.
