@@ -62,6 +62,8 @@ int pg_ipc_close(void* p);
 int pg_gemm2sm_eligible(int T, int M, int K);
 int pg_gemm2sm_bf16_tn(const void* x, const void* w, void* y, int T, int M, int K, long long ldx, long long ldw, long long ldy, void* status,
                        cudaStream_t stream);
+int pg_gemm2sm_bf16_tn_swiglu(const void* x, const void* w, void* y, int T, int M, int K, long long ldx, long long ldw, long long ldy, void* status,
+                       cudaStream_t stream);
 int pg_make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, long long rows, long long cols, long long ld, int box_rows, int box_cols);
 
 // ---- row kernels (elementwise.cu) --------------------------------------------------

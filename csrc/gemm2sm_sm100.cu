@@ -48,6 +48,7 @@ struct Gemm2Params {
   int stages;  // shared-memory ring depth
   uint32_t tmem_cols;
   uint32_t* status;
+  int epi;  // 0: y = x W^T; 1: the weight rows alternate (gate_i, up_i) and y [T, M / 2] = bf16(silu(gate)) * up
 };
 
 // Work item -> (weight-row pair, token tile).  Items walk RASTER_GROUP weight-row pairs across
@@ -250,7 +251,24 @@ gemm2sm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
         tmem_ld16(t_row + c, v[0]);
         tmem_ld16(t_row + c + 16, v[1]);
         tmem_ld_wait();
-        if (m < p.M) {
+        if (p.epi == 1) {
+          // SwiGLU: lanes 2 i and 2 i + 1 hold gate and up of output column m / 2 (both rounded to bf16 first, as the
+          // separate kernel sees them); the shuffles run on all lanes, the even ones store
+          bf16* ys = p.y + (m >> 1);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float mine = __bfloat162float(__float2bfloat16(__uint_as_float(v[h][j])));
+              const float other = __shfl_xor_sync(0xFFFFFFFFu, mine, 1);
+              const int n = n0 + c + h * 16 + j;
+              if (!(lane & 1) && m < p.M && n < p.T) {
+                const float a = __bfloat162float(__float2bfloat16(mine / (1.f + __expf(-mine))));
+                ys[(long long)n * p.ldy] = __float2bfloat16(a * other);
+              }
+            }
+          }
+        } else if (m < p.M) {
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
 #pragma unroll
@@ -315,8 +333,21 @@ extern "C" int pg_gemm2sm_eligible(int T, int M, int K) {
   return (long long)ceil_div(M, 2 * BM) * ceil_div(T, 256) >= 64 ? 1 : 0;
 }
 
+static int gemm2sm_impl(const void* x, const void* w, void* y, int T, int M, int K, long long ldx, long long ldw, long long ldy, void* status, int epi, cudaStream_t stream);
+
 extern "C" int pg_gemm2sm_bf16_tn(const void* x, const void* w, void* y, int T, int M, int K, long long ldx, long long ldw, long long ldy, void* status,
                                   cudaStream_t stream) {
+  return gemm2sm_impl(x, w, y, T, M, K, ldx, ldw, ldy, status, 0, stream);
+}
+
+// The same product with SwiGLU in the epilogue: w [M, K] with rows alternating (gate_i, up_i), y [T, M / 2].
+extern "C" int pg_gemm2sm_bf16_tn_swiglu(const void* x, const void* w, void* y, int T, int M, int K, long long ldx, long long ldw, long long ldy, void* status,
+                                         cudaStream_t stream) {
+  PG_REQUIRE(M % 2 == 0, "gemm2sm swiglu: M %d must be even (interleaved gate / up rows)", M);
+  return gemm2sm_impl(x, w, y, T, M, K, ldx, ldw, ldy, status, 1, stream);
+}
+
+static int gemm2sm_impl(const void* x, const void* w, void* y, int T, int M, int K, long long ldx, long long ldw, long long ldy, void* status, int epi, cudaStream_t stream) {
   PG_REQUIRE(T > 0 && M > 0 && K > 0 && K % 8 == 0, "gemm2sm: bad problem %dx%dx%d", T, M, K);
   PG_REQUIRE(status != nullptr, "gemm2sm: a device status word is required");
   int dev = 0;
@@ -379,6 +410,7 @@ extern "C" int pg_gemm2sm_bf16_tn(const void* x, const void* w, void* y, int T, 
   PG_REQUIRE(p.stages >= 2, "gemm2sm: not enough shared memory");
   p.tmem_cols = 2 * p.bn > 256 ? 512u : 256u;
   p.status = (uint32_t*)status;
+  p.epi = epi;
   const size_t smem = 1024 + (size_t)p.stages * stage_bytes + tail;
   CUtensorMap tm_w, tm_x;
   int rc = pg_make_tmap_bf16_2d(&tm_w, w, M, K, ldw, BM, BK);

@@ -206,7 +206,13 @@ class Qwen3Model:
                 x = tp.row_linear_add_norm(a, l.o, residual, l.post_norm, eps)
                 if decode:
                     ops.prefetch_weights(l.down)
-                act = ops.swiglu(tp.col_linear(x, l.gate_up), il)
+                act = None
+                if il and tp.world == 1 and x.is_cuda and ops.get_mode() == "sm100":
+                    from ..ops import cuda as Kc
+
+                    act = Kc.linear_swiglu_2sm(x, l.gate_up)  # prefill-sized steps: SwiGLU in the epilogue of the two-SM GEMM
+                if act is None:
+                    act = ops.swiglu(tp.col_linear(x, l.gate_up), il)
                 if decode:
                     ops.prefetch_weights(self.layers[i + 1].qkv if i + 1 < n else self.lm_head)
                 x = tp.row_linear_add_norm(act, l.down, residual, next_norm, eps)

@@ -402,6 +402,22 @@ def linear_2sm(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return out.view(*x.shape[:-1], m)
 
 
+def linear_swiglu_2sm(x: torch.Tensor, w: torch.Tensor) -> Optional[torch.Tensor]:
+    """``swiglu(x @ w.T)`` for a gate_up weight whose rows alternate (gate_i, up_i), with SwiGLU in the epilogue of the
+    two-SM GEMM (prefill-sized steps); ``None`` when the two-SM kernel does not take the problem."""
+    _bf16(x)
+    x2 = _rows2d(x)
+    t, k = x2.shape
+    m = w.shape[0]
+    if not lib().pg_gemm2sm_eligible(_ci(t), _ci(m), _ci(k)) or _BATCH_INVARIANT or w.stride(-1) != 1:
+        return None
+    out = torch.empty((t, m // 2), dtype=torch.bfloat16, device=x.device)
+    c = ctx(x.device)
+    rc = lib().pg_gemm2sm_bf16_tn_swiglu(_ptr(x2), _ptr(w), _ptr(out), _ci(t), _ci(m), _ci(k), _ll(x2.stride(0)), _ll(w.stride(0)), _ll(out.stride(0)), _ptr(c.status), _stream())
+    _check(rc, c)
+    return out.view(*x.shape[:-1], m // 2)
+
+
 class _ChainPhase(ctypes.Structure):
     _fields_ = [("x", _vp), ("ldx", _ll), ("w", _vp), ("ldw", _ll), ("M", _ci), ("K", _ci), ("epi", _ci), ("out", _vp), ("ld_out", _ll), ("norm_w", _vp), ("norm_offset", _ci),
                 ("in_ssp", _vp), ("in_parts", _ci), ("in_ld", _ci), ("in_width", _ci), ("in_eps", _cf), ("out_ssp", _vp), ("out_ld", _ci),
