@@ -101,11 +101,14 @@ def test_metrics_gauges_and_partitions():
 
         t = threading.Thread(target=slow)
         t.start()
-        # deadlines, not iteration counts: on a loaded machine the poster thread may start late
+        # deadlines, not iteration counts: on a loaded machine the poster thread may start late.  The gauges are read
+        # through a client of their own: one test client runs its requests one after the other, so a GET behind the slow
+        # POST on the same client would only be answered once the request is over
+        watcher = TestClient(c.app)
         seen_running = False
         deadline = time.monotonic() + 20.0
         while time.monotonic() < deadline and t.is_alive():
-            m = c.get("/metrics").text
+            m = watcher.get("/metrics").text
             if 'vllm:num_requests_running{engine="0",model_name="sim-model"} 1' in m or 'vllm:num_requests_running{engine="1",model_name="sim-model"} 1' in m:
                 seen_running = True
                 break
