@@ -116,7 +116,10 @@ class OtlpHttpExporter:
             self._post(batch)
 
     def close(self) -> None:
+        """Stop the sender, wait for the post it may be in the middle of, then send what is left."""
         self._stop.set()
+        if self._thread.is_alive() and threading.current_thread() is not self._thread:
+            self._thread.join(timeout=5.0)
         self.flush()
 
 

@@ -92,7 +92,7 @@ def test_unsupported_params_are_rejected_not_ignored():
 
 
 def test_metrics_gauges_and_partitions():
-    eng, c = make(SimConfig(base_ttft_s=1.0, tpot_s=0.1), partitions=2, declared=2)
+    eng, c = make(SimConfig(base_ttft_s=3.0, tpot_s=0.1), partitions=2, declared=2)  # a window of seconds: the polls below share the machine with other tests
     try:
         out = {}
 
@@ -105,16 +105,17 @@ def test_metrics_gauges_and_partitions():
         # through a client of their own: one test client runs its requests one after the other, so a GET behind the slow
         # POST on the same client would only be answered once the request is over
         watcher = TestClient(c.app)
-        seen_running = False
+        seen_running, polls, m, t_start = False, 0, "", time.monotonic()
         deadline = time.monotonic() + 20.0
         while time.monotonic() < deadline and t.is_alive():
             m = watcher.get("/metrics").text
+            polls += 1
             if 'vllm:num_requests_running{engine="0",model_name="sim-model"} 1' in m or 'vllm:num_requests_running{engine="1",model_name="sim-model"} 1' in m:
                 seen_running = True
                 break
             time.sleep(0.01)
         t.join()
-        assert seen_running and out["r"].status_code == 200
+        assert seen_running and out["r"].status_code == 200, (seen_running, polls, time.monotonic() - t_start, out["r"].status_code, out["r"].text[:200], m[-600:])
         idle = ['vllm:num_requests_running{engine="%d",model_name="sim-model"} 0' % i for i in (0, 1)]
         deadline = time.monotonic() + 10.0
         m = c.get("/metrics").text
