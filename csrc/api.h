@@ -72,6 +72,8 @@ int pg_gather_words(const void* src, const void* idx, void* dst, int n, int src_
 int pg_rms_norm(const void* x, void* residual, const void* w, void* y, int rows, int width, float eps, int offset, int round_before,
                 long long ldx, long long ldr, long long ldy, cudaStream_t stream);
 int pg_gated_rms_norm(const void* x, const void* gate, const void* w_f32, void* y, long long rows, int dim, float eps, cudaStream_t stream);
+// act 0: SiLU gate (as above); 1: bf16(norm * w) * bf16(sigmoid(gate))
+int pg_gated_rms_norm_act(const void* x, const void* gate, const void* w_f32, void* y, long long rows, int dim, float eps, int act, cudaStream_t stream);
 int pg_swiglu(const void* gate_up, void* out, int rows, int inter, long long ldin, long long ldout, int interleaved, cudaStream_t stream);
 int pg_sigmoid_gate_mul(void* x, const void* gate, long long n, cudaStream_t stream);
 int pg_qk_norm_rope_append(const void* qkv, long long ld, const void* q_w, const void* k_w, const void* cos, const void* sin,
@@ -155,6 +157,15 @@ int pg_gdn_gates(const void* a, long long lda, const void* b, long long ldb, con
 int pg_gdn_recurrent(const void* q, const void* k, long long ld_qk, const void* v, long long ld_v, const void* g, const void* beta, void* state,
                      void* out, const void* q_indptr, const void* slots, int num_seqs, int hk, int hv, int dk, int dv, int max_q_len,
                      int skip_len, cudaStream_t stream);
+// ---- KDA + attention residuals (kda.cu) ---------------------------------------------
+// Delta rule with one decay per key channel; q, k, v share the row stride ld; f [T, heads * dk] and b [T, heads] are the raw
+// gate projections (the decay and beta arithmetic runs in the kernel); state [slots, heads, dk, dv] f32.
+int pg_kda_recurrent(const void* q, const void* k, const void* v, long long ld, const void* f, long long ldf, const void* b, long long ldb,
+                     const void* a_log, const void* dt_bias, float lower, void* state, void* out, const void* q_indptr, const void* slots,
+                     int num_seqs, int heads, int dk, int dv, cudaStream_t stream);
+// Softmax mix of the first nb snapshot rows of each token (snaps [T, cap, hidden], ld_tok = cap * hidden) and its current row.
+int pg_attnres_mix(const void* cur, long long ld_cur, const void* snaps, long long ld_tok, const void* score_w, void* out, long long ld_out,
+                   int tokens, int nb, int hidden, float eps, cudaStream_t stream);
 // Chunk-wise (64-token) tensor-core form of the same rule for sequences of >= min_len tokens (gdn_chunk.cu).
 int pg_gdn_chunked(const void* q, const void* k, long long ld_qk, const void* v, long long ld_v, const void* g, const void* beta, void* state,
                    void* out, const void* q_indptr, const void* slots, int num_seqs, int hk, int hv, int dk, int dv, int min_len,

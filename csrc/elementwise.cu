@@ -119,8 +119,9 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const bf16* __restrict__ 
 }
 
 // Per (token, head): y = rms_norm(x, w_f32) * silu(gate); one warp per head row.
+// act 0: rms_norm(x) * w * silu(gate), rounded once; act 1: bf16(rms_norm(x) * w) * bf16(sigmoid(gate))
 __global__ void gated_rms_norm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ gate, const float* __restrict__ w, bf16* __restrict__ y,
-                                      long long rows, int dim, float eps) {
+                                      long long rows, int dim, float eps, int act) {
   PG_PDL_ENTRY();
   const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -137,16 +138,21 @@ __global__ void gated_rms_norm_kernel(const bf16* __restrict__ x, const bf16* __
   for (int i = lane; i < dim; i += 32) {
     float v = __bfloat162float(xr[i]);
     float g = __bfloat162float(gr[i]);
+    if (act == 1) {
+      y[row * dim + i] = __float2bfloat16(bf16_round(v * inv * w[i]) * bf16_round(1.f / (1.f + __expf(-g))));
+      continue;
+    }
     float s = g / (1.f + __expf(-g));
     y[row * dim + i] = __float2bfloat16(v * inv * w[i] * s);
   }
 }
 
 // `interleaved` = 0: a row is [gate_0 .. gate_{I-1}, up_0 .. up_{I-1}]; 1: (gate_0, up_0, gate_1, up_1, ...).
-// `flags`: bit 0 = gate / up columns interleaved, bit 1 = tanh GELU instead of SiLU on the gate (GeGLU)
+// `flags`: bit 0 = gate / up columns interleaved, bit 1 = tanh GELU instead of SiLU on the gate (GeGLU), bit 2 = the
+// saturating form 4 tanh(g / 4) sigmoid(g) * 25 tanh(u / 25), rounded once (pegainfer-k3/kernels/tilelang_defs.py:244-262)
 __global__ void swiglu_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int rows, int inter, long long ldin, long long ldout, int flags) {
   PG_PDL_ENTRY();
-  const int interleaved = flags & 1, gelu = flags & 2;
+  const int interleaved = flags & 1, gelu = flags & 2, situ = flags & 4;
   const int nvec = inter / 8;
   const long long total = (long long)rows * nvec;
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
@@ -171,6 +177,10 @@ __global__ void swiglu_kernel(const bf16* __restrict__ gu, bf16* __restrict__ ou
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const float g = gf[j];
+      if (situ) {
+        o[j] = 4.f * tanhf(0.25f * g) / (1.f + __expf(-g)) * (25.f * tanhf(0.04f * uf[j]));
+        continue;
+      }
       const float a = gelu ? 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) : g / (1.f + __expf(-g));
       o[j] = bf16_round(a) * uf[j];
     }
@@ -446,11 +456,16 @@ extern "C" int pg_rms_norm(const void* x, void* residual, const void* w, void* y
   return PG_OK;
 }
 
-extern "C" int pg_gated_rms_norm(const void* x, const void* gate, const void* w_f32, void* y, long long rows, int dim, float eps, cudaStream_t stream) {
+extern "C" int pg_gated_rms_norm_act(const void* x, const void* gate, const void* w_f32, void* y, long long rows, int dim, float eps, int act, cudaStream_t stream) {
+  PG_REQUIRE(act == 0 || act == 1, "gated_rms_norm: gate activation %d (0 = SiLU, 1 = sigmoid)", act);
   if (rows == 0) return PG_OK;
-  PG_CUDA(launch_pdl(gated_rms_norm_kernel, dim3((unsigned)((rows + 3) / 4)), dim3(128), (size_t)(0), stream, (const bf16*)x, (const bf16*)gate, (const float*)w_f32, (bf16*)y, rows, dim, eps));
+  PG_CUDA(launch_pdl(gated_rms_norm_kernel, dim3((unsigned)((rows + 3) / 4)), dim3(128), (size_t)(0), stream, (const bf16*)x, (const bf16*)gate, (const float*)w_f32, (bf16*)y, rows, dim, eps, act));
   PG_LAUNCH_CHECK();
   return PG_OK;
+}
+
+extern "C" int pg_gated_rms_norm(const void* x, const void* gate, const void* w_f32, void* y, long long rows, int dim, float eps, cudaStream_t stream) {
+  return pg_gated_rms_norm_act(x, gate, w_f32, y, rows, dim, eps, 0, stream);
 }
 
 extern "C" int pg_swiglu(const void* gate_up, void* out, int rows, int inter, long long ldin, long long ldout, int interleaved, cudaStream_t stream) {

@@ -20,7 +20,7 @@ from typing import Optional
 
 @dataclass
 class ModelConfig:
-    family: str = "qwen3"  # qwen3 | qwen35 | deepseek_v2 | kimi_k2 | glm_dsa
+    family: str = "qwen3"  # qwen3 | qwen35 | deepseek_v2 | kimi_k2 | glm_dsa | gemma4 | kimi_k3
     vocab_size: int = 1024
     hidden_size: int = 256
     num_layers: int = 2
@@ -62,7 +62,7 @@ class ModelConfig:
     norm_topk_prob: bool = False
     routed_scaling_factor: float = 1.0
     router_bias: bool = False
-    expert_quant: str = "bf16"  # bf16 | int4_g32 | fp8_block128
+    expert_quant: str = "bf16"  # bf16 | int4_g32 | fp8_block128 | mxfp4 (Kimi-K3 checkpoints; dequantised to bf16 when loaded)
     quant_group_size: int = 32
     dense_quant: str = "bf16"  # bf16 | fp8_block128: projections outside the experts stay FP8 and run the FP8 GEMM
     # MTP
@@ -80,7 +80,14 @@ class ModelConfig:
     attention_k_eq_v: bool = False  # global layers have no v_proj: V is the key projection (before key norm and RoPE)
     final_logit_softcapping: float = 0.0
     rope_theta_local: float = 10000.0
-    hidden_act: str = "silu"  # "silu" | "gelu_tanh"
+    hidden_act: str = "silu"  # "silu" | "gelu_tanh" | "situ"
+    # Kimi-K3 line: KDA linear-attention layers ("linear_attention", gdn_head_dim / gdn_conv_kernel give the head and the
+    # short convolution) interleaved with NoPE MLA layers ("full_attention"), routed experts that work in a latent of
+    # latent_moe_dim columns, and the attention-residual stream that snapshots the residual every attn_res_block layers
+    latent_moe_dim: int = 0
+    attn_res_block: int = 0
+    kda_gate_rank: int = 0
+    kda_gate_lower_bound: float = -5.0
 
     # -- derived ---------------------------------------------------------------
     @property
@@ -193,6 +200,24 @@ PRESETS["small-gemma4"] = replace(PRESETS["tiny-gemma4"], vocab_size=4096, hidde
 # KV heads of 256 against 4 global KV heads of 512 (the narrower global layers pack their pages at the front of their slab)
 PRESETS["gemma4-10b-shape"] = replace(PRESETS["small-gemma4"], vocab_size=262144, hidden_size=4096, num_layers=36, layer_types=_gemma_pattern(36), num_q_heads=32, num_kv_heads=16,
                                       num_global_kv_heads=4, intermediate_size=14336, sliding_window=1024, max_position=131072)
+
+
+def _k3_pattern(n: int) -> tuple:
+    """Full (MLA) attention on every fourth layer and on the last one, KDA elsewhere (pegainfer-k3/src/config.rs:108-114)."""
+    return tuple("full_attention" if (i + 1 == n or i % 4 == 3) else "linear_attention" for i in range(n))
+
+
+PRESETS["tiny-k3"] = ModelConfig(family="kimi_k3", vocab_size=1024, hidden_size=256, num_layers=5, layer_types=_k3_pattern(5), num_q_heads=4, num_kv_heads=4, head_dim=48, gdn_head_dim=32,
+                                 gdn_conv_kernel=4, kda_gate_rank=32, intermediate_size=512, qk_norm=False, q_lora_rank=96, kv_lora_rank=64, qk_nope_head_dim=32, qk_rope_head_dim=16,
+                                 v_head_dim=32, n_routed_experts=8, n_shared_experts=2, num_experts_per_tok=3, moe_intermediate_size=64, latent_moe_dim=128, first_k_dense_replace=1,
+                                 scoring_func="sigmoid", norm_topk_prob=True, router_bias=True, attn_res_block=2, hidden_act="situ", rms_eps=1e-5, max_position=4096)
+# head and latent sizes of the released model (KDA heads of 128, MLA 128 + 64 / 128 over a 512-wide latent), few layers and experts
+PRESETS["small-k3"] = replace(PRESETS["tiny-k3"], vocab_size=4096, hidden_size=1024, num_layers=6, layer_types=_k3_pattern(6), num_q_heads=16, num_kv_heads=16, head_dim=192, gdn_head_dim=128,
+                              kda_gate_rank=128, intermediate_size=2048, q_lora_rank=512, kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, n_routed_experts=16,
+                              num_experts_per_tok=4, moe_intermediate_size=256, latent_moe_dim=512, attn_res_block=3, max_position=8192)
+# the released text tower (pegainfer-k3/src/config.rs:26-92): 93 layers, 96 heads, 896 routed experts (top 16) in a 3584-wide latent
+PRESETS["kimi-k3"] = replace(PRESETS["small-k3"], vocab_size=163840, hidden_size=7168, num_layers=93, layer_types=_k3_pattern(93), num_q_heads=96, num_kv_heads=96, intermediate_size=33792,
+                             q_lora_rank=1536, n_routed_experts=896, num_experts_per_tok=16, moe_intermediate_size=3072, latent_moe_dim=3584, attn_res_block=12, max_position=1048576)
 PRESETS["small-glm-fp8"] = replace(PRESETS["small-glm"], expert_quant="fp8_block128", dense_quant="fp8_block128")
 for _name in ("tiny-dsv2", "small-dsv2", "dsv2-lite"):
     if _name in PRESETS:
@@ -219,6 +244,8 @@ def detect_family(cfg: dict) -> str:
         return "glm_dsa"
     if mt.startswith("gemma4") or "Gemma4" in archs:
         return "gemma4"
+    if mt == "kimi_k3" or "KimiK3" in archs or cfg.get("text_config", {}).get("model_type") == "kimi_linear":
+        return "kimi_k3"
     if mt in ("kimi_k2", "deepseek_v3", "kimi_k25") or "DeepseekV3" in archs or "Kimi" in archs:
         return "kimi_k2"
     raise ValueError(f"no model line recognises model_type={mt!r} architectures={archs!r}")
@@ -240,6 +267,30 @@ def _eos_ids(model_dir: Optional[str], cfg: dict) -> tuple:
     return tuple(dict.fromkeys(int(i) for i in ids))
 
 
+def _k3_from_hf(cfg: dict, top: dict, model_dir: Optional[str]) -> ModelConfig:
+    """Text tower of a Kimi-K3 ``config.json`` (keys as pegainfer-k3/src/config.rs:200-330 checks them)."""
+    lin = cfg.get("linear_attn_config", {})
+    n = cfg["num_hidden_layers"]
+    full = lin.get("full_attn_layers")  # one-based in the checkpoint
+    types = tuple("full_attention" if (i + 1) in full else "linear_attention" for i in range(n)) if full else _k3_pattern(n)
+    for key, want in (("hidden_act", "situ"), ("moe_router_activation_func", "sigmoid")):
+        if cfg.get(key, want) != want:
+            raise ValueError(f"Kimi-K3 line: {key}={cfg.get(key)!r} is not supported (expected {want!r})")
+    if not cfg.get("mla_use_nope", True) or not cfg.get("mla_use_output_gate", True):
+        raise ValueError("Kimi-K3 line: MLA layers without positions (mla_use_nope) and with an output gate are the supported form")
+    nope, rope = cfg["qk_nope_head_dim"], cfg["qk_rope_head_dim"]
+    return ModelConfig(family="kimi_k3", vocab_size=cfg["vocab_size"], hidden_size=cfg["hidden_size"], num_layers=n, layer_types=types, num_q_heads=cfg["num_attention_heads"],
+                       num_kv_heads=cfg.get("num_key_value_heads", cfg["num_attention_heads"]), head_dim=nope + rope, gdn_head_dim=lin.get("head_dim", 128),
+                       gdn_conv_kernel=lin.get("short_conv_kernel_size", 4), kda_gate_rank=lin.get("gate_rank", lin.get("head_dim", 128)), kda_gate_lower_bound=float(lin.get("gate_lower_bound", -5.0)),
+                       intermediate_size=cfg["intermediate_size"], qk_norm=False, q_lora_rank=cfg["q_lora_rank"], kv_lora_rank=cfg["kv_lora_rank"], qk_nope_head_dim=nope, qk_rope_head_dim=rope,
+                       v_head_dim=cfg["v_head_dim"], n_routed_experts=cfg["num_experts"], n_shared_experts=cfg.get("num_shared_experts", 0), num_experts_per_tok=cfg["num_experts_per_token"],
+                       moe_intermediate_size=cfg["moe_intermediate_size"], latent_moe_dim=cfg["routed_expert_hidden_size"], first_k_dense_replace=cfg.get("first_k_dense_replace", 1),
+                       scoring_func="sigmoid", norm_topk_prob=bool(cfg.get("moe_renormalize", True)), routed_scaling_factor=float(cfg.get("routed_scaling_factor", 1.0)), router_bias=True,
+                       expert_quant="mxfp4" if "quantization_config" in top or "quantization_config" in cfg else "bf16", attn_res_block=cfg["attn_res_block_size"], hidden_act="situ",
+                       rms_eps=cfg.get("rms_norm_eps", 1e-5), max_position=cfg.get("max_position_embeddings", 4096), tie_word_embeddings=bool(top.get("tie_word_embeddings", False)),
+                       eos_token_ids=_eos_ids(model_dir, top))
+
+
 def from_hf(cfg: dict, model_dir: Optional[str] = None) -> ModelConfig:
     family = detect_family(cfg)
     top = cfg
@@ -249,6 +300,8 @@ def from_hf(cfg: dict, model_dir: Optional[str] = None) -> ModelConfig:
         cfg = cfg["text_config"]
     if family == "gemma4" and "text_config" in cfg:
         cfg = cfg["text_config"]
+    if family == "kimi_k3":
+        return _k3_from_hf(cfg.get("text_config", cfg), top, model_dir)
     common = dict(
         family=family,
         vocab_size=cfg["vocab_size"],

@@ -41,7 +41,13 @@ def _gemma4(cfg, **kw):
     return Gemma4Model(cfg, **kw)
 
 
-BUILDERS = {"gemma4": _gemma4, "glm_dsa": _glm_dsa, "qwen3": _qwen3, "qwen35": _qwen35, "deepseek_v2": _mla_moe, "kimi_k2": _mla_moe}
+def _k3(cfg, **kw):
+    from .k3 import K3Model
+
+    return K3Model(cfg, **kw)
+
+
+BUILDERS = {"kimi_k3": _k3, "gemma4": _gemma4, "glm_dsa": _glm_dsa, "qwen3": _qwen3, "qwen35": _qwen35, "deepseek_v2": _mla_moe, "kimi_k2": _mla_moe}
 
 
 def build(cfg: ModelConfig, **kw):
@@ -60,6 +66,10 @@ def shapes_for(cfg: ModelConfig) -> dict:
         from .gemma4 import gemma4_shapes
 
         return gemma4_shapes(cfg)
+    if cfg.family == "kimi_k3":
+        from .k3 import k3_shapes
+
+        return k3_shapes(cfg)
     raise ValueError(f"no tensor-shape table for family {cfg.family!r}")
 
 
@@ -79,4 +89,16 @@ def hf_config_extras(cfg: ModelConfig) -> dict:
                     hidden_size_per_layer_input=0, vocab_size_per_layer_input=cfg.vocab_size, num_kv_shared_layers=0, enable_moe_block=False, use_double_wide_mlp=False,
                     rope_parameters={"sliding_attention": {"rope_type": "default", "rope_theta": cfg.rope_theta_local},
                                      "full_attention": {"rope_type": "proportional", "partial_rotary_factor": cfg.partial_rotary_factor, "rope_theta": cfg.rope_theta}})
+    if cfg.family == "kimi_k3":
+        full = [i + 1 for i in range(cfg.num_layers) if cfg.layer_type(i) == "full_attention"]  # one-based in the checkpoint
+        text = dict(model_type="kimi_linear", hidden_act="situ", vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size, num_hidden_layers=cfg.num_layers,
+                    first_k_dense_replace=cfg.first_k_dense_replace, max_position_embeddings=cfg.max_position, intermediate_size=cfg.intermediate_size,
+                    moe_intermediate_size=cfg.moe_intermediate_size, routed_expert_hidden_size=cfg.latent_moe_dim, attn_res_block_size=cfg.attn_res_block,
+                    num_attention_heads=cfg.num_q_heads, num_key_value_heads=cfg.num_kv_heads, q_lora_rank=cfg.q_lora_rank, kv_lora_rank=cfg.kv_lora_rank,
+                    qk_nope_head_dim=cfg.qk_nope_head_dim, qk_rope_head_dim=cfg.qk_rope_head_dim, v_head_dim=cfg.v_head_dim, mla_use_nope=True, mla_use_output_gate=True,
+                    num_experts=cfg.n_routed_experts, num_experts_per_token=cfg.num_experts_per_tok, num_shared_experts=cfg.n_shared_experts, num_expert_group=1, topk_group=1,
+                    moe_router_activation_func="sigmoid", moe_renormalize=cfg.norm_topk_prob, routed_scaling_factor=cfg.routed_scaling_factor, rms_norm_eps=cfg.rms_eps,
+                    linear_attn_config=dict(num_heads=cfg.num_q_heads, head_dim=cfg.gdn_head_dim, short_conv_kernel_size=cfg.gdn_conv_kernel, gate_rank=cfg.kda_gate_rank,
+                                            gate_lower_bound=cfg.kda_gate_lower_bound, full_attn_layers=full, use_full_rank_gate=True))
+        return dict(model_type="kimi_k3", architectures=["KimiK3ForConditionalGeneration"], text_config=text)
     return {}

@@ -62,7 +62,9 @@ def add_rms_norm(x, residual, w, eps, offset=False, round_before_norm=True):
     return _impl(x).add_rms_norm(x, residual, w, eps, offset, round_before_norm)
 
 
-def gated_rms_norm(x, gate, w, eps):
+def gated_rms_norm(x, gate, w, eps, act="silu"):
+    if act != "silu":
+        return _impl(x).gated_rms_norm(x, gate, w, eps, act)
     return _impl(x).gated_rms_norm(x, gate, w, eps)
 
 
@@ -135,7 +137,7 @@ def logprobs_topk(logits, picked, k):
 # Load-time and test helpers that are plain tensor arithmetic on whatever device their inputs
 # live on (quantisers, repackers, RoPE tables, the dense-attention oracle): these have no kernel.
 _HOST_UTILS = frozenset(
-    ("rope_tables", "dense_causal_attention", "filtered_probs", "dequant_int4_g32", "quant_int4_g32", "repack_int4_pairs", "unrepack_int4_pairs", "plain_int4", "dequant_fp8_block", "quant_fp8_block")
+    ("rope_tables", "dense_causal_attention", "filtered_probs", "dequant_int4_g32", "quant_int4_g32", "repack_int4_pairs", "unrepack_int4_pairs", "plain_int4", "dequant_fp8_block", "quant_fp8_block", "dequant_mxfp4", "quant_mxfp4")
 )
 
 

@@ -183,7 +183,8 @@ def add_rms_norm(x, residual, w, eps, offset=False, round_before_norm=True):
     return y.view(x.shape)
 
 
-def gated_rms_norm(x, gate, w, eps):
+def gated_rms_norm(x, gate, w, eps, act: str = "silu"):
+    """Per-head ``rms_norm(x) * w * silu(gate)``; ``act="sigmoid"``: ``bf16(rms_norm(x) * w) * bf16(sigmoid(gate))``."""
     _bf16(x)
     x = x.contiguous()
     gate = gate.contiguous()
@@ -191,7 +192,7 @@ def gated_rms_norm(x, gate, w, eps):
     y = torch.empty_like(x)
     rows = x.numel() // x.shape[-1]
     c = ctx(x.device)
-    _check(lib().pg_gated_rms_norm(_ptr(x), _ptr(gate), _ptr(w), _ptr(y), _ll(rows), _ci(x.shape[-1]), _cf(eps), _stream()), c)
+    _check(lib().pg_gated_rms_norm_act(_ptr(x), _ptr(gate), _ptr(w), _ptr(y), _ll(rows), _ci(x.shape[-1]), _cf(eps), _ci({"silu": 0, "sigmoid": 1}[act]), _stream()), c)
     return y
 
 
@@ -214,6 +215,29 @@ def geglu(gate_up):
     out = torch.empty((g2.shape[0], inter), dtype=g2.dtype, device=g2.device)
     _check(lib().pg_swiglu(_ptr(g2), _ptr(out), _ci(g2.shape[0]), _ci(inter), _ll(g2.stride(0)), _ll(out.stride(0)), _ci(2), _stream()), ctx(g2.device))
     return out.view(*gate_up.shape[:-1], inter)
+
+
+def situ(gate_up):
+    """``bf16(4 tanh(g / 4) sigmoid(g) * 25 tanh(u / 25))`` on a fused ``[T, 2 I]`` buffer, gate half first."""
+    _bf16(gate_up)
+    g2 = _rows2d(gate_up)
+    inter = g2.shape[1] // 2
+    out = torch.empty((g2.shape[0], inter), dtype=g2.dtype, device=g2.device)
+    _check(lib().pg_swiglu(_ptr(g2), _ptr(out), _ci(g2.shape[0]), _ci(inter), _ll(g2.stride(0)), _ll(out.stride(0)), _ci(4), _stream()), ctx(g2.device))
+    return out.view(*gate_up.shape[:-1], inter)
+
+
+def attnres_mix(cur, snaps, nb: int, score_w, eps: float):
+    """Softmax mix of each token's first ``nb`` snapshot rows (``snaps`` [T, cap, H]) and its current row ``cur`` [T, H],
+    scored by ``dot(x / rms(x), score_w)`` (``score_w`` f32 [H])."""
+    _bf16(cur)
+    t, h = cur.shape
+    assert snaps.is_contiguous() and snaps.shape[0] == t and snaps.shape[2] == h and nb <= snaps.shape[1] and cur.stride(1) == 1
+    assert score_w.dtype == torch.float32 and score_w.is_contiguous()
+    out = torch.empty((t, h), dtype=cur.dtype, device=cur.device)
+    rc = lib().pg_attnres_mix(_ptr(cur), _ll(cur.stride(0)), _ptr(snaps), _ll(snaps.stride(0)), _ptr(score_w), _ptr(out), _ll(out.stride(0)), _ci(t), _ci(nb), _ci(h), _cf(eps), _stream())
+    _check(rc, ctx(cur.device))
+    return out
 
 
 def softcap(logits, cap: float):
@@ -804,6 +828,23 @@ def gdn_recurrent(q, k, v, g, beta, state, meta: AttnMeta, chunked: Optional[boo
     return out
 
 
+def kda_recurrent(q, k, v, f, b, a_log, dt_bias, lower: float, state, meta: AttnMeta):
+    """Delta rule with one decay per key channel; the decay and beta arithmetic on the raw gate projections ``f`` [T, H * Dk]
+    and ``b`` [T, H] runs inside the kernel.  ``q, k, v`` [T, H, D] share one row stride (slices of the fused convolution
+    output); ``state`` [slots, H, Dk, Dv] f32 is updated in place."""
+    _bf16(q)
+    t, h, dk = q.shape
+    dv = v.shape[2]
+    assert q.stride(2) == 1 and q.stride(1) == dk and k.stride(1) == dk and v.stride(1) == dv and q.stride(0) == k.stride(0) == v.stride(0)
+    assert f.stride(1) == 1 and b.stride(1) == 1 and f.shape[1] == h * dk and b.shape[1] == h
+    assert state.is_contiguous() and state.dtype == torch.float32 and a_log.dtype == torch.float32 and dt_bias.dtype == torch.float32
+    out = torch.empty((t, h, dv), dtype=q.dtype, device=q.device)
+    rc = lib().pg_kda_recurrent(_ptr(q), _ptr(k), _ptr(v), _ll(q.stride(0)), _ptr(f), _ll(f.stride(0)), _ptr(b), _ll(b.stride(0)), _ptr(a_log), _ptr(dt_bias), _cf(lower),
+                                _ptr(state), _ptr(out), _ptr(meta.q_indptr), _ptr(meta.state_slots), _ci(meta.num_seqs), _ci(h), _ci(dk), _ci(dv), _stream())
+    _check(rc, ctx(q.device))
+    return out
+
+
 # ----------------------------------------------------------------------------------
 # mixture of experts
 # ----------------------------------------------------------------------------------
@@ -909,7 +950,7 @@ def grouped_gemm_fp8(xq, x_scale, offsets, w_fp8, w_scale, bn: int = 16):
     return y
 
 
-def _moe_pipeline(x, ids, weights, w13, s13, w2, s2, expert_offset):
+def _moe_pipeline(x, ids, weights, w13, s13, w2, s2, expert_offset, act: str = "swiglu"):
     _bf16(x)
     t, h = x.shape
     k = ids.shape[1]
@@ -920,6 +961,7 @@ def _moe_pipeline(x, ids, weights, w13, s13, w2, s2, expert_offset):
     xs = torch.empty((routes, h), dtype=x.dtype, device=x.device)
     _check(lib().pg_moe_gather(_ptr(x), _ll(x.stride(0)), _ptr(sorted_src), _ptr(offsets), _ci(e_local), _ci(k), _ptr(xs), _ci(h), _ci(routes), _stream()), c)
     bn = _token_tile(routes, e_local)
+    assert act == "swiglu" or quant_code(w13) == 0, "the situ activation is wired for bf16 expert weights"
     if quant_code(w13) == 2 and _MOE_FP8_TC and h % 128 == 0 and w13.shape[1] % 256 == 0 and w2.shape[1] % 128 == 0:
         # both GEMMs on the FP8 tensor-core path: activations quantised per row and 128-wide k group
         xq, xsc = quant_fp8_1x128(xs)
@@ -927,15 +969,15 @@ def _moe_pipeline(x, ids, weights, w13, s13, w2, s2, expert_offset):
         y2 = grouped_gemm_fp8(aq, asc, offsets, w2, s2, bn)
     else:
         y1 = grouped_gemm(xs, offsets, w13, s13, bn)
-        act = swiglu(y1)
-        y2 = grouped_gemm(act, offsets, w2, s2, bn)
+        mid = situ(y1) if act == "situ" else swiglu(y1)
+        y2 = grouped_gemm(mid, offsets, w2, s2, bn)
     out = torch.empty((t, h), dtype=torch.float32, device=x.device)
     _check(lib().pg_moe_combine(_ptr(y2), _ll(y2.stride(0)), _ptr(route_pos), _ptr(weights.contiguous()), _ci(t), _ci(k), _ptr(out), _ci(h), _ci(0), _stream()), c)
     return out
 
 
-def moe_experts(x, ids, weights, w13, w2, expert_offset=0):
-    return _moe_pipeline(x, ids, weights, w13, None, w2, None, expert_offset)
+def moe_experts(x, ids, weights, w13, w2, expert_offset=0, act: str = "swiglu"):
+    return _moe_pipeline(x, ids, weights, w13, None, w2, None, expert_offset, act)
 
 
 def moe_experts_int4(x, ids, weights, w13_packed, w13_scale, w2_packed, w2_scale, expert_offset=0, group=32):

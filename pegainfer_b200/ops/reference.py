@@ -96,12 +96,64 @@ def softcap(logits: torch.Tensor, cap: float) -> torch.Tensor:
     return (torch.tanh(logits.float() / cap) * cap).to(logits.dtype)
 
 
-def gated_rms_norm(x, gate, w, eps):
-    """Per-head ``rms_norm(x, w_f32) * silu(gate)``; x, gate: [T, H, D]."""
+def gated_rms_norm(x, gate, w, eps, act: str = "silu"):
+    """Per-head ``rms_norm(x, w_f32) * silu(gate)``; x, gate: [T, H, D].  ``act="sigmoid"``: the normalised row is
+    rounded to the activation dtype and multiplied by the rounded ``sigmoid(gate)`` (the KDA output gate,
+    pegainfer-k3/kernels/tilelang_defs.py:398-410)."""
     xf = x.float()
     inv = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
     g = gate.float()
+    if act == "sigmoid":
+        return ((xf * inv * w.float()).to(x.dtype).float() * torch.sigmoid(g).to(x.dtype).float()).to(x.dtype)
     return (xf * inv * w.float() * (g * torch.sigmoid(g))).to(x.dtype)
+
+
+def situ(gate_up: torch.Tensor) -> torch.Tensor:
+    """Saturating gated activation on a fused ``[T, 2I]`` buffer (gate half first):
+    ``4 tanh(g / 4) sigmoid(g) * 25 tanh(u / 25)`` in f32, rounded once (pegainfer-k3/kernels/tilelang_defs.py:244-262)."""
+    i = gate_up.shape[-1] // 2
+    g, u = gate_up[..., :i].float(), gate_up[..., i:].float()
+    return (4.0 * torch.tanh(g / 4.0) * torch.sigmoid(g) * (25.0 * torch.tanh(u / 25.0))).to(gate_up.dtype)
+
+
+def attnres_mix(cur, snaps, nb: int, score_w, eps: float):
+    """Attention-residual mix.  ``cur`` [T, H] is each token's current residual row, ``snaps`` [T, cap, H] its snapshot
+    rows (the first ``nb`` are live).  Every candidate (snapshots, then the current row) scores
+    ``dot(x / rms(x), score_w)``; the result is the softmax-weighted sum of the un-normalised candidates
+    (pegainfer-k3/kernels/tilelang_defs.py:67-139)."""
+    cand = torch.cat([snaps[:, :nb].float(), cur.float().unsqueeze(1)], 1)  # [T, nb + 1, H]
+    inv = torch.rsqrt(cand.pow(2).mean(-1) + eps)
+    score = (cand * score_w.float()).sum(-1) * inv
+    p = torch.softmax(score, -1)
+    return (p.unsqueeze(-1) * cand).sum(1).to(cur.dtype)
+
+
+_E2M1 = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+
+
+def dequant_mxfp4(packed, scales, dtype=torch.bfloat16):
+    """MXFP4 to a dense matrix: ``packed`` uint8 [..., K / 2] holds two e2m1 values per byte (low nibble first),
+    ``scales`` uint8 [..., K / 32] one e8m0 exponent per 32 values (value ``2 ** (s - 127)``)."""
+    lut = torch.tensor(_E2M1 + tuple(-v for v in _E2M1), dtype=torch.float32, device=packed.device)
+    b = packed.to(torch.int64)
+    vals = torch.stack([lut[b & 15], lut[(b >> 4) & 15]], -1).reshape(*packed.shape[:-1], packed.shape[-1] * 2)
+    sc = torch.exp2(scales.float() - 127.0).repeat_interleave(32, dim=-1)
+    return (vals * sc).to(dtype)
+
+
+def quant_mxfp4(w):
+    """Round a matrix to MXFP4 (the inverse layout of ``dequant_mxfp4``): per 32 values the e8m0 scale is the power of two
+    that brings the largest magnitude to at most 6, and every value goes to the nearest e2m1 magnitude."""
+    k = w.shape[-1]
+    g = w.float().reshape(*w.shape[:-1], k // 32, 32)
+    amax = g.abs().amax(-1, keepdim=True).clamp_min(2.0 ** -126)
+    e = torch.ceil(torch.log2(amax / 6.0)).clamp(-127, 127)
+    x = g / torch.exp2(e)
+    mags = torch.tensor(_E2M1, dtype=torch.float32, device=w.device)
+    idx = (x.abs().unsqueeze(-1) - mags).abs().argmin(-1)
+    nib = (idx + 8 * (x < 0)).reshape(*w.shape[:-1], k // 2, 2)
+    packed = (nib[..., 0] | (nib[..., 1] << 4)).to(torch.uint8)
+    return packed, (e.squeeze(-1) + 127).to(torch.uint8)
 
 
 def swiglu(gate_up: torch.Tensor, interleaved: bool = False) -> torch.Tensor:
@@ -447,11 +499,11 @@ def dequant_fp8_block(w_fp8, scale_inv, block=128):
     return (w_fp8.float() * s).to(torch.bfloat16)
 
 
-def moe_experts(x, ids, weights, w13, w2, expert_offset=0):
+def moe_experts(x, ids, weights, w13, w2, expert_offset=0, act: str = "swiglu"):
     """Routed experts on local weights.  ``w13`` [E_local, 2I, H] (gate rows then up
     rows), ``w2`` [E_local, H, I].  Tokens routed to experts outside
     [expert_offset, expert_offset + E_local) contribute nothing.  Returns f32 [T, H]
-    (sum over the local selections of weight * expert(x))."""
+    (sum over the local selections of weight * expert(x)).  ``act``: ``swiglu`` or ``situ``."""
     t, h = x.shape
     e_local = w13.shape[0]
     out = torch.zeros(t, h, dtype=torch.float32, device=x.device)
@@ -461,8 +513,8 @@ def moe_experts(x, ids, weights, w13, w2, expert_offset=0):
         if rows.numel() == 0:
             continue
         xe = x[rows]
-        act = swiglu(linear(xe, w13[e]))
-        ye = linear(act, w2[e]).float()
+        mid = situ(linear(xe, w13[e])) if act == "situ" else swiglu(linear(xe, w13[e]))
+        ye = linear(mid, w2[e]).float()
         we = (weights * sel.float()).sum(-1)[rows]
         out.index_add_(0, rows, ye * we.unsqueeze(-1))
     return out
@@ -741,6 +793,37 @@ def gdn_recurrent(q, k, v, g, beta, state, meta: AttnMeta):
             S = S + torch.einsum("hk,hv->hkv", kf[i], delta)
             out[i] = torch.einsum("hkv,hk->hv", S, qf[i]).to(q.dtype)
         state[slots[b]] = S
+    return out
+
+
+def kda_recurrent(q, k, v, f, b, a_log, dt_bias, lower: float, state, meta: AttnMeta):
+    """Token-by-token delta rule with one decay per key channel (Kimi Delta Attention).  ``q, k`` [T, H, Dk] and ``v``
+    [T, H, Dv] after the short convolution, ``f`` [T, H * Dk] the raw forget-gate projection, ``b`` [T, H] the raw beta
+    projection, ``a_log`` [H], ``dt_bias`` [H * Dk], ``state`` [slots, H, Dk, Dv] f32 updated in place.  Per token
+    ``dec = exp(lower * sigmoid(exp(a_log) * (f + dt_bias)))`` scales the state rows, then the delta rule of
+    ``gdn_recurrent`` runs with ``beta = sigmoid(b)`` (pegainfer-k3/kernels/tilelang_defs.py:304-397).  Returns [T, H, Dv]."""
+    t, h, dk = q.shape
+    dv = v.shape[2]
+    qf, kf, vf = q.float(), k.float(), v.float()
+    qf = qf * torch.rsqrt(qf.pow(2).sum(-1, keepdim=True) + 1e-6) * (dk ** -0.5)
+    kf = kf * torch.rsqrt(kf.pow(2).sum(-1, keepdim=True) + 1e-6)
+    raw = f.float().view(t, h, dk) + dt_bias.float().view(h, dk)
+    dec = torch.exp(lower * torch.sigmoid(torch.exp(a_log.float()).view(1, h, 1) * raw))
+    beta = torch.sigmoid(b.float())
+    out = torch.zeros(t, h, dv, dtype=q.dtype, device=q.device)
+    qi = meta.h_q_indptr if meta.h_q_indptr is not None else meta.q_indptr.tolist()
+    slots = meta.h_state_slots if meta.h_state_slots is not None else meta.state_slots.tolist()
+    for s in range(meta.num_seqs):
+        if slots[s] < 0:
+            continue
+        S = state[slots[s]]
+        for i in range(qi[s], qi[s + 1]):
+            S = S * dec[i].unsqueeze(-1)
+            kv = torch.einsum("hkv,hk->hv", S, kf[i])
+            delta = (vf[i] - kv) * beta[i].view(h, 1)
+            S = S + torch.einsum("hk,hv->hkv", kf[i], delta)
+            out[i] = torch.einsum("hkv,hk->hv", S, qf[i]).to(q.dtype)
+        state[slots[s]] = S
     return out
 
 

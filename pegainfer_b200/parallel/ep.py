@@ -26,6 +26,8 @@ def _local_experts(x, ids, wts, experts, cfg):
         return ops.moe_experts_fp8(x, ids, wts, experts["w13_fp8"], experts["w13_scale"], experts["w2_fp8"], experts["w2_scale"], experts["offset"])
     if "w13_packed" in experts:
         return ops.moe_experts_int4(x, ids, wts, experts["w13_packed"], experts["w13_scale"], experts["w2_packed"], experts["w2_scale"], experts["offset"], cfg.quant_group_size)
+    if getattr(cfg, "hidden_act", "silu") == "situ":
+        return ops.moe_experts(x, ids, wts, experts["w13"], experts["w2"], experts["offset"], act="situ")
     return ops.moe_experts(x, ids, wts, experts["w13"], experts["w2"], experts["offset"])
 
 

@@ -61,6 +61,7 @@ LINES = [
     ModelLine("kimi-k2", ("kimi_k2",), frozenset({"ep_backend", "spec_method"})),
     ModelLine("glm-5", ("glm_dsa",), frozenset({"ep_backend", "spec_method"})),
     ModelLine("gemma4", ("gemma4",), frozenset()),
+    ModelLine("kimi-k3", ("kimi_k3",), frozenset({"ep_backend"})),
 ]
 LINES[0].validate = _qwen3_validate  # type: ignore[method-assign]
 

@@ -180,11 +180,17 @@ def test_gemma4_sliding_window_and_wide_global_layers_kernels_vs_library():
     _family_logits_close("small-gemma4", lens=(200, 90, 150))
 
 
+def test_k3_kda_mla_latent_moe_kernels_vs_library():
+    """small-k3: KDA layers (heads of 128, decay per channel), NoPE MLA layers with an output gate, residual snapshots
+    every three layers, latent MoE with the saturating activation; one ragged prefill step against the library path."""
+    _family_logits_close("small-k3", lens=(70, 17, 33))
+
+
 def test_qwen35_hybrid_kernels_vs_library():
     _family_logits_close("small-qwen35")
 
 
-@pytest.mark.parametrize("name", ["small-dsv2", "small-kimi", "small-qwen35", "small-gemma4"])
+@pytest.mark.parametrize("name", ["small-dsv2", "small-kimi", "small-qwen35", "small-gemma4", "small-k3"])
 def test_family_generate_graph_equals_eager(name):
     e1, e2 = _family_engine(name, False), _family_engine(name, True)
     try:

@@ -416,6 +416,59 @@ def test_gated_delta_net_kernels(dk, hk, hv):
     status_clean()
 
 
+@pytest.mark.parametrize("dk,heads", [(128, 5), (32, 4)])
+def test_kda_channel_decay_recurrence(dk, heads):
+    """Delta rule with one decay per key channel (the gate arithmetic runs in the kernel): ragged step of decode rows and
+    prompt chunks, q / k / v as strided slices of one buffer, against the PyTorch recurrence."""
+    torch.manual_seed(dk + heads)
+    q_lens, slots = [1, 19, 5, 1, 40], [3, 1, 4, 2, 5]
+    meta = _state_meta(q_lens, slots)
+    t, inner = meta.num_tokens, heads * dk
+    qkv = torch.randn(t, 3 * inner, device=DEV).bfloat16()
+    q, k, v = (qkv[:, j * inner : (j + 1) * inner].view(t, heads, dk) for j in range(3))
+    f = (torch.randn(t, inner, device=DEV) * 2).bfloat16()
+    small = torch.randn(t, heads + 11, device=DEV).bfloat16()
+    b = small[:, :heads]
+    a_log, dt_bias = torch.randn(heads, device=DEV) * 0.5, torch.randn(inner, device=DEV) * 0.5
+    s1 = torch.randn(7, heads, dk, dk, device=DEV) * 0.1
+    s2 = s1.clone()
+    o1 = cu().kda_recurrent(q, k, v, f, b, a_log, dt_bias, -5.0, s1, meta)
+    o2 = R.kda_recurrent(q, k, v, f, b, a_log, dt_bias, -5.0, s2, meta)
+    bf16_close(o1, o2, rel=2 ** -6, abs_=4e-3)
+    assert (s1 - s2).abs().max().item() < 2e-3 and torch.equal(s1[0], s2[0]) and torch.equal(s1[6], s2[6])  # unused slots untouched
+    status_clean()
+
+
+def test_attnres_mix_situ_and_sigmoid_gated_norm_kernels():
+    torch.manual_seed(5)
+    t, cap, h = 37, 8, 1024
+    cur, snaps = torch.randn(t, h, device=DEV).bfloat16(), torch.randn(t, cap, h, device=DEV).bfloat16()
+    sw = torch.randn(h, device=DEV) * 0.2
+    for nb in (0, 1, 5, 8):
+        bf16_close(cu().attnres_mix(cur, snaps, nb, sw, 1e-5), R.attnres_mix(cur, snaps, nb, sw, 1e-5), rel=2 ** -6, abs_=4e-3)
+    gu = (torch.randn(19, 512, device=DEV) * 6).bfloat16()
+    bf16_close(cu().situ(gu), R.situ(gu), rel=2 ** -6, abs_=4e-3)
+    x, gate = torch.randn(23, 4, 128, device=DEV).bfloat16(), torch.randn(23, 4, 128, device=DEV).bfloat16()
+    w = torch.rand(128, device=DEV) + 0.5
+    bf16_close(cu().gated_rms_norm(x, gate, w, 1e-5, act="sigmoid"), R.gated_rms_norm(x, gate, w, 1e-5, act="sigmoid"), rel=2 ** -6, abs_=4e-3)
+    bf16_close(cu().gated_rms_norm(x, gate, w, 1e-5), R.gated_rms_norm(x, gate, w, 1e-5), rel=2 ** -6, abs_=4e-3)
+    status_clean()
+
+
+def test_moe_experts_with_the_saturating_activation():
+    torch.manual_seed(6)
+    t, h, inter, e, k = 40, 256, 128, 8, 3
+    x = torch.randn(t, h, device=DEV).bfloat16()
+    w13 = (torch.randn(e, 2 * inter, h, device=DEV) * 0.2).bfloat16()
+    w2 = (torch.randn(e, h, inter, device=DEV) * 0.1).bfloat16()
+    ids = torch.stack([torch.randperm(e, device=DEV)[:k] for _ in range(t)]).to(torch.int32)
+    wts = torch.rand(t, k, device=DEV)
+    a = cu().moe_experts(x, ids, wts, w13, w2, 0, act="situ")
+    b = R.moe_experts(x, ids, wts, w13, w2, 0, act="situ")
+    assert (a - b).abs().max().item() < 3e-2 * b.abs().max().item() and not torch.allclose(b, R.moe_experts(x, ids, wts, w13, w2, 0), atol=1e-3)
+    status_clean()
+
+
 @pytest.mark.parametrize("q_lens", [[200, 64, 1, 33, 130, 31], [2048], [65, 127]])
 def test_gated_delta_chunk_scan_matches_recurrence(q_lens):
     """The 64-token chunk-wise tensor-core scan against the token-by-token rule (fp32 PyTorch
