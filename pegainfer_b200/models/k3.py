@@ -120,7 +120,7 @@ def _kind(name: str) -> str:
 
 
 def k3_source(cfg: ModelConfig, seed: int = 0, dtype=torch.bfloat16) -> RandomSource:
-    return RandomSource(k3_shapes(cfg), seed=seed, std=0.05, dtype=dtype, kind=_kind)
+    return RandomSource(k3_shapes(cfg), seed=seed, dtype=dtype, kind=_kind)
 
 
 @dataclass
