@@ -6,7 +6,7 @@ distinct weight / KV buffers (larger than L2 in total, so every launch streams f
 HBM), replayed after warm-up and timed with CUDA events.  Fractions are against the
 measured peaks in MEASURED_PEAKS.json (copy bandwidth, cuBLAS bf16 throughput).
 
-    python bench_ops.py [--only gemm|attn|small|gdn|moe|mla] [--iters 16] [--json out.json]
+    python bench_ops.py [--only gemm|attn|small|gdn|kda|moe|mla] [--iters 16] [--json out.json]
     python bench_ops.py --single gemm:64x4096x4096      # one op, few launches (ncu target)
 
 Plays the role of the reference's kernel/op report binaries
@@ -172,6 +172,34 @@ def gdn_cases(iters, only=None):
         if max(q_lens) >= 64:  # the row above ran the chunk-wise scan; this one the token-by-token kernel
             ms = time_graph(lambda i: K.gdn_recurrent(q, k, v, g, beta, states[i], meta, chunked=False), 3, max(2, iters // 4))
             rows.append((f"  recurrence kernel {name}", ms, state_bytes + t * (2 * hk * dk + 2 * hv * dv) * 2, 4.0 * t * hv * dk * dv * 2))
+    return rows
+
+
+def kda_cases(iters, only=None):
+    """KDA recurrence (decay per key channel, gate arithmetic in the kernel) and the attention-residual mix at the Kimi-K3
+    shape: 96 heads with a 128x128 f32 state, hidden 7168, 8 snapshots."""
+    from pegainfer_b200.ops import cuda as K
+
+    rows = []
+    heads, d, hidden = 96, 128, 7168
+    inner = heads * d
+    for name, q_lens in only or (("decode bs32", [1] * 32), ("decode bs64", [1] * 64), ("prefill 1x2048", [2048])):
+        meta, _ = _meta_for(q_lens, q_lens, 16)
+        meta.state_slots = torch.arange(len(q_lens), dtype=torch.int32, device=DEV)
+        t = sum(q_lens)
+        qkv = torch.randn(t, 3 * inner, device=DEV).bfloat16()
+        q, k, v = (qkv[:, j * inner : (j + 1) * inner].view(t, heads, d) for j in range(3))
+        f, b = torch.randn(t, inner, device=DEV).bfloat16(), torch.randn(t, heads, device=DEV).bfloat16()
+        a_log, dt = torch.zeros(heads, device=DEV), torch.zeros(inner, device=DEV)
+        states = [torch.zeros(len(q_lens), heads, d, d, device=DEV) for _ in range(3)]
+        ms = time_graph(lambda i: K.kda_recurrent(q, k, v, f, b, a_log, dt, -5.0, states[i], meta), 3, max(2, iters // 4))
+        rows.append((f"kda_recurrent {name} 96h 128x128", ms, len(q_lens) * heads * d * d * 4 * 2 + t * 5 * inner * 2, 4.0 * t * heads * d * d * 2))
+    for t, nb in ((64, 8), (4096, 8)):
+        cur = [torch.randn(t, hidden, device=DEV).bfloat16() for _ in range(3)]
+        snaps = [torch.randn(t, 8, hidden, device=DEV).bfloat16() for _ in range(3)]
+        sw = torch.randn(hidden, device=DEV)
+        ms = time_graph(lambda i: K.attnres_mix(cur[i], snaps[i], nb, sw, 1e-5), 3, iters)
+        rows.append((f"attnres_mix {t}x{hidden} {nb} snapshots", ms, t * hidden * 2 * (nb + 2), 0))
     return rows
 
 
@@ -519,6 +547,8 @@ def main():
             rows.extend(small_cases(args.iters))
         if args.only in (None, "gdn"):
             rows.extend(gdn_cases(args.iters))
+        if args.only in (None, "kda"):
+            rows.extend(kda_cases(args.iters))
         if args.only in (None, "moe"):
             rows.extend(moe_cases(args.iters))
         if args.only in (None, "mla"):

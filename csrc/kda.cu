@@ -42,6 +42,9 @@ __global__ void __launch_bounds__(128) kda_recurrent_kernel(const bf16* __restri
   const int qtr = tid & 3, lc = tid >> 2, col = cg * KDA_COLS + lc;
   const bool owner = col < dv;
   float* S = state + (((long long)slot * heads + h) * DK) * dv;  // [DK][dv], v contiguous
+  // A thread's own elements sit DK / 4 rows apart, so a warp reads 32-byte pieces of four rows.  Staging the CTA's slice
+  // through shared memory (whole 128-byte rows in global memory) was measured slower: 200 us against 111 us for 32 decode
+  // rows of 96 heads, the extra 17 KB per CTA costs more resident CTAs than the wider rows gain.
   float s_col[QK];
 #pragma unroll
   for (int i = 0; i < QK; ++i) s_col[i] = owner ? S[(long long)(qtr * QK + i) * dv + col] : 0.f;

@@ -218,6 +218,9 @@ PRESETS["small-k3"] = replace(PRESETS["tiny-k3"], vocab_size=4096, hidden_size=1
 # the released text tower (pegainfer-k3/src/config.rs:26-92): 93 layers, 96 heads, 896 routed experts (top 16) in a 3584-wide latent
 PRESETS["kimi-k3"] = replace(PRESETS["small-k3"], vocab_size=163840, hidden_size=7168, num_layers=93, layer_types=_k3_pattern(93), num_q_heads=96, num_kv_heads=96, intermediate_size=33792,
                              q_lora_rank=1536, n_routed_experts=896, num_experts_per_tok=16, moe_intermediate_size=3072, latent_moe_dim=3584, attn_res_block=12, max_position=1048576)
+# a one-GPU slice of the released shape for benchmarks (not a released configuration): full-width layers (6 KDA + 2 MLA, one dense
+# and seven latent-MoE layers), 32 routed experts instead of 896, top 8
+PRESETS["k3-8layer-shape"] = replace(PRESETS["kimi-k3"], num_layers=8, layer_types=_k3_pattern(8), n_routed_experts=32, num_experts_per_tok=8, attn_res_block=4, max_position=131072)
 PRESETS["small-glm-fp8"] = replace(PRESETS["small-glm"], expert_quant="fp8_block128", dense_quant="fp8_block128")
 for _name in ("tiny-dsv2", "small-dsv2", "dsv2-lite"):
     if _name in PRESETS:
