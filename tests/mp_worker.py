@@ -37,8 +37,8 @@ def main():
     control = dist.group.WORLD
     g = torch.Generator().manual_seed(11)
     prompts = [torch.randint(0, 1024, (18 + 5 * i,), generator=g).tolist() for i in range(4)]
-    if mode == "dp_ep":
-        name, tp, ep = "tiny-dsv2", None, EPContext(rank, world, group=control, comm="nccl", tokens="dp")
+    if mode in ("dp_ep", "dp_ep_k3"):
+        name, tp, ep = ("tiny-dsv2" if mode == "dp_ep" else "tiny-k3"), None, EPContext(rank, world, group=control, comm="nccl", tokens="dp")
     else:
         name, tp, ep = "tiny-qwen3", TPContext(rank, world, group=control, comm="nccl"), None
     ecfg = EngineConfig(preset=name, kv_page_size=16, num_kv_blocks=128, cuda_graph=False, max_prefill_tokens=32)

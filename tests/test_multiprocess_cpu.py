@@ -50,6 +50,14 @@ def test_dp_attention_ep_experts_two_ranks_match_single_process(tmp_path):
     assert res["tokens"] == single_process_tokens("tiny-dsv2")
 
 
+def test_k3_latent_experts_over_two_expert_parallel_ranks_match_single_process(tmp_path):
+    """The Kimi-K3 line with its routed experts split over two ranks (tokens gathered, local experts with the saturating
+    activation in the latent, outputs reduced): same tokens as one process that owns every expert."""
+    res = run_workers("dp_ep_k3", tmp_path)
+    assert res["terminals"] == ["finished"] * 4
+    assert res["tokens"] == single_process_tokens("tiny-k3")
+
+
 def test_lost_rank_fails_open_requests_instead_of_hanging(tmp_path):
     res = run_workers("rank_loss", tmp_path)
     assert all(t == "failed" for t in res["terminals"]), res
