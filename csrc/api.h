@@ -162,7 +162,7 @@ int pg_gdn_recurrent(const void* q, const void* k, long long ld_qk, const void* 
 // gate projections (the decay and beta arithmetic runs in the kernel); state [slots, heads, dk, dv] f32.
 int pg_kda_recurrent(const void* q, const void* k, const void* v, long long ld, const void* f, long long ldf, const void* b, long long ldb,
                      const void* a_log, const void* dt_bias, float lower, void* state, void* out, const void* q_indptr, const void* slots,
-                     int num_seqs, int heads, int dk, int dv, cudaStream_t stream);
+                     int num_seqs, int heads, int dk, int dv, int max_q_len, cudaStream_t stream);
 // Softmax mix of the first nb snapshot rows of each token (snaps [T, cap, hidden], ld_tok = cap * hidden) and its current row.
 int pg_attnres_mix(const void* cur, long long ld_cur, const void* snaps, long long ld_tok, const void* score_w, void* out, long long ld_out,
                    int tokens, int nb, int hidden, float eps, cudaStream_t stream);

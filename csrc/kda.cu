@@ -23,7 +23,11 @@ namespace {
 constexpr int KDA_STAGE = 8;
 constexpr int KDA_COLS = 32;
 
-template <int DK>
+// XW = false: four adjacent lanes share a state column and reduce with shuffles (prompt chunks: no barrier per token).
+// XW = true: a warp owns one quarter of Dk for all 32 columns, so every state load and store of a warp is one 128-byte row
+// and the shared-memory reads of k, q and the decays are broadcasts; the four quarters meet through shared memory with two
+// barriers per token (decode rows and other steps of a few tokens).
+template <int DK, bool XW>
 __global__ void __launch_bounds__(128) kda_recurrent_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v, long long ld,
                                                              const bf16* __restrict__ f, long long ldf, const bf16* __restrict__ b, long long ldb,
                                                              const float* __restrict__ a_log, const float* __restrict__ dt_bias, float lower,
@@ -34,17 +38,18 @@ __global__ void __launch_bounds__(128) kda_recurrent_kernel(const bf16* __restri
   constexpr int QL = DK / 32;  // elements per lane when a warp holds one token
   __shared__ __align__(16) float sq[KDA_STAGE][4 * QS], sk[KDA_STAGE][4 * QS], sd[KDA_STAGE][4 * QS];
   __shared__ float sv[KDA_STAGE][KDA_COLS], sb[KDA_STAGE];
+  __shared__ float red_kv[4][KDA_COLS], red_o[4][KDA_COLS];
   const int h = blockIdx.x / col_groups, cg = blockIdx.x % col_groups, seq = blockIdx.y;
   const int slot = slots[seq];
   const int q0 = q_indptr[seq], q1 = q_indptr[seq + 1];
   if (q1 == q0 || slot < 0) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int qtr = tid & 3, lc = tid >> 2, col = cg * KDA_COLS + lc;
+  const int qtr = XW ? warp : (tid & 3), lc = XW ? lane : (tid >> 2), col = cg * KDA_COLS + lc;
   const bool owner = col < dv;
   float* S = state + (((long long)slot * heads + h) * DK) * dv;  // [DK][dv], v contiguous
-  // A thread's own elements sit DK / 4 rows apart, so a warp reads 32-byte pieces of four rows.  Staging the CTA's slice
-  // through shared memory (whole 128-byte rows in global memory) was measured slower: 200 us against 111 us for 32 decode
-  // rows of 96 heads, the extra 17 KB per CTA costs more resident CTAs than the wider rows gain.
+  // Shuffle mapping: a thread's own elements sit DK / 4 rows apart, so a warp reads 32-byte pieces of four rows.  Staging
+  // the CTA's slice through shared memory instead was measured slower (200 us against 111 us for 32 decode rows of 96
+  // heads: the extra 17 KB per CTA costs resident CTAs); the XW mapping reads whole rows without it (86 us).
   float s_col[QK];
 #pragma unroll
   for (int i = 0; i < QK; ++i) s_col[i] = owner ? S[(long long)(qtr * QK + i) * dv + col] : 0.f;
@@ -103,8 +108,14 @@ __global__ void __launch_bounds__(128) kda_recurrent_kernel(const bf16* __restri
         kv4.w += s_col[4 * i + 3] * kk.w;
       }
       float kv = (kv4.x + kv4.y) + (kv4.z + kv4.w);
-      kv += __shfl_xor_sync(0xffffffffu, kv, 1);
-      kv += __shfl_xor_sync(0xffffffffu, kv, 2);
+      if (XW) {
+        red_kv[qtr][lc] = kv;
+        __syncthreads();
+        kv = (red_kv[0][lc] + red_kv[1][lc]) + (red_kv[2][lc] + red_kv[3][lc]);
+      } else {
+        kv += __shfl_xor_sync(0xffffffffu, kv, 1);
+        kv += __shfl_xor_sync(0xffffffffu, kv, 2);
+      }
       const float delta = (sv[j][lc] - kv) * sb[j];
       float4 o4 = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
@@ -120,8 +131,14 @@ __global__ void __launch_bounds__(128) kda_recurrent_kernel(const bf16* __restri
         o4.w += s_col[4 * i + 3] * qv.w;
       }
       float o = (o4.x + o4.y) + (o4.z + o4.w);
-      o += __shfl_xor_sync(0xffffffffu, o, 1);
-      o += __shfl_xor_sync(0xffffffffu, o, 2);
+      if (XW) {
+        red_o[qtr][lc] = o;
+        __syncthreads();  // also orders this token's reads of red_kv before the next token's writes
+        o = (red_o[0][lc] + red_o[1][lc]) + (red_o[2][lc] + red_o[3][lc]);
+      } else {
+        o += __shfl_xor_sync(0xffffffffu, o, 1);
+        o += __shfl_xor_sync(0xffffffffu, o, 2);
+      }
       if (owner && qtr == 0) out[((long long)(t0 + j) * heads + h) * dv + col] = __float2bfloat16(o);
     }
     __syncthreads();
@@ -191,15 +208,22 @@ __global__ void __launch_bounds__(256) attnres_mix_kernel(const bf16* __restrict
 
 extern "C" int pg_kda_recurrent(const void* q, const void* k, const void* v, long long ld, const void* f, long long ldf, const void* b, long long ldb,
                                 const void* a_log, const void* dt_bias, float lower, void* state, void* out, const void* q_indptr, const void* slots,
-                                int num_seqs, int heads, int dk, int dv, cudaStream_t stream) {
+                                int num_seqs, int heads, int dk, int dv, int max_q_len, cudaStream_t stream) {
   PG_REQUIRE(dv <= 128 && lower < 0.f, "kda_recurrent: dv=%d must be <= 128 and the decay lower bound %f negative", dv, (double)lower);
   if (num_seqs == 0) return PG_OK;
   const int col_groups = (dv + KDA_COLS - 1) / KDA_COLS;
   dim3 grid(heads * col_groups, num_seqs);
-#define PG_KDA_LAUNCH(DKV)                                                                                                                          \
-  kda_recurrent_kernel<DKV><<<grid, 128, 0, stream>>>((const bf16*)q, (const bf16*)k, (const bf16*)v, ld, (const bf16*)f, ldf, (const bf16*)b, ldb, \
-                                                      (const float*)a_log, (const float*)dt_bias, lower, (float*)state, (bf16*)out,                 \
-                                                      (const int*)q_indptr, (const int*)slots, heads, dv, col_groups)
+  const bool few = max_q_len <= 4;  // decode rows and verify steps: the row-coalesced mapping
+#define PG_KDA_ARGS                                                                                                                              \
+  (const bf16*)q, (const bf16*)k, (const bf16*)v, ld, (const bf16*)f, ldf, (const bf16*)b, ldb, (const float*)a_log, (const float*)dt_bias, lower, \
+      (float*)state, (bf16*)out, (const int*)q_indptr, (const int*)slots, heads, dv, col_groups
+#define PG_KDA_LAUNCH(DKV)                                                     \
+  do {                                                                         \
+    if (few)                                                                   \
+      kda_recurrent_kernel<DKV, true><<<grid, 128, 0, stream>>>(PG_KDA_ARGS);  \
+    else                                                                       \
+      kda_recurrent_kernel<DKV, false><<<grid, 128, 0, stream>>>(PG_KDA_ARGS); \
+  } while (0)
   if (dk == 128)
     PG_KDA_LAUNCH(128);
   else if (dk == 64)
@@ -211,6 +235,7 @@ extern "C" int pg_kda_recurrent(const void* q, const void* k, const void* v, lon
     return PG_ERR_UNSUPPORTED;
   }
 #undef PG_KDA_LAUNCH
+#undef PG_KDA_ARGS
   PG_LAUNCH_CHECK();
   return PG_OK;
 }

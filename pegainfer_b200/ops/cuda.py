@@ -840,7 +840,7 @@ def kda_recurrent(q, k, v, f, b, a_log, dt_bias, lower: float, state, meta: Attn
     assert state.is_contiguous() and state.dtype == torch.float32 and a_log.dtype == torch.float32 and dt_bias.dtype == torch.float32
     out = torch.empty((t, h, dv), dtype=q.dtype, device=q.device)
     rc = lib().pg_kda_recurrent(_ptr(q), _ptr(k), _ptr(v), _ll(q.stride(0)), _ptr(f), _ll(f.stride(0)), _ptr(b), _ll(b.stride(0)), _ptr(a_log), _ptr(dt_bias), _cf(lower),
-                                _ptr(state), _ptr(out), _ptr(meta.q_indptr), _ptr(meta.state_slots), _ci(meta.num_seqs), _ci(h), _ci(dk), _ci(dv), _stream())
+                                _ptr(state), _ptr(out), _ptr(meta.q_indptr), _ptr(meta.state_slots), _ci(meta.num_seqs), _ci(h), _ci(dk), _ci(dv), _ci(int(meta.max_q_len)), _stream())
     _check(rc, ctx(q.device))
     return out
 

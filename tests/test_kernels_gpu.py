@@ -416,12 +416,14 @@ def test_gated_delta_net_kernels(dk, hk, hv):
     status_clean()
 
 
+@pytest.mark.parametrize("q_lens", [[1, 19, 5, 1, 40], [1, 3, 1, 4, 2]])
 @pytest.mark.parametrize("dk,heads", [(128, 5), (32, 4)])
-def test_kda_channel_decay_recurrence(dk, heads):
+def test_kda_channel_decay_recurrence(dk, heads, q_lens):
     """Delta rule with one decay per key channel (the gate arithmetic runs in the kernel): ragged step of decode rows and
-    prompt chunks, q / k / v as strided slices of one buffer, against the PyTorch recurrence."""
+    prompt chunks (the shuffle mapping) and a step of at most four tokens per sequence (the row-coalesced mapping of decode
+    and verify steps), q / k / v as strided slices of one buffer, against the PyTorch recurrence."""
     torch.manual_seed(dk + heads)
-    q_lens, slots = [1, 19, 5, 1, 40], [3, 1, 4, 2, 5]
+    slots = [3, 1, 4, 2, 5]
     meta = _state_meta(q_lens, slots)
     t, inner = meta.num_tokens, heads * dk
     qkv = torch.randn(t, 3 * inner, device=DEV).bfloat16()
