@@ -76,7 +76,10 @@ constexpr int GDN_COLS = 32;  // state columns per CTA (4 threads per column)
 // 16 tokens.  The kernel is bound by FMA issue (3 x Dk x Dv multiply-adds per token and head
 // on the CUDA cores): measured variants with two columns per thread and fp16 staging moved
 // shared-memory traffic down 4x without changing the time.
-template <int DK, bool PIPE>
+// XW (steps of at most four tokens per sequence: decode and verify rows): a warp owns one quarter of Dk for all 32 columns
+// of the CTA, so each of its state loads and stores is one 128-byte row and its shared-memory reads of k and q are
+// broadcasts; the four quarters meet through shared memory with two barriers per token instead of two shuffles.
+template <int DK, bool PIPE, bool XW>
 __global__ void __launch_bounds__(128) gdn_recurrent_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, long long ld_qk,
                                                              const bf16* __restrict__ v, long long ld_v, const float* __restrict__ g,
                                                              const float* __restrict__ beta, float* __restrict__ state, bf16* __restrict__ out,
@@ -85,10 +88,13 @@ __global__ void __launch_bounds__(128) gdn_recurrent_kernel(const bf16* __restri
   constexpr int QK = DK / 4;    // state elements per thread
   constexpr int QS = QK + 4;    // padded quarter stride in shared memory: the four quarters land in different banks
   constexpr int QL = DK / 32;   // q / k elements per lane when a warp holds one token
-  constexpr int TPW = TOK_STAGE / 4;  // tokens per warp and stage
-  constexpr int VPT = TOK_STAGE * GDN_COLS / 128;
-  __shared__ __align__(16) float sq[2][TOK_STAGE][4 * QS], sk[2][TOK_STAGE][4 * QS];
-  __shared__ float sv[2][TOK_STAGE][GDN_COLS], sg[2][TOK_STAGE], sb[2][TOK_STAGE];
+  constexpr int ST = XW ? 4 : TOK_STAGE;  // tokens per stage: short steps keep shared memory small, so more CTAs stay resident
+  constexpr int NBUF = PIPE ? 2 : 1;      // only the prefetching variant needs a second stage buffer
+  constexpr int TPW = ST / 4;             // tokens per warp and stage
+  constexpr int VPT = ST * GDN_COLS / 128;
+  __shared__ __align__(16) float sq[NBUF][ST][4 * QS], sk[NBUF][ST][4 * QS];
+  __shared__ float sv[NBUF][ST][GDN_COLS], sg[NBUF][ST], sb[NBUF][ST];
+  __shared__ float red_kv[4][GDN_COLS], red_o[4][GDN_COLS];
   const int h = blockIdx.x / col_groups, cg = blockIdx.x % col_groups, b = blockIdx.y;
   const int slot = slots[b];
   const int q0 = q_indptr[b], q1 = q_indptr[b + 1];
@@ -96,7 +102,7 @@ __global__ void __launch_bounds__(128) gdn_recurrent_kernel(const bf16* __restri
   if (skip_len > 0 && q1 - q0 >= skip_len) return;  // long sequences belong to the chunk-wise kernel
   const int kh = h / (hv / hk);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int qtr = tid & 3, lc = tid >> 2, col = cg * GDN_COLS + lc;
+  const int qtr = XW ? warp : (tid & 3), lc = XW ? lane : (tid >> 2), col = cg * GDN_COLS + lc;
   const bool owner = col < dv;
   float* S = state + (((long long)slot * hv + h) * DK) * dv;  // [DK][dv], v contiguous
   float s_col[QK];
@@ -178,8 +184,14 @@ __global__ void __launch_bounds__(128) gdn_recurrent_kernel(const bf16* __restri
         kv4.w += s_col[4 * i + 3] * kk.w;
       }
       float kv = (kv4.x + kv4.y) + (kv4.z + kv4.w);
-      kv += __shfl_xor_sync(0xffffffffu, kv, 1);
-      kv += __shfl_xor_sync(0xffffffffu, kv, 2);
+      if (XW) {
+        red_kv[qtr][lc] = kv;
+        __syncthreads();
+        kv = (red_kv[0][lc] + red_kv[1][lc]) + (red_kv[2][lc] + red_kv[3][lc]);
+      } else {
+        kv += __shfl_xor_sync(0xffffffffu, kv, 1);
+        kv += __shfl_xor_sync(0xffffffffu, kv, 2);
+      }
       const float delta = (sv[buf][j][lc] - kv) * sb[buf][j];
       float4 o4 = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
@@ -195,29 +207,35 @@ __global__ void __launch_bounds__(128) gdn_recurrent_kernel(const bf16* __restri
         o4.w += s_col[4 * i + 3] * qv.w;
       }
       float o = (o4.x + o4.y) + (o4.z + o4.w);
-      o += __shfl_xor_sync(0xffffffffu, o, 1);
-      o += __shfl_xor_sync(0xffffffffu, o, 2);
+      if (XW) {
+        red_o[qtr][lc] = o;
+        __syncthreads();  // also orders this token's reads of red_kv before the next token's writes
+        o = (red_o[0][lc] + red_o[1][lc]) + (red_o[2][lc] + red_o[3][lc]);
+      } else {
+        o += __shfl_xor_sync(0xffffffffu, o, 1);
+        o += __shfl_xor_sync(0xffffffffu, o, 2);
+      }
       if (owner && qtr == 0) out[((long long)(t0 + j) * hv + h) * dv + col] = __float2bfloat16(o);
     }
   };
 
   if (PIPE) {
-    fetch(q0, min(TOK_STAGE, q1 - q0));
-    commit(0, min(TOK_STAGE, q1 - q0));
+    fetch(q0, min(ST, q1 - q0));
+    commit(0, min(ST, q1 - q0));
     __syncthreads();
     int buf = 0;
-    for (int t0 = q0; t0 < q1; t0 += TOK_STAGE, buf ^= 1) {
-      const int nt = min(TOK_STAGE, q1 - t0);
-      const int nnext = min(TOK_STAGE, q1 - (t0 + TOK_STAGE));
-      if (nnext > 0) fetch(t0 + TOK_STAGE, nnext);
+    for (int t0 = q0; t0 < q1; t0 += ST, buf ^= 1) {
+      const int nt = min(ST, q1 - t0);
+      const int nnext = min(ST, q1 - (t0 + ST));
+      if (nnext > 0) fetch(t0 + ST, nnext);
       process(buf, t0, nt);
       if (nnext > 0) commit(buf ^ 1, nnext);
       __syncthreads();
     }
   } else {
     // decode and other short steps: no prefetch registers, more CTAs per SM for the state stream
-    for (int t0 = q0; t0 < q1; t0 += TOK_STAGE) {
-      const int nt = min(TOK_STAGE, q1 - t0);
+    for (int t0 = q0; t0 < q1; t0 += ST) {
+      const int nt = min(ST, q1 - t0);
       fetch(t0, nt);
       commit(0, nt);
       __syncthreads();
@@ -263,16 +281,18 @@ extern "C" int pg_gdn_recurrent(const void* q, const void* k, long long ld_qk, c
   if (num_seqs == 0) return PG_OK;
   const int col_groups = (dv + GDN_COLS - 1) / GDN_COLS;
   dim3 grid(hv * col_groups, num_seqs);
-#define PG_GDN_LAUNCH(DKV)                                                                                                                  \
-  do {                                                                                                                                      \
-    if (long_steps)                                                                                                                         \
-      gdn_recurrent_kernel<DKV, true><<<grid, 128, 0, stream>>>((const bf16*)q, (const bf16*)k, ld_qk, (const bf16*)v, ld_v, (const float*)g, \
-                                                                (const float*)beta, (float*)state, (bf16*)out, (const int*)q_indptr,        \
-                                                                (const int*)slots, hk, hv, dv, col_groups, skip_len);                        \
-    else                                                                                                                                    \
-      gdn_recurrent_kernel<DKV, false><<<grid, 128, 0, stream>>>((const bf16*)q, (const bf16*)k, ld_qk, (const bf16*)v, ld_v, (const float*)g, \
-                                                                 (const float*)beta, (float*)state, (bf16*)out, (const int*)q_indptr,       \
-                                                                 (const int*)slots, hk, hv, dv, col_groups, skip_len);                       \
+  const bool few = max_q_len <= 4;  // decode and verify rows: the row-coalesced mapping
+#define PG_GDN_ARGS                                                                                                                       \
+  (const bf16*)q, (const bf16*)k, ld_qk, (const bf16*)v, ld_v, (const float*)g, (const float*)beta, (float*)state, (bf16*)out,           \
+      (const int*)q_indptr, (const int*)slots, hk, hv, dv, col_groups, skip_len
+#define PG_GDN_LAUNCH(DKV)                                                               \
+  do {                                                                                   \
+    if (long_steps)                                                                      \
+      gdn_recurrent_kernel<DKV, true, false><<<grid, 128, 0, stream>>>(PG_GDN_ARGS);     \
+    else if (few)                                                                        \
+      gdn_recurrent_kernel<DKV, false, true><<<grid, 128, 0, stream>>>(PG_GDN_ARGS);     \
+    else                                                                                 \
+      gdn_recurrent_kernel<DKV, false, false><<<grid, 128, 0, stream>>>(PG_GDN_ARGS);    \
   } while (0)
   if (dk == 128)
     PG_GDN_LAUNCH(128);
@@ -285,6 +305,7 @@ extern "C" int pg_gdn_recurrent(const void* q, const void* k, long long ld_qk, c
     return PG_ERR_UNSUPPORTED;
   }
 #undef PG_GDN_LAUNCH
+#undef PG_GDN_ARGS
   PG_LAUNCH_CHECK();
   return PG_OK;
 }

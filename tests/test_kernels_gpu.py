@@ -381,11 +381,12 @@ def _state_meta(q_lens, slots):
     return meta
 
 
+@pytest.mark.parametrize("q_lens", [[1, 19, 5, 1], [1, 3, 1, 4], [1, 1, 1, 1]])  # pipelined prompt path; row-coalesced mapping of short steps; decode
 @pytest.mark.parametrize("dk,hk,hv", [(128, 2, 6), (32, 2, 4)])
-def test_gated_delta_net_kernels(dk, hk, hv):
+def test_gated_delta_net_kernels(dk, hk, hv, q_lens):
     torch.manual_seed(dk)
     dv = dk
-    q_lens, slots = [1, 19, 5, 1], [3, 1, 4, 2]
+    slots = [3, 1, 4, 2]
     meta = _state_meta(q_lens, slots)
     t = meta.num_tokens
     ch = 2 * hk * dk + hv * dv
