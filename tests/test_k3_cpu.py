@@ -149,8 +149,32 @@ def test_k3_mxfp4_experts_load_like_their_dequantised_values():
     assert not torch.equal(a.layers[2].experts["w13"], plain.layers[2].experts["w13"])  # the quantiser did something
 
 
-def test_k3_generates_through_the_engine_with_two_expert_ranks_worth_of_experts():
+def test_k3_generation_through_the_engine_is_deterministic():
     ps = prompts_for(3, 19, seed=5)
     one, _ = gen("tiny-k3", ps, 6)
     again, _ = gen("tiny-k3", ps, 6)
     assert one == again and all(len(t) == 6 for t in one)
+
+
+def test_k3_checkpoint_directory_round_trip(tmp_path):
+    """Write the tiny model as a Hugging Face style directory (wrapper config with a text_config, sharded safetensors with
+    the text-tower prefix), load it back through the config probe and the safetensors source: same tokens as the preset."""
+    from pegainfer_b200.config import EngineConfig, load_model_config
+    from pegainfer_b200.engine.build import build_engine
+    from pegainfer_b200.engine.contract import SamplingParams
+    from pegainfer_b200.loader.export import export_checkpoint
+
+    cfg = preset("tiny-k3")
+    export_checkpoint(cfg, str(tmp_path), seed=0, dtype=torch.float32)
+    back = load_model_config(str(tmp_path))
+    assert back.family == "kimi_k3" and back.layer_types == cfg.layer_types and back.latent_moe_dim == cfg.latent_moe_dim
+    prompt = [list(range(3, 30))]
+    outs = []
+    for ecfg, mcfg in ((EngineConfig(model_path=str(tmp_path), kv_page_size=16, num_kv_blocks=64, cuda_graph=False), back),
+                       (EngineConfig(preset="tiny-k3", kv_page_size=16, num_kv_blocks=64, cuda_graph=False), cfg)):
+        eng = build_engine(ecfg, mcfg, device="cpu", dtype=torch.float32)
+        try:
+            outs.append(eng.generate(prompt, SamplingParams(temperature=0.0, ignore_eos=True), max_tokens=5, timeout=120)[0][0])
+        finally:
+            eng.shutdown()
+    assert outs[0] == outs[1]
